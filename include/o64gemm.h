@@ -1,0 +1,215 @@
+/*
+ * o64gemm.h — C ABI of libo64gemm.so, a B200 (sm_100a) dense GEMM / fused-linear engine
+ * that sits behind the matrix-multiply boundary of the Open64 compiler's runtime.
+ *
+ * Two layers:
+ *
+ *   compat layer  — the symbols the reference's own callers already bind:
+ *       sgemm_        the BLAS hook resolved by dlsym when F90_MATMUL_BLAS is set
+ *                     (osprey/libfi/matrix/mmx_dlutil.c:75-136, called as
+ *                     ('n','n',m,n,k,alpha,A,m,B,k,beta,R,m), mmx_fort.h:94-95)
+ *       _s4gemmx__    the strided "X interface" kernel behind _MATMUL_S4S4
+ *                     (osprey/libfi/matrix/s4gemmx.f:37-199, template xgemmx.h:156-236,
+ *                     call site matmul_s4s4.c:107-109)
+ *       _s4gemvx__    its matrix-vector sibling (osprey/libfi/matrix/s4gemvx.f,
+ *                     call sites matmul_s4s4.c:91-101)
+ *     Fortran ABI: every scalar by reference, synchronous, void.  Host or device
+ *     pointers are accepted (host operands are staged through device memory).
+ *
+ *   native layer  — o64_* functions: device pointers (host pointers are staged when
+ *     detected), asynchronous on the caller's CUDA stream, int status returned, never
+ *     abort.  These are what host code lowered from a tiled loop nest calls.
+ *
+ * Error codes mirror the runtime's abort codes (osprey/libfi/matrix/matmul.h:217,258,
+ * 333-369; osprey/clibinc/liberrno.h:326,442-443): FESCIRNK -> O64_ERR_RANK,
+ * FESCICNF -> O64_ERR_CONFORM, FENOMEMY -> O64_ERR_NOMEM.
+ *
+ * No C++ or torch types cross this boundary.  cudaStream_t is passed as void*.
+ */
+#ifndef O64GEMM_H
+#define O64GEMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct o64_handle_s *o64_handle_t;
+
+/* ---- status codes ------------------------------------------------------------------- */
+enum {
+    O64_OK = 0,
+    O64_ERR_RANK = -1,    /* illegal rank / bad argument          (FESCIRNK) */
+    O64_ERR_CONFORM = -2, /* operands not conformable             (FESCICNF) */
+    O64_ERR_NOMEM = -3,   /* allocation failed                    (FENOMEMY) */
+    O64_ERR_ALIGN = -4,   /* pointer or leading dimension not 16-byte aligned */
+    O64_ERR_DTYPE = -5,   /* unsupported element type / layout combination */
+    O64_ERR_TIMEOUT = -6, /* a bounded device-side wait ran out (read by o64_last_status) */
+    O64_ERR_CUDA = -7,    /* a CUDA runtime or driver call failed */
+    O64_ERR_NCCL = -8     /* an NCCL call failed or no communicator is bound */
+};
+
+/* ---- epilogue vocabulary --------------------------------------------------------------
+ * The elementwise tail of a fused linear: what OPR_MAX and the exp/tanh intrinsics express
+ * in the reference's IR (osprey/be/cg/x8664/expand.cxx:4517,
+ * osprey/common/com/intrn_entry.def:915,1346). */
+enum {
+    O64_ACT_NONE = 0,
+    O64_ACT_RELU = 1,
+    O64_ACT_GELU_TANH = 2,
+    O64_ACT_GELU_ERF = 3,
+    O64_ACT_SILU = 4
+};
+
+typedef struct {
+    const float *bias; /* [N] fp32, device pointer, may be NULL */
+    int act;           /* O64_ACT_* */
+} o64_epilogue_t;
+
+/* ---- element kinds (plan queries, naive reference kernels) ---------------------------- */
+enum {
+    O64_KIND_F32 = 0,  /* fp32 SIMT */
+    O64_KIND_BF16 = 1, /* bf16 x bf16 -> fp32 accumulate */
+    O64_KIND_FP8 = 2,  /* e4m3 x e4m3 -> fp32 accumulate */
+    O64_KIND_S8 = 3    /* s8 x s8 -> s32 accumulate */
+};
+
+/* ---- the tile plan ----------------------------------------------------------------------
+ * Carries the vocabulary of the reference's tile decision (LOOP_MODEL results,
+ * osprey/be/lno/model.h:57-118, handed on as SNL_TILE_INFO, osprey/be/lno/snl_utils.h:388)
+ * onto the B200 memory hierarchy:
+ *   Block_Number (register tile)      -> mma_m x mma_n x mma_k of one tensor-core instruction
+ *   Stripsz at level 1 (L1 block)     -> tile_m x tile_n x tile_k staged in shared memory
+ *   number of in-flight L1 blocks     -> stages of the shared-memory ring
+ *   Stripsz at level 2 (L2 block)     -> group_m: rows of tiles rasterised together in L2
+ *   New_Order (loop permutation)      -> raster: 0 = tiles walk M fastest inside a group,
+ *                                                1 = N fastest
+ * cta_group = 1 or 2 CTAs cooperating on one accumulator tile. */
+typedef struct {
+    int kind;      /* O64_KIND_* */
+    int tile_m;    /* rows of C per CTA tile (per CTA pair when cta_group == 2) */
+    int tile_n;    /* accumulator columns per tile */
+    int tile_k;    /* K elements per shared-memory stage */
+    int stages;    /* depth of the TMA -> MMA ring */
+    int cta_group; /* 1 or 2 */
+    int group_m;   /* L2 rasterisation group, in tiles */
+    int raster;    /* 0 = M fastest, 1 = N fastest */
+    int mma_m, mma_n, mma_k;
+    int num_ctas;        /* persistent grid size */
+    int split_k;         /* K slices reduced through scratch memory (1 = none) */
+    double predicted_ms; /* model estimate, compare with the measured time */
+} o64_plan_t;
+
+/* ---- handle ------------------------------------------------------------------------- */
+/* A handle is bound to one device and is not thread-safe; distinct handles are independent.
+ * It owns the device status word, staging buffers for host operands and the NCCL
+ * communicator (if one is bound). */
+int o64_create(o64_handle_t *out, int device);
+int o64_destroy(o64_handle_t h);
+/* Synchronises `stream`, reads and clears the device status word: O64_OK or
+ * O64_ERR_TIMEOUT.  `detail`, if not NULL, receives the raw word (which wait gave up). */
+int o64_last_status(o64_handle_t h, void *stream, int *detail);
+const char *o64_status_string(int status);
+const char *o64_version(void);
+
+/* Plan query / override.  o64_plan_get fills the plan the engine would use for this shape.
+ * o64_plan_set pins fields for later calls of `kind` (fields set to 0 stay automatic);
+ * plan == NULL clears the override.  The environment variable O64_LNO
+ * ("blocking_size=128x256x64:stages=4:cta_group=1:group_m=8", after the reference's
+ * -LNO:blocking_size / pragma BLOCKING SIZE vocabulary, osprey/common/com/config_lno.cxx:128-129,
+ * osprey/common/com/wn_pragmas.h:143-151) does the same for every handle. */
+int o64_plan_get(o64_handle_t h, int kind, int64_t M, int64_t N, int64_t K, o64_plan_t *plan);
+int o64_plan_set(o64_handle_t h, int kind, const o64_plan_t *plan);
+
+/* ---- native layer -------------------------------------------------------------------
+ * Row-major operands; ld* in elements.  A is [M,K].  B is [K,N] when transB == 0 and
+ * [N,K] when transB != 0.  `stream` is a cudaStream_t (NULL = default stream). */
+
+/* Y = act(A*B + bias), fp32, B [K,N].  Replaces the loop nest the compiler builds for
+ * MATMUL plus its elementwise tail (osprey/be/vho/f90_lower.cxx:5116-5178). */
+int o64_linear_f32(o64_handle_t h, int64_t M, int64_t N, int64_t K, const float *A, int64_t lda,
+                   const float *B, int64_t ldb, const float *bias, float *Y, int64_t ldy, int act,
+                   void *stream);
+
+/* C = act(A*op(B) + bias): bf16 operands, fp32 accumulate, bf16 result.  Same nest on a
+ * 16-bit element type the reference's IR lacks (osprey/common/com/mtypes.h:81-143). */
+int o64_gemm_bf16(o64_handle_t h, int64_t M, int64_t N, int64_t K, const void *A, int64_t lda,
+                  const void *B, int64_t ldb, int transB, void *C, int64_t ldc,
+                  const o64_epilogue_t *epi, void *stream);
+
+/* H = silu(X*Wg) (.) (X*Wu): X [M,K], Wg and Wu [K,N] (ldw), H [M,N], all bf16; both
+ * products accumulate side by side and the SiLU-multiply runs in the epilogue. */
+int o64_gemm_bf16_swiglu(o64_handle_t h, int64_t M, int64_t N, int64_t K, const void *X,
+                         int64_t ldx, const void *Wg, const void *Wu, int64_t ldw, void *H,
+                         int64_t ldh, void *stream);
+
+/* C = bf16( (A8*B8^T) * scaleA[m] * scaleB[n] + bias[n] ): e4m3 operands, A8 [M,K], B8 [N,K],
+ * fp32 accumulate.  scaleA, scaleB, bias are fp32 device vectors and may be NULL. */
+int o64_gemm_fp8_scaled(o64_handle_t h, int64_t M, int64_t N, int64_t K, const void *A8,
+                        int64_t lda, const void *B8, int64_t ldb, const float *scaleA,
+                        const float *scaleB, const float *bias, void *C, int64_t ldc,
+                        void *stream);
+
+/* C = A*B^T: int8 operands, A [M,K], B [N,K], int32 accumulate and result, exact.  The
+ * reference's integer kernels are instances of the same template
+ * (osprey/libfi/matrix/i1i4gemmx.f; front-end table osprey/crayf90/fe90/intrin.h:4276-4303). */
+int o64_gemm_s8s8_s32(o64_handle_t h, int64_t M, int64_t N, int64_t K, const int8_t *A,
+                      int64_t lda, const int8_t *B, int64_t ldb, int32_t *C, int64_t ldc,
+                      void *stream);
+
+/* One-thread-per-output reference kernels: an independent device implementation of the same
+ * contracts, used to compare full matrices where a CPU check would take minutes.
+ * out_f32: fp32 result [M,N] (s32 for O64_KIND_S8).  For O64_KIND_FP8 the scales and bias
+ * apply; for the others `bias`/`act` apply and the scales must be NULL. */
+int o64_naive_gemm(o64_handle_t h, int kind, int64_t M, int64_t N, int64_t K, const void *A,
+                   int64_t lda, const void *B, int64_t ldb, int transB, const float *scaleA,
+                   const float *scaleB, const float *bias, int act, void *out, int64_t ldo,
+                   void *stream);
+
+/* ---- multi-GPU: output columns sharded over the ranks of one node ----------------------
+ * Rank r of g owns B[r*N/g : (r+1)*N/g, :] and produces C[:, r*N/g : (r+1)*N/g]; no
+ * reduction.  The only exchange is an all-gather of the column slabs when every rank wants
+ * the whole C. */
+#define O64_UNIQUE_ID_BYTES 128
+/* Rank 0 creates the id, the caller distributes the bytes, every rank calls o64_comm_init. */
+int o64_comm_unique_id(void *id_bytes);
+int o64_comm_init(o64_handle_t h, const void *id_bytes, int rank, int nranks);
+int o64_comm_destroy(o64_handle_t h);
+
+enum {
+    O64_GATHER_NONE = 0,      /* write only this rank's slab into C_full[:, r*N/g ...] */
+    O64_GATHER_ROWMAJOR = 1,  /* all-gather, then permute into row-major C_full [M,N] */
+    O64_GATHER_SLABS = 2      /* all-gather only: C_full is [g][M][N/g] (slab-major) */
+};
+/* A [M,K] replicated, B_slab [N/g,K] local, C_full [M,N] int32 (ldc = N) on every rank.
+ * workspace: device scratch of at least o64_gemm_s8_sharded_workspace(...) bytes, or NULL to
+ * let the handle grow its own. */
+size_t o64_gemm_s8_sharded_workspace(int64_t M, int64_t N, int nranks, int gather);
+int o64_gemm_s8_sharded(o64_handle_t h, int64_t M, int64_t N, int64_t K, const int8_t *A,
+                        int64_t lda, const int8_t *B_slab, int64_t ldb, int32_t *C_full,
+                        int gather, void *workspace, void *stream);
+
+/* ---- compat layer (Fortran ABI) -------------------------------------------------------- */
+/* Column-major BLAS sgemm: C = alpha*op(A)*op(B) + beta*C. */
+void sgemm_(const char *transa, const char *transb, const int *m, const int *n, const int *k,
+            const float *alpha, const float *a, const int *lda, const float *b, const int *ldb,
+            const float *beta, float *c, const int *ldc);
+/* C = alpha*A*B + beta*C, element (i,j) of X at X[inc1x*i + inc2x*j]; quick returns and the
+ * skip of zero B(l,j) follow osprey/libfi/matrix/xgemmx.h:172-236. */
+void _s4gemmx__(const int *m, const int *n, const int *k, const float *alpha, const float *a,
+                const int *inc1a, const int *inc2a, const float *b, const int *inc1b,
+                const int *inc2b, const float *beta, float *c, const int *inc1c,
+                const int *inc2c);
+/* y = alpha*A*x + beta*y (osprey/libfi/matrix/s4gemvx.f). */
+void _s4gemvx__(const int *m, const int *n, const float *alpha, const float *a,
+                const int *incca, const int *incra, const float *x, const int *incx,
+                const float *beta, float *y, const int *incy);
+/* Status of the last compat call on this thread (the Fortran entry points return void). */
+int o64_compat_last_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* O64GEMM_H */

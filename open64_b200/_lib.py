@@ -1,0 +1,103 @@
+"""Loads libo64gemm.so (built in-tree by ``open64_b200.build``) and declares its C ABI.
+
+There is no fallback: if the library is missing the import fails with instructions, and every
+compute call needs a B200.  Prototypes follow ``include/o64gemm.h``.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libo64gemm.so")
+
+OK = 0
+ERR_RANK, ERR_CONFORM, ERR_NOMEM, ERR_ALIGN, ERR_DTYPE, ERR_TIMEOUT, ERR_CUDA, ERR_NCCL = range(-1, -9, -1)
+ACT_NONE, ACT_RELU, ACT_GELU_TANH, ACT_GELU_ERF, ACT_SILU = range(5)
+KIND_F32, KIND_BF16, KIND_FP8, KIND_S8 = range(4)
+GATHER_NONE, GATHER_ROWMAJOR, GATHER_SLABS = range(3)
+UNIQUE_ID_BYTES = 128
+
+# every symbol include/o64gemm.h declares
+EXPORTS = [
+    "o64_create", "o64_destroy", "o64_last_status", "o64_status_string", "o64_version",
+    "o64_plan_get", "o64_plan_set", "o64_linear_f32", "o64_gemm_bf16", "o64_gemm_bf16_swiglu",
+    "o64_gemm_fp8_scaled", "o64_gemm_s8s8_s32", "o64_naive_gemm", "o64_comm_unique_id",
+    "o64_comm_init", "o64_comm_destroy", "o64_gemm_s8_sharded_workspace", "o64_gemm_s8_sharded",
+    "sgemm_", "_s4gemmx__", "_s4gemvx__", "o64_compat_last_status",
+]
+
+
+class Plan(ctypes.Structure):
+    _fields_ = [
+        ("kind", ctypes.c_int), ("tile_m", ctypes.c_int), ("tile_n", ctypes.c_int),
+        ("tile_k", ctypes.c_int), ("stages", ctypes.c_int), ("cta_group", ctypes.c_int),
+        ("group_m", ctypes.c_int), ("raster", ctypes.c_int), ("mma_m", ctypes.c_int),
+        ("mma_n", ctypes.c_int), ("mma_k", ctypes.c_int), ("num_ctas", ctypes.c_int),
+        ("split_k", ctypes.c_int), ("predicted_ms", ctypes.c_double),
+    ]
+
+    def as_dict(self):
+        return {n: getattr(self, n) for n, _ in self._fields_}
+
+
+class Epilogue(ctypes.Structure):
+    _fields_ = [("bias", ctypes.c_void_p), ("act", ctypes.c_int)]
+
+
+class O64Error(RuntimeError):
+    def __init__(self, status, where=""):
+        self.status = status
+        msg = lib().o64_status_string(status).decode()
+        super().__init__(f"{where}: {msg} ({status})" if where else f"{msg} ({status})")
+
+
+_lib = None
+
+
+def lib():
+    """The loaded library.  Raises if it has not been built: there is no other code path."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m open64_b200.build` "
+            "(nvcc, sm_100a).  open64_b200 has no CPU or eager fallback.")
+    L = ctypes.CDLL(LIB_PATH)
+    vp, i64, ci, cf = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float
+    pi, pf = ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_float)
+    L.o64_create.argtypes = [ctypes.POINTER(vp), ci]
+    L.o64_destroy.argtypes = [vp]
+    L.o64_last_status.argtypes = [vp, vp, pi]
+    L.o64_status_string.argtypes = [ci]
+    L.o64_status_string.restype = ctypes.c_char_p
+    L.o64_version.restype = ctypes.c_char_p
+    L.o64_plan_get.argtypes = [vp, ci, i64, i64, i64, ctypes.POINTER(Plan)]
+    L.o64_plan_set.argtypes = [vp, ci, ctypes.POINTER(Plan)]
+    L.o64_linear_f32.argtypes = [vp, i64, i64, i64, vp, i64, vp, i64, vp, vp, i64, ci, vp]
+    L.o64_gemm_bf16.argtypes = [vp, i64, i64, i64, vp, i64, vp, i64, ci, vp, i64,
+                                ctypes.POINTER(Epilogue), vp]
+    L.o64_gemm_bf16_swiglu.argtypes = [vp, i64, i64, i64, vp, i64, vp, vp, i64, vp, i64, vp]
+    L.o64_gemm_fp8_scaled.argtypes = [vp, i64, i64, i64, vp, i64, vp, i64, vp, vp, vp, vp, i64, vp]
+    L.o64_gemm_s8s8_s32.argtypes = [vp, i64, i64, i64, vp, i64, vp, i64, vp, i64, vp]
+    L.o64_naive_gemm.argtypes = [vp, ci, i64, i64, i64, vp, i64, vp, i64, ci, vp, vp, vp, ci, vp,
+                                 i64, vp]
+    L.o64_comm_unique_id.argtypes = [vp]
+    L.o64_comm_init.argtypes = [vp, vp, ci, ci]
+    L.o64_comm_destroy.argtypes = [vp]
+    L.o64_gemm_s8_sharded_workspace.argtypes = [i64, i64, ci, ci]
+    L.o64_gemm_s8_sharded_workspace.restype = ctypes.c_size_t
+    L.o64_gemm_s8_sharded.argtypes = [vp, i64, i64, i64, vp, i64, vp, i64, vp, ci, vp, vp]
+    L.sgemm_.argtypes = [ctypes.c_char_p, ctypes.c_char_p, pi, pi, pi, pf, vp, pi, vp, pi, pf, vp, pi]
+    L.sgemm_.restype = None
+    L._s4gemmx__.argtypes = [pi, pi, pi, pf, vp, pi, pi, vp, pi, pi, pf, vp, pi, pi]
+    L._s4gemmx__.restype = None
+    L._s4gemvx__.argtypes = [pi, pi, pf, vp, pi, pi, vp, pi, pf, vp, pi]
+    L._s4gemvx__.restype = None
+    L.o64_compat_last_status.restype = ci
+    _lib = L
+    return L
+
+
+def check(status, where=""):
+    if status != OK:
+        raise O64Error(status, where)

@@ -1,0 +1,76 @@
+"""Builds libo64gemm.so in-tree with nvcc for sm_100a (cross-compiles without a GPU).
+
+Usage:  python -m open64_b200.build [--force] [--verbose]
+"""
+import os
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+OUT = os.path.join(HERE, "libo64gemm.so")
+OBJ_DIR = os.path.join(HERE, "build")
+
+SOURCES = ["api.cu", "umma_gemm.cu", "simt_kernels.cu", "plan.cpp"]
+HEADERS = ["ptx_sm100.cuh", "umma_gemm.cuh", "simt_kernels.cuh", "../../include/o64gemm.h"]
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "-Xptxas", "-v",
+]
+
+
+def _nvcc():
+    cand = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
+    return cand if os.path.exists(cand) else "nvcc"
+
+
+def _sources():
+    return [s for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
+
+
+def _stale(target, deps):
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
+
+
+def build(force=False, verbose=False):
+    """Compile every source to an object (in parallel) and link the shared library."""
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    hdrs = [os.path.join(CSRC, h) for h in HEADERS] + [os.path.abspath(__file__)]
+    jobs = []
+    objs = []
+    for s in _sources():
+        src = os.path.join(CSRC, s)
+        obj = os.path.join(OBJ_DIR, os.path.splitext(s)[0] + ".o")
+        objs.append(obj)
+        if force or _stale(obj, [src] + hdrs):
+            jobs.append([_nvcc(), *NVCC_FLAGS, "-x", "cu", "-c", src, "-o", obj])
+
+    def run(cmd):
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        return cmd, r
+
+    logs = []
+    with ThreadPoolExecutor(max_workers=4) as ex:
+        for cmd, r in ex.map(run, jobs):
+            logs.append(r.stderr)
+            if verbose:
+                sys.stderr.write(" ".join(cmd) + "\n" + r.stderr)
+            if r.returncode != 0:
+                raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + r.stdout + r.stderr)
+    if jobs or force or _stale(OUT, objs):
+        cmd = [_nvcc(), "-shared", "-o", OUT, *objs, "-ldl", "-Xcompiler", "-fPIC"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("link failed:\n" + r.stdout + r.stderr)
+    with open(os.path.join(OBJ_DIR, "ptxas.log"), "a") as f:
+        f.write("".join(logs))
+    return OUT
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -1,0 +1,628 @@
+// The C ABI of libo64gemm.so (include/o64gemm.h): handle management, argument checking in the
+// manner of the reference runtime's _premult (osprey/libfi/matrix/matmul.h:135-400, errors as
+// return codes instead of aborts), staging of host operands, the compat entry points and the
+// column-sharded int8 GEMM with its all-gather.
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+
+#include "../../include/o64gemm.h"
+#include "simt_kernels.cuh"
+#include "umma_gemm.cuh"
+
+using namespace o64;
+
+// ---- NCCL, bound at run time --------------------------------------------------------------
+// The library is resolved with dlopen so that libo64gemm.so loads (and its symbols can be
+// listed) on hosts without NCCL or without a GPU.  Prototypes follow nccl.h.
+typedef struct ncclComm *ncclComm_t;
+typedef struct { char internal[128]; } ncclUniqueId_;
+struct NcclApi {
+    void *lib = nullptr;
+    int (*GetUniqueId)(ncclUniqueId_ *) = nullptr;
+    int (*CommInitRank)(ncclComm_t *, int, ncclUniqueId_, int) = nullptr;
+    int (*CommDestroy)(ncclComm_t) = nullptr;
+    int (*AllGather)(const void *, void *, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    const char *(*GetErrorString)(int) = nullptr;
+    bool ok = false;
+};
+static const int kNcclInt32 = 2;
+
+static NcclApi &nccl() {
+    static NcclApi api;
+    static bool tried = false;
+    if (tried) return api;
+    tried = true;
+    const char *names[] = {getenv("O64_NCCL_LIB"), "libnccl.so.2", "libnccl.so"};
+    for (const char *n : names) {
+        if (!n || !*n) continue;
+        api.lib = dlopen(n, RTLD_NOW | RTLD_NOLOAD);  // prefer the copy the process already has
+        if (!api.lib) api.lib = dlopen(n, RTLD_NOW);
+        if (api.lib) break;
+    }
+    if (!api.lib) return api;
+    api.GetUniqueId = (int (*)(ncclUniqueId_ *))dlsym(api.lib, "ncclGetUniqueId");
+    api.CommInitRank = (int (*)(ncclComm_t *, int, ncclUniqueId_, int))dlsym(api.lib, "ncclCommInitRank");
+    api.CommDestroy = (int (*)(ncclComm_t))dlsym(api.lib, "ncclCommDestroy");
+    api.AllGather = (int (*)(const void *, void *, size_t, int, ncclComm_t, cudaStream_t))dlsym(
+        api.lib, "ncclAllGather");
+    api.GetErrorString = (const char *(*)(int))dlsym(api.lib, "ncclGetErrorString");
+    api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllGather;
+    return api;
+}
+
+// ---- handle ---------------------------------------------------------------------------------
+static const int kSlots = 6;
+struct o64_handle_s {
+    int device = 0;
+    int num_sms = 148;
+    int *status_word = nullptr;
+    o64_plan_t pins[4];
+    bool has_pin[4] = {false, false, false, false};
+    void *stage[kSlots] = {nullptr};
+    size_t stage_cap[kSlots] = {0};
+    void *ws = nullptr;
+    size_t ws_cap = 0;
+    ncclComm_t comm = nullptr;
+    int rank = 0, nranks = 1;
+};
+
+#define CUDA_TRY(x)                          \
+    do {                                     \
+        if ((x) != cudaSuccess) {            \
+            (void)cudaGetLastError();        \
+            return O64_ERR_CUDA;             \
+        }                                    \
+    } while (0)
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok;
+    explicit DeviceGuard(int dev) {
+        ok = cudaGetDevice(&prev) == cudaSuccess;
+        if (ok && prev != dev) ok = cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+extern "C" const char *o64_version(void) { return "o64gemm 0.1 (sm_100a)"; }
+
+extern "C" const char *o64_status_string(int s) {
+    switch (s) {
+    case O64_OK: return "ok";
+    case O64_ERR_RANK: return "illegal rank or argument";
+    case O64_ERR_CONFORM: return "operands not conformable";
+    case O64_ERR_NOMEM: return "out of memory";
+    case O64_ERR_ALIGN: return "operand not 16-byte aligned";
+    case O64_ERR_DTYPE: return "unsupported element type or layout";
+    case O64_ERR_TIMEOUT: return "device-side wait timed out";
+    case O64_ERR_CUDA: return "CUDA call failed";
+    case O64_ERR_NCCL: return "NCCL call failed or no communicator";
+    default: return "unknown status";
+    }
+}
+
+extern "C" int o64_create(o64_handle_t *out, int device) {
+    if (!out) return O64_ERR_RANK;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) {
+        (void)cudaGetLastError();
+        return O64_ERR_CUDA;
+    }
+    DeviceGuard g(device);
+    if (!g.ok) return O64_ERR_CUDA;
+    cudaDeviceProp prop;
+    CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) return O64_ERR_DTYPE;  // the kernels are sm_100a only
+    o64_handle_s *h = new (std::nothrow) o64_handle_s();
+    if (!h) return O64_ERR_NOMEM;
+    h->device = device;
+    h->num_sms = prop.multiProcessorCount;
+    memset(h->pins, 0, sizeof(h->pins));
+    if (cudaMalloc(&h->status_word, sizeof(int)) != cudaSuccess) {
+        delete h;
+        return O64_ERR_NOMEM;
+    }
+    cudaMemset(h->status_word, 0, sizeof(int));
+    *out = h;
+    return O64_OK;
+}
+
+extern "C" int o64_comm_destroy(o64_handle_t h) {
+    if (!h) return O64_ERR_RANK;
+    if (h->comm) {
+        if (nccl().ok) nccl().CommDestroy(h->comm);
+        h->comm = nullptr;
+    }
+    h->rank = 0;
+    h->nranks = 1;
+    return O64_OK;
+}
+
+extern "C" int o64_destroy(o64_handle_t h) {
+    if (!h) return O64_ERR_RANK;
+    DeviceGuard g(h->device);
+    o64_comm_destroy(h);
+    for (int i = 0; i < kSlots; ++i)
+        if (h->stage[i]) cudaFree(h->stage[i]);
+    if (h->ws) cudaFree(h->ws);
+    if (h->status_word) cudaFree(h->status_word);
+    delete h;
+    return O64_OK;
+}
+
+extern "C" int o64_last_status(o64_handle_t h, void *stream, int *detail) {
+    if (!h) return O64_ERR_RANK;
+    DeviceGuard g(h->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    int word = 0;
+    CUDA_TRY(cudaMemcpyAsync(&word, h->status_word, sizeof(int), cudaMemcpyDeviceToHost, s));
+    CUDA_TRY(cudaStreamSynchronize(s));
+    if (detail) *detail = word;
+    if (word != 0) {
+        CUDA_TRY(cudaMemsetAsync(h->status_word, 0, sizeof(int), s));
+        return O64_ERR_TIMEOUT;
+    }
+    return O64_OK;
+}
+
+extern "C" int o64_plan_set(o64_handle_t h, int kind, const o64_plan_t *plan) {
+    if (!h || kind < 0 || kind > 3) return O64_ERR_RANK;
+    if (!plan) {
+        h->has_pin[kind] = false;
+        return O64_OK;
+    }
+    if (plan->tile_m && plan->tile_m != 128) return O64_ERR_RANK;
+    if (plan->tile_n && plan->tile_n != 128 && plan->tile_n != 256) return O64_ERR_RANK;
+    if (plan->cta_group && plan->cta_group != 1) return O64_ERR_RANK;
+    if (plan->group_m < 0 || plan->num_ctas < 0) return O64_ERR_RANK;
+    h->pins[kind] = *plan;
+    h->has_pin[kind] = true;
+    return O64_OK;
+}
+
+static void choose(o64_handle_t h, int kind, int epi, int64_t M, int64_t N, int64_t K, o64_plan_t *out) {
+    plan_choose(kind, epi, M, N, K, h->num_sms, h->has_pin[kind] ? &h->pins[kind] : nullptr, out);
+}
+
+extern "C" int o64_plan_get(o64_handle_t h, int kind, int64_t M, int64_t N, int64_t K, o64_plan_t *plan) {
+    if (!h || !plan || kind < 0 || kind > 3) return O64_ERR_RANK;
+    if (M <= 0 || N <= 0 || K <= 0) return O64_ERR_RANK;
+    if (kind == O64_KIND_F32) {
+        memset(plan, 0, sizeof(*plan));
+        plan->kind = kind;
+        const bool big = ((M + 63) / 64) * ((N + 63) / 64) >= 2LL * h->num_sms;
+        plan->tile_m = plan->tile_n = big ? 64 : 32;
+        plan->tile_k = 16;
+        plan->stages = 1;
+        plan->cta_group = 1;
+        plan->mma_m = plan->mma_n = big ? 4 : 2;
+        plan->mma_k = 1;
+        plan->split_k = 1;
+        plan->num_ctas = (int)(((M + plan->tile_m - 1) / plan->tile_m) * ((N + plan->tile_n - 1) / plan->tile_n));
+        return O64_OK;
+    }
+    choose(h, kind, EPI_BF16, M, N, K, plan);
+    return O64_OK;
+}
+
+// ---- host-operand staging ---------------------------------------------------------------------
+static bool is_host_ptr(const void *p) {
+    if (!p) return false;
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return true;
+    }
+    return a.type == cudaMemoryTypeHost || a.type == cudaMemoryTypeUnregistered;
+}
+
+static int reserve(void **buf, size_t *cap, size_t bytes) {
+    if (bytes <= *cap) return O64_OK;
+    if (*buf) cudaFree(*buf);
+    *buf = nullptr;
+    *cap = 0;
+    if (cudaMalloc(buf, bytes) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return O64_ERR_NOMEM;
+    }
+    *cap = bytes;
+    return O64_OK;
+}
+
+// Bytes spanned by a row-major [rows, cols] matrix with leading dimension ld.
+static size_t span_bytes(int64_t rows, int64_t cols, int64_t ld, int elem) {
+    if (rows <= 0 || cols <= 0) return 0;
+    return (size_t)((rows - 1) * ld + cols) * (size_t)elem;
+}
+
+// Stages a host operand into slot `slot`; returns the device pointer to use (the original
+// pointer when it already is device memory).
+static int stage_in(o64_handle_t h, int slot, const void *src, size_t bytes, cudaStream_t s,
+                    const void **dev) {
+    *dev = src;
+    if (!src || !is_host_ptr(src)) return O64_OK;
+    int rc = reserve(&h->stage[slot], &h->stage_cap[slot], bytes ? bytes : 16);
+    if (rc) return rc;
+    if (bytes) CUDA_TRY(cudaMemcpyAsync(h->stage[slot], src, bytes, cudaMemcpyHostToDevice, s));
+    *dev = h->stage[slot];
+    return O64_OK;
+}
+
+struct StagedOut {
+    void *host = nullptr;
+    void *dev = nullptr;
+    size_t bytes = 0;
+};
+
+static int stage_out_begin(o64_handle_t h, int slot, void *dst, size_t bytes, bool preload,
+                           cudaStream_t s, StagedOut *o) {
+    o->host = nullptr;
+    o->dev = dst;
+    o->bytes = bytes;
+    if (!dst || !is_host_ptr(dst)) return O64_OK;
+    int rc = reserve(&h->stage[slot], &h->stage_cap[slot], bytes ? bytes : 16);
+    if (rc) return rc;
+    o->host = dst;
+    o->dev = h->stage[slot];
+    // a padded result (ld > cols) or beta != 0 needs the caller's bytes underneath
+    if (preload && bytes) CUDA_TRY(cudaMemcpyAsync(o->dev, dst, bytes, cudaMemcpyHostToDevice, s));
+    return O64_OK;
+}
+
+// Copies a staged result back and waits for it: with a host result the call is synchronous.
+static int stage_out_end(const StagedOut &o, cudaStream_t s) {
+    if (!o.host) return O64_OK;
+    if (o.bytes) CUDA_TRY(cudaMemcpyAsync(o.host, o.dev, o.bytes, cudaMemcpyDeviceToHost, s));
+    CUDA_TRY(cudaStreamSynchronize(s));
+    return O64_OK;
+}
+
+// ---- native layer ---------------------------------------------------------------------------
+extern "C" int o64_linear_f32(o64_handle_t h, int64_t M, int64_t N, int64_t K, const float *A,
+                              int64_t lda, const float *B, int64_t ldb, const float *bias, float *Y,
+                              int64_t ldy, int act, void *stream) {
+    if (!h || M < 0 || N < 0 || K < 0) return O64_ERR_RANK;
+    if (act < O64_ACT_NONE || act > O64_ACT_SILU) return O64_ERR_RANK;
+    if (M == 0 || N == 0) return O64_OK;
+    if (!A || !B || !Y) return O64_ERR_RANK;
+    if (lda < K || ldb < N || ldy < N) return O64_ERR_CONFORM;
+    DeviceGuard g(h->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    const void *dA, *dB, *dbias;
+    StagedOut out;
+    int rc;
+    if ((rc = stage_in(h, 0, A, span_bytes(M, K, lda, 4), s, &dA))) return rc;
+    if ((rc = stage_in(h, 1, B, span_bytes(K, N, ldb, 4), s, &dB))) return rc;
+    if ((rc = stage_in(h, 2, bias, (size_t)N * 4, s, &dbias))) return rc;
+    if ((rc = stage_out_begin(h, 3, Y, span_bytes(M, N, ldy, 4), ldy != N, s, &out))) return rc;
+    SimtGemmCall c;
+    c.M = M; c.N = N; c.K = K;
+    c.alpha = 1.0f; c.beta = 0.0f;
+    c.A = (const float *)dA; c.a1 = lda; c.a2 = 1;
+    c.B = (const float *)dB; c.b1 = ldb; c.b2 = 1;
+    c.C = (float *)out.dev; c.c1 = ldy; c.c2 = 1;
+    c.bias = (const float *)dbias;
+    c.act = act;
+    c.skip_zero_b = false;
+    c.num_sms = h->num_sms;
+    c.stream = s;
+    if ((rc = simt_gemm_f32(c))) return rc;
+    return stage_out_end(out, s);
+}
+
+static int umma_entry(o64_handle_t h, int kind, bool b_kn, int epi, int64_t M, int64_t N, int64_t K,
+                      const void *A, int64_t lda, const void *B, const void *B2, int64_t ldb, void *C,
+                      int64_t ldc, const float *bias, const float *sa, const float *sb, int act,
+                      void *stream) {
+    if (!h || M < 0 || N < 0 || K < 0) return O64_ERR_RANK;
+    if (act < O64_ACT_NONE || act > O64_ACT_SILU) return O64_ERR_RANK;
+    if (M == 0 || N == 0) return O64_OK;
+    if (K == 0) return O64_ERR_RANK;
+    if (!A || !B || !C) return O64_ERR_RANK;
+    const int elem = (kind == O64_KIND_BF16) ? 2 : 1;
+    const int out_elem = (epi == EPI_S32) ? 4 : 2;
+    const int64_t b_rows = b_kn ? K : N, b_cols = b_kn ? N : K;
+    if (lda < K || ldb < b_cols || ldc < N) return O64_ERR_CONFORM;
+    DeviceGuard g(h->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    const void *dA, *dB, *dB2, *dbias, *dsa, *dsb;
+    StagedOut out;
+    int rc;
+    if ((rc = stage_in(h, 0, A, span_bytes(M, K, lda, elem), s, &dA))) return rc;
+    if ((rc = stage_in(h, 1, B, span_bytes(b_rows, b_cols, ldb, elem), s, &dB))) return rc;
+    if ((rc = stage_in(h, 2, B2, span_bytes(b_rows, b_cols, ldb, elem), s, &dB2))) return rc;
+    if ((rc = stage_in(h, 3, bias, (size_t)N * 4, s, &dbias))) return rc;
+    // the two scale vectors share one slot: sa first, sb after it
+    dsa = sa;
+    dsb = sb;
+    if ((sa && is_host_ptr(sa)) || (sb && is_host_ptr(sb))) {
+        if ((rc = reserve(&h->stage[4], &h->stage_cap[4], (size_t)(M + N) * 4))) return rc;
+        float *base = (float *)h->stage[4];
+        if (sa) {
+            CUDA_TRY(cudaMemcpyAsync(base, sa, (size_t)M * 4, cudaMemcpyDefault, s));
+            dsa = base;
+        }
+        if (sb) {
+            CUDA_TRY(cudaMemcpyAsync(base + M, sb, (size_t)N * 4, cudaMemcpyDefault, s));
+            dsb = base + M;
+        }
+    }
+    if ((rc = stage_out_begin(h, 5, C, span_bytes(M, N, ldc, out_elem), ldc != N, s, &out))) return rc;
+
+    UmmaCall c;
+    c.kind = kind;
+    c.b_kn = b_kn;
+    c.epi = epi;
+    c.M = M; c.N = N; c.K = K;
+    c.A = dA; c.lda = lda;
+    c.B = dB; c.B2 = dB2; c.ldb = ldb;
+    c.C = out.dev; c.ldc = ldc;
+    c.bias = (const float *)dbias;
+    c.scale_a = (const float *)dsa;
+    c.scale_b = (const float *)dsb;
+    c.act = act;
+    choose(h, kind, epi, M, N, K, &c.plan);
+    c.status_word = h->status_word;
+    c.stream = s;
+    if ((rc = umma_launch(c))) return rc;
+    return stage_out_end(out, s);
+}
+
+extern "C" int o64_gemm_bf16(o64_handle_t h, int64_t M, int64_t N, int64_t K, const void *A, int64_t lda,
+                             const void *B, int64_t ldb, int transB, void *C, int64_t ldc,
+                             const o64_epilogue_t *epi, void *stream) {
+    return umma_entry(h, O64_KIND_BF16, transB == 0, EPI_BF16, M, N, K, A, lda, B, nullptr, ldb, C, ldc,
+                      epi ? epi->bias : nullptr, nullptr, nullptr, epi ? epi->act : O64_ACT_NONE, stream);
+}
+
+extern "C" int o64_gemm_bf16_swiglu(o64_handle_t h, int64_t M, int64_t N, int64_t K, const void *X,
+                                    int64_t ldx, const void *Wg, const void *Wu, int64_t ldw, void *H,
+                                    int64_t ldh, void *stream) {
+    if (!Wu) return O64_ERR_RANK;
+    return umma_entry(h, O64_KIND_BF16, true, EPI_SWIGLU, M, N, K, X, ldx, Wg, Wu, ldw, H, ldh, nullptr,
+                      nullptr, nullptr, O64_ACT_NONE, stream);
+}
+
+extern "C" int o64_gemm_fp8_scaled(o64_handle_t h, int64_t M, int64_t N, int64_t K, const void *A8,
+                                   int64_t lda, const void *B8, int64_t ldb, const float *scaleA,
+                                   const float *scaleB, const float *bias, void *C, int64_t ldc,
+                                   void *stream) {
+    return umma_entry(h, O64_KIND_FP8, false, EPI_SCALED_BF16, M, N, K, A8, lda, B8, nullptr, ldb, C, ldc,
+                      bias, scaleA, scaleB, O64_ACT_NONE, stream);
+}
+
+extern "C" int o64_gemm_s8s8_s32(o64_handle_t h, int64_t M, int64_t N, int64_t K, const int8_t *A,
+                                 int64_t lda, const int8_t *B, int64_t ldb, int32_t *C, int64_t ldc,
+                                 void *stream) {
+    return umma_entry(h, O64_KIND_S8, false, EPI_S32, M, N, K, A, lda, B, nullptr, ldb, C, ldc, nullptr,
+                      nullptr, nullptr, O64_ACT_NONE, stream);
+}
+
+extern "C" int o64_naive_gemm(o64_handle_t h, int kind, int64_t M, int64_t N, int64_t K, const void *A,
+                              int64_t lda, const void *B, int64_t ldb, int transB, const float *scaleA,
+                              const float *scaleB, const float *bias, int act, void *out, int64_t ldo,
+                              void *stream) {
+    if (!h || M < 0 || N < 0 || K < 0) return O64_ERR_RANK;
+    if (kind != O64_KIND_FP8 && (scaleA || scaleB)) return O64_ERR_DTYPE;
+    if (is_host_ptr(A) || is_host_ptr(B) || is_host_ptr(out)) return O64_ERR_RANK;
+    DeviceGuard g(h->device);
+    return naive_gemm(kind, M, N, K, A, lda, B, ldb, transB, scaleA, scaleB, bias, act, out, ldo,
+                      (cudaStream_t)stream);
+}
+
+// ---- multi-GPU ------------------------------------------------------------------------------
+extern "C" int o64_comm_unique_id(void *id_bytes) {
+    if (!id_bytes) return O64_ERR_RANK;
+    if (!nccl().ok) return O64_ERR_NCCL;
+    ncclUniqueId_ id;
+    if (nccl().GetUniqueId(&id) != 0) return O64_ERR_NCCL;
+    memcpy(id_bytes, &id, sizeof(id));
+    return O64_OK;
+}
+
+extern "C" int o64_comm_init(o64_handle_t h, const void *id_bytes, int rank, int nranks) {
+    if (!h || !id_bytes || nranks < 1 || rank < 0 || rank >= nranks) return O64_ERR_RANK;
+    if (!nccl().ok) return O64_ERR_NCCL;
+    DeviceGuard g(h->device);
+    o64_comm_destroy(h);
+    ncclUniqueId_ id;
+    memcpy(&id, id_bytes, sizeof(id));
+    if (nccl().CommInitRank(&h->comm, nranks, id, rank) != 0) {
+        h->comm = nullptr;
+        return O64_ERR_NCCL;
+    }
+    h->rank = rank;
+    h->nranks = nranks;
+    return O64_OK;
+}
+
+extern "C" size_t o64_gemm_s8_sharded_workspace(int64_t M, int64_t N, int nranks, int gather) {
+    (void)nranks;
+    if (gather != O64_GATHER_ROWMAJOR || M <= 0 || N <= 0) return 0;
+    return (size_t)M * (size_t)N * sizeof(int32_t);
+}
+
+extern "C" int o64_gemm_s8_sharded(o64_handle_t h, int64_t M, int64_t N, int64_t K, const int8_t *A,
+                                   int64_t lda, const int8_t *B_slab, int64_t ldb, int32_t *C_full,
+                                   int gather, void *workspace, void *stream) {
+    if (!h || M <= 0 || N <= 0 || K <= 0 || !A || !B_slab || !C_full) return O64_ERR_RANK;
+    const int g = h->nranks, r = h->rank;
+    if (N % g) return O64_ERR_CONFORM;
+    if (gather < O64_GATHER_NONE || gather > O64_GATHER_SLABS) return O64_ERR_RANK;
+    if (gather != O64_GATHER_NONE && g > 1 && !h->comm) return O64_ERR_NCCL;
+    if (is_host_ptr(A) || is_host_ptr(B_slab) || is_host_ptr(C_full)) return O64_ERR_RANK;
+    const int64_t ns = N / g;
+    DeviceGuard guard(h->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    int rc;
+
+    if (gather == O64_GATHER_NONE) {
+        return o64_gemm_s8s8_s32(h, M, ns, K, A, lda, B_slab, ldb, C_full + (int64_t)r * ns, N, stream);
+    }
+    int32_t *slabs = C_full;  // [g][M][ns]
+    if (gather == O64_GATHER_ROWMAJOR) {
+        if (g == 1) return o64_gemm_s8s8_s32(h, M, N, K, A, lda, B_slab, ldb, C_full, N, stream);
+        slabs = (int32_t *)workspace;
+        if (!slabs) {
+            if ((rc = reserve(&h->ws, &h->ws_cap, (size_t)M * N * 4))) return rc;
+            slabs = (int32_t *)h->ws;
+        }
+    }
+    int32_t *mine = slabs + (int64_t)r * M * ns;
+    if ((rc = o64_gemm_s8s8_s32(h, M, ns, K, A, lda, B_slab, ldb, mine, ns, stream))) return rc;
+    if (g > 1) {
+        // in place: this rank's slab already sits at its offset of the receive buffer
+        if (nccl().AllGather(mine, slabs, (size_t)M * ns, kNcclInt32, h->comm, s) != 0)
+            return O64_ERR_NCCL;
+    }
+    if (gather == O64_GATHER_ROWMAJOR) return permute_slabs_s32(slabs, C_full, M, ns, g, N, s);
+    return O64_OK;
+}
+
+// ---- compat layer (Fortran ABI) ---------------------------------------------------------------
+static thread_local int g_compat_status = O64_OK;
+static o64_handle_t g_compat_handle = nullptr;
+
+extern "C" int o64_compat_last_status(void) { return g_compat_status; }
+
+static o64_handle_t compat_handle() {
+    if (!g_compat_handle) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        if (o64_create(&g_compat_handle, dev) != O64_OK) g_compat_handle = nullptr;
+    }
+    return g_compat_handle;
+}
+
+// Largest element offset touched (plus one) by an extent-(n1,n2) operand with strides (s1,s2).
+static size_t strided_span(int64_t n1, int64_t n2, int64_t s1, int64_t s2) {
+    if (n1 <= 0 || n2 <= 0) return 0;
+    return (size_t)((n1 - 1) * s1 + (n2 - 1) * s2 + 1);
+}
+
+static int xgemmx_impl(int M, int N, int K, float alpha, const float *A, int64_t a1, int64_t a2,
+                       const float *B, int64_t b1, int64_t b2, float beta, float *C, int64_t c1,
+                       int64_t c2, bool skip_zero) {
+    // quick returns, in the order of osprey/libfi/matrix/xgemmx.h:172-208
+    if (M < 0 || N < 0 || K < 0) return O64_ERR_RANK;
+    if (M == 0 || N == 0 || (alpha == 0.0f && beta == 1.0f)) return O64_OK;
+    if (a1 < 0 || a2 < 0 || b1 < 0 || b2 < 0 || c1 < 0 || c2 < 0) return O64_ERR_RANK;
+    o64_handle_t h = compat_handle();
+    if (!h) return O64_ERR_CUDA;
+    DeviceGuard g(h->device);
+    cudaStream_t s = nullptr;
+    const bool only_scale = (K == 0) || (alpha == 0.0f);
+    const float beta_eff = (K == 0) ? 0.0f : beta;
+    const void *dA = A, *dB = B;
+    StagedOut out;
+    int rc;
+    if (!only_scale) {
+        if (!A || !B) return O64_ERR_RANK;
+        if ((rc = stage_in(h, 0, A, strided_span(M, K, a1, a2) * 4, s, &dA))) return rc;
+        if ((rc = stage_in(h, 1, B, strided_span(K, N, b1, b2) * 4, s, &dB))) return rc;
+    }
+    if (!C) return O64_ERR_RANK;
+    if ((rc = stage_out_begin(h, 3, C, strided_span(M, N, c1, c2) * 4, true, s, &out))) return rc;
+    if (only_scale) {
+        rc = simt_scale_f32(M, N, beta_eff, (float *)out.dev, c1, c2, s);
+    } else {
+        SimtGemmCall c;
+        c.M = M; c.N = N; c.K = K;
+        c.alpha = alpha; c.beta = beta;
+        c.A = (const float *)dA; c.a1 = a1; c.a2 = a2;
+        c.B = (const float *)dB; c.b1 = b1; c.b2 = b2;
+        c.C = (float *)out.dev; c.c1 = c1; c.c2 = c2;
+        c.bias = nullptr;
+        c.act = O64_ACT_NONE;
+        c.skip_zero_b = skip_zero;
+        c.num_sms = h->num_sms;
+        c.stream = s;
+        rc = simt_gemm_f32(c);
+    }
+    if (rc) return rc;
+    if ((rc = stage_out_end(out, s))) return rc;
+    if (!out.host) CUDA_TRY(cudaStreamSynchronize(s));  // the Fortran interface is synchronous
+    return O64_OK;
+}
+
+extern "C" void _s4gemmx__(const int *m, const int *n, const int *k, const float *alpha, const float *a,
+                           const int *inc1a, const int *inc2a, const float *b, const int *inc1b,
+                           const int *inc2b, const float *beta, float *c, const int *inc1c,
+                           const int *inc2c) {
+    g_compat_status = xgemmx_impl(*m, *n, *k, *alpha, a, *inc1a, *inc2a, b, *inc1b, *inc2b, *beta, c,
+                                  *inc1c, *inc2c, true);
+}
+
+extern "C" void sgemm_(const char *transa, const char *transb, const int *m, const int *n, const int *k,
+                       const float *alpha, const float *a, const int *lda, const float *b, const int *ldb,
+                       const float *beta, float *c, const int *ldc) {
+    auto is_n = [](char ch) { return ch == 'n' || ch == 'N'; };
+    auto is_t = [](char ch) { return ch == 't' || ch == 'T' || ch == 'c' || ch == 'C'; };
+    const bool na = is_n(*transa), nb = is_n(*transb);
+    if ((!na && !is_t(*transa)) || (!nb && !is_t(*transb))) {
+        g_compat_status = O64_ERR_RANK;
+        return;
+    }
+    const int rows_a = na ? *m : *k, rows_b = nb ? *k : *n;
+    if (*lda < (rows_a > 1 ? rows_a : 1) || *ldb < (rows_b > 1 ? rows_b : 1) ||
+        *ldc < (*m > 1 ? *m : 1)) {
+        g_compat_status = O64_ERR_CONFORM;
+        return;
+    }
+    // column-major: op(A)(i,l) = A[i + l*lda] or A[l + i*lda]
+    const int64_t a1 = na ? 1 : *lda, a2 = na ? *lda : 1;
+    const int64_t b1 = nb ? 1 : *ldb, b2 = nb ? *ldb : 1;
+    g_compat_status = xgemmx_impl(*m, *n, *k, *alpha, a, a1, a2, b, b1, b2, *beta, c, 1, *ldc, false);
+}
+
+extern "C" void _s4gemvx__(const int *m, const int *n, const float *alpha, const float *a,
+                           const int *incca, const int *incra, const float *x, const int *incx,
+                           const float *beta, float *y, const int *incy) {
+    const int M = *m, N = *n;
+    g_compat_status = O64_OK;
+    if (M < 0 || N < 0) {
+        g_compat_status = O64_ERR_RANK;
+        return;
+    }
+    // quick returns of osprey/libfi/matrix/s4gemvx.f
+    if (M == 0) return;
+    const bool zero_only = (N == 0);
+    if (!zero_only && *alpha == 0.0f && *beta == 1.0f) return;
+    o64_handle_t h = compat_handle();
+    if (!h) {
+        g_compat_status = O64_ERR_CUDA;
+        return;
+    }
+    DeviceGuard g(h->device);
+    cudaStream_t s = nullptr;
+    const void *dA = a, *dX = x;
+    StagedOut out;
+    int rc = O64_OK;
+    const bool need_ax = !zero_only && *alpha != 0.0f;
+    if (need_ax) {
+        rc = stage_in(h, 0, a, strided_span(M, N, *incca, *incra) * 4, s, &dA);
+        if (!rc) rc = stage_in(h, 1, x, strided_span(N, 1, *incx, 0) * 4, s, &dX);
+    }
+    if (!rc) rc = stage_out_begin(h, 3, y, strided_span(M, 1, *incy, 0) * 4, true, s, &out);
+    if (!rc) {
+        if (need_ax)
+            rc = simt_gemv_f32(M, N, *alpha, (const float *)dA, *incca, *incra, (const float *)dX, *incx,
+                               *beta, (float *)out.dev, *incy, s);
+        else
+            rc = simt_scale_f32(M, 1, zero_only ? 0.0f : *beta, (float *)out.dev, *incy, 0, s);
+    }
+    if (!rc) rc = stage_out_end(out, s);
+    if (!rc && !out.host && cudaStreamSynchronize(s) != cudaSuccess) rc = O64_ERR_CUDA;
+    g_compat_status = rc;
+}

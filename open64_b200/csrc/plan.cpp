@@ -1,0 +1,130 @@
+// Tile-plan chooser: the B200 counterpart of the reference's tile decision
+// (LOOP_MODEL::Model, osprey/be/lno/model.cxx:540, scored by Evaluate :1289 as
+// cycles = max(resource, latency); cache blocking from Cache_Model,
+// osprey/be/lno/cache_model.cxx:6483).  Pure host code, no CUDA calls.
+//
+// The search space is what the kernels are instantiated for: tile_m = 128, tile_n in
+// {256, 128}; each candidate is scored with a two-resource model (tensor pipe vs. the
+// shared-memory fill rate) times the number of waves over the persistent grid.
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "umma_gemm.cuh"
+
+namespace o64 {
+
+// Machine parameters (the reference keeps issue rate / register count / cache geometry here:
+// osprey/be/lno/model.cxx:739-743, osprey/common/com/x8664/config_cache_targ.cxx:80-420).
+static const double kClockGHz = 1.5;            // sustained SM clock under load, approx.
+static const double kDenseBf16FlopPerClkSm = 8192.0;
+static const double kSmemFillBytesPerClkSm = 96.0;  // L2 -> shared memory through TMA, approx.
+
+static int elem_bytes(int kind) { return kind == O64_KIND_BF16 ? 2 : (kind == O64_KIND_F32 ? 4 : 1); }
+
+static double predict_ms(int kind, int epi, int64_t M, int64_t N, int64_t K, int tile_n, int num_ctas) {
+    const int eb = elem_bytes(kind);
+    const int block_k = 128 / eb;
+    const int out_n = (epi == EPI_SWIGLU) ? tile_n / 2 : tile_n;
+    const double tiles = double((M + 127) / 128) * double((N + out_n - 1) / out_n);
+    const double waves = double(int64_t((tiles + num_ctas - 1) / num_ctas));
+    const double kblocks = double((K + block_k - 1) / block_k);
+    const double flop_rate = kDenseBf16FlopPerClkSm * (eb == 1 ? 2.0 : 1.0);
+    const double mma_clk = 2.0 * 128.0 * tile_n * block_k / flop_rate;
+    const double fill_clk = (128.0 + tile_n) * 128.0 / kSmemFillBytesPerClkSm;
+    const double stage_clk = mma_clk > fill_clk ? mma_clk : fill_clk;
+    const double prologue_clk = 2500.0;  // first TMA round trip + epilogue tail of the last tile
+    return (waves * kblocks * stage_clk + prologue_clk) / (kClockGHz * 1e6);
+}
+
+// O64_LNO="blocking_size=128x256x64:stages=4:cta_group=1:group_m=8:raster=0:num_ctas=148"
+static void apply_env(o64_plan_t *pin) {
+    const char *env = getenv("O64_LNO");
+    if (!env || !*env) return;
+    char buf[256];
+    strncpy(buf, env, sizeof(buf) - 1);
+    buf[sizeof(buf) - 1] = 0;
+    for (char *tok = strtok(buf, ":"); tok; tok = strtok(nullptr, ":")) {
+        int a, b, c;
+        if (sscanf(tok, "blocking_size=%dx%dx%d", &a, &b, &c) == 3) {
+            pin->tile_m = a;
+            pin->tile_n = b;
+            pin->tile_k = c;
+        } else if (sscanf(tok, "stages=%d", &a) == 1) {
+            pin->stages = a;
+        } else if (sscanf(tok, "cta_group=%d", &a) == 1) {
+            pin->cta_group = a;
+        } else if (sscanf(tok, "group_m=%d", &a) == 1) {
+            pin->group_m = a;
+        } else if (sscanf(tok, "raster=%d", &a) == 1) {
+            pin->raster = a;
+        } else if (sscanf(tok, "num_ctas=%d", &a) == 1) {
+            pin->num_ctas = a;
+        }
+    }
+}
+
+void plan_choose(int kind, int epi, int64_t M, int64_t N, int64_t K, int num_sms,
+                 const o64_plan_t *pin_in, o64_plan_t *out) {
+    o64_plan_t pin;
+    memset(&pin, 0, sizeof(pin));
+    if (pin_in) pin = *pin_in;
+    apply_env(&pin);
+
+    memset(out, 0, sizeof(*out));
+    out->kind = kind;
+    const int eb = elem_bytes(kind);
+    out->tile_m = 128;
+    out->tile_k = 128 / eb;
+    out->cta_group = 1;
+    out->mma_m = 128;
+    out->mma_k = 32 / eb;
+    out->split_k = 1;
+    out->num_ctas = (pin.num_ctas > 0 && pin.num_ctas <= num_sms) ? pin.num_ctas : num_sms;
+
+    int tile_n = 0;
+    if (pin.tile_n == 128 || pin.tile_n == 256) {
+        tile_n = pin.tile_n;
+    } else {
+        const double t256 = predict_ms(kind, epi, M, N, K, 256, out->num_ctas);
+        const double t128 = predict_ms(kind, epi, M, N, K, 128, out->num_ctas);
+        tile_n = (t128 < 0.97 * t256) ? 128 : 256;
+    }
+    out->tile_n = tile_n;
+    out->mma_n = tile_n;
+    out->stages = (tile_n == 256) ? 4 : 6;
+    out->predicted_ms = predict_ms(kind, epi, M, N, K, tile_n, out->num_ctas);
+
+    // L2 block: rasterise tiles so that the CTAs running together cover a near-square patch
+    // of C (fewest distinct A and B panels in flight).
+    if (pin.group_m > 0) {
+        out->group_m = pin.group_m;
+    } else {
+        const int out_n = (epi == EPI_SWIGLU) ? tile_n / 2 : tile_n;
+        int best = 1;
+        double best_cost = 1e300;
+        for (int g = 1; g <= 32; g *= 2) {
+            const double cols = double(out->num_ctas) / g;
+            const double cost = g * 128.0 + cols * out_n;  // panel rows fetched per wave
+            if (cost < best_cost) {
+                best_cost = cost;
+                best = g;
+            }
+        }
+        out->group_m = best;
+    }
+    out->raster = pin.raster ? 1 : 0;  // the automatic choice is 0 (M fastest)
+
+    const char *tr = getenv("O64_TRACE");
+    if (tr && strstr(tr, "plan")) {
+        // after -LNO:verbose, "[i,j,k --> ... blocks k(128)[L1] outside i]" (osprey/be/lno/snl_test.cxx:918-954)
+        fprintf(stderr,
+                "[o64 plan kind=%d %lldx%lldx%lld --> tile %dx%dx%d (mma %dx%dx%d) stages=%d[SMEM] "
+                "group_m=%d[L2] raster=%d ctas=%d cta_group=%d predicted=%.4f ms]\n",
+                kind, (long long)M, (long long)N, (long long)K, out->tile_m, out->tile_n, out->tile_k,
+                out->mma_m, out->mma_n, out->mma_k, out->stages, out->group_m, out->raster,
+                out->num_ctas, out->cta_group, out->predicted_ms);
+    }
+}
+
+}  // namespace o64

@@ -1,0 +1,367 @@
+// CUDA-core kernels: the fp32 fused linear / strided GEMM (FFMA), the strided GEMV, the
+// one-thread-per-output reference kernels and the slab permute.
+//
+// The fp32 kernel keeps fp32 arithmetic end to end (no TF32): the fused linear is checked
+// against the CPU loop nest to 1e-4 relative, and the compat entry points promise the
+// reference runtime's semantics (osprey/libfi/matrix/xgemmx.h:172-236).
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include "../../include/o64gemm.h"
+#include "simt_kernels.cuh"
+
+namespace o64 {
+
+__device__ __forceinline__ float act_f32(float x, int act) {
+    switch (act) {
+    case O64_ACT_RELU: return fmaxf(x, 0.0f);
+    case O64_ACT_GELU_TANH: {
+        const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+        return 0.5f * x * (1.0f + tanhf(u));
+    }
+    case O64_ACT_GELU_ERF: return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
+    case O64_ACT_SILU: return x / (1.0f + expf(-x));
+    default: return x;
+    }
+}
+
+struct SimtParams {
+    long long M, N, K;
+    float alpha, beta;
+    const float *A;
+    long long a1, a2;
+    const float *B;
+    long long b1, b2;
+    float *C;
+    long long c1, c2;
+    const float *bias;
+    int act;
+    int a_k_fast;  // A's K index is the contiguous one
+    int b_n_fast;  // B's N index is the contiguous one
+    int c_n_fast;
+};
+
+// BM x BN tile per CTA, BK deep, TM x TN outputs per thread.  The tile loop is the K strip
+// of the reference's cache blocking; the TM x TN register block is its unroll-and-jam
+// (osprey/be/lno/snl_inv.cxx:639,904).
+template <int BM, int BN, int BK, int TM, int TN, bool SKIP_ZERO>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+simt_gemm_kernel(const SimtParams p) {
+    constexpr int T = (BM / TM) * (BN / TN);
+    constexpr int PAD = 4;
+    __shared__ __align__(16) float As[BK][BM + PAD];
+    __shared__ __align__(16) float Bs[BK][BN + PAD];
+
+    const int tid = threadIdx.x;
+    const int tx = tid % (BN / TN);
+    const int ty = tid / (BN / TN);
+    const long long m0 = (long long)blockIdx.y * BM;
+    const long long n0 = (long long)blockIdx.x * BN;
+
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+
+    for (long long k0 = 0; k0 < p.K; k0 += BK) {
+#pragma unroll
+        for (int e = tid; e < BM * BK; e += T) {
+            int i, l;
+            if (p.a_k_fast) {
+                l = e % BK;
+                i = e / BK;
+            } else {
+                i = e % BM;
+                l = e / BM;
+            }
+            const long long gi = m0 + i, gl = k0 + l;
+            As[l][i] = (gi < p.M && gl < p.K) ? __ldg(p.A + gi * p.a1 + gl * p.a2) : 0.0f;
+        }
+#pragma unroll
+        for (int e = tid; e < BK * BN; e += T) {
+            int l, j;
+            if (p.b_n_fast) {
+                j = e % BN;
+                l = e / BN;
+            } else {
+                l = e % BK;
+                j = e / BK;
+            }
+            const long long gl = k0 + l, gj = n0 + j;
+            Bs[l][j] = (gl < p.K && gj < p.N) ? __ldg(p.B + gl * p.b1 + gj * p.b2) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int l = 0; l < BK; ++l) {
+            float a[TM], b[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) a[i] = As[l][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) b[j] = Bs[l][tx * TN + j];
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) {
+                    if (SKIP_ZERO) {
+                        if (b[j] != 0.0f) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                    } else {
+                        acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                    }
+                }
+        }
+        __syncthreads();
+    }
+
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const long long gi = m0 + ty * TM + i;
+        if (gi >= p.M) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const long long gj = n0 + tx * TN + j;
+            if (gj >= p.N) continue;
+            float *dst = p.C + gi * p.c1 + gj * p.c2;
+            float v = p.alpha * acc[i][j];
+            if (p.beta != 0.0f) v += p.beta * *dst;
+            if (p.bias) v += __ldg(p.bias + gj);
+            *dst = act_f32(v, p.act);
+        }
+    }
+}
+
+template <int BM, int BN, int BK, int TM, int TN>
+static int launch_simt(const SimtParams &p, bool skip_zero, cudaStream_t stream) {
+    dim3 grid((unsigned)((p.N + BN - 1) / BN), (unsigned)((p.M + BM - 1) / BM));
+    constexpr int T = (BM / TM) * (BN / TN);
+    if (skip_zero)
+        simt_gemm_kernel<BM, BN, BK, TM, TN, true><<<grid, T, 0, stream>>>(p);
+    else
+        simt_gemm_kernel<BM, BN, BK, TM, TN, false><<<grid, T, 0, stream>>>(p);
+    return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
+}
+
+int simt_gemm_f32(const SimtGemmCall &c) {
+    if (c.M < 0 || c.N < 0 || c.K < 0) return O64_ERR_RANK;
+    if (c.M == 0 || c.N == 0) return O64_OK;
+    if ((c.N + 31) / 32 > 2147483647LL || (c.M + 31) / 32 > 65535LL) return O64_ERR_RANK;
+    SimtParams p;
+    p.M = c.M; p.N = c.N; p.K = c.K;
+    p.alpha = c.alpha; p.beta = c.beta;
+    p.A = c.A; p.a1 = c.a1; p.a2 = c.a2;
+    p.B = c.B; p.b1 = c.b1; p.b2 = c.b2;
+    p.C = c.C; p.c1 = c.c1; p.c2 = c.c2;
+    p.bias = c.bias;
+    p.act = c.act;
+    auto mag = [](int64_t v) { return v < 0 ? -v : v; };
+    p.a_k_fast = mag(c.a2) <= mag(c.a1);
+    p.b_n_fast = mag(c.b2) <= mag(c.b1);
+    p.c_n_fast = mag(c.c2) <= mag(c.c1);
+    const long long big_tiles = ((c.M + 63) / 64) * ((c.N + 63) / 64);
+    if (big_tiles >= 2LL * c.num_sms) return launch_simt<64, 64, 16, 4, 4>(p, c.skip_zero_b, c.stream);
+    return launch_simt<32, 32, 16, 2, 2>(p, c.skip_zero_b, c.stream);
+}
+
+// ------------------------------------------------------------------------------------------
+// GEMV
+// ------------------------------------------------------------------------------------------
+// One warp per row: lanes stride over the columns, shuffle reduction.
+__global__ void gemv_warp_kernel(long long M, long long N, float alpha, const float *A, long long a1,
+                                 long long a2, const float *X, long long incx, float beta, float *Y,
+                                 long long incy) {
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= M) return;
+    float acc = 0.0f;
+    for (long long j = lane; j < N; j += 32) {
+        const float x = __ldg(X + j * incx);
+        if (x != 0.0f) acc = fmaf(alpha * x, __ldg(A + row * a1 + j * a2), acc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+        float *y = Y + row * incy;
+        *y = (beta == 0.0f ? 0.0f : beta * *y) + acc;
+    }
+}
+
+// One thread per row: coalesced when consecutive rows are adjacent in memory (column-major A).
+__global__ void gemv_thread_kernel(long long M, long long N, float alpha, const float *A,
+                                   long long a1, long long a2, const float *X, long long incx,
+                                   float beta, float *Y, long long incy) {
+    const long long row = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= M) return;
+    float *y = Y + row * incy;
+    float acc = (beta == 0.0f) ? 0.0f : beta * *y;
+    for (long long j = 0; j < N; ++j) {
+        const float x = __ldg(X + j * incx);
+        if (x != 0.0f) acc = fmaf(alpha * x, __ldg(A + row * a1 + j * a2), acc);
+    }
+    *y = acc;
+}
+
+int simt_gemv_f32(int64_t M, int64_t N, float alpha, const float *A, int64_t a1, int64_t a2,
+                  const float *X, int64_t incx, float beta, float *Y, int64_t incy,
+                  cudaStream_t stream) {
+    if (M <= 0) return O64_OK;
+    auto mag = [](int64_t v) { return v < 0 ? -v : v; };
+    if (mag(a1) <= mag(a2) && M >= 4096) {
+        const int T = 128;
+        gemv_thread_kernel<<<(unsigned)((M + T - 1) / T), T, 0, stream>>>(M, N, alpha, A, a1, a2, X,
+                                                                            incx, beta, Y, incy);
+    } else {
+        const int T = 128;  // 4 rows per block
+        gemv_warp_kernel<<<(unsigned)((M + 3) / 4), T, 0, stream>>>(M, N, alpha, A, a1, a2, X, incx,
+                                                                      beta, Y, incy);
+    }
+    return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
+}
+
+__global__ void scale_kernel(long long M, long long N, float beta, float *C, long long c1,
+                             long long c2, int n_fast) {
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= M * N) return;
+    long long i, j;
+    if (n_fast) {
+        j = e % N;
+        i = e / N;
+    } else {
+        i = e % M;
+        j = e / M;
+    }
+    float *c = C + i * c1 + j * c2;
+    *c = (beta == 0.0f) ? 0.0f : beta * *c;
+}
+
+int simt_scale_f32(int64_t M, int64_t N, float beta, float *C, int64_t c1, int64_t c2,
+                   cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return O64_OK;
+    auto mag = [](int64_t v) { return v < 0 ? -v : v; };
+    const long long total = (long long)M * N;
+    scale_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(M, N, beta, C, c1, c2,
+                                                                       mag(c2) <= mag(c1));
+    return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
+}
+
+// ------------------------------------------------------------------------------------------
+// reference kernels: one thread per output, ascending k, separate multiply and add — the
+// compiler's loop nest (osprey/be/vho/f90_lower.cxx:5149-5169) run as is on the device.
+// ------------------------------------------------------------------------------------------
+template <int KIND>
+__device__ __forceinline__ float load_as_f32(const void *base, long long idx) {
+    if constexpr (KIND == O64_KIND_F32) {
+        return reinterpret_cast<const float *>(base)[idx];
+    } else if constexpr (KIND == O64_KIND_BF16) {
+        return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(base)[idx]);
+    } else {
+        __nv_fp8_e4m3 v;
+        v.__x = reinterpret_cast<const unsigned char *>(base)[idx];
+        return static_cast<float>(v);
+    }
+}
+
+template <int KIND>
+__global__ void naive_float_kernel(long long M, long long N, long long K, const void *A,
+                                   long long lda, const void *B, long long ldb, int transB,
+                                   const float *scaleA, const float *scaleB, const float *bias,
+                                   int act, float *out, long long ldo) {
+    const long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long i = (long long)blockIdx.y * blockDim.y + threadIdx.y;
+    if (i >= M || j >= N) return;
+    const float sa = scaleA ? scaleA[i] : 1.0f;
+    const float sb = scaleB ? scaleB[j] : 1.0f;
+    float acc = 0.0f;
+    for (long long k = 0; k < K; ++k) {
+        float a = load_as_f32<KIND>(A, i * lda + k);
+        float b = load_as_f32<KIND>(B, transB ? j * ldb + k : k * ldb + j);
+        if (KIND == O64_KIND_FP8) {
+            a = __fmul_rn(a, sa);
+            b = __fmul_rn(b, sb);
+        }
+        acc = __fadd_rn(acc, __fmul_rn(a, b));
+    }
+    if (bias) acc = __fadd_rn(acc, bias[j]);
+    out[i * ldo + j] = act_f32(acc, act);
+}
+
+__global__ void naive_s8_kernel(long long M, long long N, long long K, const int8_t *A, long long lda,
+                                const int8_t *B, long long ldb, int transB, int32_t *out,
+                                long long ldo) {
+    const long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long i = (long long)blockIdx.y * blockDim.y + threadIdx.y;
+    if (i >= M || j >= N) return;
+    int32_t acc = 0;
+    for (long long k = 0; k < K; ++k)
+        acc += (int32_t)A[i * lda + k] * (int32_t)B[transB ? j * ldb + k : k * ldb + j];
+    out[i * ldo + j] = acc;
+}
+
+int naive_gemm(int kind, int64_t M, int64_t N, int64_t K, const void *A, int64_t lda, const void *B,
+               int64_t ldb, int transB, const float *scaleA, const float *scaleB, const float *bias,
+               int act, void *out, int64_t ldo, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return O64_OK;
+    dim3 block(32, 8);
+    dim3 grid((unsigned)((N + 31) / 32), (unsigned)((M + 7) / 8));
+    if (grid.y > 65535) return O64_ERR_RANK;
+    float *of = reinterpret_cast<float *>(out);
+    switch (kind) {
+    case O64_KIND_F32:
+        naive_float_kernel<O64_KIND_F32><<<grid, block, 0, stream>>>(M, N, K, A, lda, B, ldb, transB,
+                                                                      nullptr, nullptr, bias, act, of, ldo);
+        break;
+    case O64_KIND_BF16:
+        naive_float_kernel<O64_KIND_BF16><<<grid, block, 0, stream>>>(M, N, K, A, lda, B, ldb, transB,
+                                                                       nullptr, nullptr, bias, act, of, ldo);
+        break;
+    case O64_KIND_FP8:
+        naive_float_kernel<O64_KIND_FP8><<<grid, block, 0, stream>>>(M, N, K, A, lda, B, ldb, transB,
+                                                                      scaleA, scaleB, bias, act, of, ldo);
+        break;
+    case O64_KIND_S8:
+        naive_s8_kernel<<<grid, block, 0, stream>>>(M, N, K, reinterpret_cast<const int8_t *>(A), lda,
+                                                    reinterpret_cast<const int8_t *>(B), ldb, transB,
+                                                    reinterpret_cast<int32_t *>(out), ldo);
+        break;
+    default: return O64_ERR_DTYPE;
+    }
+    return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
+}
+
+// ------------------------------------------------------------------------------------------
+// slab permute: the all-gather delivers [g][M][N/g]; callers that want row-major [M,N] get it
+// through this copy (16-byte vectors when the slab width allows).
+// ------------------------------------------------------------------------------------------
+__global__ void permute_slabs_kernel(const int32_t *__restrict__ src, int32_t *__restrict__ dst,
+                                     long long M, long long ncols, int nslabs, long long ld_dst,
+                                     int vec) {
+    const long long per_row = ncols / vec;
+    const long long total = (long long)nslabs * M * per_row;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+         e += (long long)gridDim.x * blockDim.x) {
+        const long long jv = e % per_row;
+        const long long rest = e / per_row;
+        const long long r = rest % nslabs;  // slab varies fastest after the column: a row of dst stays contiguous
+        const long long m = rest / nslabs;
+        const int32_t *s = src + (r * M + m) * ncols + jv * vec;
+        int32_t *d = dst + m * ld_dst + r * ncols + jv * vec;
+        if (vec == 4)
+            *reinterpret_cast<int4 *>(d) = *reinterpret_cast<const int4 *>(s);
+        else
+            *d = *s;
+    }
+}
+
+int permute_slabs_s32(const int32_t *src, int32_t *dst, int64_t M, int64_t ncols, int nslabs,
+                      int64_t ld_dst, cudaStream_t stream) {
+    if (M <= 0 || ncols <= 0 || nslabs <= 0) return O64_OK;
+    const bool v4 = (ncols % 4 == 0) && (ld_dst % 4 == 0) &&
+                    ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0;
+    const int vec = v4 ? 4 : 1;
+    const long long total = (long long)nslabs * M * (ncols / vec);
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148LL * 16) blocks = 148LL * 16;
+    permute_slabs_kernel<<<(unsigned)blocks, 256, 0, stream>>>(src, dst, M, ncols, nslabs, ld_dst, vec);
+    return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
+}
+
+}  // namespace o64

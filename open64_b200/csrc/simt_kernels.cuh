@@ -1,0 +1,48 @@
+// Host-side interface of the CUDA-core kernels (simt_kernels.cu): the fp32 fused linear /
+// strided GEMM, the strided GEMV, the one-thread-per-output reference kernels and the slab
+// permute used after the all-gather.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace o64 {
+
+// C(i,j) = act( alpha * sum_l A(i,l)*B(l,j) + beta*C(i,j) + bias[j] ), fp32, with
+// X(i,j) at X[i*x1 + j*x2].  skip_zero_b: leave out terms whose B(l,j) == 0, as the
+// reference's runtime kernel does (osprey/libfi/matrix/xgemmx.h:227).
+struct SimtGemmCall {
+    int64_t M, N, K;
+    float alpha, beta;
+    const float *A;
+    int64_t a1, a2;
+    const float *B;
+    int64_t b1, b2;
+    float *C;
+    int64_t c1, c2;
+    const float *bias;
+    int act;
+    bool skip_zero_b;
+    int num_sms;
+    cudaStream_t stream;
+};
+int simt_gemm_f32(const SimtGemmCall &c);
+
+// y(i) = alpha * sum_j A(i,j)*x(j) + beta*y(i); terms with x(j) == 0 are left out
+// (osprey/libfi/matrix/s4gemvx.f).
+int simt_gemv_f32(int64_t M, int64_t N, float alpha, const float *A, int64_t a1, int64_t a2,
+                  const float *X, int64_t incx, float beta, float *Y, int64_t incy,
+                  cudaStream_t stream);
+
+// Scales or zeroes C in place: C = beta*C (beta == 0 writes zeros without reading C).
+int simt_scale_f32(int64_t M, int64_t N, float beta, float *C, int64_t c1, int64_t c2,
+                   cudaStream_t stream);
+
+int naive_gemm(int kind, int64_t M, int64_t N, int64_t K, const void *A, int64_t lda, const void *B,
+               int64_t ldb, int transB, const float *scaleA, const float *scaleB, const float *bias,
+               int act, void *out, int64_t ldo, cudaStream_t stream);
+
+// dst[m][r*ncols + j] = src[r][m][j] for r < nslabs (int32 elements).
+int permute_slabs_s32(const int32_t *src, int32_t *dst, int64_t M, int64_t ncols, int nslabs,
+                      int64_t ld_dst, cudaStream_t stream);
+
+}  // namespace o64

@@ -1,0 +1,496 @@
+// Tensor-core GEMM for sm_100a: TMA -> multi-stage shared-memory ring -> tcgen05.mma with
+// the accumulator in tensor memory -> fused epilogue.  One persistent CTA per SM walks a
+// rasterised list of 128 x BLOCK_N output tiles.
+//
+// This kernel is the tiled form of the loop nest the reference compiler builds for MATMUL
+// (osprey/be/vho/f90_lower.cxx:5149-5169): the K loop is the ring of shared-memory stages
+// (the reference's L1 strip, osprey/be/lno/snl_inv.cxx:639-887), the register tile is one
+// tcgen05.mma instruction (osprey/be/lno/snl_inv.cxx:904), software prefetch
+// (osprey/be/lno/prefetch.cxx:679) is the TMA producer warp running ahead of the MMA warp.
+//
+// Warp roles (192 threads):
+//   warp 0      producer: one lane issues the TMA loads of A and B for each K block
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma and the commits
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator, apply bias / activation /
+//               scales, convert and store; overlaps the next tile's main loop because the
+//               accumulator is double-buffered in tensor memory
+//
+// Every wait is bounded (mbar_wait_bounded): on expiry the CTA records a code in the status
+// word, leaves all role loops, frees its tensor memory and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <mutex>
+
+#include "ptx_sm100.cuh"
+#include "umma_gemm.cuh"
+
+namespace o64 {
+
+struct UmmaParams {
+    int M, N, K;
+    void *C;
+    long long ldc;
+    const float *bias;
+    const float *scale_a;
+    const float *scale_b;
+    int act;
+    int num_m_tiles, num_n_tiles, group_m, raster;
+    int num_k_blocks;
+    int vec_ok;  // C rows 16-byte aligned: vector stores allowed
+    int *status;
+};
+
+constexpr int kBlockM = 128;
+constexpr int kRowBytes = 128;  // bytes of K (or of N for a [K,N] operand) per shared-memory row
+constexpr int kThreads = 192;
+constexpr int kABytes = kBlockM * kRowBytes;
+
+// Status-word detail codes: which wait gave up.
+constexpr int kWaitProducerEmpty = 0x101;
+constexpr int kWaitMmaFull = 0x102;
+constexpr int kWaitMmaAccEmpty = 0x103;
+constexpr int kWaitEpiAccFull = 0x104;
+
+template <int BLOCK_N, int STAGES>
+struct SmemLayout {
+    static constexpr int kBBytes = BLOCK_N * kRowBytes;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kRingBytes = STAGES * kStageBytes;
+    // after the ring: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2] (8 bytes each),
+    // the TMEM base address and the abort flag
+    static constexpr int kBarOffset = kRingBytes;
+    static constexpr int kNumBars = 2 * STAGES + 4;
+    static constexpr int kTmemPtrOffset = kBarOffset + 8 * kNumBars;
+    static constexpr int kAbortOffset = kTmemPtrOffset + 4;
+    static constexpr int kTotal = kAbortOffset + 4;
+    static constexpr int kDynamic = kTotal + 1024;  // slack to align the ring to 1024 bytes
+};
+
+__device__ __forceinline__ void tile_coords(int t, const UmmaParams &p, int &mb, int &nb) {
+    if (p.raster == 0) {
+        const int per_group = p.group_m * p.num_n_tiles;
+        const int g = t / per_group;
+        const int first = g * p.group_m;
+        const int gsz = min(p.num_m_tiles - first, p.group_m);
+        const int r = t - g * per_group;
+        mb = first + r % gsz;
+        nb = r / gsz;
+    } else {
+        const int per_group = p.group_m * p.num_m_tiles;
+        const int g = t / per_group;
+        const int first = g * p.group_m;
+        const int gsz = min(p.num_n_tiles - first, p.group_m);
+        const int r = t - g * per_group;
+        nb = first + r % gsz;
+        mb = r / gsz;
+    }
+}
+
+__device__ __forceinline__ float act_apply(float x, int act) {
+    switch (act) {
+    case O64_ACT_RELU: return fmaxf(x, 0.0f);
+    case O64_ACT_GELU_TANH: {
+        const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+        return 0.5f * x * (1.0f + tanhf(u));
+    }
+    case O64_ACT_GELU_ERF: return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
+    case O64_ACT_SILU: return x / (1.0f + expf(-x));
+    default: return x;
+    }
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+// KIND: MMA_F16 (bf16 operands) / MMA_F8F6F4 (e4m3) / MMA_I8 (s8).
+// B_KN: B stored [K,N] (N contiguous) -> MN-major shared-memory descriptor; else [N,K].
+template <int KIND, bool B_KN, int EPI, int BLOCK_N, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                 const __grid_constant__ CUtensorMap tm_b2, const UmmaParams p) {
+    using L = SmemLayout<BLOCK_N, STAGES>;
+    constexpr int kElem = (KIND == MMA_F16) ? 2 : 1;
+    constexpr int kBlockK = kRowBytes / kElem;  // K elements per stage
+    constexpr int kMmaPerStage = 4;             // 32 bytes of K per tcgen05.mma
+    constexpr int kOutN = (EPI == EPI_SWIGLU) ? BLOCK_N / 2 : BLOCK_N;
+    constexpr uint32_t kTmemCols = 2 * BLOCK_N;  // two accumulator buffers
+    static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns");
+    static_assert(!B_KN || KIND == MMA_F16, "[K,N] operands are supported for bf16 only");
+    static_assert(EPI != EPI_SWIGLU || B_KN, "SwiGLU weights are [K,N]");
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + L::kBarOffset;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+    auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+    volatile uint32_t *tmem_ptr_smem =
+        reinterpret_cast<volatile uint32_t *>(smem_gen + L::kTmemPtrOffset);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_gen + L::kAbortOffset);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full_bar(b), 1);
+            mbar_init(acc_empty_bar(b), 128);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tm_a);
+        tma_prefetch_desc(&tm_b);
+        if (EPI == EPI_SWIGLU) tma_prefetch_desc(&tm_b2);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(smem_gen + L::kTmemPtrOffset), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_smem;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                int mb, nb;
+                tile_coords(t, p, mb, nb);
+                const int m0 = mb * kBlockM;
+                const int n0 = nb * kOutN;
+                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                    ok = mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
+                                           kWaitProducerEmpty);
+                    if (!ok) break;
+                    const uint32_t a_dst = smem_base + stage * L::kStageBytes;
+                    const uint32_t b_dst = a_dst + kABytes;
+                    mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
+                    tma_load_2d(a_dst, &tm_a, kb * kBlockK, m0, full_bar(stage));
+                    if constexpr (!B_KN) {
+                        tma_load_2d(b_dst, &tm_b, kb * kBlockK, n0, full_bar(stage));
+                    } else {
+                        // [K,N] operand: boxes of 64 N-elements x 64 K-rows (8 KB each)
+                        constexpr int kGroups = BLOCK_N / 64;
+#pragma unroll
+                        for (int g = 0; g < kGroups; ++g) {
+                            if constexpr (EPI == EPI_SWIGLU) {
+                                const bool up = g >= kGroups / 2;
+                                const int gg = up ? g - kGroups / 2 : g;
+                                tma_load_2d(b_dst + g * 8192, up ? &tm_b2 : &tm_b, n0 + gg * 64,
+                                            kb * kBlockK, full_bar(stage));
+                            } else {
+                                tma_load_2d(b_dst + g * 8192, &tm_b, n0 + g * 64, kb * kBlockK,
+                                            full_bar(stage));
+                            }
+                        }
+                    }
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t d_fmt = (KIND == MMA_I8) ? 2u : 1u;
+            constexpr uint32_t ab_fmt = (KIND == MMA_F8F6F4) ? 0u : 1u;  // bf16 / e4m3 / s8
+            constexpr uint32_t idesc =
+                make_idesc(d_fmt, ab_fmt, ab_fmt, B_KN ? 1u : 0u, kBlockM, BLOCK_N);
+            constexpr uint32_t kBAdvance = B_KN ? (16 * kRowBytes) >> 4 : 32 >> 4;
+            int stage = 0;
+            uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+                const int buf = it & 1;
+                const uint32_t acc_phase = (it >> 1) & 1u;
+                ok = mbar_wait_bounded(acc_empty_bar(buf), acc_phase ^ 1u, abort_flag, p.status,
+                                       kWaitMmaAccEmpty);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BLOCK_N;
+                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                    ok = mbar_wait_bounded(full_bar(stage), phase, abort_flag, p.status,
+                                           kWaitMmaFull);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_base + stage * L::kStageBytes;
+                    const uint32_t b_addr = a_addr + kABytes;
+                    const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024);
+                    const uint64_t b_desc =
+                        B_KN ? make_smem_desc(b_addr, 8192, 1024) : make_smem_desc(b_addr, 16, 1024);
+#pragma unroll
+                    for (int k = 0; k < kMmaPerStage; ++k) {
+                        tc_mma<KIND>(d_tmem, a_desc + 2u * k, b_desc + kBAdvance * k, idesc,
+                                     (kb | k) != 0 ? 1u : 0u);
+                    }
+                    tc_commit(empty_bar(stage));  // frees the stage when these MMAs retire
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) tc_commit(acc_full_bar(buf));
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------ epilogue ----------------------------------------
+        const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+        const int row_in_tile = quarter * 32 + lane;
+        int it = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+            int mb, nb;
+            tile_coords(t, p, mb, nb);
+            const int buf = it & 1;
+            const uint32_t acc_phase = (it >> 1) & 1u;
+            ok = mbar_wait_bounded(acc_full_bar(buf), acc_phase, abort_flag, p.status,
+                                   kWaitEpiAccFull);
+            ok = __all_sync(0xffffffffu, ok);  // the warp leaves together (tcgen05.ld is warp-wide)
+            if (!ok) break;
+            tc_fence_after();
+            const long long row = (long long)mb * kBlockM + row_in_tile;
+            const bool row_ok = row < p.M;
+            const int n0 = nb * kOutN;
+            const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BLOCK_N;
+            float sa = 1.0f;
+            if constexpr (EPI == EPI_SCALED_BF16) {
+                if (p.scale_a && row_ok) sa = p.scale_a[row];
+            }
+#pragma unroll 1
+            for (int c = 0; c < kOutN; c += 32) {
+                uint32_t v[32];
+                __syncwarp();
+                tmem_ld_32x32(t_row + c, v);
+                [[maybe_unused]] uint32_t u[32];
+                if constexpr (EPI == EPI_SWIGLU) tmem_ld_32x32(t_row + kOutN + c, u);
+                tmem_ld_wait();
+                const int col0 = n0 + c;
+                const bool full = col0 + 32 <= p.N;
+                if (!row_ok || col0 >= p.N) {
+                    // nothing to store for this thread; stay in step with the warp
+                } else if constexpr (EPI == EPI_S32) {
+                    int32_t *dst = reinterpret_cast<int32_t *>(p.C) + row * p.ldc + col0;
+                    if (full && p.vec_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<uint4 *>(dst + j) =
+                                make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < p.N) dst[j] = (int32_t)v[j];
+                    }
+                } else {
+                    float f[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float x = __uint_as_float(v[j]);
+                        const int col = min(col0 + j, p.N - 1);
+                        if constexpr (EPI == EPI_SWIGLU) {
+                            const float up = __uint_as_float(u[j]);
+                            x = (x / (1.0f + expf(-x))) * up;
+                        } else if constexpr (EPI == EPI_SCALED_BF16) {
+                            const float sb = p.scale_b ? __ldg(p.scale_b + col) : 1.0f;
+                            x = x * (sa * sb);
+                            if (p.bias) x += __ldg(p.bias + col);
+                        } else {
+                            if (p.bias) x += __ldg(p.bias + col);
+                            x = act_apply(x, p.act);
+                        }
+                        f[j] = x;
+                    }
+                    __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.C) + row * p.ldc + col0;
+                    if (full && p.vec_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8)
+                            *reinterpret_cast<uint4 *>(dst + j) =
+                                make_uint4(pack_bf16x2(f[j], f[j + 1]), pack_bf16x2(f[j + 2], f[j + 3]),
+                                           pack_bf16x2(f[j + 4], f[j + 5]), pack_bf16x2(f[j + 6], f[j + 7]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(f[j]);
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(acc_empty_bar(buf));
+        }
+    }
+
+    // ------------------------------ teardown --------------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (*abort_flag) {
+            // a wait ran out: give copies and MMAs still in flight time to land before the
+            // tensor memory goes back (bounded: about 200 microseconds)
+            const uint64_t t0 = globaltimer_ns();
+            while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+        }
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) ==
+                cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+// 2-D row-major tensor [rows, cols] of `elem` bytes with `ld` elements between rows; box of
+// box_cols x box_rows; 128-byte swizzle; out-of-range elements read as zero.
+static int encode_2d(CUtensorMap *tm, int kind, const void *base, int64_t rows, int64_t cols,
+                     int64_t ld, int box_cols, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return O64_ERR_CUDA;
+    const int elem = (kind == O64_KIND_BF16) ? 2 : 1;
+    const CUtensorMapDataType dt =
+        (kind == O64_KIND_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * elem};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(tm, dt, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? O64_OK : O64_ERR_CUDA;
+}
+
+template <int KIND, bool B_KN, int EPI, int BLOCK_N, int STAGES>
+static int launch_inst(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tb2,
+                       const UmmaParams &p, int grid, cudaStream_t stream) {
+    using L = SmemLayout<BLOCK_N, STAGES>;
+    auto kern = umma_gemm_kernel<KIND, B_KN, EPI, BLOCK_N, STAGES>;
+    static bool attr_set = false;  // per instantiation
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) !=
+            cudaSuccess)
+            return O64_ERR_CUDA;
+        attr_set = true;
+    }
+    kern<<<grid, kThreads, L::kDynamic, stream>>>(ta, tb, tb2, p);
+    return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
+}
+
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int umma_launch(const UmmaCall &c) {
+    const int elem = (c.kind == O64_KIND_BF16) ? 2 : 1;
+    if (c.M <= 0 || c.N <= 0 || c.K <= 0) return O64_ERR_RANK;
+    if (c.M > INT32_MAX || c.N > INT32_MAX || c.K > INT32_MAX) return O64_ERR_RANK;
+    if (c.kind != O64_KIND_BF16 && c.kind != O64_KIND_FP8 && c.kind != O64_KIND_S8)
+        return O64_ERR_DTYPE;
+    if (c.b_kn && c.kind != O64_KIND_BF16) return O64_ERR_DTYPE;
+    if (c.epi == EPI_SWIGLU && (!c.b_kn || !c.B2)) return O64_ERR_DTYPE;
+    // TMA needs 16-byte aligned bases and row pitches
+    if (!aligned16(c.A) || !aligned16(c.B) || (c.B2 && !aligned16(c.B2))) return O64_ERR_ALIGN;
+    if ((c.lda * elem) % 16 || (c.ldb * elem) % 16) return O64_ERR_ALIGN;
+    const int64_t b_cols = c.b_kn ? c.N : c.K;
+    if (c.lda < c.K || c.ldb < b_cols || c.ldc < c.N) return O64_ERR_CONFORM;
+
+    const o64_plan_t &pl = c.plan;
+    const int block_n = pl.tile_n;
+    const int block_k = kRowBytes / elem;
+    const int out_n = (c.epi == EPI_SWIGLU) ? block_n / 2 : block_n;
+
+    CUtensorMap ta, tb, tb2;
+    int rc = encode_2d(&ta, c.kind, c.A, c.M, c.K, c.lda, block_k, kBlockM);
+    if (rc) return rc;
+    if (!c.b_kn) {
+        rc = encode_2d(&tb, c.kind, c.B, c.N, c.K, c.ldb, block_k, block_n);
+        tb2 = tb;
+    } else {
+        rc = encode_2d(&tb, c.kind, c.B, c.K, c.N, c.ldb, 64, block_k);
+        tb2 = tb;
+        if (!rc && c.epi == EPI_SWIGLU) rc = encode_2d(&tb2, c.kind, c.B2, c.K, c.N, c.ldb, 64, block_k);
+    }
+    if (rc) return rc;
+
+    UmmaParams p;
+    p.M = (int)c.M;
+    p.N = (int)c.N;
+    p.K = (int)c.K;
+    p.C = c.C;
+    p.ldc = c.ldc;
+    p.bias = c.bias;
+    p.scale_a = c.scale_a;
+    p.scale_b = c.scale_b;
+    p.act = c.act;
+    p.num_m_tiles = (int)((c.M + kBlockM - 1) / kBlockM);
+    p.num_n_tiles = (int)((c.N + out_n - 1) / out_n);
+    p.group_m = pl.group_m > 0 ? pl.group_m : 8;
+    p.raster = pl.raster;
+    p.num_k_blocks = (int)((c.K + block_k - 1) / block_k);
+    const int out_elem = (c.epi == EPI_S32) ? 4 : 2;
+    p.vec_ok = aligned16(c.C) && ((c.ldc * out_elem) % 16 == 0);
+    p.status = c.status_word;
+    const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles;
+    const int grid = (int)(tiles < pl.num_ctas ? tiles : pl.num_ctas);
+
+#define O64_INST(KIND, BKN, EPI_, BN, ST) \
+    return launch_inst<KIND, BKN, EPI_, BN, ST>(ta, tb, tb2, p, grid, c.stream)
+
+    if (c.kind == O64_KIND_BF16) {
+        if (c.epi == EPI_SWIGLU) {
+            if (block_n == 256) O64_INST(MMA_F16, true, EPI_SWIGLU, 256, 4);
+            if (block_n == 128) O64_INST(MMA_F16, true, EPI_SWIGLU, 128, 6);
+        } else if (c.epi == EPI_BF16) {
+            if (c.b_kn) {
+                if (block_n == 256) O64_INST(MMA_F16, true, EPI_BF16, 256, 4);
+                if (block_n == 128) O64_INST(MMA_F16, true, EPI_BF16, 128, 6);
+            } else {
+                if (block_n == 256) O64_INST(MMA_F16, false, EPI_BF16, 256, 4);
+                if (block_n == 128) O64_INST(MMA_F16, false, EPI_BF16, 128, 6);
+            }
+        }
+    } else if (c.kind == O64_KIND_FP8 && c.epi == EPI_SCALED_BF16) {
+        if (block_n == 256) O64_INST(MMA_F8F6F4, false, EPI_SCALED_BF16, 256, 4);
+        if (block_n == 128) O64_INST(MMA_F8F6F4, false, EPI_SCALED_BF16, 128, 6);
+    } else if (c.kind == O64_KIND_S8 && c.epi == EPI_S32) {
+        if (block_n == 256) O64_INST(MMA_I8, false, EPI_S32, 256, 4);
+        if (block_n == 128) O64_INST(MMA_I8, false, EPI_S32, 128, 6);
+    }
+#undef O64_INST
+    return O64_ERR_DTYPE;
+}
+
+}  // namespace o64

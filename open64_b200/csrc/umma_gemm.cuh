@@ -1,0 +1,44 @@
+// Host-side interface of the tcgen05 GEMM kernels (umma_gemm.cu).
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "../../include/o64gemm.h"
+
+namespace o64 {
+
+enum : int { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_SCALED_BF16 = 2, EPI_S32 = 3 };
+
+// One GEMM on the tensor cores.  A is [M,K] row-major.  B is [N,K] row-major (b_kn == false)
+// or [K,N] row-major (b_kn == true, bf16 only).  For EPI_SWIGLU, B and B2 are the gate and up
+// weights, both [K,N], and C is [M,N].  Leading dimensions in elements.
+struct UmmaCall {
+    int kind;  // O64_KIND_BF16 / O64_KIND_FP8 / O64_KIND_S8
+    bool b_kn;
+    int epi;
+    int64_t M, N, K;
+    const void *A;
+    int64_t lda;
+    const void *B;
+    const void *B2;
+    int64_t ldb;
+    void *C;
+    int64_t ldc;
+    const float *bias;
+    const float *scale_a;
+    const float *scale_b;
+    int act;
+    o64_plan_t plan;
+    int *status_word;  // device int, 0 = ok
+    cudaStream_t stream;
+};
+
+// Validates alignment, encodes the tensor maps and launches.  Returns O64_OK or an error code.
+int umma_launch(const UmmaCall &call);
+
+// Fills tile_*, stages, group_m, num_ctas, ... for a shape; applies `pin` (fields != 0) and the
+// O64_LNO environment override.  Pure host code.
+void plan_choose(int kind, int epi, int64_t M, int64_t N, int64_t K, int num_sms,
+                 const o64_plan_t *pin, o64_plan_t *out);
+
+}  // namespace o64

@@ -1,0 +1,235 @@
+"""Host-side harness over the C ABI: torch tensors in, torch tensors out.
+
+torch is plumbing here (device memory, streams, process groups); all arithmetic runs in
+libo64gemm.so.  The method names follow the operator surface the engine serves:
+``linear`` / ``matmul`` with bias and activation epilogues, the scaled fp8 and int8 products,
+and the Fortran-ABI compat calls (``sgemm``, ``s4gemmx``, ``s4gemvx``) that the reference's
+runtime binds (osprey/libfi/matrix/matmul_s4s4.c:87-111, mmx_dlutil.c:122-136).
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import (ACT_GELU_ERF, ACT_GELU_TANH, ACT_NONE, ACT_RELU, ACT_SILU, GATHER_NONE,
+                   GATHER_ROWMAJOR, GATHER_SLABS, KIND_BF16, KIND_F32, KIND_FP8, KIND_S8, O64Error,
+                   Plan, check)
+
+_ACTS = {None: ACT_NONE, "none": ACT_NONE, "relu": ACT_RELU, "gelu_tanh": ACT_GELU_TANH,
+         "gelu": ACT_GELU_ERF, "gelu_erf": ACT_GELU_ERF, "silu": ACT_SILU}
+
+
+def _act(a):
+    if isinstance(a, int):
+        return a
+    return _ACTS[a]
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _stream(t):
+    if t.is_cuda:
+        return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+    return None
+
+
+def _rowmajor(t, name):
+    if t.dim() != 2:
+        raise O64Error(_lib.ERR_RANK, f"{name}: rank {t.dim()}")
+    if t.stride(1) != 1 and t.shape[1] != 1:
+        t = t.contiguous()
+    return t
+
+
+class Engine:
+    """One handle on one device.  Not thread-safe; make one per thread or per stream user."""
+
+    def __init__(self, device=0):
+        self._h = ctypes.c_void_p()
+        self.lib = _lib.lib()
+        if isinstance(device, torch.device):
+            device = device.index or 0
+        self.device = int(device)
+        check(self.lib.o64_create(ctypes.byref(self._h), self.device), "o64_create")
+
+    def close(self):
+        if self._h:
+            self.lib.o64_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- plans -------------------------------------------------------------------------
+    def plan_get(self, kind, M, N, K):
+        p = Plan()
+        check(self.lib.o64_plan_get(self._h, kind, M, N, K, ctypes.byref(p)), "o64_plan_get")
+        return p.as_dict()
+
+    def plan_set(self, kind, **fields):
+        if not fields:
+            check(self.lib.o64_plan_set(self._h, kind, None), "o64_plan_set")
+            return
+        p = Plan()
+        for k, v in fields.items():
+            setattr(p, k, v)
+        check(self.lib.o64_plan_set(self._h, kind, ctypes.byref(p)), "o64_plan_set")
+
+    def last_status(self, stream=None):
+        """Synchronises and returns (status, detail); status is 0 or ERR_TIMEOUT."""
+        detail = ctypes.c_int(0)
+        s = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream) if stream is None else stream
+        st = self.lib.o64_last_status(self._h, s, ctypes.byref(detail))
+        return st, detail.value
+
+    # ---- native layer ------------------------------------------------------------------
+    def linear_f32(self, A, B, bias=None, act="none", out=None):
+        """act(A @ B + bias), fp32; A [M,K], B [K,N]."""
+        A = _rowmajor(A, "A")
+        B = _rowmajor(B, "B")
+        M, K = A.shape
+        if B.shape[0] != K:
+            raise O64Error(_lib.ERR_CONFORM, "linear_f32")
+        N = B.shape[1]
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.float32, device=A.device)
+        check(self.lib.o64_linear_f32(self._h, M, N, K, _ptr(A), A.stride(0), _ptr(B), B.stride(0),
+                                      _ptr(bias), _ptr(out), out.stride(0), _act(act), _stream(A)),
+              "o64_linear_f32")
+        return out
+
+    def gemm_bf16(self, A, B, transB=True, bias=None, act="none", out=None):
+        """act(A @ op(B) + bias); A [M,K] bf16; B [N,K] when transB else [K,N]; bf16 result."""
+        A = _rowmajor(A, "A")
+        B = _rowmajor(B, "B")
+        M, K = A.shape
+        N = B.shape[0] if transB else B.shape[1]
+        if (B.shape[1] if transB else B.shape[0]) != K:
+            raise O64Error(_lib.ERR_CONFORM, "gemm_bf16")
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
+        epi = _lib.Epilogue(_ptr(bias), _act(act))
+        check(self.lib.o64_gemm_bf16(self._h, M, N, K, _ptr(A), A.stride(0), _ptr(B), B.stride(0),
+                                     1 if transB else 0, _ptr(out), out.stride(0), ctypes.byref(epi),
+                                     _stream(A)), "o64_gemm_bf16")
+        return out
+
+    def swiglu(self, X, Wg, Wu, out=None):
+        """bf16(silu(X @ Wg) * (X @ Wu)); X [M,K], Wg/Wu [K,N] with one leading dimension."""
+        X = _rowmajor(X, "X")
+        Wg = _rowmajor(Wg, "Wg")
+        Wu = _rowmajor(Wu, "Wu")
+        M, K = X.shape
+        if Wg.shape != Wu.shape or Wg.shape[0] != K or Wg.stride(0) != Wu.stride(0):
+            raise O64Error(_lib.ERR_CONFORM, "swiglu")
+        N = Wg.shape[1]
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=X.device)
+        check(self.lib.o64_gemm_bf16_swiglu(self._h, M, N, K, _ptr(X), X.stride(0), _ptr(Wg), _ptr(Wu),
+                                            Wg.stride(0), _ptr(out), out.stride(0), _stream(X)),
+              "o64_gemm_bf16_swiglu")
+        return out
+
+    def mlp_swiglu(self, X, Wg, Wu, Wd, h=None, out=None):
+        """(silu(X Wg) * (X Wu)) Wd with the SiLU-multiply fused into the first GEMM."""
+        h = self.swiglu(X, Wg, Wu, out=h)
+        return self.gemm_bf16(h, Wd, transB=False, out=out)
+
+    def gemm_fp8_scaled(self, A8, B8, scaleA=None, scaleB=None, bias=None, out=None):
+        """bf16((A8 @ B8^T) * sA[m] * sB[n] + bias[n]); A8 [M,K], B8 [N,K] e4m3."""
+        A8 = _rowmajor(A8, "A8")
+        B8 = _rowmajor(B8, "B8")
+        M, K = A8.shape
+        N = B8.shape[0]
+        if B8.shape[1] != K:
+            raise O64Error(_lib.ERR_CONFORM, "gemm_fp8_scaled")
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=A8.device)
+        check(self.lib.o64_gemm_fp8_scaled(self._h, M, N, K, _ptr(A8), A8.stride(0), _ptr(B8),
+                                           B8.stride(0), _ptr(scaleA), _ptr(scaleB), _ptr(bias),
+                                           _ptr(out), out.stride(0), _stream(A8)), "o64_gemm_fp8_scaled")
+        return out
+
+    def gemm_s8(self, A, B, out=None):
+        """A [M,K] int8 times B [N,K]^T int8 -> int32, exact."""
+        A = _rowmajor(A, "A")
+        B = _rowmajor(B, "B")
+        M, K = A.shape
+        N = B.shape[0]
+        if B.shape[1] != K:
+            raise O64Error(_lib.ERR_CONFORM, "gemm_s8")
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.int32, device=A.device)
+        check(self.lib.o64_gemm_s8s8_s32(self._h, M, N, K, _ptr(A), A.stride(0), _ptr(B), B.stride(0),
+                                         _ptr(out), out.stride(0), _stream(A)), "o64_gemm_s8s8_s32")
+        return out
+
+    def naive(self, kind, A, B, transB=True, scaleA=None, scaleB=None, bias=None, act="none"):
+        """One-thread-per-output device reference; fp32 result (int32 for KIND_S8)."""
+        M, K = A.shape
+        N = B.shape[0] if transB else B.shape[1]
+        out = torch.empty((M, N), dtype=torch.int32 if kind == KIND_S8 else torch.float32,
+                          device=A.device)
+        check(self.lib.o64_naive_gemm(self._h, kind, M, N, K, _ptr(A), A.stride(0), _ptr(B), B.stride(0),
+                                      1 if transB else 0, _ptr(scaleA), _ptr(scaleB), _ptr(bias),
+                                      _act(act), _ptr(out), out.stride(0), _stream(A)), "o64_naive_gemm")
+        return out
+
+    # ---- multi-GPU ---------------------------------------------------------------------
+    def comm_init_from_process_group(self, group=None):
+        """Binds an NCCL communicator over the ranks of a torch.distributed group: rank 0
+        makes the id, the group's broadcast carries the bytes."""
+        import torch.distributed as dist
+        rank = dist.get_rank(group)
+        world = dist.get_world_size(group)
+        buf = (ctypes.c_char * _lib.UNIQUE_ID_BYTES)()
+        if rank == 0:
+            check(self.lib.o64_comm_unique_id(buf), "o64_comm_unique_id")
+        obj = [bytes(buf) if rank == 0 else None]
+        dist.broadcast_object_list(obj, src=dist.get_global_rank(group, 0) if group else 0, group=group)
+        idb = ctypes.create_string_buffer(obj[0], _lib.UNIQUE_ID_BYTES)
+        check(self.lib.o64_comm_init(self._h, idb, rank, world), "o64_comm_init")
+        return rank, world
+
+    def gemm_s8_sharded(self, A, B_slab, N, gather=GATHER_ROWMAJOR, out=None, workspace=None):
+        """Column-sharded int8 GEMM: this rank owns B_slab [N/g, K]; `out` is the full [M,N]
+        int32 (row-major, or slab-major [g][M][N/g] for GATHER_SLABS)."""
+        M, K = A.shape
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.int32, device=A.device)
+        check(self.lib.o64_gemm_s8_sharded(self._h, M, N, K, _ptr(A), A.stride(0), _ptr(B_slab),
+                                           B_slab.stride(0), _ptr(out), gather, _ptr(workspace),
+                                           _stream(A)), "o64_gemm_s8_sharded")
+        return out
+
+    # ---- compat layer (Fortran ABI, synchronous) -----------------------------------------
+    def sgemm(self, transa, transb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc):
+        ci, cf = ctypes.c_int, ctypes.c_float
+        self.lib.sgemm_(transa.encode(), transb.encode(), ctypes.byref(ci(m)), ctypes.byref(ci(n)),
+                        ctypes.byref(ci(k)), ctypes.byref(cf(alpha)), _ptr(a), ctypes.byref(ci(lda)),
+                        _ptr(b), ctypes.byref(ci(ldb)), ctypes.byref(cf(beta)), _ptr(c),
+                        ctypes.byref(ci(ldc)))
+        check(self.lib.o64_compat_last_status(), "sgemm_")
+        return c
+
+    def s4gemmx(self, m, n, k, alpha, a, inc1a, inc2a, b, inc1b, inc2b, beta, c, inc1c, inc2c):
+        ci, cf = ctypes.c_int, ctypes.c_float
+        r = lambda v: ctypes.byref(ci(v))
+        self.lib._s4gemmx__(r(m), r(n), r(k), ctypes.byref(cf(alpha)), _ptr(a), r(inc1a), r(inc2a),
+                            _ptr(b), r(inc1b), r(inc2b), ctypes.byref(cf(beta)), _ptr(c), r(inc1c),
+                            r(inc2c))
+        check(self.lib.o64_compat_last_status(), "_s4gemmx__")
+        return c
+
+    def s4gemvx(self, m, n, alpha, a, incca, incra, x, incx, beta, y, incy):
+        ci, cf = ctypes.c_int, ctypes.c_float
+        r = lambda v: ctypes.byref(ci(v))
+        self.lib._s4gemvx__(r(m), r(n), ctypes.byref(cf(alpha)), _ptr(a), r(incca), r(incra), _ptr(x),
+                            r(incx), ctypes.byref(cf(beta)), _ptr(y), r(incy))
+        check(self.lib.o64_compat_last_status(), "_s4gemvx__")
+        return y

@@ -1,0 +1,326 @@
+#!/usr/bin/env python
+"""Benchmark of the GEMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-extras]
+
+Headline (`value`): bf16 NT GEMM C = A B^T, M = N = K = 8192, operands resident in HBM, one
+step = one GEMM launch, timed with CUDA events over K back-to-back steps after W warm-ups.
+Operands (268 MB) plus result (134 MB) exceed the 126 MB L2, so no explicit flush is used.
+At N > 1 (torchrun, one rank per GPU) the linear is column-sharded: every rank holds A and its
+own [8192, 8192] slab of a [8192*N, 8192] weight, so per-GPU work is fixed (weak scaling) and
+no collective is on the data path; `value` is the whole-job TFLOP/s (max time over ranks).
+
+`e2e`: the same GEMM through the C ABI with HOST operands (pinned): host->device copies of A
+and B and the device->host copy of C are inside the timed region.
+`cpu_baseline`: the CPU oracle (a port of the reference's loop nest; the reference's own Fortran
+kernels do not build here) timed on the host cores on a bounded row slab of the same GEMM.
+`--impl reference` runs only that CPU arm.
+
+All data is synthetic (seeded normal values rounded to bf16).
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M = N = K = 8192
+FLOPS = 2 * M * N * K                       # algorithmic flops per launch
+ALGO_BYTES = (M * K + N * K) * 2 + M * N * 2  # operands read once + result written once
+METRIC = "gemm_bf16_tflops (C=A*B^T, M=N=K=8192, fp32 accumulate, bf16 out)"
+NOMINAL_BF16_TFLOPS = 2250.0
+NOMINAL_8BIT_TOPS = 4500.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel, from the
+# ncu capture summarised in profiles/ (None until a capture exists)
+NCU_TRAFFIC_BYTES = 1124236168  # profiles/umma_gemm_bf16_c2_8192.md: 1.003 GB read + 121.0 MB written
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return {"burst": float(d["bf16_tflops"]), "sustained": float(d["bf16_tflops_sustained"]),
+                "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    except Exception:  # noqa: BLE001
+        return {"burst": 1590.0, "sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while a region runs."""
+
+    def __init__(self, index, period_s=0.002):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:  # noqa: BLE001
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons",
+                              getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons", None))
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                if get_reasons:
+                    r = get_reasons(self.h)
+                    for k, bit in names.items():
+                        if r & bit:
+                            self.reasons.add(k)
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=2)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def cpu_baseline(budget_s=12.0, rows=128):
+    """The oracle's bf16 nest on a [rows, K] x [N, K]^T slab of the headline GEMM, repeated until
+    `budget_s` of CPU time has gone; returns TFLOP/s and what was run."""
+    import numpy as np
+    import oracle
+    rng = np.random.default_rng(1002)
+    A = (rng.standard_normal((rows, K)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    B = (rng.standard_normal((N, K)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    oracle.gemm_bf16(A[:8], B, transB=True)  # warm the threads
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        oracle.gemm_bf16(A, B, transB=True)
+        reps += 1
+        if time.perf_counter() - t0 >= budget_s:
+            break
+    dt = time.perf_counter() - t0
+    tflops = 2.0 * rows * N * K * reps / dt / 1e12
+    return {"value": tflops, "unit": "TFLOP/s", "cores": oracle.num_threads(), "kind": "port",
+            "sample": f"{reps} x ({rows} rows x N={N} x K={K}) slab of the same GEMM, "
+                      f"{dt:.1f} s, gcc -O3 loop nest (opencc and the Fortran kernels do not build here)"}
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    t_all = time.perf_counter()
+    for _ in range(args.warmup):
+        cpu_baseline(budget_s=0.5)
+    per_step = max(1.0, min(10.0, 60.0 / max(args.steps, 1)))
+    vals = [cpu_baseline(budget_s=per_step) for _ in range(args.steps)]
+    v = statistics.mean(x["value"] for x in vals)
+    base = dict(vals[-1], value=v)
+    ms = FLOPS / (v * 1e12) * 1e3
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "C2 bf16 NT GEMM 8192x8192x8192 (extrapolated from row slabs on the host cores)"},
+        "cpu_baseline": base,
+        "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": time.perf_counter() - t_all,
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="o64", choices=["o64", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the secondary configurations")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import open64_b200 as o
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: no CUDA device is visible (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    eng = o.Engine(local_rank)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def time_steps(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1) / steps)
+
+    # ---- headline: C2, operands resident in HBM ---------------------------------------
+    A, B = o.workloads.c2_gemm_bf16(M, N, K)                    # A replicated on every rank
+    if world > 1:                                               # this rank's weight slab
+        g = torch.Generator().manual_seed(o.workloads.SEEDS["c2"] + 100 + rank)
+        B = torch.randn((N, K), generator=g).to(torch.bfloat16)
+    A_host, B_host = A.pin_memory(), B.pin_memory()
+    Ad, Bd = A_host.to(dev), B_host.to(dev)
+    C = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    plan = eng.plan_get(o.KIND_BF16, M, N, K)
+
+    with ClockSampler(local_rank) as clk:
+        ms = time_steps(lambda: eng.gemm_bf16(Ad, Bd, transB=True, out=C), args.steps, args.warmup)
+    clocks = clk.summary()
+    st, detail = eng.last_status()
+    if st != 0:
+        raise SystemExit(f"device status {st} (detail 0x{detail:x})")
+    value = world * FLOPS / (ms * 1e-3) / 1e12
+
+    # ---- e2e: host operands through the C ABI -------------------------------------------
+    C_host = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    e2e_steps = max(3, args.steps // 10)
+    for _ in range(2):
+        eng.gemm_bf16(A_host, B_host, transB=True, out=C_host)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        eng.gemm_bf16(A_host, B_host, transB=True, out=C_host)   # synchronous: result is on the host
+    torch.cuda.synchronize()
+    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3 / e2e_steps)
+    e2e = {"value": world * FLOPS / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+           "h2d_bytes_per_step": (M * K + N * K) * 2, "d2h_bytes_per_step": M * N * 2,
+           "ms_per_step": e2e_ms, "steps": e2e_steps}
+
+    peaks = measured_peaks()
+    timed_s = ms * 1e-3 * args.steps
+    peak = peaks["burst"] if timed_s < 1.0 else peaks["sustained"]
+    achieved = FLOPS / (ms * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES,
+                "peak_kind": ("burst" if timed_s < 1.0 else "sustained") + " cuBLAS bf16, of " + peaks["source"],
+                "frac_of_nominal_2250": achieved / NOMINAL_BF16_TFLOPS,
+                "algorithmic_bytes": ALGO_BYTES}
+
+    out = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "C2 bf16 NT GEMM M=N=K=8192 per GPU" +
+                   (f"; column slab of a [{N * world}, {K}] weight per rank, no collective" if world > 1 else ""),
+                   "plan": {k: plan[k] for k in ("tile_m", "tile_n", "tile_k", "stages", "cta_group", "group_m", "num_ctas")},
+                   "l2": "operands 268 MB + result 134 MB exceed the 126 MB L2; no flush between steps"},
+        "per_gpu_tflops": value / world,
+        "roofline": roofline, "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks,
+    }
+
+    # ---- secondary configurations (short runs, reported beside the headline) --------------
+    if not args.no_extras:
+        ex = {}
+        s2, w2 = max(5, args.steps // 5), 3
+        a1, b1, bias1 = (t.to(dev) for t in o.workloads.c1_linear_f32())
+        y1 = torch.empty(512, 512, device=dev)
+        t = time_steps(lambda: eng.linear_f32(a1, b1, bias1, "relu", out=y1), 50, 5)
+        ex["c1_linear_f32_512"] = {"us": t * 1e3, "gflops": 2 * 512 ** 3 / (t * 1e-3) / 1e9}
+        x, Wg, Wu, Wd = (t_.to(dev) for t_ in o.workloads.c3_swiglu())
+        h = torch.empty(4096, 14336, dtype=torch.bfloat16, device=dev)
+        o3 = torch.empty(4096, 4096, dtype=torch.bfloat16, device=dev)
+        t = time_steps(lambda: eng.mlp_swiglu(x, Wg, Wu, Wd, h=h, out=o3), s2, w2)
+        f3 = 1443109011456
+        ex["c3_swiglu_mlp"] = {"ms": t, "tflops": f3 / (t * 1e-3) / 1e12,
+                               "frac_of_nominal_2250": f3 / (t * 1e-3) / 1e12 / NOMINAL_BF16_TFLOPS}
+        del x, Wg, Wu, Wd, h, o3
+        A8, W8, sA, sB, b4 = (t_.to(dev) for t_ in o.workloads.c4_fp8())
+        c4 = torch.empty(4096, 8192, dtype=torch.bfloat16, device=dev)
+        t = time_steps(lambda: eng.gemm_fp8_scaled(A8, W8, sA, sB, b4, out=c4), s2, w2)
+        f4 = 2 * 4096 * 8192 * 8192
+        ex["c4_fp8_scaled"] = {"ms": t, "tflops": f4 / (t * 1e-3) / 1e12,
+                               "frac_of_nominal_4500": f4 / (t * 1e-3) / 1e12 / NOMINAL_8BIT_TOPS}
+        del A8, W8, c4
+        # C5: the int8 GEMM, column-sharded over the ranks (strong scaling: total work fixed)
+        M5, N5, K5 = 16384, 8192, 8192
+        A5, B5 = o.workloads.c5_int8(M5, N5, K5)
+        A5d = A5.to(dev)
+        B5d = o.workloads.shard_rows(B5, rank, world).contiguous().to(dev)
+        del A5, B5
+        if world > 1:
+            eng.comm_init_from_process_group()
+        c5 = torch.empty((M5, N5), dtype=torch.int32, device=dev)
+        f5 = 2 * M5 * N5 * K5
+        t = time_steps(lambda: eng.gemm_s8_sharded(A5d, B5d, N5, gather=o.GATHER_NONE, out=c5), s2, w2)
+        ex["c5_int8_sharded_gemm_only"] = {"ms": t, "tops": f5 / (t * 1e-3) / 1e12,
+                                           "frac_of_nominal_4500_per_gpu": f5 / (t * 1e-3) / 1e12 / NOMINAL_8BIT_TOPS / world}
+        if world > 1:
+            t = time_steps(lambda: eng.gemm_s8_sharded(A5d, B5d, N5, gather=o.GATHER_SLABS, out=c5), s2, w2)
+            ex["c5_int8_sharded_allgather_slabs"] = {"ms": t, "tops": f5 / (t * 1e-3) / 1e12}
+            ws = torch.empty((M5, N5), dtype=torch.int32, device=dev)
+            t = time_steps(lambda: eng.gemm_s8_sharded(A5d, B5d, N5, gather=o.GATHER_ROWMAJOR, out=c5, workspace=ws), s2, w2)
+            ex["c5_int8_sharded_allgather_rowmajor"] = {"ms": t, "tops": f5 / (t * 1e-3) / 1e12}
+        st, detail = eng.last_status()
+        if st != 0:
+            raise SystemExit(f"device status {st} (detail 0x{detail:x})")
+        out["other_configs"] = ex
+
+    if rank == 0 and world == 1 and not args.no_cpu:
+        out["cpu_baseline"] = cpu_baseline()
+
+    if world > 1:
+        dist.barrier()
+    if rank == 0:
+        print(json.dumps(out))
+    eng.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -122,6 +122,10 @@ const char *o64_version(void);
  * osprey/common/com/wn_pragmas.h:143-151) does the same for every handle. */
 int o64_plan_get(o64_handle_t h, int kind, int64_t M, int64_t N, int64_t K, o64_plan_t *plan);
 int o64_plan_set(o64_handle_t h, int kind, const o64_plan_t *plan);
+/* The chooser itself, without a device: the plan for a machine of `num_sms` SMs, with `pin`
+ * (may be NULL) and O64_LNO applied.  `swiglu` != 0 scores the fused gate/up GEMM. */
+int o64_plan_model(int kind, int swiglu, int64_t M, int64_t N, int64_t K, int num_sms,
+                   const o64_plan_t *pin, o64_plan_t *plan);
 
 /* ---- native layer -------------------------------------------------------------------
  * Row-major operands; ld* in elements.  A is [M,K].  B is [K,N] when transB == 0 and

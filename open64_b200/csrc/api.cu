@@ -213,6 +213,15 @@ extern "C" int o64_plan_get(o64_handle_t h, int kind, int64_t M, int64_t N, int6
     return O64_OK;
 }
 
+extern "C" int o64_plan_model(int kind, int swiglu, int64_t M, int64_t N, int64_t K, int num_sms,
+                              const o64_plan_t *pin, o64_plan_t *plan) {
+    if (!plan || kind < O64_KIND_BF16 || kind > O64_KIND_S8) return O64_ERR_RANK;
+    if (M <= 0 || N <= 0 || K <= 0 || num_sms <= 0) return O64_ERR_RANK;
+    if (swiglu && kind != O64_KIND_BF16) return O64_ERR_DTYPE;
+    plan_choose(kind, swiglu ? EPI_SWIGLU : EPI_BF16, M, N, K, num_sms, pin, plan);
+    return O64_OK;
+}
+
 // ---- host-operand staging ---------------------------------------------------------------------
 static bool is_host_ptr(const void *p) {
     if (!p) return false;
@@ -292,7 +301,7 @@ extern "C" int o64_linear_f32(o64_handle_t h, int64_t M, int64_t N, int64_t K, c
     if (!h || M < 0 || N < 0 || K < 0) return O64_ERR_RANK;
     if (act < O64_ACT_NONE || act > O64_ACT_SILU) return O64_ERR_RANK;
     if (M == 0 || N == 0) return O64_OK;
-    if (!A || !B || !Y) return O64_ERR_RANK;
+    if (!Y || (K > 0 && (!A || !B))) return O64_ERR_RANK;  // K == 0: the empty sum, Y = act(bias)
     if (lda < K || ldb < N || ldy < N) return O64_ERR_CONFORM;
     DeviceGuard g(h->device);
     cudaStream_t s = (cudaStream_t)stream;

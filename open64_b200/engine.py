@@ -185,15 +185,18 @@ class Engine:
         """Binds an NCCL communicator over the ranks of a torch.distributed group: rank 0
         makes the id, the group's broadcast carries the bytes."""
         import torch.distributed as dist
+        from .sharded import broadcast_unique_id
         rank = dist.get_rank(group)
         world = dist.get_world_size(group)
-        buf = (ctypes.c_char * _lib.UNIQUE_ID_BYTES)()
-        if rank == 0:
+
+        def make_id():
+            buf = (ctypes.c_char * _lib.UNIQUE_ID_BYTES)()
             check(self.lib.o64_comm_unique_id(buf), "o64_comm_unique_id")
-        obj = [bytes(buf) if rank == 0 else None]
-        dist.broadcast_object_list(obj, src=dist.get_global_rank(group, 0) if group else 0, group=group)
-        idb = ctypes.create_string_buffer(obj[0], _lib.UNIQUE_ID_BYTES)
-        check(self.lib.o64_comm_init(self._h, idb, rank, world), "o64_comm_init")
+            return bytes(buf)
+
+        idb = broadcast_unique_id(make_id, group)
+        check(self.lib.o64_comm_init(self._h, ctypes.create_string_buffer(idb, _lib.UNIQUE_ID_BYTES),
+                                     rank, world), "o64_comm_init")
         return rank, world
 
     def gemm_s8_sharded(self, A, B_slab, N, gather=GATHER_ROWMAJOR, out=None, workspace=None):

@@ -1,0 +1,162 @@
+"""GPU: the tcgen05 GEMM kernels through the C ABI against the CPU oracle.
+bf16 / fp8 gate: max|y - ref| / max|ref| <= 2e-2 against the fp32 loop nest on the upcast or
+dequantised operands.  int8 -> int32: bit exact."""
+import numpy as np
+import pytest
+import torch
+
+import open64_b200 as o
+import oracle
+from util import TOL_LOWP, bits16, bits8, from_bits16, from_bits8_e4m3, relmax
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+ACTS = {"none": oracle.ACT_NONE, "relu": oracle.ACT_RELU, "gelu_tanh": oracle.ACT_GELU_TANH,
+        "gelu_erf": oracle.ACT_GELU_ERF, "silu": oracle.ACT_SILU}
+
+# one tile, several K blocks, ragged edges in every dimension, several tiles per CTA
+SHAPES = [(128, 256, 64), (1, 8, 8), (7, 24, 40), (100, 200, 72), (129, 257, 136), (300, 520, 264),
+          (256, 512, 1024), (640, 1536, 192)]
+
+
+def _bf16_case(M, N, K, transB, seed=0):
+    g = torch.Generator().manual_seed(seed + M * 131 + N * 17 + K)
+    A = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    B = torch.randn((N, K) if transB else (K, N), generator=g).to(torch.bfloat16)
+    return A, B
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("transB", [True, False])
+def test_bf16_shapes(eng, shape, transB):
+    M, N, K = shape
+    if not transB and N % 8:
+        pytest.skip("[K,N] operand needs a 16-byte row pitch")
+    A, B = _bf16_case(M, N, K, transB)
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    eng.gemm_bf16(A.to(DEV), B.to(DEV), transB=transB, out=C)
+    ref = oracle.gemm_bf16(bits16(A), bits16(B), transB=transB)
+    assert relmax(C.float().cpu().numpy(), ref) <= TOL_LOWP
+
+
+def test_bf16_golden_fixture(eng, golden):
+    A = from_bits16(golden["c2_A"], DEV)
+    B = from_bits16(golden["c2_B"], DEV)
+    C = eng.gemm_bf16(A, B, transB=True)
+    assert relmax(C.float().cpu().numpy(), golden["c2_C"]) <= TOL_LOWP
+
+
+@pytest.mark.parametrize("act", list(ACTS))
+def test_bf16_bias_and_activation_epilogues(eng, act):
+    M, N, K = 200, 328, 136
+    A, B = _bf16_case(M, N, K, True, seed=5)
+    A = (A.float() * 0.2).to(torch.bfloat16)
+    bias = torch.randn(N, generator=torch.Generator().manual_seed(9))
+    C = eng.gemm_bf16(A.to(DEV), B.to(DEV), transB=True, bias=bias.to(DEV), act=act)
+    ref = oracle.gemm_bf16(bits16(A), bits16(B), bias=bias.numpy(), act=ACTS[act], transB=True)
+    assert relmax(C.float().cpu().numpy(), ref) <= TOL_LOWP
+
+
+def test_bf16_both_tile_widths_and_rasters(eng):
+    M, N, K = 700, 1100, 200
+    A, B = _bf16_case(M, N, K, True, seed=2)
+    ref = oracle.gemm_bf16(bits16(A), bits16(B), transB=True)
+    Ad, Bd = A.to(DEV), B.to(DEV)
+    try:
+        for pin in (dict(tile_n=128), dict(tile_n=256), dict(tile_n=256, group_m=1),
+                    dict(tile_n=128, group_m=3, raster=1), dict(tile_n=256, num_ctas=5)):
+            eng.plan_set(o.KIND_BF16, **pin)
+            C = eng.gemm_bf16(Ad, Bd, transB=True)
+            assert relmax(C.float().cpu().numpy(), ref) <= TOL_LOWP, pin
+    finally:
+        eng.plan_set(o.KIND_BF16)
+
+
+def test_bf16_padded_leading_dimensions_and_unaligned_result(eng):
+    M, N, K = 150, 200, 96
+    g = torch.Generator().manual_seed(4)
+    Ap = torch.randn(M, K + 8, generator=g).to(torch.bfloat16).to(DEV)
+    Bp = torch.randn(N, K + 16, generator=g).to(torch.bfloat16).to(DEV)
+    Cp = torch.full((M, N + 3), 5.0, dtype=torch.bfloat16, device=DEV)   # odd pitch: scalar stores
+    eng.gemm_bf16(Ap[:, :K], Bp[:, :K], transB=True, out=Cp[:, :N])
+    ref = oracle.gemm_bf16(bits16(Ap[:, :K].contiguous()), bits16(Bp[:, :K].contiguous()), transB=True)
+    assert relmax(Cp[:, :N].float().cpu().numpy(), ref) <= TOL_LOWP
+    assert (Cp[:, N:] == 5.0).all()
+
+
+def test_bf16_host_operands(eng):
+    A, B = _bf16_case(130, 136, 72, True, seed=8)
+    C = eng.gemm_bf16(A, B, transB=True)
+    assert not C.is_cuda
+    ref = oracle.gemm_bf16(bits16(A), bits16(B), transB=True)
+    assert relmax(C.float().numpy(), ref) <= TOL_LOWP
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 64), (32, 48, 64), (300, 264, 136), (512, 1024, 320)])
+def test_swiglu(eng, shape):
+    M, N, K = shape
+    g = torch.Generator().manual_seed(M + N + K)
+    X = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    Wg = (torch.randn(K, N, generator=g) * 0.1).to(torch.bfloat16)
+    Wu = (torch.randn(K, N, generator=g) * 0.1).to(torch.bfloat16)
+    H = eng.swiglu(X.to(DEV), Wg.to(DEV), Wu.to(DEV))
+    ref = oracle.bf16_to_f32(oracle.swiglu_bf16(bits16(X), bits16(Wg), bits16(Wu)))
+    assert relmax(H.float().cpu().numpy(), ref) <= TOL_LOWP
+
+
+def test_swiglu_golden_and_mlp(eng, golden):
+    X, Wg, Wu = (from_bits16(golden[k], DEV) for k in ("c3_X", "c3_Wg", "c3_Wu"))
+    H = eng.swiglu(X, Wg, Wu)
+    assert relmax(H.float().cpu().numpy(), golden["c3_H"]) <= TOL_LOWP
+    # the whole MLP: h stays bf16 between the two GEMMs, in the oracle too
+    x, wg, wu, wd = o.workloads.c3_swiglu(96, 128, 192)
+    out = eng.mlp_swiglu(x.to(DEV), wg.to(DEV), wu.to(DEV), wd.to(DEV))
+    h = oracle.swiglu_bf16(bits16(x), bits16(wg), bits16(wu))
+    ref = oracle.gemm_bf16(h, bits16(wd), transB=False)
+    assert relmax(out.float().cpu().numpy(), ref) <= TOL_LOWP
+
+
+@pytest.mark.parametrize("shape", [(128, 256, 128), (5, 16, 16), (100, 200, 144), (300, 520, 400),
+                                   (512, 768, 1024)])
+def test_fp8_scaled(eng, shape):
+    M, N, K = shape
+    A8, W8, sA, sB, bias = o.workloads.c4_fp8(M, N, K, seed=M + N + K)
+    C = eng.gemm_fp8_scaled(A8.to(DEV), W8.to(DEV), sA.to(DEV), sB.to(DEV), bias.to(DEV))
+    ref = oracle.gemm_fp8_scaled(bits8(A8), bits8(W8), sA.numpy(), sB.numpy(), bias.numpy())
+    assert relmax(C.float().cpu().numpy(), ref) <= TOL_LOWP
+    # scales and bias are optional
+    C2 = eng.gemm_fp8_scaled(A8.to(DEV), W8.to(DEV))
+    ref2 = oracle.gemm_fp8_scaled(bits8(A8), bits8(W8))
+    assert relmax(C2.float().cpu().numpy(), ref2) <= TOL_LOWP
+
+
+def test_fp8_golden_fixture(eng, golden):
+    A8 = from_bits8_e4m3(golden["c4_A8"], DEV)
+    B8 = from_bits8_e4m3(golden["c4_B8"], DEV)
+    sA, sB, bias = (torch.from_numpy(golden[k]).to(DEV) for k in ("c4_sA", "c4_sB", "c4_bias"))
+    C = eng.gemm_fp8_scaled(A8, B8, sA, sB, bias)
+    assert relmax(C.float().cpu().numpy(), golden["c4_C"]) <= TOL_LOWP
+
+
+@pytest.mark.parametrize("shape", [(128, 256, 128), (1, 4, 16), (3, 20, 48), (100, 200, 144),
+                                   (300, 520, 400), (512, 768, 2048)])
+def test_int8_bit_exact(eng, shape):
+    M, N, K = shape
+    A, B = o.workloads.c5_int8(M, N, K, seed=M * 3 + N + K)
+    C = torch.full((M, N), -1, dtype=torch.int32, device=DEV)
+    eng.gemm_s8(A.to(DEV), B.to(DEV), out=C)
+    assert np.array_equal(C.cpu().numpy(), oracle.gemm_s8s8_s32(A.numpy(), B.numpy()))
+
+
+def test_int8_golden_and_extremes(eng, golden):
+    A = torch.from_numpy(golden["c5_A"]).to(DEV)
+    B = torch.from_numpy(golden["c5_B"]).to(DEV)
+    assert np.array_equal(eng.gemm_s8(A, B).cpu().numpy(), golden["c5_C"])
+    # the largest magnitudes the contract allows, K = 8192: |acc| = 8192 * 127^2 < 2^31
+    K = 8192
+    A = torch.full((130, K), -127, dtype=torch.int8, device=DEV)
+    B = torch.full((24, K), 127, dtype=torch.int8, device=DEV)
+    B[1::2] = -127
+    C = eng.gemm_s8(A, B)
+    exp = torch.tensor([-K * 127 * 127, K * 127 * 127], dtype=torch.int32, device=DEV).repeat(12)
+    assert torch.equal(C, exp.expand(130, 24))

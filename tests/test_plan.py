@@ -1,0 +1,67 @@
+"""CPU: the tile-plan chooser (host-only code of the library) and its overrides."""
+import ctypes
+import os
+import subprocess
+import sys
+
+import open64_b200 as o
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def model(kind, M, N, K, swiglu=0, sms=148, **pin):
+    p = o.Plan()
+    pp = None
+    if pin:
+        pp = o.Plan()
+        for k, v in pin.items():
+            setattr(pp, k, v)
+        pp = ctypes.byref(pp)
+    rc = o.lib().o64_plan_model(kind, swiglu, M, N, K, sms, pp, ctypes.byref(p))
+    assert rc == 0
+    return p.as_dict()
+
+
+def test_headline_shapes(built):
+    p = model(o.KIND_BF16, 8192, 8192, 8192)
+    assert (p["tile_m"], p["tile_n"], p["tile_k"], p["stages"]) == (128, 256, 64, 4)
+    assert (p["mma_m"], p["mma_n"], p["mma_k"]) == (128, 256, 16)
+    assert p["num_ctas"] == 148 and p["cta_group"] == 1
+    assert 0.4 < p["predicted_ms"] < 1.5
+    for kind in (o.KIND_FP8, o.KIND_S8):
+        p = model(kind, 4096, 8192, 8192)
+        assert p["tile_k"] == 128 and p["mma_k"] == 32
+    # shared-memory ring fits: stages * (A + B stage bytes) <= 227 KB
+    for tn in (128, 256):
+        p = model(o.KIND_BF16, 4096, 4096, 4096, tile_n=tn)
+        assert p["tile_n"] == tn
+        assert p["stages"] * (128 + tn) * 128 <= 227 * 1024
+
+
+def test_group_m_makes_a_near_square_wave(built):
+    p = model(o.KIND_BF16, 8192, 8192, 8192)
+    g = p["group_m"]
+    cols = 148 / g
+    assert g in (8, 16)
+    assert g * 128 + cols * 256 <= 8 * 128 + (148 / 8) * 256
+
+
+def test_pins_and_rejections(built):
+    p = model(o.KIND_BF16, 8192, 8192, 8192, tile_n=128, group_m=4, num_ctas=64, raster=1)
+    assert (p["tile_n"], p["group_m"], p["num_ctas"], p["raster"], p["stages"]) == (128, 4, 64, 1, 6)
+    pl = o.Plan()
+    assert o.lib().o64_plan_model(o.KIND_F32, 0, 8, 8, 8, 148, None, ctypes.byref(pl)) == o.ERR_RANK
+    assert o.lib().o64_plan_model(o.KIND_FP8, 1, 8, 8, 8, 148, None, ctypes.byref(pl)) == o.ERR_DTYPE
+    assert o.lib().o64_plan_model(o.KIND_BF16, 0, 0, 8, 8, 148, None, ctypes.byref(pl)) == o.ERR_RANK
+
+
+def test_env_override_and_trace(built):
+    code = ("import ctypes, open64_b200 as o; p=o.Plan();"
+            "o.lib().o64_plan_model(1,0,4096,4096,4096,148,None,ctypes.byref(p));"
+            "print(p.tile_n,p.group_m,p.num_ctas,p.raster)")
+    env = dict(os.environ, O64_LNO="blocking_size=128x128x64:group_m=2:num_ctas=100:raster=1",
+               O64_TRACE="plan", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, cwd=ROOT)
+    assert r.returncode == 0, r.stderr
+    assert r.stdout.split() == ["128", "2", "100", "1"]
+    assert "[o64 plan" in r.stderr and "tile 128x128x64" in r.stderr

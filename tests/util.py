@@ -1,0 +1,29 @@
+"""Helpers shared by the tests: error metrics with the formulas the tolerances refer to."""
+import numpy as np
+import torch
+
+TOL_F32 = 1e-4    # max|y - ref| / max|ref|, fp32 fused linear
+TOL_LOWP = 2e-2   # max|y - ref| / max|ref|, bf16 / fp8 results against the fp32 nest
+
+
+def relmax(y, ref):
+    """max|y - ref| / max|ref| (ReLU makes exact zeros, so an elementwise ratio is meaningless)."""
+    y = np.asarray(y, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    return float(np.abs(y - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+def bits16(t):
+    return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def bits8(t):
+    return t.contiguous().view(torch.uint8).cpu().numpy()
+
+
+def from_bits16(a, device="cpu"):
+    return torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16).to(device)
+
+
+def from_bits8_e4m3(a, device="cpu"):
+    return torch.from_numpy(a.copy()).view(torch.float8_e4m3fn).to(device)

@@ -12,8 +12,8 @@ CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libo64gemm.so")
 OBJ_DIR = os.path.join(HERE, "build")
 
-SOURCES = ["api.cu", "umma_gemm.cu", "simt_kernels.cu", "plan.cpp"]
-HEADERS = ["ptx_sm100.cuh", "umma_gemm.cuh", "simt_kernels.cuh", "../../include/o64gemm.h"]
+SOURCES = ["api.cu", "umma_gemm.cu", "umma_gemm_2cta.cu", "umma_gemm_wide.cu", "simt_kernels.cu", "plan.cpp"]
+HEADERS = ["ptx_sm100.cuh", "umma_gemm.cuh", "umma_common.cuh", "simt_kernels.cuh", "../../include/o64gemm.h"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -56,7 +56,7 @@ static NcclApi &nccl() {
 }
 
 // ---- handle ---------------------------------------------------------------------------------
-static const int kSlots = 6;
+static const int kSlots = 9;  // 0-5 host staging, 6-8 repacked operands (A, B, B2)
 struct o64_handle_s {
     int device = 0;
     int num_sms = 148;
@@ -179,9 +179,11 @@ extern "C" int o64_plan_set(o64_handle_t h, int kind, const o64_plan_t *plan) {
         h->has_pin[kind] = false;
         return O64_OK;
     }
-    if (plan->tile_m && plan->tile_m != 128) return O64_ERR_RANK;
+    if (plan->tile_m && plan->tile_m != 128 && plan->tile_m != 256 && plan->tile_m != 512) return O64_ERR_RANK;
     if (plan->tile_n && plan->tile_n != 128 && plan->tile_n != 256) return O64_ERR_RANK;
-    if (plan->cta_group && plan->cta_group != 1) return O64_ERR_RANK;
+    if (plan->cta_group && plan->cta_group != 1 && plan->cta_group != 2) return O64_ERR_RANK;
+    if (plan->tile_m && plan->cta_group && (plan->cta_group == 1) != (plan->tile_m == 128)) return O64_ERR_RANK;
+    if (plan->tile_m == 512 && plan->tile_n && plan->tile_n != 256) return O64_ERR_RANK;
     if (plan->group_m < 0 || plan->num_ctas < 0) return O64_ERR_RANK;
     h->pins[kind] = *plan;
     h->has_pin[kind] = true;
@@ -294,6 +296,27 @@ static int stage_out_end(const StagedOut &o, cudaStream_t s) {
     return O64_OK;
 }
 
+// TMA needs a 16-byte aligned base and row pitch.  An operand that lacks either is copied once
+// into handle-owned scratch with the pitch rounded up (a strided device-to-device copy on the
+// caller's stream); aligned operands are used in place.
+static bool tma_aligned(const void *ptr, int64_t ld, int elem) {
+    return ((reinterpret_cast<uintptr_t>(ptr) & 15u) == 0) && ((ld * elem) % 16 == 0);
+}
+
+static int repack_if_unaligned(o64_handle_t h, int slot, const void **ptr, int64_t *ld, int64_t rows,
+                               int64_t cols, int elem, cudaStream_t s, bool force = false) {
+    if (!*ptr) return O64_OK;
+    if (!force && tma_aligned(*ptr, *ld, elem)) return O64_OK;
+    const int64_t new_ld = ((cols * elem + 15) / 16) * 16 / elem;
+    int rc = reserve(&h->stage[slot], &h->stage_cap[slot], (size_t)rows * new_ld * elem);
+    if (rc) return rc;
+    CUDA_TRY(cudaMemcpy2DAsync(h->stage[slot], (size_t)new_ld * elem, *ptr, (size_t)*ld * elem,
+                               (size_t)cols * elem, (size_t)rows, cudaMemcpyDeviceToDevice, s));
+    *ptr = h->stage[slot];
+    *ld = new_ld;
+    return O64_OK;
+}
+
 // ---- native layer ---------------------------------------------------------------------------
 extern "C" int o64_linear_f32(o64_handle_t h, int64_t M, int64_t N, int64_t K, const float *A,
                               int64_t lda, const float *B, int64_t ldb, const float *bias, float *Y,
@@ -365,14 +388,20 @@ static int umma_entry(o64_handle_t h, int kind, bool b_kn, int epi, int64_t M, i
         }
     }
     if ((rc = stage_out_begin(h, 5, C, span_bytes(M, N, ldc, out_elem), ldc != N, s, &out))) return rc;
+    int64_t lda_eff = lda, ldb_eff = ldb, ldb2_eff = ldb;
+    if ((rc = repack_if_unaligned(h, 6, &dA, &lda_eff, M, K, elem, s))) return rc;
+    // gate and up weights share one pitch: if either needs the copy, both get it
+    const bool both = dB2 && (!tma_aligned(dB, ldb, elem) || !tma_aligned(dB2, ldb, elem));
+    if ((rc = repack_if_unaligned(h, 7, &dB, &ldb_eff, b_rows, b_cols, elem, s, both))) return rc;
+    if ((rc = repack_if_unaligned(h, 8, &dB2, &ldb2_eff, b_rows, b_cols, elem, s, both))) return rc;
 
     UmmaCall c;
     c.kind = kind;
     c.b_kn = b_kn;
     c.epi = epi;
     c.M = M; c.N = N; c.K = K;
-    c.A = dA; c.lda = lda;
-    c.B = dB; c.B2 = dB2; c.ldb = ldb;
+    c.A = dA; c.lda = lda_eff;
+    c.B = dB; c.B2 = dB2; c.ldb = ldb_eff;
     c.C = out.dev; c.ldc = ldc;
     c.bias = (const float *)dbias;
     c.scale_a = (const float *)dsa;

@@ -4,7 +4,7 @@
 // osprey/be/lno/cache_model.cxx:6483).  Pure host code, no CUDA calls.
 //
 // The search space is what the kernels are instantiated for: tile_m = 128, tile_n in
-// {256, 128}; each candidate is scored with a two-resource model (tensor pipe vs. the
+// {256, 128}, one CTA or a pair of CTAs per tile; each candidate is scored with a two-resource model (tensor pipe vs. the
 // shared-memory fill rate) times the number of waves over the persistent grid.
 #include <cstdio>
 #include <cstdlib>
@@ -19,22 +19,40 @@ namespace o64 {
 static const double kClockGHz = 1.5;            // sustained SM clock under load, approx.
 static const double kDenseBf16FlopPerClkSm = 8192.0;
 static const double kSmemFillBytesPerClkSm = 96.0;  // L2 -> shared memory through TMA, approx.
+static const double kLoadLatencyClk = 1900.0;        // TMA issue -> data in shared memory -> barrier, measured ~1.3 us
 
 static int elem_bytes(int kind) { return kind == O64_KIND_BF16 ? 2 : (kind == O64_KIND_F32 ? 4 : 1); }
 
-static double predict_ms(int kind, int epi, int64_t M, int64_t N, int64_t K, int tile_n, int num_ctas) {
+// cta_group = 1: a CTA owns a 128 x tile_n tile.  cta_group = 2: a pair of CTAs owns a
+// tile_m x tile_n tile (tile_m = 256: 128 rows per CTA; tile_m = 512: 256 rows per CTA as two
+// accumulators issued by two threads); each CTA loads its rows of A and tile_n / 2 rows of B
+// per K block.
+static double predict_ms(int kind, int epi, int64_t M, int64_t N, int64_t K, int tile_n, int num_ctas,
+                         int cta_group, int tile_m) {
     const int eb = elem_bytes(kind);
     const int block_k = 128 / eb;
     const int out_n = (epi == EPI_SWIGLU) ? tile_n / 2 : tile_n;
-    const double tiles = double((M + 127) / 128) * double((N + out_n - 1) / out_n);
-    const double waves = double(int64_t((tiles + num_ctas - 1) / num_ctas));
+    const int rows_per_cta = tile_m / cta_group;
+    const int units = num_ctas / cta_group;  // CTAs or CTA pairs working side by side
+    const double tiles = double((M + tile_m - 1) / tile_m) * double((N + out_n - 1) / out_n);
+    const double waves = double(int64_t((tiles + units - 1) / units));
     const double kblocks = double((K + block_k - 1) / block_k);
     const double flop_rate = kDenseBf16FlopPerClkSm * (eb == 1 ? 2.0 : 1.0);
-    const double mma_clk = 2.0 * 128.0 * tile_n * block_k / flop_rate;
-    const double fill_clk = (128.0 + tile_n) * 128.0 / kSmemFillBytesPerClkSm;
-    const double stage_clk = mma_clk > fill_clk ? mma_clk : fill_clk;
+    // a tcgen05.mma of 128 rows costs about the same whether N is 128 or 256, and a single
+    // issuing thread adds roughly a quarter on top (two issuers hide that)
+    const double n_eff = tile_n < 256 ? 256.0 : double(tile_n);
+    const double issue = (rows_per_cta == 256) ? 1.0 : (cta_group == 2 ? 1.28 : 1.05);
+    const double mma_clk = issue * 2.0 * rows_per_cta * n_eff * block_k / flop_rate;  // per SM
+    const double fill_clk = (double(rows_per_cta) + double(tile_n) / cta_group) * 128.0 / kSmemFillBytesPerClkSm;
+    // the ring must also cover the L2 -> shared-memory latency: (stages - 1) K blocks in flight
+    const int stage_bytes = (rows_per_cta + tile_n / cta_group) * 128;
+    const int stages = (200 * 1024) / stage_bytes;
+    const double latency_clk = kLoadLatencyClk / double(stages > 1 ? stages - 1 : 1);
+    double stage_clk = mma_clk > fill_clk ? mma_clk : fill_clk;
+    if (latency_clk > stage_clk) stage_clk = latency_clk;
+    const double epilogue_clk = (rows_per_cta == 256) ? 5000.0 : 0.0;  // not overlapped when both accumulators fill TMEM
     const double prologue_clk = 2500.0;  // first TMA round trip + epilogue tail of the last tile
-    return (waves * kblocks * stage_clk + prologue_clk) / (kClockGHz * 1e6);
+    return (waves * (kblocks * stage_clk + epilogue_clk) + prologue_clk) / (kClockGHz * 1e6);
 }
 
 // O64_LNO="blocking_size=128x256x64:stages=4:cta_group=1:group_m=8:raster=0:num_ctas=148"
@@ -74,26 +92,48 @@ void plan_choose(int kind, int epi, int64_t M, int64_t N, int64_t K, int num_sms
     memset(out, 0, sizeof(*out));
     out->kind = kind;
     const int eb = elem_bytes(kind);
-    out->tile_m = 128;
     out->tile_k = 128 / eb;
-    out->cta_group = 1;
-    out->mma_m = 128;
     out->mma_k = 32 / eb;
     out->split_k = 1;
     out->num_ctas = (pin.num_ctas > 0 && pin.num_ctas <= num_sms) ? pin.num_ctas : num_sms;
 
-    int tile_n = 0;
-    if (pin.tile_n == 128 || pin.tile_n == 256) {
-        tile_n = pin.tile_n;
-    } else {
-        const double t256 = predict_ms(kind, epi, M, N, K, 256, out->num_ctas);
-        const double t128 = predict_ms(kind, epi, M, N, K, 128, out->num_ctas);
-        tile_n = (t128 < 0.97 * t256) ? 128 : 256;
+    // candidates: (cta_group, tile_m) in {(1,128), (2,256), (2,512)} x tile_n in {256, 128};
+    // pins remove candidates
+    static const int kShapes[3][2] = {{2, 512}, {2, 256}, {1, 128}};
+    int best_g = 0, best_n = 0, best_m = 0;
+    double best_t = 1e300;
+    for (int i = 0; i < 3; ++i) {
+        const int g = kShapes[i][0], tm = kShapes[i][1];
+        if (pin.cta_group && pin.cta_group != g) continue;
+        if (g == 2 && out->num_ctas < 2) continue;
+        if (pin.tile_m && pin.tile_m != tm) continue;
+        if (tm > 128 && M <= tm / 2 && !pin.tile_m && !pin.cta_group) continue;  // half the rows would be padding
+        for (int n = 256; n >= 128; n /= 2) {
+            if (pin.tile_n && pin.tile_n != n) continue;
+            if (tm == 512 && n != 256) continue;                      // not instantiated
+            if (g == 2 && n == 128 && epi == EPI_SWIGLU) continue;  // not instantiated
+            const double t = predict_ms(kind, epi, M, N, K, n, out->num_ctas, g, tm);
+            if (t < best_t) {
+                best_t = t;
+                best_g = g;
+                best_n = n;
+                best_m = tm;
+            }
+        }
     }
+    if (!best_g) {  // contradictory pins: fall back to the plain default
+        best_g = 1;
+        best_n = 256;
+        best_m = 128;
+    }
+    out->cta_group = best_g;
+    out->tile_m = best_m;
+    out->mma_m = 128 * best_g;
+    const int tile_n = best_n;
     out->tile_n = tile_n;
     out->mma_n = tile_n;
-    out->stages = (tile_n == 256) ? 4 : 6;
-    out->predicted_ms = predict_ms(kind, epi, M, N, K, tile_n, out->num_ctas);
+    out->stages = best_m == 512 ? 4 : (best_g == 2 ? ((tile_n == 256) ? 6 : 8) : ((tile_n == 256) ? 4 : 6));
+    out->predicted_ms = predict_ms(kind, epi, M, N, K, tile_n, out->num_ctas, best_g, best_m);
 
     // L2 block: rasterise tiles so that the CTAs running together cover a near-square patch
     // of C (fewest distinct A and B panels in flight).
@@ -104,8 +144,8 @@ void plan_choose(int kind, int epi, int64_t M, int64_t N, int64_t K, int num_sms
         int best = 1;
         double best_cost = 1e300;
         for (int g = 1; g <= 32; g *= 2) {
-            const double cols = double(out->num_ctas) / g;
-            const double cost = g * 128.0 + cols * out_n;  // panel rows fetched per wave
+            const double cols = double(out->num_ctas / out->cta_group) / g;
+            const double cost = g * double(out->tile_m) + cols * out_n;  // panel rows fetched per wave
             if (cost < best_cost) {
                 best_cost = cost;
                 best = g;

@@ -48,6 +48,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Non-blocking probe of a barrier phase (try_wait may suspend the thread for a while).
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+
+// One lane of the (converged) warp gets true.  The role loops run on the whole warp so that
+// addresses and descriptors stay in the uniform datapath; only the elected lane issues.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "elect.sync _|P, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -81,13 +106,24 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 }
 
 // ---------------------------------------------------------------------------------------
-// TMA: 2-D tiled bulk-tensor load, completion counted in bytes on an mbarrier.  No
-// cluster multicast anywhere: every CTA fetches its own tiles.
+// TMA: 2-D tiled bulk-tensor load, completion counted in bytes on an mbarrier.  Every CTA
+// fetches its own tiles; no load is ever shared between the CTAs of a cluster.
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void *tmap, int x, int y,
                                             uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_dst), "l"(tmap), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+// Same load issued by one CTA of a 2-CTA pair: the qualifier allows the completion barrier to
+// live in the partner CTA's shared memory (`bar` is then a shared::cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const void *tmap, int x, int y,
+                                                 uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
         "[%0], [%1, {%2, %3}], [%4];"
         ::"r"(smem_dst), "l"(tmap), "r"(x), "r"(y), "r"(bar)
         : "memory");
@@ -112,6 +148,18 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
                  : "memory");
 }
+// Paired forms: executed by the same warp of both CTAs of a pair.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+                 : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() {
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -125,7 +173,79 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
                  ::"r"(bar) : "memory");
 }
 
+// ---------------------------------------------------------------------------------------
+// 2-CTA pairs (cta_group::2): cluster helpers and the paired forms of alloc / mma / commit
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_id_x() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t num_clusters_x() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+// Arrive on an mbarrier that may live in the partner CTA (shared::cluster address).  Default
+// semantics on purpose: the .release.cluster form stalls the issuing thread for about 400
+// cycles per arrive (and far longer behind in-flight TMA loads), measured on B200.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+// One arrival on `bar` (local or partner CTA, shared::cluster address) when every paired MMA
+// issued so far by this thread has completed.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(bar) : "memory");
+}
+
+// The same arrival delivered to the barrier at this shared-memory offset in every CTA of
+// `cta_mask` (one instruction for both CTAs of a pair).
+__device__ __forceinline__ void tc_commit_pair_mask(uint32_t bar, uint16_t cta_mask) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(bar), "h"(cta_mask) : "memory");
+}
+
 enum : int { MMA_F16 = 0, MMA_F8F6F4 = 1, MMA_I8 = 2 };
+
+// Paired MMA: issued by one thread of the even CTA; A rows and D rows are split over the two
+// CTAs (128 each), each CTA's shared memory holds half of B's N extent.
+template <int KIND>
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate) {
+    if constexpr (KIND == 0) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    } else if constexpr (KIND == 1) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    }
+}
 
 // D[tmem] (+)= A[smem desc] * B[smem desc]; issued by a single thread.
 template <int KIND>

@@ -1,0 +1,236 @@
+// Pieces shared by the 1-CTA and the 2-CTA tcgen05 GEMM kernels: launch parameters, tile
+// rasterisation, the fused epilogue.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "ptx_sm100.cuh"
+#include "umma_gemm.cuh"
+
+namespace o64 {
+
+struct UmmaParams {
+    int M, N, K;
+    void *C;
+    long long ldc;
+    const float *bias;
+    const float *scale_a;
+    const float *scale_b;
+    int act;
+    int num_m_tiles, num_n_tiles, group_m, raster;
+    int num_k_blocks;
+    int vec_ok;  // C rows 16-byte aligned: vector stores allowed
+    unsigned long long *dbg;  // tuning aid (O64_TRACE=pipe): per-CTA wait/total cycles of the issuing threads
+    int probe;   // 0 = normal; 1 = skip the loads, 2 = skip the MMAs (pipeline probes, results invalid)
+    int *status;
+};
+
+constexpr int kBlockM = 128;
+constexpr int kRowBytes = 128;  // bytes of K (or of N for a [K,N] operand) per shared-memory row
+constexpr int kThreads = 192;
+constexpr int kABytes = kBlockM * kRowBytes;
+
+// Status-word detail codes: which wait gave up.
+constexpr int kWaitProducerEmpty = 0x101;
+constexpr int kWaitMmaFull = 0x102;
+constexpr int kWaitMmaAccEmpty = 0x103;
+constexpr int kWaitEpiAccFull = 0x104;
+
+__device__ __forceinline__ void tile_coords(int t, const UmmaParams &p, int &mb, int &nb) {
+    if (p.raster == 0) {
+        const int per_group = p.group_m * p.num_n_tiles;
+        const int g = t / per_group;
+        const int first = g * p.group_m;
+        const int gsz = min(p.num_m_tiles - first, p.group_m);
+        const int r = t - g * per_group;
+        mb = first + r % gsz;
+        nb = r / gsz;
+    } else {
+        const int per_group = p.group_m * p.num_m_tiles;
+        const int g = t / per_group;
+        const int first = g * p.group_m;
+        const int gsz = min(p.num_n_tiles - first, p.group_m);
+        const int r = t - g * per_group;
+        nb = first + r % gsz;
+        mb = r / gsz;
+    }
+}
+
+__device__ __forceinline__ float act_apply(float x, int act) {
+    switch (act) {
+    case O64_ACT_RELU: return fmaxf(x, 0.0f);
+    case O64_ACT_GELU_TANH: {
+        const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+        return 0.5f * x * (1.0f + tanhf(u));
+    }
+    case O64_ACT_GELU_ERF: return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
+    case O64_ACT_SILU: return x / (1.0f + expf(-x));
+    default: return x;
+    }
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+
+constexpr int kEpiStagingBytesPerWarp = 4096;  // 32 rows x 128 bytes
+constexpr int kEpiStagingBytes = 4 * kEpiStagingBytesPerWarp;
+
+// Applies the fused tail to 32 accumulator values of one row (columns col0 .. col0+31).
+template <int ACT>
+__device__ __forceinline__ float act_fixed(float x) {
+    if constexpr (ACT == O64_ACT_RELU) {
+        return fmaxf(x, 0.0f);
+    } else if constexpr (ACT == O64_ACT_GELU_TANH) {
+        const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+        return 0.5f * x * (1.0f + tanhf(u));
+    } else if constexpr (ACT == O64_ACT_GELU_ERF) {
+        return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
+    } else if constexpr (ACT == O64_ACT_SILU) {
+        return x / (1.0f + expf(-x));
+    } else {
+        return x;
+    }
+}
+
+// The activation is a template parameter: with a run-time switch inside the element loop the
+// compiler evaluates every branch (tanhf, erff, expf) for every element, which made the
+// epilogue of a 128 x 256 tile as long as its main loop.
+template <int EPI, int ACT>
+__device__ __forceinline__ void epilogue_math(const UmmaParams &p, const uint32_t (&v)[32],
+                                              const uint32_t (&u)[32], int col0, float sa, float (&f)[32]) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        float x = __uint_as_float(v[j]);
+        const int col = min(col0 + j, p.N - 1);
+        if constexpr (EPI == EPI_SWIGLU) {
+            const float up = __uint_as_float(u[j]);
+            x = (x / (1.0f + expf(-x))) * up;
+        } else if constexpr (EPI == EPI_SCALED_BF16) {
+            const float sb = p.scale_b ? __ldg(p.scale_b + col) : 1.0f;
+            x = x * (sa * sb);
+            if (p.bias) x += __ldg(p.bias + col);
+        } else {
+            if (p.bias) x += __ldg(p.bias + col);
+            x = act_fixed<ACT>(x);
+        }
+        f[j] = x;
+    }
+}
+
+// Drains one finished accumulator buffer: this warp's 32 lanes (TMEM lane quarter) by
+// 128-byte-wide column slabs.  tcgen05.ld gives every thread one ROW of the slab; a store
+// straight from those registers would have each warp instruction touch 32 rows with 16 bytes
+// each (measured: about 50 000 cycles per 128 x 256 tile, slower than the tile's main loop).
+// So the slab goes through a warp-private, XOR-swizzled shared-memory patch and comes back
+// transposed: each store instruction then writes four full 128-byte row segments.
+// Whole-warp call; rows >= M and columns >= N are computed but not stored.
+//   row0     global row of lane 0 of this warp      n0   first output column of the tile
+//   t_row    TMEM address of (first lane of the quarter, first column of the buffer)
+//   staging  this warp's 4 KB patch of shared memory
+template <int EPI, int BLOCK_N, int ACT>
+__device__ __forceinline__ void epilogue_tile_act(const UmmaParams &p, long long row0, int n0,
+                                                  uint32_t t_row, uint8_t *staging) {
+    constexpr int kOutN = (EPI == EPI_SWIGLU) ? BLOCK_N / 2 : BLOCK_N;
+    constexpr int kOutElem = (EPI == EPI_S32) ? 4 : 2;
+    constexpr int kSlabCols = 128 / kOutElem;  // 64 bf16 or 32 int32 columns per 128-byte row
+    const int lane = threadIdx.x & 31;
+    const long long row = row0 + lane;
+    const bool row_ok = row < p.M;
+    float sa = 1.0f;
+    if constexpr (EPI == EPI_SCALED_BF16) {
+        if (p.scale_a && row_ok) sa = p.scale_a[row];
+    }
+    uint4 *patch = reinterpret_cast<uint4 *>(staging);
+    const int sw = lane & 7;  // XOR swizzle of the 16-byte chunk index, by row
+
+#pragma unroll 1
+    for (int c = 0; c < kOutN; c += kSlabCols) {
+        const int col0 = n0 + c;
+        if (col0 >= p.N) break;  // uniform: nothing left in this tile's column range
+        const bool coalesced = p.vec_ok && (col0 + kSlabCols <= p.N) && !(p.probe & 32);
+#pragma unroll
+        for (int h = 0; h < kSlabCols / 32; ++h) {
+            uint32_t v[32];
+            [[maybe_unused]] uint32_t u[32];
+            __syncwarp();
+            tmem_ld_32x32(t_row + c + h * 32, v);
+            if constexpr (EPI == EPI_SWIGLU) tmem_ld_32x32(t_row + kOutN + c + h * 32, u);
+            tmem_ld_wait();
+            if constexpr (EPI == EPI_S32) {
+                if (coalesced) {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        patch[lane * 8 + (q ^ sw)] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                } else if (row_ok && !(p.probe & 32)) {
+                    int32_t *dst = reinterpret_cast<int32_t *>(p.C) + row * p.ldc + col0;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (col0 + j < p.N) dst[j] = (int32_t)v[j];
+                }
+            } else {
+                float f[32];
+                epilogue_math<EPI, ACT>(p, v, u, col0 + h * 32, sa, f);
+                if (coalesced) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        patch[lane * 8 + ((h * 4 + q) ^ sw)] =
+                            make_uint4(pack_bf16x2(f[8 * q], f[8 * q + 1]), pack_bf16x2(f[8 * q + 2], f[8 * q + 3]),
+                                       pack_bf16x2(f[8 * q + 4], f[8 * q + 5]), pack_bf16x2(f[8 * q + 6], f[8 * q + 7]));
+                } else if (row_ok && !(p.probe & 32)) {
+                    __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.C) + row * p.ldc + col0 + h * 32;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (col0 + h * 32 + j < p.N) dst[j] = __float2bfloat16_rn(f[j]);
+                }
+            }
+        }
+        if (coalesced) {
+            __syncwarp();
+            // read back transposed: lane -> (row 4*i + lane/8, 16-byte chunk lane%8)
+            const int chunk = lane & 7;
+            uint8_t *cbase = reinterpret_cast<uint8_t *>(p.C) + (size_t)col0 * kOutElem + chunk * 16;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int r = 4 * i + (lane >> 3);
+                const uint4 val = patch[r * 8 + (chunk ^ (r & 7))];
+                long long grow = row0 + r;
+                if (p.probe & 128) grow &= 31;
+                if (grow < p.M) {
+                    uint4 *dst = reinterpret_cast<uint4 *>(cbase + (size_t)grow * p.ldc * kOutElem);
+                    if (p.probe & 256)
+                        __stcs(dst, val);
+                    else
+                        *dst = val;
+                }
+            }
+            __syncwarp();
+        }
+    }
+}
+
+template <int EPI, int BLOCK_N>
+__device__ __forceinline__ void epilogue_tile(const UmmaParams &p, long long row0, int n0,
+                                              uint32_t t_row, uint8_t *staging) {
+    if constexpr (EPI == EPI_BF16) {
+        switch (p.act) {  // uniform: one branch per tile, not per element
+        case O64_ACT_RELU: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_RELU>(p, row0, n0, t_row, staging); break;
+        case O64_ACT_GELU_TANH: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_GELU_TANH>(p, row0, n0, t_row, staging); break;
+        case O64_ACT_GELU_ERF: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_GELU_ERF>(p, row0, n0, t_row, staging); break;
+        case O64_ACT_SILU: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_SILU>(p, row0, n0, t_row, staging); break;
+        default: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_NONE>(p, row0, n0, t_row, staging); break;
+        }
+    } else {
+        epilogue_tile_act<EPI, BLOCK_N, O64_ACT_NONE>(p, row0, n0, t_row, staging);
+    }
+}
+
+// host helpers shared by the launchers (umma_gemm.cu)
+int umma_launch_pair(const UmmaCall &c, const CUtensorMap &ta, const CUtensorMap &tb,
+                     const CUtensorMap &tb2, const UmmaParams &p);
+int umma_launch_wide(const UmmaCall &c, const CUtensorMap &ta, const CUtensorMap &tb,
+                     const CUtensorMap &tb2, const UmmaParams &p);
+
+}  // namespace o64

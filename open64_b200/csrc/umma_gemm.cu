@@ -22,37 +22,12 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 
-#include "ptx_sm100.cuh"
-#include "umma_gemm.cuh"
+#include "umma_common.cuh"
 
 namespace o64 {
-
-struct UmmaParams {
-    int M, N, K;
-    void *C;
-    long long ldc;
-    const float *bias;
-    const float *scale_a;
-    const float *scale_b;
-    int act;
-    int num_m_tiles, num_n_tiles, group_m, raster;
-    int num_k_blocks;
-    int vec_ok;  // C rows 16-byte aligned: vector stores allowed
-    int *status;
-};
-
-constexpr int kBlockM = 128;
-constexpr int kRowBytes = 128;  // bytes of K (or of N for a [K,N] operand) per shared-memory row
-constexpr int kThreads = 192;
-constexpr int kABytes = kBlockM * kRowBytes;
-
-// Status-word detail codes: which wait gave up.
-constexpr int kWaitProducerEmpty = 0x101;
-constexpr int kWaitMmaFull = 0x102;
-constexpr int kWaitMmaAccEmpty = 0x103;
-constexpr int kWaitEpiAccFull = 0x104;
 
 template <int BLOCK_N, int STAGES>
 struct SmemLayout {
@@ -61,51 +36,14 @@ struct SmemLayout {
     static constexpr int kRingBytes = STAGES * kStageBytes;
     // after the ring: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2] (8 bytes each),
     // the TMEM base address and the abort flag
-    static constexpr int kBarOffset = kRingBytes;
+    static constexpr int kStagingOffset = kRingBytes;  // epilogue patches, 4 KB per warp
+    static constexpr int kBarOffset = kStagingOffset + kEpiStagingBytes;
     static constexpr int kNumBars = 2 * STAGES + 4;
     static constexpr int kTmemPtrOffset = kBarOffset + 8 * kNumBars;
     static constexpr int kAbortOffset = kTmemPtrOffset + 4;
     static constexpr int kTotal = kAbortOffset + 4;
     static constexpr int kDynamic = kTotal + 1024;  // slack to align the ring to 1024 bytes
 };
-
-__device__ __forceinline__ void tile_coords(int t, const UmmaParams &p, int &mb, int &nb) {
-    if (p.raster == 0) {
-        const int per_group = p.group_m * p.num_n_tiles;
-        const int g = t / per_group;
-        const int first = g * p.group_m;
-        const int gsz = min(p.num_m_tiles - first, p.group_m);
-        const int r = t - g * per_group;
-        mb = first + r % gsz;
-        nb = r / gsz;
-    } else {
-        const int per_group = p.group_m * p.num_m_tiles;
-        const int g = t / per_group;
-        const int first = g * p.group_m;
-        const int gsz = min(p.num_n_tiles - first, p.group_m);
-        const int r = t - g * per_group;
-        nb = first + r % gsz;
-        mb = r / gsz;
-    }
-}
-
-__device__ __forceinline__ float act_apply(float x, int act) {
-    switch (act) {
-    case O64_ACT_RELU: return fmaxf(x, 0.0f);
-    case O64_ACT_GELU_TANH: {
-        const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-        return 0.5f * x * (1.0f + tanhf(u));
-    }
-    case O64_ACT_GELU_ERF: return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
-    case O64_ACT_SILU: return x / (1.0f + expf(-x));
-    default: return x;
-    }
-}
-
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t *>(&v);
-}
 
 // KIND: MMA_F16 (bf16 operands) / MMA_F8F6F4 (e4m3) / MMA_I8 (s8).
 // B_KN: B stored [K,N] (N contiguous) -> MN-major shared-memory descriptor; else [N,K].
@@ -146,7 +84,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(acc_full_bar(b), 1);
-            mbar_init(acc_empty_bar(b), 128);
+            mbar_init(acc_empty_bar(b), 4);  // one arrival per epilogue warp
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -165,52 +103,68 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------------
-        if (lane == 0) {
+        {
+            const bool leader = elect_one();
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            long long wait_clk = 0;
+            const long long t_begin = clock64();
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
                 int mb, nb;
                 tile_coords(t, p, mb, nb);
                 const int m0 = mb * kBlockM;
                 const int n0 = nb * kOutN;
                 for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                    const long long c0 = p.dbg ? clock64() : 0;
                     ok = mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
                                            kWaitProducerEmpty);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (p.dbg) wait_clk += clock64() - c0;
                     if (!ok) break;
                     const uint32_t a_dst = smem_base + stage * L::kStageBytes;
                     const uint32_t b_dst = a_dst + kABytes;
-                    mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
-                    tma_load_2d(a_dst, &tm_a, kb * kBlockK, m0, full_bar(stage));
-                    if constexpr (!B_KN) {
-                        tma_load_2d(b_dst, &tm_b, kb * kBlockK, n0, full_bar(stage));
-                    } else {
-                        // [K,N] operand: boxes of 64 N-elements x 64 K-rows (8 KB each)
-                        constexpr int kGroups = BLOCK_N / 64;
+                    if ((p.probe & 3) == 1) {
+                        if (leader) mbar_arrive(full_bar(stage));
+                    } else if (leader) {
+                        mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
+                        tma_load_2d(a_dst, &tm_a, kb * kBlockK, m0, full_bar(stage));
+                        if constexpr (!B_KN) {
+                            tma_load_2d(b_dst, &tm_b, kb * kBlockK, n0, full_bar(stage));
+                        } else {
+                            // [K,N] operand: boxes of 64 N-elements x 64 K-rows (8 KB each)
+                            constexpr int kGroups = BLOCK_N / 64;
 #pragma unroll
-                        for (int g = 0; g < kGroups; ++g) {
-                            if constexpr (EPI == EPI_SWIGLU) {
-                                const bool up = g >= kGroups / 2;
-                                const int gg = up ? g - kGroups / 2 : g;
-                                tma_load_2d(b_dst + g * 8192, up ? &tm_b2 : &tm_b, n0 + gg * 64,
-                                            kb * kBlockK, full_bar(stage));
-                            } else {
-                                tma_load_2d(b_dst + g * 8192, &tm_b, n0 + g * 64, kb * kBlockK,
-                                            full_bar(stage));
+                            for (int g = 0; g < kGroups; ++g) {
+                                if constexpr (EPI == EPI_SWIGLU) {
+                                    const bool up = g >= kGroups / 2;
+                                    const int gg = up ? g - kGroups / 2 : g;
+                                    tma_load_2d(b_dst + g * 8192, up ? &tm_b2 : &tm_b, n0 + gg * 64,
+                                                kb * kBlockK, full_bar(stage));
+                                } else {
+                                    tma_load_2d(b_dst + g * 8192, &tm_b, n0 + g * 64, kb * kBlockK,
+                                                full_bar(stage));
+                                }
                             }
                         }
                     }
+                    __syncwarp();
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
             }
+            if (p.dbg && leader) {
+                p.dbg[blockIdx.x * 8 + 2] = wait_clk;
+                p.dbg[blockIdx.x * 8 + 3] = clock64() - t_begin;
+            }
         }
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------------
-        if (lane == 0) {
+        {
+            const bool leader = elect_one();
             constexpr uint32_t d_fmt = (KIND == MMA_I8) ? 2u : 1u;
             constexpr uint32_t ab_fmt = (KIND == MMA_F8F6F4) ? 0u : 1u;  // bf16 / e4m3 / s8
             constexpr uint32_t idesc =
@@ -220,43 +174,66 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             uint32_t phase = 0;
             int it = 0;
             bool ok = true;
+            long long wait_clk = 0;
+            const long long t_begin = clock64();
+            // The thread looks at the NEXT stage's barrier before it issues the current stage's
+            // MMAs, so that the probe's latency hides behind the issue instead of opening a gap
+            // in the tensor pipe between two K blocks.
+            uint32_t ready = mbar_test_wait(full_bar(0), 0);
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
                 const int buf = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1u;
                 ok = mbar_wait_bounded(acc_empty_bar(buf), acc_phase ^ 1u, abort_flag, p.status,
                                        kWaitMmaAccEmpty);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BLOCK_N;
                 for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-                    ok = mbar_wait_bounded(full_bar(stage), phase, abort_flag, p.status,
-                                           kWaitMmaFull);
-                    if (!ok) break;
+                    if (!__all_sync(0xffffffffu, ready)) {
+                        const long long c0 = p.dbg ? clock64() : 0;
+                        ok = mbar_wait_bounded(full_bar(stage), phase, abort_flag, p.status,
+                                               kWaitMmaFull);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (p.dbg) wait_clk += clock64() - c0;
+                        if (!ok) break;
+                    }
+                    const int next_stage = (stage + 1 == STAGES) ? 0 : stage + 1;
+                    const uint32_t next_phase = (stage + 1 == STAGES) ? (phase ^ 1u) : phase;
+                    const uint32_t next_ready = mbar_test_wait(full_bar(next_stage), next_phase);
                     tc_fence_after();
                     const uint32_t a_addr = smem_base + stage * L::kStageBytes;
                     const uint32_t b_addr = a_addr + kABytes;
                     const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024);
                     const uint64_t b_desc =
                         B_KN ? make_smem_desc(b_addr, 8192, 1024) : make_smem_desc(b_addr, 16, 1024);
+                    if ((p.probe & 3) == 2) {
+                        if (leader) mbar_arrive(empty_bar(stage));
+                    } else if (leader) {
 #pragma unroll
-                    for (int k = 0; k < kMmaPerStage; ++k) {
-                        tc_mma<KIND>(d_tmem, a_desc + 2u * k, b_desc + kBAdvance * k, idesc,
-                                     (kb | k) != 0 ? 1u : 0u);
+                        for (int k = 0; k < kMmaPerStage; ++k) {
+                            tc_mma<KIND>(d_tmem, a_desc + 2u * k, b_desc + kBAdvance * k, idesc,
+                                         (kb | k) != 0 ? 1u : 0u);
+                        }
+                        tc_commit(empty_bar(stage));  // frees the stage when these MMAs retire
                     }
-                    tc_commit(empty_bar(stage));  // frees the stage when these MMAs retire
-                    if (++stage == STAGES) {
-                        stage = 0;
-                        phase ^= 1u;
-                    }
+                    __syncwarp();
+                    stage = next_stage;
+                    phase = next_phase;
+                    ready = next_ready;
                 }
-                if (ok) tc_commit(acc_full_bar(buf));
+                if (ok && leader) tc_commit(acc_full_bar(buf));
+                __syncwarp();
+            }
+            if (p.dbg && leader) {
+                p.dbg[blockIdx.x * 8 + 0] = wait_clk;
+                p.dbg[blockIdx.x * 8 + 1] = clock64() - t_begin;
             }
         }
         __syncwarp();
     } else {
         // ------------------------------ epilogue ----------------------------------------
         const int quarter = warp & 3;  // TMEM lane quarter this warp may read
-        const int row_in_tile = quarter * 32 + lane;
         int it = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
@@ -264,78 +241,21 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             tile_coords(t, p, mb, nb);
             const int buf = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1u;
-            ok = mbar_wait_bounded(acc_full_bar(buf), acc_phase, abort_flag, p.status,
-                                   kWaitEpiAccFull);
-            ok = __all_sync(0xffffffffu, ok);  // the warp leaves together (tcgen05.ld is warp-wide)
+            // one lane polls, the warp follows (tcgen05.ld is warp-wide: the warp leaves together)
+            if (lane == 0)
+                ok = mbar_wait_bounded(acc_full_bar(buf), acc_phase, abort_flag, p.status,
+                                       kWaitEpiAccFull);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             tc_fence_after();
-            const long long row = (long long)mb * kBlockM + row_in_tile;
-            const bool row_ok = row < p.M;
-            const int n0 = nb * kOutN;
+            const long long row0 = (long long)mb * kBlockM + quarter * 32;
             const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BLOCK_N;
-            float sa = 1.0f;
-            if constexpr (EPI == EPI_SCALED_BF16) {
-                if (p.scale_a && row_ok) sa = p.scale_a[row];
-            }
-#pragma unroll 1
-            for (int c = 0; c < kOutN; c += 32) {
-                uint32_t v[32];
-                __syncwarp();
-                tmem_ld_32x32(t_row + c, v);
-                [[maybe_unused]] uint32_t u[32];
-                if constexpr (EPI == EPI_SWIGLU) tmem_ld_32x32(t_row + kOutN + c, u);
-                tmem_ld_wait();
-                const int col0 = n0 + c;
-                const bool full = col0 + 32 <= p.N;
-                if (!row_ok || col0 >= p.N) {
-                    // nothing to store for this thread; stay in step with the warp
-                } else if constexpr (EPI == EPI_S32) {
-                    int32_t *dst = reinterpret_cast<int32_t *>(p.C) + row * p.ldc + col0;
-                    if (full && p.vec_ok) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            *reinterpret_cast<uint4 *>(dst + j) =
-                                make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < p.N) dst[j] = (int32_t)v[j];
-                    }
-                } else {
-                    float f[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        float x = __uint_as_float(v[j]);
-                        const int col = min(col0 + j, p.N - 1);
-                        if constexpr (EPI == EPI_SWIGLU) {
-                            const float up = __uint_as_float(u[j]);
-                            x = (x / (1.0f + expf(-x))) * up;
-                        } else if constexpr (EPI == EPI_SCALED_BF16) {
-                            const float sb = p.scale_b ? __ldg(p.scale_b + col) : 1.0f;
-                            x = x * (sa * sb);
-                            if (p.bias) x += __ldg(p.bias + col);
-                        } else {
-                            if (p.bias) x += __ldg(p.bias + col);
-                            x = act_apply(x, p.act);
-                        }
-                        f[j] = x;
-                    }
-                    __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.C) + row * p.ldc + col0;
-                    if (full && p.vec_ok) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 8)
-                            *reinterpret_cast<uint4 *>(dst + j) =
-                                make_uint4(pack_bf16x2(f[j], f[j + 1]), pack_bf16x2(f[j + 2], f[j + 3]),
-                                           pack_bf16x2(f[j + 4], f[j + 5]), pack_bf16x2(f[j + 6], f[j + 7]));
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(f[j]);
-                    }
-                }
-            }
+            if (!(p.probe & 4))
+                epilogue_tile<EPI, BLOCK_N>(p, row0, nb * kOutN, t_row,
+                                            smem_gen + L::kStagingOffset + quarter * kEpiStagingBytesPerWarp);
             tc_fence_before();
-            mbar_arrive(acc_empty_bar(buf));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar(buf));
         }
     }
 
@@ -432,11 +352,16 @@ int umma_launch(const UmmaCall &c) {
     const int block_k = kRowBytes / elem;
     const int out_n = (c.epi == EPI_SWIGLU) ? block_n / 2 : block_n;
 
+    const bool pair = pl.cta_group == 2;
+    const bool wide = pair && pl.tile_m == 512;  // each CTA of the pair owns 256 rows
+    if (wide && block_n != 256) return O64_ERR_DTYPE;
+    const int tile_m = wide ? 512 : (pair ? 2 * kBlockM : kBlockM);
     CUtensorMap ta, tb, tb2;
-    int rc = encode_2d(&ta, c.kind, c.A, c.M, c.K, c.lda, block_k, kBlockM);
+    int rc = encode_2d(&ta, c.kind, c.A, c.M, c.K, c.lda, block_k, wide ? 256 : kBlockM);
     if (rc) return rc;
     if (!c.b_kn) {
-        rc = encode_2d(&tb, c.kind, c.B, c.N, c.K, c.ldb, block_k, block_n);
+        // a CTA of a pair loads half of the B block
+        rc = encode_2d(&tb, c.kind, c.B, c.N, c.K, c.ldb, block_k, pair ? block_n / 2 : block_n);
         tb2 = tb;
     } else {
         rc = encode_2d(&tb, c.kind, c.B, c.K, c.N, c.ldb, 64, block_k);
@@ -455,7 +380,7 @@ int umma_launch(const UmmaCall &c) {
     p.scale_a = c.scale_a;
     p.scale_b = c.scale_b;
     p.act = c.act;
-    p.num_m_tiles = (int)((c.M + kBlockM - 1) / kBlockM);
+    p.num_m_tiles = (int)((c.M + tile_m - 1) / tile_m);
     p.num_n_tiles = (int)((c.N + out_n - 1) / out_n);
     p.group_m = pl.group_m > 0 ? pl.group_m : 8;
     p.raster = pl.raster;
@@ -463,11 +388,49 @@ int umma_launch(const UmmaCall &c) {
     const int out_elem = (c.epi == EPI_S32) ? 4 : 2;
     p.vec_ok = aligned16(c.C) && ((c.ldc * out_elem) % 16 == 0);
     p.status = c.status_word;
+    {
+        const char *pr = getenv("O64_PROBE");  // pipeline probes for tuning; results are invalid
+        p.probe = pr ? atoi(pr) : 0;
+    }
+    // O64_TRACE=pipe: the issuing threads count the cycles they spend waiting; the launch is then
+    // synchronous and prints the averages (a tuning aid, off by default)
+    static unsigned long long *dbg_buf = nullptr;
+    const char *tr = getenv("O64_TRACE");
+    const bool trace_pipe = tr && strstr(tr, "pipe");
+    p.dbg = nullptr;
+    if (trace_pipe) {
+        if (!dbg_buf && cudaMalloc(&dbg_buf, 8 * 1024 * sizeof(unsigned long long)) != cudaSuccess) dbg_buf = nullptr;
+        if (dbg_buf) cudaMemsetAsync(dbg_buf, 0, 8 * 1024 * sizeof(unsigned long long), c.stream);
+        p.dbg = dbg_buf;
+    }
+    auto report = [&](int rc_launch, int ctas) {
+        if (!trace_pipe || !dbg_buf || rc_launch) return rc_launch;
+        static unsigned long long host[8 * 1024];
+        cudaStreamSynchronize(c.stream);
+        cudaMemcpy(host, dbg_buf, sizeof(host), cudaMemcpyDeviceToHost);
+        double s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        int n = 0, n_mma = 0;
+        for (int i = 0; i < ctas && i < 1024; ++i) {
+            if (!host[8 * i + 1] && !host[8 * i + 3]) continue;
+            for (int j = 0; j < 8; ++j) s[j] += (double)host[8 * i + j];
+            ++n;
+            if (host[8 * i + 1]) ++n_mma;
+        }
+        if (n && n_mma)
+            fprintf(stderr,
+                    "[o64 pipe: mma thread %.0f clk, waits for data %.1f%%, for a drained accumulator %.1f%%; "
+                    "producer waits %.1f%% of %.0f clk; epilogue busy %.0f clk per CTA; %d CTAs]\n",
+                    s[1] / n_mma, 100.0 * s[0] / s[1], 100.0 * s[5] / s[1],
+                    100.0 * s[2] / (s[3] > 0 ? s[3] : 1), s[3] / n, s[4] / n, n);
+        return rc_launch;
+    };
+    if (wide) return report(umma_launch_wide(c, ta, tb, tb2, p), pl.num_ctas);
+    if (pair) return report(umma_launch_pair(c, ta, tb, tb2, p), pl.num_ctas);
     const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles;
     const int grid = (int)(tiles < pl.num_ctas ? tiles : pl.num_ctas);
 
 #define O64_INST(KIND, BKN, EPI_, BN, ST) \
-    return launch_inst<KIND, BKN, EPI_, BN, ST>(ta, tb, tb2, p, grid, c.stream)
+    return report(launch_inst<KIND, BKN, EPI_, BN, ST>(ta, tb, tb2, p, grid, c.stream), grid)
 
     if (c.kind == O64_KIND_BF16) {
         if (c.epi == EPI_SWIGLU) {

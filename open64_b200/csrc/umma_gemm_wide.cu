@@ -1,0 +1,394 @@
+// Tensor-core GEMM for sm_100a, wide 2-CTA form: a pair of CTAs computes a 512 x 256
+// tile of C; each CTA owns 256 rows of it as TWO 128 x 256 accumulators that together fill its
+// tensor memory (512 columns).
+//
+// Why this shape.  Measured on B200 with the narrower kernels of this library:
+//   * one thread cannot issue tcgen05.mma faster than about one per 130 cycles (about 160 for
+//     the paired form), which is no faster than a 128 x 256 x 16 MMA executes: a single issuing
+//     thread leaves gaps in the tensor pipe;
+//   * a CTA that computes 128 x 256 per K block must pull 48 KB through the L2 -> shared-memory
+//     path every 512 tensor cycles, and four stages in flight do not cover that path's latency.
+// Here two threads issue (one per accumulator), so the tensor pipe always has work queued, and
+// a K block of 48 KB per CTA (256 rows of A, half of the 256-row B block) feeds 1024 tensor
+// cycles: half the fill rate, twice the latency tolerance.
+//
+// Roles per CTA (256 threads):
+//   warp 0      producer: TMA loads of A (one 256-row box) and this rank's half of B, completing
+//               on the full barrier of rank 0
+//   warp 1, 2   rank 0 only: MMA issuers for accumulator 0 (rows 0..127 of each CTA) and
+//               accumulator 1 (rows 128..255); each commits to empty[stage] (count 2) and to
+//               its own acc_full barrier, in both CTAs with one masked commit
+//   warp 3      allocates tensor memory
+//   warps 4..7  epilogue: drain accumulator 0 then accumulator 1, releasing each as soon as it
+//               is drained so that the next tile's MMAs on it can start
+// Every wait is bounded; both CTAs of a pair meet at a cluster barrier before tensor memory is
+// freed.
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "umma_common.cuh"
+
+namespace o64 {
+
+constexpr int kWaitWideProducerEmpty = 0x301;
+constexpr int kWaitWideMmaFull = 0x302;
+constexpr int kWaitWideMmaAccEmpty = 0x303;
+constexpr int kWaitWideEpiAccFull = 0x304;
+constexpr int kWideTmemMismatch = 0x305;
+
+constexpr int kWideThreads = 256;
+constexpr int kWideBlockN = 256;
+constexpr int kWideStages = 4;
+constexpr int kWideRowsPerCta = 256;
+constexpr int kWideABytes = kWideRowsPerCta * kRowBytes;      // 32 KB
+constexpr int kWideBBytes = (kWideBlockN / 2) * kRowBytes;    // 16 KB: this rank's half of B
+constexpr int kWideStageBytes = kWideABytes + kWideBBytes;    // 48 KB
+
+struct WideSmem {
+    static constexpr int kRingBytes = kWideStages * kWideStageBytes;
+    static constexpr int kStagingOffset = kRingBytes;
+    static constexpr int kBarOffset = kStagingOffset + kEpiStagingBytes;
+    // full[S], empty[S], acc_full[2], acc_empty[2]
+    static constexpr int kNumBars = 2 * kWideStages + 4;
+    static constexpr int kTmemPtrOffset = kBarOffset + 8 * kNumBars;
+    static constexpr int kAbortOffset = kTmemPtrOffset + 4;
+    static constexpr int kTotal = kAbortOffset + 4;
+    static constexpr int kDynamic = kTotal + 1024;
+};
+
+template <int KIND, bool B_KN, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kWideThreads, 1)
+umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                      const __grid_constant__ CUtensorMap tm_b2, const UmmaParams p) {
+    using L = WideSmem;
+    constexpr int STAGES = kWideStages;
+    constexpr int BLOCK_N = kWideBlockN;
+    constexpr int kElem = (KIND == MMA_F16) ? 2 : 1;
+    constexpr int kBlockK = kRowBytes / kElem;
+    constexpr int kMmaPerStage = 4;
+    constexpr int kHalfN = BLOCK_N / 2;
+    constexpr int kOutN = (EPI == EPI_SWIGLU) ? BLOCK_N / 2 : BLOCK_N;
+    constexpr int kPairM = 2 * kWideRowsPerCta;  // 512
+    constexpr uint32_t kTmemCols = 512;
+    static_assert(!B_KN || KIND == MMA_F16, "[K,N] operands are supported for bf16 only");
+    static_assert(EPI != EPI_SWIGLU || B_KN, "SwiGLU weights are [K,N]");
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + L::kBarOffset;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto acc_full_bar = [&](int g) { return bar_base + 8u * (2 * STAGES + g); };
+    auto acc_empty_bar = [&](int g) { return bar_base + 8u * (2 * STAGES + 2 + g); };
+    volatile uint32_t *tmem_ptr_smem =
+        reinterpret_cast<volatile uint32_t *>(smem_gen + L::kTmemPtrOffset);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_gen + L::kAbortOffset);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair_id = (int)cluster_id_x();
+    const int num_pairs = (int)num_clusters_x();
+    const int num_tiles = p.num_m_tiles * p.num_n_tiles;  // num_m_tiles counts 512-row blocks
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);   // rank 0's arrive.expect_tx covers both CTAs' bytes
+            mbar_init(empty_bar(s), 1);  // one commit per phase from rank 0's MMA thread
+        }
+        for (int g = 0; g < 2; ++g) {
+            mbar_init(acc_full_bar(g), 1);
+            mbar_init(acc_empty_bar(g), 8);  // four epilogue warps in each CTA
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tm_a);
+        tma_prefetch_desc(&tm_b);
+        if (EPI == EPI_SWIGLU) tma_prefetch_desc(&tm_b2);
+    }
+    if (warp == 3) {
+        // the whole tensor memory of this SM, from empty: both CTAs get base column 0
+        tmem_alloc(smem_u32(smem_gen + L::kTmemPtrOffset), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_smem;
+    if (threadIdx.x == 0 && (tmem_base & 0xffffu) != 0) {
+        atomicCAS(p.status, 0, kWideTmemMismatch);
+        *abort_flag = 1;
+    }
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer (both ranks) ---------------------------
+        {
+            const bool leader = elect_one();
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            long long wait_clk = 0;
+            const long long t_begin = clock64();
+            for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+                int mb, nb;
+                tile_coords(t, p, mb, nb);
+                const int m0 = mb * kPairM + (int)rank * kWideRowsPerCta;
+                const int n0 = nb * kOutN;
+                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                    const long long c0 = p.dbg ? clock64() : 0;
+                    ok = mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
+                                           kWaitWideProducerEmpty);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (p.dbg) wait_clk += clock64() - c0;
+                    if (!ok) break;
+                    const uint32_t a_dst = smem_base + stage * kWideStageBytes;
+                    const uint32_t b_dst = a_dst + kWideABytes;
+                    const uint32_t full0 = map_to_cta(full_bar(stage), 0);
+                    if ((p.probe & 3) == 1) {
+                        if (rank == 0 && leader) mbar_arrive(full_bar(stage));
+                    } else if (leader) {
+                        if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * kWideStageBytes);
+                        tma_load_2d_pair(a_dst, &tm_a, kb * kBlockK, m0, full0);
+                        if constexpr (!B_KN) {
+                            tma_load_2d_pair(b_dst, &tm_b, kb * kBlockK, n0 + (int)rank * kHalfN, full0);
+                        } else if constexpr (EPI == EPI_SWIGLU) {
+                            // rank 0 holds the gate columns, rank 1 the up columns of the same n0
+#pragma unroll
+                            for (int g = 0; g < kHalfN / 64; ++g)
+                                tma_load_2d_pair(b_dst + g * 8192, rank ? &tm_b2 : &tm_b, n0 + g * 64,
+                                                 kb * kBlockK, full0);
+                        } else {
+#pragma unroll
+                            for (int g = 0; g < kHalfN / 64; ++g)
+                                tma_load_2d_pair(b_dst + g * 8192, &tm_b,
+                                                 n0 + (int)rank * kHalfN + g * 64, kb * kBlockK, full0);
+                        }
+                    }
+                    __syncwarp();
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (p.dbg && leader) {
+                p.dbg[blockIdx.x * 8 + 2] = wait_clk;
+                p.dbg[blockIdx.x * 8 + 3] = clock64() - t_begin;
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer (rank 0 only) ----------------------------
+        if (rank == 0) {
+            const bool leader = elect_one();
+            constexpr uint32_t d_fmt = (KIND == MMA_I8) ? 2u : 1u;
+            constexpr uint32_t ab_fmt = (KIND == MMA_F8F6F4) ? 0u : 1u;
+            constexpr uint32_t idesc = make_idesc(d_fmt, ab_fmt, ab_fmt, B_KN ? 1u : 0u, 256, BLOCK_N);
+            constexpr uint32_t kBAdvance = B_KN ? (16 * kRowBytes) >> 4 : 32 >> 4;
+            int stage = 0;
+            uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            long long wait_clk = 0, acc_wait_clk = 0;
+            const long long t_begin = clock64();
+            const bool interleave = (p.probe & 16) != 0;
+            uint32_t ready = mbar_test_wait(full_bar(0), 0);
+            for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++it) {
+                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                    if (!__all_sync(0xffffffffu, ready)) {
+                        const long long c0 = p.dbg ? clock64() : 0;
+                        ok = mbar_wait_bounded(full_bar(stage), phase, abort_flag, p.status, kWaitWideMmaFull);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (p.dbg) wait_clk += clock64() - c0;
+                        if (!ok) break;
+                    }
+                    const int next_stage = (stage + 1 == STAGES) ? 0 : stage + 1;
+                    const uint32_t next_phase = (stage + 1 == STAGES) ? (phase ^ 1u) : phase;
+                    const uint32_t next_ready = mbar_test_wait(full_bar(next_stage), next_phase);
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_base + stage * kWideStageBytes;
+                    const uint32_t b_addr = a_addr + kWideABytes;
+                    const uint64_t a_desc0 = make_smem_desc(a_addr, 16, 1024);
+                    const uint64_t a_desc1 = make_smem_desc(a_addr + kABytes, 16, 1024);
+                    const uint64_t b_desc =
+                        B_KN ? make_smem_desc(b_addr, 8192, 1024) : make_smem_desc(b_addr, 16, 1024);
+                    if ((p.probe & 3) == 2) {
+                        if (leader) {
+                            mbar_arrive(empty_bar(stage));
+                            mbar_arrive_cluster(map_to_cta(empty_bar(stage), 1));
+                        }
+                    } else {
+                        if (kb == 0) {
+                            // the first MMA of a tile overwrites the accumulator: wait until the
+                            // epilogue has drained it (accumulator 1 is drained second)
+                            const long long a0 = p.dbg ? clock64() : 0;
+                            ok = mbar_wait_bounded(acc_empty_bar(0), (it & 1u) ^ 1u, abort_flag, p.status,
+                                                   kWaitWideMmaAccEmpty);
+                            if (p.dbg) acc_wait_clk += clock64() - a0;
+                            if (ok && interleave)
+                                ok = mbar_wait_bounded(acc_empty_bar(1), (it & 1u) ^ 1u, abort_flag, p.status,
+                                                       kWaitWideMmaAccEmpty);
+                            ok = __all_sync(0xffffffffu, ok);
+                            if (!ok) break;
+                            tc_fence_after();
+                        }
+                        if (interleave) {
+                            if (leader) {
+#pragma unroll
+                            for (int k = 0; k < kMmaPerStage; ++k) {
+                                tc_mma_pair<KIND>(tmem_base, a_desc0 + 2u * k, b_desc + kBAdvance * k, idesc,
+                                                  (kb | k) != 0 ? 1u : 0u);
+                                tc_mma_pair<KIND>(tmem_base + BLOCK_N, a_desc1 + 2u * k, b_desc + kBAdvance * k,
+                                                  idesc, (kb | k) != 0 ? 1u : 0u);
+                            }
+                            }
+                        } else {
+                            if (leader) {
+#pragma unroll
+                                for (int k = 0; k < kMmaPerStage; ++k)
+                                    tc_mma_pair<KIND>(tmem_base, a_desc0 + 2u * k, b_desc + kBAdvance * k, idesc,
+                                                      (kb | k) != 0 ? 1u : 0u);
+                            }
+                            if (kb == 0) {
+                                __syncwarp();
+                                const long long a1 = p.dbg ? clock64() : 0;
+                                ok = mbar_wait_bounded(acc_empty_bar(1), (it & 1u) ^ 1u, abort_flag, p.status,
+                                                       kWaitWideMmaAccEmpty);
+                                if (p.dbg) acc_wait_clk += clock64() - a1;
+                                ok = __all_sync(0xffffffffu, ok);
+                                if (!ok) break;
+                                tc_fence_after();
+                            }
+                            if (leader) {
+#pragma unroll
+                                for (int k = 0; k < kMmaPerStage; ++k)
+                                    tc_mma_pair<KIND>(tmem_base + BLOCK_N, a_desc1 + 2u * k, b_desc + kBAdvance * k,
+                                                      idesc, (kb | k) != 0 ? 1u : 0u);
+                            }
+                        }
+                        if (leader) tc_commit_pair_mask(empty_bar(stage), 3);
+                    }
+                    __syncwarp();
+                    stage = next_stage;
+                    phase = next_phase;
+                    ready = next_ready;
+                }
+                if (ok && leader) {
+                    tc_commit_pair_mask(acc_full_bar(0), 3);
+                    tc_commit_pair_mask(acc_full_bar(1), 3);
+                }
+                __syncwarp();
+            }
+            if (p.dbg && leader) {
+                p.dbg[blockIdx.x * 8 + 0] = wait_clk;
+                p.dbg[blockIdx.x * 8 + 5] = acc_wait_clk;
+                p.dbg[blockIdx.x * 8 + 1] = clock64() - t_begin;
+            }
+        }
+        __syncwarp();
+    } else if (warp >= 4) {
+        // ------------------------------ epilogue (both ranks) -------------------------------
+        const int quarter = warp & 3;
+        int it = 0;
+        bool ok = true;
+        long long epi_clk = 0;
+        for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++it) {
+            int mb, nb;
+            tile_coords(t, p, mb, nb);
+#pragma unroll 1
+            for (int g = 0; g < 2 && ok; ++g) {
+                if (lane == 0)
+                    ok = mbar_wait_bounded(acc_full_bar(g), it & 1u, abort_flag, p.status, kWaitWideEpiAccFull);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                tc_fence_after();
+                const long long row0 = (long long)mb * kPairM + (long long)rank * kWideRowsPerCta +
+                                       g * kBlockM + quarter * 32;
+                const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + g * BLOCK_N;
+                const long long e0 = p.dbg ? clock64() : 0;
+                if (!(p.probe & 4))
+                    epilogue_tile<EPI, BLOCK_N>(p, row0, nb * kOutN, t_row,
+                                                smem_gen + L::kStagingOffset + quarter * kEpiStagingBytesPerWarp);
+                tc_fence_before();
+                __syncwarp();
+                if (p.dbg) epi_clk += clock64() - e0;
+                if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty_bar(g), 0));
+            }
+        }
+        if (p.dbg && warp == 4 && lane == 0) p.dbg[blockIdx.x * 8 + 4] = epi_clk;
+    }
+
+    // ------------------------------ teardown --------------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 3) {
+        if (*abort_flag) {
+            const uint64_t t0 = globaltimer_ns();
+            while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+        }
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+template <int KIND, bool B_KN, int EPI>
+static int launch_wide_inst(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tb2,
+                            const UmmaParams &p, int grid, cudaStream_t stream) {
+    auto kern = umma_gemm_wide_kernel<KIND, B_KN, EPI>;
+    static bool attr_set = false;
+    static int max_pairs = 0;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, WideSmem::kDynamic) !=
+            cudaSuccess)
+            return O64_ERR_CUDA;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2, 1, 1);
+        cfg.blockDim = dim3(kWideThreads, 1, 1);
+        cfg.dynamicSmemBytes = WideSmem::kDynamic;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2;
+        at[0].val.clusterDim.y = 1;
+        at[0].val.clusterDim.z = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) {
+            (void)cudaGetLastError();
+            n = 0;
+        }
+        max_pairs = n;
+        attr_set = true;
+    }
+    if (max_pairs > 0 && grid > 2 * max_pairs) grid = 2 * max_pairs;
+    kern<<<grid, kWideThreads, WideSmem::kDynamic, stream>>>(ta, tb, tb2, p);
+    return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
+}
+
+// `p.num_m_tiles` counts 512-row blocks; tile_n is 256.
+int umma_launch_wide(const UmmaCall &c, const CUtensorMap &ta, const CUtensorMap &tb,
+                     const CUtensorMap &tb2, const UmmaParams &p) {
+    const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles;
+    long long pairs = c.plan.num_ctas / 2;
+    if (pairs > tiles) pairs = tiles;
+    if (pairs < 1) pairs = 1;
+    const int grid = (int)(2 * pairs);
+    if (c.kind == O64_KIND_BF16) {
+        if (c.epi == EPI_SWIGLU) return launch_wide_inst<MMA_F16, true, EPI_SWIGLU>(ta, tb, tb2, p, grid, c.stream);
+        if (c.epi == EPI_BF16) {
+            if (c.b_kn) return launch_wide_inst<MMA_F16, true, EPI_BF16>(ta, tb, tb2, p, grid, c.stream);
+            return launch_wide_inst<MMA_F16, false, EPI_BF16>(ta, tb, tb2, p, grid, c.stream);
+        }
+    } else if (c.kind == O64_KIND_FP8 && c.epi == EPI_SCALED_BF16) {
+        return launch_wide_inst<MMA_F8F6F4, false, EPI_SCALED_BF16>(ta, tb, tb2, p, grid, c.stream);
+    } else if (c.kind == O64_KIND_S8 && c.epi == EPI_S32) {
+        return launch_wide_inst<MMA_I8, false, EPI_S32>(ta, tb, tb2, p, grid, c.stream);
+    }
+    return O64_ERR_DTYPE;
+}
+
+}  // namespace o64

@@ -30,8 +30,6 @@ def _bf16_case(M, N, K, transB, seed=0):
 @pytest.mark.parametrize("transB", [True, False])
 def test_bf16_shapes(eng, shape, transB):
     M, N, K = shape
-    if not transB and N % 8:
-        pytest.skip("[K,N] operand needs a 16-byte row pitch")
     A, B = _bf16_case(M, N, K, transB)
     C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
     eng.gemm_bf16(A.to(DEV), B.to(DEV), transB=transB, out=C)
@@ -64,7 +62,9 @@ def test_bf16_both_tile_widths_and_rasters(eng):
     Ad, Bd = A.to(DEV), B.to(DEV)
     try:
         for pin in (dict(tile_n=128), dict(tile_n=256), dict(tile_n=256, group_m=1),
-                    dict(tile_n=128, group_m=3, raster=1), dict(tile_n=256, num_ctas=5)):
+                    dict(tile_n=128, group_m=3, raster=1), dict(tile_n=256, num_ctas=5),
+                    dict(cta_group=1, tile_n=256), dict(cta_group=2, tile_n=256),
+                    dict(cta_group=2, tile_n=128, group_m=2), dict(cta_group=2, tile_n=256, num_ctas=6)):
             eng.plan_set(o.KIND_BF16, **pin)
             C = eng.gemm_bf16(Ad, Bd, transB=True)
             assert relmax(C.float().cpu().numpy(), ref) <= TOL_LOWP, pin
@@ -82,6 +82,29 @@ def test_bf16_padded_leading_dimensions_and_unaligned_result(eng):
     ref = oracle.gemm_bf16(bits16(Ap[:, :K].contiguous()), bits16(Bp[:, :K].contiguous()), transB=True)
     assert relmax(Cp[:, :N].float().cpu().numpy(), ref) <= TOL_LOWP
     assert (Cp[:, N:] == 5.0).all()
+
+
+def test_bf16_operands_tma_cannot_address(eng):
+    """Row pitches that are not multiples of 16 bytes and a misaligned base: the engine copies such
+    operands into aligned scratch first."""
+    M, N, K = 150, 90, 60                      # 120-byte rows; [K,N] rows of 180 bytes
+    A, B = _bf16_case(M, N, K, True, seed=12)
+    ref = oracle.gemm_bf16(bits16(A), bits16(B), transB=True)
+    C = eng.gemm_bf16(A.to(DEV), B.to(DEV), transB=True)
+    assert relmax(C.float().cpu().numpy(), ref) <= TOL_LOWP
+    Bkn = B.t().contiguous()
+    C = eng.gemm_bf16(A.to(DEV), Bkn.to(DEV), transB=False)
+    assert relmax(C.float().cpu().numpy(), ref) <= TOL_LOWP
+    flat = torch.zeros(M * K + 1, dtype=torch.bfloat16, device=DEV)
+    flat[1:] = A.to(DEV).reshape(-1)
+    C = eng.gemm_bf16(flat[1:].view(M, K), B.to(DEV), transB=True)   # base off by 2 bytes
+    assert relmax(C.float().cpu().numpy(), ref) <= TOL_LOWP
+    X = A
+    Wg = (torch.randn(K, 50, generator=torch.Generator().manual_seed(1)) * 0.1).to(torch.bfloat16)
+    Wu = (torch.randn(K, 50, generator=torch.Generator().manual_seed(2)) * 0.1).to(torch.bfloat16)
+    H = eng.swiglu(X.to(DEV), Wg.to(DEV), Wu.to(DEV))
+    href = oracle.bf16_to_f32(oracle.swiglu_bf16(bits16(X), bits16(Wg), bits16(Wu)))
+    assert relmax(H.float().cpu().numpy(), href) <= TOL_LOWP
 
 
 def test_bf16_host_operands(eng):
@@ -160,3 +183,37 @@ def test_int8_golden_and_extremes(eng, golden):
     C = eng.gemm_s8(A, B)
     exp = torch.tensor([-K * 127 * 127, K * 127 * 127], dtype=torch.int32, device=DEV).repeat(12)
     assert torch.equal(C, exp.expand(130, 24))
+
+
+@pytest.mark.parametrize("cta_group", [1, 2])
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_every_kind_on_one_cta_and_on_cta_pairs(eng, cta_group, tile_n):
+    """Pins the plan so that both kernel families (one CTA per tile, a pair of CTAs per tile)
+    are exercised for every element kind, on shapes with ragged edges and several tiles per CTA."""
+    M, N, K = 700, 1160, 328
+    try:
+        for kind in (o.KIND_BF16, o.KIND_FP8, o.KIND_S8):
+            eng.plan_set(kind, cta_group=cta_group, tile_n=tile_n, num_ctas=8)
+        A, B = _bf16_case(M, N, K, True, seed=3)
+        C = eng.gemm_bf16(A.to(DEV), B.to(DEV), transB=True)
+        assert relmax(C.float().cpu().numpy(), oracle.gemm_bf16(bits16(A), bits16(B), transB=True)) <= TOL_LOWP
+        Bkn = B.t().contiguous()
+        C = eng.gemm_bf16(A.to(DEV), Bkn.to(DEV), transB=False, act="gelu_tanh")
+        ref = oracle.gemm_bf16(bits16(A), bits16(Bkn), transB=False, act=oracle.ACT_GELU_TANH)
+        assert relmax(C.float().cpu().numpy(), ref) <= TOL_LOWP
+        if not (cta_group == 2 and tile_n == 128):      # the fused gate/up kernel on pairs is 256 wide only
+            Wg = (Bkn.float() * 0.1).to(torch.bfloat16)
+            Wu = (torch.randn(K, N, generator=torch.Generator().manual_seed(6)) * 0.1).to(torch.bfloat16)
+            H = eng.swiglu(A.to(DEV), Wg.to(DEV), Wu.to(DEV))
+            href = oracle.bf16_to_f32(oracle.swiglu_bf16(bits16(A), bits16(Wg), bits16(Wu)))
+            assert relmax(H.float().cpu().numpy(), href) <= TOL_LOWP
+        A8, W8, sA, sB, bias = o.workloads.c4_fp8(M, N, K, seed=5)
+        C = eng.gemm_fp8_scaled(A8.to(DEV), W8.to(DEV), sA.to(DEV), sB.to(DEV), bias.to(DEV))
+        ref = oracle.gemm_fp8_scaled(bits8(A8), bits8(W8), sA.numpy(), sB.numpy(), bias.numpy())
+        assert relmax(C.float().cpu().numpy(), ref) <= TOL_LOWP
+        Ai, Bi = o.workloads.c5_int8(M, N, K, seed=7)
+        Ci = eng.gemm_s8(Ai.to(DEV), Bi.to(DEV))
+        assert np.array_equal(Ci.cpu().numpy(), oracle.gemm_s8s8_s32(Ai.numpy(), Bi.numpy()))
+    finally:
+        for kind in (o.KIND_BF16, o.KIND_FP8, o.KIND_S8):
+            eng.plan_set(kind)

@@ -24,22 +24,27 @@ def model(kind, M, N, K, swiglu=0, sms=148, **pin):
 
 def test_headline_shapes(built):
     p = model(o.KIND_BF16, 8192, 8192, 8192)
-    assert (p["tile_m"], p["tile_n"], p["tile_k"], p["stages"]) == (128, 256, 64, 4)
-    assert (p["mma_m"], p["mma_n"], p["mma_k"]) == (128, 256, 16)
-    assert p["num_ctas"] == 148 and p["cta_group"] == 1
+    assert (p["tile_n"], p["tile_k"]) == (256, 64) and p["stages"] in (4, 6)
+    # the headline shape takes the widest form: a CTA pair per 512 x 256 tile
+    assert (p["cta_group"], p["tile_m"]) == (2, 512)
+    assert (p["mma_n"], p["mma_k"]) == (256, 16)
+    assert p["num_ctas"] == 148 and (p["cta_group"], p["tile_m"]) in ((1, 128), (2, 256), (2, 512))
     assert 0.4 < p["predicted_ms"] < 1.5
     for kind in (o.KIND_FP8, o.KIND_S8):
         p = model(kind, 4096, 8192, 8192)
         assert p["tile_k"] == 128 and p["mma_k"] == 32
-    # shared-memory ring fits: stages * (A + B stage bytes) <= 227 KB
-    for tn in (128, 256):
-        p = model(o.KIND_BF16, 4096, 4096, 4096, tile_n=tn)
-        assert p["tile_n"] == tn
-        assert p["stages"] * (128 + tn) * 128 <= 227 * 1024
+    # shared-memory ring fits: stages * (A + B bytes one CTA stages per K block) <= 227 KB
+    for cg, tm in ((1, 128), (2, 256), (2, 512)):
+        for tn in (128, 256):
+            if tm == 512 and tn == 128:
+                continue
+            p = model(o.KIND_BF16, 4096, 4096, 4096, tile_n=tn, cta_group=cg, tile_m=tm)
+            assert (p["tile_n"], p["cta_group"], p["tile_m"]) == (tn, cg, tm)
+            assert p["stages"] * (tm // cg + tn // cg) * 128 + 16384 <= 227 * 1024
 
 
 def test_group_m_makes_a_near_square_wave(built):
-    p = model(o.KIND_BF16, 8192, 8192, 8192)
+    p = model(o.KIND_BF16, 8192, 8192, 8192, cta_group=1)
     g = p["group_m"]
     cols = 148 / g
     assert g in (8, 16)
@@ -47,7 +52,7 @@ def test_group_m_makes_a_near_square_wave(built):
 
 
 def test_pins_and_rejections(built):
-    p = model(o.KIND_BF16, 8192, 8192, 8192, tile_n=128, group_m=4, num_ctas=64, raster=1)
+    p = model(o.KIND_BF16, 8192, 8192, 8192, tile_n=128, group_m=4, num_ctas=64, raster=1, cta_group=1)
     assert (p["tile_n"], p["group_m"], p["num_ctas"], p["raster"], p["stages"]) == (128, 4, 64, 1, 6)
     pl = o.Plan()
     assert o.lib().o64_plan_model(o.KIND_F32, 0, 8, 8, 8, 148, None, ctypes.byref(pl)) == o.ERR_RANK

@@ -37,7 +37,7 @@ NOMINAL_BF16_TFLOPS = 2250.0
 NOMINAL_8BIT_TOPS = 4500.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel, from the
 # ncu capture summarised in profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES = 1124236168  # profiles/umma_gemm_bf16_c2_8192.md: 1.003 GB read + 121.0 MB written
+NCU_TRAFFIC_BYTES = 1006085632  # profiles/umma_gemm_wide_kernel_bf16_c2_8192.md: 883.5 MB read + 122.6 MB written
 
 
 def measured_peaks():

@@ -38,10 +38,10 @@ static double predict_ms(int kind, int epi, int64_t M, int64_t N, int64_t K, int
     const double waves = double(int64_t((tiles + units - 1) / units));
     const double kblocks = double((K + block_k - 1) / block_k);
     const double flop_rate = kDenseBf16FlopPerClkSm * (eb == 1 ? 2.0 : 1.0);
-    // a tcgen05.mma of 128 rows costs about the same whether N is 128 or 256, and a single
-    // issuing thread adds roughly a quarter on top (two issuers hide that)
+    // measured: a tcgen05.mma of 128 rows costs about the same whether N is 128 or 256; paired
+    // MMAs chained on one accumulator run about a tenth slower than alternated between two
     const double n_eff = tile_n < 256 ? 256.0 : double(tile_n);
-    const double issue = (rows_per_cta == 256) ? 1.0 : (cta_group == 2 ? 1.28 : 1.05);
+    const double issue = (rows_per_cta == 256) ? 1.0 : (cta_group == 2 ? 1.10 : 1.02);
     const double mma_clk = issue * 2.0 * rows_per_cta * n_eff * block_k / flop_rate;  // per SM
     const double fill_clk = (double(rows_per_cta) + double(tile_n) / cta_group) * 128.0 / kSmemFillBytesPerClkSm;
     // the ring must also cover the L2 -> shared-memory latency: (stages - 1) K blocks in flight
@@ -50,7 +50,11 @@ static double predict_ms(int kind, int epi, int64_t M, int64_t N, int64_t K, int
     const double latency_clk = kLoadLatencyClk / double(stages > 1 ? stages - 1 : 1);
     double stage_clk = mma_clk > fill_clk ? mma_clk : fill_clk;
     if (latency_clk > stage_clk) stage_clk = latency_clk;
-    const double epilogue_clk = (rows_per_cta == 256) ? 5000.0 : 0.0;  // not overlapped when both accumulators fill TMEM
+    // with two accumulators per CTA the epilogue does not overlap the next tile (measured about
+    // 12 000 cycles per 256 x 256 bf16 tile, more for 4-byte results, less for the half-width
+    // SwiGLU result); with one it hides behind the next tile's main loop
+    double epilogue_clk = 0.0;
+    if (rows_per_cta == 256) epilogue_clk = (kind == O64_KIND_S8) ? 20000.0 : (epi == EPI_SWIGLU ? 8000.0 : 12000.0);
     const double prologue_clk = 2500.0;  // first TMA round trip + epilogue tail of the last tile
     return (waves * (kblocks * stage_clk + epilogue_clk) + prologue_clk) / (kClockGHz * 1e6);
 }
@@ -135,23 +139,12 @@ void plan_choose(int kind, int epi, int64_t M, int64_t N, int64_t K, int num_sms
     out->stages = best_m == 512 ? 4 : (best_g == 2 ? ((tile_n == 256) ? 6 : 8) : ((tile_n == 256) ? 4 : 6));
     out->predicted_ms = predict_ms(kind, epi, M, N, K, tile_n, out->num_ctas, best_g, best_m);
 
-    // L2 block: rasterise tiles so that the CTAs running together cover a near-square patch
-    // of C (fewest distinct A and B panels in flight).
+    // L2 block: tiles are walked in groups of group_m tile rows.  Measured best on the 8192^3
+    // GEMM: groups that span about 2048 rows of C (16 / 8 / 4 tiles of 128 / 256 / 512 rows).
     if (pin.group_m > 0) {
         out->group_m = pin.group_m;
     } else {
-        const int out_n = (epi == EPI_SWIGLU) ? tile_n / 2 : tile_n;
-        int best = 1;
-        double best_cost = 1e300;
-        for (int g = 1; g <= 32; g *= 2) {
-            const double cols = double(out->num_ctas / out->cta_group) / g;
-            const double cost = g * double(out->tile_m) + cols * out_n;  // panel rows fetched per wave
-            if (cost < best_cost) {
-                best_cost = cost;
-                best = g;
-            }
-        }
-        out->group_m = best;
+        out->group_m = 2048 / out->tile_m;
     }
     out->raster = pin.raster ? 1 : 0;  // the automatic choice is 0 (M fastest)
 

@@ -129,6 +129,13 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const void *
         : "memory");
 }
 
+// Asks L2 to fetch a box ahead of time (no shared memory, no barrier): takes the DRAM latency
+// off the path of the later load of the same box.
+__device__ __forceinline__ void tma_prefetch_l2_2d(const void *tmap, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+                 ::"l"(tmap), "r"(x), "r"(y) : "memory");
+}
+
 __device__ __forceinline__ void tma_prefetch_desc(const void *tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }

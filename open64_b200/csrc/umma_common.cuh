@@ -132,10 +132,11 @@ __device__ __forceinline__ void epilogue_math(const UmmaParams &p, const uint32_
 //   staging  this warp's 4 KB patch of shared memory
 template <int EPI, int BLOCK_N, int ACT>
 __device__ __forceinline__ void epilogue_tile_act(const UmmaParams &p, long long row0, int n0,
-                                                  uint32_t t_row, uint8_t *staging) {
+                                                  uint32_t t_row, uint8_t *staging, int c_begin, int c_end) {
     constexpr int kOutN = (EPI == EPI_SWIGLU) ? BLOCK_N / 2 : BLOCK_N;
     constexpr int kOutElem = (EPI == EPI_S32) ? 4 : 2;
     constexpr int kSlabCols = 128 / kOutElem;  // 64 bf16 or 32 int32 columns per 128-byte row
+    constexpr int kChunksPerSlab = kSlabCols / 32;
     const int lane = threadIdx.x & 31;
     const long long row = row0 + lane;
     const bool row_ok = row < p.M;
@@ -146,84 +147,113 @@ __device__ __forceinline__ void epilogue_tile_act(const UmmaParams &p, long long
     uint4 *patch = reinterpret_cast<uint4 *>(staging);
     const int sw = lane & 7;  // XOR swizzle of the 16-byte chunk index, by row
 
-#pragma unroll 1
-    for (int c = 0; c < kOutN; c += kSlabCols) {
-        const int col0 = n0 + c;
-        if (col0 >= p.N) break;  // uniform: nothing left in this tile's column range
-        const bool coalesced = p.vec_ok && (col0 + kSlabCols <= p.N) && !(p.probe & 32);
+    // 32-column chunks of the accumulator this warp has to drain (uniform over the warp)
+    const int cols_avail = min(c_end, p.N - n0) - c_begin;
+    if (cols_avail <= 0) return;
+    const int nchunks = (cols_avail + 31) >> 5;
+
+    // one chunk: fused tail on 32 values of this thread's row, into the patch or straight out
+    auto process = [&](const uint32_t (&v)[32], const uint32_t (&u)[32], int i) {
+        const int c = c_begin + 32 * i;          // column inside the tile
+        const int slab_c = c_begin + (i / kChunksPerSlab) * kSlabCols;
+        const int h = i % kChunksPerSlab;
+        const bool coalesced = p.vec_ok && (n0 + slab_c + kSlabCols <= p.N) && !(p.probe & 32);
+        if constexpr (EPI == EPI_S32) {
+            if (coalesced) {
 #pragma unroll
-        for (int h = 0; h < kSlabCols / 32; ++h) {
+                for (int q = 0; q < 8; ++q)
+                    patch[lane * 8 + (q ^ sw)] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            } else if (row_ok && !(p.probe & 32)) {
+                int32_t *dst = reinterpret_cast<int32_t *>(p.C) + row * p.ldc + n0 + c;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (n0 + c + j < p.N) dst[j] = (int32_t)v[j];
+            }
+        } else {
+            float f[32];
+            epilogue_math<EPI, ACT>(p, v, u, n0 + c, sa, f);
+            if (coalesced) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    patch[lane * 8 + ((h * 4 + q) ^ sw)] =
+                        make_uint4(pack_bf16x2(f[8 * q], f[8 * q + 1]), pack_bf16x2(f[8 * q + 2], f[8 * q + 3]),
+                                   pack_bf16x2(f[8 * q + 4], f[8 * q + 5]), pack_bf16x2(f[8 * q + 6], f[8 * q + 7]));
+            } else if (row_ok && !(p.probe & 32)) {
+                __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.C) + row * p.ldc + n0 + c;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (n0 + c + j < p.N) dst[j] = __float2bfloat16_rn(f[j]);
+            }
+        }
+        // the chunk that completes a slab sends the patch out, transposed: lane -> (row 4*r + lane/8,
+        // 16-byte piece lane%8), four full 128-byte row segments per store instruction
+        if (h == kChunksPerSlab - 1 && coalesced) {
+            __syncwarp();
+            const int piece = lane & 7;
+            uint8_t *cbase = reinterpret_cast<uint8_t *>(p.C) + (size_t)(n0 + slab_c) * kOutElem + piece * 16;
+#pragma unroll
+            for (int r4 = 0; r4 < 8; ++r4) {
+                const int r = 4 * r4 + (lane >> 3);
+                const uint4 val = patch[r * 8 + (piece ^ (r & 7))];
+                const long long grow = row0 + r;
+                if (grow < p.M) *reinterpret_cast<uint4 *>(cbase + (size_t)grow * p.ldc * kOutElem) = val;
+            }
+            __syncwarp();
+        }
+    };
+
+    if constexpr (EPI == EPI_SWIGLU || ACT != O64_ACT_NONE) {
+        // register-hungry tails (two accumulators, or tanhf / erff / expf): plain load -> wait -> use
+#pragma unroll 1
+        for (int i = 0; i < nchunks; ++i) {
             uint32_t v[32];
             [[maybe_unused]] uint32_t u[32];
             __syncwarp();
-            tmem_ld_32x32(t_row + c + h * 32, v);
-            if constexpr (EPI == EPI_SWIGLU) tmem_ld_32x32(t_row + kOutN + c + h * 32, u);
+            tmem_ld_32x32(t_row + c_begin + 32 * i, v);
+            if constexpr (EPI == EPI_SWIGLU) tmem_ld_32x32(t_row + kOutN + c_begin + 32 * i, u);
             tmem_ld_wait();
-            if constexpr (EPI == EPI_S32) {
-                if (coalesced) {
-#pragma unroll
-                    for (int q = 0; q < 8; ++q)
-                        patch[lane * 8 + (q ^ sw)] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                } else if (row_ok && !(p.probe & 32)) {
-                    int32_t *dst = reinterpret_cast<int32_t *>(p.C) + row * p.ldc + col0;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (col0 + j < p.N) dst[j] = (int32_t)v[j];
-                }
-            } else {
-                float f[32];
-                epilogue_math<EPI, ACT>(p, v, u, col0 + h * 32, sa, f);
-                if (coalesced) {
-#pragma unroll
-                    for (int q = 0; q < 4; ++q)
-                        patch[lane * 8 + ((h * 4 + q) ^ sw)] =
-                            make_uint4(pack_bf16x2(f[8 * q], f[8 * q + 1]), pack_bf16x2(f[8 * q + 2], f[8 * q + 3]),
-                                       pack_bf16x2(f[8 * q + 4], f[8 * q + 5]), pack_bf16x2(f[8 * q + 6], f[8 * q + 7]));
-                } else if (row_ok && !(p.probe & 32)) {
-                    __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.C) + row * p.ldc + col0 + h * 32;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (col0 + h * 32 + j < p.N) dst[j] = __float2bfloat16_rn(f[j]);
-                }
-            }
+            if constexpr (EPI == EPI_SWIGLU)
+                process(v, u, i);
+            else
+                process(v, v, i);
         }
-        if (coalesced) {
+    } else {
+        // two register sets: the load of the next chunk is in flight while this one is processed
+        uint32_t va[32], vb[32];
+        __syncwarp();
+        tmem_ld_32x32(t_row + c_begin, va);
+#pragma unroll 1
+        for (int i = 0; i < nchunks; i += 2) {
+            tmem_ld_wait();
             __syncwarp();
-            // read back transposed: lane -> (row 4*i + lane/8, 16-byte chunk lane%8)
-            const int chunk = lane & 7;
-            uint8_t *cbase = reinterpret_cast<uint8_t *>(p.C) + (size_t)col0 * kOutElem + chunk * 16;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int r = 4 * i + (lane >> 3);
-                const uint4 val = patch[r * 8 + (chunk ^ (r & 7))];
-                long long grow = row0 + r;
-                if (p.probe & 128) grow &= 31;
-                if (grow < p.M) {
-                    uint4 *dst = reinterpret_cast<uint4 *>(cbase + (size_t)grow * p.ldc * kOutElem);
-                    if (p.probe & 256)
-                        __stcs(dst, val);
-                    else
-                        *dst = val;
-                }
+            if (i + 1 < nchunks) tmem_ld_32x32(t_row + c_begin + 32 * (i + 1), vb);
+            process(va, va, i);
+            if (i + 1 < nchunks) {
+                tmem_ld_wait();
+                __syncwarp();
+                if (i + 2 < nchunks) tmem_ld_32x32(t_row + c_begin + 32 * (i + 2), va);
+                process(vb, vb, i + 1);
             }
-            __syncwarp();
         }
     }
 }
 
+// c_begin .. c_end: the output columns of the tile this warp drains (the whole tile by default;
+// kernels that put two warps on one lane quarter give each half of the columns).
 template <int EPI, int BLOCK_N>
 __device__ __forceinline__ void epilogue_tile(const UmmaParams &p, long long row0, int n0,
-                                              uint32_t t_row, uint8_t *staging) {
+                                              uint32_t t_row, uint8_t *staging, int c_begin = 0,
+                                              int c_end = (EPI == EPI_SWIGLU) ? BLOCK_N / 2 : BLOCK_N) {
     if constexpr (EPI == EPI_BF16) {
         switch (p.act) {  // uniform: one branch per tile, not per element
-        case O64_ACT_RELU: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_RELU>(p, row0, n0, t_row, staging); break;
-        case O64_ACT_GELU_TANH: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_GELU_TANH>(p, row0, n0, t_row, staging); break;
-        case O64_ACT_GELU_ERF: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_GELU_ERF>(p, row0, n0, t_row, staging); break;
-        case O64_ACT_SILU: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_SILU>(p, row0, n0, t_row, staging); break;
-        default: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_NONE>(p, row0, n0, t_row, staging); break;
+        case O64_ACT_RELU: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_RELU>(p, row0, n0, t_row, staging, c_begin, c_end); break;
+        case O64_ACT_GELU_TANH: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_GELU_TANH>(p, row0, n0, t_row, staging, c_begin, c_end); break;
+        case O64_ACT_GELU_ERF: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_GELU_ERF>(p, row0, n0, t_row, staging, c_begin, c_end); break;
+        case O64_ACT_SILU: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_SILU>(p, row0, n0, t_row, staging, c_begin, c_end); break;
+        default: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_NONE>(p, row0, n0, t_row, staging, c_begin, c_end); break;
         }
     } else {
-        epilogue_tile_act<EPI, BLOCK_N, O64_ACT_NONE>(p, row0, n0, t_row, staging);
+        epilogue_tile_act<EPI, BLOCK_N, O64_ACT_NONE>(p, row0, n0, t_row, staging, c_begin, c_end);
     }
 }
 

@@ -3,24 +3,27 @@
 // tensor memory (512 columns).
 //
 // Why this shape.  Measured on B200 with the narrower kernels of this library:
-//   * one thread cannot issue tcgen05.mma faster than about one per 130 cycles (about 160 for
-//     the paired form), which is no faster than a 128 x 256 x 16 MMA executes: a single issuing
-//     thread leaves gaps in the tensor pipe;
 //   * a CTA that computes 128 x 256 per K block must pull 48 KB through the L2 -> shared-memory
-//     path every 512 tensor cycles, and four stages in flight do not cover that path's latency.
-// Here two threads issue (one per accumulator), so the tensor pipe always has work queued, and
-// a K block of 48 KB per CTA (256 rows of A, half of the 256-row B block) feeds 1024 tensor
-// cycles: half the fill rate, twice the latency tolerance.
+//     path every 512 tensor cycles; with four stages of shared memory the loads in flight do
+//     not cover that path's latency (about 1.3 microseconds) and the MMA thread waits for data
+//     about a fifth of the time;
+//   * paired MMAs that all accumulate into ONE accumulator cost about 165 cycles each instead
+//     of 128; alternated between TWO accumulators they run at 129 cycles each.
+// Here a K block of 48 KB per CTA (256 rows of A, half of the 256-row B block) feeds 1024
+// tensor cycles: half the fill rate, twice the latency tolerance, and the single issuing thread
+// alternates between the two accumulators.  The price: both accumulators fill tensor memory, so
+// the epilogue of a tile cannot overlap the next tile's MMAs on the same accumulator; it is
+// kept short (eight warps, coalesced stores) and accumulator 0 is released as soon as it is
+// drained, so the next tile starts on it while accumulator 1 drains.
 //
-// Roles per CTA (256 threads):
-//   warp 0      producer: TMA loads of A (one 256-row box) and this rank's half of B, completing
-//               on the full barrier of rank 0
-//   warp 1, 2   rank 0 only: MMA issuers for accumulator 0 (rows 0..127 of each CTA) and
-//               accumulator 1 (rows 128..255); each commits to empty[stage] (count 2) and to
-//               its own acc_full barrier, in both CTAs with one masked commit
-//   warp 3      allocates tensor memory
-//   warps 4..7  epilogue: drain accumulator 0 then accumulator 1, releasing each as soon as it
-//               is drained so that the next tile's MMAs on it can start
+// Roles per CTA (320 threads); the loops run on whole warps, one elected lane issues:
+//   warp 0      producer: TMA loads of A (one 256-row box) and this rank's half of B,
+//               completing on the full barrier of rank 0
+//   warp 1      allocates tensor memory; on rank 0 issues the paired MMAs: per K block four on
+//               accumulator 0 (rows 0..127 of each CTA), four on accumulator 1 (rows 128..255),
+//               then one commit delivered to empty[stage] of both ranks
+//   warps 2..9  epilogue: two warps per TMEM lane quarter, each draining half of the columns,
+//               accumulator 0 then accumulator 1
 // Every wait is bounded; both CTAs of a pair meet at a cluster barrier before tensor memory is
 // freed.
 #include <cstdio>
@@ -37,7 +40,8 @@ constexpr int kWaitWideMmaAccEmpty = 0x303;
 constexpr int kWaitWideEpiAccFull = 0x304;
 constexpr int kWideTmemMismatch = 0x305;
 
-constexpr int kWideThreads = 256;
+constexpr int kWideThreads = 320;  // producer, MMA, eight epilogue warps
+constexpr int kWideEpiWarps = 8;
 constexpr int kWideBlockN = 256;
 constexpr int kWideStages = 4;
 constexpr int kWideRowsPerCta = 256;
@@ -48,7 +52,7 @@ constexpr int kWideStageBytes = kWideABytes + kWideBBytes;    // 48 KB
 struct WideSmem {
     static constexpr int kRingBytes = kWideStages * kWideStageBytes;
     static constexpr int kStagingOffset = kRingBytes;
-    static constexpr int kBarOffset = kStagingOffset + kEpiStagingBytes;
+    static constexpr int kBarOffset = kStagingOffset + kWideEpiWarps * kEpiStagingBytesPerWarp;
     // full[S], empty[S], acc_full[2], acc_empty[2]
     static constexpr int kNumBars = 2 * kWideStages + 4;
     static constexpr int kTmemPtrOffset = kBarOffset + 8 * kNumBars;
@@ -100,7 +104,7 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         }
         for (int g = 0; g < 2; ++g) {
             mbar_init(acc_full_bar(g), 1);
-            mbar_init(acc_empty_bar(g), 8);  // four epilogue warps in each CTA
+            mbar_init(acc_empty_bar(g), 2 * kWideEpiWarps);  // the epilogue warps of both CTAs
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -108,7 +112,7 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         tma_prefetch_desc(&tm_b);
         if (EPI == EPI_SWIGLU) tma_prefetch_desc(&tm_b2);
     }
-    if (warp == 3) {
+    if (warp == 1) {
         // the whole tensor memory of this SM, from empty: both CTAs get base column 0
         tmem_alloc(smem_u32(smem_gen + L::kTmemPtrOffset), kTmemCols);
         tmem_relinquish();
@@ -289,9 +293,12 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             }
         }
         __syncwarp();
-    } else if (warp >= 4) {
+    } else if (warp >= 2) {
         // ------------------------------ epilogue (both ranks) -------------------------------
+        // two warps per TMEM lane quarter, each draining half of the columns
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
+        constexpr int kColsPerWarp = kOutN / 2;
         int it = 0;
         bool ok = true;
         long long epi_clk = 0;
@@ -311,21 +318,22 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                 const long long e0 = p.dbg ? clock64() : 0;
                 if (!(p.probe & 4))
                     epilogue_tile<EPI, BLOCK_N>(p, row0, nb * kOutN, t_row,
-                                                smem_gen + L::kStagingOffset + quarter * kEpiStagingBytesPerWarp);
+                                                smem_gen + L::kStagingOffset + (warp - 2) * kEpiStagingBytesPerWarp,
+                                                half * kColsPerWarp, (half + 1) * kColsPerWarp);
                 tc_fence_before();
                 __syncwarp();
                 if (p.dbg) epi_clk += clock64() - e0;
                 if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty_bar(g), 0));
             }
         }
-        if (p.dbg && warp == 4 && lane == 0) p.dbg[blockIdx.x * 8 + 4] = epi_clk;
+        if (p.dbg && warp == 2 && lane == 0) p.dbg[blockIdx.x * 8 + 4] = epi_clk;
     }
 
     // ------------------------------ teardown --------------------------------------------
     tc_fence_before();
     __syncthreads();
     cluster_sync_all();
-    if (warp == 3) {
+    if (warp == 1) {
         if (*abort_flag) {
             const uint64_t t0 = globaltimer_ns();
             while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);

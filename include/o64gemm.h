@@ -163,6 +163,18 @@ int o64_gemm_s8s8_s32(o64_handle_t h, int64_t M, int64_t N, int64_t K, const int
                       int64_t lda, const int8_t *B, int64_t ldb, int32_t *C, int64_t ldc,
                       void *stream);
 
+/* The same product for callers that must not allocate device memory (no counterpart in the
+ * reference: its runtime mallocs freely, osprey/libfi/matrix/matmul.h:222-266).  No handle, no
+ * cudaMalloc / cudaFree anywhere on the path: the status word of the bounded waits and the padded
+ * copies of operands whose base or row pitch is not a multiple of 16 bytes live in one static device
+ * array of O64_STATIC_SCRATCH_BYTES per GPU.  Device pointers only.  Returns O64_ERR_NOMEM, and does
+ * nothing, when the padded copies (M*ceil16(K) for A plus N*ceil16(K) for B, each only if needed)
+ * exceed the array.  The first call on a device resolves the array's address; make it before any
+ * stream capture.  Calls on one device share the array: calls that overlap on the GPU race. */
+#define O64_STATIC_SCRATCH_BYTES (16u << 20)
+int o64_gemm_s8s8_s32_static(int64_t M, int64_t N, int64_t K, const int8_t *A, int64_t lda,
+                             const int8_t *B, int64_t ldb, int32_t *C, int64_t ldc, void *stream);
+
 /* One-thread-per-output reference kernels: an independent device implementation of the same
  * contracts, used to compare full matrices where a CPU check would take minutes.
  * out_f32: fp32 result [M,N] (s32 for O64_KIND_S8).  For O64_KIND_FP8 the scales and bias

@@ -396,7 +396,7 @@ int umma_launch(const UmmaCall &c) {
     // synchronous and prints the averages (a tuning aid, off by default)
     static unsigned long long *dbg_buf = nullptr;
     const char *tr = getenv("O64_TRACE");
-    const bool trace_pipe = tr && strstr(tr, "pipe");
+    const bool trace_pipe = tr && strstr(tr, "pipe") && c.may_allocate;
     p.dbg = nullptr;
     if (trace_pipe) {
         if (!dbg_buf && cudaMalloc(&dbg_buf, 8 * 1024 * sizeof(unsigned long long)) != cudaSuccess) dbg_buf = nullptr;

@@ -31,6 +31,7 @@ struct UmmaCall {
     o64_plan_t plan;
     int *status_word;  // device int, 0 = ok
     cudaStream_t stream;
+    bool may_allocate = true;  // false: never allocate (the pipeline trace, which needs a buffer, stays off)
 };
 
 // Validates alignment, encodes the tensor maps and launches.  Returns O64_OK or an error code.

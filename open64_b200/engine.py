@@ -169,6 +169,21 @@ class Engine:
                                          _ptr(out), out.stride(0), _stream(A)), "o64_gemm_s8s8_s32")
         return out
 
+    @staticmethod
+    def gemm_s8_static(A, B, out=None):
+        """The int8 product through the entry point that allocates nothing: no handle, scratch in
+        a static device array (see include/o64gemm.h).  Device tensors only."""
+        lib = _lib.lib()
+        M, K = A.shape
+        N = B.shape[0]
+        if B.shape[1] != K:
+            raise O64Error(_lib.ERR_CONFORM, "gemm_s8_static")
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.int32, device=A.device)
+        check(lib.o64_gemm_s8s8_s32_static(M, N, K, _ptr(A), A.stride(0), _ptr(B), B.stride(0), _ptr(out),
+                                           out.stride(0), _stream(A)), "o64_gemm_s8s8_s32_static")
+        return out
+
     def naive(self, kind, A, B, transB=True, scaleA=None, scaleB=None, bias=None, act="none"):
         """One-thread-per-output device reference; fp32 result (int32 for KIND_S8)."""
         M, K = A.shape

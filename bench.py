@@ -113,6 +113,7 @@ def cpu_baseline(budget_s=12.0, rows=128):
     `budget_s` of CPU time has gone; returns TFLOP/s and what was run."""
     import numpy as np
     import oracle
+    oracle.set_num_threads(0)  # all host cores, whatever the launcher put in OMP_NUM_THREADS
     rng = np.random.default_rng(1002)
     A = (rng.standard_normal((rows, K)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
     B = (rng.standard_normal((N, K)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
@@ -131,7 +132,7 @@ def cpu_baseline(budget_s=12.0, rows=128):
                       f"{dt:.1f} s, gcc -O3 loop nest (opencc and the Fortran kernels do not build here)"}
 
 
-def run_reference(args, rank):
+def run_reference(args, rank, emit):
     if rank != 0:
         return
     t_all = time.perf_counter()
@@ -142,7 +143,7 @@ def run_reference(args, rank):
     v = statistics.mean(x["value"] for x in vals)
     base = dict(vals[-1], value=v)
     ms = FLOPS / (v * 1e12) * 1e3
-    print(json.dumps({
+    emit({
         "impl": "reference", "metric": METRIC, "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -150,10 +151,20 @@ def run_reference(args, rank):
         "cpu_baseline": base,
         "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_s": time.perf_counter() - t_all,
-    }))
+    })
 
 
 def main():
+    # exactly one line goes to stdout: libraries that print there (NCCL's version banner) are
+    # sent to stderr, and the JSON line is written to the saved descriptor at the end
+    sys.stdout.flush()
+    real_stdout = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+
+    def emit(obj):
+        real_stdout.write(json.dumps(obj) + "\n")
+        real_stdout.flush()
+
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
@@ -169,7 +180,7 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
 
     if args.impl == "reference":
-        run_reference(args, rank)
+        run_reference(args, rank, emit)
         return
 
     import torch
@@ -316,7 +327,7 @@ def main():
     if world > 1:
         dist.barrier()
     if rank == 0:
-        print(json.dumps(out))
+        emit(out)
     eng.close()
     if world > 1:
         dist.destroy_process_group()

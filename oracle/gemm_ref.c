@@ -315,6 +315,15 @@ void o64ref_s4gemvx(int M, int N, float alpha, const float *A, int inc1a, int in
     }
 }
 
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; the CPU baseline asks for the cores back. */
+void o64ref_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int o64ref_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -18,7 +18,7 @@ __all__ = [
     "ACT_NONE", "ACT_RELU", "ACT_GELU_TANH", "ACT_GELU_ERF", "ACT_SILU", "build", "lib",
     "linear_f32", "linear_f32_acc64", "gemm_bf16", "swiglu_bf16", "gemm_fp8_scaled",
     "gemm_s8s8_s32", "s4gemmx", "s4gemvx", "internal_mm_f32", "bf16_to_f32", "f32_to_bf16",
-    "e4m3_to_f32", "f32_to_e4m3", "num_threads",
+    "e4m3_to_f32", "f32_to_e4m3", "num_threads", "set_num_threads",
 ]
 
 
@@ -184,3 +184,9 @@ def f32_to_e4m3(a):
 
 def num_threads():
     return int(lib().o64ref_num_threads())
+
+
+def set_num_threads(n):
+    """Overrides OMP_NUM_THREADS for the oracle's loops (0 or None: all cores of the host)."""
+    lib().o64ref_set_num_threads(I(int(n) if n else (os.cpu_count() or 1)))
+    return num_threads()

@@ -316,6 +316,10 @@ def main():
             ws = torch.empty((M5, N5), dtype=torch.int32, device=dev)
             t = time_steps(lambda: eng.gemm_s8_sharded(A5d, B5d, N5, gather=o.GATHER_ROWMAJOR, out=c5, workspace=ws), s2, w2)
             ex["c5_int8_sharded_allgather_rowmajor"] = {"ms": t, "tops": f5 / (t * 1e-3) / 1e12}
+            del ws
+            c5p = eng.alloc_result(M5, N5)
+            t = time_steps(lambda: eng.gemm_s8_sharded(A5d, B5d, N5, gather=o.GATHER_PUSH, out=c5p), s2, w2)
+            ex["c5_int8_sharded_fused_push_rowmajor"] = {"ms": t, "tops": f5 / (t * 1e-3) / 1e12}
         st, detail = eng.last_status()
         if st != 0:
             raise SystemExit(f"device status {st} (detail 0x{detail:x})")

@@ -197,8 +197,15 @@ int o64_comm_destroy(o64_handle_t h);
 enum {
     O64_GATHER_NONE = 0,      /* write only this rank's slab into C_full[:, r*N/g ...] */
     O64_GATHER_ROWMAJOR = 1,  /* all-gather, then permute into row-major C_full [M,N] */
-    O64_GATHER_SLABS = 2      /* all-gather only: C_full is [g][M][N/g] (slab-major) */
+    O64_GATHER_SLABS = 2,     /* all-gather only: C_full is [g][M][N/g] (slab-major) */
+    O64_GATHER_PUSH = 3       /* fused: the GEMM kernel stores each finished tile into every rank's
+                                 row-major C_full over NVLink peer memory; no separate collective.
+                                 C_full must come from o64_comm_alloc_result; N/g a multiple of 32 */
 };
+/* Allocates `bytes` of device memory on every rank (collective over the communicator) and maps
+ * every rank's allocation into every other rank's address space; returns this rank's pointer.
+ * The handle owns the memory (freed by o64_comm_destroy / o64_destroy / the next call). */
+int o64_comm_alloc_result(o64_handle_t h, size_t bytes, void **local);
 /* A [M,K] replicated, B_slab [N/g,K] local, C_full [M,N] int32 (ldc = N) on every rank.
  * workspace: device scratch of at least o64_gemm_s8_sharded_workspace(...) bytes, or NULL to
  * let the handle grow its own. */

@@ -13,7 +13,7 @@ OK = 0
 ERR_RANK, ERR_CONFORM, ERR_NOMEM, ERR_ALIGN, ERR_DTYPE, ERR_TIMEOUT, ERR_CUDA, ERR_NCCL = range(-1, -9, -1)
 ACT_NONE, ACT_RELU, ACT_GELU_TANH, ACT_GELU_ERF, ACT_SILU = range(5)
 KIND_F32, KIND_BF16, KIND_FP8, KIND_S8 = range(4)
-GATHER_NONE, GATHER_ROWMAJOR, GATHER_SLABS = range(3)
+GATHER_NONE, GATHER_ROWMAJOR, GATHER_SLABS, GATHER_PUSH = range(4)
 UNIQUE_ID_BYTES = 128
 STATIC_SCRATCH_BYTES = 16 << 20
 
@@ -22,7 +22,7 @@ EXPORTS = [
     "o64_create", "o64_destroy", "o64_last_status", "o64_status_string", "o64_version",
     "o64_plan_get", "o64_plan_set", "o64_plan_model", "o64_linear_f32", "o64_gemm_bf16", "o64_gemm_bf16_swiglu",
     "o64_gemm_fp8_scaled", "o64_gemm_s8s8_s32", "o64_gemm_s8s8_s32_static", "o64_naive_gemm", "o64_comm_unique_id",
-    "o64_comm_init", "o64_comm_destroy", "o64_gemm_s8_sharded_workspace", "o64_gemm_s8_sharded",
+    "o64_comm_init", "o64_comm_destroy", "o64_comm_alloc_result", "o64_gemm_s8_sharded_workspace", "o64_gemm_s8_sharded",
     "sgemm_", "_s4gemmx__", "_s4gemvx__", "o64_compat_last_status",
 ]
 
@@ -87,6 +87,7 @@ def lib():
     L.o64_comm_unique_id.argtypes = [vp]
     L.o64_comm_init.argtypes = [vp, vp, ci, ci]
     L.o64_comm_destroy.argtypes = [vp]
+    L.o64_comm_alloc_result.argtypes = [vp, ctypes.c_size_t, ctypes.POINTER(vp)]
     L.o64_gemm_s8_sharded_workspace.argtypes = [i64, i64, ci, ci]
     L.o64_gemm_s8_sharded_workspace.restype = ctypes.c_size_t
     L.o64_gemm_s8_sharded.argtypes = [vp, i64, i64, i64, vp, i64, vp, i64, vp, ci, vp, vp]

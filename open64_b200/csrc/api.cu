@@ -27,10 +27,13 @@ struct NcclApi {
     int (*CommInitRank)(ncclComm_t *, int, ncclUniqueId_, int) = nullptr;
     int (*CommDestroy)(ncclComm_t) = nullptr;
     int (*AllGather)(const void *, void *, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    int (*AllReduce)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
     const char *(*GetErrorString)(int) = nullptr;
     bool ok = false;
 };
 static const int kNcclInt32 = 2;
+static const int kNcclInt8 = 0;
+static const int kNcclSum = 0;
 
 static NcclApi &nccl() {
     static NcclApi api;
@@ -50,8 +53,10 @@ static NcclApi &nccl() {
     api.CommDestroy = (int (*)(ncclComm_t))dlsym(api.lib, "ncclCommDestroy");
     api.AllGather = (int (*)(const void *, void *, size_t, int, ncclComm_t, cudaStream_t))dlsym(
         api.lib, "ncclAllGather");
+    api.AllReduce = (int (*)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t))dlsym(
+        api.lib, "ncclAllReduce");
     api.GetErrorString = (const char *(*)(int))dlsym(api.lib, "ncclGetErrorString");
-    api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllGather;
+    api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllGather && api.AllReduce;
     return api;
 }
 
@@ -69,6 +74,12 @@ struct o64_handle_s {
     size_t ws_cap = 0;
     ncclComm_t comm = nullptr;
     int rank = 0, nranks = 1;
+    // symmetric result buffer for the fused GEMM + all-gather (one allocation per rank, every
+    // rank holds peer-mapped pointers to the others')
+    void *sym_local = nullptr;
+    void *sym_peer[8] = {nullptr};  // indexed by rank; [rank] == sym_local
+    size_t sym_bytes = 0;
+    int *barrier_word = nullptr;    // one int, reduced over the ranks as a stream-ordered barrier
 };
 
 #define CUDA_TRY(x)                          \
@@ -135,8 +146,22 @@ extern "C" int o64_create(o64_handle_t *out, int device) {
     return O64_OK;
 }
 
+static void free_symmetric(o64_handle_t h) {
+    for (int i = 0; i < 8; ++i) {
+        if (h->sym_peer[i] && i != h->rank) cudaIpcCloseMemHandle(h->sym_peer[i]);
+        h->sym_peer[i] = nullptr;
+    }
+    if (h->sym_local) cudaFree(h->sym_local);
+    h->sym_local = nullptr;
+    h->sym_bytes = 0;
+    if (h->barrier_word) cudaFree(h->barrier_word);
+    h->barrier_word = nullptr;
+    (void)cudaGetLastError();
+}
+
 extern "C" int o64_comm_destroy(o64_handle_t h) {
     if (!h) return O64_ERR_RANK;
+    free_symmetric(h);
     if (h->comm) {
         if (nccl().ok) nccl().CommDestroy(h->comm);
         h->comm = nullptr;
@@ -482,6 +507,70 @@ extern "C" int o64_comm_init(o64_handle_t h, const void *id_bytes, int rank, int
     return O64_OK;
 }
 
+// Stream-ordered barrier over the ranks: a one-int all-reduce.
+static int rank_barrier(o64_handle_t h, cudaStream_t s) {
+    if (h->nranks == 1) return O64_OK;
+    if (!h->comm || !h->barrier_word) return O64_ERR_NCCL;
+    return nccl().AllReduce(h->barrier_word, h->barrier_word, 1, kNcclInt32, kNcclSum, h->comm, s) == 0
+               ? O64_OK
+               : O64_ERR_NCCL;
+}
+
+extern "C" int o64_comm_alloc_result(o64_handle_t h, size_t bytes, void **local) {
+    if (!h || !local || bytes == 0) return O64_ERR_RANK;
+    *local = nullptr;
+    const int g = h->nranks;
+    if (g > 8) return O64_ERR_RANK;
+    if (g > 1 && !h->comm) return O64_ERR_NCCL;
+    DeviceGuard guard(h->device);
+    free_symmetric(h);
+    if (cudaMalloc(&h->sym_local, bytes) != cudaSuccess || cudaMalloc(&h->barrier_word, sizeof(int)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        free_symmetric(h);
+        return O64_ERR_NOMEM;
+    }
+    cudaMemset(h->barrier_word, 0, sizeof(int));
+    h->sym_bytes = bytes;
+    h->sym_peer[h->rank] = h->sym_local;
+    if (g > 1) {
+        // exchange the inter-process handles of the allocations with an all-gather of 64-byte records
+        cudaIpcMemHandle_t mine;
+        if (cudaIpcGetMemHandle(&mine, h->sym_local) != cudaSuccess) {
+            (void)cudaGetLastError();
+            free_symmetric(h);
+            return O64_ERR_CUDA;
+        }
+        static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+        unsigned char *dev_all = nullptr;
+        if (cudaMalloc(&dev_all, 64 * (size_t)g) != cudaSuccess) {
+            (void)cudaGetLastError();
+            free_symmetric(h);
+            return O64_ERR_NOMEM;
+        }
+        cudaMemcpy(dev_all + 64 * h->rank, &mine, 64, cudaMemcpyHostToDevice);
+        int rc = nccl().AllGather(dev_all + 64 * h->rank, dev_all, 64, kNcclInt8, h->comm, nullptr);
+        cudaIpcMemHandle_t all[8];
+        if (rc == 0 && cudaStreamSynchronize(nullptr) == cudaSuccess)
+            cudaMemcpy(all, dev_all, 64 * (size_t)g, cudaMemcpyDeviceToHost);
+        cudaFree(dev_all);
+        if (rc != 0) {
+            free_symmetric(h);
+            return O64_ERR_NCCL;
+        }
+        for (int i = 0; i < g; ++i) {
+            if (i == h->rank) continue;
+            if (cudaIpcOpenMemHandle(&h->sym_peer[i], all[i], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+                (void)cudaGetLastError();
+                h->sym_peer[i] = nullptr;
+                free_symmetric(h);
+                return O64_ERR_CUDA;
+            }
+        }
+    }
+    *local = h->sym_local;
+    return O64_OK;
+}
+
 extern "C" size_t o64_gemm_s8_sharded_workspace(int64_t M, int64_t N, int nranks, int gather) {
     (void)nranks;
     if (gather != O64_GATHER_ROWMAJOR || M <= 0 || N <= 0) return 0;
@@ -494,7 +583,7 @@ extern "C" int o64_gemm_s8_sharded(o64_handle_t h, int64_t M, int64_t N, int64_t
     if (!h || M <= 0 || N <= 0 || K <= 0 || !A || !B_slab || !C_full) return O64_ERR_RANK;
     const int g = h->nranks, r = h->rank;
     if (N % g) return O64_ERR_CONFORM;
-    if (gather < O64_GATHER_NONE || gather > O64_GATHER_SLABS) return O64_ERR_RANK;
+    if (gather < O64_GATHER_NONE || gather > O64_GATHER_PUSH) return O64_ERR_RANK;
     if (gather != O64_GATHER_NONE && g > 1 && !h->comm) return O64_ERR_NCCL;
     if (is_host_ptr(A) || is_host_ptr(B_slab) || is_host_ptr(C_full)) return O64_ERR_RANK;
     const int64_t ns = N / g;
@@ -504,6 +593,42 @@ extern "C" int o64_gemm_s8_sharded(o64_handle_t h, int64_t M, int64_t N, int64_t
 
     if (gather == O64_GATHER_NONE) {
         return o64_gemm_s8s8_s32(h, M, ns, K, A, lda, B_slab, ldb, C_full + (int64_t)r * ns, N, stream);
+    }
+    if (gather == O64_GATHER_PUSH) {
+        // ONE kernel computes this rank's column slab and stores every finished tile into all
+        // ranks' copies of C (its own and, over NVLink, the peers'), so the exchange overlaps the
+        // GEMM tile by tile.  C_full must be the buffer o64_comm_alloc_result handed out.
+        if (C_full != (int32_t *)h->sym_local || (size_t)M * N * 4 > h->sym_bytes) return O64_ERR_RANK;
+        if (ns % 32) return O64_ERR_CONFORM;  // whole 128-byte store slabs only
+        if (is_host_ptr(A) || is_host_ptr(B_slab)) return O64_ERR_RANK;
+        // nobody may still be reading the previous result when the first remote store lands
+        if ((rc = rank_barrier(h, s))) return rc;
+        const void *dA = A, *dB = B_slab;
+        int64_t lda_eff = lda, ldb_eff = ldb;
+        if ((rc = repack_if_unaligned(h, 6, &dA, &lda_eff, M, K, 1, s))) return rc;
+        if ((rc = repack_if_unaligned(h, 7, &dB, &ldb_eff, ns, K, 1, s))) return rc;
+        UmmaCall c;
+        c.kind = O64_KIND_S8;
+        c.b_kn = false;
+        c.epi = EPI_S32;
+        c.M = M; c.N = ns; c.K = K;
+        c.A = dA; c.lda = lda_eff;
+        c.B = dB; c.B2 = nullptr; c.ldb = ldb_eff;
+        c.C = C_full + (int64_t)r * ns; c.ldc = N;
+        c.bias = nullptr; c.scale_a = nullptr; c.scale_b = nullptr;
+        c.act = O64_ACT_NONE;
+        choose(h, O64_KIND_S8, EPI_S32, M, ns, K, &c.plan);
+        c.status_word = h->status_word;
+        c.stream = s;
+        c.n_peers = 0;
+        for (int i = 0; i < g; ++i) {
+            if (i == r) continue;
+            c.peer_c[c.n_peers++] = (int32_t *)h->sym_peer[i] + (int64_t)r * ns;
+        }
+        if ((rc = umma_launch(c))) return rc;
+        // every rank's stores are complete when its kernel is; the barrier tells each rank that
+        // all the others got there
+        return rank_barrier(h, s);
     }
     int32_t *slabs = C_full;  // [g][M][ns]
     if (gather == O64_GATHER_ROWMAJOR) {

@@ -23,6 +23,10 @@ struct UmmaParams {
     unsigned long long *dbg;  // tuning aid (O64_TRACE=pipe): per-CTA wait/total cycles of the issuing threads
     int probe;   // 0 = normal; 1 = skip the loads, 2 = skip the MMAs (pipeline probes, results invalid)
     int *status;
+    // fused all-gather: the same result tile is also stored into these peer GPUs' copies of C
+    // (peer-mapped device pointers to the same element as C); 0 peers = plain GEMM
+    int n_peers;
+    void *peer_c[7];
 };
 
 constexpr int kBlockM = 128;
@@ -196,7 +200,14 @@ __device__ __forceinline__ void epilogue_tile_act(const UmmaParams &p, long long
                 const int r = 4 * r4 + (lane >> 3);
                 const uint4 val = patch[r * 8 + (piece ^ (r & 7))];
                 const long long grow = row0 + r;
-                if (grow < p.M) *reinterpret_cast<uint4 *>(cbase + (size_t)grow * p.ldc * kOutElem) = val;
+                if (grow < p.M) {
+                    const size_t off = (size_t)(n0 + slab_c) * kOutElem + piece * 16 + (size_t)grow * p.ldc * kOutElem;
+                    *reinterpret_cast<uint4 *>(cbase + (size_t)grow * p.ldc * kOutElem) = val;
+                    // the exchange step of a column-sharded linear, fused: push the tile over NVLink
+                    // into every peer's copy of C while the next tile's MMAs run
+                    for (int d = 0; d < p.n_peers; ++d)
+                        *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.peer_c[d]) + off) = val;
+                }
             }
             __syncwarp();
         }

@@ -388,6 +388,9 @@ int umma_launch(const UmmaCall &c) {
     const int out_elem = (c.epi == EPI_S32) ? 4 : 2;
     p.vec_ok = aligned16(c.C) && ((c.ldc * out_elem) % 16 == 0);
     p.status = c.status_word;
+    p.n_peers = c.n_peers;
+    for (int i = 0; i < 7; ++i) p.peer_c[i] = c.peer_c[i];
+    if (c.n_peers > 0 && !p.vec_ok) return O64_ERR_ALIGN;  // the fused exchange uses the vector-store path only
     {
         const char *pr = getenv("O64_PROBE");  // pipeline probes for tuning; results are invalid
         p.probe = pr ? atoi(pr) : 0;

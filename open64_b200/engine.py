@@ -214,6 +214,22 @@ class Engine:
                                      rank, world), "o64_comm_init")
         return rank, world
 
+    def alloc_result(self, M, N, dtype=torch.int32):
+        """A [M,N] result buffer that every rank of the bound communicator can store into (the
+        target of GATHER_PUSH).  Collective; the engine owns the memory."""
+
+        class _Ext:
+            pass
+
+        nbytes = M * N * torch.empty((), dtype=dtype).element_size()
+        ptr = ctypes.c_void_p()
+        check(self.lib.o64_comm_alloc_result(self._h, nbytes, ctypes.byref(ptr)), "o64_comm_alloc_result")
+        ext = _Ext()
+        ext.__cuda_array_interface__ = {"shape": (M, N), "typestr": "<i4" if dtype == torch.int32 else "<u2",
+                                        "data": (ptr.value, False), "version": 2, "strides": None}
+        t = torch.as_tensor(ext, device=torch.device("cuda", self.device))
+        return t if dtype == torch.int32 else t.view(dtype)
+
     def gemm_s8_sharded(self, A, B_slab, N, gather=GATHER_ROWMAJOR, out=None, workspace=None):
         """Column-sharded int8 GEMM: this rank owns B_slab [N/g, K]; `out` is the full [M,N]
         int32 (row-major, or slab-major [g][M][N/g] for GATHER_SLABS)."""

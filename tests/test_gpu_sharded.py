@@ -26,6 +26,14 @@ def test_single_rank_modes(eng):
         C = eng.gemm_s8_sharded(Ad, Bd, N, gather=mode)
         assert np.array_equal(C.cpu().numpy(), ref), mode
     assert eng.lib.o64_gemm_s8_sharded_workspace(M, N, 1, o.GATHER_ROWMAJOR) == M * N * 4
+    # the fused form needs the engine's own result buffer
+    import pytest as _pt
+    with _pt.raises(o.O64Error):
+        eng.gemm_s8_sharded(Ad, Bd, N, gather=o.GATHER_PUSH)
+    out = eng.alloc_result(M, N)
+    out.fill_(-1)
+    eng.gemm_s8_sharded(Ad, Bd, N, gather=o.GATHER_PUSH, out=out)
+    assert np.array_equal(out.cpu().numpy(), ref)
 
 
 def _rank_main(rank, world, port, q):
@@ -55,6 +63,13 @@ def _rank_main(rank, world, port, q):
         lin(Ad, gather=oo.GATHER_NONE, out=mine)
         lo, hi = sharded.slab_bounds(N, rank, world)
         assert torch.equal(mine[:, lo:hi].cpu(), ref[:, lo:hi]) and (mine[:, :lo] == -1).all()
+        # fused GEMM + exchange: one kernel stores its tiles into every rank's result buffer
+        out = eng.alloc_result(M, N)
+        for rep in range(2):
+            out.fill_(-1 - rep)
+            lin(Ad, gather=oo.GATHER_PUSH, out=out)
+            torch.cuda.synchronize()
+            assert torch.equal(out.cpu(), ref), f"fused push, call {rep}"
         st, detail = eng.last_status()
         assert st == 0
         torch.cuda.synchronize()

@@ -154,6 +154,49 @@ def run_reference(args, rank, emit):
     })
 
 
+def run_only(args, eng, o, torch, dev, time_steps, emit):
+    """One secondary configuration by itself: a handful of launches of its kernels (what the ncu
+    summaries under profiles/ were captured from) and one JSON line."""
+    steps, warm = max(1, args.steps), args.warmup
+    if args.only == "c3":
+        x, Wg, Wu, Wd = (t_.to(dev) for t_ in o.workloads.c3_swiglu())
+        h = torch.empty(4096, 14336, dtype=torch.bfloat16, device=dev)
+        out = torch.empty(4096, 4096, dtype=torch.bfloat16, device=dev)
+        t = time_steps(lambda: eng.mlp_swiglu(x, Wg, Wu, Wd, h=h, out=out), steps, warm)
+        emit({"config": "c3_swiglu_mlp", "ms": t, "tflops": 1443109011456 / (t * 1e-3) / 1e12})
+    elif args.only == "c4":
+        A8, W8, sA, sB, b4 = (t_.to(dev) for t_ in o.workloads.c4_fp8())
+        c4 = torch.empty(4096, 8192, dtype=torch.bfloat16, device=dev)
+        t = time_steps(lambda: eng.gemm_fp8_scaled(A8, W8, sA, sB, b4, out=c4), steps, warm)
+        emit({"config": "c4_fp8_scaled", "ms": t, "tflops": 2 * 4096 * 8192 * 8192 / (t * 1e-3) / 1e12})
+    elif args.only == "c5":
+        A5, B5 = (t_.to(dev) for t_ in o.workloads.c5_int8())
+        c5 = torch.empty((16384, 8192), dtype=torch.int32, device=dev)
+        t = time_steps(lambda: eng.gemm_s8(A5, B5, out=c5), steps, warm)
+        emit({"config": "c5_int8", "ms": t, "tops": 2 * 16384 * 8192 * 8192 / (t * 1e-3) / 1e12})
+    else:
+        # skinny shapes: few rows of A against a large weight; bound by HBM (the weight is read once)
+        res = {}
+        hbm = measured_peaks()["hbm_gbs"]
+        for Ms in (16, 64, 128):
+            Ns, Ks = 8192, 8192
+            A, B = o.workloads.c2_gemm_bf16(Ms, Ns, Ks)
+            Ad, Bd = A.to(dev), B.to(dev)
+            Bs = [Bd.clone() for _ in range(2)]          # rotate weights: 2 x 134 MB exceeds L2
+            C = torch.empty((Ms, Ns), dtype=torch.bfloat16, device=dev)
+            it = [0]
+
+            def step():
+                eng.gemm_bf16(Ad, Bs[it[0] & 1], transB=True, out=C)
+                it[0] += 1
+
+            t = time_steps(step, steps, warm)
+            nbytes = (Ms * Ks + Ns * Ks + Ms * Ns) * 2
+            res[f"M{Ms}"] = {"us": t * 1e3, "gbs": nbytes / (t * 1e-3) / 1e9, "frac_of_measured_hbm": nbytes / (t * 1e-3) / 1e9 / hbm,
+                             "plan": eng.plan_get(o.KIND_BF16, Ms, Ns, Ks)["tile_n"]}
+        emit({"config": "skinny_bf16_Mx8192x8192", "results": res})
+
+
 def main():
     # exactly one line goes to stdout: libraries that print there (NCCL's version banner) are
     # sent to stderr, and the JSON line is written to the saved descriptor at the end
@@ -172,6 +215,8 @@ def main():
     ap.add_argument("--impl", default="o64", choices=["o64", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary configurations")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--only", default=None, choices=["c3", "c4", "c5", "skinny"],
+                    help="run just one secondary configuration (few launches; for profiling) and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -218,6 +263,11 @@ def main():
         e1.record()
         barrier()
         return max_over_ranks(e0.elapsed_time(e1) / steps)
+
+    if args.only:
+        run_only(args, eng, o, torch, dev, time_steps, emit)
+        eng.close()
+        return
 
     # ---- headline: C2, operands resident in HBM ---------------------------------------
     A, B = o.workloads.c2_gemm_bf16(M, N, K)                    # A replicated on every rank

@@ -229,6 +229,31 @@ void _s4gemmx__(const int *m, const int *n, const int *k, const float *alpha, co
 void _s4gemvx__(const int *m, const int *n, const float *alpha, const float *a,
                 const int *incca, const int *incra, const float *x, const int *incx,
                 const float *beta, float *y, const int *incy);
+/* The operator entry point the reference's Fortran front end emits for MATMUL on REAL*4 operands
+ * (osprey/libfi/matrix/matmul_s4s4.c:66-112; argument parsing osprey/libfi/matrix/matmul.h:135-400).
+ * o64_dopevec_t is the x86-64 little-endian layout of DopeVectorType
+ * (osprey/clibinc/cray/dopevec.h:212-334) with the bit-fields written out as words:
+ *   flags0: bit 0 assoc, bit 1 ptr_alloc, bits 2-3 p_or_a, bit 4 a_contig, bit 5 alloc_cpnt
+ *   flags1: bits 29-31 n_dim
+ *   type_bits: bits 0-7 type (3 = REAL), bit 8 dpflag, bits 9-11 kind_or_star, bits 12-23 int_len
+ *              (element length in bits), bits 24-31 dec_len
+ * stride_mult is in elements for 32-bit elements.  As in the reference: rank combinations other
+ * than (2,2), (2,1), (1,2) are an error (FESCIRNK), extents must conform (FESCICNF), and a RESULT
+ * that is not associated is allocated with malloc and handed to the caller (FENOMEMY on failure);
+ * unlike the reference nothing aborts: the code is left in o64_compat_last_status(). */
+typedef struct {
+    void *ptr;             /* base address (host or device) */
+    unsigned long el_len;  /* element length in bits */
+    uint32_t flags0, flags1;
+    uint32_t type_pad, type_bits;
+    void *orig_base;
+    unsigned long orig_size;
+    struct {
+        long low_bound, extent, stride_mult;
+    } dimension[7];
+} o64_dopevec_t;
+void _MATMUL_S4S4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+
 /* Status of the last compat call on this thread (the Fortran entry points return void). */
 int o64_compat_last_status(void);
 

@@ -23,7 +23,7 @@ EXPORTS = [
     "o64_plan_get", "o64_plan_set", "o64_plan_model", "o64_linear_f32", "o64_gemm_bf16", "o64_gemm_bf16_swiglu",
     "o64_gemm_fp8_scaled", "o64_gemm_s8s8_s32", "o64_gemm_s8s8_s32_static", "o64_naive_gemm", "o64_comm_unique_id",
     "o64_comm_init", "o64_comm_destroy", "o64_comm_alloc_result", "o64_gemm_s8_sharded_workspace", "o64_gemm_s8_sharded",
-    "sgemm_", "_s4gemmx__", "_s4gemvx__", "o64_compat_last_status",
+    "sgemm_", "_s4gemmx__", "_s4gemvx__", "_MATMUL_S4S4", "o64_compat_last_status",
 ]
 
 
@@ -38,6 +38,33 @@ class Plan(ctypes.Structure):
 
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_}
+
+
+class DvDimen(ctypes.Structure):
+    _fields_ = [("low_bound", ctypes.c_long), ("extent", ctypes.c_long), ("stride_mult", ctypes.c_long)]
+
+
+class DopeVector(ctypes.Structure):
+    """o64_dopevec_t: the reference's DopeVectorType on x86-64 (osprey/clibinc/cray/dopevec.h:212-334)."""
+    _fields_ = [("ptr", ctypes.c_void_p), ("el_len", ctypes.c_ulong), ("flags0", ctypes.c_uint32),
+                ("flags1", ctypes.c_uint32), ("type_pad", ctypes.c_uint32), ("type_bits", ctypes.c_uint32),
+                ("orig_base", ctypes.c_void_p), ("orig_size", ctypes.c_ulong), ("dimension", DvDimen * 7)]
+
+    @classmethod
+    def real4(cls, ptr, extents, strides, assoc=True):
+        """A REAL*4 array descriptor: extents and element strides per dimension."""
+        d = cls()
+        d.ptr = ptr
+        d.el_len = 32
+        d.flags0 = 1 if assoc else 0
+        d.flags1 = len(extents) << 29
+        d.type_bits = 3 | (32 << 12)
+        d.orig_base = ptr
+        for i, (e, s) in enumerate(zip(extents, strides)):
+            d.dimension[i].low_bound = 1
+            d.dimension[i].extent = e
+            d.dimension[i].stride_mult = s
+        return d
 
 
 class Epilogue(ctypes.Structure):
@@ -97,6 +124,8 @@ def lib():
     L._s4gemmx__.restype = None
     L._s4gemvx__.argtypes = [pi, pi, pf, vp, pi, pi, vp, pi, pf, vp, pi]
     L._s4gemvx__.restype = None
+    L._MATMUL_S4S4.argtypes = [ctypes.POINTER(DopeVector)] * 3
+    L._MATMUL_S4S4.restype = None
     L.o64_compat_last_status.restype = ci
     _lib = L
     return L

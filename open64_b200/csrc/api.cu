@@ -789,3 +789,110 @@ extern "C" void _s4gemvx__(const int *m, const int *n, const float *alpha, const
     if (!rc && !out.host && cudaStreamSynchronize(s) != cudaSuccess) rc = O64_ERR_CUDA;
     g_compat_status = rc;
 }
+
+// ---- the MATMUL operator entry point (osprey/libfi/matrix/matmul_s4s4.c:66-112) ----------------
+namespace {
+struct DvView {
+    float *ptr;
+    int ndim;
+    long n1, n2, inc1, inc2;
+};
+
+// Extents and element strides of a dope vector, as _premult reads them
+// (osprey/libfi/matrix/matmul.h:145-176): multi-word elements carry a factor in stride_mult.
+DvView view_of(const o64_dopevec_t *d) {
+    DvView v;
+    v.ptr = static_cast<float *>(d->ptr);
+    v.ndim = (int)(d->flags1 >> 29);
+    const unsigned int_len = (d->type_bits >> 12) & 0xfffu;
+    const int shift = int_len == 64 ? 1 : (int_len == 128 ? 2 : (int_len == 256 ? 3 : 0));
+    v.n1 = d->dimension[0].extent;
+    v.inc1 = d->dimension[0].stride_mult >> shift;
+    if (v.ndim == 1) {
+        v.n2 = 1;
+        v.inc2 = v.inc1;
+    } else {
+        v.n2 = d->dimension[1].extent;
+        v.inc2 = d->dimension[1].stride_mult >> shift;
+    }
+    return v;
+}
+}  // namespace
+
+extern "C" void _MATMUL_S4S4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B) {
+    if (!RESULT || !MATRIX_A || !MATRIX_B) {
+        g_compat_status = O64_ERR_RANK;
+        return;
+    }
+    const DvView a = view_of(MATRIX_A), b = view_of(MATRIX_B);
+    if (!((a.ndim == 1 && b.ndim == 2) || (a.ndim == 2 && b.ndim == 1) || (a.ndim == 2 && b.ndim == 2))) {
+        g_compat_status = O64_ERR_RANK;  // FESCIRNK
+        return;
+    }
+    // allocate RESULT if it is not associated (matmul.h:222-266)
+    if (!(RESULT->flags0 & 1u)) {
+        unsigned int_len = (RESULT->type_bits >> 12) & 0xfffu;
+        if (int_len == 0) int_len = 32;
+        long stride0 = int_len / 32;
+        if (stride0 == 0) stride0 = 1;
+        RESULT->dimension[0].stride_mult = stride0;
+        RESULT->dimension[0].low_bound = 1;
+        long nbits;
+        if (a.ndim == 1) {
+            RESULT->dimension[0].extent = b.n2;
+            nbits = b.n2 * (long)int_len;
+        } else if (b.ndim == 1) {
+            RESULT->dimension[0].extent = a.n1;
+            nbits = a.n1 * (long)int_len;
+        } else {
+            RESULT->dimension[0].extent = a.n1;
+            RESULT->dimension[1].low_bound = 1;
+            RESULT->dimension[1].extent = b.n2;
+            RESULT->dimension[1].stride_mult = a.n1 * stride0;
+            nbits = a.n1 * b.n2 * (long)int_len;
+        }
+        const long nbytes = nbits >> 3;
+        void *mem = nullptr;
+        if (nbytes != 0) {
+            mem = malloc((size_t)nbytes);
+            if (!mem) {
+                g_compat_status = O64_ERR_NOMEM;  // FENOMEMY
+                return;
+            }
+        }
+        RESULT->flags0 |= 1u;
+        RESULT->ptr = mem;
+        RESULT->orig_base = mem;
+        RESULT->orig_size = (unsigned long)nbits;
+    }
+    const DvView c = view_of(RESULT);
+    const int one_i = 1;
+    (void)one_i;
+    const float one = 1.0f, zero = 0.0f;
+    if (a.ndim == 2 && b.ndim == 2) {
+        if (!(a.n2 == b.n1 && c.n1 == a.n1 && c.n2 == b.n2)) {
+            g_compat_status = O64_ERR_CONFORM;  // FESCICNF
+            return;
+        }
+        const int m = (int)a.n1, n = (int)b.n2, k = (int)a.n2;
+        const int i1a = (int)a.inc1, i2a = (int)a.inc2, i1b = (int)b.inc1, i2b = (int)b.inc2;
+        const int i1c = (int)c.inc1, i2c = (int)c.inc2;
+        _s4gemmx__(&m, &n, &k, &one, a.ptr, &i1a, &i2a, b.ptr, &i1b, &i2b, &zero, c.ptr, &i1c, &i2c);
+    } else if (a.ndim == 2) {  // y = A x
+        if (!(a.n2 == b.n1 && a.n1 == c.n1)) {
+            g_compat_status = O64_ERR_CONFORM;
+            return;
+        }
+        const int m = (int)a.n1, n = (int)a.n2;
+        const int i1a = (int)a.inc1, i2a = (int)a.inc2, ix = (int)b.inc1, iy = (int)c.inc1;
+        _s4gemvx__(&m, &n, &one, a.ptr, &i1a, &i2a, b.ptr, &ix, &zero, c.ptr, &iy);
+    } else {  // y = x B, i.e. y' = B' x'
+        if (!(a.n1 == b.n1 && c.n1 == b.n2)) {
+            g_compat_status = O64_ERR_CONFORM;
+            return;
+        }
+        const int m = (int)b.n2, n = (int)b.n1;
+        const int i1 = (int)b.inc2, i2 = (int)b.inc1, ix = (int)a.inc1, iy = (int)c.inc1;
+        _s4gemvx__(&m, &n, &one, b.ptr, &i1, &i2, a.ptr, &ix, &zero, c.ptr, &iy);
+    }
+}

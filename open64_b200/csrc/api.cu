@@ -209,7 +209,7 @@ extern "C" int o64_plan_set(o64_handle_t h, int kind, const o64_plan_t *plan) {
     if (plan->cta_group && plan->cta_group != 1 && plan->cta_group != 2) return O64_ERR_RANK;
     if (plan->tile_m && plan->cta_group && (plan->cta_group == 1) != (plan->tile_m == 128)) return O64_ERR_RANK;
     if (plan->tile_m == 512 && plan->tile_n && plan->tile_n != 256) return O64_ERR_RANK;
-    if (plan->group_m < 0 || plan->num_ctas < 0) return O64_ERR_RANK;
+    if (plan->group_m < 0 || plan->num_ctas < 0 || plan->split_k < 0) return O64_ERR_RANK;
     h->pins[kind] = *plan;
     h->has_pin[kind] = true;
     return O64_OK;
@@ -435,7 +435,27 @@ static int umma_entry(o64_handle_t h, int kind, bool b_kn, int epi, int64_t M, i
     choose(h, kind, epi, M, N, K, &c.plan);
     c.status_word = h->status_word;
     c.stream = s;
+    // split-K (few tiles, long K): partial sums meet in scratch memory; a second small kernel
+    // applies the epilogue for 16-bit results, int32 results are summed in place
+    const bool split = c.plan.split_k > 1 && c.plan.cta_group == 1 && epi != EPI_SWIGLU;
+    if (split) {
+        if (epi == EPI_S32) {
+            CUDA_TRY(cudaMemset2DAsync(out.dev, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, s));
+        } else {
+            if ((rc = reserve(&h->ws, &h->ws_cap, (size_t)M * N * 4))) return rc;
+            CUDA_TRY(cudaMemsetAsync(h->ws, 0, (size_t)M * N * 4, s));
+            c.partial = h->ws;
+        }
+        c.split_ready = true;
+    } else {
+        c.plan.split_k = 1;
+    }
     if ((rc = umma_launch(c))) return rc;
+    if (split && epi != EPI_S32) {
+        if ((rc = finalize_partial_bf16((const float *)h->ws, M, N, c.scale_a, c.scale_b, c.bias, act, out.dev,
+                                        ldc, s)))
+            return rc;
+    }
     return stage_out_end(out, s);
 }
 

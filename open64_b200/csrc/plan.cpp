@@ -146,6 +146,26 @@ void plan_choose(int kind, int epi, int64_t M, int64_t N, int64_t K, int num_sms
     } else {
         out->group_m = 2048 / out->tile_m;
     }
+    // Split-K: when a CTA-per-tile plan leaves most SMs idle and K is long, slices of K go to
+    // separate CTAs (the reference's cache model blocks K the same way when one level cannot hold
+    // a whole strip, osprey/be/lno/cache_model.cxx:6650-6727).  Skinny GEMMs are bound by HBM:
+    // every SM must have loads in flight.
+    if (out->cta_group == 1 && epi != EPI_SWIGLU) {
+        const int out_n = tile_n;
+        const long long tiles = ((M + 127) / 128) * ((N + out_n - 1) / out_n);
+        const long long kblocks = (K + out->tile_k - 1) / out->tile_k;
+        int sk = pin.split_k > 0 ? pin.split_k : 1;
+        // measured on M x 8192 x 8192: worth it for M = 16 (42 -> 38 us), not for M = 128 (the
+        // atomics grow with M)
+        if (pin.split_k <= 0 && tiles * 2 <= out->num_ctas && kblocks >= 16 && (M <= 64 || tiles * 8 <= out->num_ctas)) {
+            sk = (int)(out->num_ctas / tiles);
+            if (sk > kblocks / 8) sk = (int)(kblocks / 8);
+            if (sk > 16) sk = 16;
+            if (sk < 1) sk = 1;
+        }
+        if (sk > kblocks) sk = (int)kblocks;
+        out->split_k = sk;
+    }
     out->raster = pin.raster ? 1 : 0;  // the automatic choice is 0 (M fastest)
 
     const char *tr = getenv("O64_TRACE");

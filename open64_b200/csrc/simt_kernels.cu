@@ -327,6 +327,32 @@ int naive_gemm(int kind, int64_t M, int64_t N, int64_t K, const void *A, int64_t
     return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
 }
 
+__global__ void finalize_partial_kernel(const float *__restrict__ partial, long long M, long long N,
+                                        const float *scale_a, const float *scale_b, const float *bias,
+                                        int act, __nv_bfloat16 *C, long long ldc) {
+    const long long total = M * N;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+         e += (long long)gridDim.x * blockDim.x) {
+        const long long i = e / N, j = e % N;
+        float x = partial[e];
+        if (scale_a) x *= scale_a[i];
+        if (scale_b) x *= scale_b[j];
+        if (bias) x += bias[j];
+        C[i * ldc + j] = __float2bfloat16_rn(act_f32(x, act));
+    }
+}
+
+int finalize_partial_bf16(const float *partial, int64_t M, int64_t N, const float *scale_a,
+                          const float *scale_b, const float *bias, int act, void *C, int64_t ldc,
+                          cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return O64_OK;
+    long long blocks = ((long long)M * N + 255) / 256;
+    if (blocks > 148LL * 8) blocks = 148LL * 8;
+    finalize_partial_kernel<<<(unsigned)blocks, 256, 0, stream>>>(partial, M, N, scale_a, scale_b, bias, act,
+                                                                  reinterpret_cast<__nv_bfloat16 *>(C), ldc);
+    return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
+}
+
 // ------------------------------------------------------------------------------------------
 // slab permute: the all-gather delivers [g][M][N/g]; callers that want row-major [M,N] get it
 // through this copy (16-byte vectors when the slab width allows).

@@ -23,6 +23,11 @@ struct UmmaParams {
     unsigned long long *dbg;  // tuning aid (O64_TRACE=pipe): per-CTA wait/total cycles of the issuing threads
     int probe;   // 0 = normal; 1 = skip the loads, 2 = skip the MMAs (pipeline probes, results invalid)
     int *status;
+    // split-K: each tile's K blocks are divided over split_k work items whose partial sums are
+    // added (fp32 / int32 atomics) into `partial` (fp32 results: a dense [M,N] workspace, finished
+    // by a second kernel) or straight into C (int32 results, C zeroed first); 1 = off
+    int split_k, kb_per_split;
+    void *partial;
     // fused all-gather: the same result tile is also stored into these peer GPUs' copies of C
     // (peer-mapped device pointers to the same element as C); 0 peers = plain GEMM
     int n_peers;
@@ -265,6 +270,51 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams &p, long long row
         }
     } else {
         epilogue_tile_act<EPI, BLOCK_N, O64_ACT_NONE>(p, row0, n0, t_row, staging, c_begin, c_end);
+    }
+}
+
+// Split-K epilogue: adds this work item's raw partial sums into `dst` ([M, ldd] of 4-byte
+// elements) with atomics.  Through the same swizzled patch as the normal epilogue so that a warp
+// instruction adds to four full 128-byte row segments.
+template <bool INTEGER>
+__device__ __forceinline__ void epilogue_partial(const UmmaParams &p, void *dst, long long ldd, long long row0,
+                                                 int n0, uint32_t t_row, uint8_t *staging, int ncols) {
+    const int lane = threadIdx.x & 31;
+    uint4 *patch = reinterpret_cast<uint4 *>(staging);
+    const int sw = lane & 7;
+    const int cols_avail = min(ncols, p.N - n0);
+    const int nchunks = cols_avail > 0 ? (cols_avail + 31) >> 5 : 0;
+#pragma unroll 1
+    for (int i = 0; i < nchunks; ++i) {
+        uint32_t v[32];
+        __syncwarp();
+        tmem_ld_32x32(t_row + 32 * i, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+            patch[lane * 8 + (q ^ sw)] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        __syncwarp();
+        const int piece = lane & 7;
+#pragma unroll
+        for (int r4 = 0; r4 < 8; ++r4) {
+            const int r = 4 * r4 + (lane >> 3);
+            const uint4 val = patch[r * 8 + (piece ^ (r & 7))];
+            const long long grow = row0 + r;
+            const int col = n0 + 32 * i + piece * 4;
+            if (grow < p.M) {
+                const uint32_t w[4] = {val.x, val.y, val.z, val.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    if (col + e < p.N) {
+                        if constexpr (INTEGER)
+                            atomicAdd(reinterpret_cast<int *>(dst) + grow * ldd + col + e, (int)w[e]);
+                        else
+                            atomicAdd(reinterpret_cast<float *>(dst) + grow * ldd + col + e, __uint_as_float(w[e]));
+                    }
+                }
+            }
+        }
+        __syncwarp();
     }
 }
 

@@ -76,6 +76,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+    const int num_work = num_tiles * p.split_k;  // a work item = (tile, slice of its K blocks)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -110,12 +111,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             bool ok = true;
             long long wait_clk = 0;
             const long long t_begin = clock64();
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
                 int mb, nb;
-                tile_coords(t, p, mb, nb);
+                tile_coords(w / p.split_k, p, mb, nb);
                 const int m0 = mb * kBlockM;
                 const int n0 = nb * kOutN;
-                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                const int kb_begin = (w % p.split_k) * p.kb_per_split;
+                const int kb_end = min(kb_begin + p.kb_per_split, p.num_k_blocks);
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     const long long c0 = p.dbg ? clock64() : 0;
                     ok = mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
                                            kWaitProducerEmpty);
@@ -180,16 +183,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             // MMAs, so that the probe's latency hides behind the issue instead of opening a gap
             // in the tensor pipe between two K blocks.
             uint32_t ready = mbar_test_wait(full_bar(0), 0);
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+            for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++it) {
                 const int buf = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1u;
+                const int kb_begin = (w % p.split_k) * p.kb_per_split;
+                const int kb_end = min(kb_begin + p.kb_per_split, p.num_k_blocks);
                 ok = mbar_wait_bounded(acc_empty_bar(buf), acc_phase ^ 1u, abort_flag, p.status,
                                        kWaitMmaAccEmpty);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BLOCK_N;
-                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!__all_sync(0xffffffffu, ready)) {
                         const long long c0 = p.dbg ? clock64() : 0;
                         ok = mbar_wait_bounded(full_bar(stage), phase, abort_flag, p.status,
@@ -213,7 +218,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll
                         for (int k = 0; k < kMmaPerStage; ++k) {
                             tc_mma<KIND>(d_tmem, a_desc + 2u * k, b_desc + kBAdvance * k, idesc,
-                                         (kb | k) != 0 ? 1u : 0u);
+                                         ((kb - kb_begin) | k) != 0 ? 1u : 0u);
                         }
                         tc_commit(empty_bar(stage));  // frees the stage when these MMAs retire
                     }
@@ -236,9 +241,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const int quarter = warp & 3;  // TMEM lane quarter this warp may read
         int it = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++it) {
             int mb, nb;
-            tile_coords(t, p, mb, nb);
+            tile_coords(w / p.split_k, p, mb, nb);
             const int buf = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1u;
             // one lane polls, the warp follows (tcgen05.ld is warp-wide: the warp leaves together)
@@ -250,7 +255,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             tc_fence_after();
             const long long row0 = (long long)mb * kBlockM + quarter * 32;
             const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BLOCK_N;
-            if (!(p.probe & 4))
+            if (p.split_k > 1) {
+                if constexpr (EPI == EPI_S32)
+                    epilogue_partial<true>(p, p.C, p.ldc, row0, nb * kOutN, t_row,
+                                           smem_gen + L::kStagingOffset + quarter * kEpiStagingBytesPerWarp, BLOCK_N);
+                else if constexpr (EPI != EPI_SWIGLU)
+                    epilogue_partial<false>(p, p.partial, p.N, row0, nb * kOutN, t_row,
+                                            smem_gen + L::kStagingOffset + quarter * kEpiStagingBytesPerWarp, BLOCK_N);
+            } else if (!(p.probe & 4))
                 epilogue_tile<EPI, BLOCK_N>(p, row0, nb * kOutN, t_row,
                                             smem_gen + L::kStagingOffset + quarter * kEpiStagingBytesPerWarp);
             tc_fence_before();
@@ -388,6 +400,15 @@ int umma_launch(const UmmaCall &c) {
     const int out_elem = (c.epi == EPI_S32) ? 4 : 2;
     p.vec_ok = aligned16(c.C) && ((c.ldc * out_elem) % 16 == 0);
     p.status = c.status_word;
+    p.split_k = 1;
+    p.kb_per_split = p.num_k_blocks;
+    p.partial = nullptr;
+    if (!pair && c.split_ready && pl.split_k > 1 && c.epi != EPI_SWIGLU && (c.partial || c.epi == EPI_S32)) {
+        const int per = (p.num_k_blocks + pl.split_k - 1) / pl.split_k;
+        p.kb_per_split = per;
+        p.split_k = (p.num_k_blocks + per - 1) / per;  // every slice non-empty
+        p.partial = c.partial;
+    }
     p.n_peers = c.n_peers;
     for (int i = 0; i < 7; ++i) p.peer_c[i] = c.peer_c[i];
     if (c.n_peers > 0 && !p.vec_ok) return O64_ERR_ALIGN;  // the fused exchange uses the vector-store path only
@@ -429,7 +450,7 @@ int umma_launch(const UmmaCall &c) {
     };
     if (wide) return report(umma_launch_wide(c, ta, tb, tb2, p), pl.num_ctas);
     if (pair) return report(umma_launch_pair(c, ta, tb, tb2, p), pl.num_ctas);
-    const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles;
+    const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles * p.split_k;
     const int grid = (int)(tiles < pl.num_ctas ? tiles : pl.num_ctas);
 
 #define O64_INST(KIND, BKN, EPI_, BN, ST) \

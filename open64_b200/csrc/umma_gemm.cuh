@@ -31,6 +31,8 @@ struct UmmaCall {
     o64_plan_t plan;
     int *status_word;  // device int, 0 = ok
     cudaStream_t stream;
+    bool split_ready = false;  // split-K: the caller has zeroed `partial` (or C, for int32 results)
+    void *partial = nullptr;   // split-K: zeroed fp32 [M,N] workspace (fp32-accumulating kinds)
     int n_peers = 0;           // fused all-gather: peer copies of C (same element as C), at most 7
     void *peer_c[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     bool may_allocate = true;  // false: never allocate (the pipeline trace, which needs a buffer, stays off)

@@ -217,3 +217,32 @@ def test_every_kind_on_one_cta_and_on_cta_pairs(eng, cta_group, tile_n):
     finally:
         for kind in (o.KIND_BF16, o.KIND_FP8, o.KIND_S8):
             eng.plan_set(kind)
+
+
+@pytest.mark.parametrize("shape", [(16, 1024, 4096), (60, 520, 2056), (128, 256, 8192), (40, 300, 1096)])
+def test_split_k_for_skinny_shapes(eng, shape):
+    """Few output tiles and a long K: slices of K go to separate CTAs and meet in scratch memory
+    (fp32 atomics + a finishing kernel for 16-bit results, int32 atomics in place for int8)."""
+    M, N, K = shape
+    assert eng.plan_get(o.KIND_BF16, M, N, K)["split_k"] > 1
+    A, B = _bf16_case(M, N, K, True, seed=21)
+    bias = torch.randn(N, generator=torch.Generator().manual_seed(3))
+    ref = oracle.gemm_bf16(bits16(A), bits16(B), bias=bias.numpy(), act=oracle.ACT_RELU, transB=True)
+    for rep in range(2):   # the scratch is re-zeroed by every call
+        C = eng.gemm_bf16(A.to(DEV), B.to(DEV), transB=True, bias=bias.to(DEV), act="relu")
+        assert relmax(C.float().cpu().numpy(), ref) <= TOL_LOWP
+    try:
+        eng.plan_set(o.KIND_BF16, cta_group=1, tile_n=256, split_k=5)
+        C = eng.gemm_bf16(A.to(DEV), B.to(DEV), transB=True, bias=bias.to(DEV), act="relu")
+        assert relmax(C.float().cpu().numpy(), ref) <= TOL_LOWP
+    finally:
+        eng.plan_set(o.KIND_BF16)
+    Ai, Bi = o.workloads.c5_int8(M, N, K, seed=M + K)
+    Cpad = torch.full((M, N + 4), -9, dtype=torch.int32, device=DEV)
+    eng.gemm_s8(Ai.to(DEV), Bi.to(DEV), out=Cpad[:, :N])
+    assert np.array_equal(Cpad[:, :N].cpu().numpy(), oracle.gemm_s8s8_s32(Ai.numpy(), Bi.numpy()))
+    assert (Cpad[:, N:] == -9).all()
+    A8, W8, sA, sB, b8 = o.workloads.c4_fp8(M, N, K, seed=9)
+    C8 = eng.gemm_fp8_scaled(A8.to(DEV), W8.to(DEV), sA.to(DEV), sB.to(DEV), b8.to(DEV))
+    ref8 = oracle.gemm_fp8_scaled(bits8(A8), bits8(W8), sA.numpy(), sB.numpy(), b8.numpy())
+    assert relmax(C8.float().cpu().numpy(), ref8) <= TOL_LOWP

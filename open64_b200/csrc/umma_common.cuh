@@ -21,7 +21,8 @@ struct UmmaParams {
     int num_k_blocks;
     int vec_ok;  // C rows 16-byte aligned: vector stores allowed
     unsigned long long *dbg;  // tuning aid (O64_TRACE=pipe): per-CTA wait/total cycles of the issuing threads
-    int probe;   // 0 = normal; 1 = skip the loads, 2 = skip the MMAs (pipeline probes, results invalid)
+    int probe;   // O64_PROBE, tuning only, results invalid: 1 = skip the loads, 2 = skip the MMAs,
+                 // +4 = skip the epilogue, +32 = skip the global stores
     int *status;
     // split-K: each tile's K blocks are divided over split_k work items whose partial sums are
     // added (fp32 / int32 atomics) into `partial` (fp32 results: a dense [M,N] workspace, finished

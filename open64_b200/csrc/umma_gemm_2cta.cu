@@ -12,8 +12,8 @@
 //                completing on the full barrier OF RANK 0
 //                epilogue warps: drain this rank's 128 accumulator rows (its own tensor memory)
 //   rank 0 only  MMA warp: waits for full[stage] (bytes of both ranks), issues the paired
-//                MMAs, commits to the empty[stage] and acc_full[buf] barriers of BOTH ranks
-//                (two commits, one per CTA)
+//                MMAs, then one commit that arrives on empty[stage] (and, per tile, on
+//                acc_full[buf]) of BOTH ranks
 // acc_empty[buf] lives in rank 0 and counts the epilogue warps of both ranks.
 //
 // No load is shared between CTAs: every TMA load writes the issuing CTA's own shared memory.
@@ -100,13 +100,8 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     if (warp == 1) {
         // each CTA takes all the columns it needs from its own, otherwise empty, tensor memory:
         // both CTAs of the pair therefore get the same base address, which the paired MMA needs
-        if ((p.probe & 16) && kTmemCols <= 256) {  // tuning variant, only where a double allocation still fits
-            tmem_alloc_pair(smem_u32(smem_gen + L::kTmemPtrOffset), kTmemCols);
-            tmem_relinquish_pair();
-        } else {
-            tmem_alloc(smem_u32(smem_gen + L::kTmemPtrOffset), kTmemCols);
-            tmem_relinquish();
-        }
+        tmem_alloc(smem_u32(smem_gen + L::kTmemPtrOffset), kTmemCols);
+        tmem_relinquish();
     }
     tc_fence_before();
     __syncthreads();
@@ -127,22 +122,18 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             bool ok = true;
             long long wait_clk = 0;
             const long long t_begin = clock64();
-            const bool relay = (p.probe & 8) != 0;  // tuning variant: rank 0's producer passes the freed stage on
-            long long iter = 0;  // K blocks issued so far: the first STAGES find the ring empty
             for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
                 int mb, nb;
                 tile_coords(t, p, mb, nb);
                 const int m0 = mb * kPairM + (int)rank * kBlockM;
                 const int n0 = nb * kOutN;
-                for (int kb = 0; kb < p.num_k_blocks; ++kb, ++iter) {
+                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
                     const long long c0 = p.dbg ? clock64() : 0;
                     ok = mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
                                            kWaitPairProducerEmpty);
                     ok = __all_sync(0xffffffffu, ok);
                     if (p.dbg) wait_clk += clock64() - c0;
                     if (!ok) break;
-                    if (rank == 0 && relay && iter >= STAGES && leader)
-                        mbar_arrive_cluster(map_to_cta(empty_bar(stage), 1));
                     const uint32_t a_dst = smem_base + stage * L::kStageBytes;
                     const uint32_t b_dst = a_dst + kABytes;
                     const uint32_t full0 = map_to_cta(full_bar(stage), 0);
@@ -195,7 +186,6 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             bool ok = true;
             long long wait_clk = 0;
             const long long t_begin = clock64();
-            const bool relay = (p.probe & 8) != 0;
             uint32_t ready = mbar_test_wait(full_bar(0), 0);  // see the 1-CTA kernel: probe ahead
             for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++it) {
                 const int buf = it & 1;
@@ -226,7 +216,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                     if ((p.probe & 3) == 2) {
                         if (leader) {
                             mbar_arrive(empty_bar(stage));
-                            if (!relay) mbar_arrive_cluster(map_to_cta(empty_bar(stage), 1));
+                            mbar_arrive_cluster(map_to_cta(empty_bar(stage), 1));
                         }
                     } else if (leader) {
 #pragma unroll
@@ -236,10 +226,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                         }
                         // frees the stage in both CTAs when these MMAs retire: one commit delivered
                         // to the same barrier of both ranks
-                        if (relay)
-                            tc_commit_pair(empty_bar(stage));
-                        else
-                            tc_commit_pair_mask(empty_bar(stage), 3);
+                        tc_commit_pair_mask(empty_bar(stage), 3);
                     }
                     __syncwarp();
                     stage = next_stage;
@@ -292,10 +279,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
         }
         tc_fence_after();
-        if ((p.probe & 16) && kTmemCols <= 256)
-            tmem_dealloc_pair(tmem_base, kTmemCols);
-        else
-            tmem_dealloc(tmem_base, kTmemCols);
+        tmem_dealloc(tmem_base, kTmemCols);
     }
 }
 

@@ -198,7 +198,6 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             bool ok = true;
             long long wait_clk = 0, acc_wait_clk = 0;
             const long long t_begin = clock64();
-            const bool interleave = (p.probe & 16) != 0;
             uint32_t ready = mbar_test_wait(full_bar(0), 0);
             for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++it) {
                 for (int kb = 0; kb < p.num_k_blocks; ++kb) {
@@ -232,24 +231,11 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                             ok = mbar_wait_bounded(acc_empty_bar(0), (it & 1u) ^ 1u, abort_flag, p.status,
                                                    kWaitWideMmaAccEmpty);
                             if (p.dbg) acc_wait_clk += clock64() - a0;
-                            if (ok && interleave)
-                                ok = mbar_wait_bounded(acc_empty_bar(1), (it & 1u) ^ 1u, abort_flag, p.status,
-                                                       kWaitWideMmaAccEmpty);
                             ok = __all_sync(0xffffffffu, ok);
                             if (!ok) break;
                             tc_fence_after();
                         }
-                        if (interleave) {
-                            if (leader) {
-#pragma unroll
-                            for (int k = 0; k < kMmaPerStage; ++k) {
-                                tc_mma_pair<KIND>(tmem_base, a_desc0 + 2u * k, b_desc + kBAdvance * k, idesc,
-                                                  (kb | k) != 0 ? 1u : 0u);
-                                tc_mma_pair<KIND>(tmem_base + BLOCK_N, a_desc1 + 2u * k, b_desc + kBAdvance * k,
-                                                  idesc, (kb | k) != 0 ? 1u : 0u);
-                            }
-                            }
-                        } else {
+                        {
                             if (leader) {
 #pragma unroll
                                 for (int k = 0; k < kMmaPerStage; ++k)

@@ -24,6 +24,7 @@ EXPORTS = [
     "o64_gemm_fp8_scaled", "o64_gemm_s8s8_s32", "o64_gemm_s8s8_s32_static", "o64_naive_gemm", "o64_comm_unique_id",
     "o64_comm_init", "o64_comm_destroy", "o64_comm_alloc_result", "o64_gemm_s8_sharded_workspace", "o64_gemm_s8_sharded",
     "sgemm_", "_s4gemmx__", "_s4gemvx__", "_MATMUL_S4S4", "o64_compat_last_status",
+    "dgemm_", "_sgemmx__", "_sgemvx__", "_MATMUL_SS", "_i4gemmx__", "_MATMUL_I4I4", "_jgemmx__", "_MATMUL_JJ",
 ]
 
 
@@ -50,21 +51,29 @@ class DopeVector(ctypes.Structure):
                 ("flags1", ctypes.c_uint32), ("type_pad", ctypes.c_uint32), ("type_bits", ctypes.c_uint32),
                 ("orig_base", ctypes.c_void_p), ("orig_size", ctypes.c_ulong), ("dimension", DvDimen * 7)]
 
+    TYPE_INTEGER, TYPE_REAL = 2, 3  # osprey/clibinc/cray/dopevec.h: DVTYPE_INTEGER, DVTYPE_REAL
+
     @classmethod
-    def real4(cls, ptr, extents, strides, assoc=True):
-        """A REAL*4 array descriptor: extents and element strides per dimension."""
+    def make(cls, ptr, extents, strides, bits=32, type_code=3, assoc=True):
+        """An array descriptor: extents and ELEMENT strides per dimension; `bits` is the element
+        length (stride_mult is stored in 32-bit words for 64-bit elements, as the runtime expects)."""
         d = cls()
         d.ptr = ptr
-        d.el_len = 32
+        d.el_len = bits
         d.flags0 = 1 if assoc else 0
         d.flags1 = len(extents) << 29
-        d.type_bits = 3 | (32 << 12)
+        d.type_bits = type_code | (bits << 12)
         d.orig_base = ptr
         for i, (e, s) in enumerate(zip(extents, strides)):
             d.dimension[i].low_bound = 1
             d.dimension[i].extent = e
-            d.dimension[i].stride_mult = s
+            d.dimension[i].stride_mult = s * max(bits // 32, 1)
         return d
+
+    @classmethod
+    def real4(cls, ptr, extents, strides, assoc=True):
+        """A REAL*4 array descriptor: extents and element strides per dimension."""
+        return cls.make(ptr, extents, strides, 32, cls.TYPE_REAL, assoc)
 
 
 class Epilogue(ctypes.Structure):
@@ -124,8 +133,16 @@ def lib():
     L._s4gemmx__.restype = None
     L._s4gemvx__.argtypes = [pi, pi, pf, vp, pi, pi, vp, pi, pf, vp, pi]
     L._s4gemvx__.restype = None
-    L._MATMUL_S4S4.argtypes = [ctypes.POINTER(DopeVector)] * 3
-    L._MATMUL_S4S4.restype = None
+    L.dgemm_.argtypes = [ctypes.c_char_p, ctypes.c_char_p, pi, pi, pi, vp, vp, pi, vp, pi, vp, vp, pi]
+    L.dgemm_.restype = None
+    for name in ("_sgemmx__", "_i4gemmx__", "_jgemmx__"):
+        getattr(L, name).argtypes = [pi, pi, pi, vp, vp, pi, pi, vp, pi, pi, vp, vp, pi, pi]
+        getattr(L, name).restype = None
+    L._sgemvx__.argtypes = [pi, pi, vp, vp, pi, pi, vp, pi, vp, vp, pi]
+    L._sgemvx__.restype = None
+    for name in ("_MATMUL_S4S4", "_MATMUL_SS", "_MATMUL_I4I4", "_MATMUL_JJ"):
+        getattr(L, name).argtypes = [ctypes.POINTER(DopeVector)] * 3
+        getattr(L, name).restype = None
     L.o64_compat_last_status.restype = ci
     _lib = L
     return L

@@ -9,6 +9,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <new>
+#include <type_traits>
 
 #include "../../include/o64gemm.h"
 #include "simt_kernels.cuh"
@@ -694,44 +695,60 @@ static size_t strided_span(int64_t n1, int64_t n2, int64_t s1, int64_t s2) {
     return (size_t)((n1 - 1) * s1 + (n2 - 1) * s2 + 1);
 }
 
-static int xgemmx_impl(int M, int N, int K, float alpha, const float *A, int64_t a1, int64_t a2,
-                       const float *B, int64_t b1, int64_t b2, float beta, float *C, int64_t c1,
-                       int64_t c2, bool skip_zero) {
+// Element type the CUDA-core kernels compute in: the integer kinds run on the unsigned type of
+// the same width, whose wrap-around is the two's-complement result the Fortran kernels produce.
+template <typename T> struct ComputeType { typedef T type; };
+template <> struct ComputeType<int32_t> { typedef unsigned type; };
+template <> struct ComputeType<int64_t> { typedef unsigned long long type; };
+
+template <typename T>
+static int xgemmx_impl(int M, int N, int K, T alpha, const T *A, int64_t a1, int64_t a2, const T *B,
+                       int64_t b1, int64_t b2, T beta, T *C, int64_t c1, int64_t c2, bool skip_zero) {
+    typedef typename ComputeType<T>::type U;
     // quick returns, in the order of osprey/libfi/matrix/xgemmx.h:172-208
     if (M < 0 || N < 0 || K < 0) return O64_ERR_RANK;
-    if (M == 0 || N == 0 || (alpha == 0.0f && beta == 1.0f)) return O64_OK;
+    if (M == 0 || N == 0 || (alpha == T(0) && beta == T(1))) return O64_OK;
     if (a1 < 0 || a2 < 0 || b1 < 0 || b2 < 0 || c1 < 0 || c2 < 0) return O64_ERR_RANK;
     o64_handle_t h = compat_handle();
     if (!h) return O64_ERR_CUDA;
     DeviceGuard g(h->device);
     cudaStream_t s = nullptr;
-    const bool only_scale = (K == 0) || (alpha == 0.0f);
-    const float beta_eff = (K == 0) ? 0.0f : beta;
+    const bool only_scale = (K == 0) || (alpha == T(0));
+    const T beta_eff = (K == 0) ? T(0) : beta;
     const void *dA = A, *dB = B;
     StagedOut out;
     int rc;
     if (!only_scale) {
         if (!A || !B) return O64_ERR_RANK;
-        if ((rc = stage_in(h, 0, A, strided_span(M, K, a1, a2) * 4, s, &dA))) return rc;
-        if ((rc = stage_in(h, 1, B, strided_span(K, N, b1, b2) * 4, s, &dB))) return rc;
+        if ((rc = stage_in(h, 0, A, strided_span(M, K, a1, a2) * sizeof(T), s, &dA))) return rc;
+        if ((rc = stage_in(h, 1, B, strided_span(K, N, b1, b2) * sizeof(T), s, &dB))) return rc;
     }
     if (!C) return O64_ERR_RANK;
-    if ((rc = stage_out_begin(h, 3, C, strided_span(M, N, c1, c2) * 4, true, s, &out))) return rc;
-    if (only_scale) {
-        rc = simt_scale_f32(M, N, beta_eff, (float *)out.dev, c1, c2, s);
+    if ((rc = stage_out_begin(h, 3, C, strided_span(M, N, c1, c2) * sizeof(T), true, s, &out))) return rc;
+    if constexpr (std::is_same<T, float>::value) {
+        if (only_scale) {
+            rc = simt_scale_f32(M, N, beta_eff, (float *)out.dev, c1, c2, s);
+        } else {
+            SimtGemmCall c;
+            c.M = M; c.N = N; c.K = K;
+            c.alpha = alpha; c.beta = beta;
+            c.A = (const float *)dA; c.a1 = a1; c.a2 = a2;
+            c.B = (const float *)dB; c.b1 = b1; c.b2 = b2;
+            c.C = (float *)out.dev; c.c1 = c1; c.c2 = c2;
+            c.bias = nullptr;
+            c.act = O64_ACT_NONE;
+            c.skip_zero_b = skip_zero;
+            c.num_sms = h->num_sms;
+            c.stream = s;
+            rc = simt_gemm_f32(c);
+        }
     } else {
-        SimtGemmCall c;
-        c.M = M; c.N = N; c.K = K;
-        c.alpha = alpha; c.beta = beta;
-        c.A = (const float *)dA; c.a1 = a1; c.a2 = a2;
-        c.B = (const float *)dB; c.b1 = b1; c.b2 = b2;
-        c.C = (float *)out.dev; c.c1 = c1; c.c2 = c2;
-        c.bias = nullptr;
-        c.act = O64_ACT_NONE;
-        c.skip_zero_b = skip_zero;
-        c.num_sms = h->num_sms;
-        c.stream = s;
-        rc = simt_gemm_f32(c);
+        (void)skip_zero;  // a zero factor changes nothing for integers; the REAL*8 kernel always skips
+        if (only_scale)
+            rc = generic_scale<U>(M, N, (U)beta_eff, (U *)out.dev, c1, c2, s);
+        else
+            rc = generic_gemmx<U>(M, N, K, (U)alpha, (const U *)dA, a1, a2, (const U *)dB, b1, b2, (U)beta,
+                                  (U *)out.dev, c1, c2, s);
     }
     if (rc) return rc;
     if ((rc = stage_out_end(out, s))) return rc;
@@ -739,81 +756,105 @@ static int xgemmx_impl(int M, int N, int K, float alpha, const float *A, int64_t
     return O64_OK;
 }
 
-extern "C" void _s4gemmx__(const int *m, const int *n, const int *k, const float *alpha, const float *a,
-                           const int *inc1a, const int *inc2a, const float *b, const int *inc1b,
-                           const int *inc2b, const float *beta, float *c, const int *inc1c,
-                           const int *inc2c) {
-    g_compat_status = xgemmx_impl(*m, *n, *k, *alpha, a, *inc1a, *inc2a, b, *inc1b, *inc2b, *beta, c,
-                                  *inc1c, *inc2c, true);
+#define O64_XGEMMX_ENTRY(NAME, T)                                                                          \
+    extern "C" void NAME(const int *m, const int *n, const int *k, const T *alpha, const T *a,             \
+                         const int *inc1a, const int *inc2a, const T *b, const int *inc1b,                 \
+                         const int *inc2b, const T *beta, T *c, const int *inc1c, const int *inc2c) {      \
+        g_compat_status = xgemmx_impl<T>(*m, *n, *k, *alpha, a, *inc1a, *inc2a, b, *inc1b, *inc2b, *beta,  \
+                                         c, *inc1c, *inc2c, true);                                         \
+    }
+O64_XGEMMX_ENTRY(_s4gemmx__, float)
+O64_XGEMMX_ENTRY(_sgemmx__, double)
+O64_XGEMMX_ENTRY(_i4gemmx__, int32_t)
+O64_XGEMMX_ENTRY(_jgemmx__, int64_t)
+#undef O64_XGEMMX_ENTRY
+
+template <typename T>
+static int blas_gemm_impl(const char *transa, const char *transb, const int *m, const int *n, const int *k,
+                          const T *alpha, const T *a, const int *lda, const T *b, const int *ldb,
+                          const T *beta, T *c, const int *ldc) {
+    auto is_n = [](char ch) { return ch == 'n' || ch == 'N'; };
+    auto is_t = [](char ch) { return ch == 't' || ch == 'T' || ch == 'c' || ch == 'C'; };
+    const bool na = is_n(*transa), nb = is_n(*transb);
+    if ((!na && !is_t(*transa)) || (!nb && !is_t(*transb))) return O64_ERR_RANK;
+    const int rows_a = na ? *m : *k, rows_b = nb ? *k : *n;
+    if (*lda < (rows_a > 1 ? rows_a : 1) || *ldb < (rows_b > 1 ? rows_b : 1) || *ldc < (*m > 1 ? *m : 1))
+        return O64_ERR_CONFORM;
+    // column-major: op(A)(i,l) = A[i + l*lda] or A[l + i*lda]
+    const int64_t a1 = na ? 1 : *lda, a2 = na ? *lda : 1;
+    const int64_t b1 = nb ? 1 : *ldb, b2 = nb ? *ldb : 1;
+    return xgemmx_impl<T>(*m, *n, *k, *alpha, a, a1, a2, b, b1, b2, *beta, c, 1, *ldc, false);
 }
 
 extern "C" void sgemm_(const char *transa, const char *transb, const int *m, const int *n, const int *k,
                        const float *alpha, const float *a, const int *lda, const float *b, const int *ldb,
                        const float *beta, float *c, const int *ldc) {
-    auto is_n = [](char ch) { return ch == 'n' || ch == 'N'; };
-    auto is_t = [](char ch) { return ch == 't' || ch == 'T' || ch == 'c' || ch == 'C'; };
-    const bool na = is_n(*transa), nb = is_n(*transb);
-    if ((!na && !is_t(*transa)) || (!nb && !is_t(*transb))) {
-        g_compat_status = O64_ERR_RANK;
-        return;
-    }
-    const int rows_a = na ? *m : *k, rows_b = nb ? *k : *n;
-    if (*lda < (rows_a > 1 ? rows_a : 1) || *ldb < (rows_b > 1 ? rows_b : 1) ||
-        *ldc < (*m > 1 ? *m : 1)) {
-        g_compat_status = O64_ERR_CONFORM;
-        return;
-    }
-    // column-major: op(A)(i,l) = A[i + l*lda] or A[l + i*lda]
-    const int64_t a1 = na ? 1 : *lda, a2 = na ? *lda : 1;
-    const int64_t b1 = nb ? 1 : *ldb, b2 = nb ? *ldb : 1;
-    g_compat_status = xgemmx_impl(*m, *n, *k, *alpha, a, a1, a2, b, b1, b2, *beta, c, 1, *ldc, false);
+    g_compat_status = blas_gemm_impl<float>(transa, transb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
 }
 
-extern "C" void _s4gemvx__(const int *m, const int *n, const float *alpha, const float *a,
-                           const int *incca, const int *incra, const float *x, const int *incx,
-                           const float *beta, float *y, const int *incy) {
-    const int M = *m, N = *n;
-    g_compat_status = O64_OK;
-    if (M < 0 || N < 0) {
-        g_compat_status = O64_ERR_RANK;
-        return;
-    }
-    // quick returns of osprey/libfi/matrix/s4gemvx.f
-    if (M == 0) return;
+extern "C" void dgemm_(const char *transa, const char *transb, const int *m, const int *n, const int *k,
+                       const double *alpha, const double *a, const int *lda, const double *b, const int *ldb,
+                       const double *beta, double *c, const int *ldc) {
+    g_compat_status = blas_gemm_impl<double>(transa, transb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
+}
+
+template <typename T>
+static int xgemvx_impl(int M, int N, T alpha, const T *a, int64_t incca, int64_t incra, const T *x,
+                       int64_t incx, T beta, T *y, int64_t incy) {
+    if (M < 0 || N < 0) return O64_ERR_RANK;
+    // quick returns of osprey/libfi/matrix/s4gemvx.f (sgemvx.f is the same text in REAL*8)
+    if (M == 0) return O64_OK;
     const bool zero_only = (N == 0);
-    if (!zero_only && *alpha == 0.0f && *beta == 1.0f) return;
+    if (!zero_only && alpha == T(0) && beta == T(1)) return O64_OK;
     o64_handle_t h = compat_handle();
-    if (!h) {
-        g_compat_status = O64_ERR_CUDA;
-        return;
-    }
+    if (!h) return O64_ERR_CUDA;
     DeviceGuard g(h->device);
     cudaStream_t s = nullptr;
     const void *dA = a, *dX = x;
     StagedOut out;
     int rc = O64_OK;
-    const bool need_ax = !zero_only && *alpha != 0.0f;
+    const bool need_ax = !zero_only && alpha != T(0);
     if (need_ax) {
-        rc = stage_in(h, 0, a, strided_span(M, N, *incca, *incra) * 4, s, &dA);
-        if (!rc) rc = stage_in(h, 1, x, strided_span(N, 1, *incx, 0) * 4, s, &dX);
+        rc = stage_in(h, 0, a, strided_span(M, N, incca, incra) * sizeof(T), s, &dA);
+        if (!rc) rc = stage_in(h, 1, x, strided_span(N, 1, incx, 0) * sizeof(T), s, &dX);
     }
-    if (!rc) rc = stage_out_begin(h, 3, y, strided_span(M, 1, *incy, 0) * 4, true, s, &out);
+    if (!rc) rc = stage_out_begin(h, 3, y, strided_span(M, 1, incy, 0) * sizeof(T), true, s, &out);
     if (!rc) {
-        if (need_ax)
-            rc = simt_gemv_f32(M, N, *alpha, (const float *)dA, *incca, *incra, (const float *)dX, *incx,
-                               *beta, (float *)out.dev, *incy, s);
-        else
-            rc = simt_scale_f32(M, 1, zero_only ? 0.0f : *beta, (float *)out.dev, *incy, 0, s);
+        if constexpr (std::is_same<T, float>::value) {
+            if (need_ax)
+                rc = simt_gemv_f32(M, N, alpha, (const float *)dA, incca, incra, (const float *)dX, incx, beta,
+                                   (float *)out.dev, incy, s);
+            else
+                rc = simt_scale_f32(M, 1, zero_only ? 0.0f : beta, (float *)out.dev, incy, 0, s);
+        } else {
+            if (need_ax)
+                rc = generic_gemvx<T>(M, N, alpha, (const T *)dA, incca, incra, (const T *)dX, incx, beta,
+                                      (T *)out.dev, incy, s);
+            else
+                rc = generic_scale<T>(M, 1, zero_only ? T(0) : beta, (T *)out.dev, incy, 0, s);
+        }
     }
     if (!rc) rc = stage_out_end(out, s);
     if (!rc && !out.host && cudaStreamSynchronize(s) != cudaSuccess) rc = O64_ERR_CUDA;
-    g_compat_status = rc;
+    return rc;
+}
+
+extern "C" void _s4gemvx__(const int *m, const int *n, const float *alpha, const float *a,
+                           const int *incca, const int *incra, const float *x, const int *incx,
+                           const float *beta, float *y, const int *incy) {
+    g_compat_status = xgemvx_impl<float>(*m, *n, *alpha, a, *incca, *incra, x, *incx, *beta, y, *incy);
+}
+
+extern "C" void _sgemvx__(const int *m, const int *n, const double *alpha, const double *a,
+                          const int *incca, const int *incra, const double *x, const int *incx,
+                          const double *beta, double *y, const int *incy) {
+    g_compat_status = xgemvx_impl<double>(*m, *n, *alpha, a, *incca, *incra, x, *incx, *beta, y, *incy);
 }
 
 // ---- the MATMUL operator entry point (osprey/libfi/matrix/matmul_s4s4.c:66-112) ----------------
 namespace {
 struct DvView {
-    float *ptr;
+    void *ptr;
     int ndim;
     long n1, n2, inc1, inc2;
 };
@@ -822,7 +863,7 @@ struct DvView {
 // (osprey/libfi/matrix/matmul.h:145-176): multi-word elements carry a factor in stride_mult.
 DvView view_of(const o64_dopevec_t *d) {
     DvView v;
-    v.ptr = static_cast<float *>(d->ptr);
+    v.ptr = d->ptr;
     v.ndim = (int)(d->flags1 >> 29);
     const unsigned int_len = (d->type_bits >> 12) & 0xfffu;
     const int shift = int_len == 64 ? 1 : (int_len == 128 ? 2 : (int_len == 256 ? 3 : 0));
@@ -837,22 +878,22 @@ DvView view_of(const o64_dopevec_t *d) {
     }
     return v;
 }
-}  // namespace
 
-extern "C" void _MATMUL_S4S4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B) {
-    if (!RESULT || !MATRIX_A || !MATRIX_B) {
-        g_compat_status = O64_ERR_RANK;
-        return;
-    }
+// One MATMUL entry point of the runtime: parse the dope vectors and allocate an unassociated
+// RESULT as _premult does (matmul.h:135-400), then call the strided kernels the way the entry
+// point of that type does.  `use_gemv`: the real kinds send the rank-1 cases to the
+// matrix-vector kernel (matmul_s4s4.c:86-104, matmul_ss@.c:100-117); the integer kinds send all
+// three cases to the matrix kernel with m, n, k of matmul.h:325-363 (matmul_i4i4.c:84-86).
+template <typename T>
+int matmul_impl(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B, bool use_gemv) {
+    if (!RESULT || !MATRIX_A || !MATRIX_B) return O64_ERR_RANK;
     const DvView a = view_of(MATRIX_A), b = view_of(MATRIX_B);
-    if (!((a.ndim == 1 && b.ndim == 2) || (a.ndim == 2 && b.ndim == 1) || (a.ndim == 2 && b.ndim == 2))) {
-        g_compat_status = O64_ERR_RANK;  // FESCIRNK
-        return;
-    }
+    if (!((a.ndim == 1 && b.ndim == 2) || (a.ndim == 2 && b.ndim == 1) || (a.ndim == 2 && b.ndim == 2)))
+        return O64_ERR_RANK;  // FESCIRNK
     // allocate RESULT if it is not associated (matmul.h:222-266)
     if (!(RESULT->flags0 & 1u)) {
         unsigned int_len = (RESULT->type_bits >> 12) & 0xfffu;
-        if (int_len == 0) int_len = 32;
+        if (int_len == 0) int_len = 8 * sizeof(T);
         long stride0 = int_len / 32;
         if (stride0 == 0) stride0 = 1;
         RESULT->dimension[0].stride_mult = stride0;
@@ -875,10 +916,7 @@ extern "C" void _MATMUL_S4S4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64
         void *mem = nullptr;
         if (nbytes != 0) {
             mem = malloc((size_t)nbytes);
-            if (!mem) {
-                g_compat_status = O64_ERR_NOMEM;  // FENOMEMY
-                return;
-            }
+            if (!mem) return O64_ERR_NOMEM;  // FENOMEMY
         }
         RESULT->flags0 |= 1u;
         RESULT->ptr = mem;
@@ -886,33 +924,46 @@ extern "C" void _MATMUL_S4S4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64
         RESULT->orig_size = (unsigned long)nbits;
     }
     const DvView c = view_of(RESULT);
-    const int one_i = 1;
-    (void)one_i;
-    const float one = 1.0f, zero = 0.0f;
+    const T *A = static_cast<const T *>(a.ptr), *B = static_cast<const T *>(b.ptr);
+    T *C = static_cast<T *>(c.ptr);
+    const T one = T(1), zero = T(0);
     if (a.ndim == 2 && b.ndim == 2) {
-        if (!(a.n2 == b.n1 && c.n1 == a.n1 && c.n2 == b.n2)) {
-            g_compat_status = O64_ERR_CONFORM;  // FESCICNF
-            return;
-        }
-        const int m = (int)a.n1, n = (int)b.n2, k = (int)a.n2;
-        const int i1a = (int)a.inc1, i2a = (int)a.inc2, i1b = (int)b.inc1, i2b = (int)b.inc2;
-        const int i1c = (int)c.inc1, i2c = (int)c.inc2;
-        _s4gemmx__(&m, &n, &k, &one, a.ptr, &i1a, &i2a, b.ptr, &i1b, &i2b, &zero, c.ptr, &i1c, &i2c);
-    } else if (a.ndim == 2) {  // y = A x
-        if (!(a.n2 == b.n1 && a.n1 == c.n1)) {
-            g_compat_status = O64_ERR_CONFORM;
-            return;
-        }
-        const int m = (int)a.n1, n = (int)a.n2;
-        const int i1a = (int)a.inc1, i2a = (int)a.inc2, ix = (int)b.inc1, iy = (int)c.inc1;
-        _s4gemvx__(&m, &n, &one, a.ptr, &i1a, &i2a, b.ptr, &ix, &zero, c.ptr, &iy);
-    } else {  // y = x B, i.e. y' = B' x'
-        if (!(a.n1 == b.n1 && c.n1 == b.n2)) {
-            g_compat_status = O64_ERR_CONFORM;
-            return;
-        }
-        const int m = (int)b.n2, n = (int)b.n1;
-        const int i1 = (int)b.inc2, i2 = (int)b.inc1, ix = (int)a.inc1, iy = (int)c.inc1;
-        _s4gemvx__(&m, &n, &one, b.ptr, &i1, &i2, a.ptr, &ix, &zero, c.ptr, &iy);
+        if (!(a.n2 == b.n1 && c.n1 == a.n1 && c.n2 == b.n2)) return O64_ERR_CONFORM;  // FESCICNF
+        return xgemmx_impl<T>((int)a.n1, (int)b.n2, (int)a.n2, one, A, a.inc1, a.inc2, B, b.inc1, b.inc2, zero,
+                              C, c.inc1, c.inc2, true);
     }
+    if (a.ndim == 2) {  // y = A x
+        if (!(a.n2 == b.n1 && a.n1 == c.n1)) return O64_ERR_CONFORM;
+        if (use_gemv) {
+            if constexpr (std::is_floating_point<T>::value)
+                return xgemvx_impl<T>((int)a.n1, (int)a.n2, one, A, a.inc1, a.inc2, B, b.inc1, zero, C, c.inc1);
+        }
+        return xgemmx_impl<T>((int)a.n1, 1, (int)a.n2, one, A, a.inc1, a.inc2, B, b.inc1, b.inc2, zero, C,
+                              c.inc1, c.inc2, true);
+    }
+    // y = x B, i.e. y' = B' x'
+    if (!(a.n1 == b.n1 && c.n1 == b.n2)) return O64_ERR_CONFORM;
+    if (use_gemv) {
+        if constexpr (std::is_floating_point<T>::value)
+            return xgemvx_impl<T>((int)b.n2, (int)b.n1, one, B, b.inc2, b.inc1, A, a.inc1, zero, C, c.inc1);
+    }
+    return xgemmx_impl<T>(1, (int)b.n2, (int)b.n1, one, A, a.inc1, a.inc2, B, b.inc1, b.inc2, zero, C, c.inc1,
+                          c.inc2, true);
+}
+}  // namespace
+
+extern "C" void _MATMUL_S4S4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B) {
+    g_compat_status = matmul_impl<float>(RESULT, MATRIX_A, MATRIX_B, true);
+}
+
+extern "C" void _MATMUL_SS(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B) {
+    g_compat_status = matmul_impl<double>(RESULT, MATRIX_A, MATRIX_B, true);
+}
+
+extern "C" void _MATMUL_I4I4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B) {
+    g_compat_status = matmul_impl<int32_t>(RESULT, MATRIX_A, MATRIX_B, false);
+}
+
+extern "C" void _MATMUL_JJ(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B) {
+    g_compat_status = matmul_impl<int64_t>(RESULT, MATRIX_A, MATRIX_B, false);
 }

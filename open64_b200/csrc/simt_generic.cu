@@ -1,0 +1,129 @@
+// The rest of the runtime's X-interface family on CUDA cores: C = alpha*A*B + beta*C and
+// y = alpha*A*x + beta*y for REAL*8 and for the 32- and 64-bit integer kinds, with the semantics
+// of the reference's template (osprey/libfi/matrix/xgemmx.h:172-236: element (i,j) of X at
+// X[inc1x*i + inc2x*j], beta == 0 does not read C, a zero B(l,j) skips its term; integers wrap).
+// These kinds have no tensor-core path that keeps their exact arithmetic; the kernel is a plain
+// shared-memory tiled loop nest (the L1 strip and register tile of osprey/be/lno/snl_inv.cxx:639,904).
+#include <cuda_runtime.h>
+
+#include "../../include/o64gemm.h"
+#include "simt_kernels.cuh"
+
+namespace o64 {
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+gemmx_generic_kernel(long long M, long long N, long long K, T alpha, const T *A, long long a1, long long a2,
+                     const T *B, long long b1, long long b2, T beta, T *C, long long c1, long long c2,
+                     int a_k_fast, int b_n_fast) {
+    constexpr int BM = 32, BN = 32, BK = 16, TM = 2, TN = 2;
+    __shared__ T As[BK][BM + 1];
+    __shared__ T Bs[BK][BN + 1];
+    const int tid = threadIdx.x;
+    const int tx = tid % (BN / TN), ty = tid / (BN / TN);
+    const long long m0 = (long long)blockIdx.y * BM, n0 = (long long)blockIdx.x * BN;
+    T acc[TM][TN] = {};
+    for (long long k0 = 0; k0 < K; k0 += BK) {
+        for (int e = tid; e < BM * BK; e += 256) {
+            int i, l;
+            if (a_k_fast) { l = e % BK; i = e / BK; } else { i = e % BM; l = e / BM; }
+            const long long gi = m0 + i, gl = k0 + l;
+            As[l][i] = (gi < M && gl < K) ? A[gi * a1 + gl * a2] : T(0);
+        }
+        for (int e = tid; e < BK * BN; e += 256) {
+            int l, j;
+            if (b_n_fast) { j = e % BN; l = e / BN; } else { l = e % BK; j = e / BK; }
+            const long long gl = k0 + l, gj = n0 + j;
+            Bs[l][j] = (gl < K && gj < N) ? B[gl * b1 + gj * b2] : T(0);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int l = 0; l < BK; ++l) {
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) {
+                    const T b = Bs[l][tx * TN + j];
+                    if (b != T(0)) acc[i][j] += As[l][ty * TM + i] * b;  // zero B(l,j): term left out
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const long long gi = m0 + ty * TM + i;
+        if (gi >= M) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const long long gj = n0 + tx * TN + j;
+            if (gj >= N) continue;
+            T *dst = C + gi * c1 + gj * c2;
+            T v = alpha * acc[i][j];
+            if (beta != T(0)) v += beta * *dst;
+            *dst = v;
+        }
+    }
+}
+
+template <typename T>
+__global__ void gemvx_generic_kernel(long long M, long long N, T alpha, const T *A, long long a1, long long a2,
+                                     const T *X, long long incx, T beta, T *Y, long long incy) {
+    const long long row = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= M) return;
+    T *y = Y + row * incy;
+    T acc = (beta == T(0)) ? T(0) : beta * *y;
+    for (long long j = 0; j < N; ++j) {
+        const T x = X[j * incx];
+        if (x != T(0)) acc += (alpha * x) * A[row * a1 + j * a2];
+    }
+    *y = acc;
+}
+
+template <typename T>
+__global__ void scale_generic_kernel(long long M, long long N, T beta, T *C, long long c1, long long c2) {
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= M * N) return;
+    T *c = C + (e % M) * c1 + (e / M) * c2;
+    *c = (beta == T(0)) ? T(0) : beta * *c;
+}
+
+template <typename T>
+int generic_gemmx(int64_t M, int64_t N, int64_t K, T alpha, const T *A, int64_t a1, int64_t a2, const T *B,
+                  int64_t b1, int64_t b2, T beta, T *C, int64_t c1, int64_t c2, cudaStream_t s) {
+    if (M <= 0 || N <= 0) return O64_OK;
+    if ((M + 31) / 32 > 65535) return O64_ERR_RANK;
+    auto mag = [](int64_t v) { return v < 0 ? -v : v; };
+    dim3 grid((unsigned)((N + 31) / 32), (unsigned)((M + 31) / 32));
+    gemmx_generic_kernel<T><<<grid, 256, 0, s>>>(M, N, K, alpha, A, a1, a2, B, b1, b2, beta, C, c1, c2,
+                                                 mag(a2) <= mag(a1), mag(b2) <= mag(b1));
+    return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
+}
+
+template <typename T>
+int generic_gemvx(int64_t M, int64_t N, T alpha, const T *A, int64_t a1, int64_t a2, const T *X, int64_t incx,
+                  T beta, T *Y, int64_t incy, cudaStream_t s) {
+    if (M <= 0) return O64_OK;
+    gemvx_generic_kernel<T><<<(unsigned)((M + 127) / 128), 128, 0, s>>>(M, N, alpha, A, a1, a2, X, incx, beta, Y, incy);
+    return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
+}
+
+template <typename T>
+int generic_scale(int64_t M, int64_t N, T beta, T *C, int64_t c1, int64_t c2, cudaStream_t s) {
+    if (M <= 0 || N <= 0) return O64_OK;
+    const long long total = (long long)M * N;
+    scale_generic_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(M, N, beta, C, c1, c2);
+    return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
+}
+
+#define O64_INSTANTIATE(T)                                                                                   \
+    template int generic_gemmx<T>(int64_t, int64_t, int64_t, T, const T *, int64_t, int64_t, const T *, int64_t, \
+                                  int64_t, T, T *, int64_t, int64_t, cudaStream_t);                          \
+    template int generic_gemvx<T>(int64_t, int64_t, T, const T *, int64_t, int64_t, const T *, int64_t, T, T *, \
+                                  int64_t, cudaStream_t);                                                    \
+    template int generic_scale<T>(int64_t, int64_t, T, T *, int64_t, int64_t, cudaStream_t);
+O64_INSTANTIATE(double)
+O64_INSTANTIATE(unsigned)
+O64_INSTANTIATE(unsigned long long)
+#undef O64_INSTANTIATE
+
+}  // namespace o64

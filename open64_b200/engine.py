@@ -267,3 +267,35 @@ class Engine:
                             r(incx), ctypes.byref(cf(beta)), _ptr(y), r(incy))
         check(self.lib.o64_compat_last_status(), "_s4gemvx__")
         return y
+
+    _XKINDS = {"f64": ("_sgemmx__", ctypes.c_double), "i32": ("_i4gemmx__", ctypes.c_int32),
+               "i64": ("_jgemmx__", ctypes.c_int64), "f32": ("_s4gemmx__", ctypes.c_float)}
+
+    def xgemmx(self, kind, m, n, k, alpha, a, inc1a, inc2a, b, inc1b, inc2b, beta, c, inc1c, inc2c):
+        """The strided kernel of element kind "f32" | "f64" | "i32" | "i64" (_s4gemmx__, _sgemmx__,
+        _i4gemmx__, _jgemmx__), in place on c."""
+        name, ct = self._XKINDS[kind]
+        r = lambda v: ctypes.byref(ctypes.c_int(v))
+        getattr(self.lib, name)(r(m), r(n), r(k), ctypes.byref(ct(alpha)), _ptr(a), r(inc1a), r(inc2a),
+                                _ptr(b), r(inc1b), r(inc2b), ctypes.byref(ct(beta)), _ptr(c), r(inc1c),
+                                r(inc2c))
+        check(self.lib.o64_compat_last_status(), name)
+        return c
+
+    def sgemvx(self, m, n, alpha, a, incca, incra, x, incx, beta, y, incy):
+        """_sgemvx__: the REAL*8 matrix-vector kernel."""
+        cd = ctypes.c_double
+        r = lambda v: ctypes.byref(ctypes.c_int(v))
+        self.lib._sgemvx__(r(m), r(n), ctypes.byref(cd(alpha)), _ptr(a), r(incca), r(incra), _ptr(x),
+                           r(incx), ctypes.byref(cd(beta)), _ptr(y), r(incy))
+        check(self.lib.o64_compat_last_status(), "_sgemvx__")
+        return y
+
+    def dgemm(self, transa, transb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc):
+        ci, cd = ctypes.c_int, ctypes.c_double
+        self.lib.dgemm_(transa.encode(), transb.encode(), ctypes.byref(ci(m)), ctypes.byref(ci(n)),
+                        ctypes.byref(ci(k)), ctypes.byref(cd(alpha)), _ptr(a), ctypes.byref(ci(lda)),
+                        _ptr(b), ctypes.byref(ci(ldb)), ctypes.byref(cd(beta)), _ptr(c),
+                        ctypes.byref(ci(ldc)))
+        check(self.lib.o64_compat_last_status(), "dgemm_")
+        return c

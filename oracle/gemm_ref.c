@@ -315,6 +315,77 @@ void o64ref_s4gemvx(int M, int N, float alpha, const float *A, int inc1a, int in
     }
 }
 
+/* ---- the same two kernels for the other element kinds ------------------------------------
+ * sgemmx.f / sgemvx.f are the REAL*4 texts with REAL(KIND=8) declarations; i4gemmx.f and
+ * jgemmx.f instantiate the xgemmx.h template with INTEGER(KIND=4) / INTEGER(KIND=8).  The
+ * integer kinds are computed on the unsigned type of the same width: its wrap-around is the
+ * two's-complement result of the Fortran code, without C's signed-overflow caveat. */
+#define O64REF_GEMMX(NAME, T)                                                                   \
+    void NAME(int M, int N, int K, T alpha, const T *A, int inc1a, int inc2a, const T *B,       \
+              int inc1b, int inc2b, T beta, T *C, int inc1c, int inc2c) {                       \
+        if (M == 0 || N == 0 || (alpha == (T)0 && beta == (T)1)) return;                        \
+        if (K == 0) {                                                                           \
+            for (long j = 0; j < N; ++j)                                                        \
+                for (long i = 0; i < M; ++i) C[(long)inc2c * j + (long)inc1c * i] = (T)0;       \
+            return;                                                                             \
+        }                                                                                       \
+        if (alpha == (T)0) {                                                                    \
+            for (long j = 0; j < N; ++j)                                                        \
+                for (long i = 0; i < M; ++i) {                                                  \
+                    long ic = (long)inc2c * j + (long)inc1c * i;                                \
+                    C[ic] = (beta == (T)0) ? (T)0 : beta * C[ic];                               \
+                }                                                                               \
+            return;                                                                             \
+        }                                                                                       \
+        for (long j = 0; j < N; ++j) {                                                          \
+            if (beta == (T)0) {                                                                 \
+                for (long i = 0; i < M; ++i) C[(long)inc2c * j + (long)inc1c * i] = (T)0;       \
+            } else if (beta != (T)1) {                                                          \
+                for (long i = 0; i < M; ++i) {                                                  \
+                    long ic = (long)inc2c * j + (long)inc1c * i;                                \
+                    C[ic] = beta * C[ic];                                                       \
+                }                                                                               \
+            }                                                                                   \
+            for (long l = 0; l < K; ++l) {                                                      \
+                T b = B[(long)inc2b * j + (long)inc1b * l];                                     \
+                if (b != (T)0) {                                                                \
+                    T temp = alpha * b;                                                         \
+                    for (long i = 0; i < M; ++i) {                                              \
+                        long ic = (long)inc2c * j + (long)inc1c * i;                            \
+                        C[ic] = C[ic] + temp * A[(long)inc2a * l + (long)inc1a * i];            \
+                    }                                                                           \
+                }                                                                               \
+            }                                                                                   \
+        }                                                                                       \
+    }
+O64REF_GEMMX(o64ref_sgemmx_f64, double)
+O64REF_GEMMX(o64ref_i4gemmx, uint32_t)
+O64REF_GEMMX(o64ref_jgemmx, uint64_t)
+#undef O64REF_GEMMX
+
+void o64ref_sgemvx_f64(int M, int N, double alpha, const double *A, int inc1a, int inc2a,
+                       const double *X, int incx, double beta, double *Y, int incy) {
+    if (M != 0 && N == 0) {
+        for (long i = 0; i < M; ++i) Y[(long)incy * i] = 0.0;
+        return;
+    }
+    if (M == 0 || N == 0 || (alpha == 0.0 && beta == 1.0)) return;
+    if (beta == 0.0) {
+        for (long i = 0; i < M; ++i) Y[(long)incy * i] = 0.0;
+    } else if (beta != 1.0) {
+        for (long i = 0; i < M; ++i) Y[(long)incy * i] = beta * Y[(long)incy * i];
+    }
+    if (alpha == 0.0) return;
+    for (long j = 0; j < N; ++j) {
+        double x = X[(long)incx * j];
+        if (x != 0.0) {
+            double temp = alpha * x;
+            for (long i = 0; i < M; ++i)
+                Y[(long)incy * i] = Y[(long)incy * i] + temp * A[(long)inc1a * i + (long)inc2a * j];
+        }
+    }
+}
+
 /* Launchers such as torchrun export OMP_NUM_THREADS=1; the CPU baseline asks for the cores back. */
 void o64ref_set_num_threads(int n) {
 #ifdef _OPENMP

@@ -17,7 +17,7 @@ ACT_NONE, ACT_RELU, ACT_GELU_TANH, ACT_GELU_ERF, ACT_SILU = range(5)
 __all__ = [
     "ACT_NONE", "ACT_RELU", "ACT_GELU_TANH", "ACT_GELU_ERF", "ACT_SILU", "build", "lib",
     "linear_f32", "linear_f32_acc64", "gemm_bf16", "swiglu_bf16", "gemm_fp8_scaled",
-    "gemm_s8s8_s32", "s4gemmx", "s4gemvx", "internal_mm_f32", "bf16_to_f32", "f32_to_bf16",
+    "gemm_s8s8_s32", "s4gemmx", "s4gemvx", "xgemmx", "sgemvx_f64", "internal_mm_f32", "bf16_to_f32", "f32_to_bf16",
     "e4m3_to_f32", "f32_to_e4m3", "num_threads", "set_num_threads",
 ]
 
@@ -142,6 +142,33 @@ def s4gemvx(M, N, alpha, A, inc1a, inc2a, X, incx, beta, Y, incy):
     assert A.dtype == X.dtype == Y.dtype == np.float32 and Y.flags.c_contiguous
     lib().o64ref_s4gemvx(I(M), I(N), F(alpha), _p(np.ascontiguousarray(A)), I(inc1a), I(inc2a),
                          _p(np.ascontiguousarray(X)), I(incx), F(beta), _p(Y), I(incy))
+    return Y
+
+
+_XGEMMX = {np.dtype(np.float32): ("o64ref_s4gemmx", ctypes.c_float),
+           np.dtype(np.float64): ("o64ref_sgemmx_f64", ctypes.c_double),
+           np.dtype(np.int32): ("o64ref_i4gemmx", ctypes.c_uint32),
+           np.dtype(np.int64): ("o64ref_jgemmx", ctypes.c_uint64)}
+
+
+def xgemmx(M, N, K, alpha, A, inc1a, inc2a, B, inc1b, inc2b, beta, C, inc1c, inc2c):
+    """The strided kernel for the element kind of C's dtype (float32, float64, int32, int64),
+    in place on the flat array C; integers wrap."""
+    name, ct = _XGEMMX[C.dtype]
+    assert A.dtype == B.dtype == C.dtype and C.flags.c_contiguous
+    mask = {ctypes.c_uint32: 0xFFFFFFFF, ctypes.c_uint64: 0xFFFFFFFFFFFFFFFF}.get(ct)
+    conv = (lambda v: ct(int(v) & mask)) if mask else (lambda v: ct(v))
+    getattr(lib(), name)(I(M), I(N), I(K), conv(alpha), _p(np.ascontiguousarray(A)), I(inc1a), I(inc2a),
+                         _p(np.ascontiguousarray(B)), I(inc1b), I(inc2b), conv(beta), _p(C), I(inc1c),
+                         I(inc2c))
+    return C
+
+
+def sgemvx_f64(M, N, alpha, A, inc1a, inc2a, X, incx, beta, Y, incy):
+    assert A.dtype == X.dtype == Y.dtype == np.float64 and Y.flags.c_contiguous
+    D = ctypes.c_double
+    lib().o64ref_sgemvx_f64(I(M), I(N), D(alpha), _p(np.ascontiguousarray(A)), I(inc1a), I(inc2a),
+                            _p(np.ascontiguousarray(X)), I(incx), D(beta), _p(Y), I(incy))
     return Y
 
 

@@ -133,3 +133,38 @@ def test_reassociation_spread_is_far_inside_tolerance():
     y = oracle.linear_f32(A.numpy(), B.numpy(), bias.numpy(), oracle.ACT_RELU)
     y64 = oracle.linear_f32_acc64(A.numpy(), B.numpy(), bias.numpy(), oracle.ACT_RELU)
     assert relmax(y, y64) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [np.float64, np.int32, np.int64])
+def test_xgemmx_other_kinds_against_numpy(dtype):
+    """REAL*8 and the integer kinds of the strided kernel: numpy on the same strided views;
+    integers with magnitudes that overflow, so the wrap-around is exercised."""
+    rng = np.random.default_rng(11)
+    m, n, k = 13, 9, 21
+    if dtype is np.float64:
+        a, b, c0 = (rng.standard_normal(s) for s in (m * k * 2, k * n, m * n))
+        alpha, beta = 1.5, -0.5
+    else:
+        big = np.iinfo(dtype).max // 3
+        a, b, c0 = (rng.integers(-big, big, s, dtype=dtype) for s in (m * k * 2, k * n, m * n))
+        alpha, beta = 3, -7
+    b[::5] = 0
+    # A(i,l) at a[2*i + 2*m*l] (a section with stride 2), B transposed storage, C column-major
+    c = oracle.xgemmx(m, n, k, alpha, a, 2, 2 * m, b, n, 1, beta, c0.copy(), 1, m)
+    A = a[: 2 * m * k : 2].reshape(k, m).T
+    B = b.reshape(k, n)
+    with np.errstate(over="ignore"):
+        want = (dtype(alpha) * (A @ B) + dtype(beta) * c0.reshape(n, m).T).astype(dtype)
+    got = c.reshape(n, m).T
+    if dtype is np.float64:
+        assert relmax(got, want) < 1e-14
+    else:
+        assert np.array_equal(got, want)
+
+
+def test_sgemvx_f64_against_numpy():
+    rng = np.random.default_rng(12)
+    m, n = 17, 23
+    a, x, y0 = rng.standard_normal(m * n), rng.standard_normal(n), rng.standard_normal(m)
+    y = oracle.sgemvx_f64(m, n, 0.5, a, 1, m, x, 1, 2.0, y0.copy(), 1)
+    assert relmax(y, 0.5 * (a.reshape(n, m).T @ x) + 2.0 * y0) < 1e-14

@@ -13,10 +13,10 @@
  *                     call site matmul_s4s4.c:107-109)
  *       _s4gemvx__    its matrix-vector sibling (osprey/libfi/matrix/s4gemvx.f,
  *                     call sites matmul_s4s4.c:91-101)
- *       the same three for the other element kinds the runtime multiplies without
- *       conversion: REAL*8 (dgemm_, _sgemmx__, _sgemvx__, _MATMUL_SS), INTEGER*4
- *       (_i4gemmx__, _MATMUL_I4I4) and INTEGER*8 (_jgemmx__, _MATMUL_JJ); in the runtime's
- *       naming "S" is the 64-bit real and "S4" the 32-bit one
+ *       the same three for
+ *       REAL*8 (dgemm_, _sgemmx__, _sgemvx__, _MATMUL_SS) and every pair of integer kinds
+ *       (_MATMUL_I1I1 ... _MATMUL_JJ over _i1gemmx__ ... _jgemmx__); in the runtime's naming
+ *       "S" is the 64-bit real, "S4" the 32-bit one, "J" the 64-bit integer
  *     Fortran ABI: every scalar by reference, synchronous, void.  Host or device
  *     pointers are accepted (host operands are staged through device memory).
  *
@@ -258,10 +258,11 @@ typedef struct {
 } o64_dopevec_t;
 void _MATMUL_S4S4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
 
-/* ---- the same family for REAL*8, INTEGER*4 and INTEGER*8 -------------------------------
- * Exact arithmetic of the element kind on CUDA cores (fp64 FMA; integers wrap modulo 2^32 / 2^64
+/* ---- the same family for REAL*8 and the integer kinds ------------------------------------
+ * Exact arithmetic of the element kind on CUDA cores (fp64 FMA; integers wrap in the kind of C
  * as the Fortran kernels do), same quick returns and increments as the REAL*4 entry points.
- * For 64-bit elements the dope vector's stride_mult counts 32-bit words (matmul.h:145-176). */
+ * For 64-bit elements the dope vector's stride_mult counts 32-bit words (matmul.h:145-176); for
+ * 8-, 16- and 32-bit elements it counts elements. */
 /* BLAS hook for REAL*8 MATMUL (osprey/libfi/matrix/MATMUL_SSdispatch.c:43, mmx_dlutil.c:46,133). */
 void dgemm_(const char *transa, const char *transb, const int *m, const int *n, const int *k,
             const double *alpha, const double *a, const int *lda, const double *b, const int *ldb,
@@ -274,21 +275,60 @@ void _sgemmx__(const int *m, const int *n, const int *k, const double *alpha, co
 void _sgemvx__(const int *m, const int *n, const double *alpha, const double *a, const int *incca,
                const int *incra, const double *x, const int *incx, const double *beta, double *y,
                const int *incy);
-/* osprey/libfi/matrix/i4gemmx.f (template xgemmx.h; call site matmul_i4i4.c:84-86). */
+/* The integer instances of the template osprey/libfi/matrix/xgemmx.h: i1gemmx.f, i2gemmx.f,
+ * i4gemmx.f, jgemmx.f (one kind throughout) and i1i2gemmx.f, i1i4gemmx.f, i1jgemmx.f, i2i4gemmx.f,
+ * i2jgemmx.f, i4jgemmx.f (A of the narrower kind; B, C, alpha and beta of the wider one). */
+void _i1gemmx__(const int *m, const int *n, const int *k, const int8_t *alpha, const int8_t *a,
+                const int *inc1a, const int *inc2a, const int8_t *b, const int *inc1b, const int *inc2b,
+                const int8_t *beta, int8_t *c, const int *inc1c, const int *inc2c);
+void _i1i2gemmx__(const int *m, const int *n, const int *k, const int16_t *alpha, const int8_t *a,
+                  const int *inc1a, const int *inc2a, const int16_t *b, const int *inc1b, const int *inc2b,
+                  const int16_t *beta, int16_t *c, const int *inc1c, const int *inc2c);
+void _i1i4gemmx__(const int *m, const int *n, const int *k, const int32_t *alpha, const int8_t *a,
+                  const int *inc1a, const int *inc2a, const int32_t *b, const int *inc1b, const int *inc2b,
+                  const int32_t *beta, int32_t *c, const int *inc1c, const int *inc2c);
+void _i1jgemmx__(const int *m, const int *n, const int *k, const int64_t *alpha, const int8_t *a,
+                 const int *inc1a, const int *inc2a, const int64_t *b, const int *inc1b, const int *inc2b,
+                 const int64_t *beta, int64_t *c, const int *inc1c, const int *inc2c);
+void _i2gemmx__(const int *m, const int *n, const int *k, const int16_t *alpha, const int16_t *a,
+                const int *inc1a, const int *inc2a, const int16_t *b, const int *inc1b, const int *inc2b,
+                const int16_t *beta, int16_t *c, const int *inc1c, const int *inc2c);
+void _i2i4gemmx__(const int *m, const int *n, const int *k, const int32_t *alpha, const int16_t *a,
+                  const int *inc1a, const int *inc2a, const int32_t *b, const int *inc1b, const int *inc2b,
+                  const int32_t *beta, int32_t *c, const int *inc1c, const int *inc2c);
+void _i2jgemmx__(const int *m, const int *n, const int *k, const int64_t *alpha, const int16_t *a,
+                 const int *inc1a, const int *inc2a, const int64_t *b, const int *inc1b, const int *inc2b,
+                 const int64_t *beta, int64_t *c, const int *inc1c, const int *inc2c);
 void _i4gemmx__(const int *m, const int *n, const int *k, const int32_t *alpha, const int32_t *a,
-                const int *inc1a, const int *inc2a, const int32_t *b, const int *inc1b,
-                const int *inc2b, const int32_t *beta, int32_t *c, const int *inc1c,
-                const int *inc2c);
-/* osprey/libfi/matrix/jgemmx.f (call site matmul_jj@.c:92-94). */
+                const int *inc1a, const int *inc2a, const int32_t *b, const int *inc1b, const int *inc2b,
+                const int32_t *beta, int32_t *c, const int *inc1c, const int *inc2c);
+void _i4jgemmx__(const int *m, const int *n, const int *k, const int64_t *alpha, const int32_t *a,
+                 const int *inc1a, const int *inc2a, const int64_t *b, const int *inc1b, const int *inc2b,
+                 const int64_t *beta, int64_t *c, const int *inc1c, const int *inc2c);
 void _jgemmx__(const int *m, const int *n, const int *k, const int64_t *alpha, const int64_t *a,
-               const int *inc1a, const int *inc2a, const int64_t *b, const int *inc1b,
-               const int *inc2b, const int64_t *beta, int64_t *c, const int *inc1c,
-               const int *inc2c);
-/* MATMUL on REAL*8 (matmul_ss@.c:78-125), INTEGER*4 (matmul_i4i4.c:60-88) and INTEGER*8
- * (matmul_jj@.c:71-96) arrays; the integer kinds send rank-1 operands through the matrix kernel
- * with (m,n,k) = (n1a,1,n2a) or (1,n2b,n1b) (matmul.h:343-363). */
+               const int *inc1a, const int *inc2a, const int64_t *b, const int *inc1b, const int *inc2b,
+               const int64_t *beta, int64_t *c, const int *inc1c, const int *inc2c);
+/* MATMUL on REAL*8 arrays (matmul_ss@.c:78-125) and on every pair of integer kinds
+ * (matmul_i1i1.c ... matmul_jj@.c; result kind = the wider operand kind).  The integer entry
+ * points send rank-1 operands through the matrix kernel with (m,n,k) = (n1a,1,n2a) or
+ * (1,n2b,n1b) (matmul.h:343-363, matmul_i4i4.c:84-86); when MATRIX_A is the wider kind they form
+ * C' = B'A' with exchanged increments (matmul_i2i1.c:82-84, matmul_i4i1.c:83-85). */
 void _MATMUL_SS(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I1I1(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I1I2(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I1I4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I1J(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I2I1(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I2I2(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I2I4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I2J(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I4I1(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I4I2(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
 void _MATMUL_I4I4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I4J(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_JI1(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_JI2(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_JI4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
 void _MATMUL_JJ(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
 
 /* Status of the last compat call on this thread (the Fortran entry points return void). */

@@ -24,7 +24,12 @@ EXPORTS = [
     "o64_gemm_fp8_scaled", "o64_gemm_s8s8_s32", "o64_gemm_s8s8_s32_static", "o64_naive_gemm", "o64_comm_unique_id",
     "o64_comm_init", "o64_comm_destroy", "o64_comm_alloc_result", "o64_gemm_s8_sharded_workspace", "o64_gemm_s8_sharded",
     "sgemm_", "_s4gemmx__", "_s4gemvx__", "_MATMUL_S4S4", "o64_compat_last_status",
-    "dgemm_", "_sgemmx__", "_sgemvx__", "_MATMUL_SS", "_i4gemmx__", "_MATMUL_I4I4", "_jgemmx__", "_MATMUL_JJ",
+    "dgemm_", "_sgemmx__", "_sgemvx__", "_MATMUL_SS",
+    "_i1gemmx__", "_i1i2gemmx__", "_i1i4gemmx__", "_i1jgemmx__", "_i2gemmx__", "_i2i4gemmx__", "_i2jgemmx__",
+    "_i4gemmx__", "_i4jgemmx__", "_jgemmx__",
+    "_MATMUL_I1I1", "_MATMUL_I1I2", "_MATMUL_I1I4", "_MATMUL_I1J", "_MATMUL_I2I1", "_MATMUL_I2I2", "_MATMUL_I2I4",
+    "_MATMUL_I2J", "_MATMUL_I4I1", "_MATMUL_I4I2", "_MATMUL_I4I4", "_MATMUL_I4J", "_MATMUL_JI1", "_MATMUL_JI2",
+    "_MATMUL_JI4", "_MATMUL_JJ",
 ]
 
 
@@ -135,12 +140,12 @@ def lib():
     L._s4gemvx__.restype = None
     L.dgemm_.argtypes = [ctypes.c_char_p, ctypes.c_char_p, pi, pi, pi, vp, vp, pi, vp, pi, vp, vp, pi]
     L.dgemm_.restype = None
-    for name in ("_sgemmx__", "_i4gemmx__", "_jgemmx__"):
+    for name in [e for e in EXPORTS if e.endswith("gemmx__") and e != "_s4gemmx__"]:
         getattr(L, name).argtypes = [pi, pi, pi, vp, vp, pi, pi, vp, pi, pi, vp, vp, pi, pi]
         getattr(L, name).restype = None
     L._sgemvx__.argtypes = [pi, pi, vp, vp, pi, pi, vp, pi, vp, vp, pi]
     L._sgemvx__.restype = None
-    for name in ("_MATMUL_S4S4", "_MATMUL_SS", "_MATMUL_I4I4", "_MATMUL_JJ"):
+    for name in [e for e in EXPORTS if e.startswith("_MATMUL_")]:
         getattr(L, name).argtypes = [ctypes.POINTER(DopeVector)] * 3
         getattr(L, name).restype = None
     L.o64_compat_last_status.restype = ci

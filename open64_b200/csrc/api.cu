@@ -698,11 +698,15 @@ static size_t strided_span(int64_t n1, int64_t n2, int64_t s1, int64_t s2) {
 // Element type the CUDA-core kernels compute in: the integer kinds run on the unsigned type of
 // the same width, whose wrap-around is the two's-complement result the Fortran kernels produce.
 template <typename T> struct ComputeType { typedef T type; };
-template <> struct ComputeType<int32_t> { typedef unsigned type; };
-template <> struct ComputeType<int64_t> { typedef unsigned long long type; };
+template <> struct ComputeType<int8_t> { typedef uint8_t type; };
+template <> struct ComputeType<int16_t> { typedef uint16_t type; };
+template <> struct ComputeType<int32_t> { typedef uint32_t type; };
+template <> struct ComputeType<int64_t> { typedef uint64_t type; };
 
-template <typename T>
-static int xgemmx_impl(int M, int N, int K, T alpha, const T *A, int64_t a1, int64_t a2, const T *B,
+// TA: element kind of A; T: element kind of B, C, alpha and beta (the same as TA, or wider for
+// the mixed integer kernels such as _i1i4gemmx__).
+template <typename TA, typename T>
+static int xgemmx_impl(int M, int N, int K, T alpha, const TA *A, int64_t a1, int64_t a2, const T *B,
                        int64_t b1, int64_t b2, T beta, T *C, int64_t c1, int64_t c2, bool skip_zero) {
     typedef typename ComputeType<T>::type U;
     // quick returns, in the order of osprey/libfi/matrix/xgemmx.h:172-208
@@ -720,7 +724,7 @@ static int xgemmx_impl(int M, int N, int K, T alpha, const T *A, int64_t a1, int
     int rc;
     if (!only_scale) {
         if (!A || !B) return O64_ERR_RANK;
-        if ((rc = stage_in(h, 0, A, strided_span(M, K, a1, a2) * sizeof(T), s, &dA))) return rc;
+        if ((rc = stage_in(h, 0, A, strided_span(M, K, a1, a2) * sizeof(TA), s, &dA))) return rc;
         if ((rc = stage_in(h, 1, B, strided_span(K, N, b1, b2) * sizeof(T), s, &dB))) return rc;
     }
     if (!C) return O64_ERR_RANK;
@@ -747,7 +751,7 @@ static int xgemmx_impl(int M, int N, int K, T alpha, const T *A, int64_t a1, int
         if (only_scale)
             rc = generic_scale<U>(M, N, (U)beta_eff, (U *)out.dev, c1, c2, s);
         else
-            rc = generic_gemmx<U>(M, N, K, (U)alpha, (const U *)dA, a1, a2, (const U *)dB, b1, b2, (U)beta,
+            rc = generic_gemmx<TA, U>(M, N, K, (U)alpha, (const TA *)dA, a1, a2, (const U *)dB, b1, b2, (U)beta,
                                   (U *)out.dev, c1, c2, s);
     }
     if (rc) return rc;
@@ -756,17 +760,25 @@ static int xgemmx_impl(int M, int N, int K, T alpha, const T *A, int64_t a1, int
     return O64_OK;
 }
 
-#define O64_XGEMMX_ENTRY(NAME, T)                                                                          \
-    extern "C" void NAME(const int *m, const int *n, const int *k, const T *alpha, const T *a,             \
+#define O64_XGEMMX_ENTRY(NAME, TA, T)                                                                      \
+    extern "C" void NAME(const int *m, const int *n, const int *k, const T *alpha, const TA *a,            \
                          const int *inc1a, const int *inc2a, const T *b, const int *inc1b,                 \
                          const int *inc2b, const T *beta, T *c, const int *inc1c, const int *inc2c) {      \
-        g_compat_status = xgemmx_impl<T>(*m, *n, *k, *alpha, a, *inc1a, *inc2a, b, *inc1b, *inc2b, *beta,  \
-                                         c, *inc1c, *inc2c, true);                                         \
+        g_compat_status = xgemmx_impl<TA, T>(*m, *n, *k, *alpha, a, *inc1a, *inc2a, b, *inc1b, *inc2b,     \
+                                             *beta, c, *inc1c, *inc2c, true);                              \
     }
-O64_XGEMMX_ENTRY(_s4gemmx__, float)
-O64_XGEMMX_ENTRY(_sgemmx__, double)
-O64_XGEMMX_ENTRY(_i4gemmx__, int32_t)
-O64_XGEMMX_ENTRY(_jgemmx__, int64_t)
+O64_XGEMMX_ENTRY(_s4gemmx__, float, float)
+O64_XGEMMX_ENTRY(_sgemmx__, double, double)
+O64_XGEMMX_ENTRY(_i1gemmx__, int8_t, int8_t)
+O64_XGEMMX_ENTRY(_i1i2gemmx__, int8_t, int16_t)
+O64_XGEMMX_ENTRY(_i1i4gemmx__, int8_t, int32_t)
+O64_XGEMMX_ENTRY(_i1jgemmx__, int8_t, int64_t)
+O64_XGEMMX_ENTRY(_i2gemmx__, int16_t, int16_t)
+O64_XGEMMX_ENTRY(_i2i4gemmx__, int16_t, int32_t)
+O64_XGEMMX_ENTRY(_i2jgemmx__, int16_t, int64_t)
+O64_XGEMMX_ENTRY(_i4gemmx__, int32_t, int32_t)
+O64_XGEMMX_ENTRY(_i4jgemmx__, int32_t, int64_t)
+O64_XGEMMX_ENTRY(_jgemmx__, int64_t, int64_t)
 #undef O64_XGEMMX_ENTRY
 
 template <typename T>
@@ -783,7 +795,7 @@ static int blas_gemm_impl(const char *transa, const char *transb, const int *m, 
     // column-major: op(A)(i,l) = A[i + l*lda] or A[l + i*lda]
     const int64_t a1 = na ? 1 : *lda, a2 = na ? *lda : 1;
     const int64_t b1 = nb ? 1 : *ldb, b2 = nb ? *ldb : 1;
-    return xgemmx_impl<T>(*m, *n, *k, *alpha, a, a1, a2, b, b1, b2, *beta, c, 1, *ldc, false);
+    return xgemmx_impl<T, T>(*m, *n, *k, *alpha, a, a1, a2, b, b1, b2, *beta, c, 1, *ldc, false);
 }
 
 extern "C" void sgemm_(const char *transa, const char *transb, const int *m, const int *n, const int *k,
@@ -881,11 +893,16 @@ DvView view_of(const o64_dopevec_t *d) {
 
 // One MATMUL entry point of the runtime: parse the dope vectors and allocate an unassociated
 // RESULT as _premult does (matmul.h:135-400), then call the strided kernels the way the entry
-// point of that type does.  `use_gemv`: the real kinds send the rank-1 cases to the
-// matrix-vector kernel (matmul_s4s4.c:86-104, matmul_ss@.c:100-117); the integer kinds send all
-// three cases to the matrix kernel with m, n, k of matmul.h:325-363 (matmul_i4i4.c:84-86).
-template <typename T>
-int matmul_impl(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B, bool use_gemv) {
+// point of that type does.  TN: the narrower (or equal) operand kind, T: the kind of the other
+// operand and of the result.
+//   use_gemv: the real kinds send the rank-1 cases to the matrix-vector kernel
+//     (matmul_s4s4.c:86-104, matmul_ss@.c:100-117); the integer kinds send all three cases to the
+//     matrix kernel with m, n, k of matmul.h:325-363 (matmul_i4i4.c:84-86).
+//   swapped: MATRIX_A is the wider kind, so the product is formed as C' = B'A' with every pair of
+//     increments exchanged (matmul_i2i1.c:82-84, matmul_i4i1.c:83-85, matmul_ji4.c).
+template <typename TN, typename T>
+int matmul_impl(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B, bool use_gemv,
+                bool swapped) {
     if (!RESULT || !MATRIX_A || !MATRIX_B) return O64_ERR_RANK;
     const DvView a = view_of(MATRIX_A), b = view_of(MATRIX_B);
     if (!((a.ndim == 1 && b.ndim == 2) || (a.ndim == 2 && b.ndim == 1) || (a.ndim == 2 && b.ndim == 2)))
@@ -924,46 +941,57 @@ int matmul_impl(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *M
         RESULT->orig_size = (unsigned long)nbits;
     }
     const DvView c = view_of(RESULT);
-    const T *A = static_cast<const T *>(a.ptr), *B = static_cast<const T *>(b.ptr);
     T *C = static_cast<T *>(c.ptr);
     const T one = T(1), zero = T(0);
+    int m, n, k;
     if (a.ndim == 2 && b.ndim == 2) {
         if (!(a.n2 == b.n1 && c.n1 == a.n1 && c.n2 == b.n2)) return O64_ERR_CONFORM;  // FESCICNF
-        return xgemmx_impl<T>((int)a.n1, (int)b.n2, (int)a.n2, one, A, a.inc1, a.inc2, B, b.inc1, b.inc2, zero,
-                              C, c.inc1, c.inc2, true);
-    }
-    if (a.ndim == 2) {  // y = A x
+        m = (int)a.n1, n = (int)b.n2, k = (int)a.n2;
+    } else if (a.ndim == 2) {  // y = A x
         if (!(a.n2 == b.n1 && a.n1 == c.n1)) return O64_ERR_CONFORM;
-        if (use_gemv) {
-            if constexpr (std::is_floating_point<T>::value)
-                return xgemvx_impl<T>((int)a.n1, (int)a.n2, one, A, a.inc1, a.inc2, B, b.inc1, zero, C, c.inc1);
+        if constexpr (std::is_floating_point<T>::value) {
+            if (use_gemv)
+                return xgemvx_impl<T>((int)a.n1, (int)a.n2, one, static_cast<const T *>(a.ptr), a.inc1, a.inc2,
+                                      static_cast<const T *>(b.ptr), b.inc1, zero, C, c.inc1);
         }
-        return xgemmx_impl<T>((int)a.n1, 1, (int)a.n2, one, A, a.inc1, a.inc2, B, b.inc1, b.inc2, zero, C,
-                              c.inc1, c.inc2, true);
+        m = (int)a.n1, n = 1, k = (int)a.n2;
+    } else {  // y = x B, i.e. y' = B' x'
+        if (!(a.n1 == b.n1 && c.n1 == b.n2)) return O64_ERR_CONFORM;
+        if constexpr (std::is_floating_point<T>::value) {
+            if (use_gemv)
+                return xgemvx_impl<T>((int)b.n2, (int)b.n1, one, static_cast<const T *>(b.ptr), b.inc2, b.inc1,
+                                      static_cast<const T *>(a.ptr), a.inc1, zero, C, c.inc1);
+        }
+        m = 1, n = (int)b.n2, k = (int)b.n1;
     }
-    // y = x B, i.e. y' = B' x'
-    if (!(a.n1 == b.n1 && c.n1 == b.n2)) return O64_ERR_CONFORM;
-    if (use_gemv) {
-        if constexpr (std::is_floating_point<T>::value)
-            return xgemvx_impl<T>((int)b.n2, (int)b.n1, one, B, b.inc2, b.inc1, A, a.inc1, zero, C, c.inc1);
-    }
-    return xgemmx_impl<T>(1, (int)b.n2, (int)b.n1, one, A, a.inc1, a.inc2, B, b.inc1, b.inc2, zero, C, c.inc1,
-                          c.inc2, true);
+    if (swapped)
+        return xgemmx_impl<TN, T>(n, m, k, one, static_cast<const TN *>(b.ptr), b.inc2, b.inc1,
+                                  static_cast<const T *>(a.ptr), a.inc2, a.inc1, zero, C, c.inc2, c.inc1, true);
+    return xgemmx_impl<TN, T>(m, n, k, one, static_cast<const TN *>(a.ptr), a.inc1, a.inc2,
+                              static_cast<const T *>(b.ptr), b.inc1, b.inc2, zero, C, c.inc1, c.inc2, true);
 }
 }  // namespace
 
-extern "C" void _MATMUL_S4S4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B) {
-    g_compat_status = matmul_impl<float>(RESULT, MATRIX_A, MATRIX_B, true);
-}
-
-extern "C" void _MATMUL_SS(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B) {
-    g_compat_status = matmul_impl<double>(RESULT, MATRIX_A, MATRIX_B, true);
-}
-
-extern "C" void _MATMUL_I4I4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B) {
-    g_compat_status = matmul_impl<int32_t>(RESULT, MATRIX_A, MATRIX_B, false);
-}
-
-extern "C" void _MATMUL_JJ(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B) {
-    g_compat_status = matmul_impl<int64_t>(RESULT, MATRIX_A, MATRIX_B, false);
-}
+#define O64_MATMUL_ENTRY(NAME, TN, T, GEMV, SWAPPED)                                                      \
+    extern "C" void NAME(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B) {       \
+        g_compat_status = matmul_impl<TN, T>(RESULT, MATRIX_A, MATRIX_B, GEMV, SWAPPED);                  \
+    }
+O64_MATMUL_ENTRY(_MATMUL_S4S4, float, float, true, false)
+O64_MATMUL_ENTRY(_MATMUL_SS, double, double, true, false)
+O64_MATMUL_ENTRY(_MATMUL_I1I1, int8_t, int8_t, false, false)
+O64_MATMUL_ENTRY(_MATMUL_I1I2, int8_t, int16_t, false, false)
+O64_MATMUL_ENTRY(_MATMUL_I1I4, int8_t, int32_t, false, false)
+O64_MATMUL_ENTRY(_MATMUL_I1J, int8_t, int64_t, false, false)
+O64_MATMUL_ENTRY(_MATMUL_I2I1, int8_t, int16_t, false, true)
+O64_MATMUL_ENTRY(_MATMUL_I2I2, int16_t, int16_t, false, false)
+O64_MATMUL_ENTRY(_MATMUL_I2I4, int16_t, int32_t, false, false)
+O64_MATMUL_ENTRY(_MATMUL_I2J, int16_t, int64_t, false, false)
+O64_MATMUL_ENTRY(_MATMUL_I4I1, int8_t, int32_t, false, true)
+O64_MATMUL_ENTRY(_MATMUL_I4I2, int16_t, int32_t, false, true)
+O64_MATMUL_ENTRY(_MATMUL_I4I4, int32_t, int32_t, false, false)
+O64_MATMUL_ENTRY(_MATMUL_I4J, int32_t, int64_t, false, false)
+O64_MATMUL_ENTRY(_MATMUL_JI1, int8_t, int64_t, false, true)
+O64_MATMUL_ENTRY(_MATMUL_JI2, int16_t, int64_t, false, true)
+O64_MATMUL_ENTRY(_MATMUL_JI4, int32_t, int64_t, false, true)
+O64_MATMUL_ENTRY(_MATMUL_JJ, int64_t, int64_t, false, false)
+#undef O64_MATMUL_ENTRY

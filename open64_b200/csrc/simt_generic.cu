@@ -1,19 +1,33 @@
 // The rest of the runtime's X-interface family on CUDA cores: C = alpha*A*B + beta*C and
-// y = alpha*A*x + beta*y for REAL*8 and for the 32- and 64-bit integer kinds, with the semantics
-// of the reference's template (osprey/libfi/matrix/xgemmx.h:172-236: element (i,j) of X at
-// X[inc1x*i + inc2x*j], beta == 0 does not read C, a zero B(l,j) skips its term; integers wrap).
+// y = alpha*A*x + beta*y for REAL*8 and for the integer kinds (8 to 64 bits, A of the same or a
+// narrower kind than B and C), with the semantics of the reference's template
+// (osprey/libfi/matrix/xgemmx.h:172-236: element (i,j) of X at X[inc1x*i + inc2x*j], beta == 0
+// does not read C, a zero B(l,j) skips its term; integers wrap in the kind of C).
 // These kinds have no tensor-core path that keeps their exact arithmetic; the kernel is a plain
 // shared-memory tiled loop nest (the L1 strip and register tile of osprey/be/lno/snl_inv.cxx:639,904).
 #include <cuda_runtime.h>
+
+#include <cstdint>
 
 #include "../../include/o64gemm.h"
 #include "simt_kernels.cuh"
 
 namespace o64 {
 
-template <typename T>
+// A's element in the kind of C: integers are sign-extended, then carried on the unsigned type.
+template <typename T, typename TA> __device__ __forceinline__ T widen(TA a) { return (T)(long long)a; }
+template <> __device__ __forceinline__ double widen<double, double>(double a) { return a; }
+
+// Product in the kind T.  8- and 16-bit operands are multiplied as unsigned 32-bit values: the
+// usual promotion to (signed) int would overflow for 16-bit factors.
+template <typename T> __device__ __forceinline__ T mul(T a, T b) {
+    if constexpr (sizeof(T) < 4) return (T)((unsigned)a * (unsigned)b);
+    else return a * b;
+}
+
+template <typename TA, typename T>
 __global__ void __launch_bounds__(256)
-gemmx_generic_kernel(long long M, long long N, long long K, T alpha, const T *A, long long a1, long long a2,
+gemmx_generic_kernel(long long M, long long N, long long K, T alpha, const TA *A, long long a1, long long a2,
                      const T *B, long long b1, long long b2, T beta, T *C, long long c1, long long c2,
                      int a_k_fast, int b_n_fast) {
     constexpr int BM = 32, BN = 32, BK = 16, TM = 2, TN = 2;
@@ -28,7 +42,7 @@ gemmx_generic_kernel(long long M, long long N, long long K, T alpha, const T *A,
             int i, l;
             if (a_k_fast) { l = e % BK; i = e / BK; } else { i = e % BM; l = e / BM; }
             const long long gi = m0 + i, gl = k0 + l;
-            As[l][i] = (gi < M && gl < K) ? A[gi * a1 + gl * a2] : T(0);
+            As[l][i] = (gi < M && gl < K) ? widen<T, TA>(A[gi * a1 + gl * a2]) : T(0);
         }
         for (int e = tid; e < BK * BN; e += 256) {
             int l, j;
@@ -44,7 +58,7 @@ gemmx_generic_kernel(long long M, long long N, long long K, T alpha, const T *A,
 #pragma unroll
                 for (int j = 0; j < TN; ++j) {
                     const T b = Bs[l][tx * TN + j];
-                    if (b != T(0)) acc[i][j] += As[l][ty * TM + i] * b;  // zero B(l,j): term left out
+                    if (b != T(0)) acc[i][j] = (T)(acc[i][j] + mul<T>(As[l][ty * TM + i], b));  // zero B(l,j): term left out
                 }
         }
         __syncthreads();
@@ -58,8 +72,8 @@ gemmx_generic_kernel(long long M, long long N, long long K, T alpha, const T *A,
             const long long gj = n0 + tx * TN + j;
             if (gj >= N) continue;
             T *dst = C + gi * c1 + gj * c2;
-            T v = alpha * acc[i][j];
-            if (beta != T(0)) v += beta * *dst;
+            T v = mul<T>(alpha, acc[i][j]);
+            if (beta != T(0)) v = (T)(v + mul<T>(beta, *dst));
             *dst = v;
         }
     }
@@ -84,17 +98,17 @@ __global__ void scale_generic_kernel(long long M, long long N, T beta, T *C, lon
     const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= M * N) return;
     T *c = C + (e % M) * c1 + (e / M) * c2;
-    *c = (beta == T(0)) ? T(0) : beta * *c;
+    *c = (beta == T(0)) ? T(0) : mul<T>(beta, *c);
 }
 
-template <typename T>
-int generic_gemmx(int64_t M, int64_t N, int64_t K, T alpha, const T *A, int64_t a1, int64_t a2, const T *B,
+template <typename TA, typename T>
+int generic_gemmx(int64_t M, int64_t N, int64_t K, T alpha, const TA *A, int64_t a1, int64_t a2, const T *B,
                   int64_t b1, int64_t b2, T beta, T *C, int64_t c1, int64_t c2, cudaStream_t s) {
     if (M <= 0 || N <= 0) return O64_OK;
     if ((M + 31) / 32 > 65535) return O64_ERR_RANK;
     auto mag = [](int64_t v) { return v < 0 ? -v : v; };
     dim3 grid((unsigned)((N + 31) / 32), (unsigned)((M + 31) / 32));
-    gemmx_generic_kernel<T><<<grid, 256, 0, s>>>(M, N, K, alpha, A, a1, a2, B, b1, b2, beta, C, c1, c2,
+    gemmx_generic_kernel<TA, T><<<grid, 256, 0, s>>>(M, N, K, alpha, A, a1, a2, B, b1, b2, beta, C, c1, c2,
                                                  mag(a2) <= mag(a1), mag(b2) <= mag(b1));
     return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
 }
@@ -115,15 +129,29 @@ int generic_scale(int64_t M, int64_t N, T beta, T *C, int64_t c1, int64_t c2, cu
     return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
 }
 
-#define O64_INSTANTIATE(T)                                                                                   \
-    template int generic_gemmx<T>(int64_t, int64_t, int64_t, T, const T *, int64_t, int64_t, const T *, int64_t, \
-                                  int64_t, T, T *, int64_t, int64_t, cudaStream_t);                          \
-    template int generic_gemvx<T>(int64_t, int64_t, T, const T *, int64_t, int64_t, const T *, int64_t, T, T *, \
-                                  int64_t, cudaStream_t);                                                    \
-    template int generic_scale<T>(int64_t, int64_t, T, T *, int64_t, int64_t, cudaStream_t);
-O64_INSTANTIATE(double)
-O64_INSTANTIATE(unsigned)
-O64_INSTANTIATE(unsigned long long)
-#undef O64_INSTANTIATE
+#define O64_INSTANTIATE_GEMMX(TA, T)                                                                          \
+    template int generic_gemmx<TA, T>(int64_t, int64_t, int64_t, T, const TA *, int64_t, int64_t, const T *,     \
+                                      int64_t, int64_t, T, T *, int64_t, int64_t, cudaStream_t);
+#define O64_INSTANTIATE_SCALE(T) template int generic_scale<T>(int64_t, int64_t, T, T *, int64_t, int64_t, cudaStream_t);
+O64_INSTANTIATE_GEMMX(double, double)
+O64_INSTANTIATE_GEMMX(int8_t, uint8_t)
+O64_INSTANTIATE_GEMMX(int8_t, uint16_t)
+O64_INSTANTIATE_GEMMX(int8_t, uint32_t)
+O64_INSTANTIATE_GEMMX(int8_t, uint64_t)
+O64_INSTANTIATE_GEMMX(int16_t, uint16_t)
+O64_INSTANTIATE_GEMMX(int16_t, uint32_t)
+O64_INSTANTIATE_GEMMX(int16_t, uint64_t)
+O64_INSTANTIATE_GEMMX(int32_t, uint32_t)
+O64_INSTANTIATE_GEMMX(int32_t, uint64_t)
+O64_INSTANTIATE_GEMMX(int64_t, uint64_t)
+O64_INSTANTIATE_SCALE(double)
+O64_INSTANTIATE_SCALE(uint8_t)
+O64_INSTANTIATE_SCALE(uint16_t)
+O64_INSTANTIATE_SCALE(uint32_t)
+O64_INSTANTIATE_SCALE(uint64_t)
+template int generic_gemvx<double>(int64_t, int64_t, double, const double *, int64_t, int64_t, const double *, int64_t,
+                                   double, double *, int64_t, cudaStream_t);
+#undef O64_INSTANTIATE_GEMMX
+#undef O64_INSTANTIATE_SCALE
 
 }  // namespace o64

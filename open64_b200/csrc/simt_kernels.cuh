@@ -47,9 +47,11 @@ int finalize_partial_bf16(const float *partial, int64_t M, int64_t N, const floa
                           const float *scale_b, const float *bias, int act, void *C, int64_t ldc,
                           cudaStream_t stream);
 
-// The same strided operations for REAL*8 and the 32- / 64-bit integer kinds (simt_generic.cu).
-template <typename T>
-int generic_gemmx(int64_t M, int64_t N, int64_t K, T alpha, const T *A, int64_t a1, int64_t a2, const T *B,
+// The same strided operations for REAL*8 and the integer kinds (simt_generic.cu).  T is the kind
+// of B and C (integers: the unsigned type of that width); TA the kind of A (integers: signed, of
+// the same or a smaller width, sign-extended to T).
+template <typename TA, typename T>
+int generic_gemmx(int64_t M, int64_t N, int64_t K, T alpha, const TA *A, int64_t a1, int64_t a2, const T *B,
                   int64_t b1, int64_t b2, T beta, T *C, int64_t c1, int64_t c2, cudaStream_t s);
 template <typename T>
 int generic_gemvx(int64_t M, int64_t N, T alpha, const T *A, int64_t a1, int64_t a2, const T *X, int64_t incx,

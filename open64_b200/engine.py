@@ -268,13 +268,16 @@ class Engine:
         check(self.lib.o64_compat_last_status(), "_s4gemvx__")
         return y
 
-    _XKINDS = {"f64": ("_sgemmx__", ctypes.c_double), "i32": ("_i4gemmx__", ctypes.c_int32),
-               "i64": ("_jgemmx__", ctypes.c_int64), "f32": ("_s4gemmx__", ctypes.c_float)}
+    _CTYPES = {"s4": ctypes.c_float, "s": ctypes.c_double, "i1": ctypes.c_int8, "i2": ctypes.c_int16,
+               "i4": ctypes.c_int32, "j": ctypes.c_int64}
 
     def xgemmx(self, kind, m, n, k, alpha, a, inc1a, inc2a, b, inc1b, inc2b, beta, c, inc1c, inc2c):
-        """The strided kernel of element kind "f32" | "f64" | "i32" | "i64" (_s4gemmx__, _sgemmx__,
-        _i4gemmx__, _jgemmx__), in place on c."""
-        name, ct = self._XKINDS[kind]
+        """The strided kernel `_<kind>gemmx__` of the runtime, in place on c.  kind: "s4", "s", "i1",
+        "i2", "i4", "j", or a mixed integer pair "i1i2", "i1i4", "i1j", "i2i4", "i2j", "i4j" (A of the
+        first kind; B, C, alpha, beta of the second)."""
+        name = "_%sgemmx__" % kind
+        ckind = kind if kind in self._CTYPES else (kind[2:] if kind[2:] in self._CTYPES else kind[-1:])
+        ct = self._CTYPES[ckind]
         r = lambda v: ctypes.byref(ctypes.c_int(v))
         getattr(self.lib, name)(r(m), r(n), r(k), ctypes.byref(ct(alpha)), _ptr(a), r(inc1a), r(inc2a),
                                 _ptr(b), r(inc1b), r(inc2b), ctypes.byref(ct(beta)), _ptr(c), r(inc1c),

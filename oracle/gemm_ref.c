@@ -316,12 +316,16 @@ void o64ref_s4gemvx(int M, int N, float alpha, const float *A, int inc1a, int in
 }
 
 /* ---- the same two kernels for the other element kinds ------------------------------------
- * sgemmx.f / sgemvx.f are the REAL*4 texts with REAL(KIND=8) declarations; i4gemmx.f and
- * jgemmx.f instantiate the xgemmx.h template with INTEGER(KIND=4) / INTEGER(KIND=8).  The
- * integer kinds are computed on the unsigned type of the same width: its wrap-around is the
- * two's-complement result of the Fortran code, without C's signed-overflow caveat. */
-#define O64REF_GEMMX(NAME, T)                                                                   \
-    void NAME(int M, int N, int K, T alpha, const T *A, int inc1a, int inc2a, const T *B,       \
+ * sgemmx.f / sgemvx.f are the REAL*4 texts with REAL(KIND=8) declarations.  The integer
+ * kernels instantiate the xgemmx.h template: i1gemmx.f, i2gemmx.f, i4gemmx.f, jgemmx.f with one
+ * kind throughout, and i1i2 / i1i4 / i1j / i2i4 / i2j / i4j gemmx.f with A of the narrower kind
+ * and B, C, alpha, beta, temp of the wider one (A's element is converted, i.e. sign-extended,
+ * in `temp*a(i,l)`).  Integers are computed on unsigned types (TS: signed kind of C, T: its
+ * unsigned twin, W: the unsigned type products are formed in, at least 32 bits so that C's
+ * integer promotion cannot overflow): the wrap-around is the two's-complement result of the
+ * Fortran code without C's signed-overflow caveat. */
+#define O64REF_GEMMX(NAME, TA, TS, T, W)                                                        \
+    void NAME(int M, int N, int K, T alpha, const TA *A, int inc1a, int inc2a, const T *B,      \
               int inc1b, int inc2b, T beta, T *C, int inc1c, int inc2c) {                       \
         if (M == 0 || N == 0 || (alpha == (T)0 && beta == (T)1)) return;                        \
         if (K == 0) {                                                                           \
@@ -333,7 +337,7 @@ void o64ref_s4gemvx(int M, int N, float alpha, const float *A, int inc1a, int in
             for (long j = 0; j < N; ++j)                                                        \
                 for (long i = 0; i < M; ++i) {                                                  \
                     long ic = (long)inc2c * j + (long)inc1c * i;                                \
-                    C[ic] = (beta == (T)0) ? (T)0 : beta * C[ic];                               \
+                    C[ic] = (beta == (T)0) ? (T)0 : (T)((W)beta * (W)C[ic]);                    \
                 }                                                                               \
             return;                                                                             \
         }                                                                                       \
@@ -343,24 +347,33 @@ void o64ref_s4gemvx(int M, int N, float alpha, const float *A, int inc1a, int in
             } else if (beta != (T)1) {                                                          \
                 for (long i = 0; i < M; ++i) {                                                  \
                     long ic = (long)inc2c * j + (long)inc1c * i;                                \
-                    C[ic] = beta * C[ic];                                                       \
+                    C[ic] = (T)((W)beta * (W)C[ic]);                                            \
                 }                                                                               \
             }                                                                                   \
             for (long l = 0; l < K; ++l) {                                                      \
                 T b = B[(long)inc2b * j + (long)inc1b * l];                                     \
                 if (b != (T)0) {                                                                \
-                    T temp = alpha * b;                                                         \
+                    T temp = (T)((W)alpha * (W)b);                                              \
                     for (long i = 0; i < M; ++i) {                                              \
                         long ic = (long)inc2c * j + (long)inc1c * i;                            \
-                        C[ic] = C[ic] + temp * A[(long)inc2a * l + (long)inc1a * i];            \
+                        T a = (T)(TS)A[(long)inc2a * l + (long)inc1a * i];                      \
+                        C[ic] = (T)((W)C[ic] + (W)temp * (W)a);                                 \
                     }                                                                           \
                 }                                                                               \
             }                                                                                   \
         }                                                                                       \
     }
-O64REF_GEMMX(o64ref_sgemmx_f64, double)
-O64REF_GEMMX(o64ref_i4gemmx, uint32_t)
-O64REF_GEMMX(o64ref_jgemmx, uint64_t)
+O64REF_GEMMX(o64ref_sgemmx_f64, double, double, double, double)
+O64REF_GEMMX(o64ref_i1gemmx, int8_t, int8_t, uint8_t, uint32_t)
+O64REF_GEMMX(o64ref_i1i2gemmx, int8_t, int16_t, uint16_t, uint32_t)
+O64REF_GEMMX(o64ref_i1i4gemmx, int8_t, int32_t, uint32_t, uint32_t)
+O64REF_GEMMX(o64ref_i1jgemmx, int8_t, int64_t, uint64_t, uint64_t)
+O64REF_GEMMX(o64ref_i2gemmx, int16_t, int16_t, uint16_t, uint32_t)
+O64REF_GEMMX(o64ref_i2i4gemmx, int16_t, int32_t, uint32_t, uint32_t)
+O64REF_GEMMX(o64ref_i2jgemmx, int16_t, int64_t, uint64_t, uint64_t)
+O64REF_GEMMX(o64ref_i4gemmx, int32_t, int32_t, uint32_t, uint32_t)
+O64REF_GEMMX(o64ref_i4jgemmx, int32_t, int64_t, uint64_t, uint64_t)
+O64REF_GEMMX(o64ref_jgemmx, int64_t, int64_t, uint64_t, uint64_t)
 #undef O64REF_GEMMX
 
 void o64ref_sgemvx_f64(int M, int N, double alpha, const double *A, int inc1a, int inc2a,

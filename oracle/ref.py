@@ -145,19 +145,26 @@ def s4gemvx(M, N, alpha, A, inc1a, inc2a, X, incx, beta, Y, incy):
     return Y
 
 
-_XGEMMX = {np.dtype(np.float32): ("o64ref_s4gemmx", ctypes.c_float),
-           np.dtype(np.float64): ("o64ref_sgemmx_f64", ctypes.c_double),
-           np.dtype(np.int32): ("o64ref_i4gemmx", ctypes.c_uint32),
-           np.dtype(np.int64): ("o64ref_jgemmx", ctypes.c_uint64)}
+_KIND = {np.dtype(np.int8): "i1", np.dtype(np.int16): "i2", np.dtype(np.int32): "i4", np.dtype(np.int64): "j"}
+_UCT = {1: ctypes.c_uint8, 2: ctypes.c_uint16, 4: ctypes.c_uint32, 8: ctypes.c_uint64}
 
 
 def xgemmx(M, N, K, alpha, A, inc1a, inc2a, B, inc1b, inc2b, beta, C, inc1c, inc2c):
-    """The strided kernel for the element kind of C's dtype (float32, float64, int32, int64),
-    in place on the flat array C; integers wrap."""
-    name, ct = _XGEMMX[C.dtype]
-    assert A.dtype == B.dtype == C.dtype and C.flags.c_contiguous
-    mask = {ctypes.c_uint32: 0xFFFFFFFF, ctypes.c_uint64: 0xFFFFFFFFFFFFFFFF}.get(ct)
-    conv = (lambda v: ct(int(v) & mask)) if mask else (lambda v: ct(v))
+    """The strided kernel for the element kinds of (A, C): float32, float64, or an integer pair
+    with A of the same or a narrower kind than B and C (i1gemmx ... i4jgemmx, jgemmx); in place on
+    the flat array C; integers wrap in the kind of C."""
+    assert B.dtype == C.dtype and C.flags.c_contiguous
+    if C.dtype == np.float32 or C.dtype == np.float64:
+        assert A.dtype == C.dtype
+        name, conv = (("o64ref_s4gemmx", ctypes.c_float) if C.dtype == np.float32
+                      else ("o64ref_sgemmx_f64", ctypes.c_double))
+    else:
+        ka, kc = _KIND[A.dtype], _KIND[C.dtype]
+        assert A.dtype.itemsize <= C.dtype.itemsize
+        name = "o64ref_%s%sgemmx" % (ka, "" if ka == kc else kc)
+        ct = _UCT[C.dtype.itemsize]
+        mask = (1 << (8 * C.dtype.itemsize)) - 1
+        conv = lambda v: ct(int(v) & mask)
     getattr(lib(), name)(I(M), I(N), I(K), conv(alpha), _p(np.ascontiguousarray(A)), I(inc1a), I(inc2a),
                          _p(np.ascontiguousarray(B)), I(inc1b), I(inc2b), conv(beta), _p(C), I(inc1c),
                          I(inc2c))

@@ -1,8 +1,9 @@
-"""GPU: the runtime's MATMUL family for REAL*8, INTEGER*4 and INTEGER*8 — the strided kernels
-(_sgemmx__, _sgemvx__, _i4gemmx__, _jgemmx__: osprey/libfi/matrix/sgemmx.f, sgemvx.f, i4gemmx.f,
-jgemmx.f over the template xgemmx.h), the BLAS hook dgemm_ and the operator entry points
-_MATMUL_SS / _MATMUL_I4I4 / _MATMUL_JJ — against the CPU restatement.  Integer results are
-bit-exact including wrap-around; REAL*8 within 1e-12 of the largest magnitude."""
+"""GPU: the runtime's MATMUL family beyond REAL*4 — REAL*8 and every pair of integer kinds.
+The strided kernels (_sgemmx__, _sgemvx__, _i1gemmx__ ... _jgemmx__: osprey/libfi/matrix/sgemmx.f,
+sgemvx.f and the integer instances of the template xgemmx.h), the BLAS hook dgemm_ and the
+operator entry points _MATMUL_SS, _MATMUL_I1I1 ... _MATMUL_JJ, against the CPU restatement.
+Integer results are bit-exact including wrap-around in the result kind; REAL*8 within 1e-12 of
+the largest magnitude."""
 import ctypes
 
 import numpy as np
@@ -17,80 +18,91 @@ from util import relmax
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 TOL_F64 = 1e-12
-KINDS = {"f64": np.float64, "i32": np.int32, "i64": np.int64}
+DT = {"s": np.float64, "i1": np.int8, "i2": np.int16, "i4": np.int32, "j": np.int64}
+INTS = ["i1", "i2", "i4", "j"]
+# kernel name -> (kind of A, kind of B and C)
+KERNELS = {"s": ("s", "s")}
+for _i, _a in enumerate(INTS):
+    for _c in INTS[_i:]:
+        KERNELS[_a if _a == _c else _a + _c] = (_a, _c)
 
 
-def _operands(kind, rng, sizes, overflow=True):
-    dt = KINDS[kind]
-    if kind == "f64":
-        return [rng.standard_normal(s) for s in sizes]
-    hi = np.iinfo(dt).max // 3 if overflow else 1000
-    return [rng.integers(-hi, hi, s, dtype=dt) for s in sizes]
+def _rand(kind, rng, size, overflow=True):
+    dt = DT[kind]
+    if kind == "s":
+        return rng.standard_normal(size)
+    info = np.iinfo(dt)
+    if not overflow:
+        return rng.integers(-11, 11, size, dtype=dt)
+    return rng.integers(info.min // 3, info.max // 3, size, dtype=dt)
 
 
 def _same(kind, got, want):
-    if kind == "f64":
+    if kind == "s":
         return relmax(got, want) <= TOL_F64
     return np.array_equal(got, want)
 
 
-@pytest.mark.parametrize("kind", ["f64", "i32", "i64"])
+@pytest.mark.parametrize("kernel", list(KERNELS))
 @pytest.mark.parametrize("shape", [(1, 1, 1), (19, 13, 17), (64, 64, 64), (130, 70, 33), (257, 129, 200)])
-def test_xgemmx_kinds_match_oracle(eng, kind, shape):
+def test_xgemmx_kinds_match_oracle(eng, kernel, shape):
+    ka, kc = KERNELS[kernel]
     m, n, k = shape
     rng = np.random.default_rng(m * 7 + n * 3 + k)
-    a, b, c0 = _operands(kind, rng, (m * k, k * n, m * n))
+    a, b, c0 = _rand(ka, rng, m * k), _rand(kc, rng, k * n), _rand(kc, rng, m * n)
     b[::7] = 0
-    scal = ((1, 0), (3, 1), (-2, 5)) if kind != "f64" else ((1.0, 0.0), (0.5, 1.0), (-2.0, 0.25))
+    scal = ((1, 0), (3, 1), (-2, 5)) if kc != "s" else ((1.0, 0.0), (0.5, 1.0), (-2.0, 0.25))
     for alpha, beta in scal:
         cref = oracle.xgemmx(m, n, k, alpha, a, 1, m, b, 1, k, beta, c0.copy(), 1, m)
         for where in ("host", "device"):
             ta, tb, tc = (torch.from_numpy(v.copy()) for v in (a, b, c0))
             if where == "device":
                 ta, tb, tc = ta.to(DEV), tb.to(DEV), tc.to(DEV)
-            eng.xgemmx(kind, m, n, k, alpha, ta, 1, m, tb, 1, k, beta, tc, 1, m)
-            assert _same(kind, tc.cpu().numpy(), cref), (where, alpha, beta)
+            eng.xgemmx(kernel, m, n, k, alpha, ta, 1, m, tb, 1, k, beta, tc, 1, m)
+            assert _same(kc, tc.cpu().numpy(), cref), (where, alpha, beta)
 
 
-@pytest.mark.parametrize("kind", ["f64", "i32", "i64"])
-def test_xgemmx_kinds_strided_sections(eng, kind):
+@pytest.mark.parametrize("kernel", ["s", "i1", "i1i4", "i2j", "i4", "j"])
+def test_xgemmx_kinds_strided_sections(eng, kernel):
     """A(1:2m:2, :) through inc1a = 2, B stored transposed, C row-major."""
+    ka, kc = KERNELS[kernel]
     rng = np.random.default_rng(5)
     m, n, k = 45, 37, 29
-    a, b, c0 = _operands(kind, rng, (2 * m * k, k * n, m * n))
-    one = 1 if kind != "f64" else 1.0
-    zero = 0 if kind != "f64" else 0.0
+    a, b, c0 = _rand(ka, rng, 2 * m * k), _rand(kc, rng, k * n), _rand(kc, rng, m * n)
+    one, zero = (1, 0) if kc != "s" else (1.0, 0.0)
     cref = oracle.xgemmx(m, n, k, one, a, 2, 2 * m, b, n, 1, zero, c0.copy(), n, 1)
     tc = torch.from_numpy(c0.copy())
-    eng.xgemmx(kind, m, n, k, one, torch.from_numpy(a), 2, 2 * m, torch.from_numpy(b), n, 1, zero, tc, n, 1)
-    assert _same(kind, tc.numpy(), cref)
+    eng.xgemmx(kernel, m, n, k, one, torch.from_numpy(a), 2, 2 * m, torch.from_numpy(b), n, 1, zero, tc, n, 1)
+    assert _same(kc, tc.numpy(), cref)
 
 
-@pytest.mark.parametrize("kind", ["f64", "i32", "i64"])
-def test_xgemmx_kinds_quick_returns(eng, kind):
+@pytest.mark.parametrize("kernel", ["s", "i1", "i2", "i4", "j", "i1i4"])
+def test_xgemmx_kinds_quick_returns(eng, kernel):
+    ka, kc = KERNELS[kernel]
     rng = np.random.default_rng(6)
     m, n, k = 5, 4, 3
-    a, b, c0 = (torch.from_numpy(v) for v in _operands(kind, rng, (m * k, k * n, m * n), overflow=False))
+    a = torch.from_numpy(_rand(ka, rng, m * k, overflow=False))
+    b, c0 = (torch.from_numpy(_rand(kc, rng, s, overflow=False)) for s in (k * n, m * n))
     c = c0.clone()
-    eng.xgemmx(kind, m, n, k, 0, a, 1, m, b, 1, k, 1, c, 1, m)
+    eng.xgemmx(kernel, m, n, k, 0, a, 1, m, b, 1, k, 1, c, 1, m)
     assert torch.equal(c, c0)                                  # alpha = 0, beta = 1: untouched
     c = c0.clone()
-    eng.xgemmx(kind, m, n, 0, 1, a, 1, m, b, 1, k, 3, c, 1, m)
+    eng.xgemmx(kernel, m, n, 0, 1, a, 1, m, b, 1, k, 3, c, 1, m)
     assert not c.any()                                         # K = 0: zeroed
     c = c0.clone()
-    eng.xgemmx(kind, m, n, k, 0, a, 1, m, b, 1, k, 2, c, 1, m)
+    eng.xgemmx(kernel, m, n, k, 0, a, 1, m, b, 1, k, 2, c, 1, m)
     assert torch.equal(c, 2 * c0)                              # alpha = 0: scaled
-    eng.xgemmx(kind, 0, n, k, 1, a, 1, m, b, 1, k, 0, c, 1, m)
+    eng.xgemmx(kernel, 0, n, k, 1, a, 1, m, b, 1, k, 0, c, 1, m)
     assert eng.lib.o64_compat_last_status() == o.OK            # empty extent: nothing to do
     with pytest.raises(o.O64Error) as e:
-        eng.xgemmx(kind, -1, n, k, 1, a, 1, m, b, 1, k, 0, c, 1, m)
+        eng.xgemmx(kernel, -1, n, k, 1, a, 1, m, b, 1, k, 0, c, 1, m)
     assert e.value.status == o.ERR_RANK
-    if kind == "f64":
+    if kernel == "s":
         c = torch.full((m * n,), float("nan"), dtype=torch.float64)
         a2, b2 = a.clone(), b.clone()
         a2[0 + 1 * m] = float("inf")
         b2[1::k] = 0.0
-        eng.xgemmx(kind, m, n, k, 1.0, a2, 1, m, b2, 1, k, 0.0, c, 1, m)
+        eng.xgemmx(kernel, m, n, k, 1.0, a2, 1, m, b2, 1, k, 0.0, c, 1, m)
         assert torch.isfinite(c).all()                         # beta = 0 ignores C; zero B(l,j) skips
 
 
@@ -119,62 +131,81 @@ def test_dgemm_blas_hook(eng, ta, tb):
     C0 = rng.standard_normal((m, n))
     a = np.asfortranarray(A if ta == "n" else A.T)
     b = np.asfortranarray(B if tb == "n" else B.T)
-    c = np.asfortranarray(C0.copy())
-    tc = torch.from_numpy(c.ravel(order="F").copy())
+    tc = torch.from_numpy(np.asfortranarray(C0).ravel(order="F").copy())
     eng.dgemm(ta, tb, m, n, k, 1.25, torch.from_numpy(a.ravel(order="F").copy()), a.shape[0],
               torch.from_numpy(b.ravel(order="F").copy()), b.shape[0], -0.5, tc, m)
     want = 1.25 * (A @ B) - 0.5 * C0
     assert relmax(tc.numpy().reshape(n, m).T, want) <= TOL_F64
 
 
-ENTRY = {"f64": ("_MATMUL_SS", 64, DopeVector.TYPE_REAL), "i32": ("_MATMUL_I4I4", 32, DopeVector.TYPE_INTEGER),
-         "i64": ("_MATMUL_JJ", 64, DopeVector.TYPE_INTEGER)}
+def _entry(ka, kb):
+    """(_MATMUL_<A><B>, result kind) for operand kinds ka, kb."""
+    up = {"s": "S", "i1": "I1", "i2": "I2", "i4": "I4", "j": "J"}
+    kc = "s" if ka == "s" else INTS[max(INTS.index(ka), INTS.index(kb))]
+    return "_MATMUL_" + up[ka] + up[kb], kc
 
 
 def _dv(kind, arr, extents, strides, assoc=True):
-    _, bits, code = ENTRY[kind]
-    return DopeVector.make(arr.ctypes.data if arr is not None else None, extents, strides, bits, code, assoc)
+    code = DopeVector.TYPE_REAL if kind == "s" else DopeVector.TYPE_INTEGER
+    return DopeVector.make(arr.ctypes.data if arr is not None else None, extents, strides,
+                           8 * np.dtype(DT[kind]).itemsize, code, assoc)
 
 
-@pytest.mark.parametrize("kind", ["f64", "i32", "i64"])
-def test_matmul_entry_points(eng, kind):
-    fn = getattr(eng.lib, ENTRY[kind][0])
-    dt = KINDS[kind]
+def _ref_product(ka, kb, kc, a, b, m, n, k):
+    """The product through the oracle kernel the entry point of (ka, kb) calls: directly, or as
+    C' = B'A' when MATRIX_A is the wider kind."""
+    c = np.zeros(m * n, DT[kc])
+    one, zero = (1, 0) if kc != "s" else (1.0, 0.0)
+    if ka == "s" or INTS.index(ka) <= INTS.index(kb):
+        return oracle.xgemmx(m, n, k, one, a, 1, m, b, 1, k, zero, c, 1, m)
+    return oracle.xgemmx(n, m, k, one, b, k, 1, a, m, 1, zero, c, m, 1)
+
+
+PAIRS = [("s", "s")] + [(x, y) for x in INTS for y in INTS]
+
+
+@pytest.mark.parametrize("ka,kb", PAIRS)
+def test_matmul_entry_points(eng, ka, kb):
+    name, kc = _entry(ka, kb)
+    fn = getattr(eng.lib, name)
     rng = np.random.default_rng(9)
     m, k, n = 37, 29, 41
-    a, b = _operands(kind, rng, (m * k, k * n))
-    one, zero = dt(1), dt(0)
+    a, b = _rand(ka, rng, m * k), _rand(kb, rng, k * n)
     # matrix x matrix, column-major
-    c = np.zeros(m * n, dt)
-    fn(ctypes.byref(_dv(kind, c, (m, n), (1, m))), ctypes.byref(_dv(kind, a, (m, k), (1, m))),
-       ctypes.byref(_dv(kind, b, (k, n), (1, k))))
+    c = np.zeros(m * n, DT[kc])
+    fn(ctypes.byref(_dv(kc, c, (m, n), (1, m))), ctypes.byref(_dv(ka, a, (m, k), (1, m))),
+       ctypes.byref(_dv(kb, b, (k, n), (1, k))))
     assert eng.lib.o64_compat_last_status() == o.OK
-    ref = oracle.xgemmx(m, n, k, one, a, 1, m, b, 1, k, zero, np.zeros(m * n, dt), 1, m)
-    assert _same(kind, c, ref)
+    ref = _ref_product(ka, kb, kc, a, b, m, n, k)
+    assert _same(kc, c, ref)
+    if kc != "s":   # independent check of the wrap-around in the result kind
+        with np.errstate(over="ignore"):
+            want = (a.reshape(k, m).T.astype(DT[kc]) @ b.reshape(n, k).T.astype(DT[kc])).astype(DT[kc])
+        assert np.array_equal(c.reshape(n, m).T, want)
     # matrix x vector and vector x matrix
     x = b[:k].copy()
-    y = np.zeros(m, dt)
-    fn(ctypes.byref(_dv(kind, y, (m,), (1,))), ctypes.byref(_dv(kind, a, (m, k), (1, m))),
-       ctypes.byref(_dv(kind, x, (k,), (1,))))
+    y = np.zeros(m, DT[kc])
+    fn(ctypes.byref(_dv(kc, y, (m,), (1,))), ctypes.byref(_dv(ka, a, (m, k), (1, m))),
+       ctypes.byref(_dv(kb, x, (k,), (1,))))
     assert eng.lib.o64_compat_last_status() == o.OK
-    assert _same(kind, y, oracle.xgemmx(m, 1, k, one, a, 1, m, x, 1, 1, zero, np.zeros(m, dt), 1, 1))
-    xv = a[:m].copy()
-    y2 = np.zeros(k, dt)
-    fn(ctypes.byref(_dv(kind, y2, (k,), (1,))), ctypes.byref(_dv(kind, xv, (m,), (1,))),
-       ctypes.byref(_dv(kind, a, (m, k), (1, m))))
+    assert _same(kc, y, _ref_product(ka, kb, kc, a, x, m, 1, k))
+    xv = a[:k].copy()
+    y2 = np.zeros(n, DT[kc])
+    fn(ctypes.byref(_dv(kc, y2, (n,), (1,))), ctypes.byref(_dv(ka, xv, (k,), (1,))),
+       ctypes.byref(_dv(kb, b, (k, n), (1, k))))
     assert eng.lib.o64_compat_last_status() == o.OK
-    assert _same(kind, y2, oracle.xgemmx(1, k, m, one, xv, 1, 1, a, 1, m, zero, np.zeros(k, dt), 1, 1))
+    assert _same(kc, y2, _ref_product(ka, kb, kc, xv, b, 1, n, k))
     # a RESULT that is not associated is allocated by the runtime and handed to the caller
-    R = _dv(kind, None, (0, 0), (0, 0), assoc=False)
+    R = _dv(kc, None, (0, 0), (0, 0), assoc=False)
     R.flags1 = 2 << 29
-    fn(ctypes.byref(R), ctypes.byref(_dv(kind, a, (m, k), (1, m))), ctypes.byref(_dv(kind, b, (k, n), (1, k))))
+    fn(ctypes.byref(R), ctypes.byref(_dv(ka, a, (m, k), (1, m))), ctypes.byref(_dv(kb, b, (k, n), (1, k))))
     assert eng.lib.o64_compat_last_status() == o.OK and R.ptr and (R.flags0 & 1)
     assert R.dimension[0].extent == m and R.dimension[1].extent == n
-    assert R.orig_size == m * n * ENTRY[kind][1]
-    got = np.ctypeslib.as_array(ctypes.cast(R.ptr, ctypes.POINTER(np.ctypeslib.as_ctypes_type(dt))), (m * n,))
-    assert _same(kind, got.copy(), ref)
+    assert R.orig_size == m * n * 8 * np.dtype(DT[kc]).itemsize
+    got = np.ctypeslib.as_array(ctypes.cast(R.ptr, ctypes.POINTER(np.ctypeslib.as_ctypes_type(DT[kc]))), (m * n,))
+    assert _same(kc, got.copy(), ref)
     ctypes.CDLL(None).free(ctypes.c_void_p(R.ptr))
     # extents that do not conform
-    fn(ctypes.byref(_dv(kind, c, (m, n), (1, m))), ctypes.byref(_dv(kind, a, (m, k), (1, m))),
-       ctypes.byref(_dv(kind, b, (k + 1, n), (1, k + 1))))
+    fn(ctypes.byref(_dv(kc, c, (m, n), (1, m))), ctypes.byref(_dv(ka, a, (m, k), (1, m))),
+       ctypes.byref(_dv(kb, b, (k + 1, n), (1, k + 1))))
     assert eng.lib.o64_compat_last_status() == o.ERR_CONFORM

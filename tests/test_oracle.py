@@ -135,28 +135,34 @@ def test_reassociation_spread_is_far_inside_tolerance():
     assert relmax(y, y64) < 1e-5
 
 
-@pytest.mark.parametrize("dtype", [np.float64, np.int32, np.int64])
-def test_xgemmx_other_kinds_against_numpy(dtype):
-    """REAL*8 and the integer kinds of the strided kernel: numpy on the same strided views;
-    integers with magnitudes that overflow, so the wrap-around is exercised."""
+PAIRS = [(np.float64, np.float64)] + [(a, c) for i, a in enumerate((np.int8, np.int16, np.int32, np.int64))
+                                       for c in (np.int8, np.int16, np.int32, np.int64)[i:]]
+
+
+@pytest.mark.parametrize("ta,tc", PAIRS, ids=lambda t: np.dtype(t).name)
+def test_xgemmx_other_kinds_against_numpy(ta, tc):
+    """REAL*8 and the integer kinds of the strided kernel (A of kind ta; B, C of kind tc): numpy on
+    the same strided views; integers with magnitudes that overflow, so the wrap-around in the kind
+    of C is exercised."""
     rng = np.random.default_rng(11)
     m, n, k = 13, 9, 21
-    if dtype is np.float64:
+    if tc is np.float64:
         a, b, c0 = (rng.standard_normal(s) for s in (m * k * 2, k * n, m * n))
         alpha, beta = 1.5, -0.5
     else:
-        big = np.iinfo(dtype).max // 3
-        a, b, c0 = (rng.integers(-big, big, s, dtype=dtype) for s in (m * k * 2, k * n, m * n))
+        a = rng.integers(np.iinfo(ta).min, np.iinfo(ta).max, m * k * 2, dtype=ta, endpoint=True)
+        big = np.iinfo(tc).max // 3
+        b, c0 = (rng.integers(-big, big, s, dtype=tc) for s in (k * n, m * n))
         alpha, beta = 3, -7
     b[::5] = 0
     # A(i,l) at a[2*i + 2*m*l] (a section with stride 2), B transposed storage, C column-major
     c = oracle.xgemmx(m, n, k, alpha, a, 2, 2 * m, b, n, 1, beta, c0.copy(), 1, m)
-    A = a[: 2 * m * k : 2].reshape(k, m).T
+    A = a[: 2 * m * k : 2].reshape(k, m).T.astype(tc)
     B = b.reshape(k, n)
     with np.errstate(over="ignore"):
-        want = (dtype(alpha) * (A @ B) + dtype(beta) * c0.reshape(n, m).T).astype(dtype)
+        want = (tc(alpha) * (A @ B) + tc(beta) * c0.reshape(n, m).T).astype(tc)
     got = c.reshape(n, m).T
-    if dtype is np.float64:
+    if tc is np.float64:
         assert relmax(got, want) < 1e-14
     else:
         assert np.array_equal(got, want)

@@ -12,7 +12,7 @@ CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libo64gemm.so")
 OBJ_DIR = os.path.join(HERE, "build")
 
-SOURCES = ["api.cu", "umma_gemm.cu", "umma_gemm_2cta.cu", "umma_gemm_wide.cu", "simt_kernels.cu", "simt_generic.cu", "plan.cpp", "no_alloc.cu"]
+SOURCES = ["api.cu", "umma_gemm.cu", "umma_gemm_2cta.cu", "umma_gemm_wide.cu", "umma_gemm_skinny.cu", "simt_kernels.cu", "simt_generic.cu", "plan.cpp", "no_alloc.cu"]
 HEADERS = ["ptx_sm100.cuh", "umma_gemm.cuh", "umma_common.cuh", "simt_kernels.cuh", "../../include/o64gemm.h"]
 
 NVCC_FLAGS = [

@@ -205,12 +205,17 @@ extern "C" int o64_plan_set(o64_handle_t h, int kind, const o64_plan_t *plan) {
         h->has_pin[kind] = false;
         return O64_OK;
     }
-    if (plan->tile_m && plan->tile_m != 128 && plan->tile_m != 256 && plan->tile_m != 512) return O64_ERR_RANK;
+    const bool few_rows = plan->split_k < 0;  // the kernel for M <= 128: tile_m = rows of A per stage
+    if (few_rows && plan->tile_m && plan->tile_m != 16 && plan->tile_m != 32 && plan->tile_m != 64 && plan->tile_m != 128)
+        return O64_ERR_RANK;
+    if (few_rows && (plan->cta_group == 2 || (plan->tile_n && plan->tile_n != 256))) return O64_ERR_RANK;
+    if (!few_rows && plan->tile_m && plan->tile_m != 128 && plan->tile_m != 256 && plan->tile_m != 512) return O64_ERR_RANK;
     if (plan->tile_n && plan->tile_n != 128 && plan->tile_n != 256) return O64_ERR_RANK;
     if (plan->cta_group && plan->cta_group != 1 && plan->cta_group != 2) return O64_ERR_RANK;
-    if (plan->tile_m && plan->cta_group && (plan->cta_group == 1) != (plan->tile_m == 128)) return O64_ERR_RANK;
+    if (!few_rows && plan->tile_m && plan->cta_group && (plan->cta_group == 1) != (plan->tile_m == 128)) return O64_ERR_RANK;
     if (plan->tile_m == 512 && plan->tile_n && plan->tile_n != 256) return O64_ERR_RANK;
-    if (plan->group_m < 0 || plan->num_ctas < 0 || plan->split_k < 0) return O64_ERR_RANK;
+    if (plan->group_m < 0 || plan->num_ctas < 0) return O64_ERR_RANK;
+    if (few_rows && plan->split_k != -1 && plan->split_k != -2 && plan->split_k != -4 && plan->split_k != -8) return O64_ERR_RANK;
     h->pins[kind] = *plan;
     h->has_pin[kind] = true;
     return O64_OK;
@@ -448,7 +453,7 @@ static int umma_entry(o64_handle_t h, int kind, bool b_kn, int epi, int64_t M, i
             c.partial = h->ws;
         }
         c.split_ready = true;
-    } else {
+    } else if (c.plan.split_k > 1) {
         c.plan.split_k = 1;
     }
     if ((rc = umma_launch(c))) return rc;
@@ -638,7 +643,14 @@ extern "C" int o64_gemm_s8_sharded(o64_handle_t h, int64_t M, int64_t N, int64_t
         c.C = C_full + (int64_t)r * ns; c.ldc = N;
         c.bias = nullptr; c.scale_a = nullptr; c.scale_b = nullptr;
         c.act = O64_ACT_NONE;
-        choose(h, O64_KIND_S8, EPI_S32, M, ns, K, &c.plan);
+        {
+            // the fused exchange lives in the tile kernels' epilogue
+            o64_plan_t pin;
+            memset(&pin, 0, sizeof(pin));
+            if (h->has_pin[O64_KIND_S8]) pin = h->pins[O64_KIND_S8];
+            if (pin.split_k <= 0) pin.split_k = 1;
+            plan_choose(O64_KIND_S8, EPI_S32, M, ns, K, h->num_sms, &pin, &c.plan);
+        }
         c.status_word = h->status_word;
         c.stream = s;
         c.n_peers = 0;

@@ -25,6 +25,8 @@
 // it: use the handle-based entry point when you need o64_last_status.
 #include <cuda_runtime.h>
 
+#include <cstring>
+
 #include <mutex>
 
 #include "../../include/o64gemm.h"
@@ -151,7 +153,10 @@ extern "C" int o64_gemm_s8s8_s32_static(int64_t M, int64_t N, int64_t K, const i
     c.C = C; c.ldc = ldc;
     c.bias = nullptr; c.scale_a = nullptr; c.scale_b = nullptr;
     c.act = O64_ACT_NONE;
-    o64::plan_choose(O64_KIND_S8, o64::EPI_S32, M, N, K, d->num_sms, nullptr, &c.plan);
+    o64_plan_t pin;
+    memset(&pin, 0, sizeof(pin));
+    pin.split_k = 1;  // the tile kernels only: this entry point is specified on their scratch use
+    o64::plan_choose(O64_KIND_S8, o64::EPI_S32, M, N, K, d->num_sms, &pin, &c.plan);
     c.status_word = status_word;
     c.stream = s;
     c.may_allocate = false;

@@ -59,7 +59,7 @@ static double predict_ms(int kind, int epi, int64_t M, int64_t N, int64_t K, int
     return (waves * (kblocks * stage_clk + epilogue_clk) + prologue_clk) / (kClockGHz * 1e6);
 }
 
-// O64_LNO="blocking_size=128x256x64:stages=4:cta_group=1:group_m=8:raster=0:num_ctas=148"
+// O64_LNO="blocking_size=128x256x64:stages=4:cta_group=1:group_m=8:raster=0:num_ctas=148:split_k=1"
 static void apply_env(o64_plan_t *pin) {
     const char *env = getenv("O64_LNO");
     if (!env || !*env) return;
@@ -82,6 +82,8 @@ static void apply_env(o64_plan_t *pin) {
             pin->raster = a;
         } else if (sscanf(tok, "num_ctas=%d", &a) == 1) {
             pin->num_ctas = a;
+        } else if (sscanf(tok, "split_k=%d", &a) == 1) {
+            pin->split_k = a;
         }
     }
 }
@@ -167,6 +169,42 @@ void plan_choose(int kind, int epi, int64_t M, int64_t N, int64_t K, int num_sms
         out->split_k = sk;
     }
     out->raster = pin.raster ? 1 : 0;  // the automatic choice is 0 (M fastest)
+
+    // Few rows of A against a large weight: bound by HBM.  The kernel for that case loads only the
+    // rows of A that exist (16 / 32 / 64 / 128 per stage), which leaves room for more stages of
+    // weight in flight, and gives each 128 x 256 tile to a cluster of S CTAs that split K and add
+    // their partial sums through distributed shared memory.  Reported as split_k = -S.  A pinned
+    // split_k of -1 asks for the kernel (S chosen), -2 / -4 / -8 fix S, >= 1 rules the kernel out.
+    const bool skinny_pinned = pin.split_k < 0;
+    const bool skinny_fits = M <= 128 && epi != EPI_SWIGLU && pin.cta_group != 2 &&
+                             (pin.tile_m == 0 || pin.tile_m <= 128) && (pin.tile_n == 0 || pin.tile_n == 256);
+    if (skinny_fits && (skinny_pinned || (pin.split_k == 0 && !pin.cta_group && !pin.tile_m && !pin.tile_n &&
+                                          (double)N * (double)K * eb >= 2.0 * 1024 * 1024))) {
+        const int a_rows = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+        const int64_t tiles = (N + 255) / 256;
+        const int64_t kbs = (K + out->tile_k - 1) / out->tile_k;
+        int s = pin.split_k < -1 ? -pin.split_k : umma_skinny_split(N, K, eb, out->num_ctas);
+        if (s > kbs) s = 1;
+        out->cta_group = 1;
+        out->tile_m = a_rows;
+        out->tile_n = 256;
+        out->mma_m = 128;
+        out->mma_n = 256;
+        out->stages = (6 * (256 + 16) * 128) / ((256 + a_rows) * 128);
+        if (out->stages > 6) out->stages = 6;
+        out->group_m = 1;
+        out->split_k = -s;
+        const int ctas_used = (int)(tiles * s < out->num_ctas ? tiles * s : out->num_ctas);
+        const double bytes = ((double)N * K + (double)M * K) * eb + (double)M * N * (kind == O64_KIND_S8 ? 4 : 2);
+        const double hbm_ms = bytes / 6.5e9;  // measured copy bandwidth, about 6.5 TB/s
+        // tensor pipe: every K block costs one 128 x 256 MMA group whatever M is
+        const double block_k = 128.0 / eb;
+        const double per_cta = double((tiles * kbs + ctas_used - 1) / ctas_used);
+        const double mma_clk = 1.02 * 2.0 * 128.0 * 256.0 * block_k / (kDenseBf16FlopPerClkSm * (eb == 1 ? 2.0 : 1.0));
+        const double mma_ms = per_cta * mma_clk / (kClockGHz * 1e6);
+        out->predicted_ms = (hbm_ms > mma_ms ? hbm_ms : mma_ms) + 0.005;
+        out->num_ctas = ctas_used;
+    }
 
     const char *tr = getenv("O64_TRACE");
     if (tr && strstr(tr, "plan")) {

@@ -118,6 +118,28 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void *tmap,
         : "memory");
 }
 
+// L2 policy for data that is read once: its lines are the first to be replaced, so that a
+// stream of weights does not push everything else out of L2.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+
+// tma_load_2d with an L2 cache policy.
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t smem_dst, const void *tmap, int x, int y,
+                                                 uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%2, %3}], [%4], %5;"
+        ::"r"(smem_dst), "l"(tmap), "r"(x), "r"(y), "r"(bar), "l"(policy)
+        : "memory");
+}
+
+__device__ __forceinline__ void prefetch_l2(const void *addr) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(addr));
+}
+
 // Same load issued by one CTA of a 2-CTA pair: the qualifier allows the completion barrier to
 // live in the partner CTA's shared memory (`bar` is then a shared::cluster address).
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const void *tmap, int x, int y,
@@ -295,6 +317,13 @@ __host__ __device__ constexpr uint64_t make_smem_desc(uint32_t smem_addr, uint32
            (static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16) |
            (static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32) |
            (static_cast<uint64_t>(1) << 46) | (static_cast<uint64_t>(2) << 61);
+}
+
+// Adds four consecutive floats to global memory in one reduction (no return value).
+// addr must be 16-byte aligned.
+__device__ __forceinline__ void red_add_v4_f32(float *addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+                 : "memory");
 }
 
 // Instruction descriptor (32 bit): [4,6) D format (1 = f32, 2 = s32); [7,10) A format;

@@ -33,6 +33,9 @@ struct UmmaParams {
     // (peer-mapped device pointers to the same element as C); 0 peers = plain GEMM
     int n_peers;
     void *peer_c[7];
+    // the kernel for few rows of A (umma_gemm_skinny.cu): rows in the TMA box of A, stages of its
+    // ring, K slices per tile (= CTAs per cluster)
+    int sk_a_rows, sk_stages, sk_split;
 };
 
 constexpr int kBlockM = 128;
@@ -285,6 +288,8 @@ __device__ __forceinline__ void epilogue_partial(const UmmaParams &p, void *dst,
     const int sw = lane & 7;
     const int cols_avail = min(ncols, p.N - n0);
     const int nchunks = cols_avail > 0 ? (cols_avail + 31) >> 5 : 0;
+    // fp32 sums go out four at a time when the rows of dst allow 16-byte accesses
+    const bool v4ok = !INTEGER && ((ldd & 3) == 0) && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0) && ((n0 & 3) == 0);
 #pragma unroll 1
     for (int i = 0; i < nchunks; ++i) {
         uint32_t v[32];
@@ -302,7 +307,10 @@ __device__ __forceinline__ void epilogue_partial(const UmmaParams &p, void *dst,
             const uint4 val = patch[r * 8 + (piece ^ (r & 7))];
             const long long grow = row0 + r;
             const int col = n0 + 32 * i + piece * 4;
-            if (grow < p.M) {
+            if (grow < p.M && v4ok && col + 3 < p.N) {
+                red_add_v4_f32(reinterpret_cast<float *>(dst) + grow * ldd + col, __uint_as_float(val.x),
+                               __uint_as_float(val.y), __uint_as_float(val.z), __uint_as_float(val.w));
+            } else if (grow < p.M) {
                 const uint32_t w[4] = {val.x, val.y, val.z, val.w};
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -320,6 +328,12 @@ __device__ __forceinline__ void epilogue_partial(const UmmaParams &p, void *dst,
 }
 
 // host helpers shared by the launchers (umma_gemm.cu)
+// 2-D row-major tensor [rows, cols] with `ld` elements between rows; box of box_cols x box_rows;
+// 128-byte swizzle; out-of-range elements read as zero.
+int encode_2d(CUtensorMap *tm, int kind, const void *base, int64_t rows, int64_t cols, int64_t ld,
+              int box_cols, int box_rows);
+// The kernel for M <= 128 (umma_gemm_skinny.cu); `p` carries the fields common to all kernels.
+int umma_launch_skinny(const UmmaCall &c, UmmaParams p);
 int umma_launch_pair(const UmmaCall &c, const CUtensorMap &ta, const CUtensorMap &tb,
                      const CUtensorMap &tb2, const UmmaParams &p);
 int umma_launch_wide(const UmmaCall &c, const CUtensorMap &ta, const CUtensorMap &tb,

@@ -310,8 +310,8 @@ static EncodeTiledFn encode_tiled_fn() {
 
 // 2-D row-major tensor [rows, cols] of `elem` bytes with `ld` elements between rows; box of
 // box_cols x box_rows; 128-byte swizzle; out-of-range elements read as zero.
-static int encode_2d(CUtensorMap *tm, int kind, const void *base, int64_t rows, int64_t cols,
-                     int64_t ld, int box_cols, int box_rows) {
+int encode_2d(CUtensorMap *tm, int kind, const void *base, int64_t rows, int64_t cols, int64_t ld,
+              int box_cols, int box_rows) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return O64_ERR_CUDA;
     const int elem = (kind == O64_KIND_BF16) ? 2 : 1;
@@ -368,20 +368,6 @@ int umma_launch(const UmmaCall &c) {
     const bool wide = pair && pl.tile_m == 512;  // each CTA of the pair owns 256 rows
     if (wide && block_n != 256) return O64_ERR_DTYPE;
     const int tile_m = wide ? 512 : (pair ? 2 * kBlockM : kBlockM);
-    CUtensorMap ta, tb, tb2;
-    int rc = encode_2d(&ta, c.kind, c.A, c.M, c.K, c.lda, block_k, wide ? 256 : kBlockM);
-    if (rc) return rc;
-    if (!c.b_kn) {
-        // a CTA of a pair loads half of the B block
-        rc = encode_2d(&tb, c.kind, c.B, c.N, c.K, c.ldb, block_k, pair ? block_n / 2 : block_n);
-        tb2 = tb;
-    } else {
-        rc = encode_2d(&tb, c.kind, c.B, c.K, c.N, c.ldb, 64, block_k);
-        tb2 = tb;
-        if (!rc && c.epi == EPI_SWIGLU) rc = encode_2d(&tb2, c.kind, c.B2, c.K, c.N, c.ldb, 64, block_k);
-    }
-    if (rc) return rc;
-
     UmmaParams p;
     p.M = (int)c.M;
     p.N = (int)c.N;
@@ -412,6 +398,25 @@ int umma_launch(const UmmaCall &c) {
     p.n_peers = c.n_peers;
     for (int i = 0; i < 7; ++i) p.peer_c[i] = c.peer_c[i];
     if (c.n_peers > 0 && !p.vec_ok) return O64_ERR_ALIGN;  // the fused exchange uses the vector-store path only
+    p.sk_a_rows = 0;
+    p.sk_stages = 0;
+    p.sk_split = 1;
+    if (pl.split_k < 0) return umma_launch_skinny(c, p);  // few rows of A: the stream-K kernel
+
+    CUtensorMap ta, tb, tb2;
+    int rc = encode_2d(&ta, c.kind, c.A, c.M, c.K, c.lda, block_k, wide ? 256 : kBlockM);
+    if (rc) return rc;
+    if (!c.b_kn) {
+        // a CTA of a pair loads half of the B block
+        rc = encode_2d(&tb, c.kind, c.B, c.N, c.K, c.ldb, block_k, pair ? block_n / 2 : block_n);
+        tb2 = tb;
+    } else {
+        rc = encode_2d(&tb, c.kind, c.B, c.K, c.N, c.ldb, 64, block_k);
+        tb2 = tb;
+        if (!rc && c.epi == EPI_SWIGLU) rc = encode_2d(&tb2, c.kind, c.B2, c.K, c.N, c.ldb, 64, block_k);
+    }
+    if (rc) return rc;
+
     {
         const char *pr = getenv("O64_PROBE");  // pipeline probes for tuning; results are invalid
         p.probe = pr ? atoi(pr) : 0;

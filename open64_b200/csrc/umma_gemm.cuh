@@ -41,6 +41,9 @@ struct UmmaCall {
 // Validates alignment, encodes the tensor maps and launches.  Returns O64_OK or an error code.
 int umma_launch(const UmmaCall &call);
 
+// K slices per tile (CTAs per cluster) the kernel for few rows of A uses for a shape.
+int umma_skinny_split(int64_t N, int64_t K, int elem, int num_ctas);
+
 // Fills tile_*, stages, group_m, num_ctas, ... for a shape; applies `pin` (fields != 0) and the
 // O64_LNO environment override.  Pure host code.
 void plan_choose(int kind, int epi, int64_t M, int64_t N, int64_t K, int num_sms,

@@ -1,0 +1,502 @@
+// Tensor-core GEMM for few rows of A against a large weight (M <= 128): the weight is read
+// once, so the kernel is bound by HBM and is built to keep enough loads in flight.
+//
+// Differences from the 128 x BLOCK_N tile kernel (umma_gemm.cu):
+//   * the TMA box of A holds only `a_rows` rows (16 / 32 / 64 / 128, the next size >= M), and a
+//     shared-memory stage is that many rows of A plus 256 rows of B.  The MMA still runs with
+//     M = 128: the accumulator rows beyond a_rows are computed from whatever follows the A box in
+//     shared memory and are never read back (row i of the product depends on row i of A only).
+//     A 16-row problem thus keeps 6 stages x 32 KB of weight in flight per SM instead of 4.
+//   * a 128 x 256 output tile belongs to a thread-block CLUSTER of S CTAs (S = 1, 2, 4, 8), each of
+//     which multiplies one slice of K.  The partial sums never touch global memory: after a
+//     cluster barrier (every main loop done, so every ring is free) each CTA stores the columns
+//     c * 256/S .. of its accumulator into CTA c's shared memory (distributed shared memory), a
+//     second cluster barrier follows, and each CTA adds the S slices it received, applies the
+//     epilogue and writes its 256/S columns of C.  Measured: partial sums exchanged through L2
+//     (atomics, a fence, a completion counter) cost three dependent round trips of about 2 us each
+//     at the end of the kernel, while the memory system is still saturated by the other CTAs.
+//
+// In the reference's terms this is the K loop of the nest (osprey/be/vho/f90_lower.cxx:5155)
+// strip-mined once more and its strips run in parallel, the sum being a reduction the compiler
+// may reassociate at -O3 (osprey/common/com/config.cxx:1670-1680); integer sums are exact in
+// any order.
+//
+// Warp roles as in umma_gemm.cu (192 threads): producer, MMA issuer, four epilogue warps.
+// Every mbarrier wait is bounded; on expiry the CTA records a code and leaves its loops, but
+// still takes part in both cluster barriers, so that the other CTAs of its cluster return too.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "umma_common.cuh"
+
+namespace o64 {
+
+namespace {
+
+constexpr int kSkBlockN = 256;
+constexpr int kSkBBytes = kSkBlockN * kRowBytes;      // 32 KB of weight per stage
+constexpr int kSkMaxStages = 6;
+constexpr int kSkRingBytes = 6 * (kSkBBytes + 16 * kRowBytes);  // 6 stages at a_rows = 16
+constexpr int kSkStagingOffset = kSkRingBytes;                   // epilogue patches, 4 KB per warp
+constexpr int kSkBarOffset = kSkStagingOffset + kEpiStagingBytes;
+constexpr int kSkNumBars = 2 * kSkMaxStages + 1;  // full[], empty[], accumulator ready
+constexpr int kSkTmemPtrOffset = kSkBarOffset + 8 * kSkNumBars;
+constexpr int kSkAbortOffset = kSkTmemPtrOffset + 4;
+constexpr int kSkTotal = kSkAbortOffset + 4;
+constexpr int kSkDynamic = kSkTotal + 1024;  // slack to align the ring to 1024 bytes
+static_assert(kSkDynamic <= 227 * 1024, "shared memory");
+
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint4 v) {
+    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
+// Sends this warp's 32 accumulator rows to the CTAs of the cluster: columns c*slice .. of the
+// tile go to CTA c, into slot `rank` of its receive area ([S][M][slice] 4-byte sums at `recv`,
+// the same shared-memory offset in every CTA).  Through the swizzled patch, so that a store
+// instruction writes four full 128-byte row segments.
+__device__ __forceinline__ void scatter_rows(const UmmaParams &p, int row0, uint32_t t_row, uint8_t *staging,
+                                             uint32_t recv, int rank, int slice) {
+    const int lane = threadIdx.x & 31;
+    uint4 *patch = reinterpret_cast<uint4 *>(staging);
+    const int sw = lane & 7;
+#pragma unroll 1
+    for (int i = 0; i < kSkBlockN / 32; ++i) {
+        uint32_t v[32];
+        __syncwarp();
+        tmem_ld_32x32(t_row + 32 * i, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+            patch[lane * 8 + (q ^ sw)] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        __syncwarp();
+        const int owner = (32 * i) / slice;          // uniform: slice is a multiple of 32
+        const int cin = (32 * i) % slice + (lane & 7) * 4;
+        const uint32_t base = map_to_cta(recv, owner);
+#pragma unroll
+        for (int r4 = 0; r4 < 8; ++r4) {
+            const int r = 4 * r4 + (lane >> 3);
+            const uint4 val = patch[r * 8 + ((lane & 7) ^ (r & 7))];
+            const int grow = row0 + r;
+            if (grow < p.M) st_cluster_v4(base + (uint32_t)(((rank * p.M + grow) * slice + cin) * 4), val);
+        }
+        __syncwarp();
+    }
+}
+
+// Adds the S slices received for this CTA's columns, applies the epilogue and writes C.
+// 128 threads; four columns per thread.
+template <int EPI, int ACT>
+__device__ __forceinline__ void gather_store(const UmmaParams &p, const uint8_t *recv, int n0, int rank, int S,
+                                             int slice, int t) {
+    const int tpr = slice / 4;  // threads per row
+    const int c4 = (t % tpr) * 4;
+    const int col = n0 + rank * slice + c4;
+    if (col >= p.N) return;
+    const int ncols = min(4, p.N - col);
+    float bias[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sb[4] = {1.0f, 1.0f, 1.0f, 1.0f};
+    if constexpr (EPI != EPI_S32) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (e < ncols) {
+                if (p.bias) bias[e] = __ldg(p.bias + col + e);
+                if constexpr (EPI == EPI_SCALED_BF16) {
+                    if (p.scale_b) sb[e] = __ldg(p.scale_b + col + e);
+                }
+            }
+        }
+    }
+    for (int m = t / tpr; m < p.M; m += 128 / tpr) {
+        uint4 acc = *reinterpret_cast<const uint4 *>(recv + (size_t)((m * slice) + c4) * 4);
+        for (int src = 1; src < S; ++src) {
+            const uint4 w = *reinterpret_cast<const uint4 *>(recv + (size_t)(((src * p.M + m) * slice) + c4) * 4);
+            if constexpr (EPI == EPI_S32) {
+                acc.x += w.x; acc.y += w.y; acc.z += w.z; acc.w += w.w;  // two's complement: exact
+            } else {
+                acc.x = __float_as_uint(__uint_as_float(acc.x) + __uint_as_float(w.x));
+                acc.y = __float_as_uint(__uint_as_float(acc.y) + __uint_as_float(w.y));
+                acc.z = __float_as_uint(__uint_as_float(acc.z) + __uint_as_float(w.z));
+                acc.w = __float_as_uint(__uint_as_float(acc.w) + __uint_as_float(w.w));
+            }
+        }
+        const uint32_t w[4] = {acc.x, acc.y, acc.z, acc.w};
+        if constexpr (EPI == EPI_S32) {
+            int32_t *dst = reinterpret_cast<int32_t *>(p.C) + (long long)m * p.ldc + col;
+            if (ncols == 4 && p.vec_ok) {
+                *reinterpret_cast<uint4 *>(dst) = acc;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (e < ncols) dst[e] = (int32_t)w[e];
+            }
+        } else {
+            float x[4];
+            float sa = 1.0f;
+            if constexpr (EPI == EPI_SCALED_BF16) {
+                if (p.scale_a) sa = __ldg(p.scale_a + m);
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                x[e] = __uint_as_float(w[e]);
+                if constexpr (EPI == EPI_SCALED_BF16) {
+                    x[e] = x[e] * (sa * sb[e]);
+                    if (p.bias) x[e] += bias[e];
+                } else {
+                    if (p.bias) x[e] += bias[e];
+                    x[e] = act_fixed<ACT>(x[e]);
+                }
+            }
+            __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.C) + (long long)m * p.ldc + col;
+            if (ncols == 4 && p.vec_ok) {
+                *reinterpret_cast<uint2 *>(dst) = make_uint2(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]));
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (e < ncols) dst[e] = __float2bfloat16_rn(x[e]);
+            }
+        }
+    }
+}
+
+template <int EPI>
+__device__ __forceinline__ void gather_store_dispatch(const UmmaParams &p, const uint8_t *recv, int n0, int rank,
+                                                      int S, int slice, int t) {
+    if constexpr (EPI == EPI_BF16) {
+        switch (p.act) {  // uniform: one branch per tile
+        case O64_ACT_RELU: gather_store<EPI, O64_ACT_RELU>(p, recv, n0, rank, S, slice, t); break;
+        case O64_ACT_GELU_TANH: gather_store<EPI, O64_ACT_GELU_TANH>(p, recv, n0, rank, S, slice, t); break;
+        case O64_ACT_GELU_ERF: gather_store<EPI, O64_ACT_GELU_ERF>(p, recv, n0, rank, S, slice, t); break;
+        case O64_ACT_SILU: gather_store<EPI, O64_ACT_SILU>(p, recv, n0, rank, S, slice, t); break;
+        default: gather_store<EPI, O64_ACT_NONE>(p, recv, n0, rank, S, slice, t); break;
+        }
+    } else {
+        gather_store<EPI, O64_ACT_NONE>(p, recv, n0, rank, S, slice, t);
+    }
+}
+
+}  // namespace
+
+// KIND / B_KN / EPI as in umma_gemm_kernel.  Launched with clusters of p.sk_split CTAs;
+// CTA r of cluster t multiplies K blocks [r*kbs/S, (r+1)*kbs/S) of tile t.
+template <int KIND, bool B_KN, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                        const UmmaParams p) {
+    constexpr int kElem = (KIND == MMA_F16) ? 2 : 1;
+    constexpr int kBlockK = kRowBytes / kElem;
+    constexpr int kMmaPerStage = 4;
+    constexpr uint32_t kTmemCols = kSkBlockN;  // one accumulator
+    static_assert(!B_KN || KIND == MMA_F16, "[K,N] operands are supported for bf16 only");
+    static_assert(EPI != EPI_SWIGLU, "no SwiGLU variant");
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + kSkBarOffset;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kSkMaxStages + s); };
+    const uint32_t acc_full_bar = bar_base + 8u * (2 * kSkMaxStages);
+    volatile uint32_t *tmem_ptr_smem = reinterpret_cast<volatile uint32_t *>(smem_gen + kSkTmemPtrOffset);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_gen + kSkAbortOffset);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int stages = p.sk_stages;
+    const uint32_t a_bytes = (uint32_t)p.sk_a_rows * kRowBytes;
+    const uint32_t stage_bytes = kSkBBytes + a_bytes;  // B first: the MMA's reads past the A box stay inside the allocation
+    const int S = p.sk_split;
+    const int rank = (int)cluster_ctarank();
+    const int tile = blockIdx.x / S;
+    const int n0 = tile * kSkBlockN;
+    const int kbs = p.num_k_blocks;
+    const int kb_begin = (int)((long long)kbs * rank / S);
+    const int kb_end = (int)((long long)kbs * (rank + 1) / S);
+
+    unsigned long long *dbg = p.dbg ? p.dbg + 8 * blockIdx.x : nullptr;  // O64_TRACE=pipe: time stamps (ns)
+    if (threadIdx.x == 0) {
+        if (dbg) dbg[0] = globaltimer_ns();
+        for (int s = 0; s < kSkMaxStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(acc_full_bar, 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tm_a);
+        tma_prefetch_desc(&tm_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(smem_gen + kSkTmemPtrOffset), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_smem;
+    if (dbg && threadIdx.x == 0) dbg[1] = globaltimer_ns();
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------------
+        const bool leader = elect_one();
+        const uint64_t stream_once = l2_policy_evict_first();  // the weight: read once, first out of L2
+        int stage = 0;
+        uint32_t phase = 0;
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+            bool ok = mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kWaitProducerEmpty);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            const uint32_t b_dst = smem_base + stage * stage_bytes;
+            const uint32_t a_dst = b_dst + kSkBBytes;
+            if (leader) {
+                mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
+                tma_load_2d(a_dst, &tm_a, kb * kBlockK, 0, full_bar(stage));
+                if constexpr (!B_KN) {
+                    tma_load_2d_hint(b_dst, &tm_b, kb * kBlockK, n0, full_bar(stage), stream_once);
+                } else {
+#pragma unroll
+                    for (int g = 0; g < kSkBlockN / 64; ++g)
+                        tma_load_2d_hint(b_dst + g * 8192, &tm_b, n0 + g * 64, kb * kBlockK, full_bar(stage),
+                                         stream_once);
+                }
+            }
+            __syncwarp();
+            if (++stage == stages) {
+                stage = 0;
+                phase ^= 1u;
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------------
+        const bool leader = elect_one();
+        constexpr uint32_t d_fmt = (KIND == MMA_I8) ? 2u : 1u;
+        constexpr uint32_t ab_fmt = (KIND == MMA_F8F6F4) ? 0u : 1u;
+        constexpr uint32_t idesc = make_idesc(d_fmt, ab_fmt, ab_fmt, B_KN ? 1u : 0u, kBlockM, kSkBlockN);
+        constexpr uint32_t kBAdvance = B_KN ? (16 * kRowBytes) >> 4 : 32 >> 4;
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+            ok = mbar_wait_bounded(full_bar(stage), phase, abort_flag, p.status, kWaitMmaFull);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (dbg && leader && kb == kb_begin) dbg[2] = globaltimer_ns();
+            tc_fence_after();
+            const uint32_t b_addr = smem_base + stage * stage_bytes;
+            const uint32_t a_addr = b_addr + kSkBBytes;
+            const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024);
+            const uint64_t b_desc = B_KN ? make_smem_desc(b_addr, 8192, 1024) : make_smem_desc(b_addr, 16, 1024);
+            if (leader) {
+#pragma unroll
+                for (int k = 0; k < kMmaPerStage; ++k)
+                    tc_mma<KIND>(tmem_base, a_desc + 2u * k, b_desc + kBAdvance * k, idesc,
+                                 ((kb - kb_begin) | k) != 0 ? 1u : 0u);
+                tc_commit(empty_bar(stage));
+            }
+            __syncwarp();
+            if (++stage == stages) {
+                stage = 0;
+                phase ^= 1u;
+            }
+        }
+        if (ok && leader) tc_commit(acc_full_bar);
+        if (dbg && leader) dbg[3] = globaltimer_ns();
+        __syncwarp();
+    } else {
+        // ------------------------------ epilogue warps: wait for the accumulator ---------
+        bool ok = true;
+        if (lane == 0) ok = mbar_wait_bounded(acc_full_bar, 0, abort_flag, p.status, kWaitEpiAccFull);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        tc_fence_after();
+        if (dbg && warp == 2 && lane == 0) dbg[4] = globaltimer_ns();
+        if (S == 1 && ok) {
+            const int quarter = warp & 3;
+            if (quarter * 32 < p.M)
+                epilogue_tile<EPI, kSkBlockN>(p, quarter * 32, n0, tmem_base + (uint32_t(quarter * 32) << 16),
+                                              smem_gen + kSkStagingOffset + quarter * kEpiStagingBytesPerWarp);
+        }
+        tc_fence_before();
+    }
+
+    if (S > 1) {
+        // ------------------------------ sum over the cluster ------------------------------
+        __syncthreads();
+        cluster_sync_all();  // every CTA of the cluster is past its main loop: the rings are free
+        if (dbg && threadIdx.x == 64) dbg[5] = globaltimer_ns();
+        const bool good = (*abort_flag == 0);
+        const int slice = kSkBlockN / S;
+        const int epi_tid = (int)threadIdx.x - 64;  // 0..127 over the four epilogue warps
+        if (warp >= 2 && good) {
+            const int quarter = warp & 3;
+            tc_fence_after();
+            if (quarter * 32 < p.M)
+                scatter_rows(p, quarter * 32, tmem_base + (uint32_t(quarter * 32) << 16),
+                             smem_gen + kSkStagingOffset + quarter * kEpiStagingBytesPerWarp, smem_base, rank, slice);
+            tc_fence_before();
+        }
+        cluster_sync_all();  // the slices sent to this CTA have arrived
+        if (dbg && threadIdx.x == 64) dbg[6] = globaltimer_ns();
+        if (warp >= 2 && good) gather_store_dispatch<EPI>(p, smem_gen, n0, rank, S, slice, epi_tid);
+    }
+    if (dbg && threadIdx.x == 64) dbg[7] = globaltimer_ns();
+
+    // ------------------------------ teardown --------------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (*abort_flag) {
+            const uint64_t t0 = globaltimer_ns();
+            while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+        }
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+template <int KIND, bool B_KN, int EPI>
+static int launch_skinny(const CUtensorMap &ta, const CUtensorMap &tb, UmmaParams p, int tiles, int want_split,
+                         cudaStream_t stream, int *split_out) {
+    auto kern = umma_gemm_skinny_kernel<KIND, B_KN, EPI>;
+    static bool attr_set = false;  // per instantiation
+    static int max_split = 1;      // largest cluster the device can place with this much shared memory
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkDynamic) != cudaSuccess)
+            return O64_ERR_CUDA;
+        for (int s = 8; s > 1; s /= 2) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(s, 1, 1);
+            cfg.blockDim = dim3(kThreads, 1, 1);
+            cfg.dynamicSmemBytes = kSkDynamic;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeClusterDimension;
+            at[0].val.clusterDim.x = s;
+            at[0].val.clusterDim.y = 1;
+            at[0].val.clusterDim.z = 1;
+            cfg.attrs = at;
+            cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n >= 1) {
+                max_split = s;
+                break;
+            }
+            (void)cudaGetLastError();
+        }
+        attr_set = true;
+    }
+    int split = want_split < max_split ? want_split : max_split;
+    if (split < 1) split = 1;
+    p.sk_split = split;
+    *split_out = split;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(tiles * split), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = kSkDynamic;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = split;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, ta, tb, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return O64_ERR_CUDA;
+    }
+    return O64_OK;
+}
+
+// K slices per tile: the largest cluster size (1, 2, 4, 8) that keeps tiles * S within the CTAs
+// the plan allows and leaves every slice at least one K block.
+int umma_skinny_split(int64_t N, int64_t K, int elem, int num_ctas) {
+    const int64_t tiles = (N + kSkBlockN - 1) / kSkBlockN;
+    const int64_t kbs = (K + kRowBytes / elem - 1) / (kRowBytes / elem);
+    int s = 8;
+    while (s > 1 && (tiles * s > num_ctas || s > kbs)) s /= 2;
+    return s;
+}
+
+int umma_launch_skinny(const UmmaCall &c, UmmaParams p) {
+    if (c.M > 128 || c.epi == EPI_SWIGLU || c.n_peers > 0) return O64_ERR_DTYPE;
+    const int elem = (c.kind == O64_KIND_BF16) ? 2 : 1;
+    const int block_k = kRowBytes / elem;
+    const int a_rows = c.M <= 16 ? 16 : (c.M <= 32 ? 32 : (c.M <= 64 ? 64 : 128));
+    CUtensorMap ta, tb;
+    int rc = encode_2d(&ta, c.kind, c.A, c.M, c.K, c.lda, block_k, a_rows);
+    if (rc) return rc;
+    if (!c.b_kn)
+        rc = encode_2d(&tb, c.kind, c.B, c.N, c.K, c.ldb, block_k, kSkBlockN);
+    else
+        rc = encode_2d(&tb, c.kind, c.B, c.K, c.N, c.ldb, 64, block_k);
+    if (rc) return rc;
+    p.num_m_tiles = 1;
+    p.num_n_tiles = (int)((c.N + kSkBlockN - 1) / kSkBlockN);
+    p.split_k = 1;
+    p.kb_per_split = p.num_k_blocks;
+    p.n_peers = 0;
+    p.probe = 0;
+    p.dbg = nullptr;
+    p.sk_a_rows = a_rows;
+    const int stage_bytes = kSkBBytes + a_rows * kRowBytes;
+    p.sk_stages = kSkRingBytes / stage_bytes;
+    if (p.sk_stages > kSkMaxStages) p.sk_stages = kSkMaxStages;
+    const int ctas = c.plan.num_ctas > 0 ? c.plan.num_ctas : 148;
+    // the plan's split_k is -S; -1 also stands for "choose"
+    int want = c.plan.split_k < -1 ? -c.plan.split_k : umma_skinny_split(c.N, c.K, elem, ctas);
+    if (want > p.num_k_blocks) want = 1;
+    const int tiles = p.num_n_tiles;
+
+    // O64_TRACE=pipe: every CTA leaves time stamps; the launch is then synchronous and prints where
+    // the time went (a tuning aid, off by default)
+    static unsigned long long *dbg_buf = nullptr;
+    constexpr int kDbgCtas = 1024;
+    const char *tr = getenv("O64_TRACE");
+    const bool trace = tr && strstr(tr, "pipe") && c.may_allocate && tiles * 8 <= kDbgCtas;
+    if (trace) {
+        if (!dbg_buf && cudaMalloc(&dbg_buf, 8 * kDbgCtas * sizeof(unsigned long long)) != cudaSuccess) dbg_buf = nullptr;
+        if (dbg_buf) cudaMemsetAsync(dbg_buf, 0, 8 * kDbgCtas * sizeof(unsigned long long), c.stream);
+        p.dbg = dbg_buf;
+    }
+    int split = 1;
+    auto report = [&](int rc_launch) {
+        if (!trace || !dbg_buf || rc_launch) return rc_launch;
+        static unsigned long long host[8 * kDbgCtas];
+        const int grid = tiles * split;
+        cudaStreamSynchronize(c.stream);
+        cudaMemcpy(host, dbg_buf, sizeof(host), cudaMemcpyDeviceToHost);
+        unsigned long long t0 = ~0ull;
+        for (int i = 0; i < grid; ++i)
+            if (host[8 * i] && host[8 * i] < t0) t0 = host[8 * i];
+        double sum[8] = {0}, mx[8] = {0};
+        for (int i = 0; i < grid; ++i)
+            for (int j = 0; j < 8; ++j) {
+                const double v = host[8 * i + j] ? (double)(host[8 * i + j] - t0) * 1e-3 : 0.0;
+                sum[j] += v;
+                if (v > mx[j]) mx[j] = v;
+            }
+        fprintf(stderr,
+                "[o64 few-rows timeline, us after the first CTA started, mean/max over %d CTAs (clusters of %d): start "
+                "%.1f/%.1f, set up %.1f/%.1f, first data %.1f/%.1f, last MMA issued %.1f/%.1f, accumulator ready "
+                "%.1f/%.1f, cluster past its main loops %.1f/%.1f, slices exchanged %.1f/%.1f, done %.1f/%.1f]\n",
+                grid, split, sum[0] / grid, mx[0], sum[1] / grid, mx[1], sum[2] / grid, mx[2], sum[3] / grid, mx[3],
+                sum[4] / grid, mx[4], sum[5] / grid, mx[5], sum[6] / grid, mx[6], sum[7] / grid, mx[7]);
+        return rc_launch;
+    };
+#define O64_SK(KIND, BKN, EPI_) return report(launch_skinny<KIND, BKN, EPI_>(ta, tb, p, tiles, want, c.stream, &split))
+    if (c.kind == O64_KIND_BF16 && c.epi == EPI_BF16) {
+        if (c.b_kn) O64_SK(MMA_F16, true, EPI_BF16);
+        O64_SK(MMA_F16, false, EPI_BF16);
+    } else if (c.kind == O64_KIND_FP8 && c.epi == EPI_SCALED_BF16 && !c.b_kn) {
+        O64_SK(MMA_F8F6F4, false, EPI_SCALED_BF16);
+    } else if (c.kind == O64_KIND_S8 && c.epi == EPI_S32 && !c.b_kn) {
+        O64_SK(MMA_I8, false, EPI_S32);
+    }
+#undef O64_SK
+    return O64_ERR_DTYPE;
+}
+
+}  // namespace o64

@@ -93,7 +93,8 @@ enum {
  * cta_group = 1 or 2 CTAs cooperating on one accumulator tile. */
 typedef struct {
     int kind;      /* O64_KIND_* */
-    int tile_m;    /* rows of C per CTA tile (per CTA pair when cta_group == 2) */
+    int tile_m;    /* rows of C per CTA tile (per CTA pair when cta_group == 2); with split_k < 0:
+                      rows of A loaded per stage (16, 32, 64 or 128, the next size >= M) */
     int tile_n;    /* accumulator columns per tile */
     int tile_k;    /* K elements per shared-memory stage */
     int stages;    /* depth of the TMA -> MMA ring */
@@ -102,7 +103,11 @@ typedef struct {
     int raster;    /* 0 = M fastest, 1 = N fastest */
     int mma_m, mma_n, mma_k;
     int num_ctas;        /* persistent grid size */
-    int split_k;         /* K slices reduced through scratch memory (1 = none) */
+    int split_k;         /* > 1: K slices on separate CTAs, reduced through scratch memory; 1: none;
+                            < 0: the kernel for M <= 128 - every 128 x 256 tile is split along K over a
+                            thread-block cluster of -split_k CTAs (1, 2, 4, 8) whose partial sums meet in
+                            distributed shared memory.  In a pin, -1 asks for that kernel and lets the
+                            library choose the cluster size; >= 1 rules it out */
     double predicted_ms; /* model estimate, compare with the measured time */
 } o64_plan_t;
 

@@ -10,7 +10,7 @@
 //   * a 128 x 256 output tile belongs to a thread-block CLUSTER of S CTAs (S = 1, 2, 4, 8), each of
 //     which multiplies one slice of K.  The partial sums never touch global memory: after a
 //     cluster barrier (every main loop done, so every ring is free) each CTA stores the columns
-//     c * 256/S .. of its accumulator into CTA c's shared memory (distributed shared memory), a
+//     c * 256/S .. of its accumulator into CTA c's idle ring (distributed shared memory), a
 //     second cluster barrier follows, and each CTA adds the S slices it received, applies the
 //     epilogue and writes its 256/S columns of C.  Measured: partial sums exchanged through L2
 //     (atomics, a fence, a completion counter) cost three dependent round trips of about 2 us each
@@ -49,27 +49,26 @@ constexpr int kSkAbortOffset = kSkTmemPtrOffset + 4;
 constexpr int kSkTotal = kSkAbortOffset + 4;
 constexpr int kSkDynamic = kSkTotal + 1024;  // slack to align the ring to 1024 bytes
 static_assert(kSkDynamic <= 227 * 1024, "shared memory");
+static_assert(kSkRingBytes - 2 * kEpiStagingBytesPerWarp >= 128 * 1024, "borrowed patches lie beyond the receive area");
 
 __device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint4 v) {
     asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                  : "memory");
 }
 
-// Sends this warp's 32 accumulator rows to the CTAs of the cluster: columns c*slice .. of the
-// tile go to CTA c, into slot `rank` of its receive area ([S][M][slice] 4-byte sums at `recv`,
-// the same shared-memory offset in every CTA).  Through the swizzled patch, so that a store
-// instruction writes four full 128-byte row segments.
+// Sends 32 accumulator rows (this warp's TMEM lane quarter), 32-column chunks c_begin .. c_end-1,
+// to the CTAs of the cluster: columns c*slice .. of the tile go to CTA c, into slot `rank` of its
+// receive area ([S][M][slice] 4-byte sums at `recv`, the same shared-memory offset in every
+// CTA).  Through the swizzled patch, so that a store instruction writes four full 128-byte row
+// segments (measured: storing each thread's own row straight from its registers, 32 rows per
+// instruction, takes twice as long for 128 rows); the load of the next chunk is in flight while
+// this one is sent.
 __device__ __forceinline__ void scatter_rows(const UmmaParams &p, int row0, uint32_t t_row, uint8_t *staging,
-                                             uint32_t recv, int rank, int slice) {
+                                             uint32_t recv, int rank, int slice, int c_begin, int c_end) {
     const int lane = threadIdx.x & 31;
     uint4 *patch = reinterpret_cast<uint4 *>(staging);
     const int sw = lane & 7;
-#pragma unroll 1
-    for (int i = 0; i < kSkBlockN / 32; ++i) {
-        uint32_t v[32];
-        __syncwarp();
-        tmem_ld_32x32(t_row + 32 * i, v);
-        tmem_ld_wait();
+    auto send = [&](const uint32_t (&v)[32], int i) {
 #pragma unroll
         for (int q = 0; q < 8; ++q)
             patch[lane * 8 + (q ^ sw)] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
@@ -85,11 +84,27 @@ __device__ __forceinline__ void scatter_rows(const UmmaParams &p, int row0, uint
             if (grow < p.M) st_cluster_v4(base + (uint32_t)(((rank * p.M + grow) * slice + cin) * 4), val);
         }
         __syncwarp();
+    };
+    uint32_t va[32], vb[32];
+    __syncwarp();
+    tmem_ld_32x32(t_row + 32 * c_begin, va);
+#pragma unroll 1
+    for (int i = c_begin; i < c_end; i += 2) {
+        tmem_ld_wait();
+        __syncwarp();
+        if (i + 1 < c_end) tmem_ld_32x32(t_row + 32 * (i + 1), vb);
+        send(va, i);
+        if (i + 1 < c_end) {
+            tmem_ld_wait();
+            __syncwarp();
+            if (i + 2 < c_end) tmem_ld_32x32(t_row + 32 * (i + 2), va);
+            send(vb, i + 1);
+        }
     }
 }
 
 // Adds the S slices received for this CTA's columns, applies the epilogue and writes C.
-// 128 threads; four columns per thread.
+// All threads of the CTA; four columns per thread.
 template <int EPI, int ACT>
 __device__ __forceinline__ void gather_store(const UmmaParams &p, const uint8_t *recv, int n0, int rank, int S,
                                              int slice, int t) {
@@ -110,10 +125,11 @@ __device__ __forceinline__ void gather_store(const UmmaParams &p, const uint8_t 
             }
         }
     }
-    for (int m = t / tpr; m < p.M; m += 128 / tpr) {
-        uint4 acc = *reinterpret_cast<const uint4 *>(recv + (size_t)((m * slice) + c4) * 4);
+    for (int m = t / tpr; m < p.M; m += kThreads / tpr) {
+        const int pitch = slice;
+        uint4 acc = *reinterpret_cast<const uint4 *>(recv + (size_t)((m * pitch) + c4) * 4);
         for (int src = 1; src < S; ++src) {
-            const uint4 w = *reinterpret_cast<const uint4 *>(recv + (size_t)(((src * p.M + m) * slice) + c4) * 4);
+            const uint4 w = *reinterpret_cast<const uint4 *>(recv + (size_t)(((src * p.M + m) * pitch) + c4) * 4);
             if constexpr (EPI == EPI_S32) {
                 acc.x += w.x; acc.y += w.y; acc.z += w.z; acc.w += w.w;  // two's complement: exact
             } else {
@@ -329,18 +345,26 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
         if (dbg && threadIdx.x == 64) dbg[5] = globaltimer_ns();
         const bool good = (*abort_flag == 0);
         const int slice = kSkBlockN / S;
-        const int epi_tid = (int)threadIdx.x - 64;  // 0..127 over the four epilogue warps
-        if (warp >= 2 && good) {
+        if (good) {
+            // every warp sends: warp w reads TMEM lane quarter w % 4, so quarters 0 and 1 have two
+            // warps (w and w + 4), which take four chunks each
             const int quarter = warp & 3;
+            const bool shared_quarter = quarter < 2;
+            const int c_begin = (shared_quarter && warp >= 4) ? 4 : 0;
+            const int c_end = (shared_quarter && warp < 4) ? 4 : kSkBlockN / 32;
+            // patches: the epilogue warps' own; warps 0 and 1 borrow the end of the (now idle) ring,
+            // beyond the receive area (at most 128 KB from its start)
+            uint8_t *patch = warp >= 2 ? smem_gen + kSkStagingOffset + quarter * kEpiStagingBytesPerWarp
+                                       : smem_gen + kSkRingBytes - (2 - warp) * kEpiStagingBytesPerWarp;
             tc_fence_after();
             if (quarter * 32 < p.M)
-                scatter_rows(p, quarter * 32, tmem_base + (uint32_t(quarter * 32) << 16),
-                             smem_gen + kSkStagingOffset + quarter * kEpiStagingBytesPerWarp, smem_base, rank, slice);
+                scatter_rows(p, quarter * 32, tmem_base + (uint32_t(quarter * 32) << 16), patch, smem_base, rank,
+                             slice, c_begin, c_end);
             tc_fence_before();
         }
         cluster_sync_all();  // the slices sent to this CTA have arrived
         if (dbg && threadIdx.x == 64) dbg[6] = globaltimer_ns();
-        if (warp >= 2 && good) gather_store_dispatch<EPI>(p, smem_gen, n0, rank, S, slice, epi_tid);
+        if (good) gather_store_dispatch<EPI>(p, smem_gen, n0, rank, S, slice, (int)threadIdx.x);
     }
     if (dbg && threadIdx.x == 64) dbg[7] = globaltimer_ns();
 
@@ -410,12 +434,13 @@ static int launch_skinny(const CUtensorMap &ta, const CUtensorMap &tb, UmmaParam
     return O64_OK;
 }
 
-// K slices per tile: the largest cluster size (1, 2, 4, 8) that keeps tiles * S within the CTAs
-// the plan allows and leaves every slice at least one K block.
+// K slices per tile: the largest cluster size that keeps tiles * S within the CTAs the plan
+// allows and leaves every slice at least one K block.  Clusters of 8 only for 8 tiles or fewer:
+// measured, sixteen clusters of 8 CTAs with this much shared memory do not all fit at once.
 int umma_skinny_split(int64_t N, int64_t K, int elem, int num_ctas) {
     const int64_t tiles = (N + kSkBlockN - 1) / kSkBlockN;
     const int64_t kbs = (K + kRowBytes / elem - 1) / (kRowBytes / elem);
-    int s = 8;
+    int s = tiles <= 8 ? 8 : 4;
     while (s > 1 && (tiles * s > num_ctas || s > kbs)) s /= 2;
     return s;
 }

@@ -229,14 +229,15 @@ extern "C" int o64_plan_get(o64_handle_t h, int kind, int64_t M, int64_t N, int6
     if (!h || !plan || kind < 0 || kind > 3) return O64_ERR_RANK;
     if (M <= 0 || N <= 0 || K <= 0) return O64_ERR_RANK;
     if (kind == O64_KIND_F32) {
+        // the plan of the dense fused linear (operands aligned to 16 bytes; other calls use a
+        // scalar-access kernel with 64 x 64 or 32 x 32 tiles)
         memset(plan, 0, sizeof(*plan));
         plan->kind = kind;
-        const bool big = ((M + 63) / 64) * ((N + 63) / 64) >= 2LL * h->num_sms;
-        plan->tile_m = plan->tile_n = big ? 64 : 32;
+        simt_dense_tile(M, N, h->num_sms, &plan->tile_m, &plan->tile_n);
         plan->tile_k = 16;
-        plan->stages = 1;
+        plan->stages = 2;
         plan->cta_group = 1;
-        plan->mma_m = plan->mma_n = big ? 4 : 2;
+        plan->mma_m = plan->mma_n = 4;
         plan->mma_k = 1;
         plan->split_k = 1;
         plan->num_ctas = (int)(((M + plan->tile_m - 1) / plan->tile_m) * ((N + plan->tile_n - 1) / plan->tile_n));

@@ -26,6 +26,9 @@ struct SimtGemmCall {
     cudaStream_t stream;
 };
 int simt_gemm_f32(const SimtGemmCall &c);
+// Dense row-major fast path of simt_gemm_f32: whether a call qualifies, and the CTA tile it gets.
+bool simt_dense_ok(const SimtGemmCall &c);
+void simt_dense_tile(int64_t M, int64_t N, int num_sms, int *tile_m, int *tile_n);
 
 // y(i) = alpha * sum_j A(i,j)*x(j) + beta*y(i); terms with x(j) == 0 are left out
 // (osprey/libfi/matrix/s4gemvx.f).

@@ -63,6 +63,9 @@ static NcclApi &nccl() {
 
 // ---- handle ---------------------------------------------------------------------------------
 static const int kSlots = 9;  // 0-5 host staging, 6-8 repacked operands (A, B, B2)
+static const int kMaxBlocks = 32;       // row blocks of a pipelined host-operand call
+static const int64_t kBlockRows = 1024;  // at least this many rows per block
+
 struct o64_handle_s {
     int device = 0;
     int num_sms = 148;
@@ -73,6 +76,11 @@ struct o64_handle_s {
     size_t stage_cap[kSlots] = {0};
     void *ws = nullptr;
     size_t ws_cap = 0;
+    // host operands of a large product travel in row blocks on two side streams, so that the
+    // copies in both directions overlap the kernels (created on first use)
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    cudaEvent_t ev_entry = nullptr, ev_done = nullptr;
+    cudaEvent_t ev_in[kMaxBlocks] = {nullptr}, ev_mm[kMaxBlocks] = {nullptr};
     ncclComm_t comm = nullptr;
     int rank = 0, nranks = 1;
     // symmetric result buffer for the fused GEMM + all-gather (one allocation per rank, every
@@ -179,6 +187,14 @@ extern "C" int o64_destroy(o64_handle_t h) {
     for (int i = 0; i < kSlots; ++i)
         if (h->stage[i]) cudaFree(h->stage[i]);
     if (h->ws) cudaFree(h->ws);
+    if (h->copy_in) cudaStreamDestroy(h->copy_in);
+    if (h->copy_out) cudaStreamDestroy(h->copy_out);
+    if (h->ev_entry) cudaEventDestroy(h->ev_entry);
+    if (h->ev_done) cudaEventDestroy(h->ev_done);
+    for (int i = 0; i < kMaxBlocks; ++i) {
+        if (h->ev_in[i]) cudaEventDestroy(h->ev_in[i]);
+        if (h->ev_mm[i]) cudaEventDestroy(h->ev_mm[i]);
+    }
     if (h->status_word) cudaFree(h->status_word);
     delete h;
     return O64_OK;
@@ -382,6 +398,31 @@ extern "C" int o64_linear_f32(o64_handle_t h, int64_t M, int64_t N, int64_t K, c
     return stage_out_end(out, s);
 }
 
+static int pipeline_resources(o64_handle_t h) {
+    if (h->copy_in) return O64_OK;
+    cudaStream_t a = nullptr, b = nullptr;
+    if (cudaStreamCreateWithFlags(&a, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&b, cudaStreamNonBlocking) != cudaSuccess) {
+        (void)cudaGetLastError();
+        if (a) cudaStreamDestroy(a);
+        return O64_ERR_CUDA;
+    }
+    bool ok = cudaEventCreateWithFlags(&h->ev_entry, cudaEventDisableTiming) == cudaSuccess &&
+              cudaEventCreateWithFlags(&h->ev_done, cudaEventDisableTiming) == cudaSuccess;
+    for (int i = 0; ok && i < kMaxBlocks; ++i)
+        ok = cudaEventCreateWithFlags(&h->ev_in[i], cudaEventDisableTiming) == cudaSuccess &&
+             cudaEventCreateWithFlags(&h->ev_mm[i], cudaEventDisableTiming) == cudaSuccess;
+    if (!ok) {
+        (void)cudaGetLastError();
+        cudaStreamDestroy(a);
+        cudaStreamDestroy(b);
+        return O64_ERR_CUDA;  // events created so far are released with the handle
+    }
+    h->copy_in = a;
+    h->copy_out = b;
+    return O64_OK;
+}
+
 static int umma_entry(o64_handle_t h, int kind, bool b_kn, int epi, int64_t M, int64_t N, int64_t K,
                       const void *A, int64_t lda, const void *B, const void *B2, int64_t ldb, void *C,
                       int64_t ldc, const float *bias, const float *sa, const float *sb, int act,
@@ -400,7 +441,18 @@ static int umma_entry(o64_handle_t h, int kind, bool b_kn, int epi, int64_t M, i
     const void *dA, *dB, *dB2, *dbias, *dsa, *dsb;
     StagedOut out;
     int rc;
-    if ((rc = stage_in(h, 0, A, span_bytes(M, K, lda, elem), s, &dA))) return rc;
+    // Host A and host C of a tall product: rows travel in blocks.  Block i's rows of A are copied on
+    // one side stream, multiplied on the caller's stream, and its rows of C copied back on another,
+    // so that host->device, kernels and device->host overlap (the link carries both directions at
+    // once); the weight is staged whole, first.  Everything else goes the plain way.
+    const bool piped = M >= 2 * kBlockRows && ldc == N && (lda * elem) % 16 == 0 && is_host_ptr(A) && is_host_ptr(C) &&
+                       pipeline_resources(h) == O64_OK;
+    if (piped) {
+        if ((rc = reserve(&h->stage[0], &h->stage_cap[0], span_bytes(M, K, lda, elem)))) return rc;
+        dA = h->stage[0];
+    } else if ((rc = stage_in(h, 0, A, span_bytes(M, K, lda, elem), s, &dA))) {
+        return rc;
+    }
     if ((rc = stage_in(h, 1, B, span_bytes(b_rows, b_cols, ldb, elem), s, &dB))) return rc;
     if ((rc = stage_in(h, 2, B2, span_bytes(b_rows, b_cols, ldb, elem), s, &dB2))) return rc;
     if ((rc = stage_in(h, 3, bias, (size_t)N * 4, s, &dbias))) return rc;
@@ -421,7 +473,7 @@ static int umma_entry(o64_handle_t h, int kind, bool b_kn, int epi, int64_t M, i
     }
     if ((rc = stage_out_begin(h, 5, C, span_bytes(M, N, ldc, out_elem), ldc != N, s, &out))) return rc;
     int64_t lda_eff = lda, ldb_eff = ldb, ldb2_eff = ldb;
-    if ((rc = repack_if_unaligned(h, 6, &dA, &lda_eff, M, K, elem, s))) return rc;
+    if (!piped && (rc = repack_if_unaligned(h, 6, &dA, &lda_eff, M, K, elem, s))) return rc;
     // gate and up weights share one pitch: if either needs the copy, both get it
     const bool both = dB2 && (!tma_aligned(dB, ldb, elem) || !tma_aligned(dB2, ldb, elem));
     if ((rc = repack_if_unaligned(h, 7, &dB, &ldb_eff, b_rows, b_cols, elem, s, both))) return rc;
@@ -439,9 +491,48 @@ static int umma_entry(o64_handle_t h, int kind, bool b_kn, int epi, int64_t M, i
     c.scale_a = (const float *)dsa;
     c.scale_b = (const float *)dsb;
     c.act = act;
-    choose(h, kind, epi, M, N, K, &c.plan);
     c.status_word = h->status_word;
     c.stream = s;
+    if (piped) {
+        int64_t rows = (M + kMaxBlocks - 1) / kMaxBlocks;
+        if (rows < kBlockRows) rows = kBlockRows;
+        rows = (rows + 511) / 512 * 512;  // whole tiles of every kernel
+        const int blocks = (int)((M + rows - 1) / rows);
+        // the staging buffers may still be read by an earlier call's kernels on the caller's stream
+        CUDA_TRY(cudaEventRecord(h->ev_entry, s));
+        CUDA_TRY(cudaStreamWaitEvent(h->copy_in, h->ev_entry, 0));
+        CUDA_TRY(cudaStreamWaitEvent(h->copy_out, h->ev_entry, 0));
+        o64_plan_t pin;
+        memset(&pin, 0, sizeof(pin));
+        if (h->has_pin[kind]) pin = h->pins[kind];
+        if (pin.split_k == 0) pin.split_k = 1;  // no plan that needs zeroed scratch per block
+        for (int i = 0; i < blocks; ++i) {
+            const int64_t r0 = (int64_t)i * rows;
+            const int64_t nr = (M - r0) < rows ? (M - r0) : rows;
+            const uint8_t *a_src = static_cast<const uint8_t *>(A) + (size_t)r0 * lda * elem;
+            uint8_t *a_dst = static_cast<uint8_t *>(h->stage[0]) + (size_t)r0 * lda * elem;
+            CUDA_TRY(cudaMemcpyAsync(a_dst, a_src, span_bytes(nr, K, lda, elem), cudaMemcpyHostToDevice, h->copy_in));
+            CUDA_TRY(cudaEventRecord(h->ev_in[i], h->copy_in));
+            CUDA_TRY(cudaStreamWaitEvent(s, h->ev_in[i], 0));
+            UmmaCall b = c;
+            b.M = nr;
+            b.A = a_dst;
+            b.C = static_cast<uint8_t *>(out.dev) + (size_t)r0 * ldc * out_elem;
+            if (b.scale_a) b.scale_a += r0;
+            plan_choose(kind, epi, nr, N, K, h->num_sms, &pin, &b.plan);
+            if (b.plan.split_k > 1) b.plan.split_k = 1;
+            if ((rc = umma_launch(b))) return rc;
+            CUDA_TRY(cudaEventRecord(h->ev_mm[i], s));
+            CUDA_TRY(cudaStreamWaitEvent(h->copy_out, h->ev_mm[i], 0));
+            CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t *>(out.host) + (size_t)r0 * ldc * out_elem, b.C,
+                                     (size_t)nr * ldc * out_elem, cudaMemcpyDeviceToHost, h->copy_out));
+        }
+        CUDA_TRY(cudaEventRecord(h->ev_done, h->copy_out));
+        CUDA_TRY(cudaStreamWaitEvent(s, h->ev_done, 0));
+        CUDA_TRY(cudaStreamSynchronize(s));  // with a host result the call is synchronous
+        return O64_OK;
+    }
+    choose(h, kind, epi, M, N, K, &c.plan);
     // split-K (few tiles, long K): partial sums meet in scratch memory; a second small kernel
     // applies the epilogue for 16-bit results, int32 results are summed in place
     const bool split = c.plan.split_k > 1 && c.plan.cta_group == 1 && epi != EPI_SWIGLU;

@@ -42,7 +42,10 @@ static double predict_ms(int kind, int epi, int64_t M, int64_t N, int64_t K, int
     // MMAs chained on one accumulator run about a tenth slower than alternated between two
     const double n_eff = tile_n < 256 ? 256.0 : double(tile_n);
     const double issue = (rows_per_cta == 256) ? 1.0 : (cta_group == 2 ? 1.10 : 1.02);
-    const double mma_clk = issue * 2.0 * rows_per_cta * n_eff * block_k / flop_rate;  // per SM
+    double mma_clk = issue * 2.0 * rows_per_cta * n_eff * block_k / flop_rate;  // per SM
+    // calibration on M = 192..256, N = K = 8192: a K block of a 128-column tile took 471 cycles on one
+    // CTA and 415 on a pair, where the line above says 522 and 563
+    if (tile_n < 256) mma_clk *= (cta_group == 2) ? 0.74 : 0.90;
     const double fill_clk = (double(rows_per_cta) + double(tile_n) / cta_group) * 128.0 / kSmemFillBytesPerClkSm;
     // the ring must also cover the L2 -> shared-memory latency: (stages - 1) K blocks in flight
     const int stage_bytes = (rows_per_cta + tile_n / cta_group) * 128;
@@ -57,6 +60,23 @@ static double predict_ms(int kind, int epi, int64_t M, int64_t N, int64_t K, int
     if (rows_per_cta == 256) epilogue_clk = (kind == O64_KIND_S8) ? 20000.0 : (epi == EPI_SWIGLU ? 8000.0 : 12000.0);
     const double prologue_clk = 2500.0;  // first TMA round trip + epilogue tail of the last tile
     return (waves * (kblocks * stage_clk + epilogue_clk) + prologue_clk) / (kClockGHz * 1e6);
+}
+
+// Split-K of the one-CTA tile kernel: when a CTA-per-tile plan leaves most SMs idle and K is long,
+// slices of K go to separate CTAs (the reference's cache model blocks K the same way when one level
+// cannot hold a whole strip, osprey/be/lno/cache_model.cxx:6650-6727).  Measured on M x 8192 x 8192:
+// worth it for few rows, not for M = 128 (the atomics grow with M).
+static int auto_split_k(int64_t M, int64_t N, int64_t K, int tile_n, int tile_k, int num_ctas) {
+    const long long tiles = ((M + 127) / 128) * ((N + tile_n - 1) / tile_n);
+    const long long kblocks = (K + tile_k - 1) / tile_k;
+    int sk = 1;
+    if (tiles * 2 <= num_ctas && kblocks >= 16 && (M <= 64 || tiles * 8 <= num_ctas)) {
+        sk = (int)(num_ctas / tiles);
+        if (sk > kblocks / 8) sk = (int)(kblocks / 8);
+        if (sk > 16) sk = 16;
+        if (sk < 1) sk = 1;
+    }
+    return sk;
 }
 
 // O64_LNO="blocking_size=128x256x64:stages=4:cta_group=1:group_m=8:raster=0:num_ctas=148:split_k=1"
@@ -118,7 +138,12 @@ void plan_choose(int kind, int epi, int64_t M, int64_t N, int64_t K, int num_sms
             if (pin.tile_n && pin.tile_n != n) continue;
             if (tm == 512 && n != 256) continue;                      // not instantiated
             if (g == 2 && n == 128 && epi == EPI_SWIGLU) continue;  // not instantiated
-            const double t = predict_ms(kind, epi, M, N, K, n, out->num_ctas, g, tm);
+            double t = predict_ms(kind, epi, M, N, K, n, out->num_ctas, g, tm);
+            if (g == 1 && epi != EPI_SWIGLU && pin.split_k == 0) {
+                // the one-CTA kernel may split K: the main loop shrinks, atomics and a finishing pass come on top
+                const int sk = auto_split_k(M, N, K, n, out->tile_k, out->num_ctas);
+                if (sk > 1) t = t / sk + 0.006;
+            }
             if (t < best_t) {
                 best_t = t;
                 best_g = g;
@@ -148,25 +173,12 @@ void plan_choose(int kind, int epi, int64_t M, int64_t N, int64_t K, int num_sms
     } else {
         out->group_m = 2048 / out->tile_m;
     }
-    // Split-K: when a CTA-per-tile plan leaves most SMs idle and K is long, slices of K go to
-    // separate CTAs (the reference's cache model blocks K the same way when one level cannot hold
-    // a whole strip, osprey/be/lno/cache_model.cxx:6650-6727).  Skinny GEMMs are bound by HBM:
-    // every SM must have loads in flight.
     if (out->cta_group == 1 && epi != EPI_SWIGLU) {
-        const int out_n = tile_n;
-        const long long tiles = ((M + 127) / 128) * ((N + out_n - 1) / out_n);
         const long long kblocks = (K + out->tile_k - 1) / out->tile_k;
-        int sk = pin.split_k > 0 ? pin.split_k : 1;
-        // measured on M x 8192 x 8192: worth it for M = 16 (42 -> 38 us), not for M = 128 (the
-        // atomics grow with M)
-        if (pin.split_k <= 0 && tiles * 2 <= out->num_ctas && kblocks >= 16 && (M <= 64 || tiles * 8 <= out->num_ctas)) {
-            sk = (int)(out->num_ctas / tiles);
-            if (sk > kblocks / 8) sk = (int)(kblocks / 8);
-            if (sk > 16) sk = 16;
-            if (sk < 1) sk = 1;
-        }
+        int sk = pin.split_k > 0 ? pin.split_k : auto_split_k(M, N, K, tile_n, out->tile_k, out->num_ctas);
         if (sk > kblocks) sk = (int)kblocks;
         out->split_k = sk;
+        if (sk > 1 && pin.split_k <= 0) out->predicted_ms = out->predicted_ms / sk + 0.006;
     }
     out->raster = pin.raster ? 1 : 0;  // the automatic choice is 0 (M fastest)
 

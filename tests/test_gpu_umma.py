@@ -246,3 +246,33 @@ def test_split_k_for_skinny_shapes(eng, shape):
     C8 = eng.gemm_fp8_scaled(A8.to(DEV), W8.to(DEV), sA.to(DEV), sB.to(DEV), b8.to(DEV))
     ref8 = oracle.gemm_fp8_scaled(bits8(A8), bits8(W8), sA.numpy(), sB.numpy(), b8.numpy())
     assert relmax(C8.float().cpu().numpy(), ref8) <= TOL_LOWP
+
+
+@pytest.mark.parametrize("pinned", [True, False])
+def test_tall_host_operands_travel_in_row_blocks(eng, pinned):
+    """Host A and host C with at least 2048 rows: the rows are copied, multiplied and copied back in
+    blocks on separate streams.  Same results as with device operands; the last block is ragged."""
+    M, N, K = 2304, 384, 256
+    A, B = _bf16_case(M, N, K, True, seed=31)
+    bias = torch.randn(N, generator=torch.Generator().manual_seed(5))
+    Ah = A.pin_memory() if pinned else A
+    Ch = torch.full((M, N), float("nan"), dtype=torch.bfloat16)
+    if pinned:
+        Ch = Ch.pin_memory()
+    for rep in range(2):
+        eng.gemm_bf16(Ah, B.to(DEV), transB=True, bias=bias.to(DEV), act="gelu_tanh", out=Ch)
+        Cd = eng.gemm_bf16(A.to(DEV), B.to(DEV), transB=True, bias=bias.to(DEV), act="gelu_tanh")
+        assert torch.equal(Ch, Cd.cpu())
+    ref = oracle.gemm_bf16(bits16(A[-300:]), bits16(B), bias=bias.numpy(), act=oracle.ACT_GELU_TANH, transB=True)
+    assert relmax(Ch[-300:].float().numpy(), ref) <= TOL_LOWP
+    # int8 (exact) and fp8 with per-row scales (the scale vector is offset per block), B on the host too
+    Ai, Bi = o.workloads.c5_int8(M, N, K, seed=77)
+    Ci = torch.empty((M, N), dtype=torch.int32)
+    eng.gemm_s8(Ai, Bi, out=Ci)
+    assert np.array_equal(Ci.numpy(), oracle.gemm_s8s8_s32(Ai.numpy(), Bi.numpy()))
+    A8, W8, sA, sB, b8 = o.workloads.c4_fp8(M, N, K, seed=78)
+    C8 = torch.empty((M, N), dtype=torch.bfloat16)
+    eng.gemm_fp8_scaled(A8, W8.to(DEV), sA.to(DEV), sB.to(DEV), b8.to(DEV), out=C8)
+    ref8 = oracle.gemm_fp8_scaled(bits8(A8), bits8(W8), sA.numpy(), sB.numpy(), b8.numpy())
+    assert relmax(C8.float().numpy(), ref8) <= TOL_LOWP
+    assert eng.last_status() == (o.OK, 0)

@@ -1,4 +1,5 @@
-"""Builds libo64gemm.so in-tree with nvcc for sm_100a (cross-compiles without a GPU).
+"""Builds libo64gemm.so in-tree with nvcc for sm_100a (cross-compiles without a GPU) and the
+host-only source rewriter o64nest with g++.
 
 Usage:  python -m open64_b200.build [--force] [--verbose]
 """
@@ -11,6 +12,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libo64gemm.so")
 OBJ_DIR = os.path.join(HERE, "build")
+NEST_SRC = os.path.join(HERE, "nest2c", "nest2c.cpp")
+NEST_OUT = os.path.join(HERE, "nest2c", "o64nest")
 
 SOURCES = ["api.cu", "umma_gemm.cu", "umma_gemm_2cta.cu", "umma_gemm_wide.cu", "umma_gemm_skinny.cu", "simt_kernels.cu", "simt_generic.cu", "plan.cpp", "no_alloc.cu"]
 HEADERS = ["ptx_sm100.cuh", "umma_gemm.cuh", "umma_common.cuh", "simt_kernels.cuh", "../../include/o64gemm.h"]
@@ -69,6 +72,12 @@ def build(force=False, verbose=False):
             raise RuntimeError("link failed:\n" + r.stdout + r.stderr)
     with open(os.path.join(OBJ_DIR, "ptxas.log"), "a") as f:
         f.write("".join(logs))
+    if os.path.exists(NEST_SRC) and (force or _stale(NEST_OUT, [NEST_SRC])):
+        r = subprocess.run(["g++", "-O2", "-std=c++17", "-Wall", "-o", NEST_OUT, NEST_SRC], capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("g++ failed on o64nest:\n" + r.stdout + r.stderr)
+        if verbose:
+            sys.stderr.write(r.stderr)
     return OUT
 
 

@@ -221,6 +221,16 @@ extern "C" int o64_plan_set(o64_handle_t h, int kind, const o64_plan_t *plan) {
         h->has_pin[kind] = false;
         return O64_OK;
     }
+    if (kind == O64_KIND_F32) {
+        // the CUDA-core kernel: 32 x 32, 32 x 64 or 64 x 64 tiles (tile_k and the rest are fixed)
+        const bool m_ok = plan->tile_m == 0 || plan->tile_m == 32 || plan->tile_m == 64;
+        const bool n_ok = plan->tile_n == 0 || plan->tile_n == 32 || plan->tile_n == 64;
+        if (!m_ok || !n_ok || (plan->tile_m == 64 && plan->tile_n == 32)) return O64_ERR_RANK;
+        if (plan->tile_k && plan->tile_k != 16) return O64_ERR_RANK;
+        h->pins[kind] = *plan;
+        h->has_pin[kind] = true;
+        return O64_OK;
+    }
     const bool few_rows = plan->split_k < 0;  // the kernel for M <= 128: tile_m = rows of A per stage
     if (few_rows && plan->tile_m && plan->tile_m != 16 && plan->tile_m != 32 && plan->tile_m != 64 && plan->tile_m != 128)
         return O64_ERR_RANK;
@@ -250,6 +260,7 @@ extern "C" int o64_plan_get(o64_handle_t h, int kind, int64_t M, int64_t N, int6
         memset(plan, 0, sizeof(*plan));
         plan->kind = kind;
         simt_dense_tile(M, N, h->num_sms, &plan->tile_m, &plan->tile_n);
+        if (h->has_pin[kind]) simt_apply_pin(h->pins[kind].tile_m, h->pins[kind].tile_n, &plan->tile_m, &plan->tile_n);
         plan->tile_k = 16;
         plan->stages = 2;
         plan->cta_group = 1;
@@ -394,6 +405,10 @@ extern "C" int o64_linear_f32(o64_handle_t h, int64_t M, int64_t N, int64_t K, c
     c.skip_zero_b = false;
     c.num_sms = h->num_sms;
     c.stream = s;
+    if (h->has_pin[O64_KIND_F32]) {
+        c.pin_tile_m = h->pins[O64_KIND_F32].tile_m;
+        c.pin_tile_n = h->pins[O64_KIND_F32].tile_n;
+    }
     if ((rc = simt_gemm_f32(c))) return rc;
     return stage_out_end(out, s);
 }

@@ -291,6 +291,12 @@ void simt_dense_tile(int64_t M, int64_t N, int num_sms, int *tile_m, int *tile_n
     }
 }
 
+void simt_apply_pin(int pin_m, int pin_n, int *tile_m, int *tile_n) {
+    if (pin_m == 32 || pin_m == 64) *tile_m = pin_m;
+    if (pin_n == 32 || pin_n == 64) *tile_n = pin_n;
+    if (*tile_m == 64 && *tile_n == 32) *tile_n = 64;
+}
+
 bool simt_dense_ok(const SimtGemmCall &c) {
     auto al16 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
     return c.a2 == 1 && c.b2 == 1 && c.c2 == 1 && c.alpha == 1.0f && c.beta == 0.0f && !c.skip_zero_b && c.K > 0 &&
@@ -335,6 +341,7 @@ int simt_gemm_f32(const SimtGemmCall &c) {
     if (simt_dense_ok(c)) {
         int tm, tn;
         simt_dense_tile(c.M, c.N, c.num_sms, &tm, &tn);
+        simt_apply_pin(c.pin_tile_m, c.pin_tile_n, &tm, &tn);
         // measured: the K split inside the CTA gains 5 % at 512^3 (32 x 32 tiles) and loses 15 % at
         // 1024^3 (32 x 64 tiles, already two CTAs per SM)
         if (tm == 64) return launch_dense<64, 64, 1>(p, c.stream);

@@ -24,11 +24,14 @@ struct SimtGemmCall {
     bool skip_zero_b;
     int num_sms;
     cudaStream_t stream;
+    int pin_tile_m = 0, pin_tile_n = 0;  // dense kernel: 0 = choose, else 32 or 64
 };
 int simt_gemm_f32(const SimtGemmCall &c);
 // Dense row-major fast path of simt_gemm_f32: whether a call qualifies, and the CTA tile it gets.
 bool simt_dense_ok(const SimtGemmCall &c);
 void simt_dense_tile(int64_t M, int64_t N, int num_sms, int *tile_m, int *tile_n);
+// Applies a pinned tile (0 = keep the chosen value); the pair 64 x 32 has no kernel and becomes 64 x 64.
+void simt_apply_pin(int pin_m, int pin_n, int *tile_m, int *tile_n);
 
 // y(i) = alpha * sum_j A(i,j)*x(j) + beta*y(i); terms with x(j) == 0 are left out
 // (osprey/libfi/matrix/s4gemvx.f).

@@ -86,3 +86,25 @@ def test_host_operands_are_staged(eng):
     assert not y.is_cuda
     ref = oracle.linear_f32(A.numpy(), B.numpy(), bias.numpy(), oracle.ACT_RELU)
     assert relmax(y.numpy(), ref) <= TOL_F32
+
+
+def test_pinned_tiles_of_the_dense_kernel(eng):
+    """tile_m x tile_n of the CUDA-core kernel can be pinned (what `#pragma blocking size` on the i and
+    j loops of a rewritten nest turns into); sizes without a kernel are refused."""
+    g = torch.Generator().manual_seed(12)
+    A, B = torch.rand(200, 136, generator=g) - 0.5, torch.rand(136, 328, generator=g) - 0.5
+    bias = torch.rand(328, generator=g)
+    ref = oracle.linear_f32(A.numpy(), B.numpy(), bias.numpy(), oracle.ACT_RELU)
+    try:
+        for tm, tn in ((32, 32), (32, 64), (64, 64)):
+            eng.plan_set(o.KIND_F32, tile_m=tm, tile_n=tn)
+            p = eng.plan_get(o.KIND_F32, 200, 328, 136)
+            assert (p["tile_m"], p["tile_n"]) == (tm, tn)
+            y = eng.linear_f32(A.to(DEV), B.to(DEV), bias.to(DEV), act="relu")
+            assert relmax(y.cpu().numpy(), ref) <= TOL_F32
+        for bad in (dict(tile_m=64, tile_n=32), dict(tile_m=128), dict(tile_n=48), dict(tile_k=32)):
+            with pytest.raises(o.O64Error) as e:
+                eng.plan_set(o.KIND_F32, **bad)
+            assert e.value.status == o.ERR_RANK
+    finally:
+        eng.plan_set(o.KIND_F32)

@@ -1,0 +1,84 @@
+"""CPU: o64nest, the source rewriter that turns GEMM-shaped loop nests (as the reference prints
+them back to C, osprey/be/whirl2c/wn2c.cxx:4078-4118) into calls of the engine."""
+import os
+import re
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TOOL = os.path.join(ROOT, "open64_b200", "nest2c", "o64nest")
+SRC = os.path.join(ROOT, "tests", "nests", "layers.c")
+
+
+def rewrite(text):
+    r = subprocess.run([TOOL], input=text, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    n = int(re.search(r"(\d+) nest", r.stderr).group(1))
+    return r.stdout, n
+
+
+def test_every_product_nest_of_the_fixture_is_replaced(built, tmp_path):
+    out, n = rewrite(open(SRC).read())
+    assert n == 6
+    # the fused linear: bias and ReLU in the call, extents from the inclusive bounds, the loops'
+    # blocking-size pragmas as a plan (i loop: tile_m and the L2 group; j loop: tile_n)
+    # (pitches are the declared inner extents, spelled as in the declaration)
+    assert ("o64_linear_f32(o64nest_handle(), 192, 160, 224, &A[0][0], KK, &B[0][0], NN, bias, &Y[0][0], NN, "
+            "O64_ACT_RELU, NULL)") in out
+    assert "o64_plan.tile_m = 32;" in out and "o64_plan.tile_n = 64;" in out and "o64_plan.group_m = 4;" in out
+    assert "o64_linear_f32(o64nest_handle(), MM, NN, KK, &A[0][0], KK, &B[0][0], NN, NULL, &Yplain[0][0], NN, O64_ACT_NONE" in out
+    # other kinds and layouts go to the runtime's strided kernels; a transposed operand swaps its increments
+    assert "_sgemmx__(&o64_m, &o64_n, &o64_k" in out and "o64_m = 100, o64_n = 80, o64_k = 60" in out
+    assert "_i4gemmx__(" in out and "o64_b1 = 1, o64_b2 = 32" in out
+    assert "_jgemmx__(" in out
+    assert "o64_linear_f32(o64nest_handle(), m, n, kk, &X[0], kk, &W[0], n, NULL, &O[0], n, O64_ACT_NONE" in out
+    # the nest that is not a product is untouched, and so is everything around the nests
+    assert "Y[i][j] = Y[i][j] + A[i][k] + B[k][j];" in out
+    assert "static unsigned rng_state = 12345u;" in out and "for (int j = 0; j < NN; j++) bias[j] = frand();" in out
+    # what comes out is C that compiles against the public header
+    path = tmp_path / "layers_out.c"
+    path.write_text(out)
+    r = subprocess.run(["gcc", "-fsyntax-only", "-Wall", "-Werror=implicit-function-declaration",
+                        "-I", os.path.join(ROOT, "include"), str(path)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+
+
+NOT_RECOGNISED = [
+    # lower bound not zero
+    "float A[8][8],B[8][8],C[8][8];\nvoid f(){for(int i=1;i<8;i++)for(int j=0;j<8;j++){C[i][j]=0;for(int k=0;k<8;k++)C[i][j]+=A[i][k]*B[k][j];}}",
+    # step of two
+    "float A[8][8],B[8][8],C[8][8];\nvoid f(){for(int i=0;i<8;i+=2)for(int j=0;j<8;j++){C[i][j]=0;for(int k=0;k<8;k++)C[i][j]+=A[i][k]*B[k][j];}}",
+    # accumulator not zeroed
+    "float A[8][8],B[8][8],C[8][8];\nvoid f(){for(int i=0;i<8;i++)for(int j=0;j<8;j++){C[i][j]=1;for(int k=0;k<8;k++)C[i][j]+=A[i][k]*B[k][j];}}",
+    # the output is also an operand
+    "float A[8][8],C[8][8];\nvoid f(){for(int i=0;i<8;i++)for(int j=0;j<8;j++){C[i][j]=0;for(int k=0;k<8;k++)C[i][j]+=A[i][k]*C[k][j];}}",
+    # mixed element types
+    "float A[8][8];double B[8][8];float C[8][8];\nvoid f(){for(int i=0;i<8;i++)for(int j=0;j<8;j++){C[i][j]=0;for(int k=0;k<8;k++)C[i][j]+=A[i][k]*B[k][j];}}",
+    # subscripts that are not a matrix product (both operands indexed by i and k)
+    "float A[8][8],B[8][8],C[8][8];\nvoid f(){for(int i=0;i<8;i++)for(int j=0;j<8;j++){C[i][j]=0;for(int k=0;k<8;k++)C[i][j]+=A[i][k]*B[i][k];}}",
+    # a tail the engine has no epilogue for, on a kind that only has the plain product
+    "double A[8][8],B[8][8],C[8][8],b[8];\nvoid f(){for(int i=0;i<8;i++)for(int j=0;j<8;j++){double s=0;for(int k=0;k<8;k++)s+=A[i][k]*B[k][j];C[i][j]=s+b[j];}}",
+    # undeclared arrays: the pitch is unknown
+    "void f(){for(int i=0;i<8;i++)for(int j=0;j<8;j++){C[i][j]=0;for(int k=0;k<8;k++)C[i][j]+=A[i][k]*B[k][j];}}",
+]
+
+
+@pytest.mark.parametrize("text", NOT_RECOGNISED)
+def test_nests_outside_the_pattern_pass_through_unchanged(built, text):
+    out, n = rewrite(text)
+    assert n == 0 and out == text
+
+
+def test_whirl2c_spellings(built):
+    text = ("_IEEE32 A[512LL][512LL];\n_IEEE32 B[512LL][512LL];\n_IEEE32 Y[512LL][512LL];\n_IEEE32 bias[512LL];\n"
+            "void layer() {\n  _INT32 i; _INT32 j; _INT32 k; _IEEE32 acc;\n"
+            "  for(i = 0; i <= 511; i = i + 1)\n  {\n    for(j = 0; j <= 511; j = j + 1)\n    {\n      acc = 0.0F;\n"
+            "      for(k = 0; k <= 511; k = k + 1)\n      {\n        acc = acc + (A[i][k] * B[k][j]);\n      }\n"
+            "      Y[i][j] = _MAX(acc + bias[j], 0.0F);\n    }\n  }\n}\n")
+    out, n = rewrite(text)
+    assert n == 1
+    assert "o64_linear_f32(o64nest_handle(), 512, 512, 512, &A[0][0], 512, &B[0][0], 512, bias, &Y[0][0], 512, O64_ACT_RELU, NULL)" in out
+    # x > 0 ? x : 0 is the same tail
+    out2, n2 = rewrite(text.replace("_MAX(acc + bias[j], 0.0F)", "(acc + bias[j]) > 0.0F ? (acc + bias[j]) : 0.0F"))
+    assert n2 == 1 and "O64_ACT_RELU" in out2

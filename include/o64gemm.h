@@ -223,6 +223,15 @@ int o64_gemm_s8_sharded(o64_handle_t h, int64_t M, int64_t N, int64_t K, const i
                         int64_t lda, const int8_t *B_slab, int64_t ldb, int32_t *C_full,
                         int gather, void *workspace, void *stream);
 
+/* The same column-sharded linear for bf16 (C = act(A * B^T + bias), fp32 accumulate, bf16 result):
+ * A [M,K] replicated, B_slab [N/g,K] local, bias (epilogue->bias, or NULL) the full vector of N
+ * values on every rank.  gather: O64_GATHER_NONE (this rank's columns of the row-major C_full),
+ * O64_GATHER_SLABS (slab-major [g][M][N/g], NCCL all-gather in place) or O64_GATHER_PUSH (fused,
+ * row-major on every rank; C_full from o64_comm_alloc_result; N/g a multiple of 64). */
+int o64_gemm_bf16_sharded(o64_handle_t h, int64_t M, int64_t N, int64_t K, const void *A, int64_t lda,
+                          const void *B_slab, int64_t ldb, void *C_full, int gather,
+                          const o64_epilogue_t *epilogue, void *stream);
+
 /* ---- compat layer (Fortran ABI) -------------------------------------------------------- */
 /* Column-major BLAS sgemm: C = alpha*op(A)*op(B) + beta*C. */
 void sgemm_(const char *transa, const char *transb, const int *m, const int *n, const int *k,

@@ -22,7 +22,7 @@ EXPORTS = [
     "o64_create", "o64_destroy", "o64_last_status", "o64_status_string", "o64_version",
     "o64_plan_get", "o64_plan_set", "o64_plan_model", "o64_linear_f32", "o64_gemm_bf16", "o64_gemm_bf16_swiglu",
     "o64_gemm_fp8_scaled", "o64_gemm_s8s8_s32", "o64_gemm_s8s8_s32_static", "o64_naive_gemm", "o64_comm_unique_id",
-    "o64_comm_init", "o64_comm_destroy", "o64_comm_alloc_result", "o64_gemm_s8_sharded_workspace", "o64_gemm_s8_sharded",
+    "o64_comm_init", "o64_comm_destroy", "o64_comm_alloc_result", "o64_gemm_s8_sharded_workspace", "o64_gemm_s8_sharded", "o64_gemm_bf16_sharded",
     "sgemm_", "_s4gemmx__", "_s4gemvx__", "_MATMUL_S4S4", "o64_compat_last_status",
     "dgemm_", "_sgemmx__", "_sgemvx__", "_MATMUL_SS",
     "_i1gemmx__", "_i1i2gemmx__", "_i1i4gemmx__", "_i1jgemmx__", "_i2gemmx__", "_i2i4gemmx__", "_i2jgemmx__",
@@ -132,6 +132,7 @@ def lib():
     L.o64_gemm_s8_sharded_workspace.argtypes = [i64, i64, ci, ci]
     L.o64_gemm_s8_sharded_workspace.restype = ctypes.c_size_t
     L.o64_gemm_s8_sharded.argtypes = [vp, i64, i64, i64, vp, i64, vp, i64, vp, ci, vp, vp]
+    L.o64_gemm_bf16_sharded.argtypes = [vp, i64, i64, i64, vp, i64, vp, i64, vp, ci, ctypes.POINTER(Epilogue), vp]
     L.sgemm_.argtypes = [ctypes.c_char_p, ctypes.c_char_p, pi, pi, pi, pf, vp, pi, vp, pi, pf, vp, pi]
     L.sgemm_.restype = None
     L._s4gemmx__.argtypes = [pi, pi, pi, pf, vp, pi, pi, vp, pi, pi, pf, vp, pi, pi]

@@ -33,6 +33,7 @@ struct NcclApi {
     bool ok = false;
 };
 static const int kNcclInt32 = 2;
+static const int kNcclBfloat16 = 9;  // ncclBfloat16 in ncclDataType_t
 static const int kNcclInt8 = 0;
 static const int kNcclSum = 0;
 
@@ -710,6 +711,58 @@ extern "C" size_t o64_gemm_s8_sharded_workspace(int64_t M, int64_t N, int nranks
     return (size_t)M * (size_t)N * sizeof(int32_t);
 }
 
+// The fused GEMM + exchange of a column-sharded linear: ONE kernel computes this rank's column
+// slab and stores every finished tile into all ranks' copies of C (its own and, over NVLink, the
+// peers'), so the exchange overlaps the GEMM tile by tile.  C_full must be the buffer
+// o64_comm_alloc_result handed out; bias (or NULL) is the full vector of N values.
+static int push_gemm(o64_handle_t h, int kind, int epi, int64_t M, int64_t N, int64_t K, const void *A, int64_t lda,
+                     const void *B_slab, int64_t ldb, void *C_full, int out_elem, const float *bias, int act,
+                     cudaStream_t s) {
+    const int g = h->nranks, r = h->rank;
+    const int64_t ns = N / g;
+    const int elem = (kind == O64_KIND_BF16) ? 2 : 1;
+    if (C_full != h->sym_local || (size_t)M * N * out_elem > h->sym_bytes) return O64_ERR_RANK;
+    if ((ns * out_elem) % 128) return O64_ERR_CONFORM;  // whole 128-byte store slabs only
+    if (is_host_ptr(A) || is_host_ptr(B_slab) || (bias && is_host_ptr(bias))) return O64_ERR_RANK;
+    int rc;
+    // nobody may still be reading the previous result when the first remote store lands
+    if ((rc = rank_barrier(h, s))) return rc;
+    const void *dA = A, *dB = B_slab;
+    int64_t lda_eff = lda, ldb_eff = ldb;
+    if ((rc = repack_if_unaligned(h, 6, &dA, &lda_eff, M, K, elem, s))) return rc;
+    if ((rc = repack_if_unaligned(h, 7, &dB, &ldb_eff, ns, K, elem, s))) return rc;
+    UmmaCall c;
+    c.kind = kind;
+    c.b_kn = false;
+    c.epi = epi;
+    c.M = M; c.N = ns; c.K = K;
+    c.A = dA; c.lda = lda_eff;
+    c.B = dB; c.B2 = nullptr; c.ldb = ldb_eff;
+    c.C = static_cast<uint8_t *>(C_full) + (size_t)r * ns * out_elem; c.ldc = N;
+    c.bias = bias ? bias + (int64_t)r * ns : nullptr;
+    c.scale_a = nullptr; c.scale_b = nullptr;
+    c.act = act;
+    {
+        // the fused exchange lives in the tile kernels' epilogue
+        o64_plan_t pin;
+        memset(&pin, 0, sizeof(pin));
+        if (h->has_pin[kind]) pin = h->pins[kind];
+        if (pin.split_k <= 0) pin.split_k = 1;
+        plan_choose(kind, epi, M, ns, K, h->num_sms, &pin, &c.plan);
+    }
+    c.status_word = h->status_word;
+    c.stream = s;
+    c.n_peers = 0;
+    for (int i = 0; i < g; ++i) {
+        if (i == r) continue;
+        c.peer_c[c.n_peers++] = static_cast<uint8_t *>(h->sym_peer[i]) + (size_t)r * ns * out_elem;
+    }
+    if ((rc = umma_launch(c))) return rc;
+    // every rank's stores are complete when its kernel is; the barrier tells each rank that all
+    // the others got there
+    return rank_barrier(h, s);
+}
+
 extern "C" int o64_gemm_s8_sharded(o64_handle_t h, int64_t M, int64_t N, int64_t K, const int8_t *A,
                                    int64_t lda, const int8_t *B_slab, int64_t ldb, int32_t *C_full,
                                    int gather, void *workspace, void *stream) {
@@ -727,49 +780,8 @@ extern "C" int o64_gemm_s8_sharded(o64_handle_t h, int64_t M, int64_t N, int64_t
     if (gather == O64_GATHER_NONE) {
         return o64_gemm_s8s8_s32(h, M, ns, K, A, lda, B_slab, ldb, C_full + (int64_t)r * ns, N, stream);
     }
-    if (gather == O64_GATHER_PUSH) {
-        // ONE kernel computes this rank's column slab and stores every finished tile into all
-        // ranks' copies of C (its own and, over NVLink, the peers'), so the exchange overlaps the
-        // GEMM tile by tile.  C_full must be the buffer o64_comm_alloc_result handed out.
-        if (C_full != (int32_t *)h->sym_local || (size_t)M * N * 4 > h->sym_bytes) return O64_ERR_RANK;
-        if (ns % 32) return O64_ERR_CONFORM;  // whole 128-byte store slabs only
-        if (is_host_ptr(A) || is_host_ptr(B_slab)) return O64_ERR_RANK;
-        // nobody may still be reading the previous result when the first remote store lands
-        if ((rc = rank_barrier(h, s))) return rc;
-        const void *dA = A, *dB = B_slab;
-        int64_t lda_eff = lda, ldb_eff = ldb;
-        if ((rc = repack_if_unaligned(h, 6, &dA, &lda_eff, M, K, 1, s))) return rc;
-        if ((rc = repack_if_unaligned(h, 7, &dB, &ldb_eff, ns, K, 1, s))) return rc;
-        UmmaCall c;
-        c.kind = O64_KIND_S8;
-        c.b_kn = false;
-        c.epi = EPI_S32;
-        c.M = M; c.N = ns; c.K = K;
-        c.A = dA; c.lda = lda_eff;
-        c.B = dB; c.B2 = nullptr; c.ldb = ldb_eff;
-        c.C = C_full + (int64_t)r * ns; c.ldc = N;
-        c.bias = nullptr; c.scale_a = nullptr; c.scale_b = nullptr;
-        c.act = O64_ACT_NONE;
-        {
-            // the fused exchange lives in the tile kernels' epilogue
-            o64_plan_t pin;
-            memset(&pin, 0, sizeof(pin));
-            if (h->has_pin[O64_KIND_S8]) pin = h->pins[O64_KIND_S8];
-            if (pin.split_k <= 0) pin.split_k = 1;
-            plan_choose(O64_KIND_S8, EPI_S32, M, ns, K, h->num_sms, &pin, &c.plan);
-        }
-        c.status_word = h->status_word;
-        c.stream = s;
-        c.n_peers = 0;
-        for (int i = 0; i < g; ++i) {
-            if (i == r) continue;
-            c.peer_c[c.n_peers++] = (int32_t *)h->sym_peer[i] + (int64_t)r * ns;
-        }
-        if ((rc = umma_launch(c))) return rc;
-        // every rank's stores are complete when its kernel is; the barrier tells each rank that
-        // all the others got there
-        return rank_barrier(h, s);
-    }
+    if (gather == O64_GATHER_PUSH)
+        return push_gemm(h, O64_KIND_S8, EPI_S32, M, N, K, A, lda, B_slab, ldb, C_full, 4, nullptr, O64_ACT_NONE, s);
     int32_t *slabs = C_full;  // [g][M][ns]
     if (gather == O64_GATHER_ROWMAJOR) {
         if (g == 1) return o64_gemm_s8s8_s32(h, M, N, K, A, lda, B_slab, ldb, C_full, N, stream);
@@ -787,6 +799,35 @@ extern "C" int o64_gemm_s8_sharded(o64_handle_t h, int64_t M, int64_t N, int64_t
             return O64_ERR_NCCL;
     }
     if (gather == O64_GATHER_ROWMAJOR) return permute_slabs_s32(slabs, C_full, M, ns, g, N, s);
+    return O64_OK;
+}
+
+extern "C" int o64_gemm_bf16_sharded(o64_handle_t h, int64_t M, int64_t N, int64_t K, const void *A, int64_t lda,
+                                     const void *B_slab, int64_t ldb, void *C_full, int gather,
+                                     const o64_epilogue_t *epi, void *stream) {
+    if (!h || M <= 0 || N <= 0 || K <= 0 || !A || !B_slab || !C_full) return O64_ERR_RANK;
+    const int g = h->nranks, r = h->rank;
+    if (N % g) return O64_ERR_CONFORM;
+    if (gather != O64_GATHER_NONE && gather != O64_GATHER_SLABS && gather != O64_GATHER_PUSH) return O64_ERR_RANK;
+    if (gather != O64_GATHER_NONE && g > 1 && !h->comm) return O64_ERR_NCCL;
+    if (is_host_ptr(A) || is_host_ptr(B_slab) || is_host_ptr(C_full)) return O64_ERR_RANK;
+    const int64_t ns = N / g;
+    const float *bias = epi ? epi->bias : nullptr;
+    const int act = epi ? epi->act : O64_ACT_NONE;
+    DeviceGuard guard(h->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (gather == O64_GATHER_PUSH)
+        return push_gemm(h, O64_KIND_BF16, EPI_BF16, M, N, K, A, lda, B_slab, ldb, C_full, 2, bias, act, s);
+    o64_epilogue_t mine;
+    mine.bias = bias ? bias + (int64_t)r * ns : nullptr;
+    mine.act = act;
+    uint16_t *C = static_cast<uint16_t *>(C_full);
+    if (gather == O64_GATHER_NONE)  // this rank's columns of the row-major result
+        return o64_gemm_bf16(h, M, ns, K, A, lda, B_slab, ldb, 1, C + (int64_t)r * ns, N, &mine, stream);
+    uint16_t *slab = C + (int64_t)r * M * ns;  // slab-major [g][M][ns], gathered in place
+    int rc = o64_gemm_bf16(h, M, ns, K, A, lda, B_slab, ldb, 1, slab, ns, &mine, stream);
+    if (rc) return rc;
+    if (g > 1 && nccl().AllGather(slab, C, (size_t)M * ns, kNcclBfloat16, h->comm, s) != 0) return O64_ERR_NCCL;
     return O64_OK;
 }
 

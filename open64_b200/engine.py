@@ -241,6 +241,18 @@ class Engine:
                                            _stream(A)), "o64_gemm_s8_sharded")
         return out
 
+    def gemm_bf16_sharded(self, A, B_slab, N, gather=GATHER_NONE, bias=None, act="none", out=None):
+        """Column-sharded bf16 linear: this rank owns B_slab [N/g, K]; `bias` is the full [N] vector.
+        `out` is the full [M,N] bf16 result (row-major; slab-major [g][M][N/g] for GATHER_SLABS;
+        from alloc_result(..., dtype=torch.bfloat16) for GATHER_PUSH)."""
+        M, K = A.shape
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
+        ep = _lib.Epilogue(_ptr(bias), _act(act))
+        check(self.lib.o64_gemm_bf16_sharded(self._h, M, N, K, _ptr(A), A.stride(0), _ptr(B_slab), B_slab.stride(0),
+                                             _ptr(out), gather, ctypes.byref(ep), _stream(A)), "o64_gemm_bf16_sharded")
+        return out
+
     # ---- compat layer (Fortran ABI, synchronous) -----------------------------------------
     def sgemm(self, transa, transb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc):
         ci, cf = ctypes.c_int, ctypes.c_float

@@ -36,8 +36,28 @@ def test_single_rank_modes(eng):
     assert np.array_equal(out.cpu().numpy(), ref)
 
 
+def test_single_rank_bf16_modes(eng):
+    from util import TOL_LOWP, bits16, relmax
+    M, N, K = 300, 512, 264
+    g = torch.Generator().manual_seed(8)
+    A = (torch.randn(M, K, generator=g) * 0.2).to(torch.bfloat16)
+    B = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    bias = torch.randn(N, generator=g)
+    ref = oracle.gemm_bf16(bits16(A), bits16(B), bias=bias.numpy(), act=oracle.ACT_SILU, transB=True)
+    Ad, Bd, bd = A.to(DEV), B.to(DEV), bias.to(DEV)
+    for mode in (o.GATHER_NONE, o.GATHER_SLABS):
+        C = eng.gemm_bf16_sharded(Ad, Bd, N, gather=mode, bias=bd, act="silu")
+        assert relmax(C.float().cpu().numpy(), ref) <= TOL_LOWP, mode
+    out = eng.alloc_result(M, N, dtype=torch.bfloat16)
+    eng.gemm_bf16_sharded(Ad, Bd, N, gather=o.GATHER_PUSH, bias=bd, act="silu", out=out)
+    assert relmax(out.float().cpu().numpy(), ref) <= TOL_LOWP
+    with pytest.raises(o.O64Error):
+        eng.gemm_bf16_sharded(Ad, Bd, N, gather=o.GATHER_ROWMAJOR, bias=bd)
+
+
 def _rank_main(rank, world, port, q):
     sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -70,6 +90,23 @@ def _rank_main(rank, world, port, q):
             lin(Ad, gather=oo.GATHER_PUSH, out=out)
             torch.cuda.synchronize()
             assert torch.equal(out.cpu(), ref), f"fused push, call {rep}"
+        # the bf16 linear with a fused bias + GELU, sharded the same way
+        from util import TOL_LOWP, bits16, relmax
+        g = torch.Generator().manual_seed(44)
+        Ab = (torch.randn(M, K, generator=g) * 0.2).to(torch.bfloat16)
+        Bb = torch.randn(N, K, generator=g).to(torch.bfloat16)
+        bias = torch.randn(N, generator=g)
+        refb = orc.gemm_bf16(bits16(Ab), bits16(Bb), bias=bias.numpy(), act=orc.ACT_GELU_TANH, transB=True)
+        Bs = oo.workloads.shard_rows(Bb, rank, world).contiguous().to(dev)
+        outb = eng.alloc_result(M, N, dtype=torch.bfloat16)
+        for rep in range(2):
+            outb.fill_(float(rep + 3))
+            eng.gemm_bf16_sharded(Ab.to(dev), Bs, N, gather=oo.GATHER_PUSH, bias=bias.to(dev), act="gelu_tanh", out=outb)
+            torch.cuda.synchronize()
+            assert relmax(outb.float().cpu().numpy(), refb) <= TOL_LOWP, f"bf16 fused push, call {rep}"
+        slb = eng.gemm_bf16_sharded(Ab.to(dev), Bs, N, gather=oo.GATHER_SLABS, bias=bias.to(dev), act="gelu_tanh")
+        rm = sharded.slab_major_to_row_major(slb.view(world * M, N // world), world)
+        assert relmax(rm.float().cpu().numpy(), refb) <= TOL_LOWP, "bf16 slab-major gather"
         st, detail = eng.last_status()
         assert st == 0
         torch.cuda.synchronize()

@@ -135,6 +135,14 @@ int o64_plan_set(o64_handle_t h, int kind, const o64_plan_t *plan);
  * (may be NULL) and O64_LNO applied.  `swiglu` != 0 scores the fused gate/up GEMM. */
 int o64_plan_model(int kind, int swiglu, int64_t M, int64_t N, int64_t K, int num_sms,
                    const o64_plan_t *pin, o64_plan_t *plan);
+/* Measures instead of modelling: runs every kernel shape that exists for `kind` on zero-filled
+ * scratch operands of these extents (A [M,K], B [N,K]; SwiGLU: two [K,N] weights), remembers the
+ * fastest for (kind, swiglu, M, N, K) and uses it from then on whenever the kind has no pin.
+ * Allocates and frees its scratch, synchronises `stream`; *best (may be NULL) receives the plan
+ * with predicted_ms = the measured time.  o64_plan_tune_clear forgets every measured plan. */
+int o64_plan_tune(o64_handle_t h, int kind, int swiglu, int64_t M, int64_t N, int64_t K, void *stream,
+                  o64_plan_t *best);
+int o64_plan_tune_clear(o64_handle_t h);
 
 /* ---- native layer -------------------------------------------------------------------
  * Row-major operands; ld* in elements.  A is [M,K].  B is [K,N] when transB == 0 and

@@ -8,8 +8,11 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <array>
+#include <map>
 #include <new>
 #include <type_traits>
+#include <vector>
 
 #include "../../include/o64gemm.h"
 #include "simt_kernels.cuh"
@@ -77,6 +80,8 @@ struct o64_handle_s {
     size_t stage_cap[kSlots] = {0};
     void *ws = nullptr;
     size_t ws_cap = 0;
+    // plans found by o64_plan_tune, by (kind, SwiGLU?, M, N, K): used when the kind has no pin
+    std::map<std::array<int64_t, 5>, o64_plan_t> tuned;
     // host operands of a large product travel in row blocks on two side streams, so that the
     // copies in both directions overlap the kernels (created on first use)
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
@@ -249,7 +254,12 @@ extern "C" int o64_plan_set(o64_handle_t h, int kind, const o64_plan_t *plan) {
 }
 
 static void choose(o64_handle_t h, int kind, int epi, int64_t M, int64_t N, int64_t K, o64_plan_t *out) {
-    plan_choose(kind, epi, M, N, K, h->num_sms, h->has_pin[kind] ? &h->pins[kind] : nullptr, out);
+    const o64_plan_t *pin = h->has_pin[kind] ? &h->pins[kind] : nullptr;
+    if (!pin && !h->tuned.empty()) {
+        auto it = h->tuned.find({kind, epi == EPI_SWIGLU ? 1 : 0, M, N, K});
+        if (it != h->tuned.end()) pin = &it->second;
+    }
+    plan_choose(kind, epi, M, N, K, h->num_sms, pin, out);
 }
 
 extern "C" int o64_plan_get(o64_handle_t h, int kind, int64_t M, int64_t N, int64_t K, o64_plan_t *plan) {
@@ -828,6 +838,113 @@ extern "C" int o64_gemm_bf16_sharded(o64_handle_t h, int64_t M, int64_t N, int64
     int rc = o64_gemm_bf16(h, M, ns, K, A, lda, B_slab, ldb, 1, slab, ns, &mine, stream);
     if (rc) return rc;
     if (g > 1 && nccl().AllGather(slab, C, (size_t)M * ns, kNcclBfloat16, h->comm, s) != 0) return O64_ERR_NCCL;
+    return O64_OK;
+}
+
+// ---- measured plans -----------------------------------------------------------------------------
+// The reference scores its tile candidates with a model only (LOOP_MODEL::Evaluate,
+// osprey/be/lno/model.cxx:1289); here the candidates can also be run: every kernel shape that
+// exists for the kind is timed on zero-filled operands of the given extents and the fastest is
+// remembered for that shape.
+extern "C" int o64_plan_tune(o64_handle_t h, int kind, int swiglu, int64_t M, int64_t N, int64_t K, void *stream,
+                             o64_plan_t *best) {
+    if (!h || kind < O64_KIND_BF16 || kind > O64_KIND_S8 || M <= 0 || N <= 0 || K <= 0) return O64_ERR_RANK;
+    if (swiglu && kind != O64_KIND_BF16) return O64_ERR_DTYPE;
+    DeviceGuard g(h->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int elem = (kind == O64_KIND_BF16) ? 2 : 1;
+    const int out_elem = (kind == O64_KIND_S8) ? 4 : 2;
+    const int epi = swiglu ? EPI_SWIGLU : (kind == O64_KIND_BF16 ? EPI_BF16 : (kind == O64_KIND_FP8 ? EPI_SCALED_BF16 : EPI_S32));
+    void *A = nullptr, *B = nullptr, *B2 = nullptr, *C = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    auto release = [&]() {
+        if (A) cudaFree(A);
+        if (B) cudaFree(B);
+        if (B2) cudaFree(B2);
+        if (C) cudaFree(C);
+        if (e0) cudaEventDestroy(e0);
+        if (e1) cudaEventDestroy(e1);
+    };
+    const size_t a_bytes = (size_t)M * K * elem, b_bytes = (size_t)N * K * elem, c_bytes = (size_t)M * N * out_elem;
+    bool ok = cudaMalloc(&A, a_bytes) == cudaSuccess && cudaMalloc(&B, b_bytes) == cudaSuccess &&
+              cudaMalloc(&C, c_bytes) == cudaSuccess && (!swiglu || cudaMalloc(&B2, b_bytes) == cudaSuccess);
+    if (!ok) {
+        (void)cudaGetLastError();
+        release();
+        return O64_ERR_NOMEM;
+    }
+    ok = cudaMemsetAsync(A, 0, a_bytes, s) == cudaSuccess && cudaMemsetAsync(B, 0, b_bytes, s) == cudaSuccess &&
+         (!swiglu || cudaMemsetAsync(B2, 0, b_bytes, s) == cudaSuccess) && cudaEventCreate(&e0) == cudaSuccess &&
+         cudaEventCreate(&e1) == cudaSuccess;
+    if (!ok) {
+        (void)cudaGetLastError();
+        release();
+        return O64_ERR_CUDA;
+    }
+    // candidates: every tile kernel, the one-CTA kernel with and without its automatic K split,
+    // and for few rows the cluster kernel with every cluster size
+    std::vector<o64_plan_t> cand;
+    auto add = [&](int cg, int tm, int tn, int sk) {
+        o64_plan_t c;
+        memset(&c, 0, sizeof(c));
+        c.cta_group = cg;
+        c.tile_m = tm;
+        c.tile_n = tn;
+        c.split_k = sk;
+        cand.push_back(c);
+    };
+    add(1, 128, 256, 1);
+    add(1, 128, 128, 1);
+    add(2, 256, 256, 0);
+    if (!swiglu) {
+        add(1, 128, 256, 0);
+        add(1, 128, 128, 0);
+        add(2, 256, 128, 0);
+        if (M <= 128)
+            for (int sk = -1; sk >= -8; sk *= 2) add(0, 0, 0, sk);
+    }
+    add(2, 512, 256, 0);
+    const bool had_pin = h->has_pin[kind];
+    const o64_plan_t saved = h->pins[kind];
+    double best_ms = 1e300;
+    o64_plan_t best_pin;
+    memset(&best_pin, 0, sizeof(best_pin));
+    const int64_t ldb = swiglu ? N : K;
+    for (const o64_plan_t &c : cand) {
+        h->pins[kind] = c;
+        h->has_pin[kind] = true;
+        int rc = O64_OK;
+        float ms = 0.0f;
+        for (int it = 0; it < 7 && rc == O64_OK; ++it) {  // two warm-ups, five timed
+            if (it == 2 && cudaEventRecord(e0, s) != cudaSuccess) rc = O64_ERR_CUDA;
+            if (rc == O64_OK)
+                rc = umma_entry(h, kind, swiglu != 0, epi, M, N, K, A, K, B, B2, ldb, C, N, nullptr, nullptr, nullptr,
+                                O64_ACT_NONE, stream);
+        }
+        if (rc == O64_OK && (cudaEventRecord(e1, s) != cudaSuccess || cudaEventSynchronize(e1) != cudaSuccess ||
+                             cudaEventElapsedTime(&ms, e0, e1) != cudaSuccess))
+            rc = O64_ERR_CUDA;
+        (void)cudaGetLastError();
+        if (rc == O64_OK && ms / 5.0 < best_ms) {
+            best_ms = ms / 5.0;
+            best_pin = c;
+        }
+    }
+    h->pins[kind] = saved;
+    h->has_pin[kind] = had_pin;
+    release();
+    if (best_ms == 1e300) return O64_ERR_CUDA;
+    h->tuned[{kind, swiglu ? 1 : 0, M, N, K}] = best_pin;
+    if (best) {
+        plan_choose(kind, epi, M, N, K, h->num_sms, &best_pin, best);
+        best->predicted_ms = best_ms;  // measured, not modelled
+    }
+    return O64_OK;
+}
+
+extern "C" int o64_plan_tune_clear(o64_handle_t h) {
+    if (!h) return O64_ERR_RANK;
+    h->tuned.clear();
     return O64_OK;
 }
 

@@ -80,6 +80,17 @@ class Engine:
             setattr(p, k, v)
         check(self.lib.o64_plan_set(self._h, kind, ctypes.byref(p)), "o64_plan_set")
 
+    def plan_tune(self, kind, M, N, K, swiglu=False):
+        """Times every kernel shape for these extents on scratch operands and keeps the fastest for
+        later calls of the same shape; returns it (predicted_ms holds the measured time)."""
+        p = Plan()
+        s = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        check(self.lib.o64_plan_tune(self._h, kind, 1 if swiglu else 0, M, N, K, s, ctypes.byref(p)), "o64_plan_tune")
+        return p.as_dict()
+
+    def plan_tune_clear(self):
+        check(self.lib.o64_plan_tune_clear(self._h), "o64_plan_tune_clear")
+
     def last_status(self, stream=None):
         """Synchronises and returns (status, detail); status is 0 or ERR_TIMEOUT."""
         detail = ctypes.c_int(0)

@@ -276,3 +276,48 @@ def test_tall_host_operands_travel_in_row_blocks(eng, pinned):
     ref8 = oracle.gemm_fp8_scaled(bits8(A8), bits8(W8), sA.numpy(), sB.numpy(), b8.numpy())
     assert relmax(C8.float().numpy(), ref8) <= TOL_LOWP
     assert eng.last_status() == (o.OK, 0)
+
+
+def test_measured_plans(eng):
+    """o64_plan_tune times the kernel shapes for one problem size and the engine then uses the fastest
+    for that size (until a pin says otherwise); results stay correct."""
+    M, N, K = 768, 2048, 1024
+    A, B = _bf16_case(M, N, K, True, seed=41)
+    ref = oracle.gemm_bf16(bits16(A[:64]), bits16(B), transB=True)
+    Ad, Bd = A.to(DEV), B.to(DEV)
+
+    def time_default():
+        for _ in range(3):
+            eng.gemm_bf16(Ad, Bd, transB=True)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(40):
+            eng.gemm_bf16(Ad, Bd, transB=True)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 40
+
+    before = time_default()
+    try:
+        best = eng.plan_tune(o.KIND_BF16, M, N, K)
+        assert best["predicted_ms"] > 0 and best["tile_n"] in (128, 256)
+        got = eng.plan_get(o.KIND_BF16, M, N, K)
+        assert all(got[k] == best[k] for k in ("cta_group", "tile_m", "tile_n", "split_k"))
+        assert eng.plan_get(o.KIND_BF16, M + 128, N, K) is not None          # other sizes: the model as before
+        C = eng.gemm_bf16(Ad, Bd, transB=True)
+        assert relmax(C[:64].float().cpu().numpy(), ref) <= TOL_LOWP
+        after = time_default()
+        assert after <= before * 1.3, (before, after, best)   # a sanity bound: eager timing of a 25 us kernel is noisy
+        # a pin still wins over a measured plan
+        eng.plan_set(o.KIND_BF16, cta_group=1, tile_n=128, split_k=1)
+        assert eng.plan_get(o.KIND_BF16, M, N, K)["cta_group"] == 1
+        eng.plan_set(o.KIND_BF16)
+        # few rows: the cluster kernel's cluster sizes are among the candidates
+        few = eng.plan_tune(o.KIND_S8, 32, 4096, 4096)
+        Ai, Bi = o.workloads.c5_int8(32, 4096, 4096, seed=3)
+        assert np.array_equal(eng.gemm_s8(Ai.to(DEV), Bi.to(DEV)).cpu().numpy(), oracle.gemm_s8s8_s32(Ai.numpy(), Bi.numpy()))
+        assert few["predicted_ms"] > 0
+    finally:
+        eng.plan_set(o.KIND_BF16)
+        eng.plan_tune_clear()
+    assert eng.last_status() == (o.OK, 0)

@@ -29,10 +29,17 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else None
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream(t):
-    if t.is_cuda:
-        return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
-    return None
+    """torch's current stream on t's device as a cudaStream_t (the raw handle: building a
+    torch.cuda.Stream object per call costs more than the rest of the wrapper)."""
+    if not t.is_cuda:
+        return None
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(t.device.index))
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
 
 
 def _rowmajor(t, name):

@@ -158,12 +158,12 @@ def run_only(args, eng, o, torch, dev, time_steps, emit):
     """One secondary configuration by itself: a handful of launches of its kernels (what the ncu
     summaries under profiles/ were captured from) and one JSON line."""
     steps, warm = max(1, args.steps), args.warmup
-    if args.only == "c3":
-        # the vendor library on the same box, same buffers, same timing loop: context for `value`,
-        # not part of the product path (torch.matmul dispatches to cuBLAS)
-        if rank == 0 or world > 1:
-            t = time_steps(lambda: torch.matmul(Ad, Bd.t(), out=C), s2, w2)
-            ex["library_context_torch_matmul_bf16_8192"] = {"ms": t, "tflops": FLOPS / (t * 1e-3) / 1e12}
+    if args.only == "c1":
+        a1, b1, bias1 = (t_.to(dev) for t_ in o.workloads.c1_linear_f32())
+        y1 = torch.empty(512, 512, device=dev)
+        t = time_steps(lambda: eng.linear_f32(a1, b1, bias1, "relu", out=y1), steps, warm)
+        emit({"config": "c1_linear_f32_512", "us": t * 1e3, "gflops": 2 * 512 ** 3 / (t * 1e-3) / 1e9})
+    elif args.only == "c3":
         x, Wg, Wu, Wd = (t_.to(dev) for t_ in o.workloads.c3_swiglu())
         h = torch.empty(4096, 14336, dtype=torch.bfloat16, device=dev)
         out = torch.empty(4096, 4096, dtype=torch.bfloat16, device=dev)
@@ -240,7 +240,7 @@ def main():
     ap.add_argument("--impl", default="o64", choices=["o64", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary configurations")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--only", default=None, choices=["c3", "c4", "c5", "skinny"],
+    ap.add_argument("--only", default=None, choices=["c1", "c3", "c4", "c5", "skinny"],
                     help="run just one secondary configuration (few launches; for profiling) and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -900,7 +900,7 @@ extern "C" int o64_plan_tune(o64_handle_t h, int kind, int swiglu, int64_t M, in
         add(1, 128, 256, 0);
         add(1, 128, 128, 0);
         add(2, 256, 128, 0);
-        if (M <= 128)
+        if (M <= 512)  // few rows: one to four 128-row tiles per column block, K split over a cluster
             for (int sk = -1; sk >= -8; sk *= 2) add(0, 0, 0, sk);
     }
     add(2, 512, 256, 0);

@@ -188,14 +188,14 @@ void plan_choose(int kind, int epi, int64_t M, int64_t N, int64_t K, int num_sms
     // their partial sums through distributed shared memory.  Reported as split_k = -S.  A pinned
     // split_k of -1 asks for the kernel (S chosen), -2 / -4 / -8 fix S, >= 1 rules the kernel out.
     const bool skinny_pinned = pin.split_k < 0;
-    const bool skinny_fits = M <= 128 && epi != EPI_SWIGLU && pin.cta_group != 2 &&
+    const bool skinny_fits = M <= (skinny_pinned ? 512 : 128) && epi != EPI_SWIGLU && pin.cta_group != 2 &&
                              (pin.tile_m == 0 || pin.tile_m <= 128) && (pin.tile_n == 0 || pin.tile_n == 256);
     if (skinny_fits && (skinny_pinned || (pin.split_k == 0 && !pin.cta_group && !pin.tile_m && !pin.tile_n &&
                                           (double)N * (double)K * eb >= 2.0 * 1024 * 1024))) {
         const int a_rows = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
-        const int64_t tiles = (N + 255) / 256;
+        const int64_t tiles = ((M + 127) / 128) * ((N + 255) / 256);
         const int64_t kbs = (K + out->tile_k - 1) / out->tile_k;
-        int s = pin.split_k < -1 ? -pin.split_k : umma_skinny_split(N, K, eb, out->num_ctas);
+        int s = pin.split_k < -1 ? -pin.split_k : umma_skinny_split(M, N, K, eb, out->num_ctas);
         if (s > kbs) s = 1;
         out->cta_group = 1;
         out->tile_m = a_rows;

@@ -40,6 +40,7 @@ namespace {
 constexpr int kSkBlockN = 256;
 constexpr int kSkBBytes = kSkBlockN * kRowBytes;      // 32 KB of weight per stage
 constexpr int kSkMaxStages = 6;
+constexpr int kSkMaxRows = 512;  // up to four 128-row tiles per 256-column block
 constexpr int kSkRingBytes = 6 * (kSkBBytes + 16 * kRowBytes);  // 6 stages at a_rows = 16
 constexpr int kSkStagingOffset = kSkRingBytes;                   // epilogue patches, 4 KB per warp
 constexpr int kSkBarOffset = kSkStagingOffset + kEpiStagingBytes;
@@ -56,15 +57,16 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint4 v) {
                  : "memory");
 }
 
-// Sends 32 accumulator rows (this warp's TMEM lane quarter), 32-column chunks c_begin .. c_end-1,
+// Sends 32 accumulator rows (this warp's TMEM lane quarter; row0 and `rows` count inside the
+// tile), 32-column chunks c_begin .. c_end-1,
 // to the CTAs of the cluster: columns c*slice .. of the tile go to CTA c, into slot `rank` of its
-// receive area ([S][M][slice] 4-byte sums at `recv`, the same shared-memory offset in every
+// receive area ([S][rows][slice] 4-byte sums at `recv`, the same shared-memory offset in every
 // CTA).  Through the swizzled patch, so that a store instruction writes four full 128-byte row
 // segments (measured: storing each thread's own row straight from its registers, 32 rows per
 // instruction, takes twice as long for 128 rows); the load of the next chunk is in flight while
 // this one is sent.
-__device__ __forceinline__ void scatter_rows(const UmmaParams &p, int row0, uint32_t t_row, uint8_t *staging,
-                                             uint32_t recv, int rank, int slice, int c_begin, int c_end) {
+__device__ __forceinline__ void scatter_rows(int rows, int row0, uint32_t t_row, uint8_t *staging, uint32_t recv,
+                                             int rank, int slice, int c_begin, int c_end) {
     const int lane = threadIdx.x & 31;
     uint4 *patch = reinterpret_cast<uint4 *>(staging);
     const int sw = lane & 7;
@@ -81,7 +83,7 @@ __device__ __forceinline__ void scatter_rows(const UmmaParams &p, int row0, uint
             const int r = 4 * r4 + (lane >> 3);
             const uint4 val = patch[r * 8 + ((lane & 7) ^ (r & 7))];
             const int grow = row0 + r;
-            if (grow < p.M) st_cluster_v4(base + (uint32_t)(((rank * p.M + grow) * slice + cin) * 4), val);
+            if (grow < rows) st_cluster_v4(base + (uint32_t)(((rank * rows + grow) * slice + cin) * 4), val);
         }
         __syncwarp();
     };
@@ -106,8 +108,8 @@ __device__ __forceinline__ void scatter_rows(const UmmaParams &p, int row0, uint
 // Adds the S slices received for this CTA's columns, applies the epilogue and writes C.
 // All threads of the CTA; four columns per thread.
 template <int EPI, int ACT>
-__device__ __forceinline__ void gather_store(const UmmaParams &p, const uint8_t *recv, int n0, int rank, int S,
-                                             int slice, int t) {
+__device__ __forceinline__ void gather_store(const UmmaParams &p, const uint8_t *recv, int m_base, int rows, int n0,
+                                             int rank, int S, int slice, int t) {
     const int tpr = slice / 4;  // threads per row
     const int c4 = (t % tpr) * 4;
     const int col = n0 + rank * slice + c4;
@@ -125,11 +127,11 @@ __device__ __forceinline__ void gather_store(const UmmaParams &p, const uint8_t 
             }
         }
     }
-    for (int m = t / tpr; m < p.M; m += kThreads / tpr) {
+    for (int m = t / tpr; m < rows; m += kThreads / tpr) {
         const int pitch = slice;
         uint4 acc = *reinterpret_cast<const uint4 *>(recv + (size_t)((m * pitch) + c4) * 4);
         for (int src = 1; src < S; ++src) {
-            const uint4 w = *reinterpret_cast<const uint4 *>(recv + (size_t)(((src * p.M + m) * pitch) + c4) * 4);
+            const uint4 w = *reinterpret_cast<const uint4 *>(recv + (size_t)(((src * rows + m) * pitch) + c4) * 4);
             if constexpr (EPI == EPI_S32) {
                 acc.x += w.x; acc.y += w.y; acc.z += w.z; acc.w += w.w;  // two's complement: exact
             } else {
@@ -141,7 +143,7 @@ __device__ __forceinline__ void gather_store(const UmmaParams &p, const uint8_t 
         }
         const uint32_t w[4] = {acc.x, acc.y, acc.z, acc.w};
         if constexpr (EPI == EPI_S32) {
-            int32_t *dst = reinterpret_cast<int32_t *>(p.C) + (long long)m * p.ldc + col;
+            int32_t *dst = reinterpret_cast<int32_t *>(p.C) + (long long)(m_base + m) * p.ldc + col;
             if (ncols == 4 && p.vec_ok) {
                 *reinterpret_cast<uint4 *>(dst) = acc;
             } else {
@@ -153,7 +155,7 @@ __device__ __forceinline__ void gather_store(const UmmaParams &p, const uint8_t 
             float x[4];
             float sa = 1.0f;
             if constexpr (EPI == EPI_SCALED_BF16) {
-                if (p.scale_a) sa = __ldg(p.scale_a + m);
+                if (p.scale_a) sa = __ldg(p.scale_a + m_base + m);
             }
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -166,7 +168,7 @@ __device__ __forceinline__ void gather_store(const UmmaParams &p, const uint8_t 
                     x[e] = act_fixed<ACT>(x[e]);
                 }
             }
-            __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.C) + (long long)m * p.ldc + col;
+            __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.C) + (long long)(m_base + m) * p.ldc + col;
             if (ncols == 4 && p.vec_ok) {
                 *reinterpret_cast<uint2 *>(dst) = make_uint2(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]));
             } else {
@@ -179,18 +181,18 @@ __device__ __forceinline__ void gather_store(const UmmaParams &p, const uint8_t 
 }
 
 template <int EPI>
-__device__ __forceinline__ void gather_store_dispatch(const UmmaParams &p, const uint8_t *recv, int n0, int rank,
-                                                      int S, int slice, int t) {
+__device__ __forceinline__ void gather_store_dispatch(const UmmaParams &p, const uint8_t *recv, int m_base, int rows,
+                                                      int n0, int rank, int S, int slice, int t) {
     if constexpr (EPI == EPI_BF16) {
         switch (p.act) {  // uniform: one branch per tile
-        case O64_ACT_RELU: gather_store<EPI, O64_ACT_RELU>(p, recv, n0, rank, S, slice, t); break;
-        case O64_ACT_GELU_TANH: gather_store<EPI, O64_ACT_GELU_TANH>(p, recv, n0, rank, S, slice, t); break;
-        case O64_ACT_GELU_ERF: gather_store<EPI, O64_ACT_GELU_ERF>(p, recv, n0, rank, S, slice, t); break;
-        case O64_ACT_SILU: gather_store<EPI, O64_ACT_SILU>(p, recv, n0, rank, S, slice, t); break;
-        default: gather_store<EPI, O64_ACT_NONE>(p, recv, n0, rank, S, slice, t); break;
+        case O64_ACT_RELU: gather_store<EPI, O64_ACT_RELU>(p, recv, m_base, rows, n0, rank, S, slice, t); break;
+        case O64_ACT_GELU_TANH: gather_store<EPI, O64_ACT_GELU_TANH>(p, recv, m_base, rows, n0, rank, S, slice, t); break;
+        case O64_ACT_GELU_ERF: gather_store<EPI, O64_ACT_GELU_ERF>(p, recv, m_base, rows, n0, rank, S, slice, t); break;
+        case O64_ACT_SILU: gather_store<EPI, O64_ACT_SILU>(p, recv, m_base, rows, n0, rank, S, slice, t); break;
+        default: gather_store<EPI, O64_ACT_NONE>(p, recv, m_base, rows, n0, rank, S, slice, t); break;
         }
     } else {
-        gather_store<EPI, O64_ACT_NONE>(p, recv, n0, rank, S, slice, t);
+        gather_store<EPI, O64_ACT_NONE>(p, recv, m_base, rows, n0, rank, S, slice, t);
     }
 }
 
@@ -226,8 +228,11 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
     const uint32_t stage_bytes = kSkBBytes + a_bytes;  // B first: the MMA's reads past the A box stay inside the allocation
     const int S = p.sk_split;
     const int rank = (int)cluster_ctarank();
-    const int tile = blockIdx.x / S;
-    const int n0 = tile * kSkBlockN;
+    const int tile = blockIdx.x / S;             // tiles of one 256-column block are neighbours: they share B in L2
+    const int mt = tile % p.num_m_tiles;
+    const int m_base = mt * kBlockM;
+    const int rows = min(kBlockM, p.M - m_base);  // rows of A this tile really has
+    const int n0 = (tile / p.num_m_tiles) * kSkBlockN;
     const int kbs = p.num_k_blocks;
     const int kb_begin = (int)((long long)kbs * rank / S);
     const int kb_end = (int)((long long)kbs * (rank + 1) / S);
@@ -269,7 +274,7 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
             const uint32_t a_dst = b_dst + kSkBBytes;
             if (leader) {
                 mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
-                tma_load_2d(a_dst, &tm_a, kb * kBlockK, 0, full_bar(stage));
+                tma_load_2d(a_dst, &tm_a, kb * kBlockK, m_base, full_bar(stage));
                 if constexpr (!B_KN) {
                     tma_load_2d_hint(b_dst, &tm_b, kb * kBlockK, n0, full_bar(stage), stream_once);
                 } else {
@@ -331,8 +336,8 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
         if (dbg && warp == 2 && lane == 0) dbg[4] = globaltimer_ns();
         if (S == 1 && ok) {
             const int quarter = warp & 3;
-            if (quarter * 32 < p.M)
-                epilogue_tile<EPI, kSkBlockN>(p, quarter * 32, n0, tmem_base + (uint32_t(quarter * 32) << 16),
+            if (quarter * 32 < rows)
+                epilogue_tile<EPI, kSkBlockN>(p, m_base + quarter * 32, n0, tmem_base + (uint32_t(quarter * 32) << 16),
                                               smem_gen + kSkStagingOffset + quarter * kEpiStagingBytesPerWarp);
         }
         tc_fence_before();
@@ -357,14 +362,14 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
             uint8_t *patch = warp >= 2 ? smem_gen + kSkStagingOffset + quarter * kEpiStagingBytesPerWarp
                                        : smem_gen + kSkRingBytes - (2 - warp) * kEpiStagingBytesPerWarp;
             tc_fence_after();
-            if (quarter * 32 < p.M)
-                scatter_rows(p, quarter * 32, tmem_base + (uint32_t(quarter * 32) << 16), patch, smem_base, rank,
+            if (quarter * 32 < rows)
+                scatter_rows(rows, quarter * 32, tmem_base + (uint32_t(quarter * 32) << 16), patch, smem_base, rank,
                              slice, c_begin, c_end);
             tc_fence_before();
         }
         cluster_sync_all();  // the slices sent to this CTA have arrived
         if (dbg && threadIdx.x == 64) dbg[6] = globaltimer_ns();
-        if (good) gather_store_dispatch<EPI>(p, smem_gen, n0, rank, S, slice, (int)threadIdx.x);
+        if (good) gather_store_dispatch<EPI>(p, smem_gen, m_base, rows, n0, rank, S, slice, (int)threadIdx.x);
     }
     if (dbg && threadIdx.x == 64) dbg[7] = globaltimer_ns();
 
@@ -437,8 +442,8 @@ static int launch_skinny(const CUtensorMap &ta, const CUtensorMap &tb, UmmaParam
 // K slices per tile: the largest cluster size that keeps tiles * S within the CTAs the plan
 // allows and leaves every slice at least one K block.  Clusters of 8 only for 8 tiles or fewer:
 // measured, sixteen clusters of 8 CTAs with this much shared memory do not all fit at once.
-int umma_skinny_split(int64_t N, int64_t K, int elem, int num_ctas) {
-    const int64_t tiles = (N + kSkBlockN - 1) / kSkBlockN;
+int umma_skinny_split(int64_t M, int64_t N, int64_t K, int elem, int num_ctas) {
+    const int64_t tiles = ((M + kBlockM - 1) / kBlockM) * ((N + kSkBlockN - 1) / kSkBlockN);
     const int64_t kbs = (K + kRowBytes / elem - 1) / (kRowBytes / elem);
     int s = tiles <= 8 ? 8 : 4;
     while (s > 1 && (tiles * s > num_ctas || s > kbs)) s /= 2;
@@ -446,10 +451,10 @@ int umma_skinny_split(int64_t N, int64_t K, int elem, int num_ctas) {
 }
 
 int umma_launch_skinny(const UmmaCall &c, UmmaParams p) {
-    if (c.M > 128 || c.epi == EPI_SWIGLU || c.n_peers > 0) return O64_ERR_DTYPE;
+    if (c.M > kSkMaxRows || c.epi == EPI_SWIGLU || c.n_peers > 0) return O64_ERR_DTYPE;
     const int elem = (c.kind == O64_KIND_BF16) ? 2 : 1;
     const int block_k = kRowBytes / elem;
-    const int a_rows = c.M <= 16 ? 16 : (c.M <= 32 ? 32 : (c.M <= 64 ? 64 : 128));
+    const int a_rows = c.M <= 16 ? 16 : (c.M <= 32 ? 32 : (c.M <= 64 ? 64 : 128));  // 128 per tile when M > 128
     CUtensorMap ta, tb;
     int rc = encode_2d(&ta, c.kind, c.A, c.M, c.K, c.lda, block_k, a_rows);
     if (rc) return rc;
@@ -458,7 +463,7 @@ int umma_launch_skinny(const UmmaCall &c, UmmaParams p) {
     else
         rc = encode_2d(&tb, c.kind, c.B, c.K, c.N, c.ldb, 64, block_k);
     if (rc) return rc;
-    p.num_m_tiles = 1;
+    p.num_m_tiles = (int)((c.M + kBlockM - 1) / kBlockM);
     p.num_n_tiles = (int)((c.N + kSkBlockN - 1) / kSkBlockN);
     p.split_k = 1;
     p.kb_per_split = p.num_k_blocks;
@@ -471,9 +476,9 @@ int umma_launch_skinny(const UmmaCall &c, UmmaParams p) {
     if (p.sk_stages > kSkMaxStages) p.sk_stages = kSkMaxStages;
     const int ctas = c.plan.num_ctas > 0 ? c.plan.num_ctas : 148;
     // the plan's split_k is -S; -1 also stands for "choose"
-    int want = c.plan.split_k < -1 ? -c.plan.split_k : umma_skinny_split(c.N, c.K, elem, ctas);
+    int want = c.plan.split_k < -1 ? -c.plan.split_k : umma_skinny_split(c.M, c.N, c.K, elem, ctas);
     if (want > p.num_k_blocks) want = 1;
-    const int tiles = p.num_n_tiles;
+    const int tiles = p.num_m_tiles * p.num_n_tiles;
 
     // O64_TRACE=pipe: every CTA leaves time stamps; the launch is then synchronous and prints where
     // the time went (a tuning aid, off by default)

@@ -129,3 +129,29 @@ def test_few_rows_full_size_weight_against_the_reference_kernel(eng):
     ref = oracle.gemm_bf16(bits16(A[:4]), bits16(B), transB=True)
     assert relmax(C[:4].float().cpu().numpy(), ref) <= TOL_LOWP
     assert eng.last_status() == (o.OK, 0)
+
+
+@pytest.mark.parametrize("shape", [(129, 1024, 1024), (200, 2048, 2056), (256, 1304, 1024), (300, 512, 4096), (512, 768, 512)])
+def test_several_row_tiles_per_column_block(eng, shape):
+    """128 < M <= 512 when asked for: up to four 128-row tiles share each 256-column block of the
+    weight; every (row tile, column block) has its own cluster."""
+    M, N, K = shape
+    A, B = _bf16_case(M, N, K, True, seed=13)
+    bias = torch.randn(N, generator=torch.Generator().manual_seed(2))
+    ref = oracle.gemm_bf16(bits16(A), bits16(B), bias=bias.numpy(), act=oracle.ACT_RELU, transB=True)
+    Ai, Bi = o.workloads.c5_int8(M, N, K, seed=M)
+    refi = oracle.gemm_s8s8_s32(Ai.numpy(), Bi.numpy())
+    try:
+        for sk in (-1, -2, -4):
+            eng.plan_set(o.KIND_BF16, split_k=sk)
+            eng.plan_set(o.KIND_S8, split_k=sk)
+            plan = eng.plan_get(o.KIND_BF16, M, N, K)
+            assert plan["split_k"] < 0 and plan["tile_m"] == 128
+            C = eng.gemm_bf16(A.to(DEV), B.to(DEV), transB=True, bias=bias.to(DEV), act="relu")
+            assert relmax(C.float().cpu().numpy(), ref) <= TOL_LOWP, sk
+            Ci = eng.gemm_s8(Ai.to(DEV), Bi.to(DEV))
+            assert np.array_equal(Ci.cpu().numpy(), refi), sk
+    finally:
+        eng.plan_set(o.KIND_BF16)
+        eng.plan_set(o.KIND_S8)
+    assert eng.last_status() == (o.OK, 0)

@@ -135,7 +135,7 @@ int o64_plan_set(o64_handle_t h, int kind, const o64_plan_t *plan);
  * (may be NULL) and O64_LNO applied.  `swiglu` != 0 scores the fused gate/up GEMM. */
 int o64_plan_model(int kind, int swiglu, int64_t M, int64_t N, int64_t K, int num_sms,
                    const o64_plan_t *pin, o64_plan_t *plan);
-/* Measures instead of modelling: runs every kernel shape that exists for `kind` on zero-filled
+/* Measures instead of modelling: runs every kernel shape that exists for `kind` on pseudo-random
  * scratch operands of these extents (A [M,K], B [N,K]; SwiGLU: two [K,N] weights), remembers the
  * fastest for (kind, swiglu, M, N, K) and uses it from then on whenever the kind has no pin.
  * Allocates and frees its scratch, synchronises `stream`; *best (may be NULL) receives the plan

@@ -844,7 +844,7 @@ extern "C" int o64_gemm_bf16_sharded(o64_handle_t h, int64_t M, int64_t N, int64
 // ---- measured plans -----------------------------------------------------------------------------
 // The reference scores its tile candidates with a model only (LOOP_MODEL::Evaluate,
 // osprey/be/lno/model.cxx:1289); here the candidates can also be run: every kernel shape that
-// exists for the kind is timed on zero-filled operands of the given extents and the fastest is
+// exists for the kind is timed on pseudo-random operands of the given extents and the fastest is
 // remembered for that shape.
 extern "C" int o64_plan_tune(o64_handle_t h, int kind, int swiglu, int64_t M, int64_t N, int64_t K, void *stream,
                              o64_plan_t *best) {
@@ -873,8 +873,10 @@ extern "C" int o64_plan_tune(o64_handle_t h, int kind, int swiglu, int64_t M, in
         release();
         return O64_ERR_NOMEM;
     }
-    ok = cudaMemsetAsync(A, 0, a_bytes, s) == cudaSuccess && cudaMemsetAsync(B, 0, b_bytes, s) == cudaSuccess &&
-         (!swiglu || cudaMemsetAsync(B2, 0, b_bytes, s) == cudaSuccess) && cudaEventCreate(&e0) == cudaSuccess &&
+    // pseudo-random operands: with zeros the tensor cores toggle no bits, draw far less power and run at
+    // clocks real data never sees, which ranks the candidates differently
+    ok = fill_pattern(A, a_bytes, kind, s) == O64_OK && fill_pattern(B, b_bytes, kind, s) == O64_OK &&
+         (!swiglu || fill_pattern(B2, b_bytes, kind, s) == O64_OK) && cudaEventCreate(&e0) == cudaSuccess &&
          cudaEventCreate(&e1) == cudaSuccess;
     if (!ok) {
         (void)cudaGetLastError();

@@ -545,6 +545,35 @@ int finalize_partial_bf16(const float *partial, int64_t M, int64_t N, const floa
 }
 
 // ------------------------------------------------------------------------------------------
+// operand pattern for timing runs: pseudo-random finite values (zero-filled operands toggle no
+// bits in the tensor cores, draw far less power and run at clocks real data never sees)
+// ------------------------------------------------------------------------------------------
+__global__ void fill_pattern_kernel(uint32_t *p, size_t words, int kind, uint32_t seed) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < words; i += (size_t)gridDim.x * blockDim.x) {
+        uint32_t x = (uint32_t)i * 2654435761u + seed;
+        x ^= x >> 15;
+        x *= 2246822519u;
+        x ^= x >> 13;
+        x *= 3266489917u;
+        x ^= x >> 16;
+        if (kind == O64_KIND_BF16) {
+            // two bf16 values in [1/128, 1/64) with random sign and mantissa
+            x = (x & 0x807f807fu) | 0x3c003c00u;
+        } else if (kind == O64_KIND_FP8) {
+            x &= 0xf7f7f7f7u;  // e4m3: exponent below the NaN code
+        }
+        p[i] = x;
+    }
+}
+
+int fill_pattern(void *p, size_t bytes, int kind, cudaStream_t stream) {
+    const size_t words = bytes / 4;
+    if (!words) return O64_OK;
+    fill_pattern_kernel<<<1184, 256, 0, stream>>>(static_cast<uint32_t *>(p), words, kind, 0x9e3779b9u);
+    return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
+}
+
+// ------------------------------------------------------------------------------------------
 // slab permute: the all-gather delivers [g][M][N/g]; callers that want row-major [M,N] get it
 // through this copy (16-byte vectors when the slab width allows).
 // ------------------------------------------------------------------------------------------

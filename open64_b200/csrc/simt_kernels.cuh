@@ -65,6 +65,9 @@ int generic_gemvx(int64_t M, int64_t N, T alpha, const T *A, int64_t a1, int64_t
 template <typename T>
 int generic_scale(int64_t M, int64_t N, T beta, T *C, int64_t c1, int64_t c2, cudaStream_t s);
 
+// Fills a buffer with pseudo-random finite values of the kind (bf16 / e4m3 / int8): operands for timing runs.
+int fill_pattern(void *p, size_t bytes, int kind, cudaStream_t stream);
+
 // dst[m][r*ncols + j] = src[r][m][j] for r < nslabs (int32 elements).
 int permute_slabs_s32(const int32_t *src, int32_t *dst, int64_t M, int64_t ncols, int nslabs,
                       int64_t ld_dst, cudaStream_t stream);

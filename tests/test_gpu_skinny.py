@@ -19,7 +19,7 @@ ACTS = {"none": oracle.ACT_NONE, "relu": oracle.ACT_RELU, "gelu_tanh": oracle.AC
 # (8 tiles or fewer: 8 CTAs per tile ... more than 74 tiles: one)
 SHAPES = [(1, 2048, 1024), (7, 1000, 2056), (16, 4096, 1024), (17, 520, 4104), (33, 768, 2048),
           (64, 8192, 512), (100, 1304, 1096), (128, 2048, 2048), (5, 256, 8192), (20, 19200, 128),
-          (128, 9000, 512)]
+          (128, 9000, 512), (3, 72, 16384), (9, 8, 131072)]
 
 
 def _bf16_case(M, N, K, transB, seed=0):

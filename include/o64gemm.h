@@ -330,6 +330,35 @@ void _i4jgemmx__(const int *m, const int *n, const int *k, const int64_t *alpha,
 void _jgemmx__(const int *m, const int *n, const int *k, const int64_t *alpha, const int64_t *a,
                const int *inc1a, const int *inc2a, const int64_t *b, const int *inc1b, const int *inc2b,
                const int64_t *beta, int64_t *c, const int *inc1c, const int *inc2c);
+/* The mixed instances with a REAL result (s4sgemmx.f; i1s4gemmx.f ... js4gemmx.f; i1sgemmx.f ... jsgemmx.f):
+ * A of the narrower real or of an integer kind, converted to the kind of B, C, alpha and beta. */
+void _s4sgemmx__(const int *m, const int *n, const int *k, const double *alpha, const float *a,
+                 const int *inc1a, const int *inc2a, const double *b, const int *inc1b, const int *inc2b,
+                 const double *beta, double *c, const int *inc1c, const int *inc2c);
+void _i1s4gemmx__(const int *m, const int *n, const int *k, const float *alpha, const int8_t *a,
+                  const int *inc1a, const int *inc2a, const float *b, const int *inc1b, const int *inc2b,
+                  const float *beta, float *c, const int *inc1c, const int *inc2c);
+void _i2s4gemmx__(const int *m, const int *n, const int *k, const float *alpha, const int16_t *a,
+                  const int *inc1a, const int *inc2a, const float *b, const int *inc1b, const int *inc2b,
+                  const float *beta, float *c, const int *inc1c, const int *inc2c);
+void _i4s4gemmx__(const int *m, const int *n, const int *k, const float *alpha, const int32_t *a,
+                  const int *inc1a, const int *inc2a, const float *b, const int *inc1b, const int *inc2b,
+                  const float *beta, float *c, const int *inc1c, const int *inc2c);
+void _js4gemmx__(const int *m, const int *n, const int *k, const float *alpha, const int64_t *a,
+                 const int *inc1a, const int *inc2a, const float *b, const int *inc1b, const int *inc2b,
+                 const float *beta, float *c, const int *inc1c, const int *inc2c);
+void _i1sgemmx__(const int *m, const int *n, const int *k, const double *alpha, const int8_t *a,
+                 const int *inc1a, const int *inc2a, const double *b, const int *inc1b, const int *inc2b,
+                 const double *beta, double *c, const int *inc1c, const int *inc2c);
+void _i2sgemmx__(const int *m, const int *n, const int *k, const double *alpha, const int16_t *a,
+                 const int *inc1a, const int *inc2a, const double *b, const int *inc1b, const int *inc2b,
+                 const double *beta, double *c, const int *inc1c, const int *inc2c);
+void _i4sgemmx__(const int *m, const int *n, const int *k, const double *alpha, const int32_t *a,
+                 const int *inc1a, const int *inc2a, const double *b, const int *inc1b, const int *inc2b,
+                 const double *beta, double *c, const int *inc1c, const int *inc2c);
+void _jsgemmx__(const int *m, const int *n, const int *k, const double *alpha, const int64_t *a,
+                const int *inc1a, const int *inc2a, const double *b, const int *inc1b, const int *inc2b,
+                const double *beta, double *c, const int *inc1c, const int *inc2c);
 /* MATMUL on REAL*8 arrays (matmul_ss@.c:78-125) and on every pair of integer kinds
  * (matmul_i1i1.c ... matmul_jj@.c; result kind = the wider operand kind).  The integer entry
  * points send rank-1 operands through the matrix kernel with (m,n,k) = (n1a,1,n2a) or
@@ -352,6 +381,27 @@ void _MATMUL_JI1(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *
 void _MATMUL_JI2(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
 void _MATMUL_JI4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
 void _MATMUL_JJ(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+/* MATMUL of a REAL*4 by a REAL*8 array and of integer by real arrays, either way round (matmul_s4s.c,
+ * matmul_ss4.c, matmul_i4s4.c, matmul_s4i4.c, ...): result of the real (wider) kind; when MATRIX_B is the
+ * integer or narrower operand the product is formed as C' = B'A' (matmul_ss4.c:87-89, matmul_s4i4.c:85-87). */
+void _MATMUL_S4S(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_SS4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I1S4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_S4I1(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I1S(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_SI1(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I2S4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_S4I2(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I2S(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_SI2(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I4S4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_S4I4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I4S(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_SI4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_JS4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_S4J(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_JS(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_SJ(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
 
 /* Status of the last compat call on this thread (the Fortran entry points return void). */
 int o64_compat_last_status(void);

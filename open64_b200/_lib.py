@@ -30,6 +30,8 @@ EXPORTS = [
     "_MATMUL_I1I1", "_MATMUL_I1I2", "_MATMUL_I1I4", "_MATMUL_I1J", "_MATMUL_I2I1", "_MATMUL_I2I2", "_MATMUL_I2I4",
     "_MATMUL_I2J", "_MATMUL_I4I1", "_MATMUL_I4I2", "_MATMUL_I4I4", "_MATMUL_I4J", "_MATMUL_JI1", "_MATMUL_JI2",
     "_MATMUL_JI4", "_MATMUL_JJ",
+    "_s4sgemmx__", "_i1s4gemmx__", "_i2s4gemmx__", "_i4s4gemmx__", "_js4gemmx__", "_i1sgemmx__", "_i2sgemmx__", "_i4sgemmx__", "_jsgemmx__",
+    "_MATMUL_S4S", "_MATMUL_SS4", "_MATMUL_I1S4", "_MATMUL_S4I1", "_MATMUL_I1S", "_MATMUL_SI1", "_MATMUL_I2S4", "_MATMUL_S4I2", "_MATMUL_I2S", "_MATMUL_SI2", "_MATMUL_I4S4", "_MATMUL_S4I4", "_MATMUL_I4S", "_MATMUL_SI4", "_MATMUL_JS4", "_MATMUL_S4J", "_MATMUL_JS", "_MATMUL_SJ",
 ]
 
 

@@ -1008,7 +1008,7 @@ static int xgemmx_impl(int M, int N, int K, T alpha, const TA *A, int64_t a1, in
     }
     if (!C) return O64_ERR_RANK;
     if ((rc = stage_out_begin(h, 3, C, strided_span(M, N, c1, c2) * sizeof(T), true, s, &out))) return rc;
-    if constexpr (std::is_same<T, float>::value) {
+    if constexpr (std::is_same<T, float>::value && std::is_same<TA, float>::value) {
         if (only_scale) {
             rc = simt_scale_f32(M, N, beta_eff, (float *)out.dev, c1, c2, s);
         } else {
@@ -1058,6 +1058,15 @@ O64_XGEMMX_ENTRY(_i2jgemmx__, int16_t, int64_t)
 O64_XGEMMX_ENTRY(_i4gemmx__, int32_t, int32_t)
 O64_XGEMMX_ENTRY(_i4jgemmx__, int32_t, int64_t)
 O64_XGEMMX_ENTRY(_jgemmx__, int64_t, int64_t)
+O64_XGEMMX_ENTRY(_s4sgemmx__, float, double)
+O64_XGEMMX_ENTRY(_i1s4gemmx__, int8_t, float)
+O64_XGEMMX_ENTRY(_i2s4gemmx__, int16_t, float)
+O64_XGEMMX_ENTRY(_i4s4gemmx__, int32_t, float)
+O64_XGEMMX_ENTRY(_js4gemmx__, int64_t, float)
+O64_XGEMMX_ENTRY(_i1sgemmx__, int8_t, double)
+O64_XGEMMX_ENTRY(_i2sgemmx__, int16_t, double)
+O64_XGEMMX_ENTRY(_i4sgemmx__, int32_t, double)
+O64_XGEMMX_ENTRY(_jsgemmx__, int64_t, double)
 #undef O64_XGEMMX_ENTRY
 
 template <typename T>
@@ -1273,4 +1282,23 @@ O64_MATMUL_ENTRY(_MATMUL_JI1, int8_t, int64_t, false, true)
 O64_MATMUL_ENTRY(_MATMUL_JI2, int16_t, int64_t, false, true)
 O64_MATMUL_ENTRY(_MATMUL_JI4, int32_t, int64_t, false, true)
 O64_MATMUL_ENTRY(_MATMUL_JJ, int64_t, int64_t, false, false)
+// mixed kinds with a REAL result: the narrower or integer operand is the kernel's A
+O64_MATMUL_ENTRY(_MATMUL_S4S, float, double, false, false)
+O64_MATMUL_ENTRY(_MATMUL_SS4, float, double, false, true)
+O64_MATMUL_ENTRY(_MATMUL_I1S4, int8_t, float, false, false)
+O64_MATMUL_ENTRY(_MATMUL_S4I1, int8_t, float, false, true)
+O64_MATMUL_ENTRY(_MATMUL_I1S, int8_t, double, false, false)
+O64_MATMUL_ENTRY(_MATMUL_SI1, int8_t, double, false, true)
+O64_MATMUL_ENTRY(_MATMUL_I2S4, int16_t, float, false, false)
+O64_MATMUL_ENTRY(_MATMUL_S4I2, int16_t, float, false, true)
+O64_MATMUL_ENTRY(_MATMUL_I2S, int16_t, double, false, false)
+O64_MATMUL_ENTRY(_MATMUL_SI2, int16_t, double, false, true)
+O64_MATMUL_ENTRY(_MATMUL_I4S4, int32_t, float, false, false)
+O64_MATMUL_ENTRY(_MATMUL_S4I4, int32_t, float, false, true)
+O64_MATMUL_ENTRY(_MATMUL_I4S, int32_t, double, false, false)
+O64_MATMUL_ENTRY(_MATMUL_SI4, int32_t, double, false, true)
+O64_MATMUL_ENTRY(_MATMUL_JS4, int64_t, float, false, false)
+O64_MATMUL_ENTRY(_MATMUL_S4J, int64_t, float, false, true)
+O64_MATMUL_ENTRY(_MATMUL_JS, int64_t, double, false, false)
+O64_MATMUL_ENTRY(_MATMUL_SJ, int64_t, double, false, true)
 #undef O64_MATMUL_ENTRY

@@ -8,15 +8,19 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <type_traits>
 
 #include "../../include/o64gemm.h"
 #include "simt_kernels.cuh"
 
 namespace o64 {
 
-// A's element in the kind of C: integers are sign-extended, then carried on the unsigned type.
-template <typename T, typename TA> __device__ __forceinline__ T widen(TA a) { return (T)(long long)a; }
-template <> __device__ __forceinline__ double widen<double, double>(double a) { return a; }
+// A's element in the kind of C: integers are sign-extended, then carried on the unsigned type;
+// with a REAL result (the mixed kernels such as _i4s4gemmx__, _s4sgemmx__) A is converted to it.
+template <typename T, typename TA> __device__ __forceinline__ T widen(TA a) {
+    if constexpr (std::is_floating_point<T>::value) return (T)a;  // REAL results: plain conversion
+    else return (T)(long long)a;
+}
 
 // Product in the kind T.  8- and 16-bit operands are multiplied as unsigned 32-bit values: the
 // usual promotion to (signed) int would overflow for 16-bit factors.
@@ -144,6 +148,16 @@ O64_INSTANTIATE_GEMMX(int16_t, uint64_t)
 O64_INSTANTIATE_GEMMX(int32_t, uint32_t)
 O64_INSTANTIATE_GEMMX(int32_t, uint64_t)
 O64_INSTANTIATE_GEMMX(int64_t, uint64_t)
+O64_INSTANTIATE_GEMMX(float, double)
+O64_INSTANTIATE_GEMMX(int8_t, float)
+O64_INSTANTIATE_GEMMX(int16_t, float)
+O64_INSTANTIATE_GEMMX(int32_t, float)
+O64_INSTANTIATE_GEMMX(int64_t, float)
+O64_INSTANTIATE_GEMMX(int8_t, double)
+O64_INSTANTIATE_GEMMX(int16_t, double)
+O64_INSTANTIATE_GEMMX(int32_t, double)
+O64_INSTANTIATE_GEMMX(int64_t, double)
+O64_INSTANTIATE_SCALE(float)
 O64_INSTANTIATE_SCALE(double)
 O64_INSTANTIATE_SCALE(uint8_t)
 O64_INSTANTIATE_SCALE(uint16_t)

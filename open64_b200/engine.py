@@ -303,10 +303,12 @@ class Engine:
 
     def xgemmx(self, kind, m, n, k, alpha, a, inc1a, inc2a, b, inc1b, inc2b, beta, c, inc1c, inc2c):
         """The strided kernel `_<kind>gemmx__` of the runtime, in place on c.  kind: "s4", "s", "i1",
-        "i2", "i4", "j", or a mixed integer pair "i1i2", "i1i4", "i1j", "i2i4", "i2j", "i4j" (A of the
+        "i2", "i4", "j", or a mixed pair "i1i2" ... "i4j", "s4s", "i1s4" ... "js4", "i1s" ... "js" (A of the
         first kind; B, C, alpha, beta of the second)."""
         name = "_%sgemmx__" % kind
-        ckind = kind if kind in self._CTYPES else (kind[2:] if kind[2:] in self._CTYPES else kind[-1:])
+        ckind = kind
+        if kind not in self._CTYPES:  # a pair such as "i1i4", "js4", "s4s": the kind of B and C comes last
+            ckind = next(sfx for sfx in ("s4", "i1", "i2", "i4", "s", "j") if kind.endswith(sfx) and kind[:-len(sfx)] in self._CTYPES)
         ct = self._CTYPES[ckind]
         r = lambda v: ctypes.byref(ctypes.c_int(v))
         getattr(self.lib, name)(r(m), r(n), r(k), ctypes.byref(ct(alpha)), _ptr(a), r(inc1a), r(inc2a),

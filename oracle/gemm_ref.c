@@ -374,6 +374,16 @@ O64REF_GEMMX(o64ref_i2jgemmx, int16_t, int64_t, uint64_t, uint64_t)
 O64REF_GEMMX(o64ref_i4gemmx, int32_t, int32_t, uint32_t, uint32_t)
 O64REF_GEMMX(o64ref_i4jgemmx, int32_t, int64_t, uint64_t, uint64_t)
 O64REF_GEMMX(o64ref_jgemmx, int64_t, int64_t, uint64_t, uint64_t)
+/* mixed kinds with a REAL result: A converted to the kind of B and C (s4sgemmx.f, i4s4gemmx.f, jsgemmx.f, ...) */
+O64REF_GEMMX(o64ref_s4sgemmx, float, double, double, double)
+O64REF_GEMMX(o64ref_i1s4gemmx, int8_t, float, float, float)
+O64REF_GEMMX(o64ref_i2s4gemmx, int16_t, float, float, float)
+O64REF_GEMMX(o64ref_i4s4gemmx, int32_t, float, float, float)
+O64REF_GEMMX(o64ref_js4gemmx, int64_t, float, float, float)
+O64REF_GEMMX(o64ref_i1sgemmx, int8_t, double, double, double)
+O64REF_GEMMX(o64ref_i2sgemmx, int16_t, double, double, double)
+O64REF_GEMMX(o64ref_i4sgemmx, int32_t, double, double, double)
+O64REF_GEMMX(o64ref_jsgemmx, int64_t, double, double, double)
 #undef O64REF_GEMMX
 
 void o64ref_sgemvx_f64(int M, int N, double alpha, const double *A, int inc1a, int inc2a,

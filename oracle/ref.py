@@ -150,17 +150,20 @@ _UCT = {1: ctypes.c_uint8, 2: ctypes.c_uint16, 4: ctypes.c_uint32, 8: ctypes.c_u
 
 
 def xgemmx(M, N, K, alpha, A, inc1a, inc2a, B, inc1b, inc2b, beta, C, inc1c, inc2c):
-    """The strided kernel for the element kinds of (A, C): float32, float64, or an integer pair
-    with A of the same or a narrower kind than B and C (i1gemmx ... i4jgemmx, jgemmx); in place on
+    """The strided kernel for the element kinds of (A, C): the same kind throughout (float32,
+    float64, int8 ... int64), an integer pair with A the narrower kind (i1i2gemmx ... i4jgemmx), or a
+    REAL result with a narrower real or an integer A (s4sgemmx, i1s4gemmx ... jsgemmx); in place on
     the flat array C; integers wrap in the kind of C."""
     assert B.dtype == C.dtype and C.flags.c_contiguous
-    if C.dtype == np.float32 or C.dtype == np.float64:
-        assert A.dtype == C.dtype
-        name, conv = (("o64ref_s4gemmx", ctypes.c_float) if C.dtype == np.float32
-                      else ("o64ref_sgemmx_f64", ctypes.c_double))
+    kinds = dict(_KIND)
+    kinds[np.dtype(np.float32)] = "s4"
+    kinds[np.dtype(np.float64)] = "s"
+    ka, kc = kinds[A.dtype], kinds[C.dtype]
+    if C.dtype.kind == "f":
+        conv = ctypes.c_float if C.dtype == np.float32 else ctypes.c_double
+        name = "o64ref_sgemmx_f64" if (ka, kc) == ("s", "s") else "o64ref_%s%sgemmx" % (ka, "" if ka == kc else kc)
     else:
-        ka, kc = _KIND[A.dtype], _KIND[C.dtype]
-        assert A.dtype.itemsize <= C.dtype.itemsize
+        assert A.dtype.kind == "i" and A.dtype.itemsize <= C.dtype.itemsize
         name = "o64ref_%s%sgemmx" % (ka, "" if ka == kc else kc)
         ct = _UCT[C.dtype.itemsize]
         mask = (1 << (8 * C.dtype.itemsize)) - 1

@@ -1,4 +1,5 @@
-"""GPU: the runtime's MATMUL family beyond REAL*4 — REAL*8 and every pair of integer kinds.
+"""GPU: the runtime's MATMUL family beyond REAL*4 — REAL*8, every pair of integer kinds, and the
+mixed pairs with a REAL result (REAL*4 x REAL*8, integer x real).
 The strided kernels (_sgemmx__, _sgemvx__, _i1gemmx__ ... _jgemmx__: osprey/libfi/matrix/sgemmx.f,
 sgemvx.f and the integer instances of the template xgemmx.h), the BLAS hook dgemm_ and the
 operator entry points _MATMUL_SS, _MATMUL_I1I1 ... _MATMUL_JJ, against the CPU restatement.
@@ -18,19 +19,22 @@ from util import relmax
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 TOL_F64 = 1e-12
-DT = {"s": np.float64, "i1": np.int8, "i2": np.int16, "i4": np.int32, "j": np.int64}
+DT = {"s": np.float64, "s4": np.float32, "i1": np.int8, "i2": np.int16, "i4": np.int32, "j": np.int64}
 INTS = ["i1", "i2", "i4", "j"]
+ORDER = INTS + ["s4", "s"]      # the later kind of a pair is the kind of the result
 # kernel name -> (kind of A, kind of B and C)
-KERNELS = {"s": ("s", "s")}
+KERNELS = {"s": ("s", "s"), "s4s": ("s4", "s")}
 for _i, _a in enumerate(INTS):
     for _c in INTS[_i:]:
         KERNELS[_a if _a == _c else _a + _c] = (_a, _c)
+    KERNELS[_a + "s4"] = (_a, "s4")
+    KERNELS[_a + "s"] = (_a, "s")
 
 
 def _rand(kind, rng, size, overflow=True):
     dt = DT[kind]
-    if kind == "s":
-        return rng.standard_normal(size)
+    if kind in ("s", "s4"):
+        return rng.standard_normal(size).astype(dt)
     info = np.iinfo(dt)
     if not overflow:
         return rng.integers(-11, 11, size, dtype=dt)
@@ -40,6 +44,8 @@ def _rand(kind, rng, size, overflow=True):
 def _same(kind, got, want):
     if kind == "s":
         return relmax(got, want) <= TOL_F64
+    if kind == "s4":
+        return relmax(got, want) <= 1e-4
     return np.array_equal(got, want)
 
 
@@ -51,7 +57,7 @@ def test_xgemmx_kinds_match_oracle(eng, kernel, shape):
     rng = np.random.default_rng(m * 7 + n * 3 + k)
     a, b, c0 = _rand(ka, rng, m * k), _rand(kc, rng, k * n), _rand(kc, rng, m * n)
     b[::7] = 0
-    scal = ((1, 0), (3, 1), (-2, 5)) if kc != "s" else ((1.0, 0.0), (0.5, 1.0), (-2.0, 0.25))
+    scal = ((1, 0), (3, 1), (-2, 5)) if kc in INTS else ((1.0, 0.0), (0.5, 1.0), (-2.0, 0.25))
     for alpha, beta in scal:
         cref = oracle.xgemmx(m, n, k, alpha, a, 1, m, b, 1, k, beta, c0.copy(), 1, m)
         for where in ("host", "device"):
@@ -62,14 +68,14 @@ def test_xgemmx_kinds_match_oracle(eng, kernel, shape):
             assert _same(kc, tc.cpu().numpy(), cref), (where, alpha, beta)
 
 
-@pytest.mark.parametrize("kernel", ["s", "i1", "i1i4", "i2j", "i4", "j"])
+@pytest.mark.parametrize("kernel", ["s", "i1", "i1i4", "i2j", "i4", "j", "s4s", "i2s4", "js"])
 def test_xgemmx_kinds_strided_sections(eng, kernel):
     """A(1:2m:2, :) through inc1a = 2, B stored transposed, C row-major."""
     ka, kc = KERNELS[kernel]
     rng = np.random.default_rng(5)
     m, n, k = 45, 37, 29
     a, b, c0 = _rand(ka, rng, 2 * m * k), _rand(kc, rng, k * n), _rand(kc, rng, m * n)
-    one, zero = (1, 0) if kc != "s" else (1.0, 0.0)
+    one, zero = (1, 0) if kc in INTS else (1.0, 0.0)
     cref = oracle.xgemmx(m, n, k, one, a, 2, 2 * m, b, n, 1, zero, c0.copy(), n, 1)
     tc = torch.from_numpy(c0.copy())
     eng.xgemmx(kernel, m, n, k, one, torch.from_numpy(a), 2, 2 * m, torch.from_numpy(b), n, 1, zero, tc, n, 1)
@@ -140,13 +146,13 @@ def test_dgemm_blas_hook(eng, ta, tb):
 
 def _entry(ka, kb):
     """(_MATMUL_<A><B>, result kind) for operand kinds ka, kb."""
-    up = {"s": "S", "i1": "I1", "i2": "I2", "i4": "I4", "j": "J"}
-    kc = "s" if ka == "s" else INTS[max(INTS.index(ka), INTS.index(kb))]
+    up = {"s": "S", "s4": "S4", "i1": "I1", "i2": "I2", "i4": "I4", "j": "J"}
+    kc = ORDER[max(ORDER.index(ka), ORDER.index(kb))]
     return "_MATMUL_" + up[ka] + up[kb], kc
 
 
 def _dv(kind, arr, extents, strides, assoc=True):
-    code = DopeVector.TYPE_REAL if kind == "s" else DopeVector.TYPE_INTEGER
+    code = DopeVector.TYPE_REAL if kind in ("s", "s4") else DopeVector.TYPE_INTEGER
     return DopeVector.make(arr.ctypes.data if arr is not None else None, extents, strides,
                            8 * np.dtype(DT[kind]).itemsize, code, assoc)
 
@@ -155,13 +161,14 @@ def _ref_product(ka, kb, kc, a, b, m, n, k):
     """The product through the oracle kernel the entry point of (ka, kb) calls: directly, or as
     C' = B'A' when MATRIX_A is the wider kind."""
     c = np.zeros(m * n, DT[kc])
-    one, zero = (1, 0) if kc != "s" else (1.0, 0.0)
-    if ka == "s" or INTS.index(ka) <= INTS.index(kb):
+    one, zero = (1, 0) if kc in INTS else (1.0, 0.0)
+    if ORDER.index(ka) <= ORDER.index(kb):
         return oracle.xgemmx(m, n, k, one, a, 1, m, b, 1, k, zero, c, 1, m)
     return oracle.xgemmx(n, m, k, one, b, k, 1, a, m, 1, zero, c, m, 1)
 
 
-PAIRS = [("s", "s")] + [(x, y) for x in INTS for y in INTS]
+PAIRS = ([("s", "s"), ("s4", "s"), ("s", "s4")] + [(x, y) for x in INTS for y in INTS] +
+         [p for x in INTS for p in ((x, "s4"), ("s4", x), (x, "s"), ("s", x))])
 
 
 @pytest.mark.parametrize("ka,kb", PAIRS)
@@ -178,7 +185,7 @@ def test_matmul_entry_points(eng, ka, kb):
     assert eng.lib.o64_compat_last_status() == o.OK
     ref = _ref_product(ka, kb, kc, a, b, m, n, k)
     assert _same(kc, c, ref)
-    if kc != "s":   # independent check of the wrap-around in the result kind
+    if kc in INTS:   # independent check of the wrap-around in the result kind
         with np.errstate(over="ignore"):
             want = (a.reshape(k, m).T.astype(DT[kc]) @ b.reshape(n, k).T.astype(DT[kc])).astype(DT[kc])
         assert np.array_equal(c.reshape(n, m).T, want)

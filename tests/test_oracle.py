@@ -135,8 +135,10 @@ def test_reassociation_spread_is_far_inside_tolerance():
     assert relmax(y, y64) < 1e-5
 
 
-PAIRS = [(np.float64, np.float64)] + [(a, c) for i, a in enumerate((np.int8, np.int16, np.int32, np.int64))
-                                       for c in (np.int8, np.int16, np.int32, np.int64)[i:]]
+_INTS = (np.int8, np.int16, np.int32, np.int64)
+PAIRS = ([(np.float64, np.float64), (np.float32, np.float64)] +
+         [(a, c) for i, a in enumerate(_INTS) for c in _INTS[i:]] +
+         [(a, c) for a in _INTS for c in (np.float32, np.float64)])
 
 
 @pytest.mark.parametrize("ta,tc", PAIRS, ids=lambda t: np.dtype(t).name)
@@ -146,8 +148,13 @@ def test_xgemmx_other_kinds_against_numpy(ta, tc):
     of C is exercised."""
     rng = np.random.default_rng(11)
     m, n, k = 13, 9, 21
-    if tc is np.float64:
-        a, b, c0 = (rng.standard_normal(s) for s in (m * k * 2, k * n, m * n))
+    real = tc in (np.float32, np.float64)
+    if real:
+        b, c0 = (rng.standard_normal(s).astype(tc) for s in (k * n, m * n))
+        if ta in _INTS:
+            a = rng.integers(-1000, 1000, m * k * 2, dtype=ta) if ta is not np.int8 else rng.integers(-128, 127, m * k * 2, dtype=ta)
+        else:
+            a = rng.standard_normal(m * k * 2).astype(ta)
         alpha, beta = 1.5, -0.5
     else:
         a = rng.integers(np.iinfo(ta).min, np.iinfo(ta).max, m * k * 2, dtype=ta, endpoint=True)
@@ -164,6 +171,8 @@ def test_xgemmx_other_kinds_against_numpy(ta, tc):
     got = c.reshape(n, m).T
     if tc is np.float64:
         assert relmax(got, want) < 1e-14
+    elif tc is np.float32:
+        assert relmax(got, want) < 1e-5
     else:
         assert np.array_equal(got, want)
 

@@ -66,7 +66,7 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint4 v) {
 // instruction, takes twice as long for 128 rows); the load of the next chunk is in flight while
 // this one is sent.
 __device__ __forceinline__ void scatter_rows(int rows, int row0, uint32_t t_row, uint8_t *staging, uint32_t recv,
-                                             int rank, int slice, int c_begin, int c_end) {
+                                             uint8_t *recv_local, int rank, int slice, int c_begin, int c_end) {
     const int lane = threadIdx.x & 31;
     uint4 *patch = reinterpret_cast<uint4 *>(staging);
     const int sw = lane & 7;
@@ -83,7 +83,13 @@ __device__ __forceinline__ void scatter_rows(int rows, int row0, uint32_t t_row,
             const int r = 4 * r4 + (lane >> 3);
             const uint4 val = patch[r * 8 + ((lane & 7) ^ (r & 7))];
             const int grow = row0 + r;
-            if (grow < rows) st_cluster_v4(base + (uint32_t)(((rank * rows + grow) * slice + cin) * 4), val);
+            if (grow < rows) {
+                const uint32_t off = (uint32_t)(((rank * rows + grow) * slice + cin) * 4);
+                if (owner == rank)  // this CTA's own columns: a plain shared-memory store
+                    *reinterpret_cast<uint4 *>(recv_local + off) = val;
+                else
+                    st_cluster_v4(base + off, val);
+            }
         }
         __syncwarp();
     };
@@ -363,8 +369,8 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
                                        : smem_gen + kSkRingBytes - (2 - warp) * kEpiStagingBytesPerWarp;
             tc_fence_after();
             if (quarter * 32 < rows)
-                scatter_rows(rows, quarter * 32, tmem_base + (uint32_t(quarter * 32) << 16), patch, smem_base, rank,
-                             slice, c_begin, c_end);
+                scatter_rows(rows, quarter * 32, tmem_base + (uint32_t(quarter * 32) << 16), patch, smem_base, smem_gen,
+                             rank, slice, c_begin, c_end);
             tc_fence_before();
         }
         cluster_sync_all();  // the slices sent to this CTA have arrived

@@ -403,6 +403,37 @@ void _MATMUL_S4J(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *
 void _MATMUL_JS(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
 void _MATMUL_SJ(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
 
+/* ---- COMPLEX*8 and COMPLEX*16 ------------------------------------------------------------
+ * Complex values are (re, im) pairs of floats / doubles, increments count complex elements, and
+ * the kernels take conjugation flags in front (0 = as is, 1 = conjugate), as
+ * osprey/libfi/matrix/c4gemmx.f:37-85, cgemmx.f, c4gemvx.f and cgemvx.f do.  Unlike the real and
+ * integer kernels the matrix kernel has no test for zero elements of B (c4gemmx.f:199-212). */
+void _c4gemmx__(const int *iconja, const int *iconjb, const int *m, const int *n, const int *k,
+                const float *alpha, const float *a, const int *inc1a, const int *inc2a, const float *b,
+                const int *inc1b, const int *inc2b, const float *beta, float *c, const int *inc1c,
+                const int *inc2c);
+void _cgemmx__(const int *iconja, const int *iconjb, const int *m, const int *n, const int *k,
+               const double *alpha, const double *a, const int *inc1a, const int *inc2a, const double *b,
+               const int *inc1b, const int *inc2b, const double *beta, double *c, const int *inc1c,
+               const int *inc2c);
+void _c4gemvx__(const int *iconj, const int *m, const int *n, const float *alpha, const float *a,
+                const int *incca, const int *incra, const float *x, const int *incx, const float *beta,
+                float *y, const int *incy);
+void _cgemvx__(const int *iconj, const int *m, const int *n, const double *alpha, const double *a,
+               const int *incca, const int *incra, const double *x, const int *incx, const double *beta,
+               double *y, const int *incy);
+/* BLAS hooks for complex MATMUL (mmx_dlutil.c:135-136); trans 'c' is the conjugate transpose. */
+void cgemm_(const char *transa, const char *transb, const int *m, const int *n, const int *k,
+            const float *alpha, const float *a, const int *lda, const float *b, const int *ldb,
+            const float *beta, float *c, const int *ldc);
+void zgemm_(const char *transa, const char *transb, const int *m, const int *n, const int *k,
+            const double *alpha, const double *a, const int *lda, const double *b, const int *ldb,
+            const double *beta, double *c, const int *ldc);
+/* MATMUL on COMPLEX*8 (matmul_c4c4.c:76-134) and COMPLEX*16 (matmul_cc@.c) arrays; rank-1 operands go
+ * to the matrix-vector kernels, nothing is conjugated. */
+void _MATMUL_C4C4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_CC(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+
 /* Status of the last compat call on this thread (the Fortran entry points return void). */
 int o64_compat_last_status(void);
 

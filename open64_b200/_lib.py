@@ -30,6 +30,7 @@ EXPORTS = [
     "_MATMUL_I1I1", "_MATMUL_I1I2", "_MATMUL_I1I4", "_MATMUL_I1J", "_MATMUL_I2I1", "_MATMUL_I2I2", "_MATMUL_I2I4",
     "_MATMUL_I2J", "_MATMUL_I4I1", "_MATMUL_I4I2", "_MATMUL_I4I4", "_MATMUL_I4J", "_MATMUL_JI1", "_MATMUL_JI2",
     "_MATMUL_JI4", "_MATMUL_JJ",
+    "_c4gemmx__", "_cgemmx__", "_c4gemvx__", "_cgemvx__", "cgemm_", "zgemm_", "_MATMUL_C4C4", "_MATMUL_CC",
     "_s4sgemmx__", "_i1s4gemmx__", "_i2s4gemmx__", "_i4s4gemmx__", "_js4gemmx__", "_i1sgemmx__", "_i2sgemmx__", "_i4sgemmx__", "_jsgemmx__",
     "_MATMUL_S4S", "_MATMUL_SS4", "_MATMUL_I1S4", "_MATMUL_S4I1", "_MATMUL_I1S", "_MATMUL_SI1", "_MATMUL_I2S4", "_MATMUL_S4I2", "_MATMUL_I2S", "_MATMUL_SI2", "_MATMUL_I4S4", "_MATMUL_S4I4", "_MATMUL_I4S", "_MATMUL_SI4", "_MATMUL_JS4", "_MATMUL_S4J", "_MATMUL_JS", "_MATMUL_SJ",
 ]
@@ -58,7 +59,7 @@ class DopeVector(ctypes.Structure):
                 ("flags1", ctypes.c_uint32), ("type_pad", ctypes.c_uint32), ("type_bits", ctypes.c_uint32),
                 ("orig_base", ctypes.c_void_p), ("orig_size", ctypes.c_ulong), ("dimension", DvDimen * 7)]
 
-    TYPE_INTEGER, TYPE_REAL = 2, 3  # osprey/clibinc/cray/dopevec.h: DVTYPE_INTEGER, DVTYPE_REAL
+    TYPE_INTEGER, TYPE_REAL, TYPE_COMPLEX = 2, 3, 4  # osprey/clibinc/cray/dopevec.h: DVTYPE_INTEGER, _REAL, _COMPLEX
 
     @classmethod
     def make(cls, ptr, extents, strides, bits=32, type_code=3, assoc=True):
@@ -150,6 +151,14 @@ def lib():
         getattr(L, name).restype = None
     L._sgemvx__.argtypes = [pi, pi, vp, vp, pi, pi, vp, pi, vp, vp, pi]
     L._sgemvx__.restype = None
+    for name in ("_c4gemmx__", "_cgemmx__"):  # two conjugation flags in front
+        getattr(L, name).argtypes = [pi, pi, pi, pi, pi, vp, vp, pi, pi, vp, pi, pi, vp, vp, pi, pi]
+    for name in ("_c4gemvx__", "_cgemvx__"):
+        getattr(L, name).argtypes = [pi, pi, pi, vp, vp, pi, pi, vp, pi, vp, vp, pi]
+        getattr(L, name).restype = None
+    for name in ("cgemm_", "zgemm_"):
+        getattr(L, name).argtypes = [ctypes.c_char_p, ctypes.c_char_p, pi, pi, pi, vp, vp, pi, vp, pi, vp, vp, pi]
+        getattr(L, name).restype = None
     for name in [e for e in EXPORTS if e.startswith("_MATMUL_")]:
         getattr(L, name).argtypes = [ctypes.POINTER(DopeVector)] * 3
         getattr(L, name).restype = None

@@ -976,6 +976,10 @@ static size_t strided_span(int64_t n1, int64_t n2, int64_t s1, int64_t s2) {
 
 // Element type the CUDA-core kernels compute in: the integer kinds run on the unsigned type of
 // the same width, whose wrap-around is the two's-complement result the Fortran kernels produce.
+typedef Cx<float> c4_t;   // COMPLEX*8: (re, im) single precision
+typedef Cx<double> c8_t;  // COMPLEX*16
+template <typename T> struct IsCx { static constexpr bool value = false; };
+template <typename R> struct IsCx<Cx<R>> { static constexpr bool value = true; };
 template <typename T> struct ComputeType { typedef T type; };
 template <> struct ComputeType<int8_t> { typedef uint8_t type; };
 template <> struct ComputeType<int16_t> { typedef uint16_t type; };
@@ -986,7 +990,8 @@ template <> struct ComputeType<int64_t> { typedef uint64_t type; };
 // the mixed integer kernels such as _i1i4gemmx__).
 template <typename TA, typename T>
 static int xgemmx_impl(int M, int N, int K, T alpha, const TA *A, int64_t a1, int64_t a2, const T *B,
-                       int64_t b1, int64_t b2, T beta, T *C, int64_t c1, int64_t c2, bool skip_zero) {
+                       int64_t b1, int64_t b2, T beta, T *C, int64_t c1, int64_t c2, bool skip_zero, int conj_a = 0,
+                       int conj_b = 0) {
     typedef typename ComputeType<T>::type U;
     // quick returns, in the order of osprey/libfi/matrix/xgemmx.h:172-208
     if (M < 0 || N < 0 || K < 0) return O64_ERR_RANK;
@@ -1031,7 +1036,7 @@ static int xgemmx_impl(int M, int N, int K, T alpha, const TA *A, int64_t a1, in
             rc = generic_scale<U>(M, N, (U)beta_eff, (U *)out.dev, c1, c2, s);
         else
             rc = generic_gemmx<TA, U>(M, N, K, (U)alpha, (const TA *)dA, a1, a2, (const U *)dB, b1, b2, (U)beta,
-                                  (U *)out.dev, c1, c2, s);
+                                  (U *)out.dev, c1, c2, s, conj_a, conj_b);
     }
     if (rc) return rc;
     if ((rc = stage_out_end(out, s))) return rc;
@@ -1069,6 +1074,23 @@ O64_XGEMMX_ENTRY(_i4sgemmx__, int32_t, double)
 O64_XGEMMX_ENTRY(_jsgemmx__, int64_t, double)
 #undef O64_XGEMMX_ENTRY
 
+// COMPLEX*8 / COMPLEX*16: the kernels take conjugation flags in front (osprey/libfi/matrix/c4gemmx.f:37-85,
+// cgemmx.f); complex values are (re, im) pairs of floats / doubles.
+#define O64_CGEMMX_ENTRY(NAME, R)                                                                          \
+    extern "C" void NAME(const int *iconja, const int *iconjb, const int *m, const int *n, const int *k,   \
+                         const R *alpha, const R *a, const int *inc1a, const int *inc2a, const R *b,       \
+                         const int *inc1b, const int *inc2b, const R *beta, R *c, const int *inc1c,        \
+                         const int *inc2c) {                                                               \
+        typedef Cx<R> T;                                                                                   \
+        g_compat_status = xgemmx_impl<T, T>(*m, *n, *k, T(alpha[0], alpha[1]), reinterpret_cast<const T *>(a), \
+                                            *inc1a, *inc2a, reinterpret_cast<const T *>(b), *inc1b, *inc2b, \
+                                            T(beta[0], beta[1]), reinterpret_cast<T *>(c), *inc1c, *inc2c, \
+                                            false, *iconja != 0, *iconjb != 0);                            \
+    }
+O64_CGEMMX_ENTRY(_c4gemmx__, float)
+O64_CGEMMX_ENTRY(_cgemmx__, double)
+#undef O64_CGEMMX_ENTRY
+
 template <typename T>
 static int blas_gemm_impl(const char *transa, const char *transb, const int *m, const int *n, const int *k,
                           const T *alpha, const T *a, const int *lda, const T *b, const int *ldb,
@@ -1100,7 +1122,7 @@ extern "C" void dgemm_(const char *transa, const char *transb, const int *m, con
 
 template <typename T>
 static int xgemvx_impl(int M, int N, T alpha, const T *a, int64_t incca, int64_t incra, const T *x,
-                       int64_t incx, T beta, T *y, int64_t incy) {
+                       int64_t incx, T beta, T *y, int64_t incy, int conj_a = 0) {
     if (M < 0 || N < 0) return O64_ERR_RANK;
     // quick returns of osprey/libfi/matrix/s4gemvx.f (sgemvx.f is the same text in REAL*8)
     if (M == 0) return O64_OK;
@@ -1129,7 +1151,7 @@ static int xgemvx_impl(int M, int N, T alpha, const T *a, int64_t incca, int64_t
         } else {
             if (need_ax)
                 rc = generic_gemvx<T>(M, N, alpha, (const T *)dA, incca, incra, (const T *)dX, incx, beta,
-                                      (T *)out.dev, incy, s);
+                                      (T *)out.dev, incy, s, conj_a);
             else
                 rc = generic_scale<T>(M, 1, zero_only ? T(0) : beta, (T *)out.dev, incy, 0, s);
         }
@@ -1149,6 +1171,50 @@ extern "C" void _sgemvx__(const int *m, const int *n, const double *alpha, const
                           const int *incca, const int *incra, const double *x, const int *incx,
                           const double *beta, double *y, const int *incy) {
     g_compat_status = xgemvx_impl<double>(*m, *n, *alpha, a, *incca, *incra, x, *incx, *beta, y, *incy);
+}
+
+#define O64_CGEMVX_ENTRY(NAME, R)                                                                          \
+    extern "C" void NAME(const int *iconj, const int *m, const int *n, const R *alpha, const R *a,         \
+                         const int *incca, const int *incra, const R *x, const int *incx, const R *beta,   \
+                         R *y, const int *incy) {                                                          \
+        typedef Cx<R> T;                                                                                   \
+        g_compat_status = xgemvx_impl<T>(*m, *n, T(alpha[0], alpha[1]), reinterpret_cast<const T *>(a), *incca, \
+                                         *incra, reinterpret_cast<const T *>(x), *incx, T(beta[0], beta[1]), \
+                                         reinterpret_cast<T *>(y), *incy, *iconj != 0);                    \
+    }
+O64_CGEMVX_ENTRY(_c4gemvx__, float)
+O64_CGEMVX_ENTRY(_cgemvx__, double)
+#undef O64_CGEMVX_ENTRY
+
+// BLAS hooks for COMPLEX MATMUL (osprey/libfi/matrix/mmx_dlutil.c:135-136): 'c' is the conjugate transpose.
+template <typename R>
+static int blas_cgemm_impl(const char *transa, const char *transb, const int *m, const int *n, const int *k,
+                           const R *alpha, const R *a, const int *lda, const R *b, const int *ldb, const R *beta,
+                           R *c, const int *ldc) {
+    typedef Cx<R> T;
+    auto kind = [](char ch) { return (ch == 'n' || ch == 'N') ? 0 : (ch == 't' || ch == 'T') ? 1 : (ch == 'c' || ch == 'C') ? 2 : -1; };
+    const int ka = kind(*transa), kb = kind(*transb);
+    if (ka < 0 || kb < 0) return O64_ERR_RANK;
+    const int rows_a = ka == 0 ? *m : *k, rows_b = kb == 0 ? *k : *n;
+    if (*lda < (rows_a > 1 ? rows_a : 1) || *ldb < (rows_b > 1 ? rows_b : 1) || *ldc < (*m > 1 ? *m : 1))
+        return O64_ERR_CONFORM;
+    const int64_t a1 = ka == 0 ? 1 : *lda, a2 = ka == 0 ? *lda : 1;
+    const int64_t b1 = kb == 0 ? 1 : *ldb, b2 = kb == 0 ? *ldb : 1;
+    return xgemmx_impl<T, T>(*m, *n, *k, T(alpha[0], alpha[1]), reinterpret_cast<const T *>(a), a1, a2,
+                             reinterpret_cast<const T *>(b), b1, b2, T(beta[0], beta[1]), reinterpret_cast<T *>(c), 1,
+                             *ldc, false, ka == 2, kb == 2);
+}
+
+extern "C" void cgemm_(const char *transa, const char *transb, const int *m, const int *n, const int *k,
+                       const float *alpha, const float *a, const int *lda, const float *b, const int *ldb,
+                       const float *beta, float *c, const int *ldc) {
+    g_compat_status = blas_cgemm_impl<float>(transa, transb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
+}
+
+extern "C" void zgemm_(const char *transa, const char *transb, const int *m, const int *n, const int *k,
+                       const double *alpha, const double *a, const int *lda, const double *b, const int *ldb,
+                       const double *beta, double *c, const int *ldc) {
+    g_compat_status = blas_cgemm_impl<double>(transa, transb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc);
 }
 
 // ---- the MATMUL operator entry point (osprey/libfi/matrix/matmul_s4s4.c:66-112) ----------------
@@ -1237,7 +1303,7 @@ int matmul_impl(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *M
         m = (int)a.n1, n = (int)b.n2, k = (int)a.n2;
     } else if (a.ndim == 2) {  // y = A x
         if (!(a.n2 == b.n1 && a.n1 == c.n1)) return O64_ERR_CONFORM;
-        if constexpr (std::is_floating_point<T>::value) {
+        if constexpr (std::is_floating_point<T>::value || IsCx<T>::value) {
             if (use_gemv)
                 return xgemvx_impl<T>((int)a.n1, (int)a.n2, one, static_cast<const T *>(a.ptr), a.inc1, a.inc2,
                                       static_cast<const T *>(b.ptr), b.inc1, zero, C, c.inc1);
@@ -1245,7 +1311,7 @@ int matmul_impl(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *M
         m = (int)a.n1, n = 1, k = (int)a.n2;
     } else {  // y = x B, i.e. y' = B' x'
         if (!(a.n1 == b.n1 && c.n1 == b.n2)) return O64_ERR_CONFORM;
-        if constexpr (std::is_floating_point<T>::value) {
+        if constexpr (std::is_floating_point<T>::value || IsCx<T>::value) {
             if (use_gemv)
                 return xgemvx_impl<T>((int)b.n2, (int)b.n1, one, static_cast<const T *>(b.ptr), b.inc2, b.inc1,
                                       static_cast<const T *>(a.ptr), a.inc1, zero, C, c.inc1);
@@ -1266,6 +1332,8 @@ int matmul_impl(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *M
     }
 O64_MATMUL_ENTRY(_MATMUL_S4S4, float, float, true, false)
 O64_MATMUL_ENTRY(_MATMUL_SS, double, double, true, false)
+O64_MATMUL_ENTRY(_MATMUL_C4C4, c4_t, c4_t, true, false)
+O64_MATMUL_ENTRY(_MATMUL_CC, c8_t, c8_t, true, false)
 O64_MATMUL_ENTRY(_MATMUL_I1I1, int8_t, int8_t, false, false)
 O64_MATMUL_ENTRY(_MATMUL_I1I2, int8_t, int16_t, false, false)
 O64_MATMUL_ENTRY(_MATMUL_I1I4, int8_t, int32_t, false, false)

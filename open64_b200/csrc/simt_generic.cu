@@ -1,6 +1,6 @@
 // The rest of the runtime's X-interface family on CUDA cores: C = alpha*A*B + beta*C and
-// y = alpha*A*x + beta*y for REAL*8 and for the integer kinds (8 to 64 bits, A of the same or a
-// narrower kind than B and C), with the semantics of the reference's template
+// y = alpha*A*x + beta*y for REAL*8, COMPLEX*8 / *16 and the integer kinds (8 to 64 bits, A of the
+// same or a narrower kind than B and C), with the semantics of the reference's template
 // (osprey/libfi/matrix/xgemmx.h:172-236: element (i,j) of X at X[inc1x*i + inc2x*j], beta == 0
 // does not read C, a zero B(l,j) skips its term; integers wrap in the kind of C).
 // These kinds have no tensor-core path that keeps their exact arithmetic; the kernel is a plain
@@ -18,9 +18,14 @@ namespace o64 {
 // A's element in the kind of C: integers are sign-extended, then carried on the unsigned type;
 // with a REAL result (the mixed kernels such as _i4s4gemmx__, _s4sgemmx__) A is converted to it.
 template <typename T, typename TA> __device__ __forceinline__ T widen(TA a) {
-    if constexpr (std::is_floating_point<T>::value) return (T)a;  // REAL results: plain conversion
+    if constexpr (std::is_same<T, TA>::value) return a;
+    else if constexpr (std::is_floating_point<T>::value) return (T)a;  // REAL results: plain conversion
     else return (T)(long long)a;
 }
+template <typename T> struct IsComplex { static constexpr bool value = false; };
+template <typename R> struct IsComplex<Cx<R>> { static constexpr bool value = true; };
+template <typename T> __device__ __forceinline__ T conj_if(T x, int) { return x; }
+template <typename R> __device__ __forceinline__ Cx<R> conj_if(Cx<R> x, int on) { return on ? Cx<R>(x.re, -x.im) : x; }
 
 // Product in the kind T.  8- and 16-bit operands are multiplied as unsigned 32-bit values: the
 // usual promotion to (signed) int would overflow for 16-bit factors.
@@ -33,7 +38,7 @@ template <typename TA, typename T>
 __global__ void __launch_bounds__(256)
 gemmx_generic_kernel(long long M, long long N, long long K, T alpha, const TA *A, long long a1, long long a2,
                      const T *B, long long b1, long long b2, T beta, T *C, long long c1, long long c2,
-                     int a_k_fast, int b_n_fast) {
+                     int a_k_fast, int b_n_fast, int conj_a, int conj_b) {
     constexpr int BM = 32, BN = 32, BK = 16, TM = 2, TN = 2;
     __shared__ T As[BK][BM + 1];
     __shared__ T Bs[BK][BN + 1];
@@ -46,13 +51,13 @@ gemmx_generic_kernel(long long M, long long N, long long K, T alpha, const TA *A
             int i, l;
             if (a_k_fast) { l = e % BK; i = e / BK; } else { i = e % BM; l = e / BM; }
             const long long gi = m0 + i, gl = k0 + l;
-            As[l][i] = (gi < M && gl < K) ? widen<T, TA>(A[gi * a1 + gl * a2]) : T(0);
+            As[l][i] = (gi < M && gl < K) ? conj_if(widen<T, TA>(A[gi * a1 + gl * a2]), conj_a) : T(0);
         }
         for (int e = tid; e < BK * BN; e += 256) {
             int l, j;
             if (b_n_fast) { j = e % BN; l = e / BN; } else { l = e % BK; j = e / BK; }
             const long long gl = k0 + l, gj = n0 + j;
-            Bs[l][j] = (gl < K && gj < N) ? B[gl * b1 + gj * b2] : T(0);
+            Bs[l][j] = (gl < K && gj < N) ? conj_if(B[gl * b1 + gj * b2], conj_b) : T(0);
         }
         __syncthreads();
 #pragma unroll
@@ -62,7 +67,9 @@ gemmx_generic_kernel(long long M, long long N, long long K, T alpha, const TA *A
 #pragma unroll
                 for (int j = 0; j < TN; ++j) {
                     const T b = Bs[l][tx * TN + j];
-                    if (b != T(0)) acc[i][j] = (T)(acc[i][j] + mul<T>(As[l][ty * TM + i], b));  // zero B(l,j): term left out
+                    // zero B(l,j): term left out (the template of the real and integer kernels; the
+                    // complex kernels have no such test, osprey/libfi/matrix/c4gemmx.f:199-212)
+                    if (IsComplex<T>::value || b != T(0)) acc[i][j] = (T)(acc[i][j] + mul<T>(As[l][ty * TM + i], b));
                 }
         }
         __syncthreads();
@@ -85,14 +92,14 @@ gemmx_generic_kernel(long long M, long long N, long long K, T alpha, const TA *A
 
 template <typename T>
 __global__ void gemvx_generic_kernel(long long M, long long N, T alpha, const T *A, long long a1, long long a2,
-                                     const T *X, long long incx, T beta, T *Y, long long incy) {
+                                     const T *X, long long incx, T beta, T *Y, long long incy, int conj_a) {
     const long long row = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (row >= M) return;
     T *y = Y + row * incy;
-    T acc = (beta == T(0)) ? T(0) : beta * *y;
+    T acc = (beta == T(0)) ? T(0) : mul<T>(beta, *y);
     for (long long j = 0; j < N; ++j) {
         const T x = X[j * incx];
-        if (x != T(0)) acc += (alpha * x) * A[row * a1 + j * a2];
+        if (x != T(0)) acc = acc + mul<T>(mul<T>(alpha, x), conj_if(A[row * a1 + j * a2], conj_a));
     }
     *y = acc;
 }
@@ -107,21 +114,21 @@ __global__ void scale_generic_kernel(long long M, long long N, T beta, T *C, lon
 
 template <typename TA, typename T>
 int generic_gemmx(int64_t M, int64_t N, int64_t K, T alpha, const TA *A, int64_t a1, int64_t a2, const T *B,
-                  int64_t b1, int64_t b2, T beta, T *C, int64_t c1, int64_t c2, cudaStream_t s) {
+                  int64_t b1, int64_t b2, T beta, T *C, int64_t c1, int64_t c2, cudaStream_t s, int conj_a, int conj_b) {
     if (M <= 0 || N <= 0) return O64_OK;
     if ((M + 31) / 32 > 65535) return O64_ERR_RANK;
     auto mag = [](int64_t v) { return v < 0 ? -v : v; };
     dim3 grid((unsigned)((N + 31) / 32), (unsigned)((M + 31) / 32));
     gemmx_generic_kernel<TA, T><<<grid, 256, 0, s>>>(M, N, K, alpha, A, a1, a2, B, b1, b2, beta, C, c1, c2,
-                                                 mag(a2) <= mag(a1), mag(b2) <= mag(b1));
+                                                 mag(a2) <= mag(a1), mag(b2) <= mag(b1), conj_a, conj_b);
     return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
 }
 
 template <typename T>
 int generic_gemvx(int64_t M, int64_t N, T alpha, const T *A, int64_t a1, int64_t a2, const T *X, int64_t incx,
-                  T beta, T *Y, int64_t incy, cudaStream_t s) {
+                  T beta, T *Y, int64_t incy, cudaStream_t s, int conj_a) {
     if (M <= 0) return O64_OK;
-    gemvx_generic_kernel<T><<<(unsigned)((M + 127) / 128), 128, 0, s>>>(M, N, alpha, A, a1, a2, X, incx, beta, Y, incy);
+    gemvx_generic_kernel<T><<<(unsigned)((M + 127) / 128), 128, 0, s>>>(M, N, alpha, A, a1, a2, X, incx, beta, Y, incy, conj_a);
     return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
 }
 
@@ -135,7 +142,7 @@ int generic_scale(int64_t M, int64_t N, T beta, T *C, int64_t c1, int64_t c2, cu
 
 #define O64_INSTANTIATE_GEMMX(TA, T)                                                                          \
     template int generic_gemmx<TA, T>(int64_t, int64_t, int64_t, T, const TA *, int64_t, int64_t, const T *,     \
-                                      int64_t, int64_t, T, T *, int64_t, int64_t, cudaStream_t);
+                                      int64_t, int64_t, T, T *, int64_t, int64_t, cudaStream_t, int, int);
 #define O64_INSTANTIATE_SCALE(T) template int generic_scale<T>(int64_t, int64_t, T, T *, int64_t, int64_t, cudaStream_t);
 O64_INSTANTIATE_GEMMX(double, double)
 O64_INSTANTIATE_GEMMX(int8_t, uint8_t)
@@ -163,8 +170,17 @@ O64_INSTANTIATE_SCALE(uint8_t)
 O64_INSTANTIATE_SCALE(uint16_t)
 O64_INSTANTIATE_SCALE(uint32_t)
 O64_INSTANTIATE_SCALE(uint64_t)
-template int generic_gemvx<double>(int64_t, int64_t, double, const double *, int64_t, int64_t, const double *, int64_t,
-                                   double, double *, int64_t, cudaStream_t);
+#define O64_INSTANTIATE_GEMVX(T)                                                                              \
+    template int generic_gemvx<T>(int64_t, int64_t, T, const T *, int64_t, int64_t, const T *, int64_t, T, T *,  \
+                                  int64_t, cudaStream_t, int);
+O64_INSTANTIATE_GEMVX(double)
+O64_INSTANTIATE_GEMVX(Cx<float>)
+O64_INSTANTIATE_GEMVX(Cx<double>)
+O64_INSTANTIATE_GEMMX(Cx<float>, Cx<float>)
+O64_INSTANTIATE_GEMMX(Cx<double>, Cx<double>)
+O64_INSTANTIATE_SCALE(Cx<float>)
+O64_INSTANTIATE_SCALE(Cx<double>)
+#undef O64_INSTANTIATE_GEMVX
 #undef O64_INSTANTIATE_GEMMX
 #undef O64_INSTANTIATE_SCALE
 

@@ -53,15 +53,30 @@ int finalize_partial_bf16(const float *partial, int64_t M, int64_t N, const floa
                           const float *scale_b, const float *bias, int act, void *C, int64_t ldc,
                           cudaStream_t stream);
 
+// COMPLEX*8 / COMPLEX*16 element: (re, im) as Fortran stores it.
+template <typename R>
+struct Cx {
+    R re, im;
+    Cx() = default;
+    __host__ __device__ Cx(R r) : re(r), im(R(0)) {}
+    __host__ __device__ Cx(R r, R i) : re(r), im(i) {}
+    __host__ __device__ Cx operator+(const Cx &o) const { return Cx(re + o.re, im + o.im); }
+    __host__ __device__ Cx operator*(const Cx &o) const { return Cx(re * o.re - im * o.im, re * o.im + im * o.re); }
+    __host__ __device__ bool operator==(const Cx &o) const { return re == o.re && im == o.im; }
+    __host__ __device__ bool operator!=(const Cx &o) const { return !(*this == o); }
+};
+
 // The same strided operations for REAL*8 and the integer kinds (simt_generic.cu).  T is the kind
 // of B and C (integers: the unsigned type of that width); TA the kind of A (integers: signed, of
-// the same or a smaller width, sign-extended to T).
+// the same or a smaller width, sign-extended to T).  conj_a / conj_b: use the conjugate of a
+// complex operand (the complex kernels of the runtime take these flags, osprey/libfi/matrix/c4gemmx.f:77-85).
 template <typename TA, typename T>
 int generic_gemmx(int64_t M, int64_t N, int64_t K, T alpha, const TA *A, int64_t a1, int64_t a2, const T *B,
-                  int64_t b1, int64_t b2, T beta, T *C, int64_t c1, int64_t c2, cudaStream_t s);
+                  int64_t b1, int64_t b2, T beta, T *C, int64_t c1, int64_t c2, cudaStream_t s, int conj_a = 0,
+                  int conj_b = 0);
 template <typename T>
 int generic_gemvx(int64_t M, int64_t N, T alpha, const T *A, int64_t a1, int64_t a2, const T *X, int64_t incx,
-                  T beta, T *Y, int64_t incy, cudaStream_t s);
+                  T beta, T *Y, int64_t incy, cudaStream_t s, int conj_a = 0);
 template <typename T>
 int generic_scale(int64_t M, int64_t N, T beta, T *C, int64_t c1, int64_t c2, cudaStream_t s);
 

@@ -334,3 +334,43 @@ class Engine:
                         ctypes.byref(ci(ldc)))
         check(self.lib.o64_compat_last_status(), "dgemm_")
         return c
+
+    def cgemmx(self, m, n, k, alpha, a, inc1a, inc2a, b, inc1b, inc2b, beta, c, inc1c, inc2c, conja=False, conjb=False):
+        """_c4gemmx__ / _cgemmx__ (by c's dtype: complex64 / complex128), in place on c; increments in
+        complex elements."""
+        single = c.dtype == torch.complex64
+        fn = self.lib._c4gemmx__ if single else self.lib._cgemmx__
+        ct = ctypes.c_float if single else ctypes.c_double
+        r = lambda v: ctypes.byref(ctypes.c_int(int(v)))
+        cx = lambda z: (ct * 2)(complex(z).real, complex(z).imag)
+        al, be = cx(alpha), cx(beta)
+        fn(r(conja), r(conjb), r(m), r(n), r(k), ctypes.cast(al, ctypes.c_void_p), _ptr(a), r(inc1a), r(inc2a),
+           _ptr(b), r(inc1b), r(inc2b), ctypes.cast(be, ctypes.c_void_p), _ptr(c), r(inc1c), r(inc2c))
+        check(self.lib.o64_compat_last_status(), "_cgemmx__")
+        return c
+
+    def cgemvx(self, m, n, alpha, a, incca, incra, x, incx, beta, y, incy, conj=False):
+        """_c4gemvx__ / _cgemvx__ by y's dtype, in place on y."""
+        single = y.dtype == torch.complex64
+        fn = self.lib._c4gemvx__ if single else self.lib._cgemvx__
+        ct = ctypes.c_float if single else ctypes.c_double
+        r = lambda v: ctypes.byref(ctypes.c_int(int(v)))
+        cx = lambda z: (ct * 2)(complex(z).real, complex(z).imag)
+        al, be = cx(alpha), cx(beta)
+        fn(r(conj), r(m), r(n), ctypes.cast(al, ctypes.c_void_p), _ptr(a), r(incca), r(incra), _ptr(x), r(incx),
+           ctypes.cast(be, ctypes.c_void_p), _ptr(y), r(incy))
+        check(self.lib.o64_compat_last_status(), "_cgemvx__")
+        return y
+
+    def cgemm(self, transa, transb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc):
+        """cgemm_ / zgemm_ by c's dtype (column-major BLAS)."""
+        single = c.dtype == torch.complex64
+        fn = self.lib.cgemm_ if single else self.lib.zgemm_
+        ct = ctypes.c_float if single else ctypes.c_double
+        r = lambda v: ctypes.byref(ctypes.c_int(int(v)))
+        cx = lambda z: (ct * 2)(complex(z).real, complex(z).imag)
+        al, be = cx(alpha), cx(beta)
+        fn(transa.encode(), transb.encode(), r(m), r(n), r(k), ctypes.cast(al, ctypes.c_void_p), _ptr(a), r(lda),
+           _ptr(b), r(ldb), ctypes.cast(be, ctypes.c_void_p), _ptr(c), r(ldc))
+        check(self.lib.o64_compat_last_status(), "cgemm_")
+        return c

@@ -409,6 +409,82 @@ void o64ref_sgemvx_f64(int M, int N, double alpha, const double *A, int inc1a, i
     }
 }
 
+/* ---- COMPLEX*8 / COMPLEX*16 (c4gemmx.f:156-244, cgemmx.f; c4gemvx.f, cgemvx.f) -------------
+ * Values are (re, im) pairs; increments count complex elements.  The matrix kernel applies the
+ * conjugation flags and, unlike the real template, does not test B for zeros; the vector kernel
+ * skips a column when x(j) == 0. */
+#define O64REF_CGEMMX(NAME, NAMEV, R)                                                            \
+    void NAME(int conja, int conjb, int M, int N, int K, const R *alpha, const R *A, int inc1a,   \
+              int inc2a, const R *B, int inc1b, int inc2b, const R *beta, R *C, int inc1c,       \
+              int inc2c) {                                                                       \
+        const R ar = alpha[0], ai = alpha[1], br = beta[0], bi = beta[1];                        \
+        const int a_zero = (ar == 0 && ai == 0), b_one = (br == 1 && bi == 0);                   \
+        const int b_zero = (br == 0 && bi == 0);                                                 \
+        if (M == 0 || N == 0 || (a_zero && b_one)) return;                                       \
+        for (long j = 0; j < N; ++j) {                                                           \
+            for (long i = 0; i < M; ++i) {                                                       \
+                R *c = C + 2 * ((long)inc2c * j + (long)inc1c * i);                              \
+                if (b_zero || K == 0) { /* K == 0: the result is set to zero (c4gemmx.f:164-172) */ \
+                    c[0] = 0, c[1] = 0;                                                          \
+                    continue;                                                                    \
+                }                                                                                \
+                if (b_zero) {                                                                    \
+                    c[0] = 0, c[1] = 0;                                                          \
+                } else if (!b_one) {                                                             \
+                    const R cr = c[0], ci = c[1];                                                \
+                    c[0] = br * cr - bi * ci, c[1] = br * ci + bi * cr;                          \
+                }                                                                                \
+            }                                                                                    \
+            if (a_zero) continue;                                                                \
+            for (long l = 0; l < K; ++l) {                                                       \
+                const R *b = B + 2 * ((long)inc2b * j + (long)inc1b * l);                        \
+                const R xr = b[0], xi = conjb ? -b[1] : b[1];                                    \
+                const R tr = ar * xr - ai * xi, ti = ar * xi + ai * xr;                          \
+                for (long i = 0; i < M; ++i) {                                                   \
+                    const R *a = A + 2 * ((long)inc2a * l + (long)inc1a * i);                    \
+                    const R yr = a[0], yi = conja ? -a[1] : a[1];                                \
+                    R *c = C + 2 * ((long)inc2c * j + (long)inc1c * i);                          \
+                    c[0] = c[0] + (tr * yr - ti * yi);                                           \
+                    c[1] = c[1] + (tr * yi + ti * yr);                                           \
+                }                                                                                \
+            }                                                                                    \
+        }                                                                                        \
+    }                                                                                            \
+    void NAMEV(int conj, int M, int N, const R *alpha, const R *A, int inc1a, int inc2a,         \
+               const R *X, int incx, const R *beta, R *Y, int incy) {                            \
+        const R ar = alpha[0], ai = alpha[1], br = beta[0], bi = beta[1];                        \
+        if (M != 0 && N == 0) {                                                                  \
+            for (long i = 0; i < M; ++i) Y[2 * (long)incy * i] = 0, Y[2 * (long)incy * i + 1] = 0; \
+            return;                                                                              \
+        }                                                                                        \
+        if (M == 0 || N == 0 || (ar == 0 && ai == 0 && br == 1 && bi == 0)) return;              \
+        for (long i = 0; i < M; ++i) {                                                           \
+            R *y = Y + 2 * (long)incy * i;                                                       \
+            if (br == 0 && bi == 0) {                                                            \
+                y[0] = 0, y[1] = 0;                                                              \
+            } else if (!(br == 1 && bi == 0)) {                                                  \
+                const R yr = y[0], yi = y[1];                                                    \
+                y[0] = br * yr - bi * yi, y[1] = br * yi + bi * yr;                              \
+            }                                                                                    \
+        }                                                                                        \
+        if (ar == 0 && ai == 0) return;                                                          \
+        for (long j = 0; j < N; ++j) {                                                           \
+            const R xr = X[2 * (long)incx * j], xi = X[2 * (long)incx * j + 1];                  \
+            if (xr == 0 && xi == 0) continue;                                                    \
+            const R tr = ar * xr - ai * xi, ti = ar * xi + ai * xr;                              \
+            for (long i = 0; i < M; ++i) {                                                       \
+                const R *a = A + 2 * ((long)inc1a * i + (long)inc2a * j);                        \
+                const R zr = a[0], zi = conj ? -a[1] : a[1];                                     \
+                R *y = Y + 2 * (long)incy * i;                                                   \
+                y[0] = y[0] + (tr * zr - ti * zi);                                               \
+                y[1] = y[1] + (tr * zi + ti * zr);                                               \
+            }                                                                                    \
+        }                                                                                        \
+    }
+O64REF_CGEMMX(o64ref_c4gemmx, o64ref_c4gemvx, float)
+O64REF_CGEMMX(o64ref_cgemmx, o64ref_cgemvx, double)
+#undef O64REF_CGEMMX
+
 /* Launchers such as torchrun export OMP_NUM_THREADS=1; the CPU baseline asks for the cores back. */
 void o64ref_set_num_threads(int n) {
 #ifdef _OPENMP

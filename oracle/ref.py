@@ -17,7 +17,7 @@ ACT_NONE, ACT_RELU, ACT_GELU_TANH, ACT_GELU_ERF, ACT_SILU = range(5)
 __all__ = [
     "ACT_NONE", "ACT_RELU", "ACT_GELU_TANH", "ACT_GELU_ERF", "ACT_SILU", "build", "lib",
     "linear_f32", "linear_f32_acc64", "gemm_bf16", "swiglu_bf16", "gemm_fp8_scaled",
-    "gemm_s8s8_s32", "s4gemmx", "s4gemvx", "xgemmx", "sgemvx_f64", "internal_mm_f32", "bf16_to_f32", "f32_to_bf16",
+    "gemm_s8s8_s32", "s4gemmx", "s4gemvx", "xgemmx", "sgemvx_f64", "cgemmx", "cgemvx", "internal_mm_f32", "bf16_to_f32", "f32_to_bf16",
     "e4m3_to_f32", "f32_to_e4m3", "num_threads", "set_num_threads",
 ]
 
@@ -179,6 +179,34 @@ def sgemvx_f64(M, N, alpha, A, inc1a, inc2a, X, incx, beta, Y, incy):
     D = ctypes.c_double
     lib().o64ref_sgemvx_f64(I(M), I(N), D(alpha), _p(np.ascontiguousarray(A)), I(inc1a), I(inc2a),
                             _p(np.ascontiguousarray(X)), I(incx), D(beta), _p(Y), I(incy))
+    return Y
+
+
+def _cpair(z, dt):
+    return np.array([complex(z).real, complex(z).imag], dtype=dt)
+
+
+def cgemmx(M, N, K, alpha, A, inc1a, inc2a, B, inc1b, inc2b, beta, C, inc1c, inc2c, conja=False, conjb=False):
+    """The complex strided kernel (complex64: c4gemmx, complex128: cgemmx), in place on the flat
+    array C; increments in complex elements."""
+    assert A.dtype == B.dtype == C.dtype and C.dtype in (np.complex64, np.complex128) and C.flags.c_contiguous
+    single = C.dtype == np.complex64
+    rt = np.float32 if single else np.float64
+    fn = lib().o64ref_c4gemmx if single else lib().o64ref_cgemmx
+    al, be = _cpair(alpha, rt), _cpair(beta, rt)
+    fn(I(int(conja)), I(int(conjb)), I(M), I(N), I(K), _p(al), _p(np.ascontiguousarray(A)), I(inc1a), I(inc2a),
+       _p(np.ascontiguousarray(B)), I(inc1b), I(inc2b), _p(be), _p(C), I(inc1c), I(inc2c))
+    return C
+
+
+def cgemvx(M, N, alpha, A, inc1a, inc2a, X, incx, beta, Y, incy, conj=False):
+    assert A.dtype == X.dtype == Y.dtype and Y.dtype in (np.complex64, np.complex128) and Y.flags.c_contiguous
+    single = Y.dtype == np.complex64
+    rt = np.float32 if single else np.float64
+    fn = lib().o64ref_c4gemvx if single else lib().o64ref_cgemvx
+    al, be = _cpair(alpha, rt), _cpair(beta, rt)
+    fn(I(int(conj)), I(M), I(N), _p(al), _p(np.ascontiguousarray(A)), I(inc1a), I(inc2a),
+       _p(np.ascontiguousarray(X)), I(incx), _p(be), _p(Y), I(incy))
     return Y
 
 

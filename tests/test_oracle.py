@@ -183,3 +183,23 @@ def test_sgemvx_f64_against_numpy():
     a, x, y0 = rng.standard_normal(m * n), rng.standard_normal(n), rng.standard_normal(m)
     y = oracle.sgemvx_f64(m, n, 0.5, a, 1, m, x, 1, 2.0, y0.copy(), 1)
     assert relmax(y, 0.5 * (a.reshape(n, m).T @ x) + 2.0 * y0) < 1e-14
+
+
+@pytest.mark.parametrize("dtype", [np.complex64, np.complex128])
+def test_complex_kernels_against_numpy(dtype):
+    rng = np.random.default_rng(21)
+    m, n, k = 11, 7, 13
+    cplx = lambda size: (rng.standard_normal(size) + 1j * rng.standard_normal(size)).astype(dtype)
+    a, b, c0 = cplx(m * k), cplx(k * n), cplx(m * n)
+    A, B, C0 = a.reshape(k, m).T, b.reshape(n, k).T, c0.reshape(n, m).T          # column-major views
+    tol = 1e-5 if dtype is np.complex64 else 1e-13
+    for conja, conjb in ((False, False), (True, False), (False, True), (True, True)):
+        c = oracle.cgemmx(m, n, k, 0.5 - 2j, a, 1, m, b, 1, k, 1.5 + 0.25j, c0.copy(), 1, m, conja, conjb)
+        want = (0.5 - 2j) * ((A.conj() if conja else A) @ (B.conj() if conjb else B)) + (1.5 + 0.25j) * C0
+        assert np.abs(c.reshape(n, m).T - want).max() / np.abs(want).max() < tol
+    assert not oracle.cgemmx(m, n, 0, 1.0, a, 1, m, b, 1, k, 3.0, c0.copy(), 1, m).any()   # K = 0: zeroed
+    x, y0 = cplx(k), cplx(m)
+    for conj in (False, True):
+        y = oracle.cgemvx(m, k, 2.0 + 1j, a, 1, m, x, 1, -1j, y0.copy(), 1, conj)
+        want = (2.0 + 1j) * ((A.conj() if conj else A) @ x) + (-1j) * y0
+        assert np.abs(y - want).max() / np.abs(want).max() < tol

@@ -436,6 +436,60 @@ void zgemm_(const char *transa, const char *transb, const int *m, const int *n, 
 void _MATMUL_C4C4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
 void _MATMUL_CC(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
 
+/* ---- LOGICAL kinds ------------------------------------------------------------------------
+ * C(i,j) = (beta .AND. C(i,j)) .OR. (alpha .AND. OR over l of A(i,l) .AND. B(l,j)), the template
+ * osprey/libfi/matrix/lgemmx.h instantiated by l1gemmx.f, l1l2gemmx.f, ... lgemmx.f: A of the same or
+ * a narrower kind than B, C, alpha and beta; 1-, 2-, 4- and 8-byte logicals are carried as integers of
+ * that width, any non-zero value is true, results are 1 or 0.  K == 0 clears C. */
+void _l1gemmx__(const int *m, const int *n, const int *k, const int8_t *alpha, const int8_t *a,
+                const int *inc1a, const int *inc2a, const int8_t *b, const int *inc1b, const int *inc2b,
+                const int8_t *beta, int8_t *c, const int *inc1c, const int *inc2c);
+void _l1l2gemmx__(const int *m, const int *n, const int *k, const int16_t *alpha, const int8_t *a,
+                  const int *inc1a, const int *inc2a, const int16_t *b, const int *inc1b, const int *inc2b,
+                  const int16_t *beta, int16_t *c, const int *inc1c, const int *inc2c);
+void _l1l4gemmx__(const int *m, const int *n, const int *k, const int32_t *alpha, const int8_t *a,
+                  const int *inc1a, const int *inc2a, const int32_t *b, const int *inc1b, const int *inc2b,
+                  const int32_t *beta, int32_t *c, const int *inc1c, const int *inc2c);
+void _l1lgemmx__(const int *m, const int *n, const int *k, const int64_t *alpha, const int8_t *a,
+                 const int *inc1a, const int *inc2a, const int64_t *b, const int *inc1b, const int *inc2b,
+                 const int64_t *beta, int64_t *c, const int *inc1c, const int *inc2c);
+void _l2gemmx__(const int *m, const int *n, const int *k, const int16_t *alpha, const int16_t *a,
+                const int *inc1a, const int *inc2a, const int16_t *b, const int *inc1b, const int *inc2b,
+                const int16_t *beta, int16_t *c, const int *inc1c, const int *inc2c);
+void _l2l4gemmx__(const int *m, const int *n, const int *k, const int32_t *alpha, const int16_t *a,
+                  const int *inc1a, const int *inc2a, const int32_t *b, const int *inc1b, const int *inc2b,
+                  const int32_t *beta, int32_t *c, const int *inc1c, const int *inc2c);
+void _l2lgemmx__(const int *m, const int *n, const int *k, const int64_t *alpha, const int16_t *a,
+                 const int *inc1a, const int *inc2a, const int64_t *b, const int *inc1b, const int *inc2b,
+                 const int64_t *beta, int64_t *c, const int *inc1c, const int *inc2c);
+void _l4gemmx__(const int *m, const int *n, const int *k, const int32_t *alpha, const int32_t *a,
+                const int *inc1a, const int *inc2a, const int32_t *b, const int *inc1b, const int *inc2b,
+                const int32_t *beta, int32_t *c, const int *inc1c, const int *inc2c);
+void _l4lgemmx__(const int *m, const int *n, const int *k, const int64_t *alpha, const int32_t *a,
+                 const int *inc1a, const int *inc2a, const int64_t *b, const int *inc1b, const int *inc2b,
+                 const int64_t *beta, int64_t *c, const int *inc1c, const int *inc2c);
+void _lgemmx__(const int *m, const int *n, const int *k, const int64_t *alpha, const int64_t *a,
+               const int *inc1a, const int *inc2a, const int64_t *b, const int *inc1b, const int *inc2b,
+               const int64_t *beta, int64_t *c, const int *inc1c, const int *inc2c);
+/* MATMUL on LOGICAL arrays (matmul_l1l1.c ... matmul_ll@.c): alpha = .TRUE., beta = .FALSE.; the wider
+ * operand first means C' = B'A' as for the integer kinds. */
+void _MATMUL_L1L1(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_L1L2(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_L1L4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_L1L(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_L2L1(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_L2L2(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_L2L4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_L2L(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_L4L1(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_L4L2(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_L4L4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_L4L(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_LL1(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_LL2(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_LL4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_LL(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+
 /* Status of the last compat call on this thread (the Fortran entry points return void). */
 int o64_compat_last_status(void);
 

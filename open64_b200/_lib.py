@@ -30,6 +30,9 @@ EXPORTS = [
     "_MATMUL_I1I1", "_MATMUL_I1I2", "_MATMUL_I1I4", "_MATMUL_I1J", "_MATMUL_I2I1", "_MATMUL_I2I2", "_MATMUL_I2I4",
     "_MATMUL_I2J", "_MATMUL_I4I1", "_MATMUL_I4I2", "_MATMUL_I4I4", "_MATMUL_I4J", "_MATMUL_JI1", "_MATMUL_JI2",
     "_MATMUL_JI4", "_MATMUL_JJ",
+    "_l1gemmx__", "_l1l2gemmx__", "_l1l4gemmx__", "_l1lgemmx__", "_l2gemmx__", "_l2l4gemmx__", "_l2lgemmx__", "_l4gemmx__", "_l4lgemmx__", "_lgemmx__",
+    "_MATMUL_L1L1", "_MATMUL_L1L2", "_MATMUL_L1L4", "_MATMUL_L1L", "_MATMUL_L2L1", "_MATMUL_L2L2", "_MATMUL_L2L4", "_MATMUL_L2L",
+    "_MATMUL_L4L1", "_MATMUL_L4L2", "_MATMUL_L4L4", "_MATMUL_L4L", "_MATMUL_LL1", "_MATMUL_LL2", "_MATMUL_LL4", "_MATMUL_LL",
     "_c4gemmx__", "_cgemmx__", "_c4gemvx__", "_cgemvx__", "cgemm_", "zgemm_", "_MATMUL_C4C4", "_MATMUL_CC",
     "_s4sgemmx__", "_i1s4gemmx__", "_i2s4gemmx__", "_i4s4gemmx__", "_js4gemmx__", "_i1sgemmx__", "_i2sgemmx__", "_i4sgemmx__", "_jsgemmx__",
     "_MATMUL_S4S", "_MATMUL_SS4", "_MATMUL_I1S4", "_MATMUL_S4I1", "_MATMUL_I1S", "_MATMUL_SI1", "_MATMUL_I2S4", "_MATMUL_S4I2", "_MATMUL_I2S", "_MATMUL_SI2", "_MATMUL_I4S4", "_MATMUL_S4I4", "_MATMUL_I4S", "_MATMUL_SI4", "_MATMUL_JS4", "_MATMUL_S4J", "_MATMUL_JS", "_MATMUL_SJ",
@@ -59,6 +62,7 @@ class DopeVector(ctypes.Structure):
                 ("flags1", ctypes.c_uint32), ("type_pad", ctypes.c_uint32), ("type_bits", ctypes.c_uint32),
                 ("orig_base", ctypes.c_void_p), ("orig_size", ctypes.c_ulong), ("dimension", DvDimen * 7)]
 
+    TYPE_LOGICAL = 5
     TYPE_INTEGER, TYPE_REAL, TYPE_COMPLEX = 2, 3, 4  # osprey/clibinc/cray/dopevec.h: DVTYPE_INTEGER, _REAL, _COMPLEX
 
     @classmethod

@@ -1074,6 +1074,58 @@ O64_XGEMMX_ENTRY(_i4sgemmx__, int32_t, double)
 O64_XGEMMX_ENTRY(_jsgemmx__, int64_t, double)
 #undef O64_XGEMMX_ENTRY
 
+// LOGICAL kinds (osprey/libfi/matrix/lgemmx.h:  quick returns in its order: empty extents; K == 0 clears
+// C; alpha false leaves C, or clears it when beta is false too).
+template <typename TA, typename T>
+static int lgemmx_impl(int M, int N, int K, bool alpha, const TA *A, int64_t a1, int64_t a2, const T *B, int64_t b1,
+                       int64_t b2, bool beta, T *C, int64_t c1, int64_t c2) {
+    if (M < 0 || N < 0 || K < 0) return O64_ERR_RANK;
+    if (M == 0 || N == 0) return O64_OK;
+    if (K > 0 && !alpha && beta) return O64_OK;
+    if (a1 < 0 || a2 < 0 || b1 < 0 || b2 < 0 || c1 < 0 || c2 < 0) return O64_ERR_RANK;
+    o64_handle_t h = compat_handle();
+    if (!h) return O64_ERR_CUDA;
+    DeviceGuard g(h->device);
+    cudaStream_t s = nullptr;
+    const bool clear_only = (K == 0) || !alpha;
+    const void *dA = A, *dB = B;
+    StagedOut out;
+    int rc;
+    if (!clear_only) {
+        if (!A || !B) return O64_ERR_RANK;
+        if ((rc = stage_in(h, 0, A, strided_span(M, K, a1, a2) * sizeof(TA), s, &dA))) return rc;
+        if ((rc = stage_in(h, 1, B, strided_span(K, N, b1, b2) * sizeof(T), s, &dB))) return rc;
+    }
+    if (!C) return O64_ERR_RANK;
+    if ((rc = stage_out_begin(h, 3, C, strided_span(M, N, c1, c2) * sizeof(T), true, s, &out))) return rc;
+    // clearing is the product with alpha and beta false
+    rc = logical_gemmx<TA, T>(M, N, clear_only ? 0 : K, clear_only ? 0 : 1, (const TA *)dA, a1, a2, (const T *)dB, b1, b2,
+                              clear_only ? 0 : (beta ? 1 : 0), (T *)out.dev, c1, c2, s);
+    if (rc) return rc;
+    if ((rc = stage_out_end(out, s))) return rc;
+    if (!out.host) CUDA_TRY(cudaStreamSynchronize(s));
+    return O64_OK;
+}
+
+#define O64_LGEMMX_ENTRY(NAME, TA, T)                                                                      \
+    extern "C" void NAME(const int *m, const int *n, const int *k, const T *alpha, const TA *a,            \
+                         const int *inc1a, const int *inc2a, const T *b, const int *inc1b,                 \
+                         const int *inc2b, const T *beta, T *c, const int *inc1c, const int *inc2c) {      \
+        g_compat_status = lgemmx_impl<TA, T>(*m, *n, *k, *alpha != 0, a, *inc1a, *inc2a, b, *inc1b, *inc2b, \
+                                             *beta != 0, c, *inc1c, *inc2c);                               \
+    }
+O64_LGEMMX_ENTRY(_l1gemmx__, int8_t, int8_t)
+O64_LGEMMX_ENTRY(_l1l2gemmx__, int8_t, int16_t)
+O64_LGEMMX_ENTRY(_l1l4gemmx__, int8_t, int32_t)
+O64_LGEMMX_ENTRY(_l1lgemmx__, int8_t, int64_t)
+O64_LGEMMX_ENTRY(_l2gemmx__, int16_t, int16_t)
+O64_LGEMMX_ENTRY(_l2l4gemmx__, int16_t, int32_t)
+O64_LGEMMX_ENTRY(_l2lgemmx__, int16_t, int64_t)
+O64_LGEMMX_ENTRY(_l4gemmx__, int32_t, int32_t)
+O64_LGEMMX_ENTRY(_l4lgemmx__, int32_t, int64_t)
+O64_LGEMMX_ENTRY(_lgemmx__, int64_t, int64_t)
+#undef O64_LGEMMX_ENTRY
+
 // COMPLEX*8 / COMPLEX*16: the kernels take conjugation flags in front (osprey/libfi/matrix/c4gemmx.f:37-85,
 // cgemmx.f); complex values are (re, im) pairs of floats / doubles.
 #define O64_CGEMMX_ENTRY(NAME, R)                                                                          \
@@ -1254,7 +1306,7 @@ DvView view_of(const o64_dopevec_t *d) {
 //     matrix kernel with m, n, k of matmul.h:325-363 (matmul_i4i4.c:84-86).
 //   swapped: MATRIX_A is the wider kind, so the product is formed as C' = B'A' with every pair of
 //     increments exchanged (matmul_i2i1.c:82-84, matmul_i4i1.c:83-85, matmul_ji4.c).
-template <typename TN, typename T>
+template <typename TN, typename T, bool LOGICAL = false>
 int matmul_impl(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B, bool use_gemv,
                 bool swapped) {
     if (!RESULT || !MATRIX_A || !MATRIX_B) return O64_ERR_RANK;
@@ -1318,6 +1370,13 @@ int matmul_impl(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *M
         }
         m = 1, n = (int)b.n2, k = (int)b.n1;
     }
+    if constexpr (LOGICAL) {  // alpha = .TRUE., beta = .FALSE. (matmul_ll@.c:92-94)
+        if (swapped)
+            return lgemmx_impl<TN, T>(n, m, k, true, static_cast<const TN *>(b.ptr), b.inc2, b.inc1,
+                                      static_cast<const T *>(a.ptr), a.inc2, a.inc1, false, C, c.inc2, c.inc1);
+        return lgemmx_impl<TN, T>(m, n, k, true, static_cast<const TN *>(a.ptr), a.inc1, a.inc2,
+                                  static_cast<const T *>(b.ptr), b.inc1, b.inc2, false, C, c.inc1, c.inc2);
+    }
     if (swapped)
         return xgemmx_impl<TN, T>(n, m, k, one, static_cast<const TN *>(b.ptr), b.inc2, b.inc1,
                                   static_cast<const T *>(a.ptr), a.inc2, a.inc1, zero, C, c.inc2, c.inc1, true);
@@ -1370,3 +1429,25 @@ O64_MATMUL_ENTRY(_MATMUL_S4J, int64_t, float, false, true)
 O64_MATMUL_ENTRY(_MATMUL_JS, int64_t, double, false, false)
 O64_MATMUL_ENTRY(_MATMUL_SJ, int64_t, double, false, true)
 #undef O64_MATMUL_ENTRY
+// LOGICAL arrays: every pair of the four kinds, result of the wider kind (matmul_l1l1.c ... matmul_ll@.c)
+#define O64_LMATMUL_ENTRY(NAME, TN, T, SWAPPED)                                                           \
+    extern "C" void NAME(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B) {       \
+        g_compat_status = matmul_impl<TN, T, true>(RESULT, MATRIX_A, MATRIX_B, false, SWAPPED);           \
+    }
+O64_LMATMUL_ENTRY(_MATMUL_L1L1, int8_t, int8_t, false)
+O64_LMATMUL_ENTRY(_MATMUL_L1L2, int8_t, int16_t, false)
+O64_LMATMUL_ENTRY(_MATMUL_L1L4, int8_t, int32_t, false)
+O64_LMATMUL_ENTRY(_MATMUL_L1L, int8_t, int64_t, false)
+O64_LMATMUL_ENTRY(_MATMUL_L2L1, int8_t, int16_t, true)
+O64_LMATMUL_ENTRY(_MATMUL_L2L2, int16_t, int16_t, false)
+O64_LMATMUL_ENTRY(_MATMUL_L2L4, int16_t, int32_t, false)
+O64_LMATMUL_ENTRY(_MATMUL_L2L, int16_t, int64_t, false)
+O64_LMATMUL_ENTRY(_MATMUL_L4L1, int8_t, int32_t, true)
+O64_LMATMUL_ENTRY(_MATMUL_L4L2, int16_t, int32_t, true)
+O64_LMATMUL_ENTRY(_MATMUL_L4L4, int32_t, int32_t, false)
+O64_LMATMUL_ENTRY(_MATMUL_L4L, int32_t, int64_t, false)
+O64_LMATMUL_ENTRY(_MATMUL_LL1, int8_t, int64_t, true)
+O64_LMATMUL_ENTRY(_MATMUL_LL2, int16_t, int64_t, true)
+O64_LMATMUL_ENTRY(_MATMUL_LL4, int32_t, int64_t, true)
+O64_LMATMUL_ENTRY(_MATMUL_LL, int64_t, int64_t, false)
+#undef O64_LMATMUL_ENTRY

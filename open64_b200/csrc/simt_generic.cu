@@ -140,6 +140,45 @@ int generic_scale(int64_t M, int64_t N, T beta, T *C, int64_t c1, int64_t c2, cu
     return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
 }
 
+// LOGICAL kinds (osprey/libfi/matrix/lgemmx.h): C(i,j) = (beta .AND. C(i,j)) .OR. (alpha .AND. OR over l of
+// A(i,l) .AND. B(l,j)); any non-zero value is true, results are stored as 1 / 0.  One thread per
+// result element: a logical MATMUL is rare and small.
+template <typename TA, typename T>
+__global__ void lgemmx_kernel(long long M, long long N, long long K, int alpha, const TA *A, long long a1, long long a2,
+                              const T *B, long long b1, long long b2, int beta, T *C, long long c1, long long c2) {
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= M * N) return;
+    const long long i = e % M, j = e / M;
+    T *c = C + i * c1 + j * c2;
+    bool acc = beta && (*c != T(0));
+    if (alpha)
+        for (long long l = 0; l < K && !acc; ++l) acc = (B[l * b1 + j * b2] != T(0)) && (A[i * a1 + l * a2] != TA(0));
+    *c = acc ? T(1) : T(0);
+}
+
+template <typename TA, typename T>
+int logical_gemmx(int64_t M, int64_t N, int64_t K, int alpha, const TA *A, int64_t a1, int64_t a2, const T *B,
+                  int64_t b1, int64_t b2, int beta, T *C, int64_t c1, int64_t c2, cudaStream_t s) {
+    if (M <= 0 || N <= 0) return O64_OK;
+    const long long total = (long long)M * N;
+    lgemmx_kernel<TA, T><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(M, N, K, alpha, A, a1, a2, B, b1, b2, beta, C, c1, c2);
+    return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
+}
+#define O64_INSTANTIATE_LGEMMX(TA, T)                                                                          \
+    template int logical_gemmx<TA, T>(int64_t, int64_t, int64_t, int, const TA *, int64_t, int64_t, const T *,    \
+                                      int64_t, int64_t, int, T *, int64_t, int64_t, cudaStream_t);
+O64_INSTANTIATE_LGEMMX(int8_t, int8_t)
+O64_INSTANTIATE_LGEMMX(int8_t, int16_t)
+O64_INSTANTIATE_LGEMMX(int8_t, int32_t)
+O64_INSTANTIATE_LGEMMX(int8_t, int64_t)
+O64_INSTANTIATE_LGEMMX(int16_t, int16_t)
+O64_INSTANTIATE_LGEMMX(int16_t, int32_t)
+O64_INSTANTIATE_LGEMMX(int16_t, int64_t)
+O64_INSTANTIATE_LGEMMX(int32_t, int32_t)
+O64_INSTANTIATE_LGEMMX(int32_t, int64_t)
+O64_INSTANTIATE_LGEMMX(int64_t, int64_t)
+#undef O64_INSTANTIATE_LGEMMX
+
 #define O64_INSTANTIATE_GEMMX(TA, T)                                                                          \
     template int generic_gemmx<TA, T>(int64_t, int64_t, int64_t, T, const TA *, int64_t, int64_t, const T *,     \
                                       int64_t, int64_t, T, T *, int64_t, int64_t, cudaStream_t, int, int);

@@ -80,6 +80,11 @@ int generic_gemvx(int64_t M, int64_t N, T alpha, const T *A, int64_t a1, int64_t
 template <typename T>
 int generic_scale(int64_t M, int64_t N, T beta, T *C, int64_t c1, int64_t c2, cudaStream_t s);
 
+// LOGICAL kinds: C = (beta AND C) OR (alpha AND (A AND B, OR-reduced over K)); non-zero is true.
+template <typename TA, typename T>
+int logical_gemmx(int64_t M, int64_t N, int64_t K, int alpha, const TA *A, int64_t a1, int64_t a2, const T *B,
+                  int64_t b1, int64_t b2, int beta, T *C, int64_t c1, int64_t c2, cudaStream_t s);
+
 // Fills a buffer with pseudo-random finite values of the kind (bf16 / e4m3 / int8): operands for timing runs.
 int fill_pattern(void *p, size_t bytes, int kind, cudaStream_t stream);
 

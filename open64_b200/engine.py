@@ -374,3 +374,18 @@ class Engine:
            _ptr(b), r(ldb), ctypes.cast(be, ctypes.c_void_p), _ptr(c), r(ldc))
         check(self.lib.o64_compat_last_status(), "cgemm_")
         return c
+
+    _LTYPES = {"l1": ctypes.c_int8, "l2": ctypes.c_int16, "l4": ctypes.c_int32, "l": ctypes.c_int64}
+
+    def lgemmx(self, kind, m, n, k, alpha, a, inc1a, inc2a, b, inc1b, inc2b, beta, c, inc1c, inc2c):
+        """The LOGICAL strided kernel `_<kind>gemmx__`: kind "l1", "l2", "l4", "l" or a pair "l1l2" ... "l4l"
+        (A of the first kind; B, C, alpha, beta of the second); logicals are integer tensors, non-zero is true."""
+        ckind = kind if kind in self._LTYPES else next(sfx for sfx in ("l1", "l2", "l4", "l")
+                                                        if kind.endswith(sfx) and kind[:-len(sfx)] in self._LTYPES)
+        ct = self._LTYPES[ckind]
+        r = lambda v: ctypes.byref(ctypes.c_int(v))
+        getattr(self.lib, "_%sgemmx__" % kind)(r(m), r(n), r(k), ctypes.byref(ct(1 if alpha else 0)), _ptr(a), r(inc1a),
+                                               r(inc2a), _ptr(b), r(inc1b), r(inc2b), ctypes.byref(ct(1 if beta else 0)),
+                                               _ptr(c), r(inc1c), r(inc2c))
+        check(self.lib.o64_compat_last_status(), "_%sgemmx__" % kind)
+        return c

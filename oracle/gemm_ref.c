@@ -409,6 +409,41 @@ void o64ref_sgemvx_f64(int M, int N, double alpha, const double *A, int inc1a, i
     }
 }
 
+/* ---- LOGICAL kinds (lgemmx.h): non-zero is true, results are 1 / 0 ------------------------------ */
+#define O64REF_LGEMMX(NAME, TA, T)                                                               \
+    void NAME(int M, int N, int K, int alpha, const TA *A, int inc1a, int inc2a, const T *B,     \
+              int inc1b, int inc2b, int beta, T *C, int inc1c, int inc2c) {                      \
+        if (M == 0 || N == 0) return;                                                            \
+        if (K == 0 || (!alpha && !beta)) {                                                       \
+            for (long j = 0; j < N; ++j)                                                         \
+                for (long i = 0; i < M; ++i) C[(long)inc2c * j + (long)inc1c * i] = 0;           \
+            return;                                                                              \
+        }                                                                                        \
+        if (!alpha) return;                                                                      \
+        for (long j = 0; j < N; ++j) {                                                           \
+            for (long i = 0; i < M; ++i) {                                                       \
+                T *c = C + (long)inc2c * j + (long)inc1c * i;                                    \
+                *c = (beta && *c != 0) ? 1 : 0;                                                  \
+            }                                                                                    \
+            for (long l = 0; l < K; ++l) {                                                       \
+                if (B[(long)inc2b * j + (long)inc1b * l] == 0) continue;                         \
+                for (long i = 0; i < M; ++i)                                                     \
+                    if (A[(long)inc2a * l + (long)inc1a * i] != 0) C[(long)inc2c * j + (long)inc1c * i] = 1; \
+            }                                                                                    \
+        }                                                                                        \
+    }
+O64REF_LGEMMX(o64ref_l1gemmx, int8_t, int8_t)
+O64REF_LGEMMX(o64ref_l1l2gemmx, int8_t, int16_t)
+O64REF_LGEMMX(o64ref_l1l4gemmx, int8_t, int32_t)
+O64REF_LGEMMX(o64ref_l1lgemmx, int8_t, int64_t)
+O64REF_LGEMMX(o64ref_l2gemmx, int16_t, int16_t)
+O64REF_LGEMMX(o64ref_l2l4gemmx, int16_t, int32_t)
+O64REF_LGEMMX(o64ref_l2lgemmx, int16_t, int64_t)
+O64REF_LGEMMX(o64ref_l4gemmx, int32_t, int32_t)
+O64REF_LGEMMX(o64ref_l4lgemmx, int32_t, int64_t)
+O64REF_LGEMMX(o64ref_lgemmx, int64_t, int64_t)
+#undef O64REF_LGEMMX
+
 /* ---- COMPLEX*8 / COMPLEX*16 (c4gemmx.f:156-244, cgemmx.f; c4gemvx.f, cgemvx.f) -------------
  * Values are (re, im) pairs; increments count complex elements.  The matrix kernel applies the
  * conjugation flags and, unlike the real template, does not test B for zeros; the vector kernel

@@ -17,7 +17,7 @@ ACT_NONE, ACT_RELU, ACT_GELU_TANH, ACT_GELU_ERF, ACT_SILU = range(5)
 __all__ = [
     "ACT_NONE", "ACT_RELU", "ACT_GELU_TANH", "ACT_GELU_ERF", "ACT_SILU", "build", "lib",
     "linear_f32", "linear_f32_acc64", "gemm_bf16", "swiglu_bf16", "gemm_fp8_scaled",
-    "gemm_s8s8_s32", "s4gemmx", "s4gemvx", "xgemmx", "sgemvx_f64", "cgemmx", "cgemvx", "internal_mm_f32", "bf16_to_f32", "f32_to_bf16",
+    "gemm_s8s8_s32", "s4gemmx", "s4gemvx", "xgemmx", "sgemvx_f64", "cgemmx", "cgemvx", "lgemmx", "internal_mm_f32", "bf16_to_f32", "f32_to_bf16",
     "e4m3_to_f32", "f32_to_e4m3", "num_threads", "set_num_threads",
 ]
 
@@ -208,6 +208,17 @@ def cgemvx(M, N, alpha, A, inc1a, inc2a, X, incx, beta, Y, incy, conj=False):
     fn(I(int(conj)), I(M), I(N), _p(al), _p(np.ascontiguousarray(A)), I(inc1a), I(inc2a),
        _p(np.ascontiguousarray(X)), I(incx), _p(be), _p(Y), I(incy))
     return Y
+
+
+def lgemmx(M, N, K, alpha, A, inc1a, inc2a, B, inc1b, inc2b, beta, C, inc1c, inc2c):
+    """The LOGICAL strided kernel for the integer carrier kinds of (A, C) (l1gemmx ... l4lgemmx, lgemmx)."""
+    assert B.dtype == C.dtype and C.flags.c_contiguous and A.dtype.itemsize <= C.dtype.itemsize
+    lk = {1: "l1", 2: "l2", 4: "l4", 8: "l"}
+    ka, kc = lk[A.dtype.itemsize], lk[C.dtype.itemsize]
+    name = "o64ref_%s%sgemmx" % (ka, "" if ka == kc else kc)
+    getattr(lib(), name)(I(M), I(N), I(K), I(int(bool(alpha))), _p(np.ascontiguousarray(A)), I(inc1a), I(inc2a),
+                         _p(np.ascontiguousarray(B)), I(inc1b), I(inc2b), I(int(bool(beta))), _p(C), I(inc1c), I(inc2c))
+    return C
 
 
 def internal_mm_f32(A_colmajor, B_colmajor, M, N, K):

@@ -203,3 +203,18 @@ def test_complex_kernels_against_numpy(dtype):
         y = oracle.cgemvx(m, k, 2.0 + 1j, a, 1, m, x, 1, -1j, y0.copy(), 1, conj)
         want = (2.0 + 1j) * ((A.conj() if conj else A) @ x) + (-1j) * y0
         assert np.abs(y - want).max() / np.abs(want).max() < tol
+
+
+def test_logical_kernel_against_numpy():
+    rng = np.random.default_rng(31)
+    m, n, k = 9, 14, 22
+    a = ((rng.random(m * k) < 0.1) * rng.integers(1, 50, m * k)).astype(np.int8)
+    b = ((rng.random(k * n) < 0.1) * -rng.integers(1, 50, k * n)).astype(np.int32)
+    c0 = (rng.random(m * n) < 0.3).astype(np.int32) * 5
+    A, B, C0 = a.reshape(k, m).T != 0, b.reshape(n, k).T != 0, c0.reshape(n, m).T != 0
+    prod = (A.astype(int) @ B.astype(int)) > 0
+    for alpha, beta, want in ((1, 0, prod), (1, 1, prod | C0), (0, 0, np.zeros_like(prod))):
+        c = oracle.lgemmx(m, n, k, alpha, a, 1, m, b, 1, k, beta, c0.copy(), 1, m)
+        assert np.array_equal(c.reshape(n, m).T, want.astype(np.int32))
+    assert np.array_equal(oracle.lgemmx(m, n, k, 0, a, 1, m, b, 1, k, 1, c0.copy(), 1, m), c0)   # untouched
+    assert not oracle.lgemmx(m, n, 0, 1, a, 1, m, b, 1, k, 1, c0.copy(), 1, m).any()

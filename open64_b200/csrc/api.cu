@@ -10,6 +10,7 @@
 #include <cstring>
 #include <array>
 #include <map>
+#include <mutex>
 #include <new>
 #include <type_traits>
 #include <vector>
@@ -956,7 +957,13 @@ static o64_handle_t g_compat_handle = nullptr;
 
 extern "C" int o64_compat_last_status(void) { return g_compat_status; }
 
+// One engine handle for all Fortran-ABI calls of the process, on the device that is current at the
+// first call.  Its creation is guarded; the calls themselves share the handle's staging buffers and
+// are not thread-safe (the runtime they replace has no locks either).
+static std::mutex g_compat_mutex;
+
 static o64_handle_t compat_handle() {
+    std::lock_guard<std::mutex> lock(g_compat_mutex);
     if (!g_compat_handle) {
         int dev = 0;
         if (cudaGetDevice(&dev) != cudaSuccess) {

@@ -436,6 +436,40 @@ void zgemm_(const char *transa, const char *transb, const int *m, const int *n, 
 void _MATMUL_C4C4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
 void _MATMUL_CC(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
 
+/* COMPLEX with a REAL or INTEGER operand, or with COMPLEX of the other width: the 26 entry points
+ * osprey/libfi/matrix/matmul_c4s4.c, matmul_s4c4.c, matmul_c4i1.c ... matmul_jc@.c, matmul_c4c.c and
+ * matmul_cc4.c.  The result is COMPLEX*8 when both operands are 4 bytes per component or INTEGER
+ * with COMPLEX*8, COMPLEX*16 otherwise.  As in the reference the real and imaginary parts are
+ * separate products of the REAL kernel for the pair of component kinds (_s4gemmx__, _s4sgemmx__,
+ * _sgemmx__, _i1s4gemmx__ ... _jsgemmx__) with the increments of the COMPLEX arrays doubled; four
+ * products when both operands are COMPLEX (matmul_c4c.c:88-128). */
+void _MATMUL_C4S4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_S4C4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_C4S(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_SC4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_CS4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_S4C(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_CS(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_SC(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_C4C(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_CC4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_C4I1(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_C4I2(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_C4I4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_C4J(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I1C4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I2C4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I4C4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_JC4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_CI1(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_CI2(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_CI4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_CJ(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I1C(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I2C(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_I4C(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+void _MATMUL_JC(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
+
 /* ---- LOGICAL kinds ------------------------------------------------------------------------
  * C(i,j) = (beta .AND. C(i,j)) .OR. (alpha .AND. OR over l of A(i,l) .AND. B(l,j)), the template
  * osprey/libfi/matrix/lgemmx.h instantiated by l1gemmx.f, l1l2gemmx.f, ... lgemmx.f: A of the same or

@@ -36,6 +36,9 @@ EXPORTS = [
     "_c4gemmx__", "_cgemmx__", "_c4gemvx__", "_cgemvx__", "cgemm_", "zgemm_", "_MATMUL_C4C4", "_MATMUL_CC",
     "_s4sgemmx__", "_i1s4gemmx__", "_i2s4gemmx__", "_i4s4gemmx__", "_js4gemmx__", "_i1sgemmx__", "_i2sgemmx__", "_i4sgemmx__", "_jsgemmx__",
     "_MATMUL_S4S", "_MATMUL_SS4", "_MATMUL_I1S4", "_MATMUL_S4I1", "_MATMUL_I1S", "_MATMUL_SI1", "_MATMUL_I2S4", "_MATMUL_S4I2", "_MATMUL_I2S", "_MATMUL_SI2", "_MATMUL_I4S4", "_MATMUL_S4I4", "_MATMUL_I4S", "_MATMUL_SI4", "_MATMUL_JS4", "_MATMUL_S4J", "_MATMUL_JS", "_MATMUL_SJ",
+    "_MATMUL_C4S4", "_MATMUL_S4C4", "_MATMUL_C4S", "_MATMUL_SC4", "_MATMUL_CS4", "_MATMUL_S4C", "_MATMUL_CS", "_MATMUL_SC", "_MATMUL_C4C",
+    "_MATMUL_CC4", "_MATMUL_C4I1", "_MATMUL_C4I2", "_MATMUL_C4I4", "_MATMUL_C4J", "_MATMUL_I1C4", "_MATMUL_I2C4", "_MATMUL_I4C4", "_MATMUL_JC4",
+    "_MATMUL_CI1", "_MATMUL_CI2", "_MATMUL_CI4", "_MATMUL_CJ", "_MATMUL_I1C", "_MATMUL_I2C", "_MATMUL_I4C", "_MATMUL_JC",
 ]
 
 

@@ -1304,26 +1304,23 @@ DvView view_of(const o64_dopevec_t *d) {
     return v;
 }
 
-// One MATMUL entry point of the runtime: parse the dope vectors and allocate an unassociated
-// RESULT as _premult does (matmul.h:135-400), then call the strided kernels the way the entry
-// point of that type does.  TN: the narrower (or equal) operand kind, T: the kind of the other
-// operand and of the result.
-//   use_gemv: the real kinds send the rank-1 cases to the matrix-vector kernel
-//     (matmul_s4s4.c:86-104, matmul_ss@.c:100-117); the integer kinds send all three cases to the
-//     matrix kernel with m, n, k of matmul.h:325-363 (matmul_i4i4.c:84-86).
-//   swapped: MATRIX_A is the wider kind, so the product is formed as C' = B'A' with every pair of
-//     increments exchanged (matmul_i2i1.c:82-84, matmul_i4i1.c:83-85, matmul_ji4.c).
-template <typename TN, typename T, bool LOGICAL = false>
-int matmul_impl(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B, bool use_gemv,
-                bool swapped) {
+struct MatDims {
+    DvView a, b, c;
+    int m, n, k;
+};
+
+// The part of _premult every entry point shares: rank check, allocation of an unassociated
+// RESULT (matmul.h:222-266; default_bits is the result's element size where its type word gives
+// none), conformance checks and m, n, k (matmul.h:325-363).
+int matmul_premult(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B, unsigned default_bits,
+                   MatDims *d) {
     if (!RESULT || !MATRIX_A || !MATRIX_B) return O64_ERR_RANK;
     const DvView a = view_of(MATRIX_A), b = view_of(MATRIX_B);
     if (!((a.ndim == 1 && b.ndim == 2) || (a.ndim == 2 && b.ndim == 1) || (a.ndim == 2 && b.ndim == 2)))
         return O64_ERR_RANK;  // FESCIRNK
-    // allocate RESULT if it is not associated (matmul.h:222-266)
     if (!(RESULT->flags0 & 1u)) {
         unsigned int_len = (RESULT->type_bits >> 12) & 0xfffu;
-        if (int_len == 0) int_len = 8 * sizeof(T);
+        if (int_len == 0) int_len = default_bits;
         long stride0 = int_len / 32;
         if (stride0 == 0) stride0 = 1;
         RESULT->dimension[0].stride_mult = stride0;
@@ -1354,28 +1351,46 @@ int matmul_impl(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *M
         RESULT->orig_size = (unsigned long)nbits;
     }
     const DvView c = view_of(RESULT);
-    T *C = static_cast<T *>(c.ptr);
-    const T one = T(1), zero = T(0);
-    int m, n, k;
+    d->a = a, d->b = b, d->c = c;
     if (a.ndim == 2 && b.ndim == 2) {
         if (!(a.n2 == b.n1 && c.n1 == a.n1 && c.n2 == b.n2)) return O64_ERR_CONFORM;  // FESCICNF
-        m = (int)a.n1, n = (int)b.n2, k = (int)a.n2;
+        d->m = (int)a.n1, d->n = (int)b.n2, d->k = (int)a.n2;
     } else if (a.ndim == 2) {  // y = A x
         if (!(a.n2 == b.n1 && a.n1 == c.n1)) return O64_ERR_CONFORM;
-        if constexpr (std::is_floating_point<T>::value || IsCx<T>::value) {
-            if (use_gemv)
-                return xgemvx_impl<T>((int)a.n1, (int)a.n2, one, static_cast<const T *>(a.ptr), a.inc1, a.inc2,
-                                      static_cast<const T *>(b.ptr), b.inc1, zero, C, c.inc1);
-        }
-        m = (int)a.n1, n = 1, k = (int)a.n2;
-    } else {  // y = x B, i.e. y' = B' x'
+        d->m = (int)a.n1, d->n = 1, d->k = (int)a.n2;
+    } else {  // y = x B
         if (!(a.n1 == b.n1 && c.n1 == b.n2)) return O64_ERR_CONFORM;
-        if constexpr (std::is_floating_point<T>::value || IsCx<T>::value) {
-            if (use_gemv)
-                return xgemvx_impl<T>((int)b.n2, (int)b.n1, one, static_cast<const T *>(b.ptr), b.inc2, b.inc1,
-                                      static_cast<const T *>(a.ptr), a.inc1, zero, C, c.inc1);
-        }
-        m = 1, n = (int)b.n2, k = (int)b.n1;
+        d->m = 1, d->n = (int)b.n2, d->k = (int)b.n1;
+    }
+    return O64_OK;
+}
+
+// One MATMUL entry point of the runtime: parse the dope vectors and allocate an unassociated
+// RESULT as _premult does (matmul.h:135-400), then call the strided kernels the way the entry
+// point of that type does.  TN: the narrower (or equal) operand kind, T: the kind of the other
+// operand and of the result.
+//   use_gemv: the real kinds send the rank-1 cases to the matrix-vector kernel
+//     (matmul_s4s4.c:86-104, matmul_ss@.c:100-117); the integer kinds send all three cases to the
+//     matrix kernel with m, n, k of matmul.h:325-363 (matmul_i4i4.c:84-86).
+//   swapped: MATRIX_A is the wider kind, so the product is formed as C' = B'A' with every pair of
+//     increments exchanged (matmul_i2i1.c:82-84, matmul_i4i1.c:83-85, matmul_ji4.c).
+template <typename TN, typename T, bool LOGICAL = false>
+int matmul_impl(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B, bool use_gemv,
+                bool swapped) {
+    MatDims d;
+    const int rc_dims = matmul_premult(RESULT, MATRIX_A, MATRIX_B, 8 * sizeof(T), &d);
+    if (rc_dims) return rc_dims;
+    const DvView &a = d.a, &b = d.b, &c = d.c;
+    T *C = static_cast<T *>(c.ptr);
+    const T one = T(1), zero = T(0);
+    const int m = d.m, n = d.n, k = d.k;
+    if constexpr (std::is_floating_point<T>::value || IsCx<T>::value) {
+        if (use_gemv && a.ndim == 2 && b.ndim == 1)  // y = A x
+            return xgemvx_impl<T>((int)a.n1, (int)a.n2, one, static_cast<const T *>(a.ptr), a.inc1, a.inc2,
+                                  static_cast<const T *>(b.ptr), b.inc1, zero, C, c.inc1);
+        if (use_gemv && a.ndim == 1)  // y = x B, i.e. y' = B' x'
+            return xgemvx_impl<T>((int)b.n2, (int)b.n1, one, static_cast<const T *>(b.ptr), b.inc2, b.inc1,
+                                  static_cast<const T *>(a.ptr), a.inc1, zero, C, c.inc1);
     }
     if constexpr (LOGICAL) {  // alpha = .TRUE., beta = .FALSE. (matmul_ll@.c:92-94)
         if (swapped)
@@ -1437,6 +1452,80 @@ O64_MATMUL_ENTRY(_MATMUL_JS, int64_t, double, false, false)
 O64_MATMUL_ENTRY(_MATMUL_SJ, int64_t, double, false, true)
 #undef O64_MATMUL_ENTRY
 // LOGICAL arrays: every pair of the four kinds, result of the wider kind (matmul_l1l1.c ... matmul_ll@.c)
+// COMPLEX with a REAL or INTEGER operand, or with COMPLEX of the other width: real and imaginary
+// parts are separate products of the REAL kernel for the pair of component kinds, every increment
+// of a COMPLEX array doubled (osprey/libfi/matrix/matmul_c4s4.c:84-108, matmul_i1c4.c,
+// matmul_c4c.c:88-128).  TA / T: the kernel's first operand kind and its second operand / result
+// kind.  swapped: the kernel's first operand is MATRIX_B, so the product is formed as C' = B'A'
+// (matmul_c4i1.c:95-106, matmul_cs4.c, matmul_sc4.c, matmul_cc4.c).
+namespace {
+template <typename TA, typename T>
+int matmul_cx_impl(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B, bool a_cx, bool b_cx,
+                   bool swapped) {
+    MatDims d;
+    int rc = matmul_premult(RESULT, MATRIX_A, MATRIX_B, 16 * sizeof(T), &d);
+    if (rc) return rc;
+    const long fa = a_cx ? 2 : 1, fb = b_cx ? 2 : 1;
+    const long a1 = d.a.inc1 * fa, a2 = d.a.inc2 * fa, b1 = d.b.inc1 * fb, b2 = d.b.inc2 * fb;
+    const long c1 = d.c.inc1 * 2, c2 = d.c.inc2 * 2;
+    T *Cr = static_cast<T *>(d.c.ptr);
+    // part 0 / 1 of an operand: real / imaginary (a REAL or INTEGER operand has part 0 only)
+    auto mul = [&](T alpha, int part_a, int part_b, T beta, T *C) {
+        if (!swapped) {
+            const TA *A = static_cast<const TA *>(d.a.ptr);
+            const T *B = static_cast<const T *>(d.b.ptr);
+            return xgemmx_impl<TA, T>(d.m, d.n, d.k, alpha, A ? A + part_a : A, a1, a2, B ? B + part_b : B, b1, b2, beta,
+                                      C, c1, c2, true);
+        }
+        const TA *B = static_cast<const TA *>(d.b.ptr);
+        const T *A = static_cast<const T *>(d.a.ptr);
+        return xgemmx_impl<TA, T>(d.n, d.m, d.k, alpha, B ? B + part_b : B, b2, b1, A ? A + part_a : A, a2, a1, beta, C,
+                                  c2, c1, true);
+    };
+    T *Ci = Cr ? Cr + 1 : Cr;
+    if (a_cx && b_cx) {  // (Ar Br - Ai Bi) + (Ar Bi + Ai Br) i
+        if ((rc = mul(T(1), 0, 0, T(0), Cr))) return rc;
+        if ((rc = mul(T(-1), 1, 1, T(1), Cr))) return rc;
+        if ((rc = mul(T(1), 0, 1, T(0), Ci))) return rc;
+        return mul(T(1), 1, 0, T(1), Ci);
+    }
+    if ((rc = mul(T(1), 0, 0, T(0), Cr))) return rc;
+    return mul(T(1), a_cx ? 1 : 0, b_cx ? 1 : 0, T(0), Ci);
+}
+}  // namespace
+
+#define O64_CXMATMUL_ENTRY(NAME, TA, T, A_CX, B_CX, SWAPPED)                                              \
+    extern "C" void NAME(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B) {       \
+        g_compat_status = matmul_cx_impl<TA, T>(RESULT, MATRIX_A, MATRIX_B, A_CX, B_CX, SWAPPED);         \
+    }
+O64_CXMATMUL_ENTRY(_MATMUL_C4S4, float, float, true, false, false)
+O64_CXMATMUL_ENTRY(_MATMUL_S4C4, float, float, false, true, false)
+O64_CXMATMUL_ENTRY(_MATMUL_C4S, float, double, true, false, false)
+O64_CXMATMUL_ENTRY(_MATMUL_SC4, float, double, false, true, true)
+O64_CXMATMUL_ENTRY(_MATMUL_CS4, float, double, true, false, true)
+O64_CXMATMUL_ENTRY(_MATMUL_S4C, float, double, false, true, false)
+O64_CXMATMUL_ENTRY(_MATMUL_CS, double, double, true, false, false)
+O64_CXMATMUL_ENTRY(_MATMUL_SC, double, double, false, true, false)
+O64_CXMATMUL_ENTRY(_MATMUL_C4C, float, double, true, true, false)
+O64_CXMATMUL_ENTRY(_MATMUL_CC4, float, double, true, true, true)
+O64_CXMATMUL_ENTRY(_MATMUL_C4I1, int8_t, float, true, false, true)
+O64_CXMATMUL_ENTRY(_MATMUL_C4I2, int16_t, float, true, false, true)
+O64_CXMATMUL_ENTRY(_MATMUL_C4I4, int32_t, float, true, false, true)
+O64_CXMATMUL_ENTRY(_MATMUL_C4J, int64_t, float, true, false, true)
+O64_CXMATMUL_ENTRY(_MATMUL_I1C4, int8_t, float, false, true, false)
+O64_CXMATMUL_ENTRY(_MATMUL_I2C4, int16_t, float, false, true, false)
+O64_CXMATMUL_ENTRY(_MATMUL_I4C4, int32_t, float, false, true, false)
+O64_CXMATMUL_ENTRY(_MATMUL_JC4, int64_t, float, false, true, false)
+O64_CXMATMUL_ENTRY(_MATMUL_CI1, int8_t, double, true, false, true)
+O64_CXMATMUL_ENTRY(_MATMUL_CI2, int16_t, double, true, false, true)
+O64_CXMATMUL_ENTRY(_MATMUL_CI4, int32_t, double, true, false, true)
+O64_CXMATMUL_ENTRY(_MATMUL_CJ, int64_t, double, true, false, true)
+O64_CXMATMUL_ENTRY(_MATMUL_I1C, int8_t, double, false, true, false)
+O64_CXMATMUL_ENTRY(_MATMUL_I2C, int16_t, double, false, true, false)
+O64_CXMATMUL_ENTRY(_MATMUL_I4C, int32_t, double, false, true, false)
+O64_CXMATMUL_ENTRY(_MATMUL_JC, int64_t, double, false, true, false)
+#undef O64_CXMATMUL_ENTRY
+
 #define O64_LMATMUL_ENTRY(NAME, TN, T, SWAPPED)                                                           \
     extern "C" void NAME(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B) {       \
         g_compat_status = matmul_impl<TN, T, true>(RESULT, MATRIX_A, MATRIX_B, false, SWAPPED);           \

@@ -17,7 +17,8 @@
  *       REAL*8 (dgemm_, _sgemmx__, _sgemvx__, _MATMUL_SS), COMPLEX*8 / *16 (cgemm_, zgemm_,
  *       _c4gemmx__, _cgemmx__, _MATMUL_C4C4, _MATMUL_CC), every pair of integer kinds
  *       (_MATMUL_I1I1 ... _MATMUL_JJ over _i1gemmx__ ... _jgemmx__) and the real x real / integer x
- *       real pairs (_MATMUL_S4S, _MATMUL_I4S4, ...); in the runtime's naming "S" is the 64-bit
+ *       real pairs (_MATMUL_S4S, _MATMUL_I4S4, ...), and COMPLEX with any of those or with the
+ *       other COMPLEX width (_MATMUL_C4S4, _MATMUL_I1C4, _MATMUL_C4C, ...); in the runtime's naming "S" is the 64-bit
  *       real, "S4" the 32-bit one, "J" the 64-bit integer, "C" / "C4" the complex kinds
  *     Fortran ABI: every scalar by reference, synchronous, void.  Host or device
  *     pointers are accepted (host operands are staged through device memory).

@@ -21,7 +21,8 @@
 // may reassociate at -O3 (osprey/common/com/config.cxx:1670-1680); integer sums are exact in
 // any order.
 //
-// Warp roles as in umma_gemm.cu (192 threads): producer, MMA issuer, four epilogue warps.
+// Warp roles as in umma_gemm.cu (producer, MMA issuer, four epilogue warps) plus two warps that
+// only help with the exchange: 256 threads, two warps for each quarter of the TMEM lanes.
 // Every mbarrier wait is bounded; on expiry the CTA records a code and leaves its loops, but
 // still takes part in both cluster barriers, so that the other CTAs of its cluster return too.
 #include <cuda.h>
@@ -40,6 +41,7 @@ namespace {
 constexpr int kSkBlockN = 256;
 constexpr int kSkBBytes = kSkBlockN * kRowBytes;      // 32 KB of weight per stage
 constexpr int kSkMaxStages = 6;
+constexpr int kSkThreads = 256;  // producer, MMA issuer, four epilogue warps, two more for the exchange
 constexpr int kSkMaxRows = 512;  // up to four 128-row tiles per 256-column block
 constexpr int kSkRingBytes = 6 * (kSkBBytes + 16 * kRowBytes);  // 6 stages at a_rows = 16
 constexpr int kSkStagingOffset = kSkRingBytes;                   // epilogue patches, 4 KB per warp
@@ -50,7 +52,7 @@ constexpr int kSkAbortOffset = kSkTmemPtrOffset + 4;
 constexpr int kSkTotal = kSkAbortOffset + 4;
 constexpr int kSkDynamic = kSkTotal + 1024;  // slack to align the ring to 1024 bytes
 static_assert(kSkDynamic <= 227 * 1024, "shared memory");
-static_assert(kSkRingBytes - 2 * kEpiStagingBytesPerWarp >= 128 * 1024, "borrowed patches lie beyond the receive area");
+static_assert(kSkRingBytes - 4 * kEpiStagingBytesPerWarp >= 128 * 1024, "borrowed patches lie beyond the receive area");
 
 __device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint4 v) {
     asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
@@ -133,7 +135,7 @@ __device__ __forceinline__ void gather_store(const UmmaParams &p, const uint8_t 
             }
         }
     }
-    for (int m = t / tpr; m < rows; m += kThreads / tpr) {
+    for (int m = t / tpr; m < rows; m += kSkThreads / tpr) {
         const int pitch = slice;
         uint4 acc = *reinterpret_cast<const uint4 *>(recv + (size_t)((m * pitch) + c4) * 4);
         for (int src = 1; src < S; ++src) {
@@ -207,7 +209,7 @@ __device__ __forceinline__ void gather_store_dispatch(const UmmaParams &p, const
 // KIND / B_KN / EPI as in umma_gemm_kernel.  Launched with clusters of p.sk_split CTAs;
 // CTA r of cluster t multiplies K blocks [r*kbs/S, (r+1)*kbs/S) of tile t.
 template <int KIND, bool B_KN, int EPI>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kSkThreads, 1)
 umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                         const UmmaParams p) {
     constexpr int kElem = (KIND == MMA_F16) ? 2 : 1;
@@ -340,7 +342,7 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
         ok = __shfl_sync(0xffffffffu, ok, 0);
         tc_fence_after();
         if (dbg && warp == 2 && lane == 0) dbg[4] = globaltimer_ns();
-        if (S == 1 && ok) {
+        if (S == 1 && ok && warp < 6) {
             const int quarter = warp & 3;
             if (quarter * 32 < rows)
                 epilogue_tile<EPI, kSkBlockN>(p, m_base + quarter * 32, n0, tmem_base + (uint32_t(quarter * 32) << 16),
@@ -357,16 +359,17 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
         const bool good = (*abort_flag == 0);
         const int slice = kSkBlockN / S;
         if (good) {
-            // every warp sends: warp w reads TMEM lane quarter w % 4, so quarters 0 and 1 have two
-            // warps (w and w + 4), which take four chunks each
+            // every warp sends: warp w reads TMEM lane quarter w % 4, so each quarter has two warps
+            // (w and w + 4), which take four chunks each
             const int quarter = warp & 3;
-            const bool shared_quarter = quarter < 2;
-            const int c_begin = (shared_quarter && warp >= 4) ? 4 : 0;
-            const int c_end = (shared_quarter && warp < 4) ? 4 : kSkBlockN / 32;
-            // patches: the epilogue warps' own; warps 0 and 1 borrow the end of the (now idle) ring,
-            // beyond the receive area (at most 128 KB from its start)
-            uint8_t *patch = warp >= 2 ? smem_gen + kSkStagingOffset + quarter * kEpiStagingBytesPerWarp
-                                       : smem_gen + kSkRingBytes - (2 - warp) * kEpiStagingBytesPerWarp;
+            const int c_begin = warp >= 4 ? 4 : 0;
+            const int c_end = warp < 4 ? 4 : kSkBlockN / 32;
+            // patches: the epilogue warps' own; warps 0, 1, 6 and 7 borrow the end of the (now idle)
+            // ring, beyond the receive area (at most 128 KB from its start)
+            const int borrowed = warp < 2 ? warp : warp - 4;
+            uint8_t *patch = (warp >= 2 && warp < 6)
+                                 ? smem_gen + kSkStagingOffset + quarter * kEpiStagingBytesPerWarp
+                                 : smem_gen + kSkRingBytes - (borrowed + 1) * kEpiStagingBytesPerWarp;
             tc_fence_after();
             if (quarter * 32 < rows)
                 scatter_rows(rows, quarter * 32, tmem_base + (uint32_t(quarter * 32) << 16), patch, smem_base, smem_gen,
@@ -404,7 +407,7 @@ static int launch_skinny(const CUtensorMap &ta, const CUtensorMap &tb, UmmaParam
         for (int s = 8; s > 1; s /= 2) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(s, 1, 1);
-            cfg.blockDim = dim3(kThreads, 1, 1);
+            cfg.blockDim = dim3(kSkThreads, 1, 1);
             cfg.dynamicSmemBytes = kSkDynamic;
             cudaLaunchAttribute at[1];
             at[0].id = cudaLaunchAttributeClusterDimension;
@@ -428,7 +431,7 @@ static int launch_skinny(const CUtensorMap &ta, const CUtensorMap &tb, UmmaParam
     *split_out = split;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(tiles * split), 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.blockDim = dim3(kSkThreads, 1, 1);
     cfg.dynamicSmemBytes = kSkDynamic;
     cfg.stream = stream;
     cudaLaunchAttribute at[1];

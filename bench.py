@@ -187,12 +187,12 @@ def run_only(args, eng, o, torch, dev, time_steps, emit):
             Ns, Ks = 8192, 8192
             A, B = o.workloads.c2_gemm_bf16(Ms, Ns, Ks)
             Ad, Bd = A.to(dev), B.to(dev)
-            Bs = [Bd.clone() for _ in range(2)]          # rotate weights: 2 x 134 MB exceeds L2
+            Bs = [Bd.clone() for _ in range(4)]          # rotate weights: 4 x 134 MB, so that none of a weight is still in the 126 MB L2 when its turn comes again
             C = torch.empty((Ms, Ns), dtype=torch.bfloat16, device=dev)
             it = [0]
 
             def step():
-                eng.gemm_bf16(Ad, Bs[it[0] & 1], transB=True, out=C)
+                eng.gemm_bf16(Ad, Bs[it[0] & 3], transB=True, out=C)
                 it[0] += 1
 
             t = time_steps(step, steps, warm)

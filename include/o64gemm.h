@@ -107,9 +107,9 @@ typedef struct {
     int mma_m, mma_n, mma_k;
     int num_ctas;        /* persistent grid size */
     int split_k;         /* > 1: K slices on separate CTAs, reduced through scratch memory; 1: none;
-                            < 0: the kernel for M <= 128 - every 128 x 256 tile is split along K over a
-                            thread-block cluster of -split_k CTAs (1, 2, 4, 8) whose partial sums meet in
-                            distributed shared memory.  In a pin, -1 asks for that kernel and lets the
+                            < 0: the kernel for M <= 128 - every 128 x tile_n tile (tile_n = 256 or 128)
+                            is split along K over a thread-block cluster of -split_k CTAs (1, 2, 4, 8;
+                            at most tile_n / 32) whose partial sums meet in distributed shared memory.  In a pin, -1 asks for that kernel and lets the
                             library choose the cluster size; >= 1 rules it out */
     double predicted_ms; /* model estimate, compare with the measured time */
 } o64_plan_t;

@@ -241,7 +241,7 @@ extern "C" int o64_plan_set(o64_handle_t h, int kind, const o64_plan_t *plan) {
     const bool few_rows = plan->split_k < 0;  // the kernel for M <= 128: tile_m = rows of A per stage
     if (few_rows && plan->tile_m && plan->tile_m != 16 && plan->tile_m != 32 && plan->tile_m != 64 && plan->tile_m != 128)
         return O64_ERR_RANK;
-    if (few_rows && (plan->cta_group == 2 || (plan->tile_n && plan->tile_n != 256))) return O64_ERR_RANK;
+    if (few_rows && plan->cta_group == 2) return O64_ERR_RANK;  // tile_n: 256 or 128, checked below
     if (!few_rows && plan->tile_m && plan->tile_m != 128 && plan->tile_m != 256 && plan->tile_m != 512) return O64_ERR_RANK;
     if (plan->tile_n && plan->tile_n != 128 && plan->tile_n != 256) return O64_ERR_RANK;
     if (plan->cta_group && plan->cta_group != 1 && plan->cta_group != 2) return O64_ERR_RANK;

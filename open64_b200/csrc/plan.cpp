@@ -189,21 +189,28 @@ void plan_choose(int kind, int epi, int64_t M, int64_t N, int64_t K, int num_sms
     // split_k of -1 asks for the kernel (S chosen), -2 / -4 / -8 fix S, >= 1 rules the kernel out.
     const bool skinny_pinned = pin.split_k < 0;
     const bool skinny_fits = M <= (skinny_pinned ? 512 : 128) && epi != EPI_SWIGLU && pin.cta_group != 2 &&
-                             (pin.tile_m == 0 || pin.tile_m <= 128) && (pin.tile_n == 0 || pin.tile_n == 256);
+                             (pin.tile_m == 0 || pin.tile_m <= 128) && (pin.tile_n == 0 || pin.tile_n == 256 || pin.tile_n == 128);
     if (skinny_fits && (skinny_pinned || (pin.split_k == 0 && !pin.cta_group && !pin.tile_m && !pin.tile_n &&
                                           (double)N * (double)K * eb >= 2.0 * 1024 * 1024))) {
         const int a_rows = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
-        const int64_t tiles = ((M + 127) / 128) * ((N + 255) / 256);
+        // 128-column tiles halve the partial sums a CTA exchanges and double the tiles: measured
+        // faster for more than 64 rows, and where 256-column tiles on clusters of 4 would leave
+        // half of the SMs idle (more than 8 tiles; up to 8 take clusters of 8)
+        const int64_t tiles256 = ((M + 127) / 128) * ((N + 255) / 256);
+        int bn = pin.tile_n ? pin.tile_n : 256;
+        if (!pin.tile_n && (M > 64 || (tiles256 > 8 && tiles256 * 8 <= out->num_ctas))) bn = 128;
+        const int64_t tiles = ((M + 127) / 128) * ((N + bn - 1) / bn);
         const int64_t kbs = (K + out->tile_k - 1) / out->tile_k;
-        int s = pin.split_k < -1 ? -pin.split_k : umma_skinny_split(M, N, K, eb, out->num_ctas);
+        int s = pin.split_k < -1 ? -pin.split_k : umma_skinny_split(M, N, K, eb, out->num_ctas, bn);
+        if (s > bn / 32) s = bn / 32;
         if (s > kbs) s = 1;
         out->cta_group = 1;
         out->tile_m = a_rows;
-        out->tile_n = 256;
+        out->tile_n = bn;
         out->mma_m = 128;
-        out->mma_n = 256;
-        out->stages = (6 * (256 + 16) * 128) / ((256 + a_rows) * 128);
-        if (out->stages > 6) out->stages = 6;
+        out->mma_n = bn;
+        out->stages = (6 * (256 + 16) * 128) / ((bn + a_rows) * 128);
+        if (out->stages > 8) out->stages = 8;
         out->group_m = 1;
         out->split_k = -s;
         const int ctas_used = (int)(tiles * s < out->num_ctas ? tiles * s : out->num_ctas);
@@ -212,7 +219,7 @@ void plan_choose(int kind, int epi, int64_t M, int64_t N, int64_t K, int num_sms
         // tensor pipe: every K block costs one 128 x 256 MMA group whatever M is
         const double block_k = 128.0 / eb;
         const double per_cta = double((tiles * kbs + ctas_used - 1) / ctas_used);
-        const double mma_clk = 1.02 * 2.0 * 128.0 * 256.0 * block_k / (kDenseBf16FlopPerClkSm * (eb == 1 ? 2.0 : 1.0));
+        const double mma_clk = 1.02 * 2.0 * 128.0 * bn * block_k / (kDenseBf16FlopPerClkSm * (eb == 1 ? 2.0 : 1.0));
         const double mma_ms = per_cta * mma_clk / (kClockGHz * 1e6);
         out->predicted_ms = (hbm_ms > mma_ms ? hbm_ms : mma_ms) + 0.005;
         out->num_ctas = ctas_used;

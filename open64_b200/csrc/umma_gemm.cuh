@@ -42,7 +42,7 @@ struct UmmaCall {
 int umma_launch(const UmmaCall &call);
 
 // K slices per tile (CTAs per cluster) the kernel for few rows of A uses for a shape.
-int umma_skinny_split(int64_t M, int64_t N, int64_t K, int elem, int num_ctas);
+int umma_skinny_split(int64_t M, int64_t N, int64_t K, int elem, int num_ctas, int bn = 256);
 
 // Fills tile_*, stages, group_m, num_ctas, ... for a shape; applies `pin` (fields != 0) and the
 // O64_LNO environment override.  Pure host code.

@@ -3,16 +3,17 @@
 //
 // Differences from the 128 x BLOCK_N tile kernel (umma_gemm.cu):
 //   * the TMA box of A holds only `a_rows` rows (16 / 32 / 64 / 128, the next size >= M), and a
-//     shared-memory stage is that many rows of A plus 256 rows of B.  The MMA still runs with
+//     shared-memory stage is that many rows of A plus BN rows of B.  The MMA still runs with
 //     M = 128: the accumulator rows beyond a_rows are computed from whatever follows the A box in
 //     shared memory and are never read back (row i of the product depends on row i of A only).
 //     A 16-row problem thus keeps 6 stages x 32 KB of weight in flight per SM instead of 4.
-//   * a 128 x 256 output tile belongs to a thread-block CLUSTER of S CTAs (S = 1, 2, 4, 8), each of
-//     which multiplies one slice of K.  The partial sums never touch global memory: after a
+//   * a 128 x 256 (or 128 x 128: template parameter BN) output tile belongs to a thread-block
+//     CLUSTER of S CTAs (S = 1, 2, 4, 8; at most BN / 32), each of which multiplies one slice of
+//     K.  The partial sums never touch global memory: after a
 //     cluster barrier (every main loop done, so every ring is free) each CTA stores the columns
-//     c * 256/S .. of its accumulator into CTA c's idle ring (distributed shared memory), a
+//     c * BN/S .. of its accumulator into CTA c's idle ring (distributed shared memory), a
 //     second cluster barrier follows, and each CTA adds the S slices it received, applies the
-//     epilogue and writes its 256/S columns of C.  Measured: partial sums exchanged through L2
+//     epilogue and writes its BN/S columns of C.  Measured: partial sums exchanged through L2
 //     (atomics, a fence, a completion counter) cost three dependent round trips of about 2 us each
 //     at the end of the kernel, while the memory system is still saturated by the other CTAs.
 //
@@ -38,12 +39,10 @@ namespace o64 {
 
 namespace {
 
-constexpr int kSkBlockN = 256;
-constexpr int kSkBBytes = kSkBlockN * kRowBytes;      // 32 KB of weight per stage
-constexpr int kSkMaxStages = 6;
+constexpr int kSkMaxStages = 8;
 constexpr int kSkThreads = 256;  // producer, MMA issuer, four epilogue warps, two more for the exchange
 constexpr int kSkMaxRows = 512;  // up to four 128-row tiles per 256-column block
-constexpr int kSkRingBytes = 6 * (kSkBBytes + 16 * kRowBytes);  // 6 stages at a_rows = 16
+constexpr int kSkRingBytes = 6 * (256 + 16) * kRowBytes;  // 6 stages of 256 columns at a_rows = 16
 constexpr int kSkStagingOffset = kSkRingBytes;                   // epilogue patches, 4 KB per warp
 constexpr int kSkBarOffset = kSkStagingOffset + kEpiStagingBytes;
 constexpr int kSkNumBars = 2 * kSkMaxStages + 1;  // full[], empty[], accumulator ready
@@ -206,16 +205,18 @@ __device__ __forceinline__ void gather_store_dispatch(const UmmaParams &p, const
 
 }  // namespace
 
-// KIND / B_KN / EPI as in umma_gemm_kernel.  Launched with clusters of p.sk_split CTAs;
-// CTA r of cluster t multiplies K blocks [r*kbs/S, (r+1)*kbs/S) of tile t.
-template <int KIND, bool B_KN, int EPI>
+// KIND / B_KN / EPI as in umma_gemm_kernel; BN: columns of a tile (256, or 128: half the partial
+// sums to exchange per CTA and twice the tiles, for 128 rows or a narrow weight).  Launched with
+// clusters of p.sk_split CTAs; CTA r of cluster t multiplies K blocks [r*kbs/S, (r+1)*kbs/S) of tile t.
+template <int KIND, bool B_KN, int EPI, int BN>
 __global__ void __launch_bounds__(kSkThreads, 1)
 umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                         const UmmaParams p) {
     constexpr int kElem = (KIND == MMA_F16) ? 2 : 1;
     constexpr int kBlockK = kRowBytes / kElem;
     constexpr int kMmaPerStage = 4;
-    constexpr uint32_t kTmemCols = kSkBlockN;  // one accumulator
+    constexpr uint32_t kTmemCols = BN;  // one accumulator
+    constexpr int kBBytes = BN * kRowBytes;  // 32 or 16 KB of weight per stage
     static_assert(!B_KN || KIND == MMA_F16, "[K,N] operands are supported for bf16 only");
     static_assert(EPI != EPI_SWIGLU, "no SwiGLU variant");
 
@@ -233,14 +234,14 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
     const int lane = threadIdx.x & 31;
     const int stages = p.sk_stages;
     const uint32_t a_bytes = (uint32_t)p.sk_a_rows * kRowBytes;
-    const uint32_t stage_bytes = kSkBBytes + a_bytes;  // B first: the MMA's reads past the A box stay inside the allocation
+    const uint32_t stage_bytes = kBBytes + a_bytes;  // B first: the MMA's reads past the A box stay inside the allocation
     const int S = p.sk_split;
     const int rank = (int)cluster_ctarank();
     const int tile = blockIdx.x / S;             // tiles of one 256-column block are neighbours: they share B in L2
     const int mt = tile % p.num_m_tiles;
     const int m_base = mt * kBlockM;
     const int rows = min(kBlockM, p.M - m_base);  // rows of A this tile really has
-    const int n0 = (tile / p.num_m_tiles) * kSkBlockN;
+    const int n0 = (tile / p.num_m_tiles) * BN;
     const int kbs = p.num_k_blocks;
     const int kb_begin = (int)((long long)kbs * rank / S);
     const int kb_end = (int)((long long)kbs * (rank + 1) / S);
@@ -279,7 +280,7 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             const uint32_t b_dst = smem_base + stage * stage_bytes;
-            const uint32_t a_dst = b_dst + kSkBBytes;
+            const uint32_t a_dst = b_dst + kBBytes;
             if (leader) {
                 mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
                 tma_load_2d(a_dst, &tm_a, kb * kBlockK, m_base, full_bar(stage));
@@ -287,7 +288,7 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
                     tma_load_2d_hint(b_dst, &tm_b, kb * kBlockK, n0, full_bar(stage), stream_once);
                 } else {
 #pragma unroll
-                    for (int g = 0; g < kSkBlockN / 64; ++g)
+                    for (int g = 0; g < BN / 64; ++g)
                         tma_load_2d_hint(b_dst + g * 8192, &tm_b, n0 + g * 64, kb * kBlockK, full_bar(stage),
                                          stream_once);
                 }
@@ -304,7 +305,7 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
         const bool leader = elect_one();
         constexpr uint32_t d_fmt = (KIND == MMA_I8) ? 2u : 1u;
         constexpr uint32_t ab_fmt = (KIND == MMA_F8F6F4) ? 0u : 1u;
-        constexpr uint32_t idesc = make_idesc(d_fmt, ab_fmt, ab_fmt, B_KN ? 1u : 0u, kBlockM, kSkBlockN);
+        constexpr uint32_t idesc = make_idesc(d_fmt, ab_fmt, ab_fmt, B_KN ? 1u : 0u, kBlockM, BN);
         constexpr uint32_t kBAdvance = B_KN ? (16 * kRowBytes) >> 4 : 32 >> 4;
         int stage = 0;
         uint32_t phase = 0;
@@ -316,7 +317,7 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
             if (dbg && leader && kb == kb_begin) dbg[2] = globaltimer_ns();
             tc_fence_after();
             const uint32_t b_addr = smem_base + stage * stage_bytes;
-            const uint32_t a_addr = b_addr + kSkBBytes;
+            const uint32_t a_addr = b_addr + kBBytes;
             const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024);
             const uint64_t b_desc = B_KN ? make_smem_desc(b_addr, 8192, 1024) : make_smem_desc(b_addr, 16, 1024);
             if (leader) {
@@ -345,7 +346,7 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
         if (S == 1 && ok && warp < 6) {
             const int quarter = warp & 3;
             if (quarter * 32 < rows)
-                epilogue_tile<EPI, kSkBlockN>(p, m_base + quarter * 32, n0, tmem_base + (uint32_t(quarter * 32) << 16),
+                epilogue_tile<EPI, BN>(p, m_base + quarter * 32, n0, tmem_base + (uint32_t(quarter * 32) << 16),
                                               smem_gen + kSkStagingOffset + quarter * kEpiStagingBytesPerWarp);
         }
         tc_fence_before();
@@ -357,13 +358,13 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
         cluster_sync_all();  // every CTA of the cluster is past its main loop: the rings are free
         if (dbg && threadIdx.x == 64) dbg[5] = globaltimer_ns();
         const bool good = (*abort_flag == 0);
-        const int slice = kSkBlockN / S;
+        const int slice = BN / S;  // a multiple of 32: S <= BN / 32
         if (good) {
             // every warp sends: warp w reads TMEM lane quarter w % 4, so each quarter has two warps
             // (w and w + 4), which take four chunks each
             const int quarter = warp & 3;
-            const int c_begin = warp >= 4 ? 4 : 0;
-            const int c_end = warp < 4 ? 4 : kSkBlockN / 32;
+            const int c_begin = warp >= 4 ? BN / 64 : 0;
+            const int c_end = warp < 4 ? BN / 64 : BN / 32;
             // patches: the epilogue warps' own; warps 0, 1, 6 and 7 borrow the end of the (now idle)
             // ring, beyond the receive area (at most 128 KB from its start)
             const int borrowed = warp < 2 ? warp : warp - 4;
@@ -395,10 +396,10 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
     }
 }
 
-template <int KIND, bool B_KN, int EPI>
+template <int KIND, bool B_KN, int EPI, int BN>
 static int launch_skinny(const CUtensorMap &ta, const CUtensorMap &tb, UmmaParams p, int tiles, int want_split,
                          cudaStream_t stream, int *split_out) {
-    auto kern = umma_gemm_skinny_kernel<KIND, B_KN, EPI>;
+    auto kern = umma_gemm_skinny_kernel<KIND, B_KN, EPI, BN>;
     static bool attr_set = false;  // per instantiation
     static int max_split = 1;      // largest cluster the device can place with this much shared memory
     if (!attr_set) {
@@ -451,10 +452,11 @@ static int launch_skinny(const CUtensorMap &ta, const CUtensorMap &tb, UmmaParam
 // K slices per tile: the largest cluster size that keeps tiles * S within the CTAs the plan
 // allows and leaves every slice at least one K block.  Clusters of 8 only for 8 tiles or fewer:
 // measured, sixteen clusters of 8 CTAs with this much shared memory do not all fit at once.
-int umma_skinny_split(int64_t M, int64_t N, int64_t K, int elem, int num_ctas) {
-    const int64_t tiles = ((M + kBlockM - 1) / kBlockM) * ((N + kSkBlockN - 1) / kSkBlockN);
+int umma_skinny_split(int64_t M, int64_t N, int64_t K, int elem, int num_ctas, int bn) {
+    const int64_t tiles = ((M + kBlockM - 1) / kBlockM) * ((N + bn - 1) / bn);
     const int64_t kbs = (K + kRowBytes / elem - 1) / (kRowBytes / elem);
     int s = tiles <= 8 ? 8 : 4;
+    if (s > bn / 32) s = bn / 32;  // every CTA owns at least one 32-column chunk
     while (s > 1 && (tiles * s > num_ctas || s > kbs)) s /= 2;
     return s;
 }
@@ -464,28 +466,30 @@ int umma_launch_skinny(const UmmaCall &c, UmmaParams p) {
     const int elem = (c.kind == O64_KIND_BF16) ? 2 : 1;
     const int block_k = kRowBytes / elem;
     const int a_rows = c.M <= 16 ? 16 : (c.M <= 32 ? 32 : (c.M <= 64 ? 64 : 128));  // 128 per tile when M > 128
+    const int bn = c.plan.tile_n == 128 ? 128 : 256;
     CUtensorMap ta, tb;
     int rc = encode_2d(&ta, c.kind, c.A, c.M, c.K, c.lda, block_k, a_rows);
     if (rc) return rc;
     if (!c.b_kn)
-        rc = encode_2d(&tb, c.kind, c.B, c.N, c.K, c.ldb, block_k, kSkBlockN);
+        rc = encode_2d(&tb, c.kind, c.B, c.N, c.K, c.ldb, block_k, bn);
     else
         rc = encode_2d(&tb, c.kind, c.B, c.K, c.N, c.ldb, 64, block_k);
     if (rc) return rc;
     p.num_m_tiles = (int)((c.M + kBlockM - 1) / kBlockM);
-    p.num_n_tiles = (int)((c.N + kSkBlockN - 1) / kSkBlockN);
+    p.num_n_tiles = (int)((c.N + bn - 1) / bn);
     p.split_k = 1;
     p.kb_per_split = p.num_k_blocks;
     p.n_peers = 0;
     p.probe = 0;
     p.dbg = nullptr;
     p.sk_a_rows = a_rows;
-    const int stage_bytes = kSkBBytes + a_rows * kRowBytes;
+    const int stage_bytes = (bn + a_rows) * kRowBytes;
     p.sk_stages = kSkRingBytes / stage_bytes;
     if (p.sk_stages > kSkMaxStages) p.sk_stages = kSkMaxStages;
     const int ctas = c.plan.num_ctas > 0 ? c.plan.num_ctas : 148;
     // the plan's split_k is -S; -1 also stands for "choose"
-    int want = c.plan.split_k < -1 ? -c.plan.split_k : umma_skinny_split(c.M, c.N, c.K, elem, ctas);
+    int want = c.plan.split_k < -1 ? -c.plan.split_k : umma_skinny_split(c.M, c.N, c.K, elem, ctas, bn);
+    if (want > bn / 32) want = bn / 32;
     if (want > p.num_k_blocks) want = 1;
     const int tiles = p.num_m_tiles * p.num_n_tiles;
 
@@ -525,7 +529,9 @@ int umma_launch_skinny(const UmmaCall &c, UmmaParams p) {
                 sum[4] / grid, mx[4], sum[5] / grid, mx[5], sum[6] / grid, mx[6], sum[7] / grid, mx[7]);
         return rc_launch;
     };
-#define O64_SK(KIND, BKN, EPI_) return report(launch_skinny<KIND, BKN, EPI_>(ta, tb, p, tiles, want, c.stream, &split))
+#define O64_SK(KIND, BKN, EPI_)                                                                              \
+    return report(bn == 128 ? launch_skinny<KIND, BKN, EPI_, 128>(ta, tb, p, tiles, want, c.stream, &split)  \
+                            : launch_skinny<KIND, BKN, EPI_, 256>(ta, tb, p, tiles, want, c.stream, &split))
     if (c.kind == O64_KIND_BF16 && c.epi == EPI_BF16) {
         if (c.b_kn) O64_SK(MMA_F16, true, EPI_BF16);
         O64_SK(MMA_F16, false, EPI_BF16);

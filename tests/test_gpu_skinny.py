@@ -155,3 +155,39 @@ def test_several_row_tiles_per_column_block(eng, shape):
         eng.plan_set(o.KIND_BF16)
         eng.plan_set(o.KIND_S8)
     assert eng.last_status() == (o.OK, 0)
+
+
+@pytest.mark.parametrize("shape", [(1, 2048, 1024), (17, 520, 4104), (64, 1304, 1096), (128, 4096, 2048),
+                                   (100, 9000, 512), (300, 640, 2048), (9, 8, 131072)])
+def test_128_column_tiles(eng, shape):
+    """tile_n = 128: twice the tiles and half the partial sums to exchange per CTA; clusters of
+    1, 2 and 4 (the plan reports what it took), both layouts of B, bias + activation, int8 and fp8."""
+    M, N, K = shape
+    A, B = _bf16_case(M, N, K, True, seed=21)
+    bias = torch.randn(N, generator=torch.Generator().manual_seed(4))
+    ref = oracle.gemm_bf16(bits16(A), bits16(B), bias=bias.numpy(), act=oracle.ACT_SILU, transB=True)
+    Ai, Bi = o.workloads.c5_int8(M, N, K, seed=M + 1)
+    refi = oracle.gemm_s8s8_s32(Ai.numpy(), Bi.numpy())
+    Bkn = B.t().contiguous()
+    A8, W8, sA, sB, b8 = o.workloads.c4_fp8(M, N, K, seed=M + N)
+    ref8 = oracle.gemm_fp8_scaled(bits8(A8), bits8(W8), sA.numpy(), sB.numpy(), b8.numpy())
+    try:
+        for sk in (-1, -2, -4, -8):
+            eng.plan_set(o.KIND_BF16, split_k=sk, tile_n=128)
+            eng.plan_set(o.KIND_S8, split_k=sk, tile_n=128)
+            eng.plan_set(o.KIND_FP8, split_k=sk, tile_n=128)
+            plan = eng.plan_get(o.KIND_BF16, M, N, K)
+            assert plan["tile_n"] == 128 and -4 <= plan["split_k"] <= -1
+            C = eng.gemm_bf16(A.to(DEV), B.to(DEV), transB=True, bias=bias.to(DEV), act="silu")
+            assert relmax(C.float().cpu().numpy(), ref) <= TOL_LOWP, sk
+            C = eng.gemm_bf16(A.to(DEV), Bkn.to(DEV), transB=False, bias=bias.to(DEV), act="silu")
+            assert relmax(C.float().cpu().numpy(), ref) <= TOL_LOWP, sk
+            Ci = eng.gemm_s8(Ai.to(DEV), Bi.to(DEV))
+            assert np.array_equal(Ci.cpu().numpy(), refi), sk
+            C8 = eng.gemm_fp8_scaled(A8.to(DEV), W8.to(DEV), sA.to(DEV), sB.to(DEV), b8.to(DEV))
+            assert relmax(C8.float().cpu().numpy(), ref8) <= TOL_LOWP, sk
+    finally:
+        eng.plan_set(o.KIND_BF16)
+        eng.plan_set(o.KIND_S8)
+        eng.plan_set(o.KIND_FP8)
+    assert eng.last_status() == (o.OK, 0)

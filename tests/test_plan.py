@@ -62,16 +62,21 @@ def test_pins_and_rejections(built):
 
 def test_few_rows_of_a_take_the_cluster_split_kernel(built):
     for kind, eb in ((o.KIND_BF16, 2), (o.KIND_FP8, 1), (o.KIND_S8, 1)):
-        for M, rows, stages in ((1, 16, 6), (16, 16, 6), (17, 32, 5), (64, 64, 5), (100, 128, 4), (128, 128, 4)):
+        for M, rows, cols, stages in ((1, 16, 256, 6), (16, 16, 256, 6), (17, 32, 256, 5), (64, 64, 256, 5),
+                                      (100, 128, 128, 6), (128, 128, 128, 6)):
             p = model(kind, M, 8192, 8192)
-            # 32 tiles of 256 columns, each split over a cluster of 4 CTAs: 128 of the 148 SMs
-            assert p["split_k"] == -4 and p["num_ctas"] == 128
-            assert (p["tile_m"], p["tile_n"], p["cta_group"]) == (rows, 256, 1)
-            assert p["stages"] == stages and p["stages"] * (256 + rows) * 128 + 16384 + 1024 + 256 <= 227 * 1024
+            # 32 tiles of 256 columns, each split over a cluster of 4 CTAs: 128 of the 148 SMs; more
+            # than 64 rows: 64 tiles of 128 columns on clusters of 2 (a third of the partial sums to exchange)
+            assert p["split_k"] == (-4 if cols == 256 else -2) and p["num_ctas"] == 128
+            assert (p["tile_m"], p["tile_n"], p["cta_group"]) == (rows, cols, 1)
+            assert p["stages"] == stages and p["stages"] * (cols + rows) * 128 + 16384 + 1024 + 256 <= 227 * 1024
             # bound by HBM: the weight once at about 6.5 TB/s, plus launch and tail
             assert 8192 * 8192 * eb / 6.5e9 < p["predicted_ms"] < 2.5 * 8192 * 8192 * eb / 6.5e9
     assert model(o.KIND_BF16, 16, 28672, 4096)["split_k"] == -1         # 112 tiles: one CTA each
     assert model(o.KIND_BF16, 16, 2048, 8192)["split_k"] == -8          # 8 tiles: clusters of 8
+    p = model(o.KIND_BF16, 16, 4096, 8192)      # 16 tiles of 256 columns would use 64 SMs: 32 of 128 columns
+    assert (p["tile_n"], p["split_k"], p["num_ctas"]) == (128, -4, 128)
+    assert model(o.KIND_BF16, 16, 8192, 8192, split_k=-8, tile_n=128)["split_k"] == -4   # a CTA owns 32 columns at least
     assert model(o.KIND_BF16, 16, 65536, 128, split_k=-1)["split_k"] == -1
     assert model(o.KIND_BF16, 16, 8192, 8192, split_k=-2)["split_k"] == -2
     assert model(o.KIND_BF16, 129, 8192, 8192)["split_k"] >= 1          # more rows: the tile kernels

@@ -158,6 +158,18 @@ __device__ __forceinline__ void tma_prefetch_l2_2d(const void *tmap, int x, int 
                  ::"l"(tmap), "r"(x), "r"(y) : "memory");
 }
 
+// Programmatic dependent launch.  launch_dependents: the next kernel of the stream, if it was
+// launched with programmatic stream serialization, may be scheduled once every CTA of this grid
+// has executed this (or exited).  wait: blocks until the grids this one depends on have completed
+// and their memory is visible; a no-op for a kernel launched without the attribute.
+__device__ __forceinline__ void griddep_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ void griddep_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 __device__ __forceinline__ void tma_prefetch_desc(const void *tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }

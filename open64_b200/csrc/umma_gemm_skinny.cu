@@ -246,6 +246,11 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
     const int kb_begin = (int)((long long)kbs * rank / S);
     const int kb_end = (int)((long long)kbs * (rank + 1) / S);
 
+    // The next launch of the stream may take the SMs this grid leaves idle, and each SM a CTA of
+    // this grid leaves, without waiting for the whole grid to drain: its set-up and an L2 prefetch
+    // of its first weights then overlap this grid's tail (it waits below before it reads or writes
+    // anything this grid may touch).
+    griddep_launch_dependents();
     unsigned long long *dbg = p.dbg ? p.dbg + 8 * blockIdx.x : nullptr;  // O64_TRACE=pipe: time stamps (ns)
     if (threadIdx.x == 0) {
         if (dbg) dbg[0] = globaltimer_ns();
@@ -267,6 +272,15 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr_smem;
+    // Before the dependency wait nothing may be read into the SM or written: an earlier kernel of
+    // the stream may still be producing A, B or bias, or reading C.  A prefetch into L2 is safe (L2
+    // is where those writes land, so it never holds stale data) and starts the weight's first
+    // blocks on their way from HBM.
+    if (!B_KN && threadIdx.x == 0) {
+        const int ahead = min(stages, kb_end - kb_begin);
+        for (int i = 0; i < ahead; ++i) tma_prefetch_l2_2d(&tm_b, (kb_begin + i) * kBlockK, n0);
+    }
+    griddep_wait();
     if (dbg && threadIdx.x == 0) dbg[1] = globaltimer_ns();
 
     if (warp == 0) {
@@ -435,13 +449,21 @@ static int launch_skinny(const CUtensorMap &ta, const CUtensorMap &tb, UmmaParam
     cfg.blockDim = dim3(kSkThreads, 1, 1);
     cfg.dynamicSmemBytes = kSkDynamic;
     cfg.stream = stream;
-    cudaLaunchAttribute at[1];
+    cudaLaunchAttribute at[2];
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = split;
     at[0].val.clusterDim.y = 1;
     at[0].val.clusterDim.z = 1;
+    // programmatic dependent launch: this grid may be scheduled before the previous kernel of the
+    // stream has drained (the kernel waits for it before touching memory); O64_PDL=0 turns it off
+    static const bool pdl = [] {
+        const char *e = getenv("O64_PDL");
+        return !(e && e[0] == '0');
+    }();
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl ? 2 : 1;
     if (cudaLaunchKernelEx(&cfg, kern, ta, tb, p) != cudaSuccess) {
         (void)cudaGetLastError();
         return O64_ERR_CUDA;

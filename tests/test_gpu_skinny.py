@@ -191,3 +191,38 @@ def test_128_column_tiles(eng, shape):
         eng.plan_set(o.KIND_S8)
         eng.plan_set(o.KIND_FP8)
     assert eng.last_status() == (o.OK, 0)
+
+
+def test_back_to_back_calls_that_depend_on_each_other(eng):
+    """The kernel is launched so that it may be placed on SMs before the previous kernel of the
+    stream has finished, and prefetches weight lines into L2 before it waits for that kernel.
+    Chains without any synchronisation in between must still read what the previous call wrote:
+    its result as the next A, and its result as the next WEIGHT (lines prefetched early are
+    overwritten afterwards)."""
+    g = torch.Generator().manual_seed(77)
+    K, N = 4096, 8192
+    W1 = (torch.randn(N, K, generator=g) / 64).to(torch.bfloat16).to(DEV)
+    W2 = (torch.randn(1024, N, generator=g) / 64).to(torch.bfloat16).to(DEV)
+    X = torch.randn(16, N, generator=g).to(torch.bfloat16).to(DEV)
+    C1 = torch.zeros(128, N, dtype=torch.bfloat16, device=DEV)
+    y1 = torch.zeros(16, N, dtype=torch.bfloat16, device=DEV)
+    y2 = torch.zeros(16, 1024, dtype=torch.bfloat16, device=DEV)
+    y3 = torch.zeros(16, 128, dtype=torch.bfloat16, device=DEV)
+    try:
+        eng.plan_set(o.KIND_BF16, split_k=-1)
+        for rep in range(6):
+            A16 = torch.randn(16, K, generator=g).to(torch.bfloat16).to(DEV)
+            A128 = torch.randn(128, K, generator=g).to(torch.bfloat16).to(DEV)
+            torch.cuda.synchronize()
+            eng.gemm_bf16(A16, W1, transB=True, out=y1)      # layer 1
+            eng.gemm_bf16(y1, W2, transB=True, out=y2)       # layer 2 reads layer 1's result as A
+            eng.gemm_bf16(A128, W1, transB=True, out=C1)     # a 128 x 8192 product ...
+            eng.gemm_bf16(X, C1, transB=True, out=y3)        # ... that is the next call's weight
+            torch.cuda.synchronize()
+            assert relmax(y1.float().cpu().numpy(), (A16.float() @ W1.float().t()).cpu().numpy()) <= TOL_LOWP
+            assert relmax(y2.float().cpu().numpy(), (y1.float() @ W2.float().t()).cpu().numpy()) <= TOL_LOWP, rep
+            assert relmax(C1.float().cpu().numpy(), (A128.float() @ W1.float().t()).cpu().numpy()) <= TOL_LOWP
+            assert relmax(y3.float().cpu().numpy(), (X.float() @ C1.float().t()).cpu().numpy()) <= TOL_LOWP, rep
+    finally:
+        eng.plan_set(o.KIND_BF16)
+    assert eng.last_status() == (o.OK, 0)

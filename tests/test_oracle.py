@@ -218,3 +218,22 @@ def test_logical_kernel_against_numpy():
         assert np.array_equal(c.reshape(n, m).T, want.astype(np.int32))
     assert np.array_equal(oracle.lgemmx(m, n, k, 0, a, 1, m, b, 1, k, 1, c0.copy(), 1, m), c0)   # untouched
     assert not oracle.lgemmx(m, n, 0, 1, a, 1, m, b, 1, k, 1, c0.copy(), 1, m).any()
+
+
+@pytest.mark.parametrize("ka,kb", [("c4", "s4"), ("s4", "c4"), ("c4", "i1"), ("j", "c4"), ("c", "s4"), ("s", "c4"),
+                                   ("c4", "c"), ("c", "c4"), ("c", "i2"), ("i4", "c"), ("c", "s"), ("s", "c")])
+def test_complex_with_other_kinds_through_the_real_kernels(ka, kb):
+    """MATMUL of a COMPLEX operand with a REAL / INTEGER / other-width COMPLEX one, formed as the
+    entry points of osprey/libfi/matrix/matmul_c4s4.c, matmul_c4i1.c, matmul_c4c.c do: real and
+    imaginary parts as separate products of the REAL kernel, increments of COMPLEX arrays doubled,
+    C' = B'A' where MATRIX_A has the wider components.  The same sequence of kernel calls the GPU
+    parity test replays, here against numpy's complex product."""
+    import test_gpu_compat_complex_mixed as cm
+    rng = np.random.default_rng(5)
+    m, k, n = 13, 11, 17
+    a, b = cm._rand(ka, rng, m * k), cm._rand(kb, rng, k * n)
+    got = cm._ref_product(ka, kb, a, b, m, n, k, (1, m), (1, k))
+    kc = cm._result_kind(ka, kb)
+    assert got.dtype == cm.DT[kc]
+    want = a.reshape(k, m).T.astype(np.complex128) @ b.reshape(n, k).T.astype(np.complex128)
+    assert cm._close(kc, got.reshape(n, m).T, want)

@@ -276,9 +276,16 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
     // the stream may still be producing A, B or bias, or reading C.  A prefetch into L2 is safe (L2
     // is where those writes land, so it never holds stale data) and starts the weight's first
     // blocks on their way from HBM.
-    if (!B_KN && threadIdx.x == 0) {
+    if (threadIdx.x == 0) {
         const int ahead = min(stages, kb_end - kb_begin);
-        for (int i = 0; i < ahead; ++i) tma_prefetch_l2_2d(&tm_b, (kb_begin + i) * kBlockK, n0);
+        for (int i = 0; i < ahead; ++i) {
+            if constexpr (!B_KN) {
+                tma_prefetch_l2_2d(&tm_b, (kb_begin + i) * kBlockK, n0);
+            } else {
+#pragma unroll
+                for (int g = 0; g < BN / 64; ++g) tma_prefetch_l2_2d(&tm_b, n0 + g * 64, (kb_begin + i) * kBlockK);
+            }
+        }
     }
     griddep_wait();
     if (dbg && threadIdx.x == 0) dbg[1] = globaltimer_ns();

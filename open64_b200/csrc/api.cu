@@ -904,7 +904,10 @@ extern "C" int o64_plan_tune(o64_handle_t h, int kind, int swiglu, int64_t M, in
         add(1, 128, 128, 0);
         add(2, 256, 128, 0);
         if (M <= 512)  // few rows: one to four 128-row tiles per column block, K split over a cluster
-            for (int sk = -1; sk >= -8; sk *= 2) add(0, 0, 0, sk);
+            for (int sk = -1; sk >= -8; sk *= 2) {
+                add(0, 0, 256, sk);
+                if (sk >= -4) add(0, 0, 128, sk);  // 128-column tiles: clusters of at most 4
+            }
     }
     add(2, 512, 256, 0);
     const bool had_pin = h->has_pin[kind];

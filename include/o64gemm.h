@@ -281,6 +281,18 @@ typedef struct {
         long low_bound, extent, stride_mult;
     } dimension[7];
 } o64_dopevec_t;
+/* the sizes and offsets the reference's compiler gives DopeVectorType on x86-64 */
+#if defined(__cplusplus)
+static_assert(sizeof(o64_dopevec_t) == 216 && offsetof(o64_dopevec_t, flags0) == 16 &&
+                  offsetof(o64_dopevec_t, type_bits) == 28 && offsetof(o64_dopevec_t, orig_base) == 32 &&
+                  offsetof(o64_dopevec_t, dimension) == 48,
+              "o64_dopevec_t does not match DopeVectorType");
+#elif defined(__STDC_VERSION__) && __STDC_VERSION__ >= 201112L
+_Static_assert(sizeof(o64_dopevec_t) == 216 && offsetof(o64_dopevec_t, flags0) == 16 &&
+                   offsetof(o64_dopevec_t, type_bits) == 28 && offsetof(o64_dopevec_t, orig_base) == 32 &&
+                   offsetof(o64_dopevec_t, dimension) == 48,
+               "o64_dopevec_t does not match DopeVectorType");
+#endif
 void _MATMUL_S4S4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
 
 /* ---- the same family for REAL*8 and the integer kinds ------------------------------------

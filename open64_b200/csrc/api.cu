@@ -1323,7 +1323,12 @@ int matmul_premult(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t
         return O64_ERR_RANK;  // FESCIRNK
     if (!(RESULT->flags0 & 1u)) {
         unsigned int_len = (RESULT->type_bits >> 12) & 0xfffu;
-        if (int_len == 0) int_len = default_bits;
+        if (int_len == 0) {
+            // a RESULT whose type word carries no element length gets the entry point's result kind,
+            // written back so that the strides below and their later reading agree
+            int_len = default_bits;
+            RESULT->type_bits = (RESULT->type_bits & ~(0xfffu << 12)) | ((int_len & 0xfffu) << 12);
+        }
         long stride0 = int_len / 32;
         if (stride0 == 0) stride0 = 1;
         RESULT->dimension[0].stride_mult = stride0;

@@ -29,7 +29,10 @@
  *
  * Error codes mirror the runtime's abort codes (osprey/libfi/matrix/matmul.h:217,258,
  * 333-369; osprey/clibinc/liberrno.h:326,442-443): FESCIRNK -> O64_ERR_RANK,
- * FESCICNF -> O64_ERR_CONFORM, FENOMEMY -> O64_ERR_NOMEM.
+ * FESCICNF -> O64_ERR_CONFORM, FENOMEMY -> O64_ERR_NOMEM.  An operand that is device memory of a GPU
+ * other than the one the call runs on is refused with O64_ERR_RANK before anything is launched.
+ * K == 0 is the empty sum: the result is the epilogue applied to zero (osprey/libfi/matrix/xgemmx.h:185-196
+ * sets C to zero); only the no-allocation entry point rejects it.
  *
  * No C++ or torch types cross this boundary.  cudaStream_t is passed as void*.
  */
@@ -123,6 +126,12 @@ int o64_destroy(o64_handle_t h);
 /* Synchronises `stream`, reads and clears the device status word: O64_OK or
  * O64_ERR_TIMEOUT.  `detail`, if not NULL, receives the raw word (which wait gave up). */
 int o64_last_status(o64_handle_t h, void *stream, int *detail);
+/* Budget of the kernels' bounded device-side waits for later calls on this handle, in microseconds
+ * (0 = the default, two seconds; the environment variable O64_WAIT_BUDGET_US sets the default of new
+ * handles).  A wait that outlasts it ends its kernel in the ordinary way - tensor memory freed, no
+ * trap - with O64_ERR_TIMEOUT left for o64_last_status: the runtime this library replaces names the
+ * failing phase and aborts (osprey/common/util/errors.cxx:343-417); here the code names the wait. */
+int o64_set_wait_budget_us(o64_handle_t h, int64_t microseconds);
 const char *o64_status_string(int status);
 const char *o64_version(void);
 
@@ -187,13 +196,23 @@ int o64_gemm_s8s8_s32(o64_handle_t h, int64_t M, int64_t N, int64_t K, const int
  * reference: its runtime mallocs freely, osprey/libfi/matrix/matmul.h:222-266).  No handle, no
  * cudaMalloc / cudaFree anywhere on the path: the status word of the bounded waits and the padded
  * copies of operands whose base or row pitch is not a multiple of 16 bytes live in one static device
- * array of O64_STATIC_SCRATCH_BYTES per GPU.  Device pointers only.  Returns O64_ERR_NOMEM, and does
+ * array of O64_STATIC_SCRATCH_BYTES per GPU.  Device pointers only, of the device that is current at
+ * the call (`stream` too); anything else is O64_ERR_RANK.  Returns O64_ERR_NOMEM, and does
  * nothing, when the padded copies (M*ceil16(K) for A plus N*ceil16(K) for B, each only if needed)
  * exceed the array.  The first call on a device resolves the array's address; make it before any
  * stream capture.  Calls on one device share the array: calls that overlap on the GPU race. */
 #define O64_STATIC_SCRATCH_BYTES (16u << 20)
 int o64_gemm_s8s8_s32_static(int64_t M, int64_t N, int64_t K, const int8_t *A, int64_t lda,
                              const int8_t *B, int64_t ldb, int32_t *C, int64_t ldc, void *stream);
+
+/* Test hook for the failure path (no counterpart in the reference): o64_gemm_bf16 with B [N,K] and no
+ * epilogue, run by the kernel the handle's plan pin selects in an instantiation whose loader leaves
+ * out the loads of its `withhold_kblock`-th K block.  The kernel's waits then run out of the handle's
+ * wait budget and it returns; o64_last_status gives O64_ERR_TIMEOUT and which wait gave up.  Device
+ * pointers only; C is undefined afterwards.  Shipped kernels carry no such branch. */
+int o64_test_gemm_bf16_withheld(o64_handle_t h, int64_t M, int64_t N, int64_t K, const void *A, int64_t lda,
+                                const void *B, int64_t ldb, void *C, int64_t ldc, int withhold_kblock,
+                                void *stream);
 
 /* One-thread-per-output reference kernels: an independent device implementation of the same
  * contracts, used to compare full matrices where a CPU check would take minutes.

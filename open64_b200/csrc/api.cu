@@ -9,6 +9,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <array>
+#include <initializer_list>
 #include <map>
 #include <mutex>
 #include <new>
@@ -96,6 +97,7 @@ struct o64_handle_s {
     void *sym_peer[8] = {nullptr};  // indexed by rank; [rank] == sym_local
     size_t sym_bytes = 0;
     int *barrier_word = nullptr;    // one int, reduced over the ranks as a stream-ordered barrier
+    unsigned long long wait_ns = 0;  // budget of the kernels' bounded waits; 0 = the default (two seconds)
 };
 
 #define CUDA_TRY(x)                          \
@@ -153,6 +155,10 @@ extern "C" int o64_create(o64_handle_t *out, int device) {
     h->device = device;
     h->num_sms = prop.multiProcessorCount;
     memset(h->pins, 0, sizeof(h->pins));
+    if (const char *wb = getenv("O64_WAIT_BUDGET_US")) {
+        const long long us = atoll(wb);
+        if (us > 0) h->wait_ns = (unsigned long long)us * 1000ull;
+    }
     if (cudaMalloc(&h->status_word, sizeof(int)) != cudaSuccess) {
         delete h;
         return O64_ERR_NOMEM;
@@ -219,6 +225,12 @@ extern "C" int o64_last_status(o64_handle_t h, void *stream, int *detail) {
         CUDA_TRY(cudaMemsetAsync(h->status_word, 0, sizeof(int), s));
         return O64_ERR_TIMEOUT;
     }
+    return O64_OK;
+}
+
+extern "C" int o64_set_wait_budget_us(o64_handle_t h, int64_t microseconds) {
+    if (!h || microseconds < 0) return O64_ERR_RANK;
+    h->wait_ns = (unsigned long long)microseconds * 1000ull;  // 0: back to the default
     return O64_OK;
 }
 
@@ -296,6 +308,24 @@ extern "C" int o64_plan_model(int kind, int swiglu, int64_t M, int64_t N, int64_
 }
 
 // ---- host-operand staging ---------------------------------------------------------------------
+enum { PTR_DEVICE = 0, PTR_HOST = 1, PTR_OTHER_DEVICE = 2 };
+
+// Where an operand lives, seen from device `dev`: host memory (to be staged), memory the device can
+// use in place (its own or managed), or memory of ANOTHER GPU.  The last kind is refused by every
+// entry point: kernels, tensor maps and copies are made for the handle's device, and a pointer of
+// another GPU would end in an illegal-address fault (no peer access) or in silent peer traffic.
+static int ptr_class(const void *p, int dev) {
+    if (!p) return PTR_DEVICE;
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return PTR_HOST;
+    }
+    if (a.type == cudaMemoryTypeHost || a.type == cudaMemoryTypeUnregistered) return PTR_HOST;
+    if (a.type == cudaMemoryTypeDevice && a.device != dev) return PTR_OTHER_DEVICE;
+    return PTR_DEVICE;
+}
+
 static bool is_host_ptr(const void *p) {
     if (!p) return false;
     cudaPointerAttributes a;
@@ -304,6 +334,13 @@ static bool is_host_ptr(const void *p) {
         return true;
     }
     return a.type == cudaMemoryTypeHost || a.type == cudaMemoryTypeUnregistered;
+}
+
+// True when every pointer is host memory, memory of the handle's device, or NULL.
+static bool on_handles_device(o64_handle_t h, std::initializer_list<const void *> ptrs) {
+    for (const void *p : ptrs)
+        if (ptr_class(p, h->device) == PTR_OTHER_DEVICE) return false;
+    return true;
 }
 
 static int reserve(void **buf, size_t *cap, size_t bytes) {
@@ -330,7 +367,9 @@ static size_t span_bytes(int64_t rows, int64_t cols, int64_t ld, int elem) {
 static int stage_in(o64_handle_t h, int slot, const void *src, size_t bytes, cudaStream_t s,
                     const void **dev) {
     *dev = src;
-    if (!src || !is_host_ptr(src)) return O64_OK;
+    const int where = ptr_class(src, h->device);
+    if (where == PTR_OTHER_DEVICE) return O64_ERR_RANK;
+    if (!src || where != PTR_HOST) return O64_OK;
     int rc = reserve(&h->stage[slot], &h->stage_cap[slot], bytes ? bytes : 16);
     if (rc) return rc;
     if (bytes) CUDA_TRY(cudaMemcpyAsync(h->stage[slot], src, bytes, cudaMemcpyHostToDevice, s));
@@ -349,7 +388,9 @@ static int stage_out_begin(o64_handle_t h, int slot, void *dst, size_t bytes, bo
     o->host = nullptr;
     o->dev = dst;
     o->bytes = bytes;
-    if (!dst || !is_host_ptr(dst)) return O64_OK;
+    const int where = ptr_class(dst, h->device);
+    if (where == PTR_OTHER_DEVICE) return O64_ERR_RANK;
+    if (!dst || where != PTR_HOST) return O64_OK;
     int rc = reserve(&h->stage[slot], &h->stage_cap[slot], bytes ? bytes : 16);
     if (rc) return rc;
     o->host = dst;
@@ -453,18 +494,34 @@ static int pipeline_resources(o64_handle_t h) {
 static int umma_entry(o64_handle_t h, int kind, bool b_kn, int epi, int64_t M, int64_t N, int64_t K,
                       const void *A, int64_t lda, const void *B, const void *B2, int64_t ldb, void *C,
                       int64_t ldc, const float *bias, const float *sa, const float *sb, int act,
-                      void *stream) {
+                      void *stream, int test_withhold = -1) {
     if (!h || M < 0 || N < 0 || K < 0) return O64_ERR_RANK;
     if (act < O64_ACT_NONE || act > O64_ACT_SILU) return O64_ERR_RANK;
     if (M == 0 || N == 0) return O64_OK;
-    if (K == 0) return O64_ERR_RANK;
-    if (!A || !B || !C) return O64_ERR_RANK;
+    if (!C || (K > 0 && (!A || !B))) return O64_ERR_RANK;
     const int elem = (kind == O64_KIND_BF16) ? 2 : 1;
     const int out_elem = (epi == EPI_S32) ? 4 : 2;
     const int64_t b_rows = b_kn ? K : N, b_cols = b_kn ? N : K;
     if (lda < K || ldb < b_cols || ldc < N) return O64_ERR_CONFORM;
-    DeviceGuard g(h->device);
+    DeviceGuard g(h->device);  // (operands of another GPU are refused where each is staged, below)
     cudaStream_t s = (cudaStream_t)stream;
+    if (K == 0) {
+        // the empty sum, as the runtime's kernels treat it (osprey/libfi/matrix/xgemmx.h:185-196 sets
+        // C to zero): every accumulator is zero and the fused tail runs on that
+        StagedOut o0;
+        const void *dbias0;
+        int rc0;
+        if ((rc0 = stage_in(h, 3, bias, (size_t)N * 4, s, &dbias0))) return rc0;
+        if ((rc0 = stage_out_begin(h, 5, C, span_bytes(M, N, ldc, out_elem), ldc != N, s, &o0))) return rc0;
+        if (epi == EPI_S32 || epi == EPI_SWIGLU || (!dbias0 && epi == EPI_BF16) || (!dbias0 && epi == EPI_SCALED_BF16)) {
+            // act(0) = 0 for every activation of the vocabulary; silu(0) * 0 = 0
+            CUDA_TRY(cudaMemset2DAsync(o0.dev, (size_t)ldc * out_elem, 0, (size_t)N * out_elem, (size_t)M, s));
+        } else if ((rc0 = finalize_partial_bf16(nullptr, M, N, nullptr, nullptr, (const float *)dbias0,
+                                                epi == EPI_BF16 ? act : O64_ACT_NONE, o0.dev, ldc, s))) {
+            return rc0;
+        }
+        return stage_out_end(o0, s);
+    }
     const void *dA, *dB, *dB2, *dbias, *dsa, *dsb;
     StagedOut out;
     int rc;
@@ -472,7 +529,7 @@ static int umma_entry(o64_handle_t h, int kind, bool b_kn, int epi, int64_t M, i
     // one side stream, multiplied on the caller's stream, and its rows of C copied back on another,
     // so that host->device, kernels and device->host overlap (the link carries both directions at
     // once); the weight is staged whole, first.  Everything else goes the plain way.
-    const bool piped = M >= 2 * kBlockRows && ldc == N && (lda * elem) % 16 == 0 && is_host_ptr(A) && is_host_ptr(C) &&
+    const bool piped = test_withhold < 0 && M >= 2 * kBlockRows && ldc == N && (lda * elem) % 16 == 0 && is_host_ptr(A) && is_host_ptr(C) &&
                        pipeline_resources(h) == O64_OK;
     if (piped) {
         if ((rc = reserve(&h->stage[0], &h->stage_cap[0], span_bytes(M, K, lda, elem)))) return rc;
@@ -486,7 +543,9 @@ static int umma_entry(o64_handle_t h, int kind, bool b_kn, int epi, int64_t M, i
     // the two scale vectors share one slot: sa first, sb after it
     dsa = sa;
     dsb = sb;
-    if ((sa && is_host_ptr(sa)) || (sb && is_host_ptr(sb))) {
+    const int sa_where = ptr_class(sa, h->device), sb_where = ptr_class(sb, h->device);
+    if (sa_where == PTR_OTHER_DEVICE || sb_where == PTR_OTHER_DEVICE) return O64_ERR_RANK;
+    if ((sa && sa_where == PTR_HOST) || (sb && sb_where == PTR_HOST)) {
         if ((rc = reserve(&h->stage[4], &h->stage_cap[4], (size_t)(M + N) * 4))) return rc;
         float *base = (float *)h->stage[4];
         if (sa) {
@@ -520,6 +579,8 @@ static int umma_entry(o64_handle_t h, int kind, bool b_kn, int epi, int64_t M, i
     c.act = act;
     c.status_word = h->status_word;
     c.stream = s;
+    c.wait_ns = h->wait_ns;
+    c.test_withhold = test_withhold;
     if (piped) {
         int64_t rows = (M + kMaxBlocks - 1) / kMaxBlocks;
         if (rows < kBlockRows) rows = kBlockRows;
@@ -548,7 +609,15 @@ static int umma_entry(o64_handle_t h, int kind, bool b_kn, int epi, int64_t M, i
             if (b.scale_a) b.scale_a += r0;
             plan_choose(kind, epi, nr, N, K, h->num_sms, &pin, &b.plan);
             if (b.plan.split_k > 1) b.plan.split_k = 1;
-            if ((rc = umma_launch(b))) return rc;
+            if ((rc = umma_launch(b))) {
+                // leave nothing queued behind the caller's back: the side streams' copies and the
+                // waits recorded so far drain before the error is returned
+                cudaStreamSynchronize(h->copy_in);
+                cudaStreamSynchronize(h->copy_out);
+                cudaStreamSynchronize(s);
+                (void)cudaGetLastError();
+                return rc;
+            }
             CUDA_TRY(cudaEventRecord(h->ev_mm[i], s));
             CUDA_TRY(cudaStreamWaitEvent(h->copy_out, h->ev_mm[i], 0));
             CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t *>(out.host) + (size_t)r0 * ldc * out_elem, b.C,
@@ -614,6 +683,20 @@ extern "C" int o64_gemm_s8s8_s32(o64_handle_t h, int64_t M, int64_t N, int64_t K
                       nullptr, nullptr, O64_ACT_NONE, stream);
 }
 
+// Test hook: o64_gemm_bf16 (B [N,K], no epilogue) run by the kernel the handle's pin selects, in an
+// instantiation whose producer leaves out the loads of one K block.  The stage's barrier then never
+// completes, the waits behind it use up the handle's wait budget, the kernel records which wait gave
+// up, frees its tensor memory and returns; o64_last_status reports O64_ERR_TIMEOUT.  Nothing traps or
+// spins without a limit.  C's contents are undefined afterwards.
+extern "C" int o64_test_gemm_bf16_withheld(o64_handle_t h, int64_t M, int64_t N, int64_t K, const void *A, int64_t lda,
+                                           const void *B, int64_t ldb, void *C, int64_t ldc, int withhold_kblock,
+                                           void *stream) {
+    if (withhold_kblock < 0) return O64_ERR_RANK;
+    if (is_host_ptr(A) || is_host_ptr(B) || is_host_ptr(C)) return O64_ERR_RANK;
+    return umma_entry(h, O64_KIND_BF16, false, EPI_BF16, M, N, K, A, lda, B, nullptr, ldb, C, ldc, nullptr, nullptr,
+                      nullptr, O64_ACT_NONE, stream, withhold_kblock);
+}
+
 extern "C" int o64_naive_gemm(o64_handle_t h, int kind, int64_t M, int64_t N, int64_t K, const void *A,
                               int64_t lda, const void *B, int64_t ldb, int transB, const float *scaleA,
                               const float *scaleB, const float *bias, int act, void *out, int64_t ldo,
@@ -621,6 +704,7 @@ extern "C" int o64_naive_gemm(o64_handle_t h, int kind, int64_t M, int64_t N, in
     if (!h || M < 0 || N < 0 || K < 0) return O64_ERR_RANK;
     if (kind != O64_KIND_FP8 && (scaleA || scaleB)) return O64_ERR_DTYPE;
     if (is_host_ptr(A) || is_host_ptr(B) || is_host_ptr(out)) return O64_ERR_RANK;
+    if (!on_handles_device(h, {A, B, out, scaleA, scaleB, bias})) return O64_ERR_RANK;
     DeviceGuard g(h->device);
     return naive_gemm(kind, M, N, K, A, lda, B, ldb, transB, scaleA, scaleB, bias, act, out, ldo,
                       (cudaStream_t)stream);
@@ -763,6 +847,7 @@ static int push_gemm(o64_handle_t h, int kind, int epi, int64_t M, int64_t N, in
     }
     c.status_word = h->status_word;
     c.stream = s;
+    c.wait_ns = h->wait_ns;
     c.n_peers = 0;
     for (int i = 0; i < g; ++i) {
         if (i == r) continue;
@@ -783,6 +868,7 @@ extern "C" int o64_gemm_s8_sharded(o64_handle_t h, int64_t M, int64_t N, int64_t
     if (gather < O64_GATHER_NONE || gather > O64_GATHER_PUSH) return O64_ERR_RANK;
     if (gather != O64_GATHER_NONE && g > 1 && !h->comm) return O64_ERR_NCCL;
     if (is_host_ptr(A) || is_host_ptr(B_slab) || is_host_ptr(C_full)) return O64_ERR_RANK;
+    if (!on_handles_device(h, {A, B_slab, C_full, workspace})) return O64_ERR_RANK;
     const int64_t ns = N / g;
     DeviceGuard guard(h->device);
     cudaStream_t s = (cudaStream_t)stream;
@@ -822,6 +908,7 @@ extern "C" int o64_gemm_bf16_sharded(o64_handle_t h, int64_t M, int64_t N, int64
     if (gather != O64_GATHER_NONE && gather != O64_GATHER_SLABS && gather != O64_GATHER_PUSH) return O64_ERR_RANK;
     if (gather != O64_GATHER_NONE && g > 1 && !h->comm) return O64_ERR_NCCL;
     if (is_host_ptr(A) || is_host_ptr(B_slab) || is_host_ptr(C_full)) return O64_ERR_RANK;
+    if (!on_handles_device(h, {A, B_slab, C_full, epi ? epi->bias : nullptr})) return O64_ERR_RANK;
     const int64_t ns = N / g;
     const float *bias = epi ? epi->bias : nullptr;
     const int act = epi ? epi->act : O64_ACT_NONE;

@@ -17,7 +17,9 @@
 //
 // The array's name is only a host-side stand-in: the device address comes from
 // cudaGetSymbolAddress, once per device, on the first call made with that device current.  Make
-// that first call before any stream capture begins.
+// that first call before any stream capture begins.  A, B and C must be memory of the device that
+// is current at the call (or managed memory) and `stream` a stream of that device; operands of
+// another device are refused with O64_ERR_RANK before anything is launched.
 //
 // All calls on a device share the array and it keeps the previous call's contents, so two calls
 // that overlap on the GPU (different streams, no dependency) race on it; serialise them.  A wait
@@ -43,6 +45,7 @@ static __device__ __align__(256) unsigned char g_static_scratch[kScratchBytes];
 struct PerDevice {
     unsigned char *scratch = nullptr;  // device address of g_static_scratch on this device
     int num_sms = 0;
+    int index = 0;
     bool ready = false;
 };
 PerDevice g_devices[kMaxDevices];
@@ -72,19 +75,24 @@ int setup_current_device(PerDevice **out) {
         if (major != 10) return O64_ERR_DTYPE;  // the kernels are sm_100a only
         d.scratch = static_cast<unsigned char *>(ptr);
         d.num_sms = sms;
+        d.index = dev;
         d.ready = true;
     }
     *out = &d;
     return O64_OK;
 }
 
-bool is_device_pointer(const void *p) {
+// Device (or managed) memory, and memory of the device this call runs on: the padded copies and
+// the tensor maps below are made for the current device, so an operand that lives on another GPU
+// would end in a launch failure or in reads over a peer link nobody asked for.
+bool is_pointer_of_device(const void *p, int dev) {
     cudaPointerAttributes a;
     if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
         (void)cudaGetLastError();
         return false;
     }
-    return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+    if (a.type == cudaMemoryTypeManaged) return true;
+    return a.type == cudaMemoryTypeDevice && a.device == dev;
 }
 
 bool tma_addressable(const void *p, int64_t ld_bytes) {
@@ -102,11 +110,12 @@ extern "C" int o64_gemm_s8s8_s32_static(int64_t M, int64_t N, int64_t K, const i
     if (M == 0 || N == 0) return O64_OK;
     if (K == 0 || !A || !B || !C) return O64_ERR_RANK;
     if (lda < K || ldb < K || ldc < N) return O64_ERR_CONFORM;
-    if (!is_device_pointer(A) || !is_device_pointer(B) || !is_device_pointer(C))
-        return O64_ERR_RANK;  // staging host operands would need an allocation
     PerDevice *d = nullptr;
     int rc = setup_current_device(&d);
     if (rc) return rc;
+    // host operands would need staging, i.e. an allocation; operands of another GPU are refused
+    if (!is_pointer_of_device(A, d->index) || !is_pointer_of_device(B, d->index) || !is_pointer_of_device(C, d->index))
+        return O64_ERR_RANK;
     cudaStream_t s = (cudaStream_t)stream;
 
     // operands TMA cannot address are copied to a 16-byte pitch inside the static array

@@ -80,12 +80,13 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 }
 
 // Bounded wait.  Spins on try_wait; every 1024 failed probes it looks at the clock and at the
-// CTA's abort flag.  After `budget_ns` without success it records `code` in the device status
-// word, raises the abort flag so the other roles of the CTA leave their loops too, and returns
-// false.  No trap, no endless loop: the CTA then runs its normal teardown.
+// CTA's abort flag.  After `budget_ns` without success (the launch parameter wait_ns: two seconds
+// unless the handle was given another budget) it records `code` in the device status word, raises
+// the abort flag so the other roles of the CTA leave their loops too, and returns false.  No trap,
+// no endless loop: the CTA then runs its normal teardown.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   volatile int *abort_flag, int *status_word,
-                                                  int code, uint64_t budget_ns = 2000000000ull) {
+                                                  int code, uint64_t budget_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     uint32_t probes = 0;
     uint64_t t0 = 0;

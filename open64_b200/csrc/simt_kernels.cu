@@ -525,7 +525,7 @@ __global__ void finalize_partial_kernel(const float *__restrict__ partial, long 
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
          e += (long long)gridDim.x * blockDim.x) {
         const long long i = e / N, j = e % N;
-        float x = partial[e];
+        float x = partial ? partial[e] : 0.0f;  // no partial sums: the empty sum (K == 0)
         if (scale_a) x *= scale_a[i];
         if (scale_b) x *= scale_b[j];
         if (bias) x += bias[j];

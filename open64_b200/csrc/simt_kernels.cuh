@@ -48,7 +48,7 @@ int naive_gemm(int kind, int64_t M, int64_t N, int64_t K, const void *A, int64_t
                int act, void *out, int64_t ldo, cudaStream_t stream);
 
 // Second pass of a split-K GEMM with a 16-bit result: C = bf16(act(partial * sa[m] * sb[n] + bias[n])),
-// `partial` a dense fp32 [M,N].  scale vectors and bias may be NULL.
+// `partial` a dense fp32 [M,N], or NULL for the empty sum (every partial zero).  scale vectors and bias may be NULL.
 int finalize_partial_bf16(const float *partial, int64_t M, int64_t N, const float *scale_a,
                           const float *scale_b, const float *bias, int act, void *C, int64_t ldc,
                           cudaStream_t stream);

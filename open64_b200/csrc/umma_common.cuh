@@ -4,10 +4,24 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <mutex>
+
 #include "ptx_sm100.cuh"
 #include "umma_gemm.cuh"
 
 namespace o64 {
+
+// Tuning aids exist only in a build with -DO64_TUNING (python -m open64_b200.build --tuning): the
+// pipeline probes (O64_PROBE: skip the loads / the MMAs / the epilogue / the stores; results are
+// invalid) and the cycle counters behind O64_TRACE=pipe.  In the shipped build both macros are
+// constants and every branch on them is removed by the compiler.
+#ifdef O64_TUNING
+#define O64_PROBE(p) ((p).probe)
+#define O64_DBG(p) ((p).dbg)
+#else
+#define O64_PROBE(p) 0
+#define O64_DBG(p) (static_cast<unsigned long long *>(nullptr))
+#endif
 
 struct UmmaParams {
     int M, N, K;
@@ -20,10 +34,17 @@ struct UmmaParams {
     int num_m_tiles, num_n_tiles, group_m, raster;
     int num_k_blocks;
     int vec_ok;  // C rows 16-byte aligned: vector stores allowed
-    unsigned long long *dbg;  // tuning aid (O64_TRACE=pipe): per-CTA wait/total cycles of the issuing threads
-    int probe;   // O64_PROBE, tuning only, results invalid: 1 = skip the loads, 2 = skip the MMAs,
-                 // +4 = skip the epilogue, +32 = skip the global stores
+#ifdef O64_TUNING
+    unsigned long long *dbg;  // O64_TRACE=pipe: per-CTA wait/total cycles of the issuing threads
+    int probe;   // O64_PROBE: 1 = skip the loads, 2 = skip the MMAs, +4 = skip the epilogue,
+                 // +32 = skip the global stores
+#endif
     int *status;
+    unsigned long long wait_ns;  // budget of every bounded wait, in nanoseconds
+    // test hook (kernels instantiated with HOOK = true only, reached through o64_test_*): the
+    // producer leaves out the loads of the k-th K block it would issue, so that the stage's "full"
+    // barrier never completes and the waits behind it run out; -1 = none
+    int test_withhold;
     // split-K: each tile's K blocks are divided over split_k work items whose partial sums are
     // added (fp32 / int32 atomics) into `partial` (fp32 results: a dense [M,N] workspace, finished
     // by a second kernel) or straight into C (int32 results, C zeroed first); 1 = off
@@ -170,13 +191,13 @@ __device__ __forceinline__ void epilogue_tile_act(const UmmaParams &p, long long
         const int c = c_begin + 32 * i;          // column inside the tile
         const int slab_c = c_begin + (i / kChunksPerSlab) * kSlabCols;
         const int h = i % kChunksPerSlab;
-        const bool coalesced = p.vec_ok && (n0 + slab_c + kSlabCols <= p.N) && !(p.probe & 32);
+        const bool coalesced = p.vec_ok && (n0 + slab_c + kSlabCols <= p.N) && !(O64_PROBE(p) & 32);
         if constexpr (EPI == EPI_S32) {
             if (coalesced) {
 #pragma unroll
                 for (int q = 0; q < 8; ++q)
                     patch[lane * 8 + (q ^ sw)] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-            } else if (row_ok && !(p.probe & 32)) {
+            } else if (row_ok && !(O64_PROBE(p) & 32)) {
                 int32_t *dst = reinterpret_cast<int32_t *>(p.C) + row * p.ldc + n0 + c;
 #pragma unroll
                 for (int j = 0; j < 32; ++j)
@@ -191,7 +212,7 @@ __device__ __forceinline__ void epilogue_tile_act(const UmmaParams &p, long long
                     patch[lane * 8 + ((h * 4 + q) ^ sw)] =
                         make_uint4(pack_bf16x2(f[8 * q], f[8 * q + 1]), pack_bf16x2(f[8 * q + 2], f[8 * q + 3]),
                                    pack_bf16x2(f[8 * q + 4], f[8 * q + 5]), pack_bf16x2(f[8 * q + 6], f[8 * q + 7]));
-            } else if (row_ok && !(p.probe & 32)) {
+            } else if (row_ok && !(O64_PROBE(p) & 32)) {
                 __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.C) + row * p.ldc + n0 + c;
 #pragma unroll
                 for (int j = 0; j < 32; ++j)
@@ -326,6 +347,36 @@ __device__ __forceinline__ void epilogue_partial(const UmmaParams &p, void *dst,
         __syncwarp();
     }
 }
+
+// Per-device set-up of one kernel instantiation.  cudaFuncSetAttribute and the cluster occupancy
+// query act on the CURRENT device, so a process that drives several GPUs needs them once per
+// (instantiation, device); each launcher keeps one of these in a function-local static.
+constexpr int kMaxDevices = 64;
+struct KernelSetup {
+    std::mutex mu;
+    bool done[kMaxDevices] = {};
+    int max_clusters[kMaxDevices] = {};
+    // Runs `setup(&max_clusters)` (returns an O64 status) the first time this instantiation is
+    // launched on the current device; *clusters receives the value it stored.
+    template <typename F>
+    int once(F setup, int *clusters) {
+        int dev = -1;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+            (void)cudaGetLastError();
+            return O64_ERR_CUDA;
+        }
+        std::lock_guard<std::mutex> lock(mu);
+        if (!done[dev]) {
+            int n = 0;
+            const int rc = setup(&n);
+            if (rc) return rc;
+            max_clusters[dev] = n;
+            done[dev] = true;
+        }
+        if (clusters) *clusters = max_clusters[dev];
+        return O64_OK;
+    }
+};
 
 // host helpers shared by the launchers (umma_gemm.cu)
 // 2-D row-major tensor [rows, cols] with `ld` elements between rows; box of box_cols x box_rows;

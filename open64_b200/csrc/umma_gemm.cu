@@ -47,7 +47,7 @@ struct SmemLayout {
 
 // KIND: MMA_F16 (bf16 operands) / MMA_F8F6F4 (e4m3) / MMA_I8 (s8).
 // B_KN: B stored [K,N] (N contiguous) -> MN-major shared-memory descriptor; else [N,K].
-template <int KIND, bool B_KN, int EPI, int BLOCK_N, int STAGES>
+template <int KIND, bool B_KN, int EPI, int BLOCK_N, int STAGES, bool HOOK = false>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                  const __grid_constant__ CUtensorMap tm_b2, const UmmaParams p) {
@@ -110,6 +110,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             uint32_t phase = 0;
             bool ok = true;
             long long wait_clk = 0;
+            [[maybe_unused]] int issued = 0;  // K blocks this producer has dealt with (test hook)
             const long long t_begin = clock64();
             for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
                 int mb, nb;
@@ -119,17 +120,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 const int kb_begin = (w % p.split_k) * p.kb_per_split;
                 const int kb_end = min(kb_begin + p.kb_per_split, p.num_k_blocks);
                 for (int kb = kb_begin; kb < kb_end; ++kb) {
-                    const long long c0 = p.dbg ? clock64() : 0;
+                    const long long c0 = O64_DBG(p) ? clock64() : 0;
                     ok = mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
-                                           kWaitProducerEmpty);
+                                           kWaitProducerEmpty, p.wait_ns);
                     ok = __all_sync(0xffffffffu, ok);
-                    if (p.dbg) wait_clk += clock64() - c0;
+                    if (O64_DBG(p)) wait_clk += clock64() - c0;
                     if (!ok) break;
                     const uint32_t a_dst = smem_base + stage * L::kStageBytes;
                     const uint32_t b_dst = a_dst + kABytes;
-                    if ((p.probe & 3) == 1) {
+                    bool withhold = false;
+                    if constexpr (HOOK) withhold = (issued++ == p.test_withhold);
+                    if ((O64_PROBE(p) & 3) == 1) {
                         if (leader) mbar_arrive(full_bar(stage));
-                    } else if (leader) {
+                    } else if (leader && !withhold) {
                         mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
                         tma_load_2d(a_dst, &tm_a, kb * kBlockK, m0, full_bar(stage));
                         if constexpr (!B_KN) {
@@ -158,9 +161,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     }
                 }
             }
-            if (p.dbg && leader) {
-                p.dbg[blockIdx.x * 8 + 2] = wait_clk;
-                p.dbg[blockIdx.x * 8 + 3] = clock64() - t_begin;
+            if (O64_DBG(p) && leader) {
+                O64_DBG(p)[blockIdx.x * 8 + 2] = wait_clk;
+                O64_DBG(p)[blockIdx.x * 8 + 3] = clock64() - t_begin;
             }
         }
         __syncwarp();
@@ -189,18 +192,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 const int kb_begin = (w % p.split_k) * p.kb_per_split;
                 const int kb_end = min(kb_begin + p.kb_per_split, p.num_k_blocks);
                 ok = mbar_wait_bounded(acc_empty_bar(buf), acc_phase ^ 1u, abort_flag, p.status,
-                                       kWaitMmaAccEmpty);
+                                       kWaitMmaAccEmpty, p.wait_ns);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BLOCK_N;
                 for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!__all_sync(0xffffffffu, ready)) {
-                        const long long c0 = p.dbg ? clock64() : 0;
+                        const long long c0 = O64_DBG(p) ? clock64() : 0;
                         ok = mbar_wait_bounded(full_bar(stage), phase, abort_flag, p.status,
-                                               kWaitMmaFull);
+                                               kWaitMmaFull, p.wait_ns);
                         ok = __all_sync(0xffffffffu, ok);
-                        if (p.dbg) wait_clk += clock64() - c0;
+                        if (O64_DBG(p)) wait_clk += clock64() - c0;
                         if (!ok) break;
                     }
                     const int next_stage = (stage + 1 == STAGES) ? 0 : stage + 1;
@@ -212,7 +215,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024);
                     const uint64_t b_desc =
                         B_KN ? make_smem_desc(b_addr, 8192, 1024) : make_smem_desc(b_addr, 16, 1024);
-                    if ((p.probe & 3) == 2) {
+                    if ((O64_PROBE(p) & 3) == 2) {
                         if (leader) mbar_arrive(empty_bar(stage));
                     } else if (leader) {
 #pragma unroll
@@ -230,9 +233,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 if (ok && leader) tc_commit(acc_full_bar(buf));
                 __syncwarp();
             }
-            if (p.dbg && leader) {
-                p.dbg[blockIdx.x * 8 + 0] = wait_clk;
-                p.dbg[blockIdx.x * 8 + 1] = clock64() - t_begin;
+            if (O64_DBG(p) && leader) {
+                O64_DBG(p)[blockIdx.x * 8 + 0] = wait_clk;
+                O64_DBG(p)[blockIdx.x * 8 + 1] = clock64() - t_begin;
             }
         }
         __syncwarp();
@@ -249,7 +252,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             // one lane polls, the warp follows (tcgen05.ld is warp-wide: the warp leaves together)
             if (lane == 0)
                 ok = mbar_wait_bounded(acc_full_bar(buf), acc_phase, abort_flag, p.status,
-                                       kWaitEpiAccFull);
+                                       kWaitEpiAccFull, p.wait_ns);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             tc_fence_after();
@@ -262,7 +265,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 else if constexpr (EPI != EPI_SWIGLU)
                     epilogue_partial<false>(p, p.partial, p.N, row0, nb * kOutN, t_row,
                                             smem_gen + L::kStagingOffset + quarter * kEpiStagingBytesPerWarp, BLOCK_N);
-            } else if (!(p.probe & 4))
+            } else if (!(O64_PROBE(p) & 4))
                 epilogue_tile<EPI, BLOCK_N>(p, row0, nb * kOutN, t_row,
                                             smem_gen + L::kStagingOffset + quarter * kEpiStagingBytesPerWarp);
             tc_fence_before();
@@ -327,18 +330,20 @@ int encode_2d(CUtensorMap *tm, int kind, const void *base, int64_t rows, int64_t
     return r == CUDA_SUCCESS ? O64_OK : O64_ERR_CUDA;
 }
 
-template <int KIND, bool B_KN, int EPI, int BLOCK_N, int STAGES>
+template <int KIND, bool B_KN, int EPI, int BLOCK_N, int STAGES, bool HOOK = false>
 static int launch_inst(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tb2,
                        const UmmaParams &p, int grid, cudaStream_t stream) {
     using L = SmemLayout<BLOCK_N, STAGES>;
-    auto kern = umma_gemm_kernel<KIND, B_KN, EPI, BLOCK_N, STAGES>;
-    static bool attr_set = false;  // per instantiation
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) !=
-            cudaSuccess)
-            return O64_ERR_CUDA;
-        attr_set = true;
-    }
+    auto kern = umma_gemm_kernel<KIND, B_KN, EPI, BLOCK_N, STAGES, HOOK>;
+    static KernelSetup ks;  // per instantiation; one set-up per device
+    const int rc = ks.once(
+        [&](int *) {
+            return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) == cudaSuccess
+                       ? O64_OK
+                       : O64_ERR_CUDA;
+        },
+        nullptr);
+    if (rc) return rc;
     kern<<<grid, kThreads, L::kDynamic, stream>>>(ta, tb, tb2, p);
     return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
 }
@@ -386,6 +391,8 @@ int umma_launch(const UmmaCall &c) {
     const int out_elem = (c.epi == EPI_S32) ? 4 : 2;
     p.vec_ok = aligned16(c.C) && ((c.ldc * out_elem) % 16 == 0);
     p.status = c.status_word;
+    p.wait_ns = c.wait_ns ? c.wait_ns : kDefaultWaitNs;
+    p.test_withhold = c.test_withhold;
     p.split_k = 1;
     p.kb_per_split = p.num_k_blocks;
     p.partial = nullptr;
@@ -417,13 +424,17 @@ int umma_launch(const UmmaCall &c) {
     }
     if (rc) return rc;
 
+#ifdef O64_TUNING
     {
         const char *pr = getenv("O64_PROBE");  // pipeline probes for tuning; results are invalid
         p.probe = pr ? atoi(pr) : 0;
     }
     // O64_TRACE=pipe: the issuing threads count the cycles they spend waiting; the launch is then
-    // synchronous and prints the averages (a tuning aid, off by default)
-    static unsigned long long *dbg_buf = nullptr;
+    // synchronous and prints the averages
+    static unsigned long long *dbg_bufs[kMaxDevices] = {nullptr};  // one buffer per device
+    int dbg_dev = 0;
+    if (cudaGetDevice(&dbg_dev) != cudaSuccess || dbg_dev < 0 || dbg_dev >= kMaxDevices) dbg_dev = 0;
+    unsigned long long *&dbg_buf = dbg_bufs[dbg_dev];
     const char *tr = getenv("O64_TRACE");
     const bool trace_pipe = tr && strstr(tr, "pipe") && c.may_allocate;
     p.dbg = nullptr;
@@ -453,6 +464,9 @@ int umma_launch(const UmmaCall &c) {
                     100.0 * s[2] / (s[3] > 0 ? s[3] : 1), s[3] / n, s[4] / n, n);
         return rc_launch;
     };
+#else
+    auto report = [](int rc_launch, int) { return rc_launch; };
+#endif
     if (wide) return report(umma_launch_wide(c, ta, tb, tb2, p), pl.num_ctas);
     if (pair) return report(umma_launch_pair(c, ta, tb, tb2, p), pl.num_ctas);
     const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles * p.split_k;
@@ -460,6 +474,12 @@ int umma_launch(const UmmaCall &c) {
 
 #define O64_INST(KIND, BKN, EPI_, BN, ST) \
     return report(launch_inst<KIND, BKN, EPI_, BN, ST>(ta, tb, tb2, p, grid, c.stream), grid)
+
+    // the one instantiation with the test hook: bf16, B [N,K], 128 x 256 tiles
+    if (c.test_withhold >= 0) {
+        if (c.kind != O64_KIND_BF16 || c.epi != EPI_BF16 || c.b_kn || block_n != 256 || p.split_k != 1) return O64_ERR_DTYPE;
+        return launch_inst<MMA_F16, false, EPI_BF16, 256, 4, true>(ta, tb, tb2, p, grid, c.stream);
+    }
 
     if (c.kind == O64_KIND_BF16) {
         if (c.epi == EPI_SWIGLU) {

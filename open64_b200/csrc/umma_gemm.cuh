@@ -7,6 +7,8 @@
 
 namespace o64 {
 
+constexpr unsigned long long kDefaultWaitNs = 2000000000ull;  // two seconds
+
 enum : int { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_SCALED_BF16 = 2, EPI_S32 = 3 };
 
 // One GEMM on the tensor cores.  A is [M,K] row-major.  B is [N,K] row-major (b_kn == false)
@@ -36,6 +38,8 @@ struct UmmaCall {
     int n_peers = 0;           // fused all-gather: peer copies of C (same element as C), at most 7
     void *peer_c[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     bool may_allocate = true;  // false: never allocate (the pipeline trace, which needs a buffer, stays off)
+    unsigned long long wait_ns = 0;  // budget of the kernels' bounded waits; 0 = kDefaultWaitNs
+    int test_withhold = -1;          // o64_test_* only: K block whose loads the producer leaves out
 };
 
 // Validates alignment, encodes the tensor maps and launches.  Returns O64_OK or an error code.

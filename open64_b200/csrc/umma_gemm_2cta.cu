@@ -47,7 +47,7 @@ struct PairSmemLayout {
     static constexpr int kDynamic = kTotal + 1024;
 };
 
-template <int KIND, bool B_KN, int EPI, int BLOCK_N, int STAGES>
+template <int KIND, bool B_KN, int EPI, int BLOCK_N, int STAGES, bool HOOK = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                       const __grid_constant__ CUtensorMap tm_b2, const UmmaParams p) {
@@ -121,6 +121,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             uint32_t phase = 0;
             bool ok = true;
             long long wait_clk = 0;
+            [[maybe_unused]] int issued = 0;  // K blocks this producer has dealt with (test hook)
             const long long t_begin = clock64();
             for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
                 int mb, nb;
@@ -128,18 +129,20 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                 const int m0 = mb * kPairM + (int)rank * kBlockM;
                 const int n0 = nb * kOutN;
                 for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-                    const long long c0 = p.dbg ? clock64() : 0;
+                    const long long c0 = O64_DBG(p) ? clock64() : 0;
                     ok = mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
-                                           kWaitPairProducerEmpty);
+                                           kWaitPairProducerEmpty, p.wait_ns);
                     ok = __all_sync(0xffffffffu, ok);
-                    if (p.dbg) wait_clk += clock64() - c0;
+                    if (O64_DBG(p)) wait_clk += clock64() - c0;
                     if (!ok) break;
                     const uint32_t a_dst = smem_base + stage * L::kStageBytes;
                     const uint32_t b_dst = a_dst + kABytes;
                     const uint32_t full0 = map_to_cta(full_bar(stage), 0);
-                    if ((p.probe & 3) == 1) {
+                    bool withhold = false;  // both CTAs count alike, so both leave the same K block out
+                    if constexpr (HOOK) withhold = (issued++ == p.test_withhold);
+                    if ((O64_PROBE(p) & 3) == 1) {
                         if (rank == 0 && leader) mbar_arrive(full_bar(stage));
-                    } else if (leader) {
+                    } else if (leader && !withhold) {
                         if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * L::kStageBytes);
                         tma_load_2d_pair(a_dst, &tm_a, kb * kBlockK, m0, full0);
                         if constexpr (!B_KN) {
@@ -166,9 +169,9 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                     }
                 }
             }
-            if (p.dbg && leader) {
-                p.dbg[blockIdx.x * 8 + 2] = wait_clk;
-                p.dbg[blockIdx.x * 8 + 3] = clock64() - t_begin;
+            if (O64_DBG(p) && leader) {
+                O64_DBG(p)[blockIdx.x * 8 + 2] = wait_clk;
+                O64_DBG(p)[blockIdx.x * 8 + 3] = clock64() - t_begin;
             }
         }
         __syncwarp();
@@ -191,17 +194,17 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                 const int buf = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1u;
                 ok = mbar_wait_bounded(acc_empty_bar(buf), acc_phase ^ 1u, abort_flag, p.status,
-                                       kWaitPairMmaAccEmpty);
+                                       kWaitPairMmaAccEmpty, p.wait_ns);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BLOCK_N;
                 for (int kb = 0; kb < p.num_k_blocks; ++kb) {
                     if (!__all_sync(0xffffffffu, ready)) {
-                        const long long c0 = p.dbg ? clock64() : 0;
-                        ok = mbar_wait_bounded(full_bar(stage), phase, abort_flag, p.status, kWaitPairMmaFull);
+                        const long long c0 = O64_DBG(p) ? clock64() : 0;
+                        ok = mbar_wait_bounded(full_bar(stage), phase, abort_flag, p.status, kWaitPairMmaFull, p.wait_ns);
                         ok = __all_sync(0xffffffffu, ok);
-                        if (p.dbg) wait_clk += clock64() - c0;
+                        if (O64_DBG(p)) wait_clk += clock64() - c0;
                         if (!ok) break;
                     }
                     const int next_stage = (stage + 1 == STAGES) ? 0 : stage + 1;
@@ -213,7 +216,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                     const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024);
                     const uint64_t b_desc =
                         B_KN ? make_smem_desc(b_addr, 8192, 1024) : make_smem_desc(b_addr, 16, 1024);
-                    if ((p.probe & 3) == 2) {
+                    if ((O64_PROBE(p) & 3) == 2) {
                         if (leader) {
                             mbar_arrive(empty_bar(stage));
                             mbar_arrive_cluster(map_to_cta(empty_bar(stage), 1));
@@ -236,9 +239,9 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                 if (ok && leader) tc_commit_pair_mask(acc_full_bar(buf), 3);
                 __syncwarp();
             }
-            if (p.dbg && leader) {
-                p.dbg[blockIdx.x * 8 + 0] = wait_clk;
-                p.dbg[blockIdx.x * 8 + 1] = clock64() - t_begin;
+            if (O64_DBG(p) && leader) {
+                O64_DBG(p)[blockIdx.x * 8 + 0] = wait_clk;
+                O64_DBG(p)[blockIdx.x * 8 + 1] = clock64() - t_begin;
             }
         }
         __syncwarp();
@@ -253,13 +256,13 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             const int buf = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1u;
             if (lane == 0)
-                ok = mbar_wait_bounded(acc_full_bar(buf), acc_phase, abort_flag, p.status, kWaitPairEpiAccFull);
+                ok = mbar_wait_bounded(acc_full_bar(buf), acc_phase, abort_flag, p.status, kWaitPairEpiAccFull, p.wait_ns);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             tc_fence_after();
             const long long row0 = (long long)mb * kPairM + (long long)rank * kBlockM + quarter * 32;
             const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BLOCK_N;
-            if (!(p.probe & 4))
+            if (!(O64_PROBE(p) & 4))
                 epilogue_tile<EPI, BLOCK_N>(p, row0, nb * kOutN, t_row,
                                             smem_gen + L::kStagingOffset + quarter * kEpiStagingBytesPerWarp);
             tc_fence_before();
@@ -283,38 +286,40 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     }
 }
 
-template <int KIND, bool B_KN, int EPI, int BLOCK_N, int STAGES>
+template <int KIND, bool B_KN, int EPI, int BLOCK_N, int STAGES, bool HOOK = false>
 static int launch_pair_inst(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tb2,
                             const UmmaParams &p, int grid, cudaStream_t stream) {
     using L = PairSmemLayout<BLOCK_N, STAGES>;
-    auto kern = umma_gemm_pair_kernel<KIND, B_KN, EPI, BLOCK_N, STAGES>;
-    static bool attr_set = false;
-    static int max_pairs = 0;  // pairs the device can hold at once (the tile walk assumes co-residency)
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) !=
-            cudaSuccess)
-            return O64_ERR_CUDA;
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(2, 1, 1);
-        cfg.blockDim = dim3(kThreads, 1, 1);
-        cfg.dynamicSmemBytes = L::kDynamic;
-        cudaLaunchAttribute at[1];
-        at[0].id = cudaLaunchAttributeClusterDimension;
-        at[0].val.clusterDim.x = 2;
-        at[0].val.clusterDim.y = 1;
-        at[0].val.clusterDim.z = 1;
-        cfg.attrs = at;
-        cfg.numAttrs = 1;
-        int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) {
-            (void)cudaGetLastError();
-            n = 0;
-        }
-        max_pairs = n;
-        const char *tr = getenv("O64_TRACE");
-        if (tr && strstr(tr, "plan")) fprintf(stderr, "[o64 pair kernel: %d CTA pairs can be resident]\n", n);
-        attr_set = true;
-    }
+    auto kern = umma_gemm_pair_kernel<KIND, B_KN, EPI, BLOCK_N, STAGES, HOOK>;
+    static KernelSetup ks;  // per instantiation; one set-up per device
+    int max_pairs = 0;      // pairs the device can hold at once (the tile walk assumes co-residency)
+    const int rc = ks.once(
+        [&](int *clusters) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) != cudaSuccess)
+                return (int)O64_ERR_CUDA;
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(2, 1, 1);
+            cfg.blockDim = dim3(kThreads, 1, 1);
+            cfg.dynamicSmemBytes = L::kDynamic;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeClusterDimension;
+            at[0].val.clusterDim.x = 2;
+            at[0].val.clusterDim.y = 1;
+            at[0].val.clusterDim.z = 1;
+            cfg.attrs = at;
+            cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) {
+                (void)cudaGetLastError();
+                n = 0;
+            }
+            *clusters = n;
+            const char *tr = getenv("O64_TRACE");
+            if (tr && strstr(tr, "plan")) fprintf(stderr, "[o64 pair kernel: %d CTA pairs can be resident]\n", n);
+            return (int)O64_OK;
+        },
+        &max_pairs);
+    if (rc) return rc;
     if (max_pairs > 0 && grid > 2 * max_pairs) grid = 2 * max_pairs;
     kern<<<grid, kThreads, L::kDynamic, stream>>>(ta, tb, tb2, p);
     return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
@@ -333,6 +338,10 @@ int umma_launch_pair(const UmmaCall &c, const CUtensorMap &ta, const CUtensorMap
 #define O64_PAIR(KIND, BKN, EPI_, BN, ST) \
     return launch_pair_inst<KIND, BKN, EPI_, BN, ST>(ta, tb, tb2, p, grid, c.stream)
 
+    if (c.test_withhold >= 0) {  // the one instantiation with the test hook: bf16, B [N,K], 256 x 256 tiles
+        if (c.kind != O64_KIND_BF16 || c.epi != EPI_BF16 || c.b_kn || block_n != 256) return O64_ERR_DTYPE;
+        return launch_pair_inst<MMA_F16, false, EPI_BF16, 256, 6, true>(ta, tb, tb2, p, grid, c.stream);
+    }
     if (c.kind == O64_KIND_BF16) {
         if (c.epi == EPI_SWIGLU) {
             if (block_n == 256) O64_PAIR(MMA_F16, true, EPI_SWIGLU, 256, 6);

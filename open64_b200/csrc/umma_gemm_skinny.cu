@@ -208,7 +208,7 @@ __device__ __forceinline__ void gather_store_dispatch(const UmmaParams &p, const
 // KIND / B_KN / EPI as in umma_gemm_kernel; BN: columns of a tile (256, or 128: half the partial
 // sums to exchange per CTA and twice the tiles, for 128 rows or a narrow weight).  Launched with
 // clusters of p.sk_split CTAs; CTA r of cluster t multiplies K blocks [r*kbs/S, (r+1)*kbs/S) of tile t.
-template <int KIND, bool B_KN, int EPI, int BN>
+template <int KIND, bool B_KN, int EPI, int BN, bool HOOK = false>
 __global__ void __launch_bounds__(kSkThreads, 1)
 umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                         const UmmaParams p) {
@@ -251,7 +251,7 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
     // of its first weights then overlap this grid's tail (it waits below before it reads or writes
     // anything this grid may touch).
     griddep_launch_dependents();
-    unsigned long long *dbg = p.dbg ? p.dbg + 8 * blockIdx.x : nullptr;  // O64_TRACE=pipe: time stamps (ns)
+    unsigned long long *dbg = O64_DBG(p) ? O64_DBG(p) + 8 * blockIdx.x : nullptr;  // O64_TRACE=pipe: time stamps (ns)
     if (threadIdx.x == 0) {
         if (dbg) dbg[0] = globaltimer_ns();
         for (int s = 0; s < kSkMaxStages; ++s) {
@@ -297,12 +297,14 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
         int stage = 0;
         uint32_t phase = 0;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
-            bool ok = mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kWaitProducerEmpty);
+            bool ok = mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kWaitProducerEmpty, p.wait_ns);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             const uint32_t b_dst = smem_base + stage * stage_bytes;
             const uint32_t a_dst = b_dst + kBBytes;
-            if (leader) {
+            bool withhold = false;  // test hook: this K block's loads are left out
+            if constexpr (HOOK) withhold = (kb - kb_begin == p.test_withhold);
+            if (leader && !withhold) {
                 mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
                 tma_load_2d(a_dst, &tm_a, kb * kBlockK, m_base, full_bar(stage));
                 if constexpr (!B_KN) {
@@ -332,7 +334,7 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
         uint32_t phase = 0;
         bool ok = true;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
-            ok = mbar_wait_bounded(full_bar(stage), phase, abort_flag, p.status, kWaitMmaFull);
+            ok = mbar_wait_bounded(full_bar(stage), phase, abort_flag, p.status, kWaitMmaFull, p.wait_ns);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             if (dbg && leader && kb == kb_begin) dbg[2] = globaltimer_ns();
@@ -360,7 +362,7 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
     } else {
         // ------------------------------ epilogue warps: wait for the accumulator ---------
         bool ok = true;
-        if (lane == 0) ok = mbar_wait_bounded(acc_full_bar, 0, abort_flag, p.status, kWaitEpiAccFull);
+        if (lane == 0) ok = mbar_wait_bounded(acc_full_bar, 0, abort_flag, p.status, kWaitEpiAccFull, p.wait_ns);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         tc_fence_after();
         if (dbg && warp == 2 && lane == 0) dbg[4] = globaltimer_ns();
@@ -417,36 +419,40 @@ umma_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
     }
 }
 
-template <int KIND, bool B_KN, int EPI, int BN>
+template <int KIND, bool B_KN, int EPI, int BN, bool HOOK = false>
 static int launch_skinny(const CUtensorMap &ta, const CUtensorMap &tb, UmmaParams p, int tiles, int want_split,
                          cudaStream_t stream, int *split_out) {
-    auto kern = umma_gemm_skinny_kernel<KIND, B_KN, EPI, BN>;
-    static bool attr_set = false;  // per instantiation
-    static int max_split = 1;      // largest cluster the device can place with this much shared memory
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkDynamic) != cudaSuccess)
-            return O64_ERR_CUDA;
-        for (int s = 8; s > 1; s /= 2) {
-            cudaLaunchConfig_t cfg = {};
-            cfg.gridDim = dim3(s, 1, 1);
-            cfg.blockDim = dim3(kSkThreads, 1, 1);
-            cfg.dynamicSmemBytes = kSkDynamic;
-            cudaLaunchAttribute at[1];
-            at[0].id = cudaLaunchAttributeClusterDimension;
-            at[0].val.clusterDim.x = s;
-            at[0].val.clusterDim.y = 1;
-            at[0].val.clusterDim.z = 1;
-            cfg.attrs = at;
-            cfg.numAttrs = 1;
-            int n = 0;
-            if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n >= 1) {
-                max_split = s;
-                break;
+    auto kern = umma_gemm_skinny_kernel<KIND, B_KN, EPI, BN, HOOK>;
+    static KernelSetup ks;  // per instantiation; one set-up per device
+    int max_split = 1;      // largest cluster the device can place with this much shared memory
+    const int rc = ks.once(
+        [&](int *clusters) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkDynamic) != cudaSuccess)
+                return (int)O64_ERR_CUDA;
+            *clusters = 1;
+            for (int s = 8; s > 1; s /= 2) {
+                cudaLaunchConfig_t cfg = {};
+                cfg.gridDim = dim3(s, 1, 1);
+                cfg.blockDim = dim3(kSkThreads, 1, 1);
+                cfg.dynamicSmemBytes = kSkDynamic;
+                cudaLaunchAttribute at[1];
+                at[0].id = cudaLaunchAttributeClusterDimension;
+                at[0].val.clusterDim.x = s;
+                at[0].val.clusterDim.y = 1;
+                at[0].val.clusterDim.z = 1;
+                cfg.attrs = at;
+                cfg.numAttrs = 1;
+                int n = 0;
+                if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n >= 1) {
+                    *clusters = s;
+                    break;
+                }
+                (void)cudaGetLastError();
             }
-            (void)cudaGetLastError();
-        }
-        attr_set = true;
-    }
+            return (int)O64_OK;
+        },
+        &max_split);
+    if (rc) return rc;
     int split = want_split < max_split ? want_split : max_split;
     if (split < 1) split = 1;
     p.sk_split = split;
@@ -509,8 +515,10 @@ int umma_launch_skinny(const UmmaCall &c, UmmaParams p) {
     p.split_k = 1;
     p.kb_per_split = p.num_k_blocks;
     p.n_peers = 0;
+#ifdef O64_TUNING
     p.probe = 0;
     p.dbg = nullptr;
+#endif
     p.sk_a_rows = a_rows;
     const int stage_bytes = (bn + a_rows) * kRowBytes;
     p.sk_stages = kSkRingBytes / stage_bytes;
@@ -522,9 +530,14 @@ int umma_launch_skinny(const UmmaCall &c, UmmaParams p) {
     if (want > p.num_k_blocks) want = 1;
     const int tiles = p.num_m_tiles * p.num_n_tiles;
 
+    int split = 1;
+#ifdef O64_TUNING
     // O64_TRACE=pipe: every CTA leaves time stamps; the launch is then synchronous and prints where
     // the time went (a tuning aid, off by default)
-    static unsigned long long *dbg_buf = nullptr;
+    static unsigned long long *dbg_bufs[kMaxDevices] = {nullptr};  // one buffer per device
+    int dbg_dev = 0;
+    if (cudaGetDevice(&dbg_dev) != cudaSuccess || dbg_dev < 0 || dbg_dev >= kMaxDevices) dbg_dev = 0;
+    unsigned long long *&dbg_buf = dbg_bufs[dbg_dev];
     constexpr int kDbgCtas = 1024;
     const char *tr = getenv("O64_TRACE");
     const bool trace = tr && strstr(tr, "pipe") && c.may_allocate && tiles * 8 <= kDbgCtas;
@@ -533,7 +546,6 @@ int umma_launch_skinny(const UmmaCall &c, UmmaParams p) {
         if (dbg_buf) cudaMemsetAsync(dbg_buf, 0, 8 * kDbgCtas * sizeof(unsigned long long), c.stream);
         p.dbg = dbg_buf;
     }
-    int split = 1;
     auto report = [&](int rc_launch) {
         if (!trace || !dbg_buf || rc_launch) return rc_launch;
         static unsigned long long host[8 * kDbgCtas];
@@ -558,9 +570,16 @@ int umma_launch_skinny(const UmmaCall &c, UmmaParams p) {
                 sum[4] / grid, mx[4], sum[5] / grid, mx[5], sum[6] / grid, mx[6], sum[7] / grid, mx[7]);
         return rc_launch;
     };
+#else
+    auto report = [](int rc_launch) { return rc_launch; };
+#endif
 #define O64_SK(KIND, BKN, EPI_)                                                                              \
     return report(bn == 128 ? launch_skinny<KIND, BKN, EPI_, 128>(ta, tb, p, tiles, want, c.stream, &split)  \
                             : launch_skinny<KIND, BKN, EPI_, 256>(ta, tb, p, tiles, want, c.stream, &split))
+    if (c.test_withhold >= 0) {  // the one instantiation with the test hook: bf16, B [N,K], 256-column tiles
+        if (c.kind != O64_KIND_BF16 || c.epi != EPI_BF16 || c.b_kn || bn != 256) return O64_ERR_DTYPE;
+        return launch_skinny<MMA_F16, false, EPI_BF16, 256, true>(ta, tb, p, tiles, want, c.stream, &split);
+    }
     if (c.kind == O64_KIND_BF16 && c.epi == EPI_BF16) {
         if (c.b_kn) O64_SK(MMA_F16, true, EPI_BF16);
         O64_SK(MMA_F16, false, EPI_BF16);

@@ -61,7 +61,7 @@ struct WideSmem {
     static constexpr int kDynamic = kTotal + 1024;
 };
 
-template <int KIND, bool B_KN, int EPI>
+template <int KIND, bool B_KN, int EPI, bool HOOK = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kWideThreads, 1)
 umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                       const __grid_constant__ CUtensorMap tm_b2, const UmmaParams p) {
@@ -135,6 +135,7 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             uint32_t phase = 0;
             bool ok = true;
             long long wait_clk = 0;
+            [[maybe_unused]] int issued = 0;  // K blocks this producer has dealt with (test hook)
             const long long t_begin = clock64();
             for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
                 int mb, nb;
@@ -142,18 +143,20 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                 const int m0 = mb * kPairM + (int)rank * kWideRowsPerCta;
                 const int n0 = nb * kOutN;
                 for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-                    const long long c0 = p.dbg ? clock64() : 0;
+                    const long long c0 = O64_DBG(p) ? clock64() : 0;
                     ok = mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
-                                           kWaitWideProducerEmpty);
+                                           kWaitWideProducerEmpty, p.wait_ns);
                     ok = __all_sync(0xffffffffu, ok);
-                    if (p.dbg) wait_clk += clock64() - c0;
+                    if (O64_DBG(p)) wait_clk += clock64() - c0;
                     if (!ok) break;
                     const uint32_t a_dst = smem_base + stage * kWideStageBytes;
                     const uint32_t b_dst = a_dst + kWideABytes;
                     const uint32_t full0 = map_to_cta(full_bar(stage), 0);
-                    if ((p.probe & 3) == 1) {
+                    bool withhold = false;  // both CTAs count alike, so both leave the same K block out
+                    if constexpr (HOOK) withhold = (issued++ == p.test_withhold);
+                    if ((O64_PROBE(p) & 3) == 1) {
                         if (rank == 0 && leader) mbar_arrive(full_bar(stage));
-                    } else if (leader) {
+                    } else if (leader && !withhold) {
                         if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * kWideStageBytes);
                         tma_load_2d_pair(a_dst, &tm_a, kb * kBlockK, m0, full0);
                         if constexpr (!B_KN) {
@@ -178,9 +181,9 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                     }
                 }
             }
-            if (p.dbg && leader) {
-                p.dbg[blockIdx.x * 8 + 2] = wait_clk;
-                p.dbg[blockIdx.x * 8 + 3] = clock64() - t_begin;
+            if (O64_DBG(p) && leader) {
+                O64_DBG(p)[blockIdx.x * 8 + 2] = wait_clk;
+                O64_DBG(p)[blockIdx.x * 8 + 3] = clock64() - t_begin;
             }
         }
         __syncwarp();
@@ -202,10 +205,10 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++it) {
                 for (int kb = 0; kb < p.num_k_blocks; ++kb) {
                     if (!__all_sync(0xffffffffu, ready)) {
-                        const long long c0 = p.dbg ? clock64() : 0;
-                        ok = mbar_wait_bounded(full_bar(stage), phase, abort_flag, p.status, kWaitWideMmaFull);
+                        const long long c0 = O64_DBG(p) ? clock64() : 0;
+                        ok = mbar_wait_bounded(full_bar(stage), phase, abort_flag, p.status, kWaitWideMmaFull, p.wait_ns);
                         ok = __all_sync(0xffffffffu, ok);
-                        if (p.dbg) wait_clk += clock64() - c0;
+                        if (O64_DBG(p)) wait_clk += clock64() - c0;
                         if (!ok) break;
                     }
                     const int next_stage = (stage + 1 == STAGES) ? 0 : stage + 1;
@@ -218,7 +221,7 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                     const uint64_t a_desc1 = make_smem_desc(a_addr + kABytes, 16, 1024);
                     const uint64_t b_desc =
                         B_KN ? make_smem_desc(b_addr, 8192, 1024) : make_smem_desc(b_addr, 16, 1024);
-                    if ((p.probe & 3) == 2) {
+                    if ((O64_PROBE(p) & 3) == 2) {
                         if (leader) {
                             mbar_arrive(empty_bar(stage));
                             mbar_arrive_cluster(map_to_cta(empty_bar(stage), 1));
@@ -227,10 +230,10 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                         if (kb == 0) {
                             // the first MMA of a tile overwrites the accumulator: wait until the
                             // epilogue has drained it (accumulator 1 is drained second)
-                            const long long a0 = p.dbg ? clock64() : 0;
+                            const long long a0 = O64_DBG(p) ? clock64() : 0;
                             ok = mbar_wait_bounded(acc_empty_bar(0), (it & 1u) ^ 1u, abort_flag, p.status,
-                                                   kWaitWideMmaAccEmpty);
-                            if (p.dbg) acc_wait_clk += clock64() - a0;
+                                                   kWaitWideMmaAccEmpty, p.wait_ns);
+                            if (O64_DBG(p)) acc_wait_clk += clock64() - a0;
                             ok = __all_sync(0xffffffffu, ok);
                             if (!ok) break;
                             tc_fence_after();
@@ -244,10 +247,10 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                             }
                             if (kb == 0) {
                                 __syncwarp();
-                                const long long a1 = p.dbg ? clock64() : 0;
+                                const long long a1 = O64_DBG(p) ? clock64() : 0;
                                 ok = mbar_wait_bounded(acc_empty_bar(1), (it & 1u) ^ 1u, abort_flag, p.status,
-                                                       kWaitWideMmaAccEmpty);
-                                if (p.dbg) acc_wait_clk += clock64() - a1;
+                                                       kWaitWideMmaAccEmpty, p.wait_ns);
+                                if (O64_DBG(p)) acc_wait_clk += clock64() - a1;
                                 ok = __all_sync(0xffffffffu, ok);
                                 if (!ok) break;
                                 tc_fence_after();
@@ -272,10 +275,10 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                 }
                 __syncwarp();
             }
-            if (p.dbg && leader) {
-                p.dbg[blockIdx.x * 8 + 0] = wait_clk;
-                p.dbg[blockIdx.x * 8 + 5] = acc_wait_clk;
-                p.dbg[blockIdx.x * 8 + 1] = clock64() - t_begin;
+            if (O64_DBG(p) && leader) {
+                O64_DBG(p)[blockIdx.x * 8 + 0] = wait_clk;
+                O64_DBG(p)[blockIdx.x * 8 + 5] = acc_wait_clk;
+                O64_DBG(p)[blockIdx.x * 8 + 1] = clock64() - t_begin;
             }
         }
         __syncwarp();
@@ -294,25 +297,25 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
 #pragma unroll 1
             for (int g = 0; g < 2 && ok; ++g) {
                 if (lane == 0)
-                    ok = mbar_wait_bounded(acc_full_bar(g), it & 1u, abort_flag, p.status, kWaitWideEpiAccFull);
+                    ok = mbar_wait_bounded(acc_full_bar(g), it & 1u, abort_flag, p.status, kWaitWideEpiAccFull, p.wait_ns);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
                 tc_fence_after();
                 const long long row0 = (long long)mb * kPairM + (long long)rank * kWideRowsPerCta +
                                        g * kBlockM + quarter * 32;
                 const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + g * BLOCK_N;
-                const long long e0 = p.dbg ? clock64() : 0;
-                if (!(p.probe & 4))
+                const long long e0 = O64_DBG(p) ? clock64() : 0;
+                if (!(O64_PROBE(p) & 4))
                     epilogue_tile<EPI, BLOCK_N>(p, row0, nb * kOutN, t_row,
                                                 smem_gen + L::kStagingOffset + (warp - 2) * kEpiStagingBytesPerWarp,
                                                 half * kColsPerWarp, (half + 1) * kColsPerWarp);
                 tc_fence_before();
                 __syncwarp();
-                if (p.dbg) epi_clk += clock64() - e0;
+                if (O64_DBG(p)) epi_clk += clock64() - e0;
                 if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty_bar(g), 0));
             }
         }
-        if (p.dbg && warp == 2 && lane == 0) p.dbg[blockIdx.x * 8 + 4] = epi_clk;
+        if (O64_DBG(p) && warp == 2 && lane == 0) O64_DBG(p)[blockIdx.x * 8 + 4] = epi_clk;
     }
 
     // ------------------------------ teardown --------------------------------------------
@@ -329,35 +332,38 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     }
 }
 
-template <int KIND, bool B_KN, int EPI>
+template <int KIND, bool B_KN, int EPI, bool HOOK = false>
 static int launch_wide_inst(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tb2,
                             const UmmaParams &p, int grid, cudaStream_t stream) {
-    auto kern = umma_gemm_wide_kernel<KIND, B_KN, EPI>;
-    static bool attr_set = false;
-    static int max_pairs = 0;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, WideSmem::kDynamic) !=
-            cudaSuccess)
-            return O64_ERR_CUDA;
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(2, 1, 1);
-        cfg.blockDim = dim3(kWideThreads, 1, 1);
-        cfg.dynamicSmemBytes = WideSmem::kDynamic;
-        cudaLaunchAttribute at[1];
-        at[0].id = cudaLaunchAttributeClusterDimension;
-        at[0].val.clusterDim.x = 2;
-        at[0].val.clusterDim.y = 1;
-        at[0].val.clusterDim.z = 1;
-        cfg.attrs = at;
-        cfg.numAttrs = 1;
-        int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) {
-            (void)cudaGetLastError();
-            n = 0;
-        }
-        max_pairs = n;
-        attr_set = true;
-    }
+    auto kern = umma_gemm_wide_kernel<KIND, B_KN, EPI, HOOK>;
+    static KernelSetup ks;  // per instantiation; one set-up per device
+    int max_pairs = 0;
+    const int rc = ks.once(
+        [&](int *clusters) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, WideSmem::kDynamic) !=
+                cudaSuccess)
+                return (int)O64_ERR_CUDA;
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(2, 1, 1);
+            cfg.blockDim = dim3(kWideThreads, 1, 1);
+            cfg.dynamicSmemBytes = WideSmem::kDynamic;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeClusterDimension;
+            at[0].val.clusterDim.x = 2;
+            at[0].val.clusterDim.y = 1;
+            at[0].val.clusterDim.z = 1;
+            cfg.attrs = at;
+            cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) {
+                (void)cudaGetLastError();
+                n = 0;
+            }
+            *clusters = n;
+            return (int)O64_OK;
+        },
+        &max_pairs);
+    if (rc) return rc;
     if (max_pairs > 0 && grid > 2 * max_pairs) grid = 2 * max_pairs;
     kern<<<grid, kWideThreads, WideSmem::kDynamic, stream>>>(ta, tb, tb2, p);
     return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
@@ -371,6 +377,10 @@ int umma_launch_wide(const UmmaCall &c, const CUtensorMap &ta, const CUtensorMap
     if (pairs > tiles) pairs = tiles;
     if (pairs < 1) pairs = 1;
     const int grid = (int)(2 * pairs);
+    if (c.test_withhold >= 0) {  // the one instantiation with the test hook: bf16, B [N,K]
+        if (c.kind != O64_KIND_BF16 || c.epi != EPI_BF16 || c.b_kn) return O64_ERR_DTYPE;
+        return launch_wide_inst<MMA_F16, false, EPI_BF16, true>(ta, tb, tb2, p, grid, c.stream);
+    }
     if (c.kind == O64_KIND_BF16) {
         if (c.epi == EPI_SWIGLU) return launch_wide_inst<MMA_F16, true, EPI_SWIGLU>(ta, tb, tb2, p, grid, c.stream);
         if (c.epi == EPI_BF16) {

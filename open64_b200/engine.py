@@ -105,6 +105,23 @@ class Engine:
         st = self.lib.o64_last_status(self._h, s, ctypes.byref(detail))
         return st, detail.value
 
+    def set_wait_budget_us(self, microseconds):
+        """Budget of the kernels' bounded waits for later calls (0 = the default, two seconds)."""
+        check(self.lib.o64_set_wait_budget_us(self._h, int(microseconds)), "o64_set_wait_budget_us")
+
+    def test_gemm_bf16_withheld(self, A, B, withhold_kblock, out=None):
+        """The failure-path hook: a bf16 GEMM (B [N,K]) whose loader leaves out one K block, so the
+        kernel's waits run out of the wait budget.  Returns the (undefined) result buffer; read
+        last_status() afterwards."""
+        M, K = A.shape
+        N = B.shape[0]
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
+        check(self.lib.o64_test_gemm_bf16_withheld(self._h, M, N, K, _ptr(A), A.stride(0), _ptr(B), B.stride(0),
+                                                   _ptr(out), out.stride(0), int(withhold_kblock), _stream(A)),
+              "o64_test_gemm_bf16_withheld")
+        return out
+
     # ---- native layer ------------------------------------------------------------------
     def linear_f32(self, A, B, bias=None, act="none", out=None):
         """act(A @ B + bias), fp32; A [M,K], B [K,N]."""

@@ -167,3 +167,38 @@ def test_blas_hook_binds_the_engines_symbols(front):
             env["F90_MATMUL_BLAS"] = "1"
         r = subprocess.run([sys.executable, "-c", prog], capture_output=True, text=True, env=env, cwd=ROOT)
         assert r.returncode == 0 and r.stdout.strip() == "ok", r.stdout + r.stderr
+
+
+@pytest.mark.parametrize("name", ["S4S4", "SS", "I1I4", "JI2", "C4S", "LL1"])
+def test_zero_sized_result_needs_no_device(front, name):
+    """A(0,k) x B(k,n): both the reference wrapper and the engine's entry point return before any
+    kernel would run, so the RESULT descriptors can be compared on a machine without a GPU."""
+    import open64_b200 as o
+    ka, kb = rf.split_kinds(name)
+    kr = rf.result_kind(ka, kb)
+    rng = np.random.default_rng(3)
+    a, b = fu.Operand(ka, (0, 5), rng), fu.Operand(kb, (5, 4), rng)
+    r_ref, r_eng = fu.Result(kr, (0, 4), associated=False), fu.Result(kr, (0, 4), associated=False)
+    assert rf.call(name, r_ref.desc, a.dv(), b.dv()) == 0
+    A, B = a.dv(), b.dv()
+    getattr(o.lib(), "_MATMUL_" + name)(ctypes.byref(r_eng.desc), ctypes.byref(A), ctypes.byref(B))
+    assert o.lib().o64_compat_last_status() == o.OK
+    # all words but the address: with nothing to allocate the reference stores an uninitialised
+    # MatrixDimenType.C (matmul.h:252-262 skips the malloc), the engine stores NULL
+    assert r_ref.descriptor_words()[:7] == r_eng.descriptor_words()[:7]
+    assert not r_eng.desc.ptr
+
+
+def test_result_without_element_length_gets_the_entry_points_kind(built):
+    """An unassociated REAL*8 RESULT whose type word carries no length: the engine sizes it from the
+    entry point's result kind and records that length, so strides are read back with the same unit."""
+    import open64_b200 as o
+    rng = np.random.default_rng(4)
+    a, b = fu.Operand("S", (0, 3), rng), fu.Operand("S", (3, 2), rng)
+    r = fu.Result("S", (0, 2), associated=False)
+    r.desc.type_bits = DopeVector.TYPE_REAL            # int_len = 0
+    A, B = a.dv(), b.dv()
+    o.lib()._MATMUL_SS(ctypes.byref(r.desc), ctypes.byref(A), ctypes.byref(B))
+    assert o.lib().o64_compat_last_status() == o.OK
+    assert (r.desc.type_bits >> 12) & 0xfff == 64
+    assert r.desc.dimension[0].stride_mult == 2 and r.desc.dimension[1].stride_mult == 0

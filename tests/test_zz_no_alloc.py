@@ -81,3 +81,21 @@ def test_rejections(built):
     assert 40000 * 512 > o._lib.STATIC_SCRATCH_BYTES
     assert f(40000, 64, 500, _ptr(big), 500, _ptr(Bb), 500, _ptr(Cb), 64, None) == o.ERR_NOMEM
     torch.cuda.synchronize()
+
+
+def test_no_device_memory_is_taken(eng):
+    """The property the entry point exists for: after the first call on the device (which resolves the
+    static array's address) a call whose operands need padded copies leaves the device's free memory
+    exactly where it was."""
+    A, B = o.workloads.c5_int8(130, 72, 200, seed=9)
+    Ad, Bd = A.to(DEV), B.to(DEV)
+    C = torch.empty((130, 72), dtype=torch.int32, device=DEV)
+    o.Engine.gemm_s8_static(Ad, Bd, out=C)               # warm-up: set-up and module load are behind us
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        o.Engine.gemm_s8_static(Ad, Bd, out=C)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert np.array_equal(C.cpu().numpy(), oracle.gemm_s8s8_s32(A.numpy(), B.numpy()))

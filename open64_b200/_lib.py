@@ -7,7 +7,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libo64gemm.so")
+# O64_LIBRARY: another build of the same library (the -DO64_TUNING one, for instance)
+LIB_PATH = os.environ.get("O64_LIBRARY") or os.path.join(_HERE, "libo64gemm.so")
 
 OK = 0
 ERR_RANK, ERR_CONFORM, ERR_NOMEM, ERR_ALIGN, ERR_DTYPE, ERR_TIMEOUT, ERR_CUDA, ERR_NCCL = range(-1, -9, -1)

@@ -1,7 +1,11 @@
 """Builds libo64gemm.so in-tree with nvcc for sm_100a (cross-compiles without a GPU) and the
 host-only source rewriter o64nest with g++.
 
-Usage:  python -m open64_b200.build [--force] [--verbose]
+Usage:  python -m open64_b200.build [--force] [--verbose] [--tuning]
+
+--tuning builds a second library, libo64gemm_tuning.so, with -DO64_TUNING: the kernels then carry
+the pipeline probes (O64_PROBE) and the cycle counters behind O64_TRACE=pipe, which the shipped
+library does not.  Point O64_LIBRARY at it to load it instead of the shipped one.
 """
 import os
 import subprocess
@@ -40,8 +44,11 @@ def _stale(target, deps):
     return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
 
 
-def build(force=False, verbose=False):
+def build(force=False, verbose=False, tuning=False):
     """Compile every source to an object (in parallel) and link the shared library."""
+    OBJ_DIR = os.path.join(HERE, "build", "tuning") if tuning else globals()["OBJ_DIR"]
+    OUT = os.path.join(HERE, "libo64gemm_tuning.so") if tuning else globals()["OUT"]
+    NVCC_FLAGS = globals()["NVCC_FLAGS"] + (["-DO64_TUNING"] if tuning else [])
     os.makedirs(OBJ_DIR, exist_ok=True)
     hdrs = [os.path.join(CSRC, h) for h in HEADERS] + [os.path.abspath(__file__)]
     jobs = []
@@ -82,4 +89,4 @@ def build(force=False, verbose=False):
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, tuning="--tuning" in sys.argv))

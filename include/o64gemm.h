@@ -214,6 +214,14 @@ int o64_test_gemm_bf16_withheld(o64_handle_t h, int64_t M, int64_t N, int64_t K,
                                 const void *B, int64_t ldb, void *C, int64_t ldc, int withhold_kblock,
                                 void *stream);
 
+/* Test hook: what the last launch of a CTA-pair kernel made from this thread did about a partly
+ * filled last wave of tiles - how many tiles it cut along K and over how many CTA pairs (0, 0: it ran
+ * whole tiles only).  No counterpart in the reference. */
+int o64_test_last_tail_split(int *tiles, int *pairs);
+/* Test hook, process-wide: 1 = cut the last wave's tiles along K whenever that wave is partly filled
+ * (also where the model expects no gain), 0 = never, -1 = back to the model's decision. */
+int o64_test_force_tail_split(int mode);
+
 /* One-thread-per-output reference kernels: an independent device implementation of the same
  * contracts, used to compare full matrices where a CPU check would take minutes.
  * out_f32: fp32 result [M,N] (s32 for O64_KIND_S8).  For O64_KIND_FP8 the scales and bias

@@ -20,7 +20,7 @@ STATIC_SCRATCH_BYTES = 16 << 20
 
 # every symbol include/o64gemm.h declares
 EXPORTS = [
-    "o64_create", "o64_destroy", "o64_last_status", "o64_set_wait_budget_us", "o64_test_gemm_bf16_withheld", "o64_status_string", "o64_version",
+    "o64_create", "o64_destroy", "o64_last_status", "o64_set_wait_budget_us", "o64_test_gemm_bf16_withheld", "o64_test_last_tail_split", "o64_test_force_tail_split", "o64_status_string", "o64_version",
     "o64_plan_get", "o64_plan_set", "o64_plan_model", "o64_plan_tune", "o64_plan_tune_clear", "o64_linear_f32", "o64_gemm_bf16", "o64_gemm_bf16_swiglu",
     "o64_gemm_fp8_scaled", "o64_gemm_s8s8_s32", "o64_gemm_s8s8_s32_static", "o64_naive_gemm", "o64_comm_unique_id",
     "o64_comm_init", "o64_comm_destroy", "o64_comm_alloc_result", "o64_gemm_s8_sharded_workspace", "o64_gemm_s8_sharded", "o64_gemm_bf16_sharded",
@@ -122,6 +122,8 @@ def lib():
     L.o64_destroy.argtypes = [vp]
     L.o64_last_status.argtypes = [vp, vp, pi]
     L.o64_status_string.argtypes = [ci]
+    L.o64_test_last_tail_split.argtypes = [pi, pi]
+    L.o64_test_force_tail_split.argtypes = [ci]
     L.o64_set_wait_budget_us.argtypes = [vp, i64]
     L.o64_test_gemm_bf16_withheld.argtypes = [vp, i64, i64, i64, vp, i64, vp, i64, vp, i64, ci, vp]
     L.o64_status_string.restype = ctypes.c_char_p

@@ -98,6 +98,10 @@ struct o64_handle_s {
     size_t sym_bytes = 0;
     int *barrier_word = nullptr;    // one int, reduced over the ranks as a stream-ordered barrier
     unsigned long long wait_ns = 0;  // budget of the kernels' bounded waits; 0 = the default (two seconds)
+    // CTA-pair kernels: slots and flags for the K split of a last, partly filled wave of tiles
+    // (allocated on the first launch of such a kernel; the kernels leave the flags at zero)
+    void *tail_slots = nullptr;
+    unsigned *tail_flags = nullptr;
 };
 
 #define CUDA_TRY(x)                          \
@@ -208,6 +212,8 @@ extern "C" int o64_destroy(o64_handle_t h) {
         if (h->ev_in[i]) cudaEventDestroy(h->ev_in[i]);
         if (h->ev_mm[i]) cudaEventDestroy(h->ev_mm[i]);
     }
+    if (h->tail_slots) cudaFree(h->tail_slots);
+    if (h->tail_flags) cudaFree(h->tail_flags);
     if (h->status_word) cudaFree(h->status_word);
     delete h;
     return O64_OK;
@@ -223,6 +229,8 @@ extern "C" int o64_last_status(o64_handle_t h, void *stream, int *detail) {
     if (detail) *detail = word;
     if (word != 0) {
         CUDA_TRY(cudaMemsetAsync(h->status_word, 0, sizeof(int), s));
+        // a kernel that gave up may have left words of the last-wave K split set
+        if (h->tail_flags) CUDA_TRY(cudaMemsetAsync(h->tail_flags, 0, kTailFlagWords * sizeof(unsigned), s));
         return O64_ERR_TIMEOUT;
     }
     return O64_OK;
@@ -491,6 +499,28 @@ static int pipeline_resources(o64_handle_t h) {
     return O64_OK;
 }
 
+// Gives a call of a CTA-pair kernel the handle's slot and flag memory for the K split of its last
+// wave (allocated once, 40 MB; without it the kernels simply run whole tiles).
+static void attach_tail(o64_handle_t h, UmmaCall *c) {
+    if (c->plan.cta_group != 2 || c->plan.split_k < 0) return;
+    if (!h->tail_slots) {
+        void *slots = nullptr, *flags = nullptr;
+        if (cudaMalloc(&slots, (size_t)kTailMaxPairs * kTailSlotBytesMax) != cudaSuccess ||
+            cudaMalloc(&flags, kTailFlagWords * sizeof(unsigned)) != cudaSuccess ||
+            cudaMemset(flags, 0, kTailFlagWords * sizeof(unsigned)) != cudaSuccess) {
+            (void)cudaGetLastError();
+            if (slots) cudaFree(slots);
+            if (flags) cudaFree(flags);
+            return;
+        }
+        h->tail_slots = slots;
+        h->tail_flags = static_cast<unsigned *>(flags);
+    }
+    c->tail_slots = h->tail_slots;
+    c->tail_flags = h->tail_flags;
+    c->tail_bytes = (size_t)kTailMaxPairs * kTailSlotBytesMax;
+}
+
 static int umma_entry(o64_handle_t h, int kind, bool b_kn, int epi, int64_t M, int64_t N, int64_t K,
                       const void *A, int64_t lda, const void *B, const void *B2, int64_t ldb, void *C,
                       int64_t ldc, const float *bias, const float *sa, const float *sb, int act,
@@ -609,6 +639,7 @@ static int umma_entry(o64_handle_t h, int kind, bool b_kn, int epi, int64_t M, i
             if (b.scale_a) b.scale_a += r0;
             plan_choose(kind, epi, nr, N, K, h->num_sms, &pin, &b.plan);
             if (b.plan.split_k > 1) b.plan.split_k = 1;
+            attach_tail(h, &b);
             if ((rc = umma_launch(b))) {
                 // leave nothing queued behind the caller's back: the side streams' copies and the
                 // waits recorded so far drain before the error is returned
@@ -644,6 +675,7 @@ static int umma_entry(o64_handle_t h, int kind, bool b_kn, int epi, int64_t M, i
     } else if (c.plan.split_k > 1) {
         c.plan.split_k = 1;
     }
+    attach_tail(h, &c);
     if ((rc = umma_launch(c))) return rc;
     if (split && epi != EPI_S32) {
         if ((rc = finalize_partial_bf16((const float *)h->ws, M, N, c.scale_a, c.scale_b, c.bias, act, out.dev,
@@ -695,6 +727,17 @@ extern "C" int o64_test_gemm_bf16_withheld(o64_handle_t h, int64_t M, int64_t N,
     if (is_host_ptr(A) || is_host_ptr(B) || is_host_ptr(C)) return O64_ERR_RANK;
     return umma_entry(h, O64_KIND_BF16, false, EPI_BF16, M, N, K, A, lda, B, nullptr, ldb, C, ldc, nullptr, nullptr,
                       nullptr, O64_ACT_NONE, stream, withhold_kblock);
+}
+
+extern "C" int o64_test_force_tail_split(int mode) {
+    force_tail_split(mode);
+    return O64_OK;
+}
+
+extern "C" int o64_test_last_tail_split(int *tiles, int *pairs) {
+    if (!tiles || !pairs) return O64_ERR_RANK;
+    last_tail_split(tiles, pairs);
+    return O64_OK;
 }
 
 extern "C" int o64_naive_gemm(o64_handle_t h, int kind, int64_t M, int64_t N, int64_t K, const void *A,
@@ -853,6 +896,7 @@ static int push_gemm(o64_handle_t h, int kind, int epi, int64_t M, int64_t N, in
         if (i == r) continue;
         c.peer_c[c.n_peers++] = static_cast<uint8_t *>(h->sym_peer[i]) + (size_t)r * ns * out_elem;
     }
+    attach_tail(h, &c);
     if ((rc = umma_launch(c))) return rc;
     // every rank's stores are complete when its kernel is; the barrier tells each rank that all
     // the others got there

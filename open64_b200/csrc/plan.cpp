@@ -23,6 +23,37 @@ static const double kLoadLatencyClk = 1900.0;        // TMA issue -> data in sha
 
 static int elem_bytes(int kind) { return kind == O64_KIND_BF16 ? 2 : (kind == O64_KIND_F32 ? 4 : 1); }
 
+// The K split of a last, partly filled wave of tiles (CTA-pair kernels): `tiles` tiles of `kb` K
+// blocks on `pairs` CTA pairs.  Whole tiles take (tiles / pairs + 1) * kb K-block times; with the
+// tiles of the last wave cut along K over the pairs it is tiles / pairs whole tiles, one piece, and
+// the hand-over (a partial accumulator stored, published, read back and added: measured at about 24
+// K-block times of the 256-row kernel).  Pieces stay at least a sixth of a tile long (at most seven pieces per tile) and the split
+// must save 8 % to be taken.  Returns the K-block times per pair; *tail_tiles = 0: whole tiles.
+long long tail_model(long long tiles, int pairs, long long kb, int rows_per_cta, long long max_pairs_by_memory,
+                     int force, int *tail_tiles, int *tail_pairs) {
+    *tail_tiles = 0;
+    *tail_pairs = 0;
+    if (pairs < 1) pairs = 1;
+    const long long rem = tiles % pairs, full = tiles / pairs;
+    const long long whole = (full + (rem ? 1 : 0)) * kb;
+    // the 512-row kernel keeps whole tiles: both of its accumulators fill tensor memory, its epilogue is
+    // exposed, and the extra registers of the hand-over cost its ordinary epilogue more than the split saves
+    if (rem == 0 || pairs < 2 || force == 0 || rows_per_cta == 256) return whole;
+    long long min_share = (kb + 5) / 6;
+    if (min_share < 4) min_share = 4;
+    long long sp = pairs;
+    if (rem * kb / sp < min_share) sp = rem * kb / min_share;
+    if (sp > max_pairs_by_memory) sp = max_pairs_by_memory;
+    if (sp <= rem) return whole;  // pieces as long as whole tiles: nothing to gain
+    const long long share = (rem * kb + sp - 1) / sp;
+    const long long handover = 24;
+    const long long cut = full * kb + share + handover;
+    if (force != 1 && cut * 100 > whole * 92) return whole;
+    *tail_tiles = (int)rem;
+    *tail_pairs = (int)sp;
+    return cut;
+}
+
 // cta_group = 1: a CTA owns a 128 x tile_n tile.  cta_group = 2: a pair of CTAs owns a
 // tile_m x tile_n tile (tile_m = 256: 128 rows per CTA; tile_m = 512: 256 rows per CTA as two
 // accumulators issued by two threads); each CTA loads its rows of A and tile_n / 2 rows of B
@@ -35,8 +66,17 @@ static double predict_ms(int kind, int epi, int64_t M, int64_t N, int64_t K, int
     const int rows_per_cta = tile_m / cta_group;
     const int units = num_ctas / cta_group;  // CTAs or CTA pairs working side by side
     const double tiles = double((M + tile_m - 1) / tile_m) * double((N + out_n - 1) / out_n);
-    const double waves = double(int64_t((tiles + units - 1) / units));
+    double waves = double(int64_t((tiles + units - 1) / units));
     const double kblocks = double((K + block_k - 1) / block_k);
+    if (cta_group == 2 && units >= 2) {
+        // a partly filled last wave may be cut along K (umma_common.cuh, work_item)
+        int tt = 0, tp = 0;
+        const long long t = tail_model((long long)tiles, units, (long long)kblocks, rows_per_cta, kTailMaxPairs, -1, &tt, &tp);
+        // measured on M x 8192 x 8192 (M = 129 ... 1024): about a third of the K-block times the split
+        // saves on paper come back as time - with every SM busy the chip, which runs these kernels at
+        // its power limit, clocks lower - so a shape is not chosen for the full paper gain
+        if (tt > 0) waves -= 0.35 * (waves - double(t) / kblocks);
+    }
     const double flop_rate = kDenseBf16FlopPerClkSm * (eb == 1 ? 2.0 : 1.0);
     // measured: a tcgen05.mma of 128 rows costs about the same whether N is 128 or 256; paired
     // MMAs chained on one accumulator run about a tenth slower than alternated between two

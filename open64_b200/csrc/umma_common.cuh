@@ -57,6 +57,14 @@ struct UmmaParams {
     // the kernel for few rows of A (umma_gemm_skinny.cu): rows in the TMA box of A, stages of its
     // ring, K slices per tile (= CTAs per cluster)
     int sk_a_rows, sk_stages, sk_split;
+    // CTA-pair kernels: the first tail_tiles tiles of the walk (the ones a last, partly filled wave
+    // of whole tiles would hold) are divided along K over tail_pairs pairs; a pair that does not
+    // reach a tile's last K block leaves its partial sums in its slot of tail_slots and sets its
+    // words of tail_flags; the pair that does reach it adds them up.  0 tiles = off.
+    int tail_tiles, tail_pairs;
+    void *tail_slots;
+    unsigned *tail_flags;
+    long long tail_slot_bytes;  // bytes of one pair's slot
 };
 
 constexpr int kBlockM = 128;
@@ -108,6 +116,236 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return *reinterpret_cast<uint32_t *>(&v);
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// The work list of one CTA pair.  Whole tiles are dealt out pair by pair (pair p takes tiles
+// tail_tiles + p, + pairs, + 2 pairs, ...).  When the tile count does not divide by the number of
+// pairs, a last wave of whole tiles would leave pairs idle; those tail_tiles tiles come FIRST and are
+// cut along K instead: their tail_tiles * num_k_blocks K blocks form one line that is dealt out evenly,
+// pair q taking blocks [U q / tail_pairs, U (q + 1) / tail_pairs).  A pair's piece can start inside a
+// tile and end inside another:
+//   * the piece of its last tile, if it stops short of that tile's last K block, makes the pair a
+//     CONTRIBUTOR: it writes the raw partial accumulator into its slot and raises its flags.  This
+//     item runs first, so that no contributor ever waits for anybody before it delivers;
+//   * every other tile of the range ends at the tile's last K block and is OWNED: if the piece
+//     starts inside the tile, the owner adds the slots of the pairs before it (in a fixed order,
+//     so results do not depend on timing) before it applies the epilogue.
+// This is the blocking of the K strip the reference's cache model applies when a level cannot hold
+// a whole strip (osprey/be/lno/cache_model.cxx:6650-6727), used here to level the last wave.
+// ------------------------------------------------------------------------------------------------
+enum : int { WORK_FULL = 0, WORK_PARTIAL_OUT = 1, WORK_FIXUP_IN = 2 };
+struct WorkItem {
+    int tile, kb0, kb1, mode;
+};
+constexpr int kWaitTailFlag = 0x401;
+
+__device__ __forceinline__ long long tail_range_begin(const UmmaParams &p, int pair) {
+    return (long long)p.tail_tiles * p.num_k_blocks * pair / p.tail_pairs;
+}
+
+// The idx-th item of pair `pair`; false when the list is exhausted.  TAIL = false: the kernel was
+// built without the K split (whole tiles only, none of the split's code or registers).
+template <bool TAIL>
+__device__ __forceinline__ bool work_item(const UmmaParams &p, int pair, int num_pairs, int idx, WorkItem &w) {
+    const int kb = p.num_k_blocks;
+    const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+    int n_tail = 0;
+    if (TAIL && p.tail_tiles > 0 && pair < p.tail_pairs) {
+        const long long a = tail_range_begin(p, pair), b = tail_range_begin(p, pair + 1);
+        if (b > a) {
+            const int tf = (int)(a / kb), tl = (int)((b - 1) / kb);
+            const int end_in_tile = (int)(b - (long long)tl * kb);  // 1 .. kb
+            const int contrib = end_in_tile < kb ? 1 : 0;
+            n_tail = tl - tf + 1;  // contributor piece (if any) + owned tiles
+            if (idx < n_tail) {
+                if (contrib && idx == 0) {
+                    const long long t0 = (long long)tl * kb;
+                    w.tile = tl;
+                    w.kb0 = (int)((a > t0 ? a : t0) - t0);
+                    w.kb1 = end_in_tile;
+                    w.mode = WORK_PARTIAL_OUT;
+                } else {
+                    const int t = tf + idx - contrib;
+                    const long long t0 = (long long)t * kb;
+                    w.tile = t;
+                    w.kb0 = a > t0 ? (int)(a - t0) : 0;
+                    w.kb1 = kb;
+                    w.mode = w.kb0 > 0 ? WORK_FIXUP_IN : WORK_FULL;
+                }
+                return true;
+            }
+        }
+    }
+    const long long t = (TAIL ? (long long)p.tail_tiles : 0LL) + pair + (long long)(idx - n_tail) * num_pairs;
+    if (t >= num_tiles) return false;
+    w.tile = (int)t;
+    w.kb0 = 0;
+    w.kb1 = kb;
+    w.mode = WORK_FULL;
+    return true;
+}
+
+// First of the pairs whose pieces of tile `tile` the owner `pair` has to add: pairs first .. pair - 1.
+__device__ __forceinline__ int tail_first_contributor(const UmmaParams &p, int pair, int tile) {
+    const long long t0 = (long long)tile * p.num_k_blocks;
+    int q = pair - 1;
+    while (q > 0 && tail_range_begin(p, q) > t0) --q;
+    return q;
+}
+
+// A pair's slot holds, per CTA and per 32-row unit of its accumulator rows, BLOCK_N raw 32-bit
+// columns in the order the epilogue warps hold them in registers: [chunk of 32 columns][group of 4
+// columns][lane] as 16-byte words, so that contributor and owner both move 512 contiguous bytes per
+// warp instruction and no transposition is needed.
+template <int BLOCK_N>
+__device__ __forceinline__ uint4 *tail_unit(const UmmaParams &p, int pair, int rank, int units_per_cta, int unit) {
+    constexpr long long kUnitBytes = 32LL * BLOCK_N * 4;
+    return reinterpret_cast<uint4 *>(static_cast<uint8_t *>(p.tail_slots) + (long long)pair * p.tail_slot_bytes +
+                                     ((long long)rank * units_per_cta + unit) * kUnitBytes);
+}
+
+__device__ __forceinline__ unsigned *tail_flag(const UmmaParams &p, int pair, int rank, int warp_slot) {
+    return p.tail_flags + ((pair * 2 + rank) * 8 + warp_slot);
+}
+
+// Contributor: this warp's columns [c_begin, c_end) of the finished partial accumulator go to the slot.
+// Two register sets: the next chunk is on its way out of tensor memory while this one is stored.
+static __device__ __noinline__ void tail_store_partial(uint32_t t_row, uint4 *unit, int c_begin, int c_end) {
+    const int lane = threadIdx.x & 31;
+    auto put = [&](const uint32_t (&v)[32], int c) {
+        uint4 *dst = unit + (c >> 5) * 256 + lane;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) dst[q * 32] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    };
+    uint32_t va[32], vb[32];
+    __syncwarp();
+    tmem_ld_32x32(t_row + c_begin, va);
+#pragma unroll 1
+    for (int c = c_begin; c < c_end; c += 64) {
+        tmem_ld_wait();
+        __syncwarp();
+        if (c + 32 < c_end) tmem_ld_32x32(t_row + c + 32, vb);
+        put(va, c);
+        if (c + 32 < c_end) {
+            tmem_ld_wait();
+            __syncwarp();
+            if (c + 64 < c_end) tmem_ld_32x32(t_row + c + 64, va);
+            put(vb, c + 32);
+        }
+    }
+}
+
+// Flag words start at zero and return to zero by themselves, so that a launch replayed from a CUDA
+// graph (whose parameters are frozen) finds them as the first launch did:
+//   contributor   stores its partial sums, fences, sets the word to 1;
+//   each consumer waits until the word is not zero, reads the slot, then adds 1; the consumer that
+//                 brings it to 1 + `consumers` sets it back to zero.
+// A launch that ended in a time-out can leave words set; o64_last_status clears them when it
+// reports one.
+__device__ __forceinline__ void tail_publish(unsigned *flag) {
+    __threadfence();
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(1u) : "memory");
+}
+
+// Consumer: waits (bounded) until a contributor's word is set.  Whole-warp call.
+__device__ __forceinline__ bool tail_wait_flag(const unsigned *flag, volatile int *abort_flag, int *status_word,
+                                               unsigned long long budget_ns) {
+    bool ok = true;
+    if ((threadIdx.x & 31) == 0) {
+        uint64_t t0 = 0;
+        uint32_t probes = 0;
+        for (;;) {
+            unsigned v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+            if (v != 0) break;
+            if ((++probes & 63u) == 0) {
+                if (*abort_flag) {
+                    ok = false;
+                    break;
+                }
+                const uint64_t now = globaltimer_ns();
+                if (t0 == 0) {
+                    t0 = now;
+                } else if (now - t0 > budget_ns) {
+                    atomicCAS(status_word, 0, kWaitTailFlag);
+                    *abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+            }
+            __nanosleep(64);
+        }
+    }
+    return __shfl_sync(0xffffffffu, ok, 0);
+}
+
+// Consumer, after it has read the slot: the last of `consumers` clears the word.  Whole-warp call.
+__device__ __forceinline__ void tail_release(unsigned *flag, unsigned consumers) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) {
+        if (atomicAdd(flag, 1u) == consumers) atomicExch(flag, 0u);
+    }
+}
+
+// What an owner adds to its accumulator before the epilogue: the same unit of every contributor.
+// The contributors are consecutive pairs, so their units lie one slot apart.
+struct TailFix {
+    const uint8_t *first_unit = nullptr;  // this warp's unit in the first contributor's slot
+    long long stride = 0;                 // bytes from one pair's slot to the next
+    int n = 0;                            // contributors
+};
+
+// Owner: adds the contributors' partial sums for columns [c_begin, c_end) INTO the accumulator in
+// tensor memory (tcgen05.ld, add, tcgen05.st), one contributor after the other in pair order, so the
+// ordinary epilogue then runs on the complete sums.  The slot reads come through L2 from another SM
+// at about a microsecond per round trip: each chunk's reads are issued one chunk ahead, so that the
+// loop runs at the rate of the loads, not of their latency.
+// (Not inlined: a rare path whose two register sets must not cost the ordinary epilogue its registers.)
+template <bool INTEGER>
+__device__ __noinline__ void tail_reduce(uint32_t t_row, int c_begin, int c_end, const TailFix &fix) {
+    const int lane = threadIdx.x & 31;
+    auto fetch = [&](uint4 (&x)[8], const uint4 *unit, int c) {
+        const uint4 *src = unit + (c >> 5) * 256 + lane;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) x[q] = __ldcg(src + q * 32);  // written by another SM: read through L2
+    };
+    auto add = [&](int c, const uint4 (&x)[8]) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_row + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const uint32_t w[4] = {x[q].x, x[q].y, x[q].z, x[q].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if constexpr (INTEGER)
+                    v[4 * q + e] += w[e];
+                else
+                    v[4 * q + e] = __float_as_uint(__uint_as_float(v[4 * q + e]) + __uint_as_float(w[e]));
+            }
+        }
+        tmem_st_32x32(t_row + c, v);
+    };
+    for (int f = 0; f < fix.n; ++f) {
+        const uint4 *unit = reinterpret_cast<const uint4 *>(fix.first_unit + f * fix.stride);
+        uint4 xa[8], xb[8];
+        fetch(xa, unit, c_begin);
+#pragma unroll 1
+        for (int c = c_begin; c < c_end; c += 64) {
+            if (c + 32 < c_end) fetch(xb, unit, c + 32);
+            __syncwarp();
+            add(c, xa);
+            if (c + 32 < c_end) {
+                if (c + 64 < c_end) fetch(xa, unit, c + 64);
+                __syncwarp();
+                add(c + 32, xb);
+            }
+        }
+        tmem_st_wait();  // the next contributor (or the epilogue) reads what was just written
+        __syncwarp();
+    }
+}
 
 constexpr int kEpiStagingBytesPerWarp = 4096;  // 32 rows x 128 bytes
 constexpr int kEpiStagingBytes = 4 * kEpiStagingBytesPerWarp;
@@ -180,6 +418,7 @@ __device__ __forceinline__ void epilogue_tile_act(const UmmaParams &p, long long
     }
     uint4 *patch = reinterpret_cast<uint4 *>(staging);
     const int sw = lane & 7;  // XOR swizzle of the 16-byte chunk index, by row
+
 
     // 32-column chunks of the accumulator this warp has to drain (uniform over the warp)
     const int cols_avail = min(c_end, p.N - n0) - c_begin;
@@ -298,6 +537,16 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams &p, long long row
     }
 }
 
+// An owner of a tile cut along K completes the sums of its columns in tensor memory (for the SwiGLU
+// epilogue: the gate and the up columns), then the ordinary epilogue runs.
+template <int EPI, int BLOCK_N>
+__device__ __forceinline__ void tail_complete(uint32_t t_row, int c_begin, int c_end, const TailFix &fix) {
+    constexpr int kOutN = (EPI == EPI_SWIGLU) ? BLOCK_N / 2 : BLOCK_N;
+    if (fix.n == 0) return;
+    tail_reduce<EPI == EPI_S32>(t_row, c_begin, c_end, fix);
+    if constexpr (EPI == EPI_SWIGLU) tail_reduce<false>(t_row, kOutN + c_begin, kOutN + c_end, fix);
+}
+
 // Split-K epilogue: adds this work item's raw partial sums into `dst` ([M, ldd] of 4-byte
 // elements) with atomics.  Through the same swizzled patch as the normal epilogue so that a warp
 // instruction adds to four full 128-byte row segments.
@@ -377,6 +626,11 @@ struct KernelSetup {
         return O64_OK;
     }
 };
+
+// Decides, for a launch on `pairs` CTA pairs, whether the tiles of the last, partly filled wave are
+// cut along K (see work_item) and over how many pairs; needs the slot and flag memory in `p`.
+// slot_bytes: one pair's slot for this kernel; capacity: bytes behind p.tail_slots.
+void plan_tail(UmmaParams &p, int pairs, long long slot_bytes, long long capacity);
 
 // host helpers shared by the launchers (umma_gemm.cu)
 // 2-D row-major tensor [rows, cols] with `ld` elements between rows; box of box_cols x box_rows;

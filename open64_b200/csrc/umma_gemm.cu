@@ -23,6 +23,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 
 #include "umma_common.cuh"
@@ -330,6 +331,41 @@ int encode_2d(CUtensorMap *tm, int kind, const void *base, int64_t rows, int64_t
     return r == CUDA_SUCCESS ? O64_OK : O64_ERR_CUDA;
 }
 
+static std::atomic<int> g_force_tail{-1};
+void force_tail_split(int mode) { g_force_tail.store(mode < 0 ? -1 : (mode ? 1 : 0)); }
+
+// what the last launch of a CTA-pair kernel on this thread decided (read by o64_test_last_tail_split)
+static thread_local int g_last_tail_tiles = 0, g_last_tail_pairs = 0;
+void last_tail_split(int *tiles, int *pairs) {
+    *tiles = g_last_tail_tiles;
+    *pairs = g_last_tail_pairs;
+}
+
+void plan_tail(UmmaParams &p, int pairs, long long slot_bytes, long long capacity) {
+    p.tail_tiles = 0;
+    p.tail_pairs = 0;
+    g_last_tail_tiles = g_last_tail_pairs = 0;
+    p.tail_slot_bytes = slot_bytes;
+    if (!p.tail_slots || !p.tail_flags || pairs < 2 || slot_bytes <= 0) return;
+    // O64_TAIL_SPLIT=0 turns the split off, =1 takes it whenever a last wave is partly filled;
+    // o64_test_force_tail_split overrides the environment
+    static const int env_mode = [] {
+        const char *e = getenv("O64_TAIL_SPLIT");
+        return e ? atoi(e) : -1;
+    }();
+    const int forced = g_force_tail.load(std::memory_order_relaxed);
+    const int mode = forced >= 0 ? forced : env_mode;
+    const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles;
+    const int rows_per_cta = slot_bytes >= (long long)kTailSlotBytesMax ? 256 : 128;
+    tail_model(tiles, pairs, p.num_k_blocks, rows_per_cta, capacity / slot_bytes, mode, &p.tail_tiles, &p.tail_pairs);
+    g_last_tail_tiles = p.tail_tiles;
+    g_last_tail_pairs = p.tail_pairs;
+    const char *tr = getenv("O64_TRACE");
+    if (p.tail_tiles && tr && strstr(tr, "plan"))
+        fprintf(stderr, "[o64 last wave: %d of %lld tiles cut along K over %d of %d CTA pairs]\n", p.tail_tiles, tiles,
+                p.tail_pairs, pairs);
+}
+
 template <int KIND, bool B_KN, int EPI, int BLOCK_N, int STAGES, bool HOOK = false>
 static int launch_inst(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tb2,
                        const UmmaParams &p, int grid, cudaStream_t stream) {
@@ -402,6 +438,11 @@ int umma_launch(const UmmaCall &c) {
         p.split_k = (p.num_k_blocks + per - 1) / per;  // every slice non-empty
         p.partial = c.partial;
     }
+    p.tail_tiles = 0;
+    p.tail_pairs = 0;
+    p.tail_slots = c.tail_slots;
+    p.tail_flags = c.tail_flags;
+    p.tail_slot_bytes = (long long)c.tail_bytes;  // capacity until a launcher has planned the split
     p.n_peers = c.n_peers;
     for (int i = 0; i < 7; ++i) p.peer_c[i] = c.peer_c[i];
     if (c.n_peers > 0 && !p.vec_ok) return O64_ERR_ALIGN;  // the fused exchange uses the vector-store path only
@@ -459,9 +500,10 @@ int umma_launch(const UmmaCall &c) {
         if (n && n_mma)
             fprintf(stderr,
                     "[o64 pipe: mma thread %.0f clk, waits for data %.1f%%, for a drained accumulator %.1f%%; "
-                    "producer waits %.1f%% of %.0f clk; epilogue busy %.0f clk per CTA; %d CTAs]\n",
+                    "producer waits %.1f%% of %.0f clk; epilogue busy %.0f clk per CTA; %d CTAs; pair kernels: waiting for "
+                    "contributors %.0f, partial sums out %.0f, epilogue warp loop %.0f clk]\n",
                     s[1] / n_mma, 100.0 * s[0] / s[1], 100.0 * s[5] / s[1],
-                    100.0 * s[2] / (s[3] > 0 ? s[3] : 1), s[3] / n, s[4] / n, n);
+                    100.0 * s[2] / (s[3] > 0 ? s[3] : 1), s[3] / n, s[4] / n, n, s[5] / n, s[6] / n, s[7] / n);
         return rc_launch;
     };
 #else

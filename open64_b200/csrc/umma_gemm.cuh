@@ -7,6 +7,9 @@
 
 namespace o64 {
 
+constexpr int kTailMaxPairs = 80;                 // flag words cover this many CTA pairs
+constexpr int kTailFlagWords = kTailMaxPairs * 16;  // [pair][CTA of the pair][8 epilogue warps]
+constexpr size_t kTailSlotBytesMax = 512 * 1024;   // a pair's slot in the 512-row kernel
 constexpr unsigned long long kDefaultWaitNs = 2000000000ull;  // two seconds
 
 enum : int { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_SCALED_BF16 = 2, EPI_S32 = 3 };
@@ -39,11 +42,26 @@ struct UmmaCall {
     void *peer_c[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     bool may_allocate = true;  // false: never allocate (the pipeline trace, which needs a buffer, stays off)
     unsigned long long wait_ns = 0;  // budget of the kernels' bounded waits; 0 = kDefaultWaitNs
+    // CTA-pair kernels, K split of the last wave's tiles: slot memory (tail_bytes) and flag words
+    // (kTailFlagWords, zero between launches: the kernels leave them so); NULL = no split
+    void *tail_slots = nullptr;
+    unsigned *tail_flags = nullptr;
+    size_t tail_bytes = 0;
     int test_withhold = -1;          // o64_test_* only: K block whose loads the producer leaves out
 };
 
 // Validates alignment, encodes the tensor maps and launches.  Returns O64_OK or an error code.
 int umma_launch(const UmmaCall &call);
+
+// Model and decision of the K split of a last, partly filled wave (plan.cpp); force: -1 = decide,
+// 0 = never, 1 = whenever a last wave is partly filled.
+long long tail_model(long long tiles, int pairs, long long kb, int rows_per_cta, long long max_pairs_by_memory,
+                     int force, int *tail_tiles, int *tail_pairs);
+
+// Tiles and CTA pairs of the K split the last CTA-pair launch of this thread chose (0, 0: none).
+void last_tail_split(int *tiles, int *pairs);
+// Test hook: -1 = the model decides (default), 0 = never split, 1 = split whenever a last wave is partly filled.
+void force_tail_split(int mode);
 
 // K slices per tile (CTAs per cluster) the kernel for few rows of A uses for a shape.
 int umma_skinny_split(int64_t M, int64_t N, int64_t K, int elem, int num_ctas, int bn = 256);

@@ -47,7 +47,7 @@ struct PairSmemLayout {
     static constexpr int kDynamic = kTotal + 1024;
 };
 
-template <int KIND, bool B_KN, int EPI, int BLOCK_N, int STAGES, bool HOOK = false>
+template <int KIND, bool B_KN, int EPI, int BLOCK_N, int STAGES, bool HOOK = false, bool TAIL = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                       const __grid_constant__ CUtensorMap tm_b2, const UmmaParams p) {
@@ -123,12 +123,13 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             long long wait_clk = 0;
             [[maybe_unused]] int issued = 0;  // K blocks this producer has dealt with (test hook)
             const long long t_begin = clock64();
-            for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+            WorkItem w;
+            for (int item = 0; ok && work_item<TAIL>(p, pair_id, num_pairs, item, w); ++item) {
                 int mb, nb;
-                tile_coords(t, p, mb, nb);
+                tile_coords(w.tile, p, mb, nb);
                 const int m0 = mb * kPairM + (int)rank * kBlockM;
                 const int n0 = nb * kOutN;
-                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     const long long c0 = O64_DBG(p) ? clock64() : 0;
                     ok = mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
                                            kWaitPairProducerEmpty, p.wait_ns);
@@ -190,7 +191,8 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             long long wait_clk = 0;
             const long long t_begin = clock64();
             uint32_t ready = mbar_test_wait(full_bar(0), 0);  // see the 1-CTA kernel: probe ahead
-            for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++it) {
+            WorkItem w;
+            for (; ok && work_item<TAIL>(p, pair_id, num_pairs, it, w); ++it) {
                 const int buf = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1u;
                 ok = mbar_wait_bounded(acc_empty_bar(buf), acc_phase ^ 1u, abort_flag, p.status,
@@ -199,7 +201,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BLOCK_N;
-                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     if (!__all_sync(0xffffffffu, ready)) {
                         const long long c0 = O64_DBG(p) ? clock64() : 0;
                         ok = mbar_wait_bounded(full_bar(stage), phase, abort_flag, p.status, kWaitPairMmaFull, p.wait_ns);
@@ -225,7 +227,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
 #pragma unroll
                         for (int k = 0; k < kMmaPerStage; ++k) {
                             tc_mma_pair<KIND>(d_tmem, a_desc + 2u * k, b_desc + kBAdvance * k, idesc,
-                                              (kb | k) != 0 ? 1u : 0u);
+                                              ((kb - w.kb0) | k) != 0 ? 1u : 0u);
                         }
                         // frees the stage in both CTAs when these MMAs retire: one commit delivered
                         // to the same barrier of both ranks
@@ -250,24 +252,58 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         const int quarter = warp & 3;
         int it = 0;
         bool ok = true;
-        for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++it) {
+        WorkItem w;
+        long long clk_store = 0, clk_flags = 0, clk_fix = 0, clk_accwait = 0;  // O64_TRACE=pipe
+        const long long t_begin = clock64();
+        for (; ok && work_item<TAIL>(p, pair_id, num_pairs, it, w); ++it) {
             int mb, nb;
-            tile_coords(t, p, mb, nb);
+            tile_coords(w.tile, p, mb, nb);
             const int buf = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1u;
+            const long long w0 = O64_DBG(p) ? clock64() : 0;
             if (lane == 0)
                 ok = mbar_wait_bounded(acc_full_bar(buf), acc_phase, abort_flag, p.status, kWaitPairEpiAccFull, p.wait_ns);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             tc_fence_after();
+            if (O64_DBG(p)) clk_accwait += clock64() - w0;
             const long long row0 = (long long)mb * kPairM + (long long)rank * kBlockM + quarter * 32;
             const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + buf * BLOCK_N;
-            if (!(O64_PROBE(p) & 4))
+            const long long e0 = O64_DBG(p) ? clock64() : 0;
+            if (TAIL && w.mode == WORK_PARTIAL_OUT) {
+                // this pair stops short of the tile's last K block: the raw sums go to its slot
+                tail_store_partial(t_row, tail_unit<BLOCK_N>(p, pair_id, (int)rank, 4, quarter), 0, BLOCK_N);
+                tail_publish(tail_flag(p, pair_id, (int)rank, quarter));
+                if (O64_DBG(p)) clk_store += clock64() - e0;
+            } else if (!(O64_PROBE(p) & 4)) {
+                if (TAIL && w.mode == WORK_FIXUP_IN) {
+                    TailFix fix;
+                    // the tile's earlier K blocks were multiplied by the pairs before this one
+                    const int first = tail_first_contributor(p, pair_id, w.tile);
+                    for (int q = first; q < pair_id && ok; ++q)
+                        ok = tail_wait_flag(tail_flag(p, q, (int)rank, quarter), abort_flag, p.status, p.wait_ns);
+                    if (!ok) break;
+                    fix.first_unit = reinterpret_cast<const uint8_t *>(tail_unit<BLOCK_N>(p, first, (int)rank, 4, quarter));
+                    fix.stride = p.tail_slot_bytes;
+                    fix.n = pair_id - first;
+                    if (O64_DBG(p)) clk_flags += clock64() - e0;
+                    tail_complete<EPI, BLOCK_N>(t_row, 0, kOutN, fix);
+                    for (int q = first; q < pair_id; ++q) tail_release(tail_flag(p, q, (int)rank, quarter), 1);
+                }
+                const long long f0 = O64_DBG(p) ? clock64() : 0;
                 epilogue_tile<EPI, BLOCK_N>(p, row0, nb * kOutN, t_row,
                                             smem_gen + L::kStagingOffset + quarter * kEpiStagingBytesPerWarp);
+                if (O64_DBG(p)) clk_fix += clock64() - f0;
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty_bar(buf), 0));
+        }
+        if (O64_DBG(p) && warp == 2 && lane == 0) {
+            O64_DBG(p)[blockIdx.x * 8 + 4] = clk_fix;                 // epilogues (owned tiles)
+            O64_DBG(p)[blockIdx.x * 8 + 5] = clk_flags;               // waiting for contributors
+            O64_DBG(p)[blockIdx.x * 8 + 6] = clk_store;               // partial sums stored and published
+            O64_DBG(p)[blockIdx.x * 8 + 7] = clock64() - t_begin;     // epilogue warp's whole loop
         }
     }
 
@@ -321,6 +357,32 @@ static int launch_pair_inst(const CUtensorMap &ta, const CUtensorMap &tb, const 
         &max_pairs);
     if (rc) return rc;
     if (max_pairs > 0 && grid > 2 * max_pairs) grid = 2 * max_pairs;
+    if constexpr (!HOOK) {
+        UmmaParams q = p;
+        long long cap = q.tail_slot_bytes;  // the capacity, as umma_launch left it
+        // all pairs of the grid must be resident at once for one to wait for another's piece
+        if (grid / 2 > kTailMaxPairs || max_pairs <= 0) cap = 0;
+        plan_tail(q, grid / 2, 2LL * 4 * 32 * BLOCK_N * 4, cap);
+        if (q.tail_tiles > 0) {
+            // the instantiation that carries the K split of the last wave (its own set-up per device)
+            auto kern_tail = umma_gemm_pair_kernel<KIND, B_KN, EPI, BLOCK_N, STAGES, false, true>;
+            static KernelSetup ks_tail;
+            const int rc_tail = ks_tail.once(
+                [&](int *) {
+                    return cudaFuncSetAttribute(kern_tail, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) ==
+                                   cudaSuccess
+                               ? (int)O64_OK
+                               : (int)O64_ERR_CUDA;
+                },
+                nullptr);
+            if (rc_tail) return rc_tail;
+            kern_tail<<<grid, kThreads, L::kDynamic, stream>>>(ta, tb, tb2, q);
+            return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
+        }
+        // whole tiles only: no more pairs than tiles
+        const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles;
+        if (grid / 2 > tiles) grid = (int)(2 * tiles);
+    }
     kern<<<grid, kThreads, L::kDynamic, stream>>>(ta, tb, tb2, p);
     return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
 }
@@ -330,7 +392,8 @@ int umma_launch_pair(const UmmaCall &c, const CUtensorMap &ta, const CUtensorMap
                      const CUtensorMap &tb2, const UmmaParams &p) {
     const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles;
     long long pairs = c.plan.num_ctas / 2;
-    if (pairs > tiles) pairs = tiles;
+    // with memory for a K split even fewer tiles than pairs can keep every pair busy
+    if (pairs > tiles && !(p.tail_slots && p.tail_flags)) pairs = tiles;
     if (pairs < 1) pairs = 1;
     const int grid = (int)(2 * pairs);
     const int block_n = c.plan.tile_n;

@@ -137,12 +137,13 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             long long wait_clk = 0;
             [[maybe_unused]] int issued = 0;  // K blocks this producer has dealt with (test hook)
             const long long t_begin = clock64();
-            for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+            WorkItem w;
+            for (int item = 0; ok && work_item<false>(p, pair_id, num_pairs, item, w); ++item) {
                 int mb, nb;
-                tile_coords(t, p, mb, nb);
+                tile_coords(w.tile, p, mb, nb);
                 const int m0 = mb * kPairM + (int)rank * kWideRowsPerCta;
                 const int n0 = nb * kOutN;
-                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     const long long c0 = O64_DBG(p) ? clock64() : 0;
                     ok = mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.status,
                                            kWaitWideProducerEmpty, p.wait_ns);
@@ -202,8 +203,9 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             long long wait_clk = 0, acc_wait_clk = 0;
             const long long t_begin = clock64();
             uint32_t ready = mbar_test_wait(full_bar(0), 0);
-            for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++it) {
-                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+            WorkItem w;
+            for (; ok && work_item<false>(p, pair_id, num_pairs, it, w); ++it) {
+                for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     if (!__all_sync(0xffffffffu, ready)) {
                         const long long c0 = O64_DBG(p) ? clock64() : 0;
                         ok = mbar_wait_bounded(full_bar(stage), phase, abort_flag, p.status, kWaitWideMmaFull, p.wait_ns);
@@ -227,7 +229,7 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                             mbar_arrive_cluster(map_to_cta(empty_bar(stage), 1));
                         }
                     } else {
-                        if (kb == 0) {
+                        if (kb == w.kb0) {
                             // the first MMA of a tile overwrites the accumulator: wait until the
                             // epilogue has drained it (accumulator 1 is drained second)
                             const long long a0 = O64_DBG(p) ? clock64() : 0;
@@ -243,9 +245,9 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
 #pragma unroll
                                 for (int k = 0; k < kMmaPerStage; ++k)
                                     tc_mma_pair<KIND>(tmem_base, a_desc0 + 2u * k, b_desc + kBAdvance * k, idesc,
-                                                      (kb | k) != 0 ? 1u : 0u);
+                                                      ((kb - w.kb0) | k) != 0 ? 1u : 0u);
                             }
-                            if (kb == 0) {
+                            if (kb == w.kb0) {
                                 __syncwarp();
                                 const long long a1 = O64_DBG(p) ? clock64() : 0;
                                 ok = mbar_wait_bounded(acc_empty_bar(1), (it & 1u) ^ 1u, abort_flag, p.status,
@@ -259,7 +261,7 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
 #pragma unroll
                                 for (int k = 0; k < kMmaPerStage; ++k)
                                     tc_mma_pair<KIND>(tmem_base + BLOCK_N, a_desc1 + 2u * k, b_desc + kBAdvance * k,
-                                                      idesc, (kb | k) != 0 ? 1u : 0u);
+                                                      idesc, ((kb - w.kb0) | k) != 0 ? 1u : 0u);
                             }
                         }
                         if (leader) tc_commit_pair_mask(empty_bar(stage), 3);
@@ -291,9 +293,10 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         int it = 0;
         bool ok = true;
         long long epi_clk = 0;
-        for (int t = pair_id; t < num_tiles && ok; t += num_pairs, ++it) {
+        WorkItem w;
+        for (; ok && work_item<false>(p, pair_id, num_pairs, it, w); ++it) {
             int mb, nb;
-            tile_coords(t, p, mb, nb);
+            tile_coords(w.tile, p, mb, nb);
 #pragma unroll 1
             for (int g = 0; g < 2 && ok; ++g) {
                 if (lane == 0)
@@ -305,10 +308,11 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                                        g * kBlockM + quarter * 32;
                 const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + g * BLOCK_N;
                 const long long e0 = O64_DBG(p) ? clock64() : 0;
-                if (!(O64_PROBE(p) & 4))
+                if (!(O64_PROBE(p) & 4)) {
                     epilogue_tile<EPI, BLOCK_N>(p, row0, nb * kOutN, t_row,
                                                 smem_gen + L::kStagingOffset + (warp - 2) * kEpiStagingBytesPerWarp,
                                                 half * kColsPerWarp, (half + 1) * kColsPerWarp);
+                }
                 tc_fence_before();
                 __syncwarp();
                 if (O64_DBG(p)) epi_clk += clock64() - e0;

@@ -105,6 +105,16 @@ class Engine:
         st = self.lib.o64_last_status(self._h, s, ctypes.byref(detail))
         return st, detail.value
 
+    def last_tail_split(self):
+        """(tiles, pairs) of the K split the last CTA-pair launch chose for its last wave; (0, 0) = none."""
+        t, p = ctypes.c_int(0), ctypes.c_int(0)
+        check(self.lib.o64_test_last_tail_split(ctypes.byref(t), ctypes.byref(p)), "o64_test_last_tail_split")
+        return t.value, p.value
+
+    def force_tail_split(self, mode):
+        """Test hook, process-wide: 1 = always cut a partly filled last wave along K, 0 = never, -1 = model."""
+        check(self.lib.o64_test_force_tail_split(int(mode)), "o64_test_force_tail_split")
+
     def set_wait_budget_us(self, microseconds):
         """Budget of the kernels' bounded waits for later calls (0 = the default, two seconds)."""
         check(self.lib.o64_set_wait_budget_us(self._h, int(microseconds)), "o64_set_wait_budget_us")

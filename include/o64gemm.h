@@ -185,6 +185,25 @@ int o64_gemm_fp8_scaled(o64_handle_t h, int64_t M, int64_t N, int64_t K, const v
                         const float *scaleB, const float *bias, void *C, int64_t ldc,
                         void *stream);
 
+/* The scaled products with a fused activation and a choice of result type ("requantisation"):
+ *   C = convert( act( acc * (scaleA[m] * scaleB[n]) + bias[n] ) )
+ * acc: the fp32 (e4m3 operands) or int32 (int8 operands, converted to fp32) accumulator; every fp32
+ * operation is rounded by itself (nothing is fused), so the value is reproducible bit for bit on a
+ * CPU; scaleA, scaleB, bias may be NULL (1, 1, 0).  out_kind: O64_OUT_BF16 (ldc in 2-byte elements),
+ * or the operands' own 8-bit type - O64_OUT_E4M3 for the fp8 product, O64_OUT_S8 for the int8 product,
+ * ldc in bytes - rounded to nearest even and saturated (e4m3: +-448, int8: -128 ... 127), which is
+ * what feeds the next 8-bit layer without a pass over a wide intermediate.  The narrow integer result
+ * has a relative in the reference's MATMUL of INTEGER*1 arrays, which returns INTEGER*1
+ * (osprey/crayf90/fe90/intrin.h:4294, osprey/libfi/matrix/i1gemmx.f) - there by wrap-around, here by
+ * scaling and saturation; the elementwise vocabulary is the one of O64_ACT_*. */
+enum { O64_OUT_BF16 = 0, O64_OUT_S8 = 1, O64_OUT_E4M3 = 2 };
+int o64_gemm_fp8_scaled_ex(o64_handle_t h, int64_t M, int64_t N, int64_t K, const void *A8, int64_t lda,
+                           const void *B8, int64_t ldb, const float *scaleA, const float *scaleB,
+                           const float *bias, int act, void *C, int64_t ldc, int out_kind, void *stream);
+int o64_gemm_s8_scaled(o64_handle_t h, int64_t M, int64_t N, int64_t K, const int8_t *A, int64_t lda,
+                       const int8_t *B, int64_t ldb, const float *scaleA, const float *scaleB,
+                       const float *bias, int act, void *C, int64_t ldc, int out_kind, void *stream);
+
 /* C = A*B^T: int8 operands, A [M,K], B [N,K], int32 accumulate and result, exact.  The
  * reference's integer kernels are instances of the same template
  * (osprey/libfi/matrix/i1i4gemmx.f; front-end table osprey/crayf90/fe90/intrin.h:4276-4303). */

@@ -15,6 +15,7 @@ ERR_RANK, ERR_CONFORM, ERR_NOMEM, ERR_ALIGN, ERR_DTYPE, ERR_TIMEOUT, ERR_CUDA, E
 ACT_NONE, ACT_RELU, ACT_GELU_TANH, ACT_GELU_ERF, ACT_SILU = range(5)
 KIND_F32, KIND_BF16, KIND_FP8, KIND_S8 = range(4)
 GATHER_NONE, GATHER_ROWMAJOR, GATHER_SLABS, GATHER_PUSH = range(4)
+OUT_BF16, OUT_S8, OUT_E4M3 = range(3)
 UNIQUE_ID_BYTES = 128
 STATIC_SCRATCH_BYTES = 16 << 20
 
@@ -22,7 +23,7 @@ STATIC_SCRATCH_BYTES = 16 << 20
 EXPORTS = [
     "o64_create", "o64_destroy", "o64_last_status", "o64_set_wait_budget_us", "o64_test_gemm_bf16_withheld", "o64_test_last_tail_split", "o64_test_force_tail_split", "o64_status_string", "o64_version",
     "o64_plan_get", "o64_plan_set", "o64_plan_model", "o64_plan_tune", "o64_plan_tune_clear", "o64_linear_f32", "o64_gemm_bf16", "o64_gemm_bf16_swiglu",
-    "o64_gemm_fp8_scaled", "o64_gemm_s8s8_s32", "o64_gemm_s8s8_s32_static", "o64_naive_gemm", "o64_comm_unique_id",
+    "o64_gemm_fp8_scaled", "o64_gemm_fp8_scaled_ex", "o64_gemm_s8_scaled", "o64_gemm_s8s8_s32", "o64_gemm_s8s8_s32_static", "o64_naive_gemm", "o64_comm_unique_id",
     "o64_comm_init", "o64_comm_destroy", "o64_comm_alloc_result", "o64_gemm_s8_sharded_workspace", "o64_gemm_s8_sharded", "o64_gemm_bf16_sharded",
     "sgemm_", "_s4gemmx__", "_s4gemvx__", "_MATMUL_S4S4", "o64_compat_last_status",
     "dgemm_", "_sgemmx__", "_sgemvx__", "_MATMUL_SS",
@@ -139,6 +140,8 @@ def lib():
     L.o64_gemm_bf16_swiglu.argtypes = [vp, i64, i64, i64, vp, i64, vp, vp, i64, vp, i64, vp]
     L.o64_gemm_fp8_scaled.argtypes = [vp, i64, i64, i64, vp, i64, vp, i64, vp, vp, vp, vp, i64, vp]
     L.o64_gemm_s8s8_s32.argtypes = [vp, i64, i64, i64, vp, i64, vp, i64, vp, i64, vp]
+    L.o64_gemm_fp8_scaled_ex.argtypes = [vp, i64, i64, i64, vp, i64, vp, i64, vp, vp, vp, ci, vp, i64, ci, vp]
+    L.o64_gemm_s8_scaled.argtypes = [vp, i64, i64, i64, vp, i64, vp, i64, vp, vp, vp, ci, vp, i64, ci, vp]
     L.o64_gemm_s8s8_s32_static.argtypes = [i64, i64, i64, vp, i64, vp, i64, vp, i64, vp]
     L.o64_naive_gemm.argtypes = [vp, ci, i64, i64, i64, vp, i64, vp, i64, ci, vp, vp, vp, ci, vp,
                                  i64, vp]

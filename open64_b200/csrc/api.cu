@@ -530,7 +530,7 @@ static int umma_entry(o64_handle_t h, int kind, bool b_kn, int epi, int64_t M, i
     if (M == 0 || N == 0) return O64_OK;
     if (!C || (K > 0 && (!A || !B))) return O64_ERR_RANK;
     const int elem = (kind == O64_KIND_BF16) ? 2 : 1;
-    const int out_elem = (epi == EPI_S32) ? 4 : 2;
+    const int out_elem = epi_out_bytes(epi);
     const int64_t b_rows = b_kn ? K : N, b_cols = b_kn ? N : K;
     if (lda < K || ldb < b_cols || ldc < N) return O64_ERR_CONFORM;
     DeviceGuard g(h->device);  // (operands of another GPU are refused where each is staged, below)
@@ -543,12 +543,15 @@ static int umma_entry(o64_handle_t h, int kind, bool b_kn, int epi, int64_t M, i
         int rc0;
         if ((rc0 = stage_in(h, 3, bias, (size_t)N * 4, s, &dbias0))) return rc0;
         if ((rc0 = stage_out_begin(h, 5, C, span_bytes(M, N, ldc, out_elem), ldc != N, s, &o0))) return rc0;
-        if (epi == EPI_S32 || epi == EPI_SWIGLU || (!dbias0 && epi == EPI_BF16) || (!dbias0 && epi == EPI_SCALED_BF16)) {
-            // act(0) = 0 for every activation of the vocabulary; silu(0) * 0 = 0
+        if (epi == EPI_S32 || epi == EPI_SWIGLU || !dbias0) {
+            // act(0) = 0 for every activation of the vocabulary; silu(0) * 0 = 0; zero is all bits clear
+            // in every result type
             CUDA_TRY(cudaMemset2DAsync(o0.dev, (size_t)ldc * out_elem, 0, (size_t)N * out_elem, (size_t)M, s));
-        } else if ((rc0 = finalize_partial_bf16(nullptr, M, N, nullptr, nullptr, (const float *)dbias0,
-                                                epi == EPI_BF16 ? act : O64_ACT_NONE, o0.dev, ldc, s))) {
-            return rc0;
+        } else {
+            const int out_kind = epi == EPI_ISCALED_S8 ? 1 : (epi == EPI_SCALED_E4M3 ? 2 : 0);
+            if ((rc0 = finalize_partial_bf16(nullptr, M, N, nullptr, nullptr, (const float *)dbias0, act, o0.dev, ldc, s,
+                                             out_kind)))
+                return rc0;
         }
         return stage_out_end(o0, s);
     }
@@ -662,7 +665,8 @@ static int umma_entry(o64_handle_t h, int kind, bool b_kn, int epi, int64_t M, i
     choose(h, kind, epi, M, N, K, &c.plan);
     // split-K (few tiles, long K): partial sums meet in scratch memory; a second small kernel
     // applies the epilogue for 16-bit results, int32 results are summed in place
-    const bool split = c.plan.split_k > 1 && c.plan.cta_group == 1 && epi != EPI_SWIGLU;
+    const bool split = c.plan.split_k > 1 && c.plan.cta_group == 1 &&
+                       (epi == EPI_BF16 || epi == EPI_SCALED_BF16 || epi == EPI_S32);
     if (split) {
         if (epi == EPI_S32) {
             CUDA_TRY(cudaMemset2DAsync(out.dev, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, s));
@@ -706,6 +710,23 @@ extern "C" int o64_gemm_fp8_scaled(o64_handle_t h, int64_t M, int64_t N, int64_t
                                    void *stream) {
     return umma_entry(h, O64_KIND_FP8, false, EPI_SCALED_BF16, M, N, K, A8, lda, B8, nullptr, ldb, C, ldc,
                       bias, scaleA, scaleB, O64_ACT_NONE, stream);
+}
+
+// The scaled products with a choice of result type and an activation after the dequantisation.
+extern "C" int o64_gemm_fp8_scaled_ex(o64_handle_t h, int64_t M, int64_t N, int64_t K, const void *A8, int64_t lda,
+                                      const void *B8, int64_t ldb, const float *scaleA, const float *scaleB,
+                                      const float *bias, int act, void *C, int64_t ldc, int out_kind, void *stream) {
+    if (out_kind != O64_OUT_BF16 && out_kind != O64_OUT_E4M3) return O64_ERR_DTYPE;
+    return umma_entry(h, O64_KIND_FP8, false, out_kind == O64_OUT_E4M3 ? EPI_SCALED_E4M3 : EPI_SCALED_BF16, M, N, K, A8,
+                      lda, B8, nullptr, ldb, C, ldc, bias, scaleA, scaleB, act, stream);
+}
+
+extern "C" int o64_gemm_s8_scaled(o64_handle_t h, int64_t M, int64_t N, int64_t K, const int8_t *A, int64_t lda,
+                                  const int8_t *B, int64_t ldb, const float *scaleA, const float *scaleB,
+                                  const float *bias, int act, void *C, int64_t ldc, int out_kind, void *stream) {
+    if (out_kind != O64_OUT_BF16 && out_kind != O64_OUT_S8) return O64_ERR_DTYPE;
+    return umma_entry(h, O64_KIND_S8, false, out_kind == O64_OUT_S8 ? EPI_ISCALED_S8 : EPI_ISCALED_BF16, M, N, K, A, lda,
+                      B, nullptr, ldb, C, ldc, bias, scaleA, scaleB, act, stream);
 }
 
 extern "C" int o64_gemm_s8s8_s32(o64_handle_t h, int64_t M, int64_t N, int64_t K, const int8_t *A,

@@ -177,9 +177,10 @@ void plan_choose(int kind, int epi, int64_t M, int64_t N, int64_t K, int num_sms
         for (int n = 256; n >= 128; n /= 2) {
             if (pin.tile_n && pin.tile_n != n) continue;
             if (tm == 512 && n != 256) continue;                      // not instantiated
+            if (tm == 512 && epi > EPI_S32) continue;                 // the requantising tails: 128- and 256-row kernels only
             if (g == 2 && n == 128 && epi == EPI_SWIGLU) continue;  // not instantiated
             double t = predict_ms(kind, epi, M, N, K, n, out->num_ctas, g, tm);
-            if (g == 1 && epi != EPI_SWIGLU && pin.split_k == 0) {
+            if (g == 1 && epi != EPI_SWIGLU && epi <= EPI_S32 && pin.split_k == 0) {
                 // the one-CTA kernel may split K: the main loop shrinks, atomics and a finishing pass come on top
                 const int sk = auto_split_k(M, N, K, n, out->tile_k, out->num_ctas);
                 if (sk > 1) t = t / sk + 0.006;
@@ -213,7 +214,7 @@ void plan_choose(int kind, int epi, int64_t M, int64_t N, int64_t K, int num_sms
     } else {
         out->group_m = 2048 / out->tile_m;
     }
-    if (out->cta_group == 1 && epi != EPI_SWIGLU) {
+    if (out->cta_group == 1 && epi != EPI_SWIGLU && epi <= EPI_S32) {
         const long long kblocks = (K + out->tile_k - 1) / out->tile_k;
         int sk = pin.split_k > 0 ? pin.split_k : auto_split_k(M, N, K, tile_n, out->tile_k, out->num_ctas);
         if (sk > kblocks) sk = (int)kblocks;
@@ -228,7 +229,7 @@ void plan_choose(int kind, int epi, int64_t M, int64_t N, int64_t K, int num_sms
     // their partial sums through distributed shared memory.  Reported as split_k = -S.  A pinned
     // split_k of -1 asks for the kernel (S chosen), -2 / -4 / -8 fix S, >= 1 rules the kernel out.
     const bool skinny_pinned = pin.split_k < 0;
-    const bool skinny_fits = M <= (skinny_pinned ? 512 : 128) && epi != EPI_SWIGLU && pin.cta_group != 2 &&
+    const bool skinny_fits = M <= (skinny_pinned ? 512 : 128) && epi != EPI_SWIGLU && epi <= EPI_S32 && pin.cta_group != 2 &&
                              (pin.tile_m == 0 || pin.tile_m <= 128) && (pin.tile_n == 0 || pin.tile_n == 256 || pin.tile_n == 128);
     if (skinny_fits && (skinny_pinned || (pin.split_k == 0 && !pin.cta_group && !pin.tile_m && !pin.tile_n &&
                                           (double)N * (double)K * eb >= 2.0 * 1024 * 1024))) {

@@ -520,27 +520,36 @@ int naive_gemm(int kind, int64_t M, int64_t N, int64_t K, const void *A, int64_t
 
 __global__ void finalize_partial_kernel(const float *__restrict__ partial, long long M, long long N,
                                         const float *scale_a, const float *scale_b, const float *bias,
-                                        int act, __nv_bfloat16 *C, long long ldc) {
+                                        int act, __nv_bfloat16 *C, long long ldc, int out_kind) {
     const long long total = M * N;
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
          e += (long long)gridDim.x * blockDim.x) {
         const long long i = e / N, j = e % N;
         float x = partial ? partial[e] : 0.0f;  // no partial sums: the empty sum (K == 0)
-        if (scale_a) x *= scale_a[i];
-        if (scale_b) x *= scale_b[j];
-        if (bias) x += bias[j];
-        C[i * ldc + j] = __float2bfloat16_rn(act_f32(x, act));
+        if (scale_a || scale_b)  // as the tile kernels' scaled tail: acc * (sa * sb) + bias, nothing fused
+            x = __fmul_rn(x, __fmul_rn(scale_a ? scale_a[i] : 1.0f, scale_b ? scale_b[j] : 1.0f));
+        if (bias) x = __fadd_rn(x, bias[j]);
+        x = act_f32(x, act);
+        if (out_kind == 1) {  // int8, round to nearest even, saturating
+            int q = __float2int_rn(x);
+            q = max(-128, min(127, q));
+            reinterpret_cast<int8_t *>(C)[i * ldc + j] = (int8_t)q;
+        } else if (out_kind == 2) {  // e4m3, round to nearest even, saturating
+            reinterpret_cast<uint8_t *>(C)[i * ldc + j] = (uint8_t)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
+        } else {
+            C[i * ldc + j] = __float2bfloat16_rn(x);
+        }
     }
 }
 
 int finalize_partial_bf16(const float *partial, int64_t M, int64_t N, const float *scale_a,
                           const float *scale_b, const float *bias, int act, void *C, int64_t ldc,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, int out_kind) {
     if (M <= 0 || N <= 0) return O64_OK;
     long long blocks = ((long long)M * N + 255) / 256;
     if (blocks > 148LL * 8) blocks = 148LL * 8;
     finalize_partial_kernel<<<(unsigned)blocks, 256, 0, stream>>>(partial, M, N, scale_a, scale_b, bias, act,
-                                                                  reinterpret_cast<__nv_bfloat16 *>(C), ldc);
+                                                                  reinterpret_cast<__nv_bfloat16 *>(C), ldc, out_kind);
     return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
 }
 

@@ -49,9 +49,11 @@ int naive_gemm(int kind, int64_t M, int64_t N, int64_t K, const void *A, int64_t
 
 // Second pass of a split-K GEMM with a 16-bit result: C = bf16(act(partial * sa[m] * sb[n] + bias[n])),
 // `partial` a dense fp32 [M,N], or NULL for the empty sum (every partial zero).  scale vectors and bias may be NULL.
+// out_kind: 0 = bf16 (ldc in 2-byte elements), 1 = int8, 2 = e4m3 (both round to nearest even, saturating;
+// ldc in bytes).
 int finalize_partial_bf16(const float *partial, int64_t M, int64_t N, const float *scale_a,
                           const float *scale_b, const float *bias, int act, void *C, int64_t ldc,
-                          cudaStream_t stream);
+                          cudaStream_t stream, int out_kind = 0);
 
 // COMPLEX*8 / COMPLEX*16 element: (re, im) as Fortran stores it.
 template <typename R>

@@ -3,6 +3,7 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 
 #include <mutex>
 
@@ -367,29 +368,78 @@ __device__ __forceinline__ float act_fixed(float x) {
     }
 }
 
+// 32 consecutive values of a per-column vector (bias, scale_b) starting at column col0, the same for
+// every lane: eight 16-byte loads where the vector allows them (a per-element load of the same
+// address by all lanes costs the load pipe 64 instructions per chunk instead of 16), else scalar loads
+// clamped to the last column.  base == NULL gives `neutral`.
+__device__ __forceinline__ void load_column_values(const float *base, int col0, int N, float neutral, float (&out)[32]) {
+    if (!base) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) out[j] = neutral;
+    } else if (col0 + 32 <= N && ((reinterpret_cast<uintptr_t>(base + col0) & 15u) == 0)) {
+        const float4 *src = reinterpret_cast<const float4 *>(base + col0);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float4 x = __ldg(src + q);
+            out[4 * q] = x.x, out[4 * q + 1] = x.y, out[4 * q + 2] = x.z, out[4 * q + 3] = x.w;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) out[j] = __ldg(base + min(col0 + j, N - 1));
+    }
+}
+
 // The activation is a template parameter: with a run-time switch inside the element loop the
 // compiler evaluates every branch (tanhf, erff, expf) for every element, which made the
 // epilogue of a 128 x 256 tile as long as its main loop.
 template <int EPI, int ACT>
 __device__ __forceinline__ void epilogue_math(const UmmaParams &p, const uint32_t (&v)[32],
                                               const uint32_t (&u)[32], int col0, float sa, float (&f)[32]) {
+    if constexpr (EPI == EPI_SWIGLU) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-        float x = __uint_as_float(v[j]);
-        const int col = min(col0 + j, p.N - 1);
-        if constexpr (EPI == EPI_SWIGLU) {
-            const float up = __uint_as_float(u[j]);
-            x = (x / (1.0f + expf(-x))) * up;
-        } else if constexpr (EPI == EPI_SCALED_BF16) {
-            const float sb = p.scale_b ? __ldg(p.scale_b + col) : 1.0f;
-            x = x * (sa * sb);
-            if (p.bias) x += __ldg(p.bias + col);
-        } else {
-            if (p.bias) x += __ldg(p.bias + col);
-            x = act_fixed<ACT>(x);
+        for (int j = 0; j < 32; ++j) {
+            const float x = __uint_as_float(v[j]);
+            f[j] = (x / (1.0f + expf(-x))) * __uint_as_float(u[j]);
         }
-        f[j] = x;
+    } else if constexpr (epi_scaled(EPI)) {
+        float sb[32], bias[32];
+        load_column_values(p.scale_b, col0, p.N, 1.0f, sb);
+        load_column_values(p.bias, col0, p.N, 0.0f, bias);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float acc = epi_int_acc(EPI) ? __int2float_rn((int)v[j]) : __uint_as_float(v[j]);
+            // each operation rounded by itself: the CPU restatement computes the same bits
+            const float x = __fadd_rn(__fmul_rn(acc, __fmul_rn(sa, sb[j])), bias[j]);
+            f[j] = act_fixed<ACT>(x);
+        }
+    } else {
+        if (p.bias) {
+            float bias[32];
+            load_column_values(p.bias, col0, p.N, 0.0f, bias);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = act_fixed<ACT>(__uint_as_float(v[j]) + bias[j]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = act_fixed<ACT>(__uint_as_float(v[j]));
+        }
     }
+}
+
+// Conversions of the requantising tails: round to nearest even, saturating.
+__device__ __forceinline__ uint32_t quant_s8(float x) {
+    int q = __float2int_rn(x);  // NaN -> 0
+    q = max(-128, min(127, q));
+    return (uint32_t)q & 0xffu;
+}
+__device__ __forceinline__ uint32_t quant_e4m3(float x) {
+    return (uint32_t)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
+}
+template <int EPI>
+__device__ __forceinline__ uint32_t quant4(float a, float b, float c, float d) {
+    if constexpr (EPI == EPI_ISCALED_S8)
+        return quant_s8(a) | (quant_s8(b) << 8) | (quant_s8(c) << 16) | (quant_s8(d) << 24);
+    else
+        return quant_e4m3(a) | (quant_e4m3(b) << 8) | (quant_e4m3(c) << 16) | (quant_e4m3(d) << 24);
 }
 
 // Drains one finished accumulator buffer: this warp's 32 lanes (TMEM lane quarter) by
@@ -406,14 +456,14 @@ template <int EPI, int BLOCK_N, int ACT>
 __device__ __forceinline__ void epilogue_tile_act(const UmmaParams &p, long long row0, int n0,
                                                   uint32_t t_row, uint8_t *staging, int c_begin, int c_end) {
     constexpr int kOutN = (EPI == EPI_SWIGLU) ? BLOCK_N / 2 : BLOCK_N;
-    constexpr int kOutElem = (EPI == EPI_S32) ? 4 : 2;
-    constexpr int kSlabCols = 128 / kOutElem;  // 64 bf16 or 32 int32 columns per 128-byte row
+    constexpr int kOutElem = epi_out_bytes(EPI);
+    constexpr int kSlabCols = 128 / kOutElem;  // 128 one-byte, 64 bf16 or 32 int32 columns per 128-byte row
     constexpr int kChunksPerSlab = kSlabCols / 32;
     const int lane = threadIdx.x & 31;
     const long long row = row0 + lane;
     const bool row_ok = row < p.M;
     float sa = 1.0f;
-    if constexpr (EPI == EPI_SCALED_BF16) {
+    if constexpr (epi_scaled(EPI)) {
         if (p.scale_a && row_ok) sa = p.scale_a[row];
     }
     uint4 *patch = reinterpret_cast<uint4 *>(staging);
@@ -441,6 +491,23 @@ __device__ __forceinline__ void epilogue_tile_act(const UmmaParams &p, long long
 #pragma unroll
                 for (int j = 0; j < 32; ++j)
                     if (n0 + c + j < p.N) dst[j] = (int32_t)v[j];
+            }
+        } else if constexpr (kOutElem == 1) {
+            float f[32];
+            epilogue_math<EPI, ACT>(p, v, u, n0 + c, sa, f);
+            if (coalesced) {  // 32 one-byte results: two 16-byte pieces of the row's 128-byte slab
+#pragma unroll
+                for (int q = 0; q < 2; ++q)
+                    patch[lane * 8 + ((h * 2 + q) ^ sw)] =
+                        make_uint4(quant4<EPI>(f[16 * q], f[16 * q + 1], f[16 * q + 2], f[16 * q + 3]),
+                                   quant4<EPI>(f[16 * q + 4], f[16 * q + 5], f[16 * q + 6], f[16 * q + 7]),
+                                   quant4<EPI>(f[16 * q + 8], f[16 * q + 9], f[16 * q + 10], f[16 * q + 11]),
+                                   quant4<EPI>(f[16 * q + 12], f[16 * q + 13], f[16 * q + 14], f[16 * q + 15]));
+            } else if (row_ok && !(O64_PROBE(p) & 32)) {
+                uint8_t *dst = reinterpret_cast<uint8_t *>(p.C) + row * p.ldc + n0 + c;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (n0 + c + j < p.N) dst[j] = (uint8_t)(EPI == EPI_ISCALED_S8 ? quant_s8(f[j]) : quant_e4m3(f[j]));
             }
         } else {
             float f[32];
@@ -524,7 +591,7 @@ template <int EPI, int BLOCK_N>
 __device__ __forceinline__ void epilogue_tile(const UmmaParams &p, long long row0, int n0,
                                               uint32_t t_row, uint8_t *staging, int c_begin = 0,
                                               int c_end = (EPI == EPI_SWIGLU) ? BLOCK_N / 2 : BLOCK_N) {
-    if constexpr (EPI == EPI_BF16) {
+    if constexpr (EPI == EPI_BF16 || epi_scaled(EPI)) {
         switch (p.act) {  // uniform: one branch per tile, not per element
         case O64_ACT_RELU: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_RELU>(p, row0, n0, t_row, staging, c_begin, c_end); break;
         case O64_ACT_GELU_TANH: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_GELU_TANH>(p, row0, n0, t_row, staging, c_begin, c_end); break;
@@ -543,7 +610,7 @@ template <int EPI, int BLOCK_N>
 __device__ __forceinline__ void tail_complete(uint32_t t_row, int c_begin, int c_end, const TailFix &fix) {
     constexpr int kOutN = (EPI == EPI_SWIGLU) ? BLOCK_N / 2 : BLOCK_N;
     if (fix.n == 0) return;
-    tail_reduce<EPI == EPI_S32>(t_row, c_begin, c_end, fix);
+    tail_reduce<epi_int_acc(EPI)>(t_row, c_begin, c_end, fix);
     if constexpr (EPI == EPI_SWIGLU) tail_reduce<false>(t_row, kOutN + c_begin, kOutN + c_end, fix);
 }
 

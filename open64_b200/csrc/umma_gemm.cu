@@ -263,7 +263,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 if constexpr (EPI == EPI_S32)
                     epilogue_partial<true>(p, p.C, p.ldc, row0, nb * kOutN, t_row,
                                            smem_gen + L::kStagingOffset + quarter * kEpiStagingBytesPerWarp, BLOCK_N);
-                else if constexpr (EPI != EPI_SWIGLU)
+                else if constexpr (EPI == EPI_BF16 || EPI == EPI_SCALED_BF16)
                     epilogue_partial<false>(p, p.partial, p.N, row0, nb * kOutN, t_row,
                                             smem_gen + L::kStagingOffset + quarter * kEpiStagingBytesPerWarp, BLOCK_N);
             } else if (!(O64_PROBE(p) & 4))
@@ -424,7 +424,7 @@ int umma_launch(const UmmaCall &c) {
     p.group_m = pl.group_m > 0 ? pl.group_m : 8;
     p.raster = pl.raster;
     p.num_k_blocks = (int)((c.K + block_k - 1) / block_k);
-    const int out_elem = (c.epi == EPI_S32) ? 4 : 2;
+    const int out_elem = epi_out_bytes(c.epi);
     p.vec_ok = aligned16(c.C) && ((c.ldc * out_elem) % 16 == 0);
     p.status = c.status_word;
     p.wait_ns = c.wait_ns ? c.wait_ns : kDefaultWaitNs;
@@ -432,7 +432,8 @@ int umma_launch(const UmmaCall &c) {
     p.split_k = 1;
     p.kb_per_split = p.num_k_blocks;
     p.partial = nullptr;
-    if (!pair && c.split_ready && pl.split_k > 1 && c.epi != EPI_SWIGLU && (c.partial || c.epi == EPI_S32)) {
+    if (!pair && c.split_ready && pl.split_k > 1 && (c.epi == EPI_BF16 || c.epi == EPI_SCALED_BF16 || c.epi == EPI_S32) &&
+        (c.partial || c.epi == EPI_S32)) {
         const int per = (p.num_k_blocks + pl.split_k - 1) / pl.split_k;
         p.kb_per_split = per;
         p.split_k = (p.num_k_blocks + per - 1) / per;  // every slice non-empty
@@ -542,6 +543,15 @@ int umma_launch(const UmmaCall &c) {
     } else if (c.kind == O64_KIND_S8 && c.epi == EPI_S32) {
         if (block_n == 256) O64_INST(MMA_I8, false, EPI_S32, 256, 4);
         if (block_n == 128) O64_INST(MMA_I8, false, EPI_S32, 128, 6);
+    } else if (c.kind == O64_KIND_FP8 && c.epi == EPI_SCALED_E4M3) {
+        if (block_n == 256) O64_INST(MMA_F8F6F4, false, EPI_SCALED_E4M3, 256, 4);
+        if (block_n == 128) O64_INST(MMA_F8F6F4, false, EPI_SCALED_E4M3, 128, 6);
+    } else if (c.kind == O64_KIND_S8 && c.epi == EPI_ISCALED_BF16) {
+        if (block_n == 256) O64_INST(MMA_I8, false, EPI_ISCALED_BF16, 256, 4);
+        if (block_n == 128) O64_INST(MMA_I8, false, EPI_ISCALED_BF16, 128, 6);
+    } else if (c.kind == O64_KIND_S8 && c.epi == EPI_ISCALED_S8) {
+        if (block_n == 256) O64_INST(MMA_I8, false, EPI_ISCALED_S8, 256, 4);
+        if (block_n == 128) O64_INST(MMA_I8, false, EPI_ISCALED_S8, 128, 6);
     }
 #undef O64_INST
     return O64_ERR_DTYPE;

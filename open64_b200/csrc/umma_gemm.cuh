@@ -12,7 +12,22 @@ constexpr int kTailFlagWords = kTailMaxPairs * 16;  // [pair][CTA of the pair][8
 constexpr size_t kTailSlotBytesMax = 512 * 1024;   // a pair's slot in the 512-row kernel
 constexpr unsigned long long kDefaultWaitNs = 2000000000ull;  // two seconds
 
-enum : int { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_SCALED_BF16 = 2, EPI_S32 = 3 };
+// Fused tails.  The "scaled" ones compute  act( acc * (scale_a[m] * scale_b[n]) + bias[n] )  in fp32 with
+// every operation rounded by itself (no fused multiply-add), so that a CPU restatement gives the same
+// bits, and then convert: to bf16, or - the requantising forms - to e4m3 / int8, round to nearest
+// even, saturating.
+enum : int {
+    EPI_BF16 = 0,          // fp32 accumulator: act(acc + bias) -> bf16
+    EPI_SWIGLU = 1,        // two fp32 accumulators: silu(gate) * up -> bf16
+    EPI_SCALED_BF16 = 2,   // fp32 accumulator (fp8 operands), scaled -> bf16
+    EPI_S32 = 3,           // int32 accumulator as it is
+    EPI_SCALED_E4M3 = 4,   // fp32 accumulator (fp8 operands), scaled -> e4m3
+    EPI_ISCALED_BF16 = 5,  // int32 accumulator (int8 operands), scaled -> bf16
+    EPI_ISCALED_S8 = 6     // int32 accumulator (int8 operands), scaled -> int8
+};
+__host__ __device__ constexpr bool epi_scaled(int e) { return e == EPI_SCALED_BF16 || e == EPI_SCALED_E4M3 || e == EPI_ISCALED_BF16 || e == EPI_ISCALED_S8; }
+__host__ __device__ constexpr bool epi_int_acc(int e) { return e == EPI_S32 || e == EPI_ISCALED_BF16 || e == EPI_ISCALED_S8; }
+__host__ __device__ constexpr int epi_out_bytes(int e) { return e == EPI_S32 ? 4 : ((e == EPI_SCALED_E4M3 || e == EPI_ISCALED_S8) ? 1 : 2); }
 
 // One GEMM on the tensor cores.  A is [M,K] row-major.  B is [N,K] row-major (b_kn == false)
 // or [K,N] row-major (b_kn == true, bf16 only).  For EPI_SWIGLU, B and B2 are the gate and up

@@ -423,6 +423,15 @@ int umma_launch_pair(const UmmaCall &c, const CUtensorMap &ta, const CUtensorMap
     } else if (c.kind == O64_KIND_S8 && c.epi == EPI_S32) {
         if (block_n == 256) O64_PAIR(MMA_I8, false, EPI_S32, 256, 6);
         if (block_n == 128) O64_PAIR(MMA_I8, false, EPI_S32, 128, 8);
+    } else if (c.kind == O64_KIND_FP8 && c.epi == EPI_SCALED_E4M3) {
+        if (block_n == 256) O64_PAIR(MMA_F8F6F4, false, EPI_SCALED_E4M3, 256, 6);
+        if (block_n == 128) O64_PAIR(MMA_F8F6F4, false, EPI_SCALED_E4M3, 128, 8);
+    } else if (c.kind == O64_KIND_S8 && c.epi == EPI_ISCALED_BF16) {
+        if (block_n == 256) O64_PAIR(MMA_I8, false, EPI_ISCALED_BF16, 256, 6);
+        if (block_n == 128) O64_PAIR(MMA_I8, false, EPI_ISCALED_BF16, 128, 8);
+    } else if (c.kind == O64_KIND_S8 && c.epi == EPI_ISCALED_S8) {
+        if (block_n == 256) O64_PAIR(MMA_I8, false, EPI_ISCALED_S8, 256, 6);
+        if (block_n == 128) O64_PAIR(MMA_I8, false, EPI_ISCALED_S8, 128, 8);
     }
 #undef O64_PAIR
     return O64_ERR_DTYPE;

@@ -168,8 +168,8 @@ __device__ __forceinline__ void gather_store(const UmmaParams &p, const uint8_t 
             for (int e = 0; e < 4; ++e) {
                 x[e] = __uint_as_float(w[e]);
                 if constexpr (EPI == EPI_SCALED_BF16) {
-                    x[e] = x[e] * (sa * sb[e]);
-                    if (p.bias) x[e] += bias[e];
+                    // every operation rounded by itself, as in the tile kernels' scaled tail
+                    x[e] = act_fixed<ACT>(__fadd_rn(__fmul_rn(x[e], __fmul_rn(sa, sb[e])), bias[e]));
                 } else {
                     if (p.bias) x[e] += bias[e];
                     x[e] = act_fixed<ACT>(x[e]);
@@ -190,7 +190,7 @@ __device__ __forceinline__ void gather_store(const UmmaParams &p, const uint8_t 
 template <int EPI>
 __device__ __forceinline__ void gather_store_dispatch(const UmmaParams &p, const uint8_t *recv, int m_base, int rows,
                                                       int n0, int rank, int S, int slice, int t) {
-    if constexpr (EPI == EPI_BF16) {
+    if constexpr (EPI == EPI_BF16 || EPI == EPI_SCALED_BF16) {
         switch (p.act) {  // uniform: one branch per tile
         case O64_ACT_RELU: gather_store<EPI, O64_ACT_RELU>(p, recv, m_base, rows, n0, rank, S, slice, t); break;
         case O64_ACT_GELU_TANH: gather_store<EPI, O64_ACT_GELU_TANH>(p, recv, m_base, rows, n0, rank, S, slice, t); break;

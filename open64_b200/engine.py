@@ -200,6 +200,34 @@ class Engine:
                                            _ptr(out), out.stride(0), _stream(A8)), "o64_gemm_fp8_scaled")
         return out
 
+    def gemm_fp8_scaled_ex(self, A8, B8, scaleA=None, scaleB=None, bias=None, act="none", out_kind=_lib.OUT_BF16, out=None):
+        """convert(act((A8 @ B8^T) * sA[m] * sB[n] + bias[n])): bf16, or e4m3 again (saturating, nearest even)."""
+        M, K = A8.shape
+        N = B8.shape[0]
+        if B8.shape[1] != K:
+            raise O64Error(_lib.ERR_CONFORM, "gemm_fp8_scaled_ex")
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.float8_e4m3fn if out_kind == _lib.OUT_E4M3 else torch.bfloat16,
+                              device=A8.device)
+        check(self.lib.o64_gemm_fp8_scaled_ex(self._h, M, N, K, _ptr(A8), A8.stride(0), _ptr(B8), B8.stride(0),
+                                              _ptr(scaleA), _ptr(scaleB), _ptr(bias), _act(act), _ptr(out),
+                                              out.stride(0), out_kind, _stream(A8)), "o64_gemm_fp8_scaled_ex")
+        return out
+
+    def gemm_s8_scaled(self, A, B, scaleA=None, scaleB=None, bias=None, act="none", out_kind=_lib.OUT_BF16, out=None):
+        """convert(act(float(A @ B^T) * sA[m] * sB[n] + bias[n])), int8 operands: bf16, or int8 again
+        (saturating, nearest even)."""
+        M, K = A.shape
+        N = B.shape[0]
+        if B.shape[1] != K:
+            raise O64Error(_lib.ERR_CONFORM, "gemm_s8_scaled")
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.int8 if out_kind == _lib.OUT_S8 else torch.bfloat16, device=A.device)
+        check(self.lib.o64_gemm_s8_scaled(self._h, M, N, K, _ptr(A), A.stride(0), _ptr(B), B.stride(0), _ptr(scaleA),
+                                          _ptr(scaleB), _ptr(bias), _act(act), _ptr(out), out.stride(0), out_kind,
+                                          _stream(A)), "o64_gemm_s8_scaled")
+        return out
+
     def gemm_s8(self, A, B, out=None):
         """A [M,K] int8 times B [N,K]^T int8 -> int32, exact."""
         A = _rowmajor(A, "A")

@@ -236,6 +236,72 @@ void o64ref_gemm_s8s8_s32(long M, long N, long K, const int8_t *A, long lda, con
     }
 }
 
+/* ---- the scaled ("requantising") tails -------------------------------------------------
+ * out = convert( act( acc * (scaleA[m] * scaleB[n]) + bias[n] ) ), every fp32 operation rounded by
+ * itself (this file is compiled with -ffp-contract=off), as the device kernels' scaled tail does.
+ * out_kind: 0 = fp32 (the value before any conversion, for tolerance checks), 1 = int8 (nearest even,
+ * saturating at -128 / 127), 2 = e4m3 (nearest even, saturating at +-448), 3 = bf16 bits.
+ * The reference has no scaled product; its narrow integer MATMUL (INTEGER*1 in, INTEGER*1 out,
+ * osprey/libfi/matrix/i1gemmx.f) wraps instead of scaling.  The tail's vocabulary is apply_act's. */
+static inline void store_scaled(float x, int out_kind, void *C, long idx) {
+    if (out_kind == 1) {
+        float r = nearbyintf(x);
+        if (isnan(r)) r = 0.0f;
+        if (r < -128.0f) r = -128.0f;
+        if (r > 127.0f) r = 127.0f;
+        ((int8_t *)C)[idx] = (int8_t)r;
+    } else if (out_kind == 2) {
+        ((uint8_t *)C)[idx] = f32_to_e4m3(x);
+    } else if (out_kind == 3) {
+        ((uint16_t *)C)[idx] = f32_to_bf16(x);
+    } else {
+        ((float *)C)[idx] = x;
+    }
+}
+
+/* int8 operands: the accumulator is the exact int32 sum, so the whole result is reproducible bit for
+ * bit wherever act is exact (none, ReLU). */
+void o64ref_gemm_s8_scaled(long M, long N, long K, const int8_t *A, long lda, const int8_t *B, long ldb,
+                           const float *scaleA, const float *scaleB, const float *bias, int act, int out_kind,
+                           void *C, long ldc) {
+#pragma omp parallel for schedule(static)
+    for (long i = 0; i < M; ++i) {
+        const int8_t *a = A + i * lda;
+        const float sa = scaleA ? scaleA[i] : 1.0f;
+        for (long j = 0; j < N; ++j) {
+            const int8_t *b = B + j * ldb;
+            int32_t acc = 0;
+            for (long k = 0; k < K; ++k) acc += (int32_t)a[k] * (int32_t)b[k];
+            const float s = sa * (scaleB ? scaleB[j] : 1.0f);
+            float x = (float)acc * s;
+            x = x + (bias ? bias[j] : 0.0f);
+            store_scaled(apply_act(x, act), out_kind, C, i * ldc + j);
+        }
+    }
+}
+
+/* e4m3 operands: fp32 nest on the unscaled values (what the tensor cores accumulate), then the tail. */
+void o64ref_gemm_fp8_scaled_ex(long M, long N, long K, const uint8_t *A8, long lda, const uint8_t *B8, long ldb,
+                               const float *scaleA, const float *scaleB, const float *bias, int act, int out_kind,
+                               void *C, long ldc) {
+    float lut[256];
+    for (int v = 0; v < 256; ++v) lut[v] = e4m3_to_f32((uint8_t)v);
+#pragma omp parallel for schedule(static)
+    for (long i = 0; i < M; ++i) {
+        const uint8_t *a = A8 + i * lda;
+        const float sa = scaleA ? scaleA[i] : 1.0f;
+        for (long j = 0; j < N; ++j) {
+            const uint8_t *b = B8 + j * ldb;
+            float acc = 0.0f;
+            for (long k = 0; k < K; ++k) acc = acc + lut[a[k]] * lut[b[k]];
+            const float s = sa * (scaleB ? scaleB[j] : 1.0f);
+            float x = acc * s;
+            x = x + (bias ? bias[j] : 0.0f);
+            store_scaled(apply_act(x, act), out_kind, C, i * ldc + j);
+        }
+    }
+}
+
 /* ---- the runtime's strided kernel (xgemmx.h:172-236, s4gemmx.f:151-196) ---------------
  * C = alpha*A*B + beta*C with element(i,j) of X at X[inc1x*i + inc2x*j] (0-based).
  * Loop order J > L > I; the axpy over a column of C is skipped when B(L,J) == 0. */

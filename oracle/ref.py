@@ -17,7 +17,7 @@ ACT_NONE, ACT_RELU, ACT_GELU_TANH, ACT_GELU_ERF, ACT_SILU = range(5)
 __all__ = [
     "ACT_NONE", "ACT_RELU", "ACT_GELU_TANH", "ACT_GELU_ERF", "ACT_SILU", "build", "lib",
     "linear_f32", "linear_f32_acc64", "gemm_bf16", "swiglu_bf16", "gemm_fp8_scaled",
-    "gemm_s8s8_s32", "s4gemmx", "s4gemvx", "xgemmx", "sgemvx_f64", "cgemmx", "cgemvx", "lgemmx", "internal_mm_f32", "bf16_to_f32", "f32_to_bf16",
+    "gemm_s8s8_s32", "gemm_s8_scaled", "gemm_fp8_scaled_ex", "s4gemmx", "s4gemvx", "xgemmx", "sgemvx_f64", "cgemmx", "cgemvx", "lgemmx", "internal_mm_f32", "bf16_to_f32", "f32_to_bf16",
     "e4m3_to_f32", "f32_to_e4m3", "num_threads", "set_num_threads",
 ]
 
@@ -126,6 +126,43 @@ def gemm_s8s8_s32(A, B):
     assert B.shape[1] == K
     C = np.empty((M, N), np.int32)
     lib().o64ref_gemm_s8s8_s32(L(M), L(N), L(K), _p(A), L(K), _p(B), L(K), _p(C), L(N))
+    return C
+
+
+_OUT_DT = {0: np.float32, 1: np.int8, 2: np.uint8, 3: np.uint16}
+
+
+def gemm_s8_scaled(A, B, scaleA=None, scaleB=None, bias=None, act=ACT_NONE, out_kind=0):
+    """convert(act(float(A @ B^T) * (sA[m] * sB[n]) + bias[n])), int8 operands; out_kind 0 = fp32 value,
+    1 = int8 (nearest even, saturating), 3 = bf16 bits."""
+    A = _c(A, np.int8)
+    B = _c(B, np.int8)
+    M, K = A.shape
+    N = B.shape[0]
+    assert B.shape[1] == K
+    sA = _c(scaleA, np.float32) if scaleA is not None else None
+    sB = _c(scaleB, np.float32) if scaleB is not None else None
+    bias = _c(bias, np.float32) if bias is not None else None
+    C = np.empty((M, N), _OUT_DT[out_kind])
+    lib().o64ref_gemm_s8_scaled(L(M), L(N), L(K), _p(A), L(K), _p(B), L(K), _p(sA), _p(sB), _p(bias), I(act),
+                                I(out_kind), _p(C), L(N))
+    return C
+
+
+def gemm_fp8_scaled_ex(A8, B8, scaleA=None, scaleB=None, bias=None, act=ACT_NONE, out_kind=0):
+    """The same tail on the fp32 nest over e4m3 bit patterns; out_kind 0 = fp32 value, 2 = e4m3 bits
+    (nearest even, saturating), 3 = bf16 bits."""
+    A8 = _c(A8, np.uint8)
+    B8 = _c(B8, np.uint8)
+    M, K = A8.shape
+    N = B8.shape[0]
+    assert B8.shape[1] == K
+    sA = _c(scaleA, np.float32) if scaleA is not None else None
+    sB = _c(scaleB, np.float32) if scaleB is not None else None
+    bias = _c(bias, np.float32) if bias is not None else None
+    C = np.empty((M, N), _OUT_DT[out_kind])
+    lib().o64ref_gemm_fp8_scaled_ex(L(M), L(N), L(K), _p(A8), L(K), _p(B8), L(K), _p(sA), _p(sB), _p(bias), I(act),
+                                    I(out_kind), _p(C), L(N))
     return C
 
 

@@ -1,0 +1,120 @@
+"""GPU: the scaled products with a fused activation and a requantised result.
+int8 operands: the accumulator is an exact integer and the tail is specified operation by operation
+(nothing fused), so bf16 and int8 results must equal the oracle's BIT FOR BIT where the activation is
+exact (none, ReLU); with GELU / SiLU (libm vs the device's expf / tanhf) an int8 result may differ by
+one step in a few places.  e4m3 operands accumulate in a different order on the tensor cores: results
+are held to the contract's tolerance, e4m3 results to one step of that format."""
+import numpy as np
+import pytest
+import torch
+
+import open64_b200 as o
+import oracle
+from util import TOL_LOWP, bits8, relmax
+
+pytestmark = pytest.mark.gpu
+ACTS = {"none": oracle.ACT_NONE, "relu": oracle.ACT_RELU, "gelu_tanh": oracle.ACT_GELU_TANH, "silu": oracle.ACT_SILU}
+
+PINS = [None, dict(cta_group=1, tile_m=128, tile_n=256, split_k=1), dict(cta_group=1, tile_m=128, tile_n=128, split_k=1),
+        dict(cta_group=2, tile_m=256, tile_n=256), dict(cta_group=2, tile_m=256, tile_n=128)]
+
+
+def _int8_case(M, N, K, seed):
+    A, B = o.workloads.c5_int8(M, N, K, seed=seed)
+    g = torch.Generator().manual_seed(seed + 1)
+    sA = (torch.rand(M, generator=g) * 0.01 + 0.002).float()
+    sB = (torch.rand(N, generator=g) * 0.01 + 0.002).float()
+    bias = (torch.rand(N, generator=g) * 8 - 4).float()
+    return A, B, sA, sB, bias
+
+
+@pytest.mark.parametrize("pin", PINS, ids=["auto", "1cta256", "1cta128", "pair256", "pair128"])
+@pytest.mark.parametrize("M,N,K", [(256, 512, 384), (300, 1000, 1100), (130, 72, 200)])
+def test_int8_scaled_exact(eng, pin, M, N, K):
+    dev = torch.device("cuda", eng.device)
+    A, B, sA, sB, bias = _int8_case(M, N, K, seed=M + N)
+    if pin:
+        eng.plan_set(o.KIND_S8, **pin)
+    try:
+        for act in ("none", "relu"):
+            for out_kind, okind in ((o.OUT_S8, 1), (o.OUT_BF16, 3)):
+                want = oracle.gemm_s8_scaled(A.numpy(), B.numpy(), sA.numpy(), sB.numpy(), bias.numpy(), ACTS[act], okind)
+                got = eng.gemm_s8_scaled(A.to(dev), B.to(dev), sA.to(dev), sB.to(dev), bias.to(dev), act, out_kind)
+                got = got.cpu().numpy() if out_kind == o.OUT_S8 else got.view(torch.int16).cpu().numpy().view(np.uint16)
+                assert np.array_equal(got, want), (pin, act, out_kind, int((got != want).sum()))
+            if act == "relu":
+                assert (want >= 0).all() if okind == 1 else True
+        assert eng.last_status() == (o.OK, 0)
+    finally:
+        eng.plan_set(o.KIND_S8)
+
+
+def test_int8_requant_saturates_and_rounds_to_even(eng):
+    dev = torch.device("cuda", eng.device)
+    M, N, K = 128, 128, 64
+    A = torch.ones((M, K), dtype=torch.int8)
+    B = torch.ones((N, K), dtype=torch.int8)                      # acc = 64 everywhere
+    sB = torch.ones(N)
+    # 64 * s: halves round to even, large magnitudes saturate
+    sA = torch.tensor([0.0078125 * v for v in (1, 3, 5, 7)] * (M // 4))    # 0.5, 1.5, 2.5, 3.5
+    got = eng.gemm_s8_scaled(A.to(dev), B.to(dev), sA.to(dev), sB.to(dev), None, "none", o.OUT_S8).cpu()
+    assert got[:4, 0].tolist() == [0, 2, 2, 4]
+    big = eng.gemm_s8_scaled(A.to(dev), B.to(dev), torch.full((M,), 100.0, device=dev), None,
+                             None, "none", o.OUT_S8).cpu()
+    assert (big == 127).all()
+    neg = eng.gemm_s8_scaled(A.to(dev), (-B).to(dev), torch.full((M,), 100.0, device=dev), None,
+                             None, "none", o.OUT_S8).cpu()
+    assert (neg == -128).all()
+
+
+@pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
+def test_int8_scaled_with_transcendental_activation(eng, act):
+    dev = torch.device("cuda", eng.device)
+    A, B, sA, sB, bias = _int8_case(256, 512, 512, seed=9)
+    ref = oracle.gemm_s8_scaled(A.numpy(), B.numpy(), sA.numpy(), sB.numpy(), bias.numpy(), ACTS[act], 0)
+    got = eng.gemm_s8_scaled(A.to(dev), B.to(dev), sA.to(dev), sB.to(dev), bias.to(dev), act, o.OUT_BF16)
+    assert relmax(got.float().cpu().numpy(), ref) <= 4e-3
+    q = eng.gemm_s8_scaled(A.to(dev), B.to(dev), sA.to(dev), sB.to(dev), bias.to(dev), act, o.OUT_S8).cpu().numpy()
+    want = oracle.gemm_s8_scaled(A.numpy(), B.numpy(), sA.numpy(), sB.numpy(), bias.numpy(), ACTS[act], 1)
+    diff = np.abs(q.astype(np.int32) - want.astype(np.int32))
+    assert diff.max() <= 1 and (diff != 0).mean() < 1e-3
+
+
+@pytest.mark.parametrize("pin", [None, dict(cta_group=2, tile_m=256, tile_n=256), dict(cta_group=1, tile_m=128, tile_n=128, split_k=1)],
+                         ids=["auto", "pair256", "1cta128"])
+def test_fp8_scaled_activation_and_e4m3_result(eng, pin):
+    dev = torch.device("cuda", eng.device)
+    A8, W8, sA, sB, b = o.workloads.c4_fp8(300, 1000, 1100)
+    a8, w8 = bits8(A8), bits8(W8)
+    if pin:
+        eng.plan_set(o.KIND_FP8, **pin)
+    try:
+        for act in ("none", "silu"):
+            ref = oracle.gemm_fp8_scaled_ex(a8, w8, sA.numpy(), sB.numpy(), b.numpy(), ACTS[act], 0)
+            got = eng.gemm_fp8_scaled_ex(A8.to(dev), W8.to(dev), sA.to(dev), sB.to(dev), b.to(dev), act, o.OUT_BF16)
+            assert relmax(got.float().cpu().numpy(), ref) <= 4e-3
+            # requantised: scale so that the result spans e4m3's range
+            s_out = (200.0 / np.abs(ref).max()).astype(np.float32)
+            ref8 = oracle.gemm_fp8_scaled_ex(a8, w8, sA.numpy() * s_out, sB.numpy(), b.numpy() * s_out, ACTS["none"], 2)
+            got8 = eng.gemm_fp8_scaled_ex(A8.to(dev), W8.to(dev), (sA * float(s_out)).to(dev), sB.to(dev),
+                                          (b * float(s_out)).to(dev), "none", o.OUT_E4M3)
+            g = oracle.e4m3_to_f32(bits8(got8))
+            r = oracle.e4m3_to_f32(ref8)
+            assert np.isfinite(g).all()
+            # one step of e4m3 is 1/8 of the value's binade: 12.5 % of it at most
+            assert (np.abs(g - r) <= 0.126 * np.maximum(np.abs(r), 2.0 ** -6)).all()
+            assert (g == r).mean() > 0.9
+        assert eng.last_status() == (o.OK, 0)
+    finally:
+        eng.plan_set(o.KIND_FP8)
+
+
+def test_host_operands_and_errors(eng):
+    A, B, sA, sB, bias = _int8_case(128, 256, 128, seed=4)
+    want = oracle.gemm_s8_scaled(A.numpy(), B.numpy(), sA.numpy(), sB.numpy(), bias.numpy(), oracle.ACT_RELU, 1)
+    out = torch.empty((128, 256), dtype=torch.int8)
+    eng.gemm_s8_scaled(A, B, sA, sB, bias, "relu", o.OUT_S8, out=out)             # all on the host: staged
+    assert np.array_equal(out.numpy(), want)
+    with pytest.raises(o.O64Error) as e:
+        eng.gemm_s8_scaled(A, B, sA, sB, bias, "relu", o.OUT_E4M3, out=out)
+    assert e.value.status == o.ERR_DTYPE

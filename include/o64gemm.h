@@ -583,6 +583,39 @@ void _MATMUL_LL2(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *
 void _MATMUL_LL4(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
 void _MATMUL_LL(o64_dopevec_t *RESULT, o64_dopevec_t *MATRIX_A, o64_dopevec_t *MATRIX_B);
 
+/* ---- DOT_PRODUCT ------------------------------------------------------------------------------
+ * MATMUL's rank-1 sibling in the same runtime: _DOT_<A><B>(VECTOR_A, VECTOR_B) over two rank-1 dope
+ * vectors (osprey/libfi/dotprod/dot_s4s4.f ... dot_ll.f; argument parsing predot@.c:52-93; the sums
+ * dot90.h:83-86, dotc90.h:84-87 - COMPLEX conjugates VECTOR_A -, dotl90.h:84-87 - LOGICAL is the .OR. of
+ * the .AND.s).  The result has the wider (or the REAL) kind of the two; integers wrap; a LOGICAL result
+ * is 1 or 0.  COMPLEX results come back as a (re, im) structure, which the x86-64 ABI returns in the
+ * registers a C99 _Complex value uses.  The kinds with a REAL*16 / COMPLEX*32 operand and the Cray
+ * default-integer names are not provided.  Errors are left in o64_compat_last_status() and give 0. */
+typedef struct { float re, im; } o64_complex8_t;
+typedef struct { double re, im; } o64_complex16_t;
+float _DOT_S4S4(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+double _DOT_SS(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+double _DOT_S4S(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+double _DOT_SS4(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+int32_t _DOT_I4I4(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+int64_t _DOT_JJ(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+int64_t _DOT_I4J(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+int64_t _DOT_JI4(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+float _DOT_I4S4(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+float _DOT_S4I4(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+double _DOT_I4S(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+double _DOT_SI4(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+float _DOT_JS4(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+float _DOT_S4J(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+double _DOT_JS(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+double _DOT_SJ(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+int32_t _DOT_L4L4(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+int64_t _DOT_LL(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+int64_t _DOT_L4L(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+int64_t _DOT_LL4(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+o64_complex8_t _DOT_C4C4(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+o64_complex16_t _DOT_CC(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
+
 /* Status of the last compat call on this thread (the Fortran entry points return void). */
 int o64_compat_last_status(void);
 

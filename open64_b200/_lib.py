@@ -41,7 +41,29 @@ EXPORTS = [
     "_MATMUL_C4S4", "_MATMUL_S4C4", "_MATMUL_C4S", "_MATMUL_SC4", "_MATMUL_CS4", "_MATMUL_S4C", "_MATMUL_CS", "_MATMUL_SC", "_MATMUL_C4C",
     "_MATMUL_CC4", "_MATMUL_C4I1", "_MATMUL_C4I2", "_MATMUL_C4I4", "_MATMUL_C4J", "_MATMUL_I1C4", "_MATMUL_I2C4", "_MATMUL_I4C4", "_MATMUL_JC4",
     "_MATMUL_CI1", "_MATMUL_CI2", "_MATMUL_CI4", "_MATMUL_CJ", "_MATMUL_I1C", "_MATMUL_I2C", "_MATMUL_I4C", "_MATMUL_JC",
+    "_DOT_S4S4", "_DOT_SS", "_DOT_S4S", "_DOT_SS4", "_DOT_I4I4", "_DOT_JJ", "_DOT_I4J", "_DOT_JI4", "_DOT_I4S4", "_DOT_S4I4",
+    "_DOT_I4S", "_DOT_SI4", "_DOT_JS4", "_DOT_S4J", "_DOT_JS", "_DOT_SJ", "_DOT_L4L4", "_DOT_LL", "_DOT_L4L", "_DOT_LL4",
+    "_DOT_C4C4", "_DOT_CC",
 ]
+
+
+class Complex8(ctypes.Structure):
+    _fields_ = [("re", ctypes.c_float), ("im", ctypes.c_float)]
+
+
+class Complex16(ctypes.Structure):
+    _fields_ = [("re", ctypes.c_double), ("im", ctypes.c_double)]
+
+
+# result type of each DOT_PRODUCT entry point
+DOT_RESTYPE = {
+    "_DOT_S4S4": ctypes.c_float, "_DOT_SS": ctypes.c_double, "_DOT_S4S": ctypes.c_double, "_DOT_SS4": ctypes.c_double,
+    "_DOT_I4I4": ctypes.c_int32, "_DOT_JJ": ctypes.c_int64, "_DOT_I4J": ctypes.c_int64, "_DOT_JI4": ctypes.c_int64,
+    "_DOT_I4S4": ctypes.c_float, "_DOT_S4I4": ctypes.c_float, "_DOT_I4S": ctypes.c_double, "_DOT_SI4": ctypes.c_double,
+    "_DOT_JS4": ctypes.c_float, "_DOT_S4J": ctypes.c_float, "_DOT_JS": ctypes.c_double, "_DOT_SJ": ctypes.c_double,
+    "_DOT_L4L4": ctypes.c_int32, "_DOT_LL": ctypes.c_int64, "_DOT_L4L": ctypes.c_int64, "_DOT_LL4": ctypes.c_int64,
+    "_DOT_C4C4": Complex8, "_DOT_CC": Complex16,
+}
 
 
 class Plan(ctypes.Structure):
@@ -177,6 +199,9 @@ def lib():
     for name in [e for e in EXPORTS if e.startswith("_MATMUL_")]:
         getattr(L, name).argtypes = [ctypes.POINTER(DopeVector)] * 3
         getattr(L, name).restype = None
+    for name, rt in DOT_RESTYPE.items():
+        getattr(L, name).argtypes = [ctypes.POINTER(DopeVector)] * 2
+        getattr(L, name).restype = rt
     L.o64_compat_last_status.restype = ci
     _lib = L
     return L

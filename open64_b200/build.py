@@ -19,7 +19,7 @@ OBJ_DIR = os.path.join(HERE, "build")
 NEST_SRC = os.path.join(HERE, "nest2c", "nest2c.cpp")
 NEST_OUT = os.path.join(HERE, "nest2c", "o64nest")
 
-SOURCES = ["api.cu", "umma_gemm.cu", "umma_gemm_2cta.cu", "umma_gemm_wide.cu", "umma_gemm_skinny.cu", "simt_kernels.cu", "simt_generic.cu", "plan.cpp", "no_alloc.cu"]
+SOURCES = ["api.cu", "umma_gemm.cu", "umma_gemm_2cta.cu", "umma_gemm_wide.cu", "umma_gemm_skinny.cu", "simt_kernels.cu", "simt_generic.cu", "plan.cpp", "no_alloc.cu", "dotprod.cu"]
 HEADERS = ["ptx_sm100.cuh", "umma_gemm.cuh", "umma_common.cuh", "simt_kernels.cuh", "../../include/o64gemm.h"]
 
 NVCC_FLAGS = [

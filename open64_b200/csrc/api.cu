@@ -1707,3 +1707,85 @@ O64_LMATMUL_ENTRY(_MATMUL_LL2, int16_t, int64_t, true)
 O64_LMATMUL_ENTRY(_MATMUL_LL4, int32_t, int64_t, true)
 O64_LMATMUL_ENTRY(_MATMUL_LL, int64_t, int64_t, false)
 #undef O64_LMATMUL_ENTRY
+
+// ---- DOT_PRODUCT over dope vectors (osprey/libfi/dotprod) ----------------------------------------
+// _DOT_<A><B>(VECTOR_A, VECTOR_B): the vectors' addresses, length and element strides are read as the
+// runtime's _PREDOT reads them (osprey/libfi/dotprod/predot@.c:52-93: the length is VECTOR_A's extent,
+// strides of 64- and 128-bit elements are divided down from 32-bit words), then one pass on the GPU
+// (dotprod.cu) forms the sum of dot90.h / dotc90.h / dotl90.h.  Host vectors are staged.  Unlike the
+// reference a VECTOR_B shorter than VECTOR_A is reported (O64_ERR_CONFORM, result 0) instead of read
+// past its end.
+namespace {
+template <typename TX, typename TY, typename TR, int MODE>
+TR dot_impl(const o64_dopevec_t *X, const o64_dopevec_t *Y) {
+    TR result = TR(0);
+    g_compat_status = O64_OK;
+    if (!X || !Y) {
+        g_compat_status = O64_ERR_RANK;
+        return result;
+    }
+    const DvView x = view_of(X), y = view_of(Y);
+    if (x.ndim != 1 || y.ndim != 1) {
+        g_compat_status = O64_ERR_RANK;
+        return result;
+    }
+    const long n = x.n1;
+    if (n <= 0) return result;
+    if (y.n1 < n) {
+        g_compat_status = O64_ERR_CONFORM;
+        return result;
+    }
+    if (!x.ptr || !y.ptr || x.inc1 < 0 || y.inc1 < 0) {
+        g_compat_status = O64_ERR_RANK;
+        return result;
+    }
+    o64_handle_t h = compat_handle();
+    if (!h) {
+        g_compat_status = O64_ERR_CUDA;
+        return result;
+    }
+    DeviceGuard g(h->device);
+    cudaStream_t s = nullptr;
+    const void *dx, *dy;
+    int rc = stage_in(h, 0, x.ptr, strided_span(n, 1, x.inc1, 0) * sizeof(TX), s, &dx);
+    if (!rc) rc = stage_in(h, 1, y.ptr, strided_span(n, 1, y.inc1, 0) * sizeof(TY), s, &dy);
+    if (!rc) rc = reserve(&h->ws, &h->ws_cap, dot_workspace_bytes());
+    if (!rc)
+        rc = dot_device<TX, TY, TR, MODE>(n, static_cast<const TX *>(dx), x.inc1, static_cast<const TY *>(dy), y.inc1, h->ws,
+                                          &result, s);
+    g_compat_status = rc;
+    return rc ? TR(0) : result;
+}
+}  // namespace
+
+#define O64_DOT_ENTRY(NAME, RET, TX, TY, TR, MODE)                                       \
+    extern "C" RET NAME(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B) {  \
+        const TR r = dot_impl<TX, TY, TR, MODE>(VECTOR_A, VECTOR_B);                     \
+        RET out;                                                                         \
+        static_assert(sizeof(out) == sizeof(r), "result size");                          \
+        memcpy(&out, &r, sizeof(out));                                                   \
+        return out;                                                                      \
+    }
+O64_DOT_ENTRY(_DOT_S4S4, float, float, float, float, 0)
+O64_DOT_ENTRY(_DOT_SS, double, double, double, double, 0)
+O64_DOT_ENTRY(_DOT_S4S, double, float, double, double, 0)
+O64_DOT_ENTRY(_DOT_SS4, double, double, float, double, 0)
+O64_DOT_ENTRY(_DOT_I4I4, int32_t, int32_t, int32_t, uint32_t, 0)
+O64_DOT_ENTRY(_DOT_JJ, int64_t, int64_t, int64_t, uint64_t, 0)
+O64_DOT_ENTRY(_DOT_I4J, int64_t, int32_t, int64_t, uint64_t, 0)
+O64_DOT_ENTRY(_DOT_JI4, int64_t, int64_t, int32_t, uint64_t, 0)
+O64_DOT_ENTRY(_DOT_I4S4, float, int32_t, float, float, 0)
+O64_DOT_ENTRY(_DOT_S4I4, float, float, int32_t, float, 0)
+O64_DOT_ENTRY(_DOT_I4S, double, int32_t, double, double, 0)
+O64_DOT_ENTRY(_DOT_SI4, double, double, int32_t, double, 0)
+O64_DOT_ENTRY(_DOT_JS4, float, int64_t, float, float, 0)
+O64_DOT_ENTRY(_DOT_S4J, float, float, int64_t, float, 0)
+O64_DOT_ENTRY(_DOT_JS, double, int64_t, double, double, 0)
+O64_DOT_ENTRY(_DOT_SJ, double, double, int64_t, double, 0)
+O64_DOT_ENTRY(_DOT_L4L4, int32_t, int32_t, int32_t, int32_t, 1)
+O64_DOT_ENTRY(_DOT_LL, int64_t, int64_t, int64_t, int64_t, 1)
+O64_DOT_ENTRY(_DOT_L4L, int64_t, int32_t, int64_t, int64_t, 1)
+O64_DOT_ENTRY(_DOT_LL4, int64_t, int64_t, int32_t, int64_t, 1)
+O64_DOT_ENTRY(_DOT_C4C4, o64_complex8_t, c4_t, c4_t, c4_t, 2)
+O64_DOT_ENTRY(_DOT_CC, o64_complex16_t, c8_t, c8_t, c8_t, 2)
+#undef O64_DOT_ENTRY

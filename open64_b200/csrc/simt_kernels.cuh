@@ -82,6 +82,15 @@ int generic_gemvx(int64_t M, int64_t N, T alpha, const T *A, int64_t a1, int64_t
 template <typename T>
 int generic_scale(int64_t M, int64_t N, T beta, T *C, int64_t c1, int64_t c2, cudaStream_t s);
 
+// DOT_PRODUCT (dotprod.cu): sum over i of x(i) * y(i) with element strides, formed in TR (integers on
+// the unsigned type of the result's width); MODE 0 arithmetic, 1 LOGICAL (.OR. of .AND.), 2 COMPLEX with
+// x conjugated.  `workspace`: device memory of dot_workspace_bytes(); the result arrives in *host_result
+// and the call waits for it.
+size_t dot_workspace_bytes();
+template <typename TX, typename TY, typename TR, int MODE>
+int dot_device(long long n, const TX *x, long long incx, const TY *y, long long incy, void *workspace, TR *host_result,
+               cudaStream_t s);
+
 // LOGICAL kinds: C = (beta AND C) OR (alpha AND (A AND B, OR-reduced over K)); non-zero is true.
 template <typename TA, typename T>
 int logical_gemmx(int64_t M, int64_t N, int64_t K, int alpha, const TA *A, int64_t a1, int64_t a2, const T *B,

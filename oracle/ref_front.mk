@@ -8,6 +8,7 @@
 #   osprey/libfi/matrix/MATMUL_*dispatch.c  the 16 rank dispatchers in front of the BLAS hook
 #   osprey/libfi/matrix/mmx_dlutil.c        the dlsym("sgemm_" ...) hook behind F90_MATMUL_BLAS
 #   osprey/libfi/matrix/f90_mmult_error.c
+#   osprey/libfi/dotprod/predot@.c          _PREDOT, the dope-vector parser of DOT_PRODUCT (as ref_PREDOT)
 # Every reference entry point is renamed on the command line (-D_MATMUL_S4S4=ref_MATMUL_S4S4 for the
 # wrappers, refdisp_MATMUL_S4S4 for the dispatchers) so that it can live in one process with the
 # engine's entry point of the same name.  The arithmetic kernels of the reference are Fortran
@@ -32,7 +33,7 @@ DISP    := C4C4 C4C C4S4 C4S CC4 CC CS4 CS S4C4 S4C S4S4 S4S SC4 SC SS4 SS
 upper    = $(shell echo '$(subst @,,$(1))' | tr 'a-z' 'A-Z')
 WRAP_O  := $(foreach k,$(KINDS),$(OUT)/obj/matmul_$(subst @,,$(k)).o)
 DISP_O  := $(foreach d,$(DISP),$(OUT)/obj/disp_$(d).o)
-MISC_O  := $(OUT)/obj/mmx_dlutil.o $(OUT)/obj/f90_mmult_error.o $(OUT)/obj/glue.o
+MISC_O  := $(OUT)/obj/mmx_dlutil.o $(OUT)/obj/f90_mmult_error.o $(OUT)/obj/predot.o $(OUT)/obj/glue.o
 
 all: $(OUT)/libfi_front_oracle.so $(OUT)/libfi_front_engine.so
 
@@ -55,6 +56,8 @@ $(OUT)/obj/mmx_dlutil.o: $(SRC)/mmx_dlutil.c | $(OUT)/obj
 	$(CC) $(CFLAGS) -c $< -o $@
 $(OUT)/obj/f90_mmult_error.o: $(SRC)/f90_mmult_error.c | $(OUT)/obj
 	$(CC) $(CFLAGS) -c $< -o $@
+$(OUT)/obj/predot.o: $(REF)/osprey/libfi/dotprod/predot@.c | $(OUT)/obj
+	$(CC) $(CFLAGS) -D_PREDOT=ref_PREDOT -c '$<' -o $@
 $(OUT)/obj/glue.o: $(HERE)ref_front_glue.c | $(OUT)/obj
 	$(CC) -O1 -fPIC -Wall -std=gnu11 -ffp-contract=off -D_LITTLE_ENDIAN -DKEY -I$(REF)/osprey/clibinc -c $< -o $@
 $(OUT)/obj/xiface.o: $(HERE)ref_front_xiface.c | $(OUT)/obj

@@ -202,3 +202,17 @@ def test_result_without_element_length_gets_the_entry_points_kind(built):
     assert o.lib().o64_compat_last_status() == o.OK
     assert (r.desc.type_bits >> 12) & 0xfff == 64
     assert r.desc.dimension[0].stride_mult == 2 and r.desc.dimension[1].stride_mult == 0
+
+
+@pytest.mark.parametrize("kind", ["S4", "S", "C4", "C", "I4", "J", "L4", "L"])
+def test_predot_reads_vectors_as_the_engine_does(front, kind):
+    """_PREDOT (osprey/libfi/dotprod/predot@.c, compiled from the reference tree): length, addresses
+    and element strides of two rank-1 dope vectors built the way the engine's tests build them."""
+    rng = np.random.default_rng(2)
+    a, b = fu.Operand(kind, (37,), rng, "section"), fu.Operand(kind, (37,), rng, "dense")
+    n, lx, ix, ly, iy = (ctypes.c_long() for _ in range(5))
+    A, B = a.dv(), b.dv()
+    rf.lib().ref_PREDOT(ctypes.byref(A), ctypes.byref(B), ctypes.byref(n), ctypes.byref(lx), ctypes.byref(ix),
+                        ctypes.byref(ly), ctypes.byref(iy))
+    assert (n.value, ix.value, iy.value) == (37, a.inc[0], b.inc[0])
+    assert lx.value == a.storage.ctypes.data and ly.value == b.storage.ctypes.data

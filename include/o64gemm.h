@@ -155,6 +155,16 @@ int o64_plan_model(int kind, int swiglu, int64_t M, int64_t N, int64_t K, int nu
 int o64_plan_tune(o64_handle_t h, int kind, int swiglu, int64_t M, int64_t N, int64_t K, void *stream,
                   o64_plan_t *best);
 int o64_plan_tune_clear(o64_handle_t h);
+/* Measured plans outlive the handle in a JSON file: one object per (kind, epilogue, M, N, K, ranks of the
+ * communicator) with the kernel shape and the time it was measured at, under the device name and SM
+ * count they were measured on (the reference hands each phase's decisions to the next through the WHIRL
+ * file it writes, osprey/common/com/ir_bwrite.cxx:1505).  o64_plan_load merges a file into the handle:
+ * O64_ERR_RANK if it cannot be read, O64_ERR_CONFORM if it was measured on another device type,
+ * O64_ERR_DTYPE if it holds no usable plan; entries that name no existing kernel are skipped.  With
+ * O64_PLAN_CACHE=<path> in the environment o64_create loads that file and o64_plan_tune rewrites it. */
+int o64_plan_save(o64_handle_t h, const char *path);
+int o64_plan_load(o64_handle_t h, const char *path);
+int o64_plan_count(o64_handle_t h);
 
 /* ---- native layer -------------------------------------------------------------------
  * Row-major operands; ld* in elements.  A is [M,K].  B is [K,N] when transB == 0 and
@@ -616,6 +626,10 @@ int64_t _DOT_LL4(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
 o64_complex8_t _DOT_C4C4(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
 o64_complex16_t _DOT_CC(const o64_dopevec_t *VECTOR_A, const o64_dopevec_t *VECTOR_B);
 
+/* The handle behind the Fortran-ABI entry points (one per process, on the device current at the first
+ * call; created here if need be; NULL without a usable GPU): for o64_plan_set / o64_set_wait_budget_us /
+ * o64_last_status on the calls that take no handle.  Do not destroy it. */
+o64_handle_t o64_compat_handle(void);
 /* Status of the last compat call on this thread (the Fortran entry points return void). */
 int o64_compat_last_status(void);
 

@@ -22,10 +22,10 @@ STATIC_SCRATCH_BYTES = 16 << 20
 # every symbol include/o64gemm.h declares
 EXPORTS = [
     "o64_create", "o64_destroy", "o64_last_status", "o64_set_wait_budget_us", "o64_test_gemm_bf16_withheld", "o64_test_last_tail_split", "o64_test_force_tail_split", "o64_status_string", "o64_version",
-    "o64_plan_get", "o64_plan_set", "o64_plan_model", "o64_plan_tune", "o64_plan_tune_clear", "o64_linear_f32", "o64_gemm_bf16", "o64_gemm_bf16_swiglu",
+    "o64_plan_get", "o64_plan_set", "o64_plan_model", "o64_plan_tune", "o64_plan_tune_clear", "o64_plan_save", "o64_plan_load", "o64_plan_count", "o64_linear_f32", "o64_gemm_bf16", "o64_gemm_bf16_swiglu",
     "o64_gemm_fp8_scaled", "o64_gemm_fp8_scaled_ex", "o64_gemm_s8_scaled", "o64_gemm_s8s8_s32", "o64_gemm_s8s8_s32_static", "o64_naive_gemm", "o64_comm_unique_id",
     "o64_comm_init", "o64_comm_destroy", "o64_comm_alloc_result", "o64_gemm_s8_sharded_workspace", "o64_gemm_s8_sharded", "o64_gemm_bf16_sharded",
-    "sgemm_", "_s4gemmx__", "_s4gemvx__", "_MATMUL_S4S4", "o64_compat_last_status",
+    "sgemm_", "_s4gemmx__", "_s4gemvx__", "_MATMUL_S4S4", "o64_compat_last_status", "o64_compat_handle",
     "dgemm_", "_sgemmx__", "_sgemvx__", "_MATMUL_SS",
     "_i1gemmx__", "_i1i2gemmx__", "_i1i4gemmx__", "_i1jgemmx__", "_i2gemmx__", "_i2i4gemmx__", "_i2jgemmx__",
     "_i4gemmx__", "_i4jgemmx__", "_jgemmx__",
@@ -155,6 +155,9 @@ def lib():
     L.o64_plan_set.argtypes = [vp, ci, ctypes.POINTER(Plan)]
     L.o64_plan_tune.argtypes = [vp, ci, ci, i64, i64, i64, vp, ctypes.POINTER(Plan)]
     L.o64_plan_tune_clear.argtypes = [vp]
+    L.o64_plan_save.argtypes = [vp, ctypes.c_char_p]
+    L.o64_plan_load.argtypes = [vp, ctypes.c_char_p]
+    L.o64_plan_count.argtypes = [vp]
     L.o64_plan_model.argtypes = [ci, ci, i64, i64, i64, ci, ctypes.POINTER(Plan), ctypes.POINTER(Plan)]
     L.o64_linear_f32.argtypes = [vp, i64, i64, i64, vp, i64, vp, i64, vp, vp, i64, ci, vp]
     L.o64_gemm_bf16.argtypes = [vp, i64, i64, i64, vp, i64, vp, i64, ci, vp, i64,
@@ -203,6 +206,7 @@ def lib():
         getattr(L, name).argtypes = [ctypes.POINTER(DopeVector)] * 2
         getattr(L, name).restype = rt
     L.o64_compat_last_status.restype = ci
+    L.o64_compat_handle.restype = vp
     _lib = L
     return L
 

@@ -13,6 +13,7 @@
 #include <map>
 #include <mutex>
 #include <new>
+#include <string>
 #include <type_traits>
 #include <vector>
 
@@ -83,7 +84,9 @@ struct o64_handle_s {
     void *ws = nullptr;
     size_t ws_cap = 0;
     // plans found by o64_plan_tune, by (kind, SwiGLU?, M, N, K): used when the kind has no pin
-    std::map<std::array<int64_t, 5>, o64_plan_t> tuned;
+    // (key: kind, SwiGLU?, M, N, K, ranks of the communicator; predicted_ms holds the measured time)
+    std::map<std::array<int64_t, 6>, o64_plan_t> tuned;
+    char device_name[128] = {0};
     // host operands of a large product travel in row blocks on two side streams, so that the
     // copies in both directions overlap the kernels (created on first use)
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
@@ -158,6 +161,7 @@ extern "C" int o64_create(o64_handle_t *out, int device) {
     if (!h) return O64_ERR_NOMEM;
     h->device = device;
     h->num_sms = prop.multiProcessorCount;
+    strncpy(h->device_name, prop.name, sizeof(h->device_name) - 1);
     memset(h->pins, 0, sizeof(h->pins));
     if (const char *wb = getenv("O64_WAIT_BUDGET_US")) {
         const long long us = atoll(wb);
@@ -169,6 +173,7 @@ extern "C" int o64_create(o64_handle_t *out, int device) {
     }
     cudaMemset(h->status_word, 0, sizeof(int));
     *out = h;
+    if (const char *cache = getenv("O64_PLAN_CACHE")) (void)o64_plan_load(h, cache);  // a missing file is fine
     return O64_OK;
 }
 
@@ -277,7 +282,7 @@ extern "C" int o64_plan_set(o64_handle_t h, int kind, const o64_plan_t *plan) {
 static void choose(o64_handle_t h, int kind, int epi, int64_t M, int64_t N, int64_t K, o64_plan_t *out) {
     const o64_plan_t *pin = h->has_pin[kind] ? &h->pins[kind] : nullptr;
     if (!pin && !h->tuned.empty()) {
-        auto it = h->tuned.find({kind, epi == EPI_SWIGLU ? 1 : 0, M, N, K});
+        auto it = h->tuned.find({kind, epi == EPI_SWIGLU ? 1 : 0, M, N, K, h->nranks});
         if (it != h->tuned.end()) pin = &it->second;
     }
     plan_choose(kind, epi, M, N, K, h->num_sms, pin, out);
@@ -1092,13 +1097,101 @@ extern "C" int o64_plan_tune(o64_handle_t h, int kind, int swiglu, int64_t M, in
     h->has_pin[kind] = had_pin;
     release();
     if (best_ms == 1e300) return O64_ERR_CUDA;
-    h->tuned[{kind, swiglu ? 1 : 0, M, N, K}] = best_pin;
+    best_pin.predicted_ms = best_ms;
+    h->tuned[{kind, swiglu ? 1 : 0, M, N, K, h->nranks}] = best_pin;
+    if (const char *cache = getenv("O64_PLAN_CACHE")) (void)o64_plan_save(h, cache);
     if (best) {
         plan_choose(kind, epi, M, N, K, h->num_sms, &best_pin, best);
         best->predicted_ms = best_ms;  // measured, not modelled
     }
     return O64_OK;
 }
+
+// ---- measured plans on disk ---------------------------------------------------------------------
+// The reference writes what a phase decided into the file the next phase reads (the WHIRL file,
+// osprey/common/com/ir_bwrite.cxx:1505); the decisions here are the measured plans, one JSON object
+// per (kind, epilogue, M, N, K, ranks) with the kernel shape and the time it was measured at, under the
+// device they were measured on.
+extern "C" int o64_plan_save(o64_handle_t h, const char *path) {
+    if (!h || !path || !*path) return O64_ERR_RANK;
+    std::string tmp = std::string(path) + ".tmp";
+    FILE *f = fopen(tmp.c_str(), "w");
+    if (!f) return O64_ERR_NOMEM;
+    fprintf(f, "{\"version\": 1, \"device\": \"%s\", \"num_sms\": %d,\n \"plans\": [", h->device_name, h->num_sms);
+    bool first = true;
+    for (const auto &kv : h->tuned) {
+        const auto &k = kv.first;
+        const o64_plan_t &p = kv.second;
+        fprintf(f,
+                "%s\n  {\"kind\": %lld, \"swiglu\": %lld, \"M\": %lld, \"N\": %lld, \"K\": %lld, \"gpus\": %lld, "
+                "\"cta_group\": %d, \"tile_m\": %d, \"tile_n\": %d, \"split_k\": %d, \"ms\": %.6f}",
+                first ? "" : ",", (long long)k[0], (long long)k[1], (long long)k[2], (long long)k[3], (long long)k[4],
+                (long long)k[5], p.cta_group, p.tile_m, p.tile_n, p.split_k, p.predicted_ms);
+        first = false;
+    }
+    fprintf(f, "\n ]}\n");
+    if (fclose(f) != 0 || rename(tmp.c_str(), path) != 0) return O64_ERR_NOMEM;
+    return O64_OK;
+}
+
+// Value of "key": <number> inside one JSON object's text; `missing` when the key is absent.
+static double json_number(const std::string &obj, const char *key, double missing) {
+    const std::string pat = std::string("\"") + key + "\"";
+    size_t at = obj.find(pat);
+    if (at == std::string::npos) return missing;
+    at = obj.find(':', at + pat.size());
+    if (at == std::string::npos) return missing;
+    return strtod(obj.c_str() + at + 1, nullptr);
+}
+
+extern "C" int o64_plan_load(o64_handle_t h, const char *path) {
+    if (!h || !path || !*path) return O64_ERR_RANK;
+    FILE *f = fopen(path, "r");
+    if (!f) return O64_ERR_RANK;
+    std::string text;
+    char buf[4096];
+    size_t got;
+    while ((got = fread(buf, 1, sizeof(buf), f)) > 0) text.append(buf, got);
+    fclose(f);
+    // plans measured on another kind of device (or SM count) say nothing about this one
+    const size_t dev_at = text.find("\"device\"");
+    if (dev_at == std::string::npos || text.find(std::string("\"") + h->device_name + "\"", dev_at) == std::string::npos)
+        return O64_ERR_CONFORM;
+    if ((int)json_number(text, "num_sms", -1) != h->num_sms) return O64_ERR_CONFORM;
+    size_t at = text.find("\"plans\"");
+    if (at == std::string::npos) return O64_ERR_DTYPE;
+    int loaded = 0;
+    while ((at = text.find('{', at)) != std::string::npos) {
+        const size_t end = text.find('}', at);
+        if (end == std::string::npos) break;
+        const std::string obj = text.substr(at, end - at + 1);
+        at = end + 1;
+        const int kind = (int)json_number(obj, "kind", -1);
+        const int64_t M = (int64_t)json_number(obj, "M", 0), N = (int64_t)json_number(obj, "N", 0),
+                      K = (int64_t)json_number(obj, "K", 0);
+        if (kind < O64_KIND_BF16 || kind > O64_KIND_S8 || M <= 0 || N <= 0 || K <= 0) continue;
+        o64_plan_t p;
+        memset(&p, 0, sizeof(p));
+        p.cta_group = (int)json_number(obj, "cta_group", 0);
+        p.tile_m = (int)json_number(obj, "tile_m", 0);
+        p.tile_n = (int)json_number(obj, "tile_n", 0);
+        p.split_k = (int)json_number(obj, "split_k", 0);
+        p.predicted_ms = json_number(obj, "ms", 0.0);
+        // the same checks a pin goes through: a damaged file must not select a kernel that does not exist
+        o64_plan_t saved = h->pins[kind];
+        const bool had = h->has_pin[kind];
+        const bool ok = o64_plan_set(h, kind, &p) == O64_OK;
+        h->pins[kind] = saved;
+        h->has_pin[kind] = had;
+        if (!ok) continue;
+        h->tuned[{kind, (int64_t)json_number(obj, "swiglu", 0), M, N, K, (int64_t)json_number(obj, "gpus", 1)}] = p;
+        ++loaded;
+    }
+    return loaded > 0 ? O64_OK : O64_ERR_DTYPE;
+}
+
+// Number of measured plans the handle holds (tuned here or loaded).
+extern "C" int o64_plan_count(o64_handle_t h) { return h ? (int)h->tuned.size() : 0; }
 
 extern "C" int o64_plan_tune_clear(o64_handle_t h) {
     if (!h) return O64_ERR_RANK;
@@ -1129,6 +1222,8 @@ static o64_handle_t compat_handle() {
     }
     return g_compat_handle;
 }
+
+extern "C" o64_handle_t o64_compat_handle(void) { return compat_handle(); }
 
 // Largest element offset touched (plus one) by an extent-(n1,n2) operand with strides (s1,s2).
 static size_t strided_span(int64_t n1, int64_t n2, int64_t s1, int64_t s2) {
@@ -1190,6 +1285,10 @@ static int xgemmx_impl(int M, int N, int K, T alpha, const TA *A, int64_t a1, in
             c.skip_zero_b = skip_zero;
             c.num_sms = h->num_sms;
             c.stream = s;
+            if (h->has_pin[O64_KIND_F32]) {  // pins set on o64_compat_handle()
+                c.pin_tile_m = h->pins[O64_KIND_F32].tile_m;
+                c.pin_tile_n = h->pins[O64_KIND_F32].tile_n;
+            }
             rc = simt_gemm_f32(c);
         }
     } else {

@@ -348,8 +348,10 @@ int simt_gemm_f32(const SimtGemmCall &c) {
         if (tn == 64) return launch_dense<32, 64, 1>(p, c.stream);
         return launch_dense<32, 32, 2>(p, c.stream);
     }
+    // strided operands: 64 x 64 tiles when there are enough of them, else 32 x 32; a pinned tile_m decides
     const long long big_tiles = ((c.M + 63) / 64) * ((c.N + 63) / 64);
-    if (big_tiles >= 2LL * c.num_sms) return launch_simt<64, 64, 16, 4, 4>(p, c.skip_zero_b, c.stream);
+    const bool big = c.pin_tile_m ? c.pin_tile_m == 64 : big_tiles >= 2LL * c.num_sms;
+    if (big) return launch_simt<64, 64, 16, 4, 4>(p, c.skip_zero_b, c.stream);
     return launch_simt<32, 32, 16, 2, 2>(p, c.skip_zero_b, c.stream);
 }
 

@@ -95,6 +95,14 @@ class Engine:
         check(self.lib.o64_plan_tune(self._h, kind, 1 if swiglu else 0, M, N, K, s, ctypes.byref(p)), "o64_plan_tune")
         return p.as_dict()
 
+    def plan_save(self, path):
+        check(self.lib.o64_plan_save(self._h, str(path).encode()), "o64_plan_save")
+
+    def plan_load(self, path):
+        """Merges measured plans from a file; returns how many plans the handle holds afterwards."""
+        check(self.lib.o64_plan_load(self._h, str(path).encode()), "o64_plan_load")
+        return self.lib.o64_plan_count(self._h)
+
     def plan_tune_clear(self):
         check(self.lib.o64_plan_tune_clear(self._h), "o64_plan_tune_clear")
 

@@ -29,6 +29,21 @@
 // become an o64_plan_set call in front of the product (the engine rejects sizes it has no
 // kernel for; the emitted code then falls back to the automatic plan).
 //
+// Tails: besides max(x, 0) the elementwise functions the reference lowers through its exp / tanh
+// intrinsics (osprey/common/com/intrn_entry.def:915,1346): x / (1 + expf(-x)) (SiLU),
+// 0.5 x (1 + tanhf(0.79788456 (x + 0.044715 x^3))) and 0.5 x (1 + erff(0.70710678 x)) (GELU), on
+// x = acc or acc + bias[j], written inline or through one temporary (t = acc + bias[j]; Y = f(t);).
+//
+// Nests the reference has ALREADY tiled are recognised too.  After scalar expansion and distribution the
+// accumulation is a perfect nest around  C[i][j] = C[i][j] + A[i][k] * B[k][j]  (snl_test.cxx:1036-1040);
+// cache blocking (SNL_INV_Cache_Block, osprey/be/lno/snl_inv.cxx:639-887) then puts strip loops
+// `for (it = 0; it <= ub; it = it + B)` outside and rewrites the blocked loop as
+// `for (i = it; i <= _I4MIN(it + (B - 1), ub); i = i + 1)` (snl_inv.cxx:774-805; whirl2c prints OPR_MIN
+// as _I4MIN, osprey/be/whirl2c/wn2c.cxx:658), in any loop order.  Such a nest - any permutation of the
+// three element loops, any subset of them strip-mined - becomes ONE accumulating call of the strided
+// kernel (beta = 1: the zeroing nest in front stays as it is), and the strip sizes it was blocked with
+// are handed on as plan pins of the fp32 kernel (o64_plan_set on o64_compat_handle()).
+//
 //   o64nest input.c [-o output.c]       ("-" or no input: stdin; no -o: stdout)
 //   exit status: 0, also when nothing was recognised (the count goes to stderr); 2 on usage errors
 #include <cctype>
@@ -412,6 +427,115 @@ bool parse_for(const std::vector<Tok> &t, size_t &p, Loop *L) {
     return true;
 }
 
+
+// A DO loop in the shapes whirl2c prints: for (v = lb; v <= ub; v = v + step) with a constant step.
+struct GLoop {
+    std::string var;
+    ExprP lb, ub;
+    bool inclusive = false;
+    long long step = 1;
+    std::vector<std::string> pragmas;
+};
+
+bool const_int(const ExprP &e, long long *v) {
+    if (!e) return false;
+    if (e->kind == Expr::Num && e->text.find_first_of(".eE") == std::string::npos) {
+        *v = atoll(strip_suffix(e->text).c_str());
+        return true;
+    }
+    long long a, b;
+    if (e->kind == Expr::Bin && const_int(e->kids[0], &a) && const_int(e->kids[1], &b)) {
+        if (e->text == "+") *v = a + b;
+        else if (e->text == "-") *v = a - b;
+        else if (e->text == "*") *v = a * b;
+        else return false;
+        return true;
+    }
+    return false;
+}
+
+bool parse_for_general(const std::vector<Tok> &t, size_t &p, GLoop *L) {
+    if (!(t[p].kind == Tok::Id && t[p].text == "for")) return false;
+    Parser ps(t, p + 1);
+    ps.expect("(");
+    if (ps.t[ps.p].kind == Tok::Id && Parser::is_type(ps.t[ps.p].text)) ++ps.p;
+    if (ps.t[ps.p].kind != Tok::Id) return false;
+    L->var = ps.t[ps.p++].text;
+    ps.expect("=");
+    L->lb = ps.ternary();
+    ps.expect(";");
+    ExprP test = ps.ternary();
+    ps.expect(";");
+    if (!ps.ok || !L->lb || !test || test->kind != Expr::Bin || !is_id(test->kids[0], L->var)) return false;
+    if (test->text == "<=") L->inclusive = true;
+    else if (test->text != "<") return false;
+    L->ub = test->kids[1];
+    if (mentions(L->ub, L->var) || mentions(L->lb, L->var)) return false;
+    if (!(ps.t[ps.p].kind == Tok::Id && ps.t[ps.p].text == L->var)) {
+        if (ps.accept("++") && ps.t[ps.p].kind == Tok::Id && ps.t[ps.p].text == L->var) {
+            ++ps.p;
+            L->step = 1;
+        } else {
+            return false;
+        }
+    } else {
+        ++ps.p;
+        if (ps.accept("++")) {
+            L->step = 1;
+        } else if (ps.accept("+=")) {
+            if (!const_int(ps.ternary(), &L->step)) return false;
+        } else if (ps.accept("=")) {
+            ExprP e = ps.ternary();
+            if (!e || e->kind != Expr::Bin || e->text != "+") return false;
+            if (is_id(e->kids[0], L->var) && const_int(e->kids[1], &L->step)) {
+            } else if (is_id(e->kids[1], L->var) && const_int(e->kids[0], &L->step)) {
+            } else {
+                return false;
+            }
+        } else {
+            return false;
+        }
+    }
+    ps.expect(")");
+    if (!ps.ok || L->step < 1) return false;
+    p = ps.p;
+    return true;
+}
+
+// min(a, b) in the spellings it is printed in; false if e is no minimum
+bool split_min(const ExprP &e, ExprP *a, ExprP *b) {
+    if (!e) return false;
+    if (e->kind == Expr::Call && e->kids.size() == 2) {
+        static const char *names[] = {"_I4MIN", "_I8MIN", "_U4MIN", "_U8MIN", "min", "MIN", "_MIN"};
+        for (const char *n : names)
+            if (e->text == n) {
+                *a = e->kids[0];
+                *b = e->kids[1];
+                return true;
+            }
+    }
+    if (e->kind == Expr::Cond && e->kids[0]->kind == Expr::Bin && (e->kids[0]->text == "<" || e->kids[0]->text == "<=") &&
+        same(e->kids[0]->kids[0], e->kids[1]) && same(e->kids[0]->kids[1], e->kids[2])) {
+        *a = e->kids[1];
+        *b = e->kids[2];
+        return true;
+    }
+    return false;
+}
+
+// e == var + c (either order) or var: the constant
+bool var_plus_const(const ExprP &e, const std::string &var, long long *c) {
+    if (is_id(e, var)) {
+        *c = 0;
+        return true;
+    }
+    if (e && e->kind == Expr::Bin && e->text == "+") {
+        if (is_id(e->kids[0], var) && const_int(e->kids[1], c)) return true;
+        if (is_id(e->kids[1], var) && const_int(e->kids[0], c)) return true;
+    }
+    return false;
+}
+
 // One operand of the product: X[r][c] or X[r*LD + c]; on success name, row / column loop
 // variables and the pitch.
 struct Ref {
@@ -493,7 +617,8 @@ struct Nest {
     std::string type;      // element type of C
     std::string bias;      // name of the bias vector (indexed by j), or empty
     bool relu = false;
-    bool tail = false;     // bias or relu present
+    int act = 0;           // 0 none, 1 ReLU, 2 GELU (tanh), 3 GELU (erf), 4 SiLU
+    bool tail = false;     // bias or an activation present
     size_t tok_begin, tok_end;  // tokens [begin, end) to replace (pragmas in front included)
 };
 
@@ -516,6 +641,115 @@ ExprP strip_relu(const ExprP &e, bool *relu) {
             return e->kids[1];
         }
     }
+    return e;
+}
+
+
+// ---- the elementwise tails ---------------------------------------------------------------------
+void flatten_product(const ExprP &e, std::vector<ExprP> *out) {
+    if (e && e->kind == Expr::Bin && e->text == "*") {
+        flatten_product(e->kids[0], out);
+        flatten_product(e->kids[1], out);
+    } else {
+        out->push_back(e);
+    }
+}
+bool num_near(const ExprP &e, double v, double tol) {
+    if (!e || e->kind != Expr::Num) return false;
+    const double x = atof(e->text.c_str());
+    return x > v - tol && x < v + tol;
+}
+bool call_named(const ExprP &e, std::initializer_list<const char *> names, size_t nargs) {
+    if (!e || e->kind != Expr::Call || e->kids.size() != nargs) return false;
+    for (const char *n : names)
+        if (e->text == n) return true;
+    return false;
+}
+// 1 + f  in either order: f
+ExprP one_plus(const ExprP &e) {
+    if (!e || e->kind != Expr::Bin || e->text != "+") return nullptr;
+    if (num_near(e->kids[0], 1.0, 1e-9)) return e->kids[1];
+    if (num_near(e->kids[1], 1.0, 1e-9)) return e->kids[0];
+    return nullptr;
+}
+// x / (1 + exp(-x)): x
+ExprP match_silu(const ExprP &e) {
+    if (!e || e->kind != Expr::Bin || e->text != "/") return nullptr;
+    const ExprP ex = one_plus(e->kids[1]);
+    if (!call_named(ex, {"expf", "exp", "_F4EXP", "__expf"}, 1)) return nullptr;
+    const ExprP &arg = ex->kids[0];
+    if (!arg || arg->kind != Expr::Neg || !same(arg->kids[0], e->kids[0])) return nullptr;
+    return e->kids[0];
+}
+// 0.5 * x * (1 + tanh(c1 * (x + c2 * x * x * x)))  or  0.5 * x * (1 + erf(x * c)): x and which
+ExprP match_gelu(const ExprP &e, int *which) {
+    std::vector<ExprP> f;
+    flatten_product(e, &f);
+    if (f.size() != 3) return nullptr;
+    ExprP half, x, bracket;
+    for (const ExprP &g : f) {
+        if (!half && num_near(g, 0.5, 1e-9)) half = g;
+        else if (!bracket && one_plus(g)) bracket = g;
+        else if (!x) x = g;
+    }
+    if (!half || !x || !bracket) return nullptr;
+    const ExprP fn = one_plus(bracket);
+    if (call_named(fn, {"erff", "erf", "_F4ERF"}, 1)) {
+        std::vector<ExprP> a;
+        flatten_product(fn->kids[0], &a);
+        if (a.size() == 2 && ((same(a[0], x) && num_near(a[1], 0.70710678, 1e-5)) || (same(a[1], x) && num_near(a[0], 0.70710678, 1e-5)))) {
+            *which = 3;
+            return x;
+        }
+        const ExprP &q = fn->kids[0];
+        if (q->kind == Expr::Bin && q->text == "/" && same(q->kids[0], x) && num_near(q->kids[1], 1.41421356, 1e-5)) {
+            *which = 3;
+            return x;
+        }
+        return nullptr;
+    }
+    if (call_named(fn, {"tanhf", "tanh", "_F4TANH"}, 1)) {
+        std::vector<ExprP> a;
+        flatten_product(fn->kids[0], &a);
+        if (a.size() != 2) return nullptr;
+        ExprP sum = num_near(a[0], 0.7978845608, 1e-5) ? a[1] : (num_near(a[1], 0.7978845608, 1e-5) ? a[0] : nullptr);
+        if (!sum || sum->kind != Expr::Bin || sum->text != "+") return nullptr;
+        for (int sw = 0; sw < 2; ++sw) {
+            if (!same(sum->kids[sw], x)) continue;
+            std::vector<ExprP> c;
+            flatten_product(sum->kids[1 - sw], &c);
+            int xs = 0, cs = 0;
+            for (const ExprP &g : c) {
+                if (same(g, x)) ++xs;
+                else if (num_near(g, 0.044715, 1e-6)) ++cs;
+                else return nullptr;
+            }
+            if (xs == 3 && cs == 1) {
+                *which = 2;
+                return x;
+            }
+        }
+    }
+    return nullptr;
+}
+// the activation around x, if any: returns x and sets *act (0 none, 1 ReLU, 2 / 3 GELU, 4 SiLU)
+ExprP strip_activation(const ExprP &e, int *act) {
+    bool relu = false;
+    ExprP v = strip_relu(e, &relu);
+    if (relu) {
+        *act = 1;
+        return v;
+    }
+    if (ExprP x = match_silu(e)) {
+        *act = 4;
+        return x;
+    }
+    int which = 0;
+    if (ExprP x = match_gelu(e, &which)) {
+        *act = which;
+        return x;
+    }
+    *act = 0;
     return e;
 }
 
@@ -584,26 +818,40 @@ bool match_nest(const std::vector<Tok> &t, size_t start, const std::map<std::str
     if (init.lhs->kind == Expr::Id) {  // scalar accumulator: one more statement stores it
         Assign st;
         if (!parse_assign(t, p, &st) || st.plus_equals) return false;
-        out_ref = st.lhs;
-        ExprP v = strip_relu(st.rhs, &n->relu);
-        if (v && v->kind == Expr::Bin && v->text == "+") {
-            for (int s = 0; s < 2; ++s) {
-                const ExprP &x = v->kids[s], &y = v->kids[1 - s];
-                if (same(x, init.lhs) && y->kind == Expr::Index && y->kids[0]->kind == Expr::Id &&
-                    is_id(y->kids[1], vars[1])) {
-                    n->bias = y->kids[0]->text;
-                    v = x;
-                    break;
+        // x = acc or acc + bias[j]; sets n->bias
+        auto pre_activation = [&](ExprP v) {
+            if (v && v->kind == Expr::Bin && v->text == "+") {
+                for (int s = 0; s < 2; ++s) {
+                    const ExprP &x = v->kids[s], &y = v->kids[1 - s];
+                    if (same(x, init.lhs) && y->kind == Expr::Index && y->kids[0]->kind == Expr::Id &&
+                        is_id(y->kids[1], vars[1])) {
+                        n->bias = y->kids[0]->text;
+                        return true;
+                    }
                 }
             }
+            return same(v, init.lhs);
+        };
+        ExprP temp;  // t = acc + bias[j];  in front of  Y = f(t);
+        if (st.lhs->kind == Expr::Id && !same(st.lhs, init.lhs)) {
+            if (!pre_activation(st.rhs)) return false;
+            temp = st.lhs;
+            if (!parse_assign(t, p, &st) || st.plus_equals) return false;
         }
-        if (!same(v, init.lhs)) return false;
+        out_ref = st.lhs;
+        ExprP v = strip_activation(st.rhs, &n->act);
+        n->relu = n->act == 1;
+        if (temp) {
+            if (!same(v, temp)) return false;
+        } else if (!pre_activation(v)) {
+            return false;
+        }
     } else {
         out_ref = init.lhs;  // C[i][j] accumulated in place
     }
     if (!parse_ref(out_ref, vars, decls, &n->c) || !uses(n->c, vars[0], vars[1])) return false;
     if (!close_block(t, p, bj) || !close_block(t, p, bi)) return false;
-    n->tail = n->relu || !n->bias.empty();
+    n->tail = n->act != 0 || !n->bias.empty();
     // element types: all three arrays of one kind
     auto type_of = [&](const std::string &name) {
         auto it = decls.find(name);
@@ -619,6 +867,188 @@ bool match_nest(const std::vector<Tok> &t, size_t start, const std::map<std::str
     if (n->tail && !(n->type == "f32" && plain)) return false;
     n->tok_end = p;
     return true;
+}
+
+
+// ------------------------------------------------------------------------------------------
+// a nest the reference has already tiled: strip loops outside, blocked element loops inside, the
+// accumulation statement as the only statement
+// ------------------------------------------------------------------------------------------
+struct TiledNest {
+    GLoop li, lj, lk;              // the element loops, by role
+    long long bi = 0, bj = 0, bk = 0;  // strip sizes (0: that loop was not blocked)
+    bool j_outer_of_i = false;     // the j strip (or loop) encloses the i one: the reference interchanged
+    Ref a, b, c;
+    std::string type;
+    size_t tok_begin, tok_end;
+};
+
+bool match_tiled(const std::vector<Tok> &t, size_t start, const std::map<std::string, ArrayDecl> &decls, TiledNest *n) {
+    size_t p = start;
+    n->tok_begin = start;
+    std::vector<GLoop> loops;
+    std::vector<bool> braced;
+    while (true) {
+        GLoop L;
+        take_pragmas(t, p, &L.pragmas);
+        if (!parse_for_general(t, p, &L)) break;
+        loops.push_back(L);
+        braced.push_back(open_block(t, p));
+        if (loops.size() > 9) return false;
+    }
+    if (loops.size() < 3) return false;
+    Assign upd;
+    if (!parse_assign(t, p, &upd)) return false;
+    for (size_t i = loops.size(); i-- > 0;)
+        if (!close_block(t, p, braced[i])) return false;
+    // strip loops step by the block size from 0; element loops step by 1
+    std::vector<const GLoop *> strips, elems;
+    for (const GLoop &L : loops) (L.step > 1 ? strips : elems).push_back(&L);
+    if (elems.size() != 3) return false;
+    for (const GLoop *S : strips)
+        if (!is_zero(S->lb)) return false;
+    // the statement: C = C + A * B  |  C = A * B + C  |  C += A * B
+    ExprP prod = upd.rhs;
+    if (!upd.plus_equals) {
+        if (!prod || prod->kind != Expr::Bin || prod->text != "+") return false;
+        if (same(prod->kids[0], upd.lhs)) prod = prod->kids[1];
+        else if (same(prod->kids[1], upd.lhs)) prod = prod->kids[0];
+        else return false;
+    }
+    if (!prod || prod->kind != Expr::Bin || prod->text != "*") return false;
+    const std::vector<std::string> vars = {elems[0]->var, elems[1]->var, elems[2]->var};
+    if (vars[0] == vars[1] || vars[0] == vars[2] || vars[1] == vars[2]) return false;
+    Ref r0, r1, rc;
+    if (!parse_ref(prod->kids[0], vars, decls, &r0) || !parse_ref(prod->kids[1], vars, decls, &r1) ||
+        !parse_ref(upd.lhs, vars, decls, &rc))
+        return false;
+    // roles: C is indexed by (i, j); k is the variable C does not use; A uses (i, k), B uses (k, j)
+    auto has = [](const Ref &r, const std::string &v) { return r.row == v || r.col == v; };
+    std::string vk;
+    for (const std::string &v : vars)
+        if (!has(rc, v)) vk = v;
+    if (vk.empty()) return false;
+    // i is the variable that walks C's rows, j the one that walks its columns
+    const std::string vi = rc.row, vj = rc.col;
+    if (vi == vk || vj == vk || vi == vj) return false;
+    const Ref *ra = nullptr, *rb = nullptr;
+    for (int sw = 0; sw < 2 && !ra; ++sw) {
+        const Ref &x = sw ? r1 : r0, &y = sw ? r0 : r1;
+        if (has(x, vi) && has(x, vk) && has(y, vk) && has(y, vj)) ra = &x, rb = &y;
+    }
+    if (!ra) return false;
+    n->a = *ra, n->b = *rb, n->c = rc;
+    // element loops by role; each is either whole (lb 0, plain bound) or blocked (lb = strip variable,
+    // bound = min(strip + B - 1, ub) or strip + B - 1 when the block divides the extent)
+    size_t order_i = 0, order_j = 0;
+    for (const GLoop *E : elems) {
+        GLoop whole = *E;
+        long long blk = 0;
+        size_t depth = 0;
+        for (size_t d = 0; d < loops.size(); ++d)
+            if (&loops[d] == E) depth = d;
+        if (!is_zero(E->lb)) {
+            if (E->lb->kind != Expr::Id) return false;
+            const GLoop *S = nullptr;
+            for (const GLoop *cand : strips)
+                if (cand->var == E->lb->text) S = cand;
+            if (!S) return false;
+            for (size_t d = 0; d < loops.size(); ++d)
+                if (&loops[d] == S) {
+                    if (d > depth) return false;  // a strip loop encloses its element loop
+                    depth = d;
+                }
+            blk = S->step;
+            ExprP x, y, bound = E->ub;
+            long long c = 0;
+            const long long want = E->inclusive ? blk - 1 : blk;
+            if (split_min(bound, &x, &y)) {
+                ExprP rest;
+                if (var_plus_const(x, S->var, &c) && c == want) rest = y;
+                else if (var_plus_const(y, S->var, &c) && c == want) rest = x;
+                else return false;
+                if (!same(rest, S->ub) || E->inclusive != S->inclusive) return false;  // the strip's own bound
+            } else if (!(var_plus_const(bound, S->var, &c) && c == want)) {
+                return false;
+            }
+            whole.lb = S->lb;
+            whole.ub = S->ub;
+            whole.inclusive = S->inclusive;
+        }
+        if (E->var == vi) n->li = whole, n->bi = blk, order_i = depth;
+        else if (E->var == vj) n->lj = whole, n->bj = blk, order_j = depth;
+        else n->lk = whole, n->bk = blk;
+    }
+    // every strip loop must belong to one of the element loops
+    size_t used = (n->bi ? 1 : 0) + (n->bj ? 1 : 0) + (n->bk ? 1 : 0);
+    if (used != strips.size()) return false;
+    n->j_outer_of_i = order_j < order_i;
+    auto type_of = [&](const std::string &name) {
+        auto it = decls.find(name);
+        return it == decls.end() ? std::string() : it->second.type;
+    };
+    n->type = type_of(n->c.name);
+    if (n->type.empty() || type_of(n->a.name) != n->type || type_of(n->b.name) != n->type) return false;
+    if (n->c.name == n->a.name || n->c.name == n->b.name) return false;
+    // only nests that need this matcher: the plain untiled form with a zeroed accumulator is match_nest's
+    n->tok_end = p;
+    return true;
+}
+
+std::string extent_of(const ExprP &ub, bool inclusive) {
+    long long v;
+    if (const_int(ub, &v)) return std::to_string(inclusive ? v + 1 : v);
+    return inclusive ? "(" + str(ub) + " + 1)" : str(ub);
+}
+
+std::string emit_tiled(const TiledNest &n, const std::string &indent) {
+    const std::string M = extent_of(n.li.ub, n.li.inclusive), N = extent_of(n.lj.ub, n.lj.inclusive),
+                      K = extent_of(n.lk.ub, n.lk.inclusive);
+    std::ostringstream o;
+    const std::string in2 = indent + "    ";
+    const char *fn = n.type == "f32" ? "_s4gemmx__" : n.type == "f64" ? "_sgemmx__" : n.type == "i32" ? "_i4gemmx__" : "_jgemmx__";
+    const char *ct = n.type == "f32" ? "float" : n.type == "f64" ? "double" : n.type == "i32" ? "int32_t" : "int64_t";
+    auto base = [](const Ref &r) { return "&" + str(r.whole->kids[0]->kind == Expr::Index ? r.whole->kids[0]->kids[0] : r.whole->kids[0]) +
+                                          (r.whole->kids[0]->kind == Expr::Index ? "[0][0]" : "[0]"); };
+    auto incs = [&](const Ref &r, const std::string &rowvar, std::string *i1, std::string *i2) {
+        if (r.row == rowvar) {
+            *i1 = r.ld;
+            *i2 = "1";
+        } else {
+            *i1 = "1";
+            *i2 = r.ld;
+        }
+    };
+    std::string a1, a2, b1, b2, c1, c2;
+    incs(n.a, n.li.var, &a1, &a2);
+    incs(n.b, n.lk.var, &b1, &b2);
+    incs(n.c, n.li.var, &c1, &c2);
+    o << "{\n";
+    o << in2 << "/* o64nest: " << n.c.name << "(" << M << " x " << N << ") += " << n.a.name << " * " << n.b.name << " over " << K
+      << "; the nest was blocked " << (n.bi ? std::to_string(n.bi) : std::string("-")) << " x "
+      << (n.bj ? std::to_string(n.bj) : std::string("-")) << " x " << (n.bk ? std::to_string(n.bk) : std::string("-"))
+      << " (i x j x k" << (n.j_outer_of_i ? ", j outside i" : "") << ") */\n";
+    const bool pinned = n.type == "f32" && (n.bi || n.bj || n.bk || n.j_outer_of_i);
+    if (pinned) {
+        // the strip sizes of the cache blocking become the tile of the fp32 kernel where it has one of that size
+        o << in2 << "o64_plan_t o64_plan;\n" << in2 << "memset(&o64_plan, 0, sizeof(o64_plan));\n";
+        if (n.bi) o << in2 << "o64_plan.tile_m = " << n.bi << ";\n";
+        if (n.bj) o << in2 << "o64_plan.tile_n = " << n.bj << ";\n";
+        if (n.bk) o << in2 << "o64_plan.tile_k = " << n.bk << ";\n";
+        if (n.j_outer_of_i) o << in2 << "o64_plan.raster = 1;\n";
+        o << in2 << "if (o64_plan_set(o64_compat_handle(), O64_KIND_F32, &o64_plan) != O64_OK)\n"
+          << in2 << "    o64_plan_set(o64_compat_handle(), O64_KIND_F32, NULL);  /* no kernel of that size: automatic plan */\n";
+    }
+    o << in2 << "const int o64_m = " << M << ", o64_n = " << N << ", o64_k = " << K << ";\n";
+    o << in2 << "const int o64_a1 = " << a1 << ", o64_a2 = " << a2 << ", o64_b1 = " << b1 << ", o64_b2 = " << b2
+      << ", o64_c1 = " << c1 << ", o64_c2 = " << c2 << ";\n";
+    o << in2 << "const " << ct << " o64_one = 1;  /* beta = 1: the nest accumulates into " << n.c.name << " */\n";
+    o << in2 << fn << "(&o64_m, &o64_n, &o64_k, &o64_one, (const " << ct << " *)" << base(n.a) << ", &o64_a1, &o64_a2, (const "
+      << ct << " *)" << base(n.b) << ", &o64_b1, &o64_b2, &o64_one, (" << ct << " *)" << base(n.c) << ", &o64_c1, &o64_c2);\n";
+    o << in2 << "o64nest_check(o64_compat_last_status(), \"" << fn << "\");\n";
+    if (pinned) o << in2 << "o64_plan_set(o64_compat_handle(), O64_KIND_F32, NULL);\n";
+    o << indent << "}";
+    return o.str();
 }
 
 std::string extent(const Loop &L) {
@@ -656,7 +1086,8 @@ std::string emit(const Nest &n, const std::string &indent) {
     const std::string in2 = indent + "    ";
     o << "{\n";
     o << in2 << "/* o64nest: " << n.c.name << "(" << M << " x " << N << ") = " << n.a.name << " * " << n.b.name
-      << " over " << K << (n.bias.empty() ? "" : " + " + n.bias) << (n.relu ? ", max(., 0)" : "") << " */\n";
+      << " over " << K << (n.bias.empty() ? "" : " + " + n.bias)
+      << (n.act == 1 ? ", max(., 0)" : n.act == 2 ? ", GELU (tanh)" : n.act == 3 ? ", GELU (erf)" : n.act == 4 ? ", SiLU" : "") << " */\n";
     // plan pins from the loops' pragmas
     long long tile_m = 0, tile_n = 0, tile_k = 0, group = 0, raster = 0;
     std::string ignored;
@@ -687,6 +1118,7 @@ std::string emit(const Nest &n, const std::string &indent) {
                        n.c.row == n.li.var && n.c.col == n.lj.var;
     auto base = [](const Ref &r) { return "&" + str(r.whole->kids[0]->kind == Expr::Index ? r.whole->kids[0]->kids[0] : r.whole->kids[0]) +
                                           (r.whole->kids[0]->kind == Expr::Index ? "[0][0]" : "[0]"); };
+    static const char *act_names[] = {"O64_ACT_NONE", "O64_ACT_RELU", "O64_ACT_GELU_TANH", "O64_ACT_GELU_ERF", "O64_ACT_SILU"};
     if (n.type == "f32" && plain) {
         const bool pinned = tile_m || tile_n || tile_k || group || raster;
         if (pinned) {
@@ -701,7 +1133,7 @@ std::string emit(const Nest &n, const std::string &indent) {
         }
         o << in2 << "o64nest_check(o64_linear_f32(o64nest_handle(), " << M << ", " << N << ", " << K << ", " << base(n.a)
           << ", " << n.a.ld << ", " << base(n.b) << ", " << n.b.ld << ", " << (n.bias.empty() ? "NULL" : n.bias) << ", "
-          << base(n.c) << ", " << n.c.ld << ", " << (n.relu ? "O64_ACT_RELU" : "O64_ACT_NONE") << ", NULL), \"o64_linear_f32\");\n";
+          << base(n.c) << ", " << n.c.ld << ", " << act_names[n.act] << ", NULL), \"o64_linear_f32\");\n";
         if (pinned) o << in2 << "o64_plan_set(o64nest_handle(), O64_KIND_F32, NULL);\n";
     } else {
         // the strided kernels of the runtime: element (r, c) of X at X[inc1*r + inc2*c]
@@ -786,6 +1218,24 @@ int main(int argc, char **argv) {
     for (size_t p = 0; p < toks.size();) {
         const bool starts = toks[p].kind == Tok::Pragma || (toks[p].kind == Tok::Id && toks[p].text == "for");
         Nest n;
+        TiledNest tn;
+        if (starts && !match_nest(toks, p, decls, &n) && match_tiled(toks, p, decls, &tn)) {
+            const size_t b = toks[tn.tok_begin].begin, e = toks[tn.tok_end - 1].end;
+            size_t first_for = tn.tok_begin;
+            while (toks[first_for].kind == Tok::Pragma) ++first_for;
+            const size_t fb = toks[first_for].begin;
+            size_t line = src.rfind('\n', fb);
+            line = line == std::string::npos ? 0 : line + 1;
+            std::string indent = src.substr(line, fb - line);
+            if (indent.find_first_not_of(" \t") != std::string::npos) indent.clear();
+            out += src.substr(copied, b - copied);
+            if (first_for != tn.tok_begin) out += indent;
+            out += emit_tiled(tn, indent);
+            copied = e;
+            p = tn.tok_end;
+            ++found;
+            continue;
+        }
         if (starts && match_nest(toks, p, decls, &n)) {
             const size_t b = toks[n.tok_begin].begin, e = toks[n.tok_end - 1].end;
             size_t first_for = n.tok_begin;

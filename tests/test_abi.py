@@ -13,7 +13,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def header_functions():
     text = open(os.path.join(ROOT, "include", "o64gemm.h")).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    names = re.findall(r"^\s*(?:const\s+)?(?:int|void|size_t|char|float|double|int32_t|int64_t|o64_complex8_t|o64_complex16_t)"
+    names = re.findall(r"^\s*(?:const\s+)?(?:int|void|size_t|char|float|double|int32_t|int64_t|o64_complex8_t|o64_complex16_t|o64_handle_t)"
                        r"\s*\*?\s*(\w+)\s*\(", text, flags=re.M)
     return sorted(set(names))
 

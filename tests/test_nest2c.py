@@ -82,3 +82,58 @@ def test_whirl2c_spellings(built):
     # x > 0 ? x : 0 is the same tail
     out2, n2 = rewrite(text.replace("_MAX(acc + bias[j], 0.0F)", "(acc + bias[j]) > 0.0F ? (acc + bias[j]) : 0.0F"))
     assert n2 == 1 and "O64_ACT_RELU" in out2
+
+
+TILED = os.path.join(ROOT, "tests", "nests", "tiled.c")
+
+
+def test_nests_the_reference_has_already_tiled(built, tmp_path):
+    """Strip loops + blocked loops with min() bounds, in any order, become one accumulating call of the
+    strided kernel; the strip sizes travel as plan pins; GELU / SiLU tails fuse into the linear."""
+    out, n = rewrite(open(TILED).read())
+    assert n == 8
+    assert "blocked 64 x - x 16 (i x j x k)" in out
+    assert "blocked 100 x 32 x 64 (i x j x k, j outside i)" in out and "o64_plan.raster = 1;" in out
+    assert "blocked - x - x 40" in out
+    assert "o64_plan.tile_m = 64;" in out and "o64_plan.tile_k = 16;" in out
+    assert "o64_plan_set(o64_compat_handle(), O64_KIND_F32, &o64_plan)" in out
+    # beta = 1, whole extents recovered from the strip loops' bounds
+    assert out.count("&o64_one, (float *)&C") == 3 and "o64_m = 300, o64_n = 260, o64_k = 200" in out
+    assert "_sgemmx__(&o64_m, &o64_n, &o64_k, &o64_one" in out and "o64_m = 90, o64_n = 50, o64_k = 70" in out
+    assert "_i4gemmx__(" in out and "o64_m = 40, o64_n = 56, o64_k = 24" in out
+    # the zeroing nests in front stay
+    assert out.count("C1[i][j] = 0.0F;") == 1 and "C3[i][j] = 0;" in out
+    for act in ("O64_ACT_SILU", "O64_ACT_GELU_TANH", "O64_ACT_GELU_ERF"):
+        assert out.count(act + ", NULL)") == 1
+    assert "&A[0][0], 200, &B[0][0], 260, bias, &G1[0][0], 260, O64_ACT_SILU" in out
+    # the nest whose blocked loop overruns its strip is not a tiling of a product: untouched
+    assert "for (int i = it; i < it + 64; i++)" in out
+    path = tmp_path / "tiled_out.c"
+    path.write_text(out)
+    r = subprocess.run(["gcc", "-fsyntax-only", "-Werror=implicit-function-declaration", "-I", os.path.join(ROOT, "include"),
+                        str(path)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+
+
+@pytest.mark.parametrize("text", [
+    # the blocked loop's bound is not strip + block - 1
+    "float A[8][8],B[8][8],C[8][8];\nvoid f(){for(int t=0;t<8;t+=4)for(int i=t;i<t+2;i++)for(int j=0;j<8;j++)for(int k=0;k<8;k++)C[i][j]+=A[i][k]*B[k][j];}",
+    # the minimum is taken against another bound than the strip loop's
+    "float A[8][8],B[8][8],C[8][8];\nvoid f(){for(int t=0;t<8;t+=4)for(int i=t;i<(t+4<6?t+4:6);i++)for(int j=0;j<8;j++)for(int k=0;k<8;k++)C[i][j]+=A[i][k]*B[k][j];}",
+    # a second statement in the innermost body
+    "float A[8][8],B[8][8],C[8][8];\nvoid f(){for(int i=0;i<8;i++)for(int j=0;j<8;j++)for(int k=0;k<8;k++){C[i][j]+=A[i][k]*B[k][j];A[i][k]=0;}}",
+    # an activation the engine does not have
+    "float A[8][8],B[8][8],C[8][8];\nvoid f(){for(int i=0;i<8;i++)for(int j=0;j<8;j++){float s=0;for(int k=0;k<8;k++)s+=A[i][k]*B[k][j];C[i][j]=tanhf(s);}}",
+])
+def test_near_misses_of_the_tiled_form_pass_through(built, text):
+    out, n = rewrite(text)
+    assert n == 0 and out == text
+
+
+def test_a_loop_around_a_product_nest_stays(built):
+    """A stepping loop whose variable no inner loop starts from is no strip loop: it stays, and the
+    accumulating nest inside it is replaced (and so runs once per iteration, as before)."""
+    text = ("float A[8][8],B[8][8],C[8][8];\nvoid f(){for(int t=0;t<8;t+=4)for(int i=0;i<8;i++)for(int j=0;j<8;j++)"
+            "for(int k=0;k<8;k++)C[i][j]+=A[i][k]*B[k][j];}")
+    out, n = rewrite(text)
+    assert n == 1 and "for(int t=0;t<8;t+=4){" in out and "_s4gemmx__(" in out

@@ -1,5 +1,5 @@
 """Builds libo64gemm.so in-tree with nvcc for sm_100a (cross-compiles without a GPU) and the
-host-only source rewriter o64nest with g++.
+host-only tools o64nest (source rewriter) and o64whirl (WHIRL dump matcher) with g++.
 
 Usage:  python -m open64_b200.build [--force] [--verbose] [--tuning]
 
@@ -18,6 +18,8 @@ OUT = os.path.join(HERE, "libo64gemm.so")
 OBJ_DIR = os.path.join(HERE, "build")
 NEST_SRC = os.path.join(HERE, "nest2c", "nest2c.cpp")
 NEST_OUT = os.path.join(HERE, "nest2c", "o64nest")
+WHIRL_SRC = os.path.join(HERE, "whirl", "o64whirl.cpp")
+WHIRL_OUT = os.path.join(HERE, "whirl", "o64whirl")
 
 SOURCES = ["api.cu", "umma_gemm.cu", "umma_gemm_2cta.cu", "umma_gemm_wide.cu", "umma_gemm_skinny.cu", "simt_kernels.cu", "simt_generic.cu", "plan.cpp", "no_alloc.cu", "dotprod.cu"]
 HEADERS = ["ptx_sm100.cuh", "umma_gemm.cuh", "umma_common.cuh", "simt_kernels.cuh", "../../include/o64gemm.h"]
@@ -85,6 +87,10 @@ def build(force=False, verbose=False, tuning=False):
             raise RuntimeError("g++ failed on o64nest:\n" + r.stdout + r.stderr)
         if verbose:
             sys.stderr.write(r.stderr)
+    if os.path.exists(WHIRL_SRC) and (force or _stale(WHIRL_OUT, [WHIRL_SRC])):
+        r = subprocess.run(["g++", "-O2", "-std=c++17", "-Wall", "-o", WHIRL_OUT, WHIRL_SRC], capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("g++ failed on o64whirl:\n" + r.stdout + r.stderr)
     return OUT
 
 

@@ -356,6 +356,14 @@ def run_only(args, eng, o, torch, dev, timer, emit):
         c5 = torch.empty((16384, 1024), dtype=torch.int32, device=dev)
         t = timer.steps(lambda: eng.gemm_s8(A5, B5, out=c5), steps, warm)
         emit({"config": "c5_int8_slab_16384x1024x8192", "ms": t, "tops": 2 * 16384 * 1024 * 8192 / (t * 1e-3) / 1e12})
+    elif args.only == "m768":
+        # 768 x 8192 x 8192 bf16: 96 tiles of 256 x 256 on 74 CTA pairs - the shape whose last wave is cut along K
+        A, B = o.workloads.c2_gemm_bf16(768, 8192, 8192)
+        Ad, Bd = A.to(dev), B.to(dev)
+        C = torch.empty((768, 8192), dtype=torch.bfloat16, device=dev)
+        t = timer.steps(lambda: eng.gemm_bf16(Ad, Bd, transB=True, out=C), steps, warm)
+        emit({"config": "bf16_768x8192x8192", "us": t * 1e3, "tflops": 2 * 768 * 8192 * 8192 / (t * 1e-3) / 1e12,
+              "last_wave_split": eng.last_tail_split()})
     elif args.only == "midm":
         emit({"config": "mid_m_bf16_Mx8192x8192", "results": mid_m_points(eng, o, torch, dev, timer, steps)})
     else:
@@ -380,7 +388,7 @@ def main():
     ap.add_argument("--impl", default="o64", choices=["o64", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary configurations")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--only", default=None, choices=["c1", "c2", "c3", "c4", "c5", "c5slab", "skinny", "midm"],
+    ap.add_argument("--only", default=None, choices=["c1", "c2", "c3", "c4", "c5", "c5slab", "skinny", "midm", "m768"],
                     help="run just one configuration (few launches; for profiling) and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

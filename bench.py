@@ -640,6 +640,30 @@ def main():
                     "unit": "TOP/s", "frac": tl / t_gemm, "of": "torch._int_mm (cuBLASLt) measured in this run"}
             except Exception as e:  # noqa: BLE001
                 ex["c5_int8_sharded_gemm_only"]["library_context_torch_int_mm"] = {"unavailable": repr(e)[:200]}
+        if world == 1:
+            # the same product with the requantising tail a quantised layer needs: int8 result from
+            # act(acc * sA[m] * sB[n] + bias[n]); bit-exact against the oracle on sampled rows
+            g5 = torch.Generator().manual_seed(o.workloads.SEEDS["c5"] + 7)
+            sA5 = (torch.rand(M5, generator=g5) * 4e-3 + 2e-3)   # results of a few tens: some saturate at 127
+            sB5 = (torch.rand(N5, generator=g5) * 2e-2 + 1e-2)
+            bq5 = (torch.rand(N5, generator=g5) - 0.5) * 20.0
+            sA5d, sB5d, bq5d = sA5.to(dev), sB5.to(dev), bq5.to(dev)
+            q5 = torch.empty((M5, N5), dtype=torch.int8, device=dev)
+            run_q = lambda: eng.gemm_s8_scaled(A5d, B5d, sA5d, sB5d, bq5d, act="relu", out_kind=o.OUT_S8, out=q5)
+            run_q()
+            rq = sample_rows(M5, 4, 5)
+            ref_q = oracle.gemm_s8_scaled(A5[rq].numpy(), B5.numpy(), sA5[rq].numpy(), sB5.numpy(), bq5.numpy(),
+                                          oracle.ACT_RELU, out_kind=1)
+            got_q = q5[rq.to(dev)].cpu().numpy()
+            if not np.array_equal(got_q, ref_q):
+                raise SystemExit("C5 requantised result differs from the oracle")
+            t_q = timer.steps(run_q, s2, w2)
+            ex["c5_int8_requant_relu_s8out"] = {
+                "ms": t_q, "tops": f5 / (t_q * 1e-3) / 1e12, "parity": "exact",
+                "algorithmic_bytes": M5 * K5 + N5 * K5 + M5 * N5 + (M5 + 2 * N5) * 4,
+                "nonzero_outputs_frac": float((got_q != 0).mean()),
+                "ms_int32_out_same_shape": t_gemm}
+            del q5
         if world > 1:
             from open64_b200 import sharded
             recv_bytes = (world - 1) * M5 * ns5 * 4        # what every rank receives when C is reassembled

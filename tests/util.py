@@ -3,7 +3,9 @@ import numpy as np
 import torch
 
 TOL_F32 = 1e-4    # max|y - ref| / max|ref|, fp32 fused linear
-TOL_LOWP = 2e-2   # max|y - ref| / max|ref|, bf16 / fp8 results against the fp32 nest
+import os
+
+TOL_LOWP = float(os.environ.get("O64_TOL_LOWP", 2e-2))   # max|y - ref| / max|ref|, bf16 / fp8 results against the fp32 nest
 
 
 def relmax(y, ref):

@@ -117,6 +117,27 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+def bind_host_thread_near_gpu(index):
+    """Before any pinned host buffer is allocated: restrict this process to the CPUs NVML names as local
+    to the GPU (those of them the process may use), so that first-touch places the staging buffers
+    of the host-operand leg in that socket's memory.  Returns a short description for the JSON line."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        allowed = os.sched_getaffinity(0)
+        words = (max(allowed) // 64) + 1
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+        near = {64 * w + b for w, m in enumerate(mask) for b in range(64) if (m >> b) & 1}
+        use = near & allowed
+        if not use or use == allowed:
+            return f"unchanged ({len(allowed)} CPUs allowed, {len(near & allowed)} of them local to the GPU)"
+        os.sched_setaffinity(0, use)
+        return f"{len(use)} of {len(allowed)} allowed CPUs (those local to GPU {index})"
+    except Exception as e:  # noqa: BLE001
+        return "unchanged (" + repr(e)[:80] + ")"
+
+
 def cpu_baseline(budget_s=12.0, rows=128):
     """The oracle's bf16 nest on a [rows, K] x [N, K]^T slab of the headline GEMM, repeated until
     `budget_s` of CPU time has gone; returns TFLOP/s and what was run."""
@@ -408,6 +429,7 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a B200: no CUDA device is visible (there is no CPU fallback)")
+    host_binding = bind_host_thread_near_gpu(local_rank) if world > 1 else None
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
@@ -500,6 +522,7 @@ def main():
            "h2d_bytes_per_step": (M * K + N * K) * 2, "d2h_bytes_per_step": M * N * 2,
            "ms_per_step": e2e_ms, "steps": e2e_steps}
     if world > 1:
+        e2e["host_cpus"] = host_binding
         e2e["note"] = (f"{world} ranks stage {(M * K + N * K + M * N) * 2 >> 20} MiB each through ONE host's memory and "
                        "PCIe root complexes at the same time; per-rank time grows with the ranks")
     err_e2e = rel_to_max(C_host[rows].float().numpy(), ref_rows)
@@ -699,6 +722,15 @@ def main():
             eng.gemm_s8_sharded(A5d, B5d, N5, gather=o.GATHER_PUSH, out=c5p)   # and once more after the timed calls
             verify_int8_result(torch, A5d, B5, c5p, "C5 fused push (row-major), after timing", rank, oracle_rows=False)
             record("fused_push_rowmajor", t, par)
+            # row blocks of the product, sent by the copy engines as they finish
+            c5p.fill_(-1)
+            eng.gemm_s8_sharded(A5d, B5d, N5, gather=o.GATHER_COPY, out=c5p)
+            par = verify_int8_result(torch, A5d, B5, c5p, "C5 row blocks + copy engines (row-major)", rank)
+            t = timer.steps(lambda: eng.gemm_s8_sharded(A5d, B5d, N5, gather=o.GATHER_COPY, out=c5p), s2, w2)
+            c5p.fill_(-1)
+            eng.gemm_s8_sharded(A5d, B5d, N5, gather=o.GATHER_COPY, out=c5p)
+            verify_int8_result(torch, A5d, B5, c5p, "C5 row blocks + copy engines, after timing", rank, oracle_rows=False)
+            record("copy_engine_rowmajor", t, par)
             # the same GEMM unsharded on one GPU, in the same run (every rank runs it on its own GPU)
             B5full = B5.to(dev)
             t_one = timer.steps(lambda: eng.gemm_s8(A5d, B5full, out=c5), s2, w2)

@@ -55,6 +55,19 @@ struct UmmaParams {
     // (peer-mapped device pointers to the same element as C); 0 peers = plain GEMM
     int n_peers;
     void *peer_c[7];
+    // ... and the rank barriers of that exchange, done by the kernel itself: a block of counters in every
+    // rank's memory (xchg_local here, xchg_peer[d] the same block of the rank behind peer_c[d]):
+    //   [j]      entry arrivals of rank j: rank j's stream has reached this call, so nothing of it reads
+    //            the previous result any more           (first remote store waits for all of them)
+    //   [8 + j]  exit arrivals of rank j: all of rank j's stores of this call have been performed
+    //            (the kernel does not end before all of them are in)
+    //   [16]     calls completed here      [17] CTAs of the running call that have finished storing
+    // Counters only grow (compared as signed differences), so a launch replayed from a CUDA graph
+    // needs no new parameter.  NULL = the caller orders the ranks itself.
+    unsigned *xchg_local;
+    unsigned *xchg_peer[7];
+    int xchg_rank;
+    int xchg_peer_rank[7];
     // the kernel for few rows of A (umma_gemm_skinny.cu): rows in the TMA box of A, stages of its
     // ring, K slices per tile (= CTAs per cluster)
     int sk_a_rows, sk_stages, sk_split;
@@ -287,6 +300,79 @@ __device__ __forceinline__ void tail_release(unsigned *flag, unsigned consumers)
     if ((threadIdx.x & 31) == 0) {
         if (atomicAdd(flag, 1u) == consumers) atomicExch(flag, 0u);
     }
+}
+
+// ---- rank barriers of the fused exchange (see UmmaParams::xchg_local) ------------------------------
+constexpr int kWaitXchgEntry = 0x501;
+constexpr int kWaitXchgExit = 0x502;
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *ptr) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_release_sys_add(unsigned *ptr, unsigned v) {
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+}
+
+// One thread: waits (bounded) until every peer's counter at `base` has reached `target`.
+static __device__ __noinline__ bool xchg_wait_all(const UmmaParams &p, int base, unsigned target, volatile int *abort_flag,
+                                              int code) {
+    uint64_t t0 = 0;
+    uint32_t probes = 0;
+    for (int d = 0; d < p.n_peers; ++d) {
+        const unsigned *w = p.xchg_local + base + p.xchg_peer_rank[d];
+        while ((int)(ld_acquire_sys(w) - target) < 0) {
+            if ((++probes & 15u) == 0) {
+                if (*abort_flag) return false;
+                const uint64_t now = globaltimer_ns();
+                if (t0 == 0) {
+                    t0 = now;
+                } else if (now - t0 > p.wait_ns) {
+                    atomicCAS(p.status, 0, code | (p.xchg_peer_rank[d] << 12));
+                    *abort_flag = 1;
+                    return false;
+                }
+            }
+            __nanosleep(100);
+        }
+    }
+    return true;
+}
+
+// Kernel start, one thread of the whole grid: tells every peer that this rank has reached the call.
+static __device__ __noinline__ void xchg_announce_entry(const UmmaParams &p) {
+    for (int d = 0; d < p.n_peers; ++d) red_release_sys_add(p.xchg_peer[d] + p.xchg_rank, 1u);
+}
+
+// Epilogue warp, before its first store of the call (whole-warp call): all ranks have arrived.
+static __device__ __noinline__ bool xchg_wait_entry(const UmmaParams &p, volatile int *abort_flag) {
+    bool ok = true;
+    if ((threadIdx.x & 31) == 0) {
+        // [16] is written only by the last CTA of a call, after every CTA has passed this point
+        const unsigned call = p.xchg_local[kXchgCalls] + 1u;
+        ok = xchg_wait_all(p, 0, call, abort_flag, kWaitXchgEntry);
+    }
+    return __shfl_sync(0xffffffffu, ok, 0);
+}
+
+// Every thread that stored to a peer, after its last store.
+__device__ __forceinline__ void xchg_stores_done() { __threadfence_system(); }
+
+// Teardown, one thread per CTA, after a CTA-wide barrier behind the epilogue: the last CTA of the grid
+// tells the peers that this rank's stores are complete and waits for theirs.
+static __device__ __noinline__ void xchg_finish(const UmmaParams &p, volatile int *abort_flag) {
+    __threadfence();
+    const unsigned done = atomicAdd(p.xchg_local + kXchgCtasDone, 1u);
+    if (done != gridDim.x - 1) return;
+    __threadfence();
+    p.xchg_local[kXchgCtasDone] = 0;
+    const unsigned call = p.xchg_local[kXchgCalls] + 1u;
+    __threadfence_system();
+    for (int d = 0; d < p.n_peers; ++d) red_release_sys_add(p.xchg_peer[d] + kXchgExit + p.xchg_rank, 1u);
+    (void)xchg_wait_all(p, kXchgExit, call, abort_flag, kWaitXchgExit);
+    p.xchg_local[kXchgCalls] = call;
+    __threadfence();
 }
 
 // What an owner adds to its accumulator before the epilogue: the same unit of every contributor.

@@ -51,7 +51,7 @@ struct SmemLayout {
 template <int KIND, bool B_KN, int EPI, int BLOCK_N, int STAGES, bool HOOK = false>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                 const __grid_constant__ CUtensorMap tm_b2, const UmmaParams p) {
+                 const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ UmmaParams p) {
     using L = SmemLayout<BLOCK_N, STAGES>;
     constexpr int kElem = (KIND == MMA_F16) ? 2 : 1;
     constexpr int kBlockK = kRowBytes / kElem;  // K elements per stage
@@ -102,6 +102,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr_smem;
+    if (p.xchg_local && blockIdx.x == 0 && threadIdx.x == 0) xchg_announce_entry(p);
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------------
@@ -245,6 +246,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const int quarter = warp & 3;  // TMEM lane quarter this warp may read
         int it = 0;
         bool ok = true;
+        if (p.xchg_local) ok = xchg_wait_entry(p, abort_flag);  // no remote store before every rank is here
         for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++it) {
             int mb, nb;
             tile_coords(w / p.split_k, p, mb, nb);
@@ -273,11 +275,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty_bar(buf));
         }
+        if (p.xchg_local) xchg_stores_done();
     }
 
     // ------------------------------ teardown --------------------------------------------
     tc_fence_before();
     __syncthreads();
+    if (p.xchg_local && threadIdx.x == 0) xchg_finish(p, abort_flag);
     if (warp == 1) {
         if (*abort_flag) {
             // a wait ran out: give copies and MMAs still in flight time to land before the
@@ -446,6 +450,12 @@ int umma_launch(const UmmaCall &c) {
     p.tail_slot_bytes = (long long)c.tail_bytes;  // capacity until a launcher has planned the split
     p.n_peers = c.n_peers;
     for (int i = 0; i < 7; ++i) p.peer_c[i] = c.peer_c[i];
+    p.xchg_local = c.n_peers > 0 ? c.xchg_local : nullptr;
+    p.xchg_rank = c.xchg_rank;
+    for (int i = 0; i < 7; ++i) {
+        p.xchg_peer[i] = c.xchg_peer[i];
+        p.xchg_peer_rank[i] = c.xchg_peer_rank[i];
+    }
     if (c.n_peers > 0 && !p.vec_ok) return O64_ERR_ALIGN;  // the fused exchange uses the vector-store path only
     p.sk_a_rows = 0;
     p.sk_stages = 0;

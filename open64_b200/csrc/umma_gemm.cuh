@@ -55,6 +55,11 @@ struct UmmaCall {
     void *partial = nullptr;   // split-K: zeroed fp32 [M,N] workspace (fp32-accumulating kinds)
     int n_peers = 0;           // fused all-gather: peer copies of C (same element as C), at most 7
     void *peer_c[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    // ... with the rank barriers done by the kernel (UmmaParams::xchg_local); NULL = the caller's business
+    unsigned *xchg_local = nullptr;
+    unsigned *xchg_peer[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    int xchg_rank = 0;
+    int xchg_peer_rank[7] = {0, 0, 0, 0, 0, 0, 0};
     bool may_allocate = true;  // false: never allocate (the pipeline trace, which needs a buffer, stays off)
     unsigned long long wait_ns = 0;  // budget of the kernels' bounded waits; 0 = kDefaultWaitNs
     // CTA-pair kernels, K split of the last wave's tiles: slot memory (tail_bytes) and flag words
@@ -64,6 +69,9 @@ struct UmmaCall {
     size_t tail_bytes = 0;
     int test_withhold = -1;          // o64_test_* only: K block whose loads the producer leaves out
 };
+
+// Layout of the fused exchange's counter block (UmmaParams::xchg_local), in 32-bit words.
+constexpr int kXchgExit = 8, kXchgCalls = 16, kXchgCtasDone = 17, kXchgWords = 32;
 
 // Validates alignment, encodes the tensor maps and launches.  Returns O64_OK or an error code.
 int umma_launch(const UmmaCall &call);

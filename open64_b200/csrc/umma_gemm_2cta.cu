@@ -50,7 +50,7 @@ struct PairSmemLayout {
 template <int KIND, bool B_KN, int EPI, int BLOCK_N, int STAGES, bool HOOK = false, bool TAIL = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                      const __grid_constant__ CUtensorMap tm_b2, const UmmaParams p) {
+                      const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ UmmaParams p) {
     using L = PairSmemLayout<BLOCK_N, STAGES>;
     constexpr int kElem = (KIND == MMA_F16) ? 2 : 1;
     constexpr int kBlockK = kRowBytes / kElem;
@@ -112,6 +112,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         atomicCAS(p.status, 0, kPairTmemMismatch | (int)((tmem_base & 0xfffu) << 12) | (int)(rank << 24));
         *abort_flag = 1;
     }
+    if (p.xchg_local && blockIdx.x == 0 && threadIdx.x == 0) xchg_announce_entry(p);
 
     if (warp == 0) {
         // ------------------------------ TMA producer (both ranks) ---------------------------
@@ -255,6 +256,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         WorkItem w;
         long long clk_store = 0, clk_flags = 0, clk_fix = 0, clk_accwait = 0;  // O64_TRACE=pipe
         const long long t_begin = clock64();
+        if (p.xchg_local) ok = xchg_wait_entry(p, abort_flag);  // no remote store before every rank is here
         for (; ok && work_item<TAIL>(p, pair_id, num_pairs, it, w); ++it) {
             int mb, nb;
             tile_coords(w.tile, p, mb, nb);
@@ -299,6 +301,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty_bar(buf), 0));
         }
+        if (p.xchg_local) xchg_stores_done();
         if (O64_DBG(p) && warp == 2 && lane == 0) {
             O64_DBG(p)[blockIdx.x * 8 + 4] = clk_fix;                 // epilogues (owned tiles)
             O64_DBG(p)[blockIdx.x * 8 + 5] = clk_flags;               // waiting for contributors
@@ -312,6 +315,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     __syncthreads();
     cluster_sync_all();  // neither CTA leaves (or frees tensor memory) while its partner may
                          // still read its shared memory or signal its barriers
+    if (p.xchg_local && threadIdx.x == 0) xchg_finish(p, abort_flag);
     if (warp == 1) {
         if (*abort_flag) {
             const uint64_t t0 = globaltimer_ns();

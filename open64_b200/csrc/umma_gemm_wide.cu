@@ -64,7 +64,7 @@ struct WideSmem {
 template <int KIND, bool B_KN, int EPI, bool HOOK = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kWideThreads, 1)
 umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                      const __grid_constant__ CUtensorMap tm_b2, const UmmaParams p) {
+                      const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ UmmaParams p) {
     using L = WideSmem;
     constexpr int STAGES = kWideStages;
     constexpr int BLOCK_N = kWideBlockN;
@@ -126,6 +126,7 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         atomicCAS(p.status, 0, kWideTmemMismatch);
         *abort_flag = 1;
     }
+    if (p.xchg_local && blockIdx.x == 0 && threadIdx.x == 0) xchg_announce_entry(p);
 
     if (warp == 0) {
         // ------------------------------ TMA producer (both ranks) ---------------------------
@@ -294,6 +295,7 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         bool ok = true;
         long long epi_clk = 0;
         WorkItem w;
+        if (p.xchg_local) ok = xchg_wait_entry(p, abort_flag);  // no remote store before every rank is here
         for (; ok && work_item<false>(p, pair_id, num_pairs, it, w); ++it) {
             int mb, nb;
             tile_coords(w.tile, p, mb, nb);
@@ -319,6 +321,7 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                 if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty_bar(g), 0));
             }
         }
+        if (p.xchg_local) xchg_stores_done();
         if (O64_DBG(p) && warp == 2 && lane == 0) O64_DBG(p)[blockIdx.x * 8 + 4] = epi_clk;
     }
 
@@ -326,6 +329,7 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     tc_fence_before();
     __syncthreads();
     cluster_sync_all();
+    if (p.xchg_local && threadIdx.x == 0) xchg_finish(p, abort_flag);
     if (warp == 1) {
         if (*abort_flag) {
             const uint64_t t0 = globaltimer_ns();

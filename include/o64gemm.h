@@ -195,6 +195,14 @@ int o64_gemm_fp8_scaled(o64_handle_t h, int64_t M, int64_t N, int64_t K, const v
                         const float *scaleB, const float *bias, void *C, int64_t ldc,
                         void *stream);
 
+/* The same e4m3 product with the weight stored [K,N] row-major (N contiguous, ldb >= N; device
+ * memory).  The weight is transposed into handle-owned scratch on the caller's stream first (one
+ * extra pass over N*K bytes per call); a weight that stays the same is better transposed once by
+ * the caller and given to o64_gemm_fp8_scaled_ex. */
+int o64_gemm_fp8_scaled_kn(o64_handle_t h, int64_t M, int64_t N, int64_t K, const void *A8, int64_t lda,
+                           const void *B8_kn, int64_t ldb, const float *scaleA, const float *scaleB,
+                           const float *bias, int act, void *C, int64_t ldc, int out_kind, void *stream);
+
 /* The scaled products with a fused activation and a choice of result type ("requantisation"):
  *   C = convert( act( acc * (scaleA[m] * scaleB[n]) + bias[n] ) )
  * acc: the fp32 (e4m3 operands) or int32 (int8 operands, converted to fp32) accumulator; every fp32

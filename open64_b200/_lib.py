@@ -23,7 +23,7 @@ STATIC_SCRATCH_BYTES = 16 << 20
 EXPORTS = [
     "o64_create", "o64_destroy", "o64_last_status", "o64_set_wait_budget_us", "o64_test_gemm_bf16_withheld", "o64_test_last_tail_split", "o64_test_force_tail_split", "o64_status_string", "o64_version",
     "o64_plan_get", "o64_plan_set", "o64_plan_model", "o64_plan_tune", "o64_plan_tune_clear", "o64_plan_save", "o64_plan_load", "o64_plan_count", "o64_linear_f32", "o64_gemm_bf16", "o64_gemm_bf16_swiglu",
-    "o64_gemm_fp8_scaled", "o64_gemm_fp8_scaled_ex", "o64_gemm_s8_scaled", "o64_gemm_s8s8_s32", "o64_gemm_s8s8_s32_static", "o64_naive_gemm", "o64_comm_unique_id",
+    "o64_gemm_fp8_scaled", "o64_gemm_fp8_scaled_ex", "o64_gemm_fp8_scaled_kn", "o64_gemm_s8_scaled", "o64_gemm_s8s8_s32", "o64_gemm_s8s8_s32_static", "o64_naive_gemm", "o64_comm_unique_id",
     "o64_comm_init", "o64_comm_destroy", "o64_comm_alloc_result", "o64_gemm_s8_sharded_workspace", "o64_gemm_s8_sharded", "o64_gemm_bf16_sharded",
     "sgemm_", "_s4gemmx__", "_s4gemvx__", "_MATMUL_S4S4", "o64_compat_last_status", "o64_compat_handle",
     "dgemm_", "_sgemmx__", "_sgemvx__", "_MATMUL_SS",
@@ -166,6 +166,7 @@ def lib():
     L.o64_gemm_fp8_scaled.argtypes = [vp, i64, i64, i64, vp, i64, vp, i64, vp, vp, vp, vp, i64, vp]
     L.o64_gemm_s8s8_s32.argtypes = [vp, i64, i64, i64, vp, i64, vp, i64, vp, i64, vp]
     L.o64_gemm_fp8_scaled_ex.argtypes = [vp, i64, i64, i64, vp, i64, vp, i64, vp, vp, vp, ci, vp, i64, ci, vp]
+    L.o64_gemm_fp8_scaled_kn.argtypes = [vp, i64, i64, i64, vp, i64, vp, i64, vp, vp, vp, ci, vp, i64, ci, vp]
     L.o64_gemm_s8_scaled.argtypes = [vp, i64, i64, i64, vp, i64, vp, i64, vp, vp, vp, ci, vp, i64, ci, vp]
     L.o64_gemm_s8s8_s32_static.argtypes = [i64, i64, i64, vp, i64, vp, i64, vp, i64, vp]
     L.o64_naive_gemm.argtypes = [vp, ci, i64, i64, i64, vp, i64, vp, i64, ci, vp, vp, vp, ci, vp,

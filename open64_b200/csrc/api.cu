@@ -70,7 +70,7 @@ static NcclApi &nccl() {
 }
 
 // ---- handle ---------------------------------------------------------------------------------
-static const int kSlots = 9;  // 0-5 host staging, 6-8 repacked operands (A, B, B2)
+static const int kSlots = 10;  // 0-5 host staging, 6-8 repacked operands (A, B, B2), 9 a transposed 8-bit weight
 static const int kMaxBlocks = 32;       // row blocks of a pipelined host-operand call
 static const int64_t kBlockRows = 1024;  // at least this many rows per block
 
@@ -741,6 +741,31 @@ extern "C" int o64_gemm_fp8_scaled_ex(o64_handle_t h, int64_t M, int64_t N, int6
     if (out_kind != O64_OUT_BF16 && out_kind != O64_OUT_E4M3) return O64_ERR_DTYPE;
     return umma_entry(h, O64_KIND_FP8, false, out_kind == O64_OUT_E4M3 ? EPI_SCALED_E4M3 : EPI_SCALED_BF16, M, N, K, A8,
                       lda, B8, nullptr, ldb, C, ldc, bias, scaleA, scaleB, act, stream);
+}
+
+// The e4m3 product with the weight stored [K,N] (N contiguous).  The tensor-core path of this library
+// reads 8-bit operands with K contiguous, so the weight is transposed once per call into scratch the
+// handle owns (one extra pass over N*K bytes, on the caller's stream) and the [N,K] kernels run on that.
+// A caller whose weight does not change between calls transposes it once itself and uses
+// o64_gemm_fp8_scaled_ex.
+extern "C" int o64_gemm_fp8_scaled_kn(o64_handle_t h, int64_t M, int64_t N, int64_t K, const void *A8, int64_t lda,
+                                      const void *B8_kn, int64_t ldb, const float *scaleA, const float *scaleB,
+                                      const float *bias, int act, void *C, int64_t ldc, int out_kind, void *stream) {
+    if (!h || M < 0 || N < 0 || K < 0) return O64_ERR_RANK;
+    if (out_kind != O64_OUT_BF16 && out_kind != O64_OUT_E4M3) return O64_ERR_DTYPE;
+    if (K == 0 || N == 0 || M == 0)
+        return o64_gemm_fp8_scaled_ex(h, M, N, K, A8, lda, B8_kn, K, scaleA, scaleB, bias, act, C, ldc, out_kind, stream);
+    if (!B8_kn) return O64_ERR_RANK;
+    if (ldb < N) return O64_ERR_CONFORM;
+    if (is_host_ptr(B8_kn)) return O64_ERR_RANK;  // a host weight: transpose it on the host, or copy it over first
+    if (!on_handles_device(h, {B8_kn})) return O64_ERR_RANK;
+    DeviceGuard g(h->device);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int64_t ld_t = (K + 15) / 16 * 16;
+    int rc = reserve(&h->stage[9], &h->stage_cap[9], (size_t)N * ld_t);
+    if (rc) return rc;
+    if ((rc = transpose_bytes(B8_kn, ldb, h->stage[9], ld_t, K, N, s))) return rc;
+    return o64_gemm_fp8_scaled_ex(h, M, N, K, A8, lda, h->stage[9], ld_t, scaleA, scaleB, bias, act, C, ldc, out_kind, stream);
 }
 
 extern "C" int o64_gemm_s8_scaled(o64_handle_t h, int64_t M, int64_t N, int64_t K, const int8_t *A, int64_t lda,

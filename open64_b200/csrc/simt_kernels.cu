@@ -608,6 +608,38 @@ __global__ void permute_slabs_kernel(const int32_t *__restrict__ src, int32_t *_
     }
 }
 
+// dst[c][r] = src[r][c] for one-byte elements: 64 x 64 tiles through shared memory, so that both the
+// loads (along c) and the stores (along r) are contiguous; the padding column keeps the transposed
+// reads free of bank conflicts.
+__global__ void transpose_bytes_kernel(const uint8_t *__restrict__ src, long long ld_src, uint8_t *__restrict__ dst,
+                                       long long ld_dst, long long rows, long long cols) {
+    __shared__ uint8_t tile[64][64 + 4];
+    const long long tiles_c = (cols + 63) / 64, tiles_r = (rows + 63) / 64;
+    for (long long t = blockIdx.x; t < tiles_c * tiles_r; t += gridDim.x) {
+        const long long r0 = (t / tiles_c) * 64, c0 = (t % tiles_c) * 64;
+        for (int i = threadIdx.x; i < 64 * 64; i += blockDim.x) {
+            const int r = i >> 6, c = i & 63;
+            tile[r][c] = (r0 + r < rows && c0 + c < cols) ? src[(r0 + r) * ld_src + c0 + c] : (uint8_t)0;
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < 64 * 64; i += blockDim.x) {
+            const int c = i >> 6, r = i & 63;
+            if (c0 + c < cols && r0 + r < rows) dst[(c0 + c) * ld_dst + r0 + r] = tile[r][c];
+        }
+        __syncthreads();
+    }
+}
+
+int transpose_bytes(const void *src, int64_t ld_src, void *dst, int64_t ld_dst, int64_t rows, int64_t cols,
+                    cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return O64_OK;
+    long long tiles = ((rows + 63) / 64) * ((cols + 63) / 64);
+    if (tiles > 148LL * 8) tiles = 148LL * 8;
+    transpose_bytes_kernel<<<(unsigned)tiles, 256, 0, stream>>>(static_cast<const uint8_t *>(src), ld_src,
+                                                               static_cast<uint8_t *>(dst), ld_dst, rows, cols);
+    return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
+}
+
 int permute_slabs_s32(const int32_t *src, int32_t *dst, int64_t M, int64_t ncols, int nslabs,
                       int64_t ld_dst, cudaStream_t stream) {
     if (M <= 0 || ncols <= 0 || nslabs <= 0) return O64_OK;

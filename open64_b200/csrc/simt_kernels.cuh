@@ -99,6 +99,10 @@ int logical_gemmx(int64_t M, int64_t N, int64_t K, int alpha, const TA *A, int64
 // Fills a buffer with pseudo-random finite values of the kind (bf16 / e4m3 / int8): operands for timing runs.
 int fill_pattern(void *p, size_t bytes, int kind, cudaStream_t stream);
 
+// dst[c][r] = src[r][c], one-byte elements, leading dimensions in elements.
+int transpose_bytes(const void *src, int64_t ld_src, void *dst, int64_t ld_dst, int64_t rows, int64_t cols,
+                    cudaStream_t stream);
+
 // dst[m][r*ncols + j] = src[r][m][j] for r < nslabs (int32 elements).
 int permute_slabs_s32(const int32_t *src, int32_t *dst, int64_t M, int64_t ncols, int nslabs,
                       int64_t ld_dst, cudaStream_t stream);

@@ -222,6 +222,20 @@ class Engine:
                                               out.stride(0), out_kind, _stream(A8)), "o64_gemm_fp8_scaled_ex")
         return out
 
+    def gemm_fp8_scaled_kn(self, A8, B8_kn, scaleA=None, scaleB=None, bias=None, act="none", out_kind=_lib.OUT_BF16, out=None):
+        """gemm_fp8_scaled_ex with the weight stored [K,N] (N contiguous); transposed into scratch per call."""
+        M, K = A8.shape
+        N = B8_kn.shape[1]
+        if B8_kn.shape[0] != K:
+            raise O64Error(_lib.ERR_CONFORM, "gemm_fp8_scaled_kn")
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.float8_e4m3fn if out_kind == _lib.OUT_E4M3 else torch.bfloat16,
+                              device=A8.device)
+        check(self.lib.o64_gemm_fp8_scaled_kn(self._h, M, N, K, _ptr(A8), A8.stride(0), _ptr(B8_kn), B8_kn.stride(0),
+                                              _ptr(scaleA), _ptr(scaleB), _ptr(bias), _act(act), _ptr(out),
+                                              out.stride(0), out_kind, _stream(A8)), "o64_gemm_fp8_scaled_kn")
+        return out
+
     def gemm_s8_scaled(self, A, B, scaleA=None, scaleB=None, bias=None, act="none", out_kind=_lib.OUT_BF16, out=None):
         """convert(act(float(A @ B^T) * sA[m] * sB[n] + bias[n])), int8 operands: bf16, or int8 again
         (saturating, nearest even)."""

@@ -118,3 +118,25 @@ def test_host_operands_and_errors(eng):
     with pytest.raises(o.O64Error) as e:
         eng.gemm_s8_scaled(A, B, sA, sB, bias, "relu", o.OUT_E4M3, out=out)
     assert e.value.status == o.ERR_DTYPE
+
+
+@pytest.mark.parametrize("shape", [(300, 1000, 1100), (64, 130, 70), (1, 16, 16)])
+def test_fp8_weight_stored_k_by_n(eng, shape):
+    """The [K,N] entry point gives bit for bit what the [N,K] entry point gives on the transposed
+    weight (the same kernels run on a transposed copy), also with a padded leading dimension."""
+    dev = torch.device("cuda", eng.device)
+    M, N, K = shape
+    A8, W8, sA, sB, b = o.workloads.c4_fp8(M, N, K)
+    a8, w8 = A8.to(dev), W8.to(dev)
+    want = eng.gemm_fp8_scaled_ex(a8, w8, sA.to(dev), sB.to(dev), b.to(dev), "silu", o.OUT_BF16)
+    w_kn = w8.view(torch.uint8).t().contiguous().view(torch.float8_e4m3fn)          # [K, N]
+    got = eng.gemm_fp8_scaled_kn(a8, w_kn, sA.to(dev), sB.to(dev), b.to(dev), "silu", o.OUT_BF16)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    ref = oracle.gemm_fp8_scaled_ex(bits8(A8), bits8(W8), sA.numpy(), sB.numpy(), b.numpy(), ACTS["silu"], 0)
+    assert relmax(got.float().cpu().numpy(), ref) <= 4e-3
+    wide = torch.zeros((K, N + 24), dtype=torch.uint8, device=dev)
+    wide[:, :N] = w_kn.view(torch.uint8)
+    got2 = eng.gemm_fp8_scaled_kn(a8, wide.view(torch.float8_e4m3fn)[:, :N], sA.to(dev), sB.to(dev), b.to(dev), "silu", o.OUT_BF16)
+    assert torch.equal(got2.view(torch.int16), want.view(torch.int16))
+    with pytest.raises(o.O64Error):
+        eng.gemm_fp8_scaled_kn(a8, w_kn.cpu(), sA.to(dev), sB.to(dev), b.to(dev))

@@ -722,15 +722,6 @@ def main():
             eng.gemm_s8_sharded(A5d, B5d, N5, gather=o.GATHER_PUSH, out=c5p)   # and once more after the timed calls
             verify_int8_result(torch, A5d, B5, c5p, "C5 fused push (row-major), after timing", rank, oracle_rows=False)
             record("fused_push_rowmajor", t, par)
-            # row blocks of the product, sent by the copy engines as they finish
-            c5p.fill_(-1)
-            eng.gemm_s8_sharded(A5d, B5d, N5, gather=o.GATHER_COPY, out=c5p)
-            par = verify_int8_result(torch, A5d, B5, c5p, "C5 row blocks + copy engines (row-major)", rank)
-            t = timer.steps(lambda: eng.gemm_s8_sharded(A5d, B5d, N5, gather=o.GATHER_COPY, out=c5p), s2, w2)
-            c5p.fill_(-1)
-            eng.gemm_s8_sharded(A5d, B5d, N5, gather=o.GATHER_COPY, out=c5p)
-            verify_int8_result(torch, A5d, B5, c5p, "C5 row blocks + copy engines, after timing", rank, oracle_rows=False)
-            record("copy_engine_rowmajor", t, par)
             # the same GEMM unsharded on one GPU, in the same run (every rank runs it on its own GPU)
             B5full = B5.to(dev)
             t_one = timer.steps(lambda: eng.gemm_s8(A5d, B5full, out=c5), s2, w2)

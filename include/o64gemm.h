@@ -282,18 +282,12 @@ enum {
     O64_GATHER_NONE = 0,      /* write only this rank's slab into C_full[:, r*N/g ...] */
     O64_GATHER_ROWMAJOR = 1,  /* all-gather, then permute into row-major C_full [M,N] */
     O64_GATHER_SLABS = 2,     /* all-gather only: C_full is [g][M][N/g] (slab-major) */
-    O64_GATHER_PUSH = 3,      /* fused: the GEMM kernel stores each finished tile into every rank's
+    O64_GATHER_PUSH = 3       /* fused: the GEMM kernel stores each finished tile into every rank's
                                  row-major C_full over NVLink peer memory and exchanges arrival
                                  counters with its peers itself: one launch, no separate collective.
                                  C_full must come from o64_comm_alloc_result; N/g a multiple of 32 */
-    O64_GATHER_COPY = 4       /* the product runs in row blocks; as each block finishes, the copy
-                                 engines send its columns into every rank's row-major C_full
-                                 (strided peer copies on side streams, one per peer) while the next
-                                 block is multiplied.  Same result buffer and same ordering
-                                 guarantees as O64_GATHER_PUSH; the copy engines move bytes a
-                                 little faster than stores issued by the SMs. */
 };
-/* Ordering of O64_GATHER_PUSH / O64_GATHER_COPY: work queued on `stream` before the call on ANY
+/* Ordering of O64_GATHER_PUSH: work queued on `stream` before the call on ANY
  * rank is complete before the first byte lands in that rank's C_full, and when the call's work
  * on `stream` is complete every rank's columns are in this rank's C_full.  All waits are bounded
  * by the handle's wait budget; after O64_ERR_TIMEOUT from such a call (a rank that never made
@@ -314,9 +308,8 @@ int o64_gemm_s8_sharded(o64_handle_t h, int64_t M, int64_t N, int64_t K, const i
 /* The same column-sharded linear for bf16 (C = act(A * B^T + bias), fp32 accumulate, bf16 result):
  * A [M,K] replicated, B_slab [N/g,K] local, bias (epilogue->bias, or NULL) the full vector of N
  * values on every rank.  gather: O64_GATHER_NONE (this rank's columns of the row-major C_full),
- * O64_GATHER_SLABS (slab-major [g][M][N/g], NCCL all-gather in place), O64_GATHER_PUSH (fused,
- * row-major on every rank; C_full from o64_comm_alloc_result; N/g a multiple of 64) or
- * O64_GATHER_COPY (row blocks + copy engines, same buffer). */
+ * O64_GATHER_SLABS (slab-major [g][M][N/g], NCCL all-gather in place) or O64_GATHER_PUSH (fused,
+ * row-major on every rank; C_full from o64_comm_alloc_result; N/g a multiple of 64). */
 int o64_gemm_bf16_sharded(o64_handle_t h, int64_t M, int64_t N, int64_t K, const void *A, int64_t lda,
                           const void *B_slab, int64_t ldb, void *C_full, int gather,
                           const o64_epilogue_t *epilogue, void *stream);

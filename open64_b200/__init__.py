@@ -6,7 +6,7 @@ Build the library first:  python -m open64_b200.build
 """
 from ._lib import (ACT_GELU_ERF, ACT_GELU_TANH, ACT_NONE, ACT_RELU, ACT_SILU, ERR_ALIGN,  # noqa: F401
                    ERR_CONFORM, ERR_CUDA, ERR_DTYPE, ERR_NCCL, ERR_NOMEM, ERR_RANK, ERR_TIMEOUT,
-                   EXPORTS, GATHER_COPY, GATHER_NONE, GATHER_PUSH, GATHER_ROWMAJOR, GATHER_SLABS, KIND_BF16, KIND_F32, KIND_FP8,
+                   EXPORTS, GATHER_NONE, GATHER_PUSH, GATHER_ROWMAJOR, GATHER_SLABS, KIND_BF16, KIND_F32, KIND_FP8,
                    KIND_S8, LIB_PATH, OK, OUT_BF16, OUT_E4M3, OUT_S8, O64Error, Plan, lib)
 from .engine import Engine  # noqa: F401
 from . import workloads  # noqa: F401

@@ -14,7 +14,7 @@ OK = 0
 ERR_RANK, ERR_CONFORM, ERR_NOMEM, ERR_ALIGN, ERR_DTYPE, ERR_TIMEOUT, ERR_CUDA, ERR_NCCL = range(-1, -9, -1)
 ACT_NONE, ACT_RELU, ACT_GELU_TANH, ACT_GELU_ERF, ACT_SILU = range(5)
 KIND_F32, KIND_BF16, KIND_FP8, KIND_S8 = range(4)
-GATHER_NONE, GATHER_ROWMAJOR, GATHER_SLABS, GATHER_PUSH, GATHER_COPY = range(5)
+GATHER_NONE, GATHER_ROWMAJOR, GATHER_SLABS, GATHER_PUSH = range(4)
 OUT_BF16, OUT_S8, OUT_E4M3 = range(3)
 UNIQUE_ID_BYTES = 128
 STATIC_SCRATCH_BYTES = 16 << 20

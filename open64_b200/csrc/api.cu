@@ -99,13 +99,9 @@ struct o64_handle_s {
     // rank holds peer-mapped pointers to the others')
     void *sym_local = nullptr;
     void *sym_peer[8] = {nullptr};  // indexed by rank; [rank] == sym_local
-    int peer_device[8] = {0};       // the device (as this process numbers them) behind sym_peer[i]
     size_t sym_bytes = 0;
     size_t sym_flags_offset = 0;    // the exchange's counters (kXchgWords words, zeroed) sit behind the result
     bool push_nccl_barriers = false;  // O64_PUSH_NCCL_BARRIER=1: order the ranks with two tiny all-reduces instead
-    // O64_GATHER_COPY: one side stream per peer and the events that tie them to the caller's stream
-    cudaStream_t xs[7] = {nullptr};
-    cudaEvent_t ev_block[8] = {nullptr}, ev_sent[7] = {nullptr};
     int *barrier_word = nullptr;    // one int, reduced over the ranks as a stream-ordered barrier
     unsigned long long wait_ns = 0;  // budget of the kernels' bounded waits; 0 = the default (two seconds)
     // CTA-pair kernels: slots and flags for the K split of a last, partly filled wave of tiles
@@ -194,16 +190,6 @@ static void free_symmetric(o64_handle_t h) {
     h->sym_bytes = 0;
     if (h->barrier_word) cudaFree(h->barrier_word);
     h->barrier_word = nullptr;
-    for (int i = 0; i < 7; ++i) {
-        if (h->xs[i]) cudaStreamDestroy(h->xs[i]);
-        if (h->ev_sent[i]) cudaEventDestroy(h->ev_sent[i]);
-        h->xs[i] = nullptr;
-        h->ev_sent[i] = nullptr;
-    }
-    for (int i = 0; i < 8; ++i) {
-        if (h->ev_block[i]) cudaEventDestroy(h->ev_block[i]);
-        h->ev_block[i] = nullptr;
-    }
     (void)cudaGetLastError();
 }
 
@@ -882,7 +868,6 @@ extern "C" int o64_comm_alloc_result(o64_handle_t h, size_t bytes, void **local)
     }
     h->sym_bytes = bytes;
     h->sym_peer[h->rank] = h->sym_local;
-    h->peer_device[h->rank] = h->device;
     if (g > 1) {
         // exchange the inter-process handles of the allocations with an all-gather of 64-byte records
         cudaIpcMemHandle_t mine;
@@ -916,8 +901,6 @@ extern "C" int o64_comm_alloc_result(o64_handle_t h, size_t bytes, void **local)
                 free_symmetric(h);
                 return O64_ERR_CUDA;
             }
-            cudaPointerAttributes pa;
-            h->peer_device[i] = (cudaPointerGetAttributes(&pa, h->sym_peer[i]) == cudaSuccess) ? pa.device : h->device;
         }
     }
     *local = h->sym_local;
@@ -998,156 +981,13 @@ static int push_gemm(o64_handle_t h, int kind, int epi, int64_t M, int64_t N, in
     return O64_OK;
 }
 
-// ---- O64_GATHER_COPY: row blocks of the product, sent by the copy engines as they finish ---------
-// The rank barriers use the same counters as the fused kernel (umma_common.cuh, UmmaParams::xchg_local),
-// from three tiny kernels; every wait is bounded by the handle's budget and ends in the status word.
-namespace {
-__device__ __forceinline__ unsigned xc_ld_acquire_sys(const unsigned *ptr) {
-    unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
-    return v;
-}
-__device__ __forceinline__ void xc_red_release_sys(unsigned *ptr) {
-    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ptr) : "memory");
-}
-__device__ __forceinline__ unsigned long long xc_now_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-struct XchgPeers {
-    unsigned *word[7];
-    int n;
-};
-// adds 1 to one word in each peer's block: "this rank has reached the call" / "this rank's bytes are in"
-__global__ void xchg_signal_kernel(XchgPeers peers) {
-    __threadfence_system();
-    for (int d = 0; d < peers.n; ++d) xc_red_release_sys(peers.word[d]);
-}
-// waits until the words [first, first + count) of this rank's block have reached this call's number
-// (calls completed + 1); the rank's own word is skipped; set_calls: the call is complete afterwards
-__global__ void xchg_wait_kernel(unsigned *local, int first, int count, int skip, int set_calls, int *status,
-                                 unsigned long long budget_ns, int code) {
-    const unsigned call = local[kXchgCalls] + 1u;
-    const unsigned long long t0 = xc_now_ns();
-    for (int j = first; j < first + count; ++j) {
-        if (j == skip) continue;
-        while ((int)(xc_ld_acquire_sys(local + j) - call) < 0) {
-            if (xc_now_ns() - t0 > budget_ns) {
-                atomicCAS(status, 0, code | ((j & 7) << 12));
-                j = first + count;
-                break;
-            }
-            __nanosleep(200);
-        }
-    }
-    if (set_calls) {
-        local[kXchgCalls] = call;
-        __threadfence();
-    }
-}
-}  // namespace
-
-static int copy_gemm(o64_handle_t h, int kind, int epi, int64_t M, int64_t N, int64_t K, const void *A, int64_t lda,
-                     const void *B_slab, int64_t ldb, void *C_full, int out_elem, const float *bias, int act,
-                     cudaStream_t s) {
-    const int g = h->nranks, r = h->rank;
-    const int64_t ns = N / g;
-    const int elem = (kind == O64_KIND_BF16) ? 2 : 1;
-    if (C_full != h->sym_local || (size_t)M * N * out_elem > h->sym_bytes) return O64_ERR_RANK;
-    if ((ns * out_elem) % 16) return O64_ERR_CONFORM;
-    if (is_host_ptr(A) || is_host_ptr(B_slab) || (bias && is_host_ptr(bias))) return O64_ERR_RANK;
-    int rc;
-    const void *dA = A, *dB = B_slab;
-    int64_t lda_eff = lda, ldb_eff = ldb;
-    if ((rc = repack_if_unaligned(h, 6, &dA, &lda_eff, M, K, elem, s))) return rc;
-    if ((rc = repack_if_unaligned(h, 7, &dB, &ldb_eff, ns, K, elem, s))) return rc;
-    // row blocks: whole 512-row tiles, at most four (each copy costs a few microseconds to start)
-    int blocks = (int)std::min<int64_t>(4, std::max<int64_t>(1, M / 2048));
-    const int64_t rows = ((M + blocks - 1) / blocks + 511) / 512 * 512;
-    blocks = (int)((M + rows - 1) / rows);
-    for (int i = 0; i < g - 1; ++i) {
-        if (!h->xs[i] && cudaStreamCreateWithFlags(&h->xs[i], cudaStreamNonBlocking) != cudaSuccess) return O64_ERR_CUDA;
-        if (!h->ev_sent[i] && cudaEventCreateWithFlags(&h->ev_sent[i], cudaEventDisableTiming) != cudaSuccess) return O64_ERR_CUDA;
-    }
-    for (int i = 0; i < blocks; ++i)
-        if (!h->ev_block[i] && cudaEventCreateWithFlags(&h->ev_block[i], cudaEventDisableTiming) != cudaSuccess) return O64_ERR_CUDA;
-    unsigned *xl = reinterpret_cast<unsigned *>(static_cast<uint8_t *>(h->sym_local) + h->sym_flags_offset);
-    auto peer_block = [&](int rank_i) { return reinterpret_cast<unsigned *>(static_cast<uint8_t *>(h->sym_peer[rank_i]) + h->sym_flags_offset); };
-    const unsigned long long budget = h->wait_ns ? h->wait_ns : kDefaultWaitNs;
-    if (g > 1) {
-        // this rank's stream has reached the call: nothing of it reads the previous result any more
-        XchgPeers e;
-        e.n = 0;
-        for (int k = 1; k < g; ++k) e.word[e.n++] = peer_block((r + k) % g) + r;
-        xchg_signal_kernel<<<1, 1, 0, s>>>(e);
-    }
-    for (int b = 0; b < blocks; ++b) {
-        const int64_t m0 = b * rows, mb = std::min<int64_t>(rows, M - m0);
-        UmmaCall c;
-        c.kind = kind;
-        c.b_kn = false;
-        c.epi = epi;
-        c.M = mb; c.N = ns; c.K = K;
-        c.A = static_cast<const uint8_t *>(dA) + (size_t)m0 * lda_eff * elem; c.lda = lda_eff;
-        c.B = dB; c.B2 = nullptr; c.ldb = ldb_eff;
-        c.C = static_cast<uint8_t *>(C_full) + ((size_t)m0 * N + (size_t)r * ns) * out_elem; c.ldc = N;
-        c.bias = bias ? bias + (int64_t)r * ns : nullptr;
-        c.scale_a = nullptr; c.scale_b = nullptr;
-        c.act = act;
-        o64_plan_t pin;
-        memset(&pin, 0, sizeof(pin));
-        if (h->has_pin[kind]) pin = h->pins[kind];
-        if (pin.split_k <= 0) pin.split_k = 1;
-        plan_choose(kind, epi, mb, ns, K, h->num_sms, &pin, &c.plan);
-        c.status_word = h->status_word;
-        c.stream = s;
-        c.wait_ns = h->wait_ns;
-        attach_tail(h, &c);
-        if ((rc = umma_launch(c))) return rc;
-        if (g > 1 && cudaEventRecord(h->ev_block[b], s) != cudaSuccess) return O64_ERR_CUDA;
-    }
-    if (g == 1) return O64_OK;
-    for (int k = 1; k < g; ++k) {
-        const int i = (r + k) % g;  // ring order: at any moment the ranks send to different targets
-        cudaStream_t x = h->xs[k - 1];
-        for (int b = 0; b < blocks; ++b) {
-            const int64_t m0 = b * rows, mb = std::min<int64_t>(rows, M - m0);
-            if (cudaStreamWaitEvent(x, h->ev_block[b], 0) != cudaSuccess) return O64_ERR_CUDA;
-            // the target rank has reached the call too (its consumers of the previous result are done)
-            if (b == 0) xchg_wait_kernel<<<1, 1, 0, x>>>(xl, i, 1, -1, 0, h->status_word, budget, 0x511);
-            const size_t off = ((size_t)m0 * N + (size_t)r * ns) * out_elem;
-            cudaMemcpy3DPeerParms cp;
-            memset(&cp, 0, sizeof(cp));
-            cp.srcDevice = h->device;
-            cp.dstDevice = h->peer_device[i];
-            cp.srcPtr = make_cudaPitchedPtr(static_cast<uint8_t *>(C_full) + off, (size_t)N * out_elem, (size_t)ns * out_elem, (size_t)mb);
-            cp.dstPtr = make_cudaPitchedPtr(static_cast<uint8_t *>(h->sym_peer[i]) + off, (size_t)N * out_elem, (size_t)ns * out_elem, (size_t)mb);
-            cp.extent = make_cudaExtent((size_t)ns * out_elem, (size_t)mb, 1);
-            if (cudaMemcpy3DPeerAsync(&cp, x) != cudaSuccess) {
-                (void)cudaGetLastError();
-                return O64_ERR_CUDA;
-            }
-        }
-        XchgPeers e;  // this rank's columns are in rank i's result
-        e.n = 1;
-        e.word[0] = peer_block(i) + kXchgExit + r;
-        xchg_signal_kernel<<<1, 1, 0, x>>>(e);
-        if (cudaEventRecord(h->ev_sent[k - 1], x) != cudaSuccess || cudaStreamWaitEvent(s, h->ev_sent[k - 1], 0) != cudaSuccess)
-            return O64_ERR_CUDA;
-    }
-    // ... and everybody else's columns are in this rank's result before the caller's stream goes on
-    xchg_wait_kernel<<<1, 1, 0, s>>>(xl, kXchgExit, g, kXchgExit + r, 1, h->status_word, budget, 0x512);
-    return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
-}
-
 extern "C" int o64_gemm_s8_sharded(o64_handle_t h, int64_t M, int64_t N, int64_t K, const int8_t *A,
                                    int64_t lda, const int8_t *B_slab, int64_t ldb, int32_t *C_full,
                                    int gather, void *workspace, void *stream) {
     if (!h || M <= 0 || N <= 0 || K <= 0 || !A || !B_slab || !C_full) return O64_ERR_RANK;
     const int g = h->nranks, r = h->rank;
     if (N % g) return O64_ERR_CONFORM;
-    if (gather < O64_GATHER_NONE || gather > O64_GATHER_COPY) return O64_ERR_RANK;
+    if (gather < O64_GATHER_NONE || gather > O64_GATHER_PUSH) return O64_ERR_RANK;
     if (gather != O64_GATHER_NONE && g > 1 && !h->comm) return O64_ERR_NCCL;
     if (is_host_ptr(A) || is_host_ptr(B_slab) || is_host_ptr(C_full)) return O64_ERR_RANK;
     if (!on_handles_device(h, {A, B_slab, C_full, workspace})) return O64_ERR_RANK;
@@ -1161,8 +1001,6 @@ extern "C" int o64_gemm_s8_sharded(o64_handle_t h, int64_t M, int64_t N, int64_t
     }
     if (gather == O64_GATHER_PUSH)
         return push_gemm(h, O64_KIND_S8, EPI_S32, M, N, K, A, lda, B_slab, ldb, C_full, 4, nullptr, O64_ACT_NONE, s);
-    if (gather == O64_GATHER_COPY)
-        return copy_gemm(h, O64_KIND_S8, EPI_S32, M, N, K, A, lda, B_slab, ldb, C_full, 4, nullptr, O64_ACT_NONE, s);
     int32_t *slabs = C_full;  // [g][M][ns]
     if (gather == O64_GATHER_ROWMAJOR) {
         if (g == 1) return o64_gemm_s8s8_s32(h, M, N, K, A, lda, B_slab, ldb, C_full, N, stream);
@@ -1189,8 +1027,7 @@ extern "C" int o64_gemm_bf16_sharded(o64_handle_t h, int64_t M, int64_t N, int64
     if (!h || M <= 0 || N <= 0 || K <= 0 || !A || !B_slab || !C_full) return O64_ERR_RANK;
     const int g = h->nranks, r = h->rank;
     if (N % g) return O64_ERR_CONFORM;
-    if (gather != O64_GATHER_NONE && gather != O64_GATHER_SLABS && gather != O64_GATHER_PUSH && gather != O64_GATHER_COPY)
-        return O64_ERR_RANK;
+    if (gather != O64_GATHER_NONE && gather != O64_GATHER_SLABS && gather != O64_GATHER_PUSH) return O64_ERR_RANK;
     if (gather != O64_GATHER_NONE && g > 1 && !h->comm) return O64_ERR_NCCL;
     if (is_host_ptr(A) || is_host_ptr(B_slab) || is_host_ptr(C_full)) return O64_ERR_RANK;
     if (!on_handles_device(h, {A, B_slab, C_full, epi ? epi->bias : nullptr})) return O64_ERR_RANK;
@@ -1201,8 +1038,6 @@ extern "C" int o64_gemm_bf16_sharded(o64_handle_t h, int64_t M, int64_t N, int64
     cudaStream_t s = (cudaStream_t)stream;
     if (gather == O64_GATHER_PUSH)
         return push_gemm(h, O64_KIND_BF16, EPI_BF16, M, N, K, A, lda, B_slab, ldb, C_full, 2, bias, act, s);
-    if (gather == O64_GATHER_COPY)
-        return copy_gemm(h, O64_KIND_BF16, EPI_BF16, M, N, K, A, lda, B_slab, ldb, C_full, 2, bias, act, s);
     o64_epilogue_t mine;
     mine.bias = bias ? bias + (int64_t)r * ns : nullptr;
     mine.act = act;

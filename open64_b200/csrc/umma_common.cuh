@@ -334,7 +334,7 @@ static __device__ __noinline__ bool xchg_wait_all(const UmmaParams &p, int base,
                     return false;
                 }
             }
-            __nanosleep(100);
+            __nanosleep(500);
         }
     }
     return true;
@@ -345,13 +345,60 @@ static __device__ __noinline__ void xchg_announce_entry(const UmmaParams &p) {
     for (int d = 0; d < p.n_peers; ++d) red_release_sys_add(p.xchg_peer[d] + p.xchg_rank, 1u);
 }
 
-// Epilogue warp, before its first store of the call (whole-warp call): all ranks have arrived.
-static __device__ __noinline__ bool xchg_wait_entry(const UmmaParams &p, volatile int *abort_flag) {
+// Epilogue warps, before their first store of the call (whole-warp call): all ranks have arrived.
+// Polling is kept away from the line the peers write: ONE thread of the grid (CTA 0's `leader` warp)
+// reads the peers' arrival words and then publishes the call number in a word of its own; one
+// warp per CTA polls that word and sets `ready_smem`; the CTA's other epilogue warps watch
+// shared memory.  (With every epilogue warp of every CTA polling the arrival words, the peers'
+// atomics queued behind thousands of loads on one L2 line: 8 GPUs ran five times slower.)
+static __device__ __noinline__ bool xchg_wait_entry(const UmmaParams &p, volatile int *abort_flag, volatile int *ready_smem,
+                                                  bool leader) {
     bool ok = true;
     if ((threadIdx.x & 31) == 0) {
-        // [16] is written only by the last CTA of a call, after every CTA has passed this point
-        const unsigned call = p.xchg_local[kXchgCalls] + 1u;
-        ok = xchg_wait_all(p, 0, call, abort_flag, kWaitXchgEntry);
+        if (leader) {
+            // [kXchgCalls] is written only by the last CTA of a call, after every CTA has passed this point
+            const unsigned call = p.xchg_local[kXchgCalls] + 1u;
+            if (blockIdx.x == 0) {
+                ok = xchg_wait_all(p, 0, call, abort_flag, kWaitXchgEntry);
+                if (ok) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.xchg_local + kXchgReady), "r"(call) : "memory");
+            } else {
+                uint64_t t0 = 0;
+                uint32_t probes = 0;
+                for (;;) {
+                    unsigned v;
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.xchg_local + kXchgReady) : "memory");
+                    if ((int)(v - call) >= 0) break;
+                    if ((++probes & 15u) == 0) {
+                        if (*abort_flag) { ok = false; break; }
+                        const uint64_t now = globaltimer_ns();
+                        if (t0 == 0) {
+                            t0 = now;
+                        } else if (now - t0 > p.wait_ns) {
+                            atomicCAS(p.status, 0, kWaitXchgEntry | 0x80);
+                            *abort_flag = 1;
+                            ok = false;
+                            break;
+                        }
+                    }
+                    __nanosleep(1000);
+                }
+            }
+            *ready_smem = ok ? 1 : -1;
+        } else {
+            uint32_t probes = 0;
+            uint64_t t0 = 0;
+            int v;
+            while ((v = *ready_smem) == 0) {
+                if ((++probes & 63u) == 0) {
+                    if (*abort_flag) { v = -1; break; }
+                    const uint64_t now = globaltimer_ns();
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > 2 * p.wait_ns) { v = -1; break; }  // the leader gives up first and says so
+                }
+                __nanosleep(200);
+            }
+            ok = v > 0;
+        }
     }
     return __shfl_sync(0xffffffffu, ok, 0);
 }

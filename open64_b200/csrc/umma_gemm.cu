@@ -42,7 +42,8 @@ struct SmemLayout {
     static constexpr int kNumBars = 2 * STAGES + 4;
     static constexpr int kTmemPtrOffset = kBarOffset + 8 * kNumBars;
     static constexpr int kAbortOffset = kTmemPtrOffset + 4;
-    static constexpr int kTotal = kAbortOffset + 4;
+    static constexpr int kXchgReadyOffset = kAbortOffset + 4;  // fused exchange: "all ranks have arrived"
+    static constexpr int kTotal = kXchgReadyOffset + 4;
     static constexpr int kDynamic = kTotal + 1024;  // slack to align the ring to 1024 bytes
 };
 
@@ -73,6 +74,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     volatile uint32_t *tmem_ptr_smem =
         reinterpret_cast<volatile uint32_t *>(smem_gen + L::kTmemPtrOffset);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_gen + L::kAbortOffset);
+    volatile int *xchg_ready = reinterpret_cast<volatile int *>(smem_gen + L::kXchgReadyOffset);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -89,6 +91,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             mbar_init(acc_empty_bar(b), 4);  // one arrival per epilogue warp
         }
         *abort_flag = 0;
+        *xchg_ready = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tm_a);
         tma_prefetch_desc(&tm_b);
@@ -246,7 +249,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const int quarter = warp & 3;  // TMEM lane quarter this warp may read
         int it = 0;
         bool ok = true;
-        if (p.xchg_local) ok = xchg_wait_entry(p, abort_flag);  // no remote store before every rank is here
+        if (p.xchg_local) ok = xchg_wait_entry(p, abort_flag, xchg_ready, warp == 2);  // no remote store before every rank is here
         for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++it) {
             int mb, nb;
             tile_coords(w / p.split_k, p, mb, nb);

@@ -71,7 +71,9 @@ struct UmmaCall {
 };
 
 // Layout of the fused exchange's counter block (UmmaParams::xchg_local), in 32-bit words.
-constexpr int kXchgExit = 8, kXchgCalls = 16, kXchgCtasDone = 17, kXchgWords = 32;
+// entry [0..7] and exit [8..15] arrivals share the line the peers write; what this GPU's own CTAs
+// poll and count lives on the next line
+constexpr int kXchgExit = 8, kXchgCalls = 32, kXchgCtasDone = 33, kXchgReady = 34, kXchgWords = 64;
 
 // Validates alignment, encodes the tensor maps and launches.  Returns O64_OK or an error code.
 int umma_launch(const UmmaCall &call);

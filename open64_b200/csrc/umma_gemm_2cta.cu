@@ -43,7 +43,8 @@ struct PairSmemLayout {
     static constexpr int kNumBars = 2 * STAGES + 4;
     static constexpr int kTmemPtrOffset = kBarOffset + 8 * kNumBars;
     static constexpr int kAbortOffset = kTmemPtrOffset + 4;
-    static constexpr int kTotal = kAbortOffset + 4;
+    static constexpr int kXchgReadyOffset = kAbortOffset + 4;  // fused exchange: "all ranks have arrived"
+    static constexpr int kTotal = kXchgReadyOffset + 4;
     static constexpr int kDynamic = kTotal + 1024;
 };
 
@@ -74,6 +75,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     volatile uint32_t *tmem_ptr_smem =
         reinterpret_cast<volatile uint32_t *>(smem_gen + L::kTmemPtrOffset);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_gen + L::kAbortOffset);
+    volatile int *xchg_ready = reinterpret_cast<volatile int *>(smem_gen + L::kXchgReadyOffset);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -92,6 +94,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             mbar_init(acc_empty_bar(b), 8);  // four epilogue warps in each of the two CTAs
         }
         *abort_flag = 0;
+        *xchg_ready = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tm_a);
         tma_prefetch_desc(&tm_b);
@@ -256,7 +259,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         WorkItem w;
         long long clk_store = 0, clk_flags = 0, clk_fix = 0, clk_accwait = 0;  // O64_TRACE=pipe
         const long long t_begin = clock64();
-        if (p.xchg_local) ok = xchg_wait_entry(p, abort_flag);  // no remote store before every rank is here
+        if (p.xchg_local) ok = xchg_wait_entry(p, abort_flag, xchg_ready, warp == 2);  // no remote store before every rank is here
         for (; ok && work_item<TAIL>(p, pair_id, num_pairs, it, w); ++it) {
             int mb, nb;
             tile_coords(w.tile, p, mb, nb);

@@ -57,7 +57,8 @@ struct WideSmem {
     static constexpr int kNumBars = 2 * kWideStages + 4;
     static constexpr int kTmemPtrOffset = kBarOffset + 8 * kNumBars;
     static constexpr int kAbortOffset = kTmemPtrOffset + 4;
-    static constexpr int kTotal = kAbortOffset + 4;
+    static constexpr int kXchgReadyOffset = kAbortOffset + 4;  // fused exchange: "all ranks have arrived"
+    static constexpr int kTotal = kXchgReadyOffset + 4;
     static constexpr int kDynamic = kTotal + 1024;
 };
 
@@ -89,6 +90,7 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     volatile uint32_t *tmem_ptr_smem =
         reinterpret_cast<volatile uint32_t *>(smem_gen + L::kTmemPtrOffset);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem_gen + L::kAbortOffset);
+    volatile int *xchg_ready = reinterpret_cast<volatile int *>(smem_gen + L::kXchgReadyOffset);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -107,6 +109,7 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             mbar_init(acc_empty_bar(g), 2 * kWideEpiWarps);  // the epilogue warps of both CTAs
         }
         *abort_flag = 0;
+        *xchg_ready = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tm_a);
         tma_prefetch_desc(&tm_b);
@@ -295,7 +298,7 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         bool ok = true;
         long long epi_clk = 0;
         WorkItem w;
-        if (p.xchg_local) ok = xchg_wait_entry(p, abort_flag);  // no remote store before every rank is here
+        if (p.xchg_local) ok = xchg_wait_entry(p, abort_flag, xchg_ready, warp == 2);  // no remote store before every rank is here
         for (; ok && work_item<false>(p, pair_id, num_pairs, it, w); ++it) {
             int mb, nb;
             tile_coords(w.tile, p, mb, nb);

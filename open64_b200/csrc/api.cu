@@ -100,7 +100,12 @@ struct o64_handle_s {
     void *sym_local = nullptr;
     void *sym_peer[8] = {nullptr};  // indexed by rank; [rank] == sym_local
     size_t sym_bytes = 0;
-    size_t sym_flags_offset = 0;    // the exchange's counters (kXchgWords words, zeroed) sit behind the result
+    // the exchange's counters (kXchgWords words, zeroed): an allocation of their own, mapped into every
+    // rank like the result.  (Kept out of the result's allocation on purpose: with 256 bytes of counters
+    // behind a 512 MiB result the allocation was no longer a whole number of large pages, and with seven
+    // peers' mappings of that kind the remote stores of the fused kernel ran at 96 GB/s instead of 600.)
+    void *xchg_local = nullptr;
+    void *xchg_peer[8] = {nullptr};
     bool push_nccl_barriers = false;  // O64_PUSH_NCCL_BARRIER=1: order the ranks with two tiny all-reduces instead
     int *barrier_word = nullptr;    // one int, reduced over the ranks as a stream-ordered barrier
     unsigned long long wait_ns = 0;  // budget of the kernels' bounded waits; 0 = the default (two seconds)
@@ -184,7 +189,11 @@ static void free_symmetric(o64_handle_t h) {
     for (int i = 0; i < 8; ++i) {
         if (h->sym_peer[i] && i != h->rank) cudaIpcCloseMemHandle(h->sym_peer[i]);
         h->sym_peer[i] = nullptr;
+        if (h->xchg_peer[i] && i != h->rank) cudaIpcCloseMemHandle(h->xchg_peer[i]);
+        h->xchg_peer[i] = nullptr;
     }
+    if (h->xchg_local) cudaFree(h->xchg_local);
+    h->xchg_local = nullptr;
     if (h->sym_local) cudaFree(h->sym_local);
     h->sym_local = nullptr;
     h->sym_bytes = 0;
@@ -850,17 +859,17 @@ extern "C" int o64_comm_alloc_result(o64_handle_t h, size_t bytes, void **local)
     if (g > 1 && !h->comm) return O64_ERR_NCCL;
     DeviceGuard guard(h->device);
     free_symmetric(h);
-    // the counters of the in-kernel rank barriers live in the same allocation (and so behind the same
-    // inter-process handle) as the result; zeroed before any peer can learn the handle
-    h->sym_flags_offset = (bytes + 255) & ~(size_t)255;
-    if (cudaMalloc(&h->sym_local, h->sym_flags_offset + kXchgWords * sizeof(unsigned)) != cudaSuccess ||
-        cudaMalloc(&h->barrier_word, sizeof(int)) != cudaSuccess) {
+    const size_t kXchgAlloc = 2u << 20;  // a block of its own, so that its handle exports nothing else
+    // whole 2 MiB pages (see the note at xchg_local)
+    const size_t alloc_bytes = (bytes + (2u << 20) - 1) & ~(size_t)((2u << 20) - 1);
+    if (cudaMalloc(&h->sym_local, alloc_bytes) != cudaSuccess || cudaMalloc(&h->barrier_word, sizeof(int)) != cudaSuccess ||
+        cudaMalloc(&h->xchg_local, kXchgAlloc) != cudaSuccess) {
         (void)cudaGetLastError();
         free_symmetric(h);
         return O64_ERR_NOMEM;
     }
     cudaMemset(h->barrier_word, 0, sizeof(int));
-    cudaMemset(static_cast<uint8_t *>(h->sym_local) + h->sym_flags_offset, 0, kXchgWords * sizeof(unsigned));
+    cudaMemset(h->xchg_local, 0, kXchgAlloc);  // before any peer can learn the handle
     cudaDeviceSynchronize();
     {
         const char *e = getenv("O64_PUSH_NCCL_BARRIER");
@@ -868,26 +877,27 @@ extern "C" int o64_comm_alloc_result(o64_handle_t h, size_t bytes, void **local)
     }
     h->sym_bytes = bytes;
     h->sym_peer[h->rank] = h->sym_local;
+    h->xchg_peer[h->rank] = h->xchg_local;
     if (g > 1) {
-        // exchange the inter-process handles of the allocations with an all-gather of 64-byte records
-        cudaIpcMemHandle_t mine;
-        if (cudaIpcGetMemHandle(&mine, h->sym_local) != cudaSuccess) {
+        // exchange the inter-process handles of both allocations with an all-gather of 128-byte records
+        static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+        cudaIpcMemHandle_t mine[2];
+        if (cudaIpcGetMemHandle(&mine[0], h->sym_local) != cudaSuccess || cudaIpcGetMemHandle(&mine[1], h->xchg_local) != cudaSuccess) {
             (void)cudaGetLastError();
             free_symmetric(h);
             return O64_ERR_CUDA;
         }
-        static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
         unsigned char *dev_all = nullptr;
-        if (cudaMalloc(&dev_all, 64 * (size_t)g) != cudaSuccess) {
+        if (cudaMalloc(&dev_all, 128 * (size_t)g) != cudaSuccess) {
             (void)cudaGetLastError();
             free_symmetric(h);
             return O64_ERR_NOMEM;
         }
-        cudaMemcpy(dev_all + 64 * h->rank, &mine, 64, cudaMemcpyHostToDevice);
-        int rc = nccl().AllGather(dev_all + 64 * h->rank, dev_all, 64, kNcclInt8, h->comm, nullptr);
-        cudaIpcMemHandle_t all[8];
+        cudaMemcpy(dev_all + 128 * h->rank, mine, 128, cudaMemcpyHostToDevice);
+        int rc = nccl().AllGather(dev_all + 128 * h->rank, dev_all, 128, kNcclInt8, h->comm, nullptr);
+        cudaIpcMemHandle_t all[16];
         if (rc == 0 && cudaStreamSynchronize(nullptr) == cudaSuccess)
-            cudaMemcpy(all, dev_all, 64 * (size_t)g, cudaMemcpyDeviceToHost);
+            cudaMemcpy(all, dev_all, 128 * (size_t)g, cudaMemcpyDeviceToHost);
         cudaFree(dev_all);
         if (rc != 0) {
             free_symmetric(h);
@@ -895,9 +905,9 @@ extern "C" int o64_comm_alloc_result(o64_handle_t h, size_t bytes, void **local)
         }
         for (int i = 0; i < g; ++i) {
             if (i == h->rank) continue;
-            if (cudaIpcOpenMemHandle(&h->sym_peer[i], all[i], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            if (cudaIpcOpenMemHandle(&h->sym_peer[i], all[2 * i], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess ||
+                cudaIpcOpenMemHandle(&h->xchg_peer[i], all[2 * i + 1], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
                 (void)cudaGetLastError();
-                h->sym_peer[i] = nullptr;
                 free_symmetric(h);
                 return O64_ERR_CUDA;
             }
@@ -963,12 +973,12 @@ static int push_gemm(o64_handle_t h, int kind, int epi, int64_t M, int64_t N, in
     for (int k = 1; k < g; ++k) {
         const int i = (r + k) % g;
         c.peer_c[c.n_peers] = static_cast<uint8_t *>(h->sym_peer[i]) + (size_t)r * ns * out_elem;
-        c.xchg_peer[c.n_peers] = reinterpret_cast<unsigned *>(static_cast<uint8_t *>(h->sym_peer[i]) + h->sym_flags_offset);
+        c.xchg_peer[c.n_peers] = static_cast<unsigned *>(h->xchg_peer[i]);
         c.xchg_peer_rank[c.n_peers] = i;
         ++c.n_peers;
     }
     if (own_barriers) {
-        c.xchg_local = reinterpret_cast<unsigned *>(static_cast<uint8_t *>(h->sym_local) + h->sym_flags_offset);
+        c.xchg_local = static_cast<unsigned *>(h->xchg_local);
         c.xchg_rank = r;
     }
     attach_tail(h, &c);

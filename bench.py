@@ -46,6 +46,7 @@ NOMINAL_8BIT_TOPS = 4500.0
 # capture of this kernel (the run that prints the line cannot be profiled at the same time)
 NCU_TRAFFIC_BYTES = 1002441472
 NCU_TRAFFIC_SOURCE = "ncu capture of umma_gemm_wide_kernel<bf16> on this workload (882.8 MB read + 119.6 MB written); not re-measured by this run"
+PARITY_GATE = 4e-3        # max|y - ref| / max|ref| held on every bf16 / fp8 result the bench times (the contract says 2e-2)
 NVLINK_PEER_GBS = 770.0   # measured peer-copy bandwidth per direction on this pool (900 nominal)
 
 
@@ -468,7 +469,7 @@ def main():
     rows = sample_rows(M, 6, 1)
     ref_rows = oracle.gemm_bf16(from_bits(A[rows]), from_bits(B))
     err_c2 = rel_to_max(C[rows.to(dev)].float().cpu().numpy(), ref_rows)
-    if not err_c2 <= 2e-2:
+    if not err_c2 <= PARITY_GATE:
         raise SystemExit(f"[rank {rank}] headline result differs from the oracle: {err_c2:.3e} of max|ref|")
 
     # per-launch spread (an event pair per launch), the same GEMM on operands that alternate between
@@ -526,7 +527,7 @@ def main():
         e2e["note"] = (f"{world} ranks stage {(M * K + N * K + M * N) * 2 >> 20} MiB each through ONE host's memory and "
                        "PCIe root complexes at the same time; per-rank time grows with the ranks")
     err_e2e = rel_to_max(C_host[rows].float().numpy(), ref_rows)
-    if not err_e2e <= 2e-2:
+    if not err_e2e <= PARITY_GATE:
         raise SystemExit(f"[rank {rank}] e2e result differs from the oracle: {err_e2e:.3e}")
     del C_host
 
@@ -552,7 +553,7 @@ def main():
         "per_gpu_tflops": value / world,
         "roofline": roofline, "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks,
         "parity": {"headline_rel_to_max_vs_oracle_rows": err_c2, "e2e_rel_to_max_vs_oracle_rows": err_e2e,
-                   "gate": 2e-2, "checked_rows": int(rows.numel())},
+                   "gate": PARITY_GATE, "contract": 2e-2, "checked_rows": int(rows.numel())},
     }
     if per_step:
         out["per_launch"] = per_step
@@ -594,13 +595,15 @@ def main():
         h_ref = oracle.swiglu_bf16(from_bits(x[r3]), from_bits(Wg), from_bits(Wu))
         o_ref = oracle.gemm_bf16(h_ref, from_bits(Wd), transB=False)
         err3 = rel_to_max(o3[r3.to(dev)].float().cpu().numpy(), o_ref)
+        if not err3 <= PARITY_GATE:
+            raise SystemExit(f"[rank {rank}] C3 result differs from the oracle: {err3:.3e} of max|ref|")
         tf3 = f3 / (t * 1e-3) / 1e12
         ex["c3_swiglu_mlp"] = {"ms": t, "tflops": tf3, "frac_of_nominal_2250": tf3 / NOMINAL_BF16_TFLOPS,
                                "gemm1_gate_up_swiglu": {"ms": t1, "tflops": f31 / (t1 * 1e-3) / 1e12, "algorithmic_bytes": 385875968},
                                "gemm2_down": {"ms": t2, "tflops": f32 / (t2 * 1e-3) / 1e12, "algorithmic_bytes": 268435456},
                                "roofline": {"bound": "tensor", "achieved": tf3, "peak": peaks["burst"], "unit": "TFLOP/s",
                                             "frac": tf3 / peaks["burst"], "of": peaks["source"] + " (cuBLAS bf16 burst)"},
-                               "rel_to_max_vs_oracle_rows": err3, "gate": 2e-2}
+                               "rel_to_max_vs_oracle_rows": err3, "gate": PARITY_GATE}
         del xd, Wgd, Wud, Wdd, h, o3, x, Wg, Wu, Wd
         # ---- C4
         A8, W8, sA, sB, b4 = o.workloads.c4_fp8()
@@ -613,8 +616,10 @@ def main():
         u8 = lambda t_: t_.contiguous().view(torch.uint8).cpu().numpy()
         ref4 = oracle.gemm_fp8_scaled(u8(A8[r4]), u8(W8), sA[r4].numpy(), sB.numpy(), b4.numpy())
         err4 = rel_to_max(c4[r4.to(dev)].float().cpu().numpy(), ref4)
+        if not err4 <= PARITY_GATE:
+            raise SystemExit(f"[rank {rank}] C4 result differs from the oracle: {err4:.3e} of max|ref|")
         ex["c4_fp8_scaled"] = {"ms": t, "tflops": tf4, "frac_of_nominal_4500": tf4 / NOMINAL_8BIT_TOPS,
-                               "algorithmic_bytes": 167854080, "rel_to_max_vs_oracle_rows": err4, "gate": 2e-2}
+                               "algorithmic_bytes": 167854080, "rel_to_max_vs_oracle_rows": err4, "gate": PARITY_GATE}
         try:
             # the vendor library's scaled fp8 product on the same operands (row-wise scales): the
             # measured peak for this configuration

@@ -2,10 +2,13 @@
 import numpy as np
 import torch
 
-TOL_F32 = 1e-4    # max|y - ref| / max|ref|, fp32 fused linear
-import os
-
-TOL_LOWP = float(os.environ.get("O64_TOL_LOWP", 2e-2))   # max|y - ref| / max|ref|, bf16 / fp8 results against the fp32 nest
+TOL_F32 = 1e-4            # max|y - ref| / max|ref|, fp32 fused linear
+TOL_LOWP_CONTRACT = 2e-2  # the stated bar for bf16 / fp8 results against the fp32 nest on the same operands
+# The gate the tests hold: one bf16 rounding of the largest result (2^-8).  An fp32-accumulating kernel
+# differs from the nest by the rounding of its bf16 output (observed 2.3e-3 ... 2.6e-3 at full size), so
+# everything that meets the contract for the right reason meets this too.
+TOL_LOWP = 4e-3
+assert TOL_LOWP <= TOL_LOWP_CONTRACT
 
 
 def relmax(y, ref):

@@ -338,6 +338,19 @@ int encode_2d(CUtensorMap *tm, int kind, const void *base, int64_t rows, int64_t
     return r == CUDA_SUCCESS ? O64_OK : O64_ERR_CUDA;
 }
 
+int encode_c_bytes(CUtensorMap *tm, void *base, int64_t rows, int64_t cols, int64_t ld, int elem) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return O64_ERR_CUDA;
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) || ((ld * elem) % 16) || cols * elem < 128 || rows < 1) return O64_ERR_ALIGN;
+    cuuint64_t dims[2] = {(cuuint64_t)(cols * elem), (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * elem};
+    cuuint32_t box[2] = {128, 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? O64_OK : O64_ERR_CUDA;
+}
+
 static std::atomic<int> g_force_tail{-1};
 void force_tail_split(int mode) { g_force_tail.store(mode < 0 ? -1 : (mode ? 1 : 0)); }
 
@@ -433,6 +446,7 @@ int umma_launch(const UmmaCall &c) {
     p.num_k_blocks = (int)((c.K + block_k - 1) / block_k);
     const int out_elem = epi_out_bytes(c.epi);
     p.vec_ok = aligned16(c.C) && ((c.ldc * out_elem) % 16 == 0);
+    p.tma_store = 0;
     p.status = c.status_word;
     p.wait_ns = c.wait_ns ? c.wait_ns : kDefaultWaitNs;
     p.test_withhold = c.test_withhold;

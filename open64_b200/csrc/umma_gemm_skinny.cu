@@ -515,6 +515,7 @@ int umma_launch_skinny(const UmmaCall &c, UmmaParams p) {
     p.split_k = 1;
     p.kb_per_split = p.num_k_blocks;
     p.n_peers = 0;
+    p.tma_store = 0;
     p.xchg_local = nullptr;
 #ifdef O64_TUNING
     p.probe = 0;

@@ -65,7 +65,8 @@ struct WideSmem {
 template <int KIND, bool B_KN, int EPI, bool HOOK = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kWideThreads, 1)
 umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                      const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ UmmaParams p) {
+                      const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ CUtensorMap tm_c,
+                      const __grid_constant__ UmmaParams p) {
     using L = WideSmem;
     constexpr int STAGES = kWideStages;
     constexpr int BLOCK_N = kWideBlockN;
@@ -316,7 +317,7 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                 if (!(O64_PROBE(p) & 4)) {
                     epilogue_tile<EPI, BLOCK_N>(p, row0, nb * kOutN, t_row,
                                                 smem_gen + L::kStagingOffset + (warp - 2) * kEpiStagingBytesPerWarp,
-                                                half * kColsPerWarp, (half + 1) * kColsPerWarp);
+                                                half * kColsPerWarp, (half + 1) * kColsPerWarp, p.tma_store ? &tm_c : nullptr);
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -324,6 +325,7 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                 if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty_bar(g), 0));
             }
         }
+        if (p.tma_store && lane == 0) bulk_wait_all();  // this lane's bulk stores are complete before the CTA leaves
         if (p.xchg_local) xchg_stores_done();
         if (O64_DBG(p) && warp == 2 && lane == 0) O64_DBG(p)[blockIdx.x * 8 + 4] = epi_clk;
     }
@@ -344,7 +346,7 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
 }
 
 template <int KIND, bool B_KN, int EPI, bool HOOK = false>
-static int launch_wide_inst(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tb2,
+static int launch_wide_inst(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tb2, const CUtensorMap &tc,
                             const UmmaParams &p, int grid, cudaStream_t stream) {
     auto kern = umma_gemm_wide_kernel<KIND, B_KN, EPI, HOOK>;
     static KernelSetup ks;  // per instantiation; one set-up per device
@@ -376,13 +378,22 @@ static int launch_wide_inst(const CUtensorMap &ta, const CUtensorMap &tb, const 
         &max_pairs);
     if (rc) return rc;
     if (max_pairs > 0 && grid > 2 * max_pairs) grid = 2 * max_pairs;
-    kern<<<grid, kWideThreads, WideSmem::kDynamic, stream>>>(ta, tb, tb2, p);
+    kern<<<grid, kWideThreads, WideSmem::kDynamic, stream>>>(ta, tb, tb2, tc, p);
     return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
 }
 
 // `p.num_m_tiles` counts 512-row blocks; tile_n is 256.
 int umma_launch_wide(const UmmaCall &c, const CUtensorMap &ta, const CUtensorMap &tb,
-                     const CUtensorMap &tb2, const UmmaParams &p) {
+                     const CUtensorMap &tb2, const UmmaParams &p_in) {
+    // full slabs of the result leave by TMA store when C's rows allow it and nothing is pushed to peers
+    UmmaParams p = p_in;
+    CUtensorMap tc = ta;
+    static const bool tma_store_off = [] { const char *e = getenv("O64_TMA_STORE"); return e && atoi(e) == 0; }();
+    if (!tma_store_off && p.vec_ok && p.n_peers == 0 &&
+        encode_c_bytes(&tc, c.C, c.M, p.N, c.ldc, epi_out_bytes(c.epi)) == O64_OK)
+        p.tma_store = 1;
+    else
+        tc = ta;
     const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles;
     long long pairs = c.plan.num_ctas / 2;
     if (pairs > tiles) pairs = tiles;
@@ -390,18 +401,18 @@ int umma_launch_wide(const UmmaCall &c, const CUtensorMap &ta, const CUtensorMap
     const int grid = (int)(2 * pairs);
     if (c.test_withhold >= 0) {  // the one instantiation with the test hook: bf16, B [N,K]
         if (c.kind != O64_KIND_BF16 || c.epi != EPI_BF16 || c.b_kn) return O64_ERR_DTYPE;
-        return launch_wide_inst<MMA_F16, false, EPI_BF16, true>(ta, tb, tb2, p, grid, c.stream);
+        return launch_wide_inst<MMA_F16, false, EPI_BF16, true>(ta, tb, tb2, tc, p, grid, c.stream);
     }
     if (c.kind == O64_KIND_BF16) {
-        if (c.epi == EPI_SWIGLU) return launch_wide_inst<MMA_F16, true, EPI_SWIGLU>(ta, tb, tb2, p, grid, c.stream);
+        if (c.epi == EPI_SWIGLU) return launch_wide_inst<MMA_F16, true, EPI_SWIGLU>(ta, tb, tb2, tc, p, grid, c.stream);
         if (c.epi == EPI_BF16) {
-            if (c.b_kn) return launch_wide_inst<MMA_F16, true, EPI_BF16>(ta, tb, tb2, p, grid, c.stream);
-            return launch_wide_inst<MMA_F16, false, EPI_BF16>(ta, tb, tb2, p, grid, c.stream);
+            if (c.b_kn) return launch_wide_inst<MMA_F16, true, EPI_BF16>(ta, tb, tb2, tc, p, grid, c.stream);
+            return launch_wide_inst<MMA_F16, false, EPI_BF16>(ta, tb, tb2, tc, p, grid, c.stream);
         }
     } else if (c.kind == O64_KIND_FP8 && c.epi == EPI_SCALED_BF16) {
-        return launch_wide_inst<MMA_F8F6F4, false, EPI_SCALED_BF16>(ta, tb, tb2, p, grid, c.stream);
+        return launch_wide_inst<MMA_F8F6F4, false, EPI_SCALED_BF16>(ta, tb, tb2, tc, p, grid, c.stream);
     } else if (c.kind == O64_KIND_S8 && c.epi == EPI_S32) {
-        return launch_wide_inst<MMA_I8, false, EPI_S32>(ta, tb, tb2, p, grid, c.stream);
+        return launch_wide_inst<MMA_I8, false, EPI_S32>(ta, tb, tb2, tc, p, grid, c.stream);
     }
     return O64_ERR_DTYPE;
 }

@@ -604,6 +604,16 @@ def main():
                                "roofline": {"bound": "tensor", "achieved": tf3, "peak": peaks["burst"], "unit": "TFLOP/s",
                                             "frac": tf3 / peaks["burst"], "of": peaks["source"] + " (cuBLAS bf16 burst)"},
                                "rel_to_max_vs_oracle_rows": err3, "gate": PARITY_GATE}
+        try:
+            # the same MLP through the vendor library: two cuBLAS products, an elementwise kernel, a third product
+            def lib3():
+                hh = torch.nn.functional.silu(torch.matmul(xd, Wgd)) * torch.matmul(xd, Wud)
+                return torch.matmul(hh, Wdd)
+            tl3 = timer.steps(lib3, s2, w2)
+            ex["c3_swiglu_mlp"]["library_context_torch_matmul_silu_mul_matmul"] = {
+                "ms": tl3, "tflops": f3 / (tl3 * 1e-3) / 1e12, "ours_over_library": tl3 / t}
+        except Exception as e:  # noqa: BLE001
+            ex["c3_swiglu_mlp"]["library_context_torch_matmul_silu_mul_matmul"] = {"unavailable": repr(e)[:200]}
         del xd, Wgd, Wud, Wdd, h, o3, x, Wg, Wu, Wd
         # ---- C4
         A8, W8, sA, sB, b4 = o.workloads.c4_fp8()

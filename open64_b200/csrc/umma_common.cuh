@@ -82,6 +82,13 @@ struct UmmaParams {
     long long tail_slot_bytes;  // bytes of one pair's slot
 };
 
+// Tensor maps (as bytes, like the map of C the bulk-store epilogue uses) of the peers' copies of the
+// result, in the order of UmmaParams::peer_c: the fused exchange then sends a finished slab with one
+// bulk-tensor store per peer.
+struct PeerMaps {
+    CUtensorMap m[7];
+};
+
 constexpr int kBlockM = 128;
 constexpr int kRowBytes = 128;  // bytes of K (or of N for a [K,N] operand) per shared-memory row
 constexpr int kThreads = 192;
@@ -405,7 +412,12 @@ static __device__ __noinline__ bool xchg_wait_entry(const UmmaParams &p, volatil
 }
 
 // Every thread that stored to a peer, after its last store.
-__device__ __forceinline__ void xchg_stores_done() { __threadfence_system(); }
+// (Slabs sent by bulk-tensor stores: the issuing lane has waited for its bulk groups before this; the
+// proxy fence orders what the TMA unit wrote before the counters this thread's CTA will signal.)
+__device__ __forceinline__ void xchg_stores_done() {
+    asm volatile("fence.proxy.async;" ::: "memory");
+    __threadfence_system();
+}
 
 // Teardown, one thread per CTA, after a CTA-wide barrier behind the epilogue: the last CTA of the grid
 // tells the peers that this rank's stores are complete and waits for theirs.
@@ -593,7 +605,7 @@ __device__ __forceinline__ uint32_t quant4(float a, float b, float c, float d) {
 template <int EPI, int BLOCK_N, int ACT>
 __device__ __forceinline__ void epilogue_tile_act(const UmmaParams &p, long long row0, int n0,
                                                   uint32_t t_row, uint8_t *staging, int c_begin, int c_end,
-                                                  const CUtensorMap *tm_c = nullptr) {
+                                                  const CUtensorMap *tm_c = nullptr, const PeerMaps *tm_peers = nullptr) {
     constexpr int kOutN = (EPI == EPI_SWIGLU) ? BLOCK_N / 2 : BLOCK_N;
     constexpr int kOutElem = epi_out_bytes(EPI);
     constexpr int kSlabCols = 128 / kOutElem;  // 128 one-byte, 64 bf16 or 32 int32 columns per 128-byte row
@@ -676,6 +688,10 @@ __device__ __forceinline__ void epilogue_tile_act(const UmmaParams &p, long long
             __syncwarp();
             if (lane == 0) {
                 tma_store_2d(tm_c, smem_u32(staging), (n0 + slab_c) * kOutElem, (int)row0);
+                // the exchange step of a column-sharded linear, fused: the same slab into every peer's copy of C
+                if (tm_peers)
+                    for (int d = 0; d < p.n_peers; ++d)
+                        tma_store_2d(&tm_peers->m[d], smem_u32(staging), (n0 + slab_c) * kOutElem, (int)row0);
                 bulk_commit_group();
             }
         } else if (h == kChunksPerSlab - 1 && coalesced) {
@@ -742,17 +758,17 @@ template <int EPI, int BLOCK_N>
 __device__ __forceinline__ void epilogue_tile(const UmmaParams &p, long long row0, int n0,
                                               uint32_t t_row, uint8_t *staging, int c_begin = 0,
                                               int c_end = (EPI == EPI_SWIGLU) ? BLOCK_N / 2 : BLOCK_N,
-                                              const CUtensorMap *tm_c = nullptr) {
+                                              const CUtensorMap *tm_c = nullptr, const PeerMaps *tm_peers = nullptr) {
     if constexpr (EPI == EPI_BF16 || epi_scaled(EPI)) {
         switch (p.act) {  // uniform: one branch per tile, not per element
-        case O64_ACT_RELU: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_RELU>(p, row0, n0, t_row, staging, c_begin, c_end, tm_c); break;
-        case O64_ACT_GELU_TANH: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_GELU_TANH>(p, row0, n0, t_row, staging, c_begin, c_end, tm_c); break;
-        case O64_ACT_GELU_ERF: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_GELU_ERF>(p, row0, n0, t_row, staging, c_begin, c_end, tm_c); break;
-        case O64_ACT_SILU: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_SILU>(p, row0, n0, t_row, staging, c_begin, c_end, tm_c); break;
-        default: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_NONE>(p, row0, n0, t_row, staging, c_begin, c_end, tm_c); break;
+        case O64_ACT_RELU: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_RELU>(p, row0, n0, t_row, staging, c_begin, c_end, tm_c, tm_peers); break;
+        case O64_ACT_GELU_TANH: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_GELU_TANH>(p, row0, n0, t_row, staging, c_begin, c_end, tm_c, tm_peers); break;
+        case O64_ACT_GELU_ERF: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_GELU_ERF>(p, row0, n0, t_row, staging, c_begin, c_end, tm_c, tm_peers); break;
+        case O64_ACT_SILU: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_SILU>(p, row0, n0, t_row, staging, c_begin, c_end, tm_c, tm_peers); break;
+        default: epilogue_tile_act<EPI, BLOCK_N, O64_ACT_NONE>(p, row0, n0, t_row, staging, c_begin, c_end, tm_c, tm_peers); break;
         }
     } else {
-        epilogue_tile_act<EPI, BLOCK_N, O64_ACT_NONE>(p, row0, n0, t_row, staging, c_begin, c_end, tm_c);
+        epilogue_tile_act<EPI, BLOCK_N, O64_ACT_NONE>(p, row0, n0, t_row, staging, c_begin, c_end, tm_c, tm_peers);
     }
 }
 

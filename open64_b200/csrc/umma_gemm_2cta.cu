@@ -52,6 +52,7 @@ template <int KIND, bool B_KN, int EPI, int BLOCK_N, int STAGES, bool HOOK = fal
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                       const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ CUtensorMap tm_c,
+                      const __grid_constant__ PeerMaps tm_peers,
                       const __grid_constant__ UmmaParams p) {
     using L = PairSmemLayout<BLOCK_N, STAGES>;
     constexpr int kElem = (KIND == MMA_F16) ? 2 : 1;
@@ -299,7 +300,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                 const long long f0 = O64_DBG(p) ? clock64() : 0;
                 epilogue_tile<EPI, BLOCK_N>(p, row0, nb * kOutN, t_row,
                                             smem_gen + L::kStagingOffset + quarter * kEpiStagingBytesPerWarp, 0, kOutN,
-                                            p.tma_store ? &tm_c : nullptr);
+                                            p.tma_store ? &tm_c : nullptr, (p.tma_store && p.n_peers > 0) ? &tm_peers : nullptr);
                 if (O64_DBG(p)) clk_fix += clock64() - f0;
             }
             tc_fence_before();
@@ -334,7 +335,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
 
 template <int KIND, bool B_KN, int EPI, int BLOCK_N, int STAGES, bool HOOK = false>
 static int launch_pair_inst(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tb2, const CUtensorMap &tc,
-                            const UmmaParams &p, int grid, cudaStream_t stream) {
+                            const PeerMaps &tp, const UmmaParams &p, int grid, cudaStream_t stream) {
     using L = PairSmemLayout<BLOCK_N, STAGES>;
     auto kern = umma_gemm_pair_kernel<KIND, B_KN, EPI, BLOCK_N, STAGES, HOOK>;
     static KernelSetup ks;  // per instantiation; one set-up per device
@@ -386,26 +387,31 @@ static int launch_pair_inst(const CUtensorMap &ta, const CUtensorMap &tb, const 
                 },
                 nullptr);
             if (rc_tail) return rc_tail;
-            kern_tail<<<grid, kThreads, L::kDynamic, stream>>>(ta, tb, tb2, tc, q);
+            kern_tail<<<grid, kThreads, L::kDynamic, stream>>>(ta, tb, tb2, tc, tp, q);
             return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
         }
         // whole tiles only: no more pairs than tiles
         const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles;
         if (grid / 2 > tiles) grid = (int)(2 * tiles);
     }
-    kern<<<grid, kThreads, L::kDynamic, stream>>>(ta, tb, tb2, tc, p);
+    kern<<<grid, kThreads, L::kDynamic, stream>>>(ta, tb, tb2, tc, tp, p);
     return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
 }
 
 // `p.num_m_tiles` counts 256-row blocks here; the grid is an even number of CTAs.
 int umma_launch_pair(const UmmaCall &c, const CUtensorMap &ta, const CUtensorMap &tb,
                      const CUtensorMap &tb2, const UmmaParams &p_in) {
-    // full slabs of the result leave by TMA store when C's rows allow it and nothing is pushed to peers
+    // full slabs of the result leave by TMA store when C's rows allow it
     UmmaParams p = p_in;
     CUtensorMap tc = ta;
     static const bool tma_store_off = [] { const char *e = getenv("O64_TMA_STORE"); return e && atoi(e) == 0; }();
-    if (!tma_store_off && p.vec_ok && p.n_peers == 0 &&
-        encode_c_bytes(&tc, c.C, c.M, p.N, c.ldc, epi_out_bytes(c.epi)) == O64_OK)
+    static PeerMaps tp_init;  // zero-initialised; entries beyond n_peers are never read
+    PeerMaps tp = tp_init;
+    bool bulk = !tma_store_off && p.vec_ok && encode_c_bytes(&tc, c.C, c.M, p.N, c.ldc, epi_out_bytes(c.epi)) == O64_OK;
+    // the fused exchange: one more map per peer copy of the result
+    for (int d = 0; d < p.n_peers && bulk; ++d)
+        bulk = encode_c_bytes(&tp.m[d], p.peer_c[d], c.M, p.N, c.ldc, epi_out_bytes(c.epi)) == O64_OK;
+    if (bulk)
         p.tma_store = 1;
     else
         tc = ta;
@@ -418,11 +424,11 @@ int umma_launch_pair(const UmmaCall &c, const CUtensorMap &ta, const CUtensorMap
     const int block_n = c.plan.tile_n;
 
 #define O64_PAIR(KIND, BKN, EPI_, BN, ST) \
-    return launch_pair_inst<KIND, BKN, EPI_, BN, ST>(ta, tb, tb2, tc, p, grid, c.stream)
+    return launch_pair_inst<KIND, BKN, EPI_, BN, ST>(ta, tb, tb2, tc, tp, p, grid, c.stream)
 
     if (c.test_withhold >= 0) {  // the one instantiation with the test hook: bf16, B [N,K], 256 x 256 tiles
         if (c.kind != O64_KIND_BF16 || c.epi != EPI_BF16 || c.b_kn || block_n != 256) return O64_ERR_DTYPE;
-        return launch_pair_inst<MMA_F16, false, EPI_BF16, 256, 6, true>(ta, tb, tb2, tc, p, grid, c.stream);
+        return launch_pair_inst<MMA_F16, false, EPI_BF16, 256, 6, true>(ta, tb, tb2, tc, tp, p, grid, c.stream);
     }
     if (c.kind == O64_KIND_BF16) {
         if (c.epi == EPI_SWIGLU) {

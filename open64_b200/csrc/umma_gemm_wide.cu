@@ -66,6 +66,7 @@ template <int KIND, bool B_KN, int EPI, bool HOOK = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kWideThreads, 1)
 umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                       const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ CUtensorMap tm_c,
+                      const __grid_constant__ PeerMaps tm_peers,
                       const __grid_constant__ UmmaParams p) {
     using L = WideSmem;
     constexpr int STAGES = kWideStages;
@@ -317,7 +318,7 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                 if (!(O64_PROBE(p) & 4)) {
                     epilogue_tile<EPI, BLOCK_N>(p, row0, nb * kOutN, t_row,
                                                 smem_gen + L::kStagingOffset + (warp - 2) * kEpiStagingBytesPerWarp,
-                                                half * kColsPerWarp, (half + 1) * kColsPerWarp, p.tma_store ? &tm_c : nullptr);
+                                                half * kColsPerWarp, (half + 1) * kColsPerWarp, p.tma_store ? &tm_c : nullptr, (p.tma_store && p.n_peers > 0) ? &tm_peers : nullptr);
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -347,7 +348,7 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
 
 template <int KIND, bool B_KN, int EPI, bool HOOK = false>
 static int launch_wide_inst(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tb2, const CUtensorMap &tc,
-                            const UmmaParams &p, int grid, cudaStream_t stream) {
+                            const PeerMaps &tp, const UmmaParams &p, int grid, cudaStream_t stream) {
     auto kern = umma_gemm_wide_kernel<KIND, B_KN, EPI, HOOK>;
     static KernelSetup ks;  // per instantiation; one set-up per device
     int max_pairs = 0;
@@ -378,19 +379,24 @@ static int launch_wide_inst(const CUtensorMap &ta, const CUtensorMap &tb, const 
         &max_pairs);
     if (rc) return rc;
     if (max_pairs > 0 && grid > 2 * max_pairs) grid = 2 * max_pairs;
-    kern<<<grid, kWideThreads, WideSmem::kDynamic, stream>>>(ta, tb, tb2, tc, p);
+    kern<<<grid, kWideThreads, WideSmem::kDynamic, stream>>>(ta, tb, tb2, tc, tp, p);
     return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
 }
 
 // `p.num_m_tiles` counts 512-row blocks; tile_n is 256.
 int umma_launch_wide(const UmmaCall &c, const CUtensorMap &ta, const CUtensorMap &tb,
                      const CUtensorMap &tb2, const UmmaParams &p_in) {
-    // full slabs of the result leave by TMA store when C's rows allow it and nothing is pushed to peers
+    // full slabs of the result leave by TMA store when C's rows allow it
     UmmaParams p = p_in;
     CUtensorMap tc = ta;
     static const bool tma_store_off = [] { const char *e = getenv("O64_TMA_STORE"); return e && atoi(e) == 0; }();
-    if (!tma_store_off && p.vec_ok && p.n_peers == 0 &&
-        encode_c_bytes(&tc, c.C, c.M, p.N, c.ldc, epi_out_bytes(c.epi)) == O64_OK)
+    static PeerMaps tp_init;  // zero-initialised; entries beyond n_peers are never read
+    PeerMaps tp = tp_init;
+    bool bulk = !tma_store_off && p.vec_ok && encode_c_bytes(&tc, c.C, c.M, p.N, c.ldc, epi_out_bytes(c.epi)) == O64_OK;
+    // the fused exchange: one more map per peer copy of the result
+    for (int d = 0; d < p.n_peers && bulk; ++d)
+        bulk = encode_c_bytes(&tp.m[d], p.peer_c[d], c.M, p.N, c.ldc, epi_out_bytes(c.epi)) == O64_OK;
+    if (bulk)
         p.tma_store = 1;
     else
         tc = ta;
@@ -401,18 +407,18 @@ int umma_launch_wide(const UmmaCall &c, const CUtensorMap &ta, const CUtensorMap
     const int grid = (int)(2 * pairs);
     if (c.test_withhold >= 0) {  // the one instantiation with the test hook: bf16, B [N,K]
         if (c.kind != O64_KIND_BF16 || c.epi != EPI_BF16 || c.b_kn) return O64_ERR_DTYPE;
-        return launch_wide_inst<MMA_F16, false, EPI_BF16, true>(ta, tb, tb2, tc, p, grid, c.stream);
+        return launch_wide_inst<MMA_F16, false, EPI_BF16, true>(ta, tb, tb2, tc, tp, p, grid, c.stream);
     }
     if (c.kind == O64_KIND_BF16) {
-        if (c.epi == EPI_SWIGLU) return launch_wide_inst<MMA_F16, true, EPI_SWIGLU>(ta, tb, tb2, tc, p, grid, c.stream);
+        if (c.epi == EPI_SWIGLU) return launch_wide_inst<MMA_F16, true, EPI_SWIGLU>(ta, tb, tb2, tc, tp, p, grid, c.stream);
         if (c.epi == EPI_BF16) {
-            if (c.b_kn) return launch_wide_inst<MMA_F16, true, EPI_BF16>(ta, tb, tb2, tc, p, grid, c.stream);
-            return launch_wide_inst<MMA_F16, false, EPI_BF16>(ta, tb, tb2, tc, p, grid, c.stream);
+            if (c.b_kn) return launch_wide_inst<MMA_F16, true, EPI_BF16>(ta, tb, tb2, tc, tp, p, grid, c.stream);
+            return launch_wide_inst<MMA_F16, false, EPI_BF16>(ta, tb, tb2, tc, tp, p, grid, c.stream);
         }
     } else if (c.kind == O64_KIND_FP8 && c.epi == EPI_SCALED_BF16) {
-        return launch_wide_inst<MMA_F8F6F4, false, EPI_SCALED_BF16>(ta, tb, tb2, tc, p, grid, c.stream);
+        return launch_wide_inst<MMA_F8F6F4, false, EPI_SCALED_BF16>(ta, tb, tb2, tc, tp, p, grid, c.stream);
     } else if (c.kind == O64_KIND_S8 && c.epi == EPI_S32) {
-        return launch_wide_inst<MMA_I8, false, EPI_S32>(ta, tb, tb2, tc, p, grid, c.stream);
+        return launch_wide_inst<MMA_I8, false, EPI_S32>(ta, tb, tb2, tc, tp, p, grid, c.stream);
     }
     return O64_ERR_DTYPE;
 }

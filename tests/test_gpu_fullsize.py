@@ -115,3 +115,24 @@ def test_c5_int8_exact(eng):
     b_sum = B.to(torch.float64).sum(dim=0).numpy()
     exp_rows = np.concatenate([A[i:i + 1024].to(torch.float64).numpy() @ b_sum for i in range(0, M, 1024)])
     assert np.array_equal(row_sums.astype(np.float64), exp_rows)
+
+
+def test_int8_operand_and_result_beyond_4_gib(eng):
+    """Offsets that do not fit 32 bits: A is 4.6 GB, the int32 result 4.5 GB; rows at the far end of both
+    against the oracle (bit exact), and a checksum of checksums over the whole result."""
+    M, N, K = 140000, 8064, 32768          # M*K = 4.59e9 bytes, M*N*4 = 4.52e9 bytes
+    g = torch.Generator(device=DEV).manual_seed(77)
+    A = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=DEV, generator=g)
+    B = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=DEV, generator=g)
+    C = torch.full((M, N), -7, dtype=torch.int32, device=DEV)
+    eng.gemm_s8(A, B, out=C)
+    torch.cuda.synchronize()
+    rows = torch.tensor([0, 1, 65535, 65536, 131071, 131072, M - 257, M - 2, M - 1])
+    ref = oracle.gemm_s8s8_s32(A[rows.to(DEV)].cpu().numpy(), B.cpu().numpy())
+    assert np.array_equal(C[rows.to(DEV)].cpu().numpy(), ref)
+    # sum over all of C = (column sums of A) . (column sums of B), in exact integer arithmetic
+    sa = A.sum(dim=0, dtype=torch.int64)
+    sb = B.sum(dim=0, dtype=torch.int64)
+    assert int(C.sum(dtype=torch.int64).item()) == int((sa * sb).sum().item())
+    st, detail = eng.last_status()
+    assert st == 0

@@ -1,6 +1,6 @@
 # Builds the reference's own C front half of MATMUL into oracle/_ref/ (test infrastructure).
 #
-#   make -f oracle/ref_front.mk REF=/path/to/open64        (REF defaults to /root/reference)
+#   make -f oracle/ref_front.mk REF=/path/to/open64        (REF: root of the reference tree; a default is set below)
 #
 # Compiled from the reference tree where it lies, nothing is copied:
 #   osprey/libfi/matrix/matmul_<a><b>.c     the 80 _MATMUL_<A><B> wrappers whose strided kernels the

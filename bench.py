@@ -643,7 +643,14 @@ def main():
                                                "of": "torch._scaled_mm (cuBLASLt) measured in this run"}
         except Exception as e:  # noqa: BLE001
             ex["c4_fp8_scaled"]["library_context_torch_scaled_mm"] = {"unavailable": repr(e)[:200]}
-        del A8d, W8d, c4, A8, W8
+        # the same product with the weight stored [K,N] (read in place by the CTA-pair kernel)
+        W8kn = W8d.view(torch.uint8).t().contiguous().view(torch.float8_e4m3fn)
+        c4kn = eng.gemm_fp8_scaled_kn(A8d, W8kn, sAd, sBd, b4d)
+        if not torch.equal(c4kn.view(torch.int16), c4.view(torch.int16)):
+            raise SystemExit(f"[rank {rank}] C4 with the weight stored [K,N] differs from the [N,K] result")
+        tkn = timer.steps(lambda: eng.gemm_fp8_scaled_kn(A8d, W8kn, sAd, sBd, b4d, out=c4kn), s2, w2)
+        ex["c4_fp8_scaled"]["weight_stored_k_by_n"] = {"ms": tkn, "tflops": f4 / (tkn * 1e-3) / 1e12, "parity": "bit-identical to [N,K]"}
+        del A8d, W8d, c4, A8, W8, W8kn, c4kn
         # ---- few rows and the shapes between the regimes (one GPU's worth of work; rank 0's box)
         if world == 1:
             ex["skinny_bf16_Mx8192x8192"] = skinny_points(eng, o, torch, dev, timer, 60, peaks)

@@ -196,9 +196,9 @@ int o64_gemm_fp8_scaled(o64_handle_t h, int64_t M, int64_t N, int64_t K, const v
                         void *stream);
 
 /* The same e4m3 product with the weight stored [K,N] row-major (N contiguous, ldb >= N; device
- * memory).  The weight is transposed into handle-owned scratch on the caller's stream first (one
- * extra pass over N*K bytes per call); a weight that stays the same is better transposed once by
- * the caller and given to o64_gemm_fp8_scaled_ex. */
+ * memory).  A weight whose base address and ldb are multiples of 16 is read in place (same speed
+ * and the same bits as the [N,K] entry point on the transposed weight); any other is first
+ * transposed into handle-owned scratch on the caller's stream (one extra pass over N*K bytes). */
 int o64_gemm_fp8_scaled_kn(o64_handle_t h, int64_t M, int64_t N, int64_t K, const void *A8, int64_t lda,
                            const void *B8_kn, int64_t ldb, const float *scaleA, const float *scaleB,
                            const float *bias, int act, void *C, int64_t ldc, int out_kind, void *stream);

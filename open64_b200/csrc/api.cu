@@ -738,11 +738,9 @@ extern "C" int o64_gemm_fp8_scaled_ex(o64_handle_t h, int64_t M, int64_t N, int6
                       lda, B8, nullptr, ldb, C, ldc, bias, scaleA, scaleB, act, stream);
 }
 
-// The e4m3 product with the weight stored [K,N] (N contiguous).  The tensor-core path of this library
-// reads 8-bit operands with K contiguous, so the weight is transposed once per call into scratch the
-// handle owns (one extra pass over N*K bytes, on the caller's stream) and the [N,K] kernels run on that.
-// A caller whose weight does not change between calls transposes it once itself and uses
-// o64_gemm_fp8_scaled_ex.
+// The e4m3 product with the weight stored [K,N] (N contiguous).  A weight whose base and pitch are
+// multiples of 16 bytes is read in place (below); any other is transposed into scratch the handle owns
+// (one extra pass over N*K bytes, on the caller's stream) and the [N,K] kernels run on that.
 extern "C" int o64_gemm_fp8_scaled_kn(o64_handle_t h, int64_t M, int64_t N, int64_t K, const void *A8, int64_t lda,
                                       const void *B8_kn, int64_t ldb, const float *scaleA, const float *scaleB,
                                       const float *bias, int act, void *C, int64_t ldc, int out_kind, void *stream) {
@@ -756,6 +754,27 @@ extern "C" int o64_gemm_fp8_scaled_kn(o64_handle_t h, int64_t M, int64_t N, int6
     if (!on_handles_device(h, {B8_kn})) return O64_ERR_RANK;
     DeviceGuard g(h->device);
     cudaStream_t s = (cudaStream_t)stream;
+    // A weight TMA can address (16-byte aligned base and pitch) is read as it lies: the CTA-pair kernel
+    // loads [K,N] boxes and multiplies with an N-major shared-memory descriptor on 256 x 256 tiles.
+    static const bool native_off = [] { const char *e = getenv("O64_FP8_KN_NATIVE"); return e && atoi(e) == 0; }();
+    if (!native_off && tma_aligned(B8_kn, ldb, 1) && N >= 16) {
+        const bool had = h->has_pin[O64_KIND_FP8];
+        const o64_plan_t saved = h->pins[O64_KIND_FP8];
+        o64_plan_t pin;
+        memset(&pin, 0, sizeof(pin));
+        pin.kind = O64_KIND_FP8;
+        pin.cta_group = 2;
+        pin.tile_m = 256;
+        pin.tile_n = 256;
+        pin.split_k = 1;
+        h->pins[O64_KIND_FP8] = pin;
+        h->has_pin[O64_KIND_FP8] = true;
+        const int rc_native = umma_entry(h, O64_KIND_FP8, true, out_kind == O64_OUT_E4M3 ? EPI_SCALED_E4M3 : EPI_SCALED_BF16, M, N,
+                                         K, A8, lda, B8_kn, nullptr, ldb, C, ldc, bias, scaleA, scaleB, act, stream);
+        h->pins[O64_KIND_FP8] = saved;
+        h->has_pin[O64_KIND_FP8] = had;
+        return rc_native;
+    }
     const int64_t ld_t = (K + 15) / 16 * 16;
     int rc = reserve(&h->stage[9], &h->stage_cap[9], (size_t)N * ld_t);
     if (rc) return rc;

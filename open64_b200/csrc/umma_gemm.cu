@@ -412,7 +412,11 @@ int umma_launch(const UmmaCall &c) {
     if (c.M > INT32_MAX || c.N > INT32_MAX || c.K > INT32_MAX) return O64_ERR_RANK;
     if (c.kind != O64_KIND_BF16 && c.kind != O64_KIND_FP8 && c.kind != O64_KIND_S8)
         return O64_ERR_DTYPE;
-    if (c.b_kn && c.kind != O64_KIND_BF16) return O64_ERR_DTYPE;
+    if (c.b_kn && c.kind != O64_KIND_BF16 && c.kind != O64_KIND_FP8) return O64_ERR_DTYPE;
+    // an e4m3 weight stored [K,N] is read by the CTA-pair kernel on 256 x 256 tiles only
+    if (c.b_kn && c.kind == O64_KIND_FP8 &&
+        !(c.plan.cta_group == 2 && c.plan.tile_m == 256 && c.plan.tile_n == 256 && c.plan.split_k == 1))
+        return O64_ERR_DTYPE;
     if (c.epi == EPI_SWIGLU && (!c.b_kn || !c.B2)) return O64_ERR_DTYPE;
     // TMA needs 16-byte aligned bases and row pitches
     if (!aligned16(c.A) || !aligned16(c.B) || (c.B2 && !aligned16(c.B2))) return O64_ERR_ALIGN;
@@ -487,9 +491,10 @@ int umma_launch(const UmmaCall &c) {
         rc = encode_2d(&tb, c.kind, c.B, c.N, c.K, c.ldb, block_k, pair ? block_n / 2 : block_n);
         tb2 = tb;
     } else {
-        rc = encode_2d(&tb, c.kind, c.B, c.K, c.N, c.ldb, 64, block_k);
+        const int kn_cols = (c.kind == O64_KIND_BF16) ? 64 : 128;  // 128 bytes of N per shared-memory row
+        rc = encode_2d(&tb, c.kind, c.B, c.K, c.N, c.ldb, kn_cols, block_k);
         tb2 = tb;
-        if (!rc && c.epi == EPI_SWIGLU) rc = encode_2d(&tb2, c.kind, c.B2, c.K, c.N, c.ldb, 64, block_k);
+        if (!rc && c.epi == EPI_SWIGLU) rc = encode_2d(&tb2, c.kind, c.B2, c.K, c.N, c.ldb, kn_cols, block_k);
     }
     if (rc) return rc;
 

@@ -59,11 +59,17 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     constexpr int kBlockK = kRowBytes / kElem;
     constexpr int kMmaPerStage = 4;
     constexpr int kHalfN = BLOCK_N / 2;  // B rows (N) held by each CTA
+    // a [K,N] operand (N contiguous) lands in shared memory as groups of 128 bytes of N (64 bf16 or 128
+    // one-byte columns) by kBlockK rows of K each; an MMA consumes 32 bytes of K: 16 bf16 or 32 e4m3 rows
+    constexpr int kKnCols = kRowBytes / kElem;
+    constexpr int kKnGroupBytes = kBlockK * kRowBytes;
+    constexpr int kMmaK = 32 / kElem;
+    static_assert(!B_KN || kHalfN % kKnCols == 0, "[K,N] operand: each CTA's columns must be whole 128-byte groups");
     constexpr int kOutN = (EPI == EPI_SWIGLU) ? BLOCK_N / 2 : BLOCK_N;
     constexpr int kPairM = 2 * kBlockM;
     constexpr uint32_t kTmemCols = 2 * BLOCK_N;
     static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns");
-    static_assert(!B_KN || KIND == MMA_F16, "[K,N] operands are supported for bf16 only");
+    static_assert(!B_KN || KIND == MMA_F16 || KIND == MMA_F8F6F4, "[K,N] operands: bf16 and e4m3");
     static_assert(EPI != EPI_SWIGLU || B_KN, "SwiGLU weights are [K,N]");
 
     extern __shared__ uint8_t smem_raw[];
@@ -156,16 +162,16 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                             tma_load_2d_pair(b_dst, &tm_b, kb * kBlockK, n0 + (int)rank * kHalfN, full0);
                         } else if constexpr (EPI == EPI_SWIGLU) {
                             // rank 0 holds the gate columns, rank 1 the up columns of the same n0
-                            constexpr int kGroups = kHalfN / 64;
+                            constexpr int kGroups = kHalfN / kKnCols;
 #pragma unroll
                             for (int g = 0; g < kGroups; ++g)
-                                tma_load_2d_pair(b_dst + g * 8192, rank ? &tm_b2 : &tm_b, n0 + g * 64,
+                                tma_load_2d_pair(b_dst + g * kKnGroupBytes, rank ? &tm_b2 : &tm_b, n0 + g * kKnCols,
                                                  kb * kBlockK, full0);
                         } else {
-                            constexpr int kGroups = kHalfN / 64;
+                            constexpr int kGroups = kHalfN / kKnCols;
 #pragma unroll
                             for (int g = 0; g < kGroups; ++g)
-                                tma_load_2d_pair(b_dst + g * 8192, &tm_b, n0 + (int)rank * kHalfN + g * 64,
+                                tma_load_2d_pair(b_dst + g * kKnGroupBytes, &tm_b, n0 + (int)rank * kHalfN + g * kKnCols,
                                                  kb * kBlockK, full0);
                         }
                     }
@@ -189,7 +195,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             constexpr uint32_t d_fmt = (KIND == MMA_I8) ? 2u : 1u;
             constexpr uint32_t ab_fmt = (KIND == MMA_F8F6F4) ? 0u : 1u;
             constexpr uint32_t idesc = make_idesc(d_fmt, ab_fmt, ab_fmt, B_KN ? 1u : 0u, kPairM, BLOCK_N);
-            constexpr uint32_t kBAdvance = B_KN ? (16 * kRowBytes) >> 4 : 32 >> 4;
+            constexpr uint32_t kBAdvance = B_KN ? (kMmaK * kRowBytes) >> 4 : 32 >> 4;
             int stage = 0;
             uint32_t phase = 0;
             int it = 0;
@@ -223,7 +229,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                     const uint32_t b_addr = a_addr + kABytes;
                     const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024);
                     const uint64_t b_desc =
-                        B_KN ? make_smem_desc(b_addr, 8192, 1024) : make_smem_desc(b_addr, 16, 1024);
+                        B_KN ? make_smem_desc(b_addr, kKnGroupBytes, 1024) : make_smem_desc(b_addr, 16, 1024);
                     if ((O64_PROBE(p) & 3) == 2) {
                         if (leader) {
                             mbar_arrive(empty_bar(stage));
@@ -442,6 +448,9 @@ int umma_launch_pair(const UmmaCall &c, const CUtensorMap &ta, const CUtensorMap
                 if (block_n == 128) O64_PAIR(MMA_F16, false, EPI_BF16, 128, 8);
             }
         }
+    } else if (c.kind == O64_KIND_FP8 && c.b_kn) {  // e4m3 weight stored [K,N]: 256-column tiles only
+        if (block_n == 256 && c.epi == EPI_SCALED_BF16) O64_PAIR(MMA_F8F6F4, true, EPI_SCALED_BF16, 256, 6);
+        if (block_n == 256 && c.epi == EPI_SCALED_E4M3) O64_PAIR(MMA_F8F6F4, true, EPI_SCALED_E4M3, 256, 6);
     } else if (c.kind == O64_KIND_FP8 && c.epi == EPI_SCALED_BF16) {
         if (block_n == 256) O64_PAIR(MMA_F8F6F4, false, EPI_SCALED_BF16, 256, 6);
         if (block_n == 128) O64_PAIR(MMA_F8F6F4, false, EPI_SCALED_BF16, 128, 8);

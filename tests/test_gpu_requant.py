@@ -10,7 +10,7 @@ import torch
 
 import open64_b200 as o
 import oracle
-from util import TOL_LOWP, bits8, relmax
+from util import TOL_LOWP, bits8, from_bits8_e4m3, relmax
 
 pytestmark = pytest.mark.gpu
 ACTS = {"none": oracle.ACT_NONE, "relu": oracle.ACT_RELU, "gelu_tanh": oracle.ACT_GELU_TANH, "silu": oracle.ACT_SILU}
@@ -140,3 +140,32 @@ def test_fp8_weight_stored_k_by_n(eng, shape):
     assert torch.equal(got2.view(torch.int16), want.view(torch.int16))
     with pytest.raises(o.O64Error):
         eng.gemm_fp8_scaled_kn(a8, w_kn.cpu(), sA.to(dev), sB.to(dev), b.to(dev))
+
+
+@pytest.mark.parametrize("out_kind", ["bf16", "e4m3"])
+def test_fp8_weight_stored_k_by_n_read_in_place(eng, out_kind):
+    """An aligned [K,N] e4m3 weight is multiplied as it lies (N-major shared-memory descriptor, 256 x 256
+    tiles of the CTA-pair kernel): same bits as the [N,K] kernels on the transposed weight; ragged M, N
+    and K; no scratch copy of the weight is made."""
+    dev = torch.device("cuda", eng.device)
+    M, N, K = 700, 1200, 1000            # N a multiple of 16: the pitch of the [K,N] weight is TMA-addressable
+    A8, W8, sA, sB, b = o.workloads.c4_fp8(M, N, K)
+    a8, w8 = A8.to(dev), W8.to(dev)
+    w_kn = w8.view(torch.uint8).t().contiguous().view(torch.float8_e4m3fn)
+    kind = o.OUT_E4M3 if out_kind == "e4m3" else o.OUT_BF16
+    scale = 0.05 if out_kind == "e4m3" else 1.0
+    args = ((sA * scale).to(dev), sB.to(dev), (b * scale).to(dev), "relu", kind)
+    free0 = torch.cuda.mem_get_info()[0]
+    got = eng.gemm_fp8_scaled_kn(a8, w_kn, *args)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] >= free0 - got.numel() * got.element_size() - (1 << 20)  # the result only
+    want = eng.gemm_fp8_scaled_ex(a8, w8, *args)
+    assert torch.equal(got.view(torch.uint8), want.view(torch.uint8))
+    ref = oracle.gemm_fp8_scaled_ex(bits8(A8), bits8(W8), (sA * scale).numpy(), sB.numpy(), (b * scale).numpy(), ACTS["relu"],
+                                    2 if out_kind == "e4m3" else 0)
+    if out_kind == "bf16":
+        assert relmax(got.float().cpu().numpy(), ref) <= 4e-3
+    else:
+        g8 = got.float().cpu().numpy()
+        r8 = from_bits8_e4m3(ref).float().numpy()
+        assert relmax(g8, r8) <= 7e-2    # one e4m3 rounding of the largest value

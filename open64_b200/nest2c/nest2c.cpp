@@ -8,7 +8,7 @@
 // and replaces it by one call into libo64gemm.so.  Everything else is copied through.
 //
 // Recognised (any spacing, redundant parentheses, `x = x + 1` / `x++` / `x += 1` steps, `<` or
-// `<=` bounds, lower bounds 0):
+// `<=` bounds, any lower bound that does not depend on the loop's own variable):
 //
 //     for (i ...)  for (j ...) { acc = 0; for (k ...) acc = acc + A[i][k] * B[k][j];
 //                                Y[i][j] = acc;  |  acc + bias[j];  |  max(acc + bias[j], 0); }
@@ -372,6 +372,7 @@ std::string strip_suffix(const std::string &num) {  // 512LL -> 512
 // ------------------------------------------------------------------------------------------
 struct Loop {
     std::string var;
+    ExprP lb;         // first value (0 in the nest the reference builds; a section's first index otherwise)
     ExprP ub;         // exclusive bound when !inclusive
     bool inclusive = false;
     std::vector<std::string> pragmas;  // in front of this loop
@@ -382,7 +383,7 @@ void take_pragmas(const std::vector<Tok> &t, size_t &p, std::vector<std::string>
     while (t[p].kind == Tok::Pragma) out->push_back(t[p++].text);
 }
 
-// for ( v = 0 ; v < ub ; step )   -- leaves p on the first token of the body
+// for ( v = lb ; v < ub ; step ), lb free of v   -- leaves p on the first token of the body
 bool parse_for(const std::vector<Tok> &t, size_t &p, Loop *L) {
     if (!(t[p].kind == Tok::Id && t[p].text == "for")) return false;
     Parser ps(t, p + 1);
@@ -395,7 +396,8 @@ bool parse_for(const std::vector<Tok> &t, size_t &p, Loop *L) {
     ps.expect(";");
     ExprP test = ps.ternary();
     ps.expect(";");
-    if (!ps.ok || !is_zero(lb) || !test || test->kind != Expr::Bin || !is_id(test->kids[0], L->var)) return false;
+    if (!ps.ok || !lb || mentions(lb, L->var) || !test || test->kind != Expr::Bin || !is_id(test->kids[0], L->var)) return false;
+    L->lb = lb;
     if (test->text == "<=") L->inclusive = true;
     else if (test->text != "<") return false;
     L->ub = test->kids[1];
@@ -799,6 +801,10 @@ bool match_nest(const std::vector<Tok> &t, size_t start, const std::map<std::str
     if (!prod || prod->kind != Expr::Bin || prod->text != "*") return false;
     const std::vector<std::string> vars = {n->li.var, n->lj.var, n->lk.var};
     if (vars[0] == vars[1] || vars[0] == vars[2] || vars[1] == vars[2]) return false;
+    // a rectangular iteration space only: no bound of one loop in terms of another loop's variable
+    for (const Loop *L : {&n->li, &n->lj, &n->lk})
+        for (const std::string &v : vars)
+            if (mentions(L->lb, v) || mentions(L->ub, v)) return false;
     Ref r0, r1;
     if (!parse_ref(prod->kids[0], vars, decls, &r0) || !parse_ref(prod->kids[1], vars, decls, &r1)) return false;
     auto uses = [](const Ref &r, const std::string &x, const std::string &y) {
@@ -1052,11 +1058,12 @@ std::string emit_tiled(const TiledNest &n, const std::string &indent) {
 }
 
 std::string extent(const Loop &L) {
-    if (L.ub->kind == Expr::Num) {
-        const long long v = atoll(strip_suffix(L.ub->text).c_str());
-        return std::to_string(L.inclusive ? v + 1 : v);
-    }
-    return L.inclusive ? "(" + str(L.ub) + " + 1)" : str(L.ub);
+    long long lo = 0, hi = 0;
+    const bool lo_const = const_int(L.lb, &lo), hi_const = const_int(L.ub, &hi);
+    if (lo_const && hi_const) return std::to_string((L.inclusive ? hi + 1 : hi) - lo);
+    std::string e = L.inclusive ? "(" + str(L.ub) + " + 1)" : str(L.ub);
+    if (lo_const && lo == 0) return e;
+    return "(" + e + " - (" + str(L.lb) + "))";
 }
 
 bool pragma_ints(const std::string &text, const char *name, std::vector<long long> *vals, std::vector<std::string> *ids) {
@@ -1116,8 +1123,21 @@ std::string emit(const Nest &n, const std::string &indent) {
     scan(n.lk, 2);
     const bool plain = n.a.row == n.li.var && n.a.col == n.lk.var && n.b.row == n.lk.var && n.b.col == n.lj.var &&
                        n.c.row == n.li.var && n.c.col == n.lj.var;
-    auto base = [](const Ref &r) { return "&" + str(r.whole->kids[0]->kind == Expr::Index ? r.whole->kids[0]->kids[0] : r.whole->kids[0]) +
-                                          (r.whole->kids[0]->kind == Expr::Index ? "[0][0]" : "[0]"); };
+    // the element the loops touch first: every index variable at its loop's first value
+    auto first_of = [&](const std::string &var) {
+        const Loop &L = var == n.li.var ? n.li : (var == n.lj.var ? n.lj : n.lk);
+        long long v;
+        return const_int(L.lb, &v) ? std::to_string(v) : "(" + str(L.lb) + ")";
+    };
+    auto base = [&](const Ref &r) {
+        const bool two_d = r.whole->kids[0]->kind == Expr::Index;
+        const std::string name = str(two_d ? r.whole->kids[0]->kids[0] : r.whole->kids[0]);
+        const std::string r0 = first_of(r.row), c0 = first_of(r.col);
+        if (two_d) return "&" + name + "[" + r0 + "][" + c0 + "]";
+        if (r0 == "0" && c0 == "0") return "&" + name + "[0]";
+        return "&" + name + "[" + r0 + " * (" + r.ld + ") + " + c0 + "]";
+    };
+    const std::string bias_arg = n.bias.empty() ? "NULL" : (first_of(n.lj.var) == "0" ? n.bias : "&" + n.bias + "[" + first_of(n.lj.var) + "]");
     static const char *act_names[] = {"O64_ACT_NONE", "O64_ACT_RELU", "O64_ACT_GELU_TANH", "O64_ACT_GELU_ERF", "O64_ACT_SILU"};
     if (n.type == "f32" && plain) {
         const bool pinned = tile_m || tile_n || tile_k || group || raster;
@@ -1132,7 +1152,7 @@ std::string emit(const Nest &n, const std::string &indent) {
               << in2 << "    o64_plan_set(o64nest_handle(), O64_KIND_F32, NULL);  /* no kernel of that size: automatic plan */\n";
         }
         o << in2 << "o64nest_check(o64_linear_f32(o64nest_handle(), " << M << ", " << N << ", " << K << ", " << base(n.a)
-          << ", " << n.a.ld << ", " << base(n.b) << ", " << n.b.ld << ", " << (n.bias.empty() ? "NULL" : n.bias) << ", "
+          << ", " << n.a.ld << ", " << base(n.b) << ", " << n.b.ld << ", " << bias_arg << ", "
           << base(n.c) << ", " << n.c.ld << ", " << act_names[n.act] << ", NULL), \"o64_linear_f32\");\n";
         if (pinned) o << in2 << "o64_plan_set(o64nest_handle(), O64_KIND_F32, NULL);\n";
     } else {

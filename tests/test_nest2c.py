@@ -45,8 +45,10 @@ def test_every_product_nest_of_the_fixture_is_replaced(built, tmp_path):
 
 
 NOT_RECOGNISED = [
-    # lower bound not zero
-    "float A[8][8],B[8][8],C[8][8];\nvoid f(){for(int i=1;i<8;i++)for(int j=0;j<8;j++){C[i][j]=0;for(int k=0;k<8;k++)C[i][j]+=A[i][k]*B[k][j];}}",
+    # a first value in terms of another loop's variable: not a rectangle
+    "float A[8][8],B[8][8],C[8][8];\nvoid f(){for(int i=0;i<8;i++)for(int j=i;j<8;j++){C[i][j]=0;for(int k=0;k<8;k++)C[i][j]+=A[i][k]*B[k][j];}}",
+    # a bound in terms of another loop's variable
+    "float A[8][8],B[8][8],C[8][8];\nvoid f(){for(int i=0;i<8;i++)for(int j=0;j<8;j++){C[i][j]=0;for(int k=0;k<=j;k++)C[i][j]+=A[i][k]*B[k][j];}}",
     # step of two
     "float A[8][8],B[8][8],C[8][8];\nvoid f(){for(int i=0;i<8;i+=2)for(int j=0;j<8;j++){C[i][j]=0;for(int k=0;k<8;k++)C[i][j]+=A[i][k]*B[k][j];}}",
     # accumulator not zeroed
@@ -137,3 +139,21 @@ def test_a_loop_around_a_product_nest_stays(built):
             "for(int k=0;k<8;k++)C[i][j]+=A[i][k]*B[k][j];}")
     out, n = rewrite(text)
     assert n == 1 and "for(int t=0;t<8;t+=4){" in out and "_s4gemmx__(" in out
+
+
+def test_nests_over_sections_of_arrays(built, tmp_path):
+    """Loops that do not start at zero: the operands' first elements and the extents follow the first values."""
+    out, n = rewrite(open(os.path.join(ROOT, "tests", "nests", "sections.c")).read())
+    assert n == 3
+    assert ("o64_linear_f32(o64nest_handle(), (M - (2)), (((N - 2) + 1) - (3)), (K - (1)), &A[2][1], K, &B[1][3], N, "
+            "&bias[3], &Y[2][3], N, O64_ACT_RELU, NULL)") in out
+    assert "&P[(lo) * (30) + ((lo + 1))]" in out and "&Q[((lo + 1)) * (20) + 4]" in out and "&R[(lo) * (20) + 4]" in out
+    assert "o64_m = ((hi) - (lo))" in out or "o64_m = (hi - (lo))" in out
+    assert "&Ai[5][2]" in out and "&Bi[2][7]" in out and "&Ci[5][7]" in out and "o64_m = 35, o64_n = 44, o64_k = 21" in out
+    # the triangular nest is still there
+    assert "for (j = i; j < N; j++)" in out and "T[i][j] = acc;" in out
+    path = tmp_path / "sections_out.c"
+    path.write_text(out)
+    r = subprocess.run(["gcc", "-fsyntax-only", "-Wall", "-Werror=implicit-function-declaration",
+                        "-I", os.path.join(ROOT, "include"), str(path)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr

@@ -20,7 +20,8 @@
 // with rank-2 ARRAY nodes whose subscripts are the loop indices (in either order: a transposed operand
 // only exchanges its increments).  For each nest: one line of JSON (function, element kind, extents,
 // arrays with their increments, tail) and the C call on the runtime's strided kernel (or the fused
-// fp32 linear when the layout is plain and a bias / ReLU tail is present).
+// fp32 linear when the layout is plain and a bias / ReLU tail is present).  Also recognised: MATMUL
+// before the lowering pass has expanded it (an INTRINSIC_OP, see match_intrinsic below).
 //
 //   o64whirl dump.txt            exit status 0 (the number of nests goes to stderr), 2 on usage errors
 #include <cstdio>
@@ -370,6 +371,82 @@ bool match_nest(const NodeP &outer, Match *m) {
     return true;
 }
 
+// ---- MATMUL before it is expanded --------------------------------------------------------------
+// Ahead of the F90 lowering pass the product is still one node: the front end builds an INTRINSIC_OP
+// INTRN_MATMUL with two value PARMs under an ARRAYEXP (fei_matmul, osprey/crayf90/sgi/cwh_intrin.cxx:
+// 1168-1201) and the statement stores that array expression; lower_mm_matmul later turns it into the
+// nest above (osprey/be/vho/f90_lower.cxx:5330-5337).  Printed by ir_put_wn as
+// "<type>INTRINSIC_OP 2 <number,MATMUL> ..." (osprey/common/com/ir_reader.cxx:1089-1096).  What is
+// reported: the element kind from the opcode, and the first variable named under each operand and under
+// the store's address - enough to bind the runtime's entry point _MATMUL_<K><K> on the arrays' dope
+// vectors, the call the front end emits when it does not expand the intrinsic in line.
+struct IntrinsicMatch {
+    std::string kind, a, b, c;
+};
+
+const Node *first_variable(const Node &n) {
+    if ((ends_with(n.op, "LDA") || ends_with(n.op, "LDID")) && !sym_name(n.rest).empty() &&
+        sym_name(n.rest).compare(0, 6, ".preg_") != 0)
+        return &n;
+    for (const NodeP &k : n.kids)
+        if (const Node *f = first_variable(*k)) return f;
+    return nullptr;
+}
+
+const Node *find_matmul_op(const Node &n) {
+    if (ends_with(n.op, "INTRINSIC_OP") && n.rest.find(",MATMUL>") != std::string::npos) return &n;
+    for (const NodeP &k : n.kids)
+        if (const Node *f = find_matmul_op(*k)) return f;
+    return nullptr;
+}
+
+bool match_intrinsic(const NodeP &stmt, IntrinsicMatch *m) {
+    if (!stmt || stmt->kids.empty()) return false;
+    const bool istore = ends_with(stmt->op, "ISTORE") || ends_with(stmt->op, "MSTORE");
+    const bool stid = ends_with(stmt->op, "STID");
+    if (!istore && !stid) return false;
+    const Node *op = find_matmul_op(*stmt->kids[0]);  // the stored value
+    if (!op || op->kids.size() != 2) return false;
+    for (const NodeP &k : op->kids)
+        if (!ends_with(k->op, "PARM")) return false;
+    const std::string t = op->op.substr(0, op->op.size() - strlen("INTRINSIC_OP"));
+    if (t == "F4") m->kind = "S4";
+    else if (t == "F8") m->kind = "S";
+    else if (t == "I4") m->kind = "I4";
+    else if (t == "I8") m->kind = "J";
+    else if (t == "I2") m->kind = "I2";
+    else if (t == "I1") m->kind = "I1";
+    else if (t == "C4") m->kind = "C4";
+    else if (t == "C8") m->kind = "C";
+    else return false;
+    const Node *a = first_variable(*op->kids[0]), *b = first_variable(*op->kids[1]);
+    const Node *c = istore ? (stmt->kids.size() >= 2 ? first_variable(*stmt->kids[1]) : nullptr) : stmt.get();
+    if (!a || !b || !c) return false;
+    m->a = sym_name(a->rest), m->b = sym_name(b->rest), m->c = sym_name(c->rest);
+    return !(m->c == m->a || m->c == m->b);  // the runtime's entry point may not write over an operand
+}
+
+void find_intrinsics(const NodeP &n, std::vector<IntrinsicMatch> *out) {
+    if (!n) return;
+    if (n->op == "DO_LOOP") {
+        find_intrinsics(n->body, out);
+        return;
+    }
+    if (n->op == "BLOCK") {
+        for (const NodeP &k : n->kids) find_intrinsics(k, out);
+        return;
+    }
+    IntrinsicMatch m;
+    if (match_intrinsic(n, &m)) out->push_back(m);
+}
+
+void print(const IntrinsicMatch &m, const std::string &func) {
+    printf("{\"function\": \"%s\", \"intrinsic\": \"MATMUL\", \"kind\": \"%s\", \"A\": \"%s\", \"B\": \"%s\", \"C\": \"%s\"}\n",
+           func.c_str(), m.kind.c_str(), m.a.c_str(), m.b.c_str(), m.c.c_str());
+    printf("    _MATMUL_%s%s(&%s_dope, &%s_dope, &%s_dope);   /* RESULT, MATRIX_A, MATRIX_B: the arrays' dope vectors */\n",
+           m.kind.c_str(), m.kind.c_str(), m.c.c_str(), m.a.c_str(), m.b.c_str());
+}
+
 void find(const NodeP &n, std::vector<Match> *out) {
     if (!n) return;
     if (n->op == "DO_LOOP") {
@@ -432,7 +509,7 @@ int main(int argc, char **argv) {
     }
     // every FUNC_ENTRY: its last BLOCK is the body; structured statements are parsed, anything this
     // reader does not understand ends the function's scan (nothing is guessed)
-    int found = 0;
+    int found = 0, intrinsics = 0;
     Reader r(lines);
     std::string func = "?";
     while (r.p < lines.size()) {
@@ -453,10 +530,16 @@ int main(int argc, char **argv) {
             find(b, &ms);
             for (const Match &m : ms) print(m, func);
             found += (int)ms.size();
+            std::vector<IntrinsicMatch> is;
+            find_intrinsics(b, &is);
+            for (const IntrinsicMatch &m : is) print(m, func);
+            intrinsics += (int)is.size();
         } else {
             ++r.p;
         }
     }
-    fprintf(stderr, "o64whirl: %d nest%s recognised\n", found, found == 1 ? "" : "s");
+    fprintf(stderr, "o64whirl: %d nest%s recognised", found, found == 1 ? "" : "s");
+    if (intrinsics) fprintf(stderr, ", %d MATMUL intrinsic%s", intrinsics, intrinsics == 1 ? "" : "s");
+    fprintf(stderr, "\n");
     return 0;
 }

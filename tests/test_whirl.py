@@ -20,9 +20,10 @@ def run(path_or_text, stdin=False):
 
 
 def test_fixtures_are_what_the_script_writes(built, tmp_path):
-    for name in ("matmul_f90.whirl.txt", "linear_relu.whirl.txt"):
+    names = ("matmul_f90.whirl.txt", "linear_relu.whirl.txt", "matmul_intrinsic.whirl.txt")
+    for name in names:
         assert os.path.exists(os.path.join(DUMPS, name))
-    before = {n: open(os.path.join(DUMPS, n)).read() for n in ("matmul_f90.whirl.txt", "linear_relu.whirl.txt")}
+    before = {n: open(os.path.join(DUMPS, n)).read() for n in names}
     subprocess.run([sys.executable, os.path.join(DUMPS, "make_dumps.py")], check=True)
     for n, text in before.items():
         assert open(os.path.join(DUMPS, n)).read() == text
@@ -67,3 +68,15 @@ def test_damaged_and_foreign_input(built):
     assert recs == [] and "0 nests" in err
     recs, _, err = run("this is not WHIRL\n BLOCK\n", stdin=True)
     assert recs == []
+
+
+def test_matmul_still_an_intrinsic(built):
+    """The WHIRL the lowering pass receives: MATMUL as an INTRINSIC_OP over two PARMs.  The tool names the
+    operands and the runtime entry point that takes their dope vectors."""
+    recs, out, err = run(os.path.join(DUMPS, "matmul_intrinsic.whirl.txt"))
+    assert "0 nests recognised, 2 MATMUL intrinsics" in err
+    by = {r["function"]: r for r in recs}
+    assert set(by) == {"mm_intrinsic_", "mm_intrinsic_r8_"}            # mm_in_place_ writes over its operand
+    assert by["mm_intrinsic_"] == {"function": "mm_intrinsic_", "intrinsic": "MATMUL", "kind": "S4", "A": "a_", "B": "b_", "C": "c_"}
+    assert by["mm_intrinsic_r8_"]["kind"] == "S"
+    assert "_MATMUL_S4S4(&c__dope, &a__dope, &b__dope);" in out and "_MATMUL_SS(&r__dope, &p__dope, &q__dope);" in out

@@ -139,7 +139,56 @@ def function(w, name, body):
     w.put(1, "END_BLOCK")
 
 
+def matmul_intrinsic(w, d, ty, A, B, R):
+    """R = MATMUL(A, B) as the front end leaves it for the lowering pass (fei_matmul, osprey/crayf90/sgi/
+    cwh_intrin.cxx:1168-1201): INTRINSIC_OP INTRN_MATMUL over two value PARMs, wrapped in an ARRAYEXP and
+    stored through the result's section.  The operands' own subtrees (whole-array sections: ARRSECTION over
+    LDA with one TRIPLET per dimension, loaded and wrapped in ARRAYEXP) are schematic: the node kinds and
+    their order follow the WHIRL definitions of those operators (kids of ARRSECTION: base, extents,
+    subscripts; kids of TRIPLET: first value, stride, count; kids of ARRAYEXP: value, extents), the
+    intrinsic's number is a placeholder."""
+    def section(dd, X):
+        name, idx, dims = X
+        w.put(dd + 1, f"U8LDA 0 <1,{idx},{name}> T<{60 + idx},anon_ptr.,8>")
+        for e in dims:
+            intconst(w, dd + 1, e)
+        for e in dims:
+            intconst(w, dd + 2, 0)
+            intconst(w, dd + 2, 1)
+            intconst(w, dd + 2, e)
+            w.put(dd + 1, "I4TRIPLET")
+        w.put(dd, f"U8ARRSECTION {len(dims)} {ESIZE[ty]}")
+
+    def operand(dd, X):
+        section(dd + 3, X)
+        w.put(dd + 2, f"{ty}{ty}ILOAD 0 {TY[ty]} T<{60 + X[1]},anon_ptr.,8>")
+        for e in X[2]:
+            intconst(w, dd + 2, e)
+        w.put(dd + 1, f"{ty}ARRAYEXP {len(X[2]) + 1}")
+        w.put(dd, f"{ty}PARM 2 {TY[ty]} #  by_value")
+
+    operand(d + 3, A)
+    operand(d + 3, B)
+    w.put(d + 2, f"{ty}INTRINSIC_OP 2 <0,MATMUL> 0")
+    for e in R[2]:
+        intconst(w, d + 2, e)
+    w.put(d + 1, f"{ty}ARRAYEXP {len(R[2]) + 1}")
+    section(d + 1, R)
+    w.put(d, f"{ty}ISTORE 0 T<{60 + R[1]},anon_ptr.,8>")
+
+
 def main():
+    # MATMUL still as an intrinsic (the WHIRL the lowering pass receives)
+    w = W()
+    function(w, "mm_intrinsic_", lambda d: matmul_intrinsic(
+        w, d, "F4", ("a_", 41, [200, 300]), ("b_", 42, [260, 200]), ("c_", 43, [260, 300])))
+    function(w, "mm_intrinsic_r8_", lambda d: matmul_intrinsic(
+        w, d, "F8", ("p_", 44, [70, 90]), ("q_", 45, [50, 70]), ("r_", 46, [50, 90])))
+    # the result is also an operand: A = MATMUL(A, B) needs a temporary, the entry point cannot be bound as is
+    function(w, "mm_in_place_", lambda d: matmul_intrinsic(
+        w, d, "F4", ("a_", 41, [200, 200]), ("b_", 42, [200, 200]), ("a_", 41, [200, 200])))
+    with open(os.path.join(HERE, "matmul_intrinsic.whirl.txt"), "w") as f:
+        f.write("\n".join(w.lines) + "\n")
     w = W()
     # C = MATMUL(A, B), REAL*4, constant extents: A(300,200), B(200,260), C(300,260); WHIRL dims reversed
     function(w, "mm_const_", lambda d: matmul_nest(

@@ -90,6 +90,24 @@ def _rank_main(rank, world, port, q):
             lin(Ad, gather=oo.GATHER_PUSH, out=out)
             torch.cuda.synchronize()
             assert torch.equal(out.cpu(), ref), f"fused push, call {rep}"
+        # the fused form replayed from a CUDA graph: the call number the ranks compare lives in device
+        # memory, so the frozen launch parameters are good for every replay
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            lin(Ad, gather=oo.GATHER_PUSH, out=out)          # warm-up on the capturing stream
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                lin(Ad, gather=oo.GATHER_PUSH, out=out)
+        torch.cuda.current_stream().wait_stream(side)
+        for rep in range(3):
+            out.fill_(-20 - rep)
+            torch.cuda.synchronize()
+            dist.barrier()                                   # every rank has refilled before anyone replays
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(out.cpu(), ref), f"fused push replayed from a graph, replay {rep}"
+        del graph
         # a taller product through the fused form: more tiles than CTA pairs, the last row block ragged
         M2, K2 = 4200, 256
         A2, B2 = oo.workloads.c5_int8(M2, N, K2, seed=35)

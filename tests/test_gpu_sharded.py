@@ -139,6 +139,39 @@ def _rank_main(rank, world, port, q):
         assert relmax(rm.float().cpu().numpy(), refb) <= TOL_LOWP, "bf16 slab-major gather"
         st, detail = eng.last_status()
         assert st == 0
+        # a rank that never makes the call: the other's kernel waits for its arrival for the handle's budget,
+        # gives up, stores nothing to the peer, and says which wait ran out; the context stays usable and a
+        # fresh result buffer (new counters on both ranks) works again.  Nothing faults, traps or hangs.
+        torch.cuda.synchronize()
+        dist.barrier()
+        out = eng.alloc_result(M, N)
+        out.fill_(-99)
+        torch.cuda.synchronize()
+        dist.barrier()
+        if rank == 0:
+            eng.set_wait_budget_us(30_000)
+            lin(Ad, gather=oo.GATHER_PUSH, out=out)
+            torch.cuda.synchronize()
+            st, detail = eng.last_status()
+            # 0x501: the wait for the peers' arrival (0x581 when a CTA other than the one that watches the
+            # peers' counters was the first to give up)
+            assert st == oo.ERR_TIMEOUT and (detail & 0xf7f) == 0x501, (st, hex(detail))
+            eng.set_wait_budget_us(0)
+            assert eng.last_status()[0] == 0
+        torch.cuda.synchronize()
+        dist.barrier()
+        if rank == 1:
+            assert (out == -99).all(), "a kernel whose wait ran out must not have stored into its peer"
+        dist.barrier()
+        out = eng.alloc_result(M, N)                             # collective: counters start afresh
+        out.fill_(-1)
+        torch.cuda.synchronize()
+        dist.barrier()
+        lin(Ad, gather=oo.GATHER_PUSH, out=out)
+        torch.cuda.synchronize()
+        assert torch.equal(out.cpu(), ref), "fused push after a timed-out call"
+        st, detail = eng.last_status()
+        assert st == 0
         torch.cuda.synchronize()
         dist.barrier()
         eng.close()

@@ -655,6 +655,33 @@ def main():
         if world == 1:
             ex["skinny_bf16_Mx8192x8192"] = skinny_points(eng, o, torch, dev, timer, 60, peaks)
             ex["mid_m_bf16_Mx8192x8192"] = mid_m_points(eng, o, torch, dev, timer, 36)
+        # ---- DOT_PRODUCT over dope vectors (the matmul family's sibling): two REAL*4 vectors resident in HBM
+        if world == 1:
+            import ctypes
+            from open64_b200._lib import DopeVector
+            nd = 1 << 26                                           # 2 x 256 MiB: nothing of it stays in L2
+            gd = torch.Generator(device=dev).manual_seed(o.workloads.SEEDS["c1"] + 9)
+            xv = torch.rand(nd, device=dev, generator=gd) - 0.5
+            yv = torch.rand(nd, device=dev, generator=gd) - 0.5
+            X = DopeVector.real4(xv.data_ptr(), [nd], [1])
+            Y = DopeVector.real4(yv.data_ptr(), [nd], [1])
+            dot = eng.lib._DOT_S4S4
+            got = float(dot(ctypes.byref(X), ctypes.byref(Y)))
+            want = float((xv.double() * yv.double()).sum().item())
+            scale = float((xv.double() * yv.double()).abs().sum().item())
+            if eng.lib.o64_compat_last_status() != 0 or not abs(got - want) <= 1e-6 * scale:
+                raise SystemExit(f"DOT_PRODUCT differs: {got} vs {want}")
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(10):
+                dot(ctypes.byref(X), ctypes.byref(Y))              # synchronous: the value comes back to the host
+            td = (time.perf_counter() - t0) / 10 * 1e3
+            ex["dot_product_f32_2x256MiB"] = {
+                "ms": td, "algorithmic_bytes": 2 * nd * 4, "abs_err_over_sum_abs": abs(got - want) / scale,
+                "roofline": {"bound": "hbm", "achieved": 2 * nd * 4 / (td * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                             "frac": 2 * nd * 4 / (td * 1e-3) / 1e9 / peaks["hbm_gbs"], "of": peaks["source"],
+                             "timing": "host clock around the synchronous call (launch, two reduction passes, result to the host)"}}
+            del xv, yv
         # ---- C5: the int8 GEMM, column-sharded over the ranks (strong scaling: total work fixed)
         M5, N5, K5 = 16384, 8192, 8192
         A5, B5 = o.workloads.c5_int8(M5, N5, K5)

@@ -682,6 +682,29 @@ def main():
                              "frac": 2 * nd * 4 / (td * 1e-3) / 1e9 / peaks["hbm_gbs"], "of": peaks["source"],
                              "timing": "host clock around the synchronous call (launch, two reduction passes, result to the host)"}}
             del xv, yv
+        # ---- the BLAS hooks of the runtime (column-major, device operands): REAL*4 and REAL*8 on the CUDA cores,
+        #      where the element kind's exact arithmetic matters more than speed; the vendor library beside them
+        if world == 1:
+            nb = 2048
+            gb = torch.Generator(device=dev).manual_seed(o.workloads.SEEDS["c1"] + 11)
+            blas = {}
+            for name, dt, fn in (("sgemm_", torch.float32, eng.sgemm), ("dgemm_", torch.float64, eng.dgemm)):
+                a_ = torch.rand((nb, nb), device=dev, generator=gb, dtype=dt) - 0.5
+                b_ = torch.rand((nb, nb), device=dev, generator=gb, dtype=dt) - 0.5
+                c_ = torch.zeros((nb, nb), device=dev, dtype=dt)
+                run_b = lambda: fn("n", "n", nb, nb, nb, 1.0, a_, nb, b_, nb, 0.0, c_, nb)
+                run_b()
+                # column-major C = A B is row-major C^T = B^T A^T: the buffers read as row-major give c_ = b_ @ a_
+                refb = torch.matmul(b_.double(), a_.double())
+                errb = float(((c_.double() - refb).abs().max() / refb.abs().max()).item())
+                if not errb <= (1e-4 if dt == torch.float32 else 1e-12):
+                    raise SystemExit(f"{name} differs: {errb:.3e}")
+                tb_ = timer.steps(run_b, 5, 2)
+                tl_ = timer.steps(lambda: torch.matmul(b_, a_, out=c_), 5, 2)
+                blas[name + "2048"] = {"ms": tb_, "tflops": 2 * nb ** 3 / (tb_ * 1e-3) / 1e12, "rel_to_max_vs_float64": errb,
+                                       "library_context_torch_matmul": {"ms": tl_, "tflops": 2 * nb ** 3 / (tl_ * 1e-3) / 1e12}}
+                del a_, b_, c_, refb
+            ex["compat_blas_hooks"] = blas
         # ---- C5: the int8 GEMM, column-sharded over the ranks (strong scaling: total work fixed)
         M5, N5, K5 = 16384, 8192, 8192
         A5, B5 = o.workloads.c5_int8(M5, N5, K5)

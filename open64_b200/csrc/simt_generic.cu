@@ -7,7 +7,9 @@
 // shared-memory tiled loop nest (the L1 strip and register tile of osprey/be/lno/snl_inv.cxx:639,904).
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdint>
+#include <mutex>
 #include <type_traits>
 
 #include "../../include/o64gemm.h"
@@ -90,6 +92,165 @@ gemmx_generic_kernel(long long M, long long N, long long K, T alpha, const TA *A
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// REAL*8 on plainly laid out operands (what MATMUL on whole REAL*8 arrays and the dgemm_ hook pass):
+// Y[Mr,Nr] = alpha * X[Mr,K] * W[K,Nr] + beta * Y, X with K contiguous, W and Y with Nr contiguous.
+// A column-major product C = A B is this with X = B', W = A', Y = C' (the caller exchanges the roles).
+// 64 x 64 tiles with a 4 x 4 register block per thread; strips of 8 in a four-deep ring of asynchronous
+// 16-byte copies (the structure of the REAL*4 linear in simt_kernels.cu).  The template's rule that a
+// zero factor in B leaves its term out only changes a result when the other operand holds an
+// infinity or a NaN; the launcher checks that operand first and keeps the general kernel for that case.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async_16_g(void *smem_dst, const void *gmem_src, int bytes) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem_src), "r"(bytes) : "memory");
+}
+
+template <int TM>  // rows of the register block (4: 64 x 64 tiles)
+__global__ void __launch_bounds__(256)
+dense_f64_kernel(long long Mr, long long Nr, long long K, double alpha, const double *__restrict__ X, long long ldx,
+                 const double *__restrict__ W, long long ldw, double beta, double *__restrict__ Y, long long ldy) {
+    constexpr int BM = 16 * TM, BN = 64, BK = 8, STAGES = (TM == 8) ? 3 : 4;
+    constexpr int A_PITCH = BK + 2, B_PITCH = BN + 2;  // doubles: rows stay 16-byte aligned, banks rotate by row
+    __shared__ __align__(16) double As[STAGES][BM][A_PITCH];
+    __shared__ __align__(16) double Bs[STAGES][BK][B_PITCH];
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const long long m0 = (long long)blockIdx.y * BM, n0 = (long long)blockIdx.x * BN;
+    const long long strips = (K + BK - 1) / BK;
+
+    auto fetch = [&](long long strip, int buf) {
+        const long long k0 = strip * BK;
+#pragma unroll
+        for (int r = 0; r < TM / 4; ++r) {  // X: BM rows x 4 pairs of K, 16-byte copies
+            const int e = tid + r * 256;
+            const int m = e >> 2, kp = (e & 3) * 2;
+            const long long gm = m0 + m, gk = k0 + kp;
+            const bool ok = gm < Mr && gk < K;  // K is even: a pair is inside or outside as a whole
+            cp_async_16_g(&As[buf][m][kp], ok ? X + gm * ldx + gk : X, ok ? 16 : 0);
+        }
+        {  // W: 8 rows of K x 32 pairs of Nr
+            const int k = tid >> 5, np = (tid & 31) * 2;
+            const long long gk = k0 + k, gn = n0 + np;
+            const bool ok = gk < K && gn < Nr;
+            cp_async_16_g(&Bs[buf][k][np], ok ? W + gk * ldw + gn : W, ok ? 16 : 0);
+        }
+    };
+
+    double acc[TM][4];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0;
+#pragma unroll
+    for (int st = 0; st < STAGES - 1; ++st) {
+        if (st < strips) fetch(st, st);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (long long strip = 0; strip < strips; ++strip) {
+        const int buf = (int)(strip % STAGES);
+        asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+        __syncthreads();
+        if (strip + STAGES - 1 < strips) fetch(strip + STAGES - 1, (int)((strip + STAGES - 1) % STAGES));
+        asm volatile("cp.async.commit_group;" ::: "memory");
+#pragma unroll
+        for (int l = 0; l < BK; ++l) {  // ascending k, as the loop nest sums
+            double a[TM];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) a[i] = As[buf][ty * TM + i][l];
+            // this thread's four columns are tx*2, tx*2+1 and 32 + the same: consecutive threads read
+            // consecutive 16-byte words (columns tx*4 .. tx*4+3 would put threads 0 and 4 on one bank)
+            const double2 b01 = *reinterpret_cast<const double2 *>(&Bs[buf][l][tx * 2]);
+            const double2 b23 = *reinterpret_cast<const double2 *>(&Bs[buf][l][32 + tx * 2]);
+#pragma unroll
+            for (int i = 0; i < TM; ++i) {
+                acc[i][0] = fma(a[i], b01.x, acc[i][0]);
+                acc[i][1] = fma(a[i], b01.y, acc[i][1]);
+                acc[i][2] = fma(a[i], b23.x, acc[i][2]);
+                acc[i][3] = fma(a[i], b23.y, acc[i][3]);
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const long long gm = m0 + ty * TM + i;
+        if (gm >= Mr) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j += 2) {
+            const long long gn = n0 + (j ? 32 : 0) + tx * 2;
+            if (gn >= Nr) continue;  // Nr is even: a pair is inside or outside as a whole
+            double *dst = Y + gm * ldy + gn;
+            double2 v = make_double2(alpha * acc[i][j], alpha * acc[i][j + 1]);
+            if (beta != 0.0) {
+                const double2 o = *reinterpret_cast<const double2 *>(dst);
+                v.x += beta * o.x;
+                v.y += beta * o.y;
+            }
+            *reinterpret_cast<double2 *>(dst) = v;
+        }
+    }
+}
+
+// sets *flag when any element of the rows x cols matrix (cols contiguous, pitch ld) is an infinity or a NaN
+__global__ void nonfinite_f64_kernel(const double *p, long long rows, long long cols, long long ld, int *flag) {
+    bool bad = false;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < rows * cols; e += (long long)gridDim.x * blockDim.x) {
+        const double v = p[(e / cols) * ld + (e % cols)];
+        bad |= !(fabs(v) <= 1.7976931348623157e308);
+    }
+    if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicExch(flag, 1);
+}
+
+// The dense REAL*8 path, if the call has its shape; *done says whether it ran.
+static int try_dense_f64(int64_t M, int64_t N, int64_t K, double alpha, const double *A, int64_t a1, int64_t a2, const double *B,
+                         int64_t b1, int64_t b2, double beta, double *C, int64_t c1, int64_t c2, cudaStream_t s, bool *done) {
+    *done = false;
+    if (K <= 0) return O64_OK;
+    const double *X, *W;
+    double *Y = C;
+    int64_t Mr, Nr, ldx, ldw, ldy;
+    const double *other;  // the operand whose infinities or NaNs a skipped zero term would have hidden
+    int64_t o_rows, o_cols, o_ld;
+    if (a2 == 1 && b2 == 1 && c2 == 1) {          // row-major: C[i][j], A[i][l], B[l][j]
+        X = A, ldx = a1, W = B, ldw = b1, ldy = c1, Mr = M, Nr = N;
+        other = A, o_rows = M, o_cols = K, o_ld = a1;
+    } else if (a1 == 1 && b1 == 1 && c1 == 1) {   // column-major: C' = B' A'
+        X = B, ldx = b2, W = A, ldw = a2, ldy = c2, Mr = N, Nr = M;
+        other = A, o_rows = K, o_cols = M, o_ld = a2;
+    } else {
+        return O64_OK;
+    }
+    auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    if ((K & 1) || (Nr & 1) || (ldx & 1) || (ldw & 1) || (ldy & 1) || ldx < K || ldw < Nr || ldy < Nr || !al16(X) || !al16(W) ||
+        !al16(Y) || (Mr + 63) / 64 > 65535)
+        return O64_OK;
+    static int *flags[64] = {nullptr};  // one word per device, allocated on first use
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return O64_OK;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!flags[dev] && cudaMalloc(&flags[dev], sizeof(int)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        flags[dev] = nullptr;
+        return O64_OK;
+    }
+    int bad = 0;
+    if (cudaMemsetAsync(flags[dev], 0, sizeof(int), s) != cudaSuccess) return O64_ERR_CUDA;
+    const long long total = (long long)o_rows * o_cols;
+    nonfinite_f64_kernel<<<(unsigned)std::min<long long>((total + 255) / 256, 148 * 8), 256, 0, s>>>(other, o_rows, o_cols, o_ld, flags[dev]);
+    if (cudaMemcpyAsync(&bad, flags[dev], sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+        cudaStreamSynchronize(s) != cudaSuccess)
+        return O64_ERR_CUDA;
+    if (bad) return O64_OK;  // the general kernel keeps the rule about zero factors
+    // (128 x 64 tiles with 8 x 4 register blocks were measured too: 16.0 TFLOP/s at 2048^3 against 17.8 for
+    // these - fewer CTAs per SM cover the load latency less well)
+    dim3 grid((unsigned)((Nr + 63) / 64), (unsigned)((Mr + 63) / 64));
+    dense_f64_kernel<4><<<grid, 256, 0, s>>>(Mr, Nr, K, alpha, X, ldx, W, ldw, beta, Y, ldy);
+    *done = true;
+    return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
+}
+
 template <typename T>
 __global__ void gemvx_generic_kernel(long long M, long long N, T alpha, const T *A, long long a1, long long a2,
                                      const T *X, long long incx, T beta, T *Y, long long incy, int conj_a) {
@@ -116,6 +277,13 @@ template <typename TA, typename T>
 int generic_gemmx(int64_t M, int64_t N, int64_t K, T alpha, const TA *A, int64_t a1, int64_t a2, const T *B,
                   int64_t b1, int64_t b2, T beta, T *C, int64_t c1, int64_t c2, cudaStream_t s, int conj_a, int conj_b) {
     if (M <= 0 || N <= 0) return O64_OK;
+    if constexpr (std::is_same<T, double>::value && std::is_same<TA, double>::value) {
+        if (!conj_a && !conj_b) {
+            bool done = false;
+            const int rc = try_dense_f64(M, N, K, alpha, A, a1, a2, B, b1, b2, beta, C, c1, c2, s, &done);
+            if (rc || done) return rc;
+        }
+    }
     if ((M + 31) / 32 > 65535) return O64_ERR_RANK;
     auto mag = [](int64_t v) { return v < 0 ? -v : v; };
     dim3 grid((unsigned)((N + 31) / 32), (unsigned)((M + 31) / 32));

@@ -216,3 +216,40 @@ def test_matmul_entry_points(eng, ka, kb):
     fn(ctypes.byref(_dv(kc, c, (m, n), (1, m))), ctypes.byref(_dv(ka, a, (m, k), (1, m))),
        ctypes.byref(_dv(kb, b, (k + 1, n), (1, k + 1))))
     assert eng.lib.o64_compat_last_status() == o.ERR_CONFORM
+
+
+@pytest.mark.parametrize("layout", ["column-major", "row-major"])
+def test_real8_dense_path_and_its_exceptions(eng, layout):
+    """REAL*8 on plainly laid out operands runs a blocked kernel of its own; the rule of the runtime's
+    template that a zero factor of B leaves its term out (osprey/libfi/matrix/xgemmx.h:227) still holds when
+    A carries an infinity: the result is what the general kernel gives."""
+    import torch
+    dev = torch.device("cuda", eng.device)
+    M, N, K = 200, 136, 96
+    g = torch.Generator().manual_seed(123)
+    a = torch.rand((M, K), generator=g, dtype=torch.float64) - 0.5      # mathematical A(i,l)
+    b = torch.rand((K, N), generator=g, dtype=torch.float64) - 0.5
+    c0 = torch.rand((M, N), generator=g, dtype=torch.float64)
+
+    def run(a_math, b_math):
+        if layout == "column-major":       # X(i,j) at i + ld*j: the transposed matrix stored row-major
+            A, B, C = a_math.t().contiguous().to(dev), b_math.t().contiguous().to(dev), c0.t().contiguous().to(dev)
+            eng.xgemmx("s", M, N, K, 1.5, A, 1, M, B, 1, K, 0.5, C, 1, M)
+            return C.t().cpu()
+        A, B, C = a_math.contiguous().to(dev), b_math.contiguous().to(dev), c0.clone().to(dev)
+        eng.xgemmx("s", M, N, K, 1.5, A, K, 1, B, N, 1, 0.5, C, N, 1)
+        return C.cpu()
+
+    want = 1.5 * (a @ b) + 0.5 * c0
+    got = run(a, b)
+    assert ((got - want).abs().max() / want.abs().max()).item() <= 1e-12
+    # an infinity in A whose partner in B is zero: the term is left out, the row stays finite
+    a2, b2 = a.clone(), b.clone()
+    a2[7, 5] = float("inf")
+    b2[5, :] = 0.0
+    got2 = run(a2, b2)
+    a_fin = a2.clone()
+    a_fin[7, 5] = 0.0
+    want2 = 1.5 * (a_fin @ b2) + 0.5 * c0
+    assert torch.isfinite(got2).all()
+    assert ((got2 - want2).abs().max() / want2.abs().max()).item() <= 1e-12

@@ -10,6 +10,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
+#include <mutex>
 
 #include "../../include/o64gemm.h"
 #include "simt_kernels.cuh"
@@ -322,7 +323,74 @@ static int launch_simt(const SimtParams &p, bool skip_zero, cudaStream_t stream)
     return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
 }
 
-int simt_gemm_f32(const SimtGemmCall &c) {
+// sets *flag when any element of the rows x cols matrix (cols contiguous, pitch ld) is an infinity or a NaN
+__global__ void nonfinite_f32_kernel(const float *p, long long rows, long long cols, long long ld, int *flag) {
+    bool bad = false;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < rows * cols; e += (long long)gridDim.x * blockDim.x) {
+        const float v = p[(e / cols) * ld + (e % cols)];
+        bad |= !(fabsf(v) <= 3.402823466e38f);
+    }
+    if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicExch(flag, 1);
+}
+
+// A call that has the shape of the dense kernel - plainly laid out, row-major or column-major (then as
+// C' = B' A'), alpha 1, beta 0 - but is not in its form yet.  Where it carries the runtime's rule about zero
+// factors of B (the strided kernels behind MATMUL): the rule can only change a result when A holds an
+// infinity or a NaN, so A is scanned and, if it is clean, the dense kernel runs.  Synchronises the stream (these
+// entry points are synchronous anyway).  Returns true when `*out` is to be used instead of `c`.
+static bool dense_form_of_skipping_call(const SimtGemmCall &c, SimtGemmCall *out) {
+    if (c.K <= 0 || simt_dense_ok(c)) return false;  // (already in the dense kernel's own form)
+    SimtGemmCall d = c;
+    long long o_rows, o_cols, o_ld;
+    if (c.a2 == 1 && c.b2 == 1 && c.c2 == 1) {
+        o_rows = c.M, o_cols = c.K, o_ld = c.a1;
+    } else if (c.a1 == 1 && c.b1 == 1 && c.c1 == 1) {
+        d.M = c.N, d.N = c.M;
+        d.A = c.B, d.a1 = c.b2, d.a2 = 1;
+        d.B = c.A, d.b1 = c.a2, d.b2 = 1;
+        d.c1 = c.c2, d.c2 = 1;
+        o_rows = c.K, o_cols = c.M, o_ld = c.a2;
+    } else {
+        return false;
+    }
+    d.skip_zero_b = false;
+    if (!simt_dense_ok(d)) return false;
+    if (!c.skip_zero_b) {  // no rule to keep: the exchange of roles is all
+        *out = d;
+        return true;
+    }
+    static int *flags[64] = {nullptr};  // one word per device
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!flags[dev] && cudaMalloc(&flags[dev], sizeof(int)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        flags[dev] = nullptr;
+        return false;
+    }
+    int bad = 1;
+    const long long total = o_rows * o_cols;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (cudaMemsetAsync(flags[dev], 0, sizeof(int), c.stream) != cudaSuccess) return false;
+    nonfinite_f32_kernel<<<(unsigned)blocks, 256, 0, c.stream>>>(c.A, o_rows, o_cols, o_ld, flags[dev]);
+    if (cudaMemcpyAsync(&bad, flags[dev], sizeof(int), cudaMemcpyDeviceToHost, c.stream) != cudaSuccess ||
+        cudaStreamSynchronize(c.stream) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    if (bad) return false;
+    *out = d;
+    return true;
+}
+
+int simt_gemm_f32(const SimtGemmCall &c_in) {
+    SimtGemmCall c = c_in;
+    {
+        SimtGemmCall d;
+        if (dense_form_of_skipping_call(c_in, &d)) c = d;
+    }
     if (c.M < 0 || c.N < 0 || c.K < 0) return O64_ERR_RANK;
     if (c.M == 0 || c.N == 0) return O64_OK;
     if ((c.N + 31) / 32 > 2147483647LL || (c.M + 31) / 32 > 65535LL) return O64_ERR_RANK;

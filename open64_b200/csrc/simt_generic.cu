@@ -9,6 +9,7 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
@@ -192,6 +193,100 @@ dense_f64_kernel(long long Mr, long long Nr, long long K, double alpha, const do
     }
 }
 
+// The same product on the fp64 tensor path (mma.sync m8n8k4: the only tensor instruction for REAL*8; tcgen05
+// has no 64-bit kind).  64 x 64 tiles, eight warps of 32 x 16, strips of 16 in a three-deep ring.  Each
+// instruction adds a0 b0 + ... + a3 b3 to its 8 x 8 block: 8 multiply-adds per thread for two values read
+// from shared memory, against 16 for 6 in the kernel above.  Shared-memory pitches put the eight rows of an
+// A fragment (4 doubles each) and the four rows of a B fragment (8 doubles each) on distinct banks.
+constexpr int kF64MmaBK = 16, kF64MmaStages = 3, kF64MmaAPitch = kF64MmaBK + 4, kF64MmaBPitch = 64 + 4;
+constexpr int kF64MmaSmemBytes = kF64MmaStages * (64 * kF64MmaAPitch + kF64MmaBK * kF64MmaBPitch) * 8;
+
+__global__ void __launch_bounds__(256)
+dense_f64_mma_kernel(long long Mr, long long Nr, long long K, double alpha, const double *__restrict__ X, long long ldx,
+                     const double *__restrict__ W, long long ldw, double beta, double *__restrict__ Y, long long ldy) {
+    constexpr int BM = 64, BN = 64, BK = kF64MmaBK, STAGES = kF64MmaStages, AP = kF64MmaAPitch, BP = kF64MmaBPitch;
+    extern __shared__ __align__(16) double smem_f64[];
+    double(*As)[BM][AP] = reinterpret_cast<double(*)[BM][AP]>(smem_f64);
+    double(*Bs)[BK][BP] = reinterpret_cast<double(*)[BK][BP]>(smem_f64 + STAGES * BM * AP);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = warp >> 2, wn = warp & 3;     // 2 x 4 warps, 32 x 16 each
+    const int fr = lane >> 2, fc = lane & 3;     // fragment coordinates of this lane
+    const long long m0 = (long long)blockIdx.y * BM, n0 = (long long)blockIdx.x * BN;
+    const long long strips = (K + BK - 1) / BK;
+
+    auto fetch = [&](long long strip, int buf) {
+        const long long k0 = strip * BK;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {  // X: 64 rows x 8 pairs of K
+            const int e = tid + r * 256;
+            const int m = e >> 3, kp = (e & 7) * 2;
+            const long long gm = m0 + m, gk = k0 + kp;
+            const bool ok = gm < Mr && gk < K;
+            cp_async_16_g(&As[buf][m][kp], ok ? X + gm * ldx + gk : X, ok ? 16 : 0);
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {  // W: 16 rows of K x 32 pairs of Nr
+            const int e = tid + r * 256;
+            const int k = e >> 5, np = (e & 31) * 2;
+            const long long gk = k0 + k, gn = n0 + np;
+            const bool ok = gk < K && gn < Nr;
+            cp_async_16_g(&Bs[buf][k][np], ok ? W + gk * ldw + gn : W, ok ? 16 : 0);
+        }
+    };
+
+    double acc[4][2][2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
+#pragma unroll
+    for (int st = 0; st < STAGES - 1; ++st) {
+        if (st < strips) fetch(st, st);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (long long strip = 0; strip < strips; ++strip) {
+        const int buf = (int)(strip % STAGES);
+        asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+        __syncthreads();
+        if (strip + STAGES - 1 < strips) fetch(strip + STAGES - 1, (int)((strip + STAGES - 1) % STAGES));
+        asm volatile("cp.async.commit_group;" ::: "memory");
+#pragma unroll
+        for (int k4 = 0; k4 < BK; k4 += 4) {  // ascending k, four at a time
+            double a[4], b[2];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[buf][wm * 32 + i * 8 + fr][k4 + fc];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) b[j] = Bs[buf][k4 + fc][wn * 16 + j * 8 + fr];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+                    asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
+                                 : "+d"(acc[i][j][0]), "+d"(acc[i][j][1])
+                                 : "d"(a[i]), "d"(b[j]));
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const long long gm = m0 + wm * 32 + i * 8 + fr;
+        if (gm >= Mr) continue;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const long long gn = n0 + wn * 16 + j * 8 + fc * 2;
+            if (gn >= Nr) continue;  // Nr is even: a pair is inside or outside as a whole
+            double *dst = Y + gm * ldy + gn;
+            double2 v = make_double2(alpha * acc[i][j][0], alpha * acc[i][j][1]);
+            if (beta != 0.0) {
+                const double2 o = *reinterpret_cast<const double2 *>(dst);
+                v.x += beta * o.x;
+                v.y += beta * o.y;
+            }
+            *reinterpret_cast<double2 *>(dst) = v;
+        }
+    }
+}
+
 // sets *flag when any element of the rows x cols matrix (cols contiguous, pitch ld) is an infinity or a NaN
 __global__ void nonfinite_f64_kernel(const double *p, long long rows, long long cols, long long ld, int *flag) {
     bool bad = false;
@@ -243,10 +338,20 @@ static int try_dense_f64(int64_t M, int64_t N, int64_t K, double alpha, const do
         cudaStreamSynchronize(s) != cudaSuccess)
         return O64_ERR_CUDA;
     if (bad) return O64_OK;  // the general kernel keeps the rule about zero factors
-    // (128 x 64 tiles with 8 x 4 register blocks were measured too: 16.0 TFLOP/s at 2048^3 against 17.8 for
-    // these - fewer CTAs per SM cover the load latency less well)
     dim3 grid((unsigned)((Nr + 63) / 64), (unsigned)((Mr + 63) / 64));
-    dense_f64_kernel<4><<<grid, 256, 0, s>>>(Mr, Nr, K, alpha, X, ldx, W, ldw, beta, Y, ldy);
+    static const int mma_env = [] { const char *e = getenv("O64_F64_MMA"); return e ? atoi(e) : 1; }();
+    static bool mma_ready[64] = {false};  // the larger dynamic shared memory is allowed per device
+    if (mma_env && !mma_ready[dev])
+        mma_ready[dev] = cudaFuncSetAttribute(dense_f64_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              kF64MmaSmemBytes) == cudaSuccess;
+    if (mma_env && mma_ready[dev]) {
+        dense_f64_mma_kernel<<<grid, 256, kF64MmaSmemBytes, s>>>(Mr, Nr, K, alpha, X, ldx, W, ldw, beta, Y, ldy);
+    } else {
+        // (128 x 64 tiles with 8 x 4 register blocks were measured too: 16.0 TFLOP/s at 2048^3 against 17.8 for
+        // these - fewer CTAs per SM cover the load latency less well)
+        (void)cudaGetLastError();
+        dense_f64_kernel<4><<<grid, 256, 0, s>>>(Mr, Nr, K, alpha, X, ldx, W, ldw, beta, Y, ldy);
+    }
     *done = true;
     return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;
 }

@@ -218,14 +218,15 @@ def test_matmul_entry_points(eng, ka, kb):
     assert eng.lib.o64_compat_last_status() == o.ERR_CONFORM
 
 
+@pytest.mark.parametrize("shape", [(200, 136, 96), (70, 66, 94), (64, 64, 16), (2, 2, 2), (130, 258, 1030)])
 @pytest.mark.parametrize("layout", ["column-major", "row-major"])
-def test_real8_dense_path_and_its_exceptions(eng, layout):
+def test_real8_dense_path_and_its_exceptions(eng, layout, shape):
     """REAL*8 on plainly laid out operands runs a blocked kernel of its own; the rule of the runtime's
     template that a zero factor of B leaves its term out (osprey/libfi/matrix/xgemmx.h:227) still holds when
     A carries an infinity: the result is what the general kernel gives."""
     import torch
     dev = torch.device("cuda", eng.device)
-    M, N, K = 200, 136, 96
+    M, N, K = shape
     g = torch.Generator().manual_seed(123)
     a = torch.rand((M, K), generator=g, dtype=torch.float64) - 0.5      # mathematical A(i,l)
     b = torch.rand((K, N), generator=g, dtype=torch.float64) - 0.5
@@ -245,11 +246,11 @@ def test_real8_dense_path_and_its_exceptions(eng, layout):
     assert ((got - want).abs().max() / want.abs().max()).item() <= 1e-12
     # an infinity in A whose partner in B is zero: the term is left out, the row stays finite
     a2, b2 = a.clone(), b.clone()
-    a2[7, 5] = float("inf")
-    b2[5, :] = 0.0
+    a2[M // 3, K // 2] = float("inf")
+    b2[K // 2, :] = 0.0
     got2 = run(a2, b2)
     a_fin = a2.clone()
-    a_fin[7, 5] = 0.0
+    a_fin[M // 3, K // 2] = 0.0
     want2 = 1.5 * (a_fin @ b2) + 0.5 * c0
     assert torch.isfinite(got2).all()
     assert ((got2 - want2).abs().max() / want2.abs().max()).item() <= 1e-12

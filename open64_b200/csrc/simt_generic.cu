@@ -198,40 +198,55 @@ dense_f64_kernel(long long Mr, long long Nr, long long K, double alpha, const do
 // instruction adds a0 b0 + ... + a3 b3 to its 8 x 8 block: 8 multiply-adds per thread for two values read
 // from shared memory, against 16 for 6 in the kernel above.  Shared-memory pitches put the eight rows of an
 // A fragment (4 doubles each) and the four rows of a B fragment (8 doubles each) on distinct banks.
-constexpr int kF64MmaBK = 16, kF64MmaStages = 3, kF64MmaAPitch = kF64MmaBK + 4, kF64MmaBPitch = 64 + 4;
-constexpr int kF64MmaSmemBytes = kF64MmaStages * (64 * kF64MmaAPitch + kF64MmaBK * kF64MmaBPitch) * 8;
+constexpr int kF64MmaBK = 16, kF64MmaStages = 3, kF64MmaKPitch = kF64MmaBK + 4, kF64MmaNPitch = 64 + 4;
+constexpr int kF64MmaTile = 64 * kF64MmaKPitch;  // doubles per operand tile and stage (>= 16 * kF64MmaNPitch)
+constexpr int kF64MmaSmemBytes = kF64MmaStages * 2 * kF64MmaTile * 8;
+static_assert(kF64MmaTile >= kF64MmaBK * kF64MmaNPitch, "an operand tile fits either way round");
 
+// X_MFAST: X is stored with its rows (not K) contiguous, X(m,k) at X[k*ldx + m] - a transposed first operand;
+// W_KFAST: W is stored with K (not its columns) contiguous, W(k,n) at W[n*ldw + k] - a transposed second one.
+// In shared memory a tile keeps the operand's own orientation ([64][K strip] or [K strip][64]); the
+// fragments are read accordingly, and both orientations are free of bank conflicts with these pitches.
+template <bool X_MFAST, bool W_KFAST>
 __global__ void __launch_bounds__(256)
 dense_f64_mma_kernel(long long Mr, long long Nr, long long K, double alpha, const double *__restrict__ X, long long ldx,
                      const double *__restrict__ W, long long ldw, double beta, double *__restrict__ Y, long long ldy) {
-    constexpr int BM = 64, BN = 64, BK = kF64MmaBK, STAGES = kF64MmaStages, AP = kF64MmaAPitch, BP = kF64MmaBPitch;
+    constexpr int BM = 64, BN = 64, BK = kF64MmaBK, STAGES = kF64MmaStages, KP = kF64MmaKPitch, NP = kF64MmaNPitch;
     extern __shared__ __align__(16) double smem_f64[];
-    double(*As)[BM][AP] = reinterpret_cast<double(*)[BM][AP]>(smem_f64);
-    double(*Bs)[BK][BP] = reinterpret_cast<double(*)[BK][BP]>(smem_f64 + STAGES * BM * AP);
+    double *const xs = smem_f64, *const ws = smem_f64 + STAGES * kF64MmaTile;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wm = warp >> 2, wn = warp & 3;     // 2 x 4 warps, 32 x 16 each
     const int fr = lane >> 2, fc = lane & 3;     // fragment coordinates of this lane
     const long long m0 = (long long)blockIdx.y * BM, n0 = (long long)blockIdx.x * BN;
     const long long strips = (K + BK - 1) / BK;
 
-    auto fetch = [&](long long strip, int buf) {
-        const long long k0 = strip * BK;
+    // a 64 x 16 tile of an operand whose K runs contiguously: [64][KP]; one whose other index does: [16][NP]
+    auto fetch_kfast = [&](double *dst, const double *src, long long ld, long long r0, long long rows, long long k0) {
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {  // X: 64 rows x 8 pairs of K
+        for (int r = 0; r < 2; ++r) {
             const int e = tid + r * 256;
             const int m = e >> 3, kp = (e & 7) * 2;
-            const long long gm = m0 + m, gk = k0 + kp;
-            const bool ok = gm < Mr && gk < K;
-            cp_async_16_g(&As[buf][m][kp], ok ? X + gm * ldx + gk : X, ok ? 16 : 0);
+            const long long gm = r0 + m, gk = k0 + kp;
+            const bool ok = gm < rows && gk < K;  // K is even: a pair is inside or outside as a whole
+            cp_async_16_g(dst + m * KP + kp, ok ? src + gm * ld + gk : src, ok ? 16 : 0);
         }
+    };
+    auto fetch_other = [&](double *dst, const double *src, long long ld, long long c0, long long cols, long long k0) {
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {  // W: 16 rows of K x 32 pairs of Nr
+        for (int r = 0; r < 2; ++r) {
             const int e = tid + r * 256;
             const int k = e >> 5, np = (e & 31) * 2;
-            const long long gk = k0 + k, gn = n0 + np;
-            const bool ok = gk < K && gn < Nr;
-            cp_async_16_g(&Bs[buf][k][np], ok ? W + gk * ldw + gn : W, ok ? 16 : 0);
+            const long long gk = k0 + k, gn = c0 + np;
+            const bool ok = gk < K && gn < cols;  // the extent is even
+            cp_async_16_g(dst + k * NP + np, ok ? src + gk * ld + gn : src, ok ? 16 : 0);
         }
+    };
+    auto fetch = [&](long long strip, int buf) {
+        const long long k0 = strip * BK;
+        if constexpr (X_MFAST) fetch_other(xs + buf * kF64MmaTile, X, ldx, m0, Mr, k0);
+        else fetch_kfast(xs + buf * kF64MmaTile, X, ldx, m0, Mr, k0);
+        if constexpr (W_KFAST) fetch_kfast(ws + buf * kF64MmaTile, W, ldw, n0, Nr, k0);
+        else fetch_other(ws + buf * kF64MmaTile, W, ldw, n0, Nr, k0);
     };
 
     double acc[4][2][2];
@@ -250,13 +265,20 @@ dense_f64_mma_kernel(long long Mr, long long Nr, long long K, double alpha, cons
         __syncthreads();
         if (strip + STAGES - 1 < strips) fetch(strip + STAGES - 1, (int)((strip + STAGES - 1) % STAGES));
         asm volatile("cp.async.commit_group;" ::: "memory");
+        const double *xt = xs + buf * kF64MmaTile, *wt = ws + buf * kF64MmaTile;
 #pragma unroll
         for (int k4 = 0; k4 < BK; k4 += 4) {  // ascending k, four at a time
             double a[4], b[2];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) a[i] = As[buf][wm * 32 + i * 8 + fr][k4 + fc];
+            for (int i = 0; i < 4; ++i) {
+                const int m = wm * 32 + i * 8 + fr, k = k4 + fc;
+                a[i] = X_MFAST ? xt[k * NP + m] : xt[m * KP + k];
+            }
 #pragma unroll
-            for (int j = 0; j < 2; ++j) b[j] = Bs[buf][k4 + fc][wn * 16 + j * 8 + fr];
+            for (int j = 0; j < 2; ++j) {
+                const int n = wn * 16 + j * 8 + fr, k = k4 + fc;
+                b[j] = W_KFAST ? wt[n * KP + k] : wt[k * NP + n];
+            }
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -297,28 +319,35 @@ __global__ void nonfinite_f64_kernel(const double *p, long long rows, long long 
     if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicExch(flag, 1);
 }
 
-// The dense REAL*8 path, if the call has its shape; *done says whether it ran.
+// The dense REAL*8 path, if the call has its shape; *done says whether it ran.  The shape: every matrix
+// has one index with unit stride.  The result is taken row-major (its unit-stride index as columns; a
+// column-major C = A B is C' = B' A'), the operands may each lie either way round.
 static int try_dense_f64(int64_t M, int64_t N, int64_t K, double alpha, const double *A, int64_t a1, int64_t a2, const double *B,
                          int64_t b1, int64_t b2, double beta, double *C, int64_t c1, int64_t c2, cudaStream_t s, bool *done) {
     *done = false;
     if (K <= 0) return O64_OK;
+    if ((a1 != 1 && a2 != 1) || (b1 != 1 && b2 != 1) || (c1 != 1 && c2 != 1)) return O64_OK;
     const double *X, *W;
     double *Y = C;
     int64_t Mr, Nr, ldx, ldw, ldy;
-    const double *other;  // the operand whose infinities or NaNs a skipped zero term would have hidden
-    int64_t o_rows, o_cols, o_ld;
-    if (a2 == 1 && b2 == 1 && c2 == 1) {          // row-major: C[i][j], A[i][l], B[l][j]
-        X = A, ldx = a1, W = B, ldw = b1, ldy = c1, Mr = M, Nr = N;
-        other = A, o_rows = M, o_cols = K, o_ld = a1;
-    } else if (a1 == 1 && b1 == 1 && c1 == 1) {   // column-major: C' = B' A'
-        X = B, ldx = b2, W = A, ldw = a2, ldy = c2, Mr = N, Nr = M;
-        other = A, o_rows = K, o_cols = M, o_ld = a2;
-    } else {
-        return O64_OK;
+    bool x_mfast, w_kfast;
+    if (c2 == 1) {  // Y = C: rows i, columns j
+        Mr = M, Nr = N, ldy = c1;
+        X = A, x_mfast = (a2 != 1), ldx = x_mfast ? a2 : a1;  // X(i,l) = A(i,l)
+        W = B, w_kfast = (b2 != 1), ldw = w_kfast ? b2 : b1;  // W(l,j) = B(l,j)
+    } else {        // Y = C': rows j, columns i
+        Mr = N, Nr = M, ldy = c2;
+        X = B, x_mfast = (b1 != 1), ldx = x_mfast ? b1 : b2;  // X(j,l) = B(l,j): K contiguous when b1 == 1
+        W = A, w_kfast = (a1 != 1), ldw = w_kfast ? a1 : a2;  // W(l,i) = A(i,l): i contiguous when a1 == 1
     }
+    // the operand whose infinities or NaNs a skipped zero term would have hidden: A, as it lies in memory
+    const double *other = A;
+    const int64_t o_rows = (a2 == 1) ? M : K, o_cols = (a2 == 1) ? K : M, o_ld = (a2 == 1) ? a1 : a2;
     auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
-    if ((K & 1) || (Nr & 1) || (ldx & 1) || (ldw & 1) || (ldy & 1) || ldx < K || ldw < Nr || ldy < Nr || !al16(X) || !al16(W) ||
-        !al16(Y) || (Mr + 63) / 64 > 65535)
+    // 16-byte copies: the contiguous extent of every tile is even, pitches are even, bases aligned
+    const int64_t x_run = x_mfast ? Mr : K, w_run = w_kfast ? K : Nr;
+    if ((K & 1) || (Nr & 1) || (x_run & 1) || (ldx & 1) || (ldw & 1) || (ldy & 1) || ldx < x_run || ldw < w_run || ldy < Nr ||
+        !al16(X) || !al16(W) || !al16(Y) || (Mr + 63) / 64 > 65535)
         return O64_OK;
     static int *flags[64] = {nullptr};  // one word per device, allocated on first use
     int dev = 0;
@@ -341,16 +370,30 @@ static int try_dense_f64(int64_t M, int64_t N, int64_t K, double alpha, const do
     dim3 grid((unsigned)((Nr + 63) / 64), (unsigned)((Mr + 63) / 64));
     static const int mma_env = [] { const char *e = getenv("O64_F64_MMA"); return e ? atoi(e) : 1; }();
     static bool mma_ready[64] = {false};  // the larger dynamic shared memory is allowed per device
-    if (mma_env && !mma_ready[dev])
-        mma_ready[dev] = cudaFuncSetAttribute(dense_f64_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              kF64MmaSmemBytes) == cudaSuccess;
+    if (mma_env && !mma_ready[dev]) {
+        bool ok = true;
+        ok &= cudaFuncSetAttribute(dense_f64_mma_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kF64MmaSmemBytes) == cudaSuccess;
+        ok &= cudaFuncSetAttribute(dense_f64_mma_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kF64MmaSmemBytes) == cudaSuccess;
+        ok &= cudaFuncSetAttribute(dense_f64_mma_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kF64MmaSmemBytes) == cudaSuccess;
+        ok &= cudaFuncSetAttribute(dense_f64_mma_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kF64MmaSmemBytes) == cudaSuccess;
+        mma_ready[dev] = ok;
+        if (!ok) (void)cudaGetLastError();
+    }
     if (mma_env && mma_ready[dev]) {
-        dense_f64_mma_kernel<<<grid, 256, kF64MmaSmemBytes, s>>>(Mr, Nr, K, alpha, X, ldx, W, ldw, beta, Y, ldy);
-    } else {
+        if (x_mfast && w_kfast)
+            dense_f64_mma_kernel<true, true><<<grid, 256, kF64MmaSmemBytes, s>>>(Mr, Nr, K, alpha, X, ldx, W, ldw, beta, Y, ldy);
+        else if (x_mfast)
+            dense_f64_mma_kernel<true, false><<<grid, 256, kF64MmaSmemBytes, s>>>(Mr, Nr, K, alpha, X, ldx, W, ldw, beta, Y, ldy);
+        else if (w_kfast)
+            dense_f64_mma_kernel<false, true><<<grid, 256, kF64MmaSmemBytes, s>>>(Mr, Nr, K, alpha, X, ldx, W, ldw, beta, Y, ldy);
+        else
+            dense_f64_mma_kernel<false, false><<<grid, 256, kF64MmaSmemBytes, s>>>(Mr, Nr, K, alpha, X, ldx, W, ldw, beta, Y, ldy);
+    } else if (!x_mfast && !w_kfast) {
         // (128 x 64 tiles with 8 x 4 register blocks were measured too: 16.0 TFLOP/s at 2048^3 against 17.8 for
         // these - fewer CTAs per SM cover the load latency less well)
-        (void)cudaGetLastError();
         dense_f64_kernel<4><<<grid, 256, 0, s>>>(Mr, Nr, K, alpha, X, ldx, W, ldw, beta, Y, ldy);
+    } else {
+        return O64_OK;  // transposed operands without the tensor path: the general kernel
     }
     *done = true;
     return cudaGetLastError() == cudaSuccess ? O64_OK : O64_ERR_CUDA;

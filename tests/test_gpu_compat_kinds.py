@@ -219,7 +219,8 @@ def test_matmul_entry_points(eng, ka, kb):
 
 
 @pytest.mark.parametrize("shape", [(200, 136, 96), (70, 66, 94), (64, 64, 16), (2, 2, 2), (130, 258, 1030)])
-@pytest.mark.parametrize("layout", ["column-major", "row-major"])
+@pytest.mark.parametrize("layout", ["column-major", "row-major", "row-major, A transposed", "row-major, B transposed",
+                                    "row-major, both transposed", "column-major, both transposed"])
 def test_real8_dense_path_and_its_exceptions(eng, layout, shape):
     """REAL*8 on plainly laid out operands runs a blocked kernel of its own; the rule of the runtime's
     template that a zero factor of B leaves its term out (osprey/libfi/matrix/xgemmx.h:227) still holds when
@@ -237,8 +238,17 @@ def test_real8_dense_path_and_its_exceptions(eng, layout, shape):
             A, B, C = a_math.t().contiguous().to(dev), b_math.t().contiguous().to(dev), c0.t().contiguous().to(dev)
             eng.xgemmx("s", M, N, K, 1.5, A, 1, M, B, 1, K, 0.5, C, 1, M)
             return C.t().cpu()
-        A, B, C = a_math.contiguous().to(dev), b_math.contiguous().to(dev), c0.clone().to(dev)
-        eng.xgemmx("s", M, N, K, 1.5, A, K, 1, B, N, 1, 0.5, C, N, 1)
+        if layout == "column-major, both transposed":   # A held as its transpose [M][K] rows contiguous, B likewise
+            A, B, C = a_math.contiguous().to(dev), b_math.contiguous().to(dev), c0.t().contiguous().to(dev)
+            eng.xgemmx("s", M, N, K, 1.5, A, K, 1, B, N, 1, 0.5, C, 1, M)
+            return C.t().cpu()
+        C = c0.clone().to(dev)
+        ta, tb = "A transposed" in layout or "both" in layout, "B transposed" in layout or "both" in layout
+        A = (a_math.t().contiguous() if ta else a_math.contiguous()).to(dev)     # [K][M] when transposed
+        B = (b_math.t().contiguous() if tb else b_math.contiguous()).to(dev)     # [N][K] when transposed
+        a1, a2 = (1, M) if ta else (K, 1)
+        b1, b2 = (1, K) if tb else (N, 1)
+        eng.xgemmx("s", M, N, K, 1.5, A, a1, a2, B, b1, b2, 0.5, C, N, 1)
         return C.cpu()
 
     want = 1.5 * (a @ b) + 0.5 * c0
